@@ -1,0 +1,608 @@
+/*
+ * ggb_oracle.c -- CPU restatement of ggnpu's CPU arithmetic for the Backend
+ * operator path.  TEST INFRASTRUCTURE ONLY: it is the checker the CUDA kernels
+ * are compared against, never a product path and never a fallback.
+ *
+ * Every function names the reference file:line (paths relative to the ggnpu
+ * tree) whose arithmetic, operation order and rounding it restates.  Parity is
+ * pinned: tests compare this file bit-for-bit with the reference's own
+ * functions compiled from the reference tree (oracle/_ref) and with the golden
+ * vectors of the reference's tests/test_quant.cpp and tests/test_arch.cpp.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fno-fast-math (see oracle/Makefile); the
+ * reference is built -O3 for baseline x86-64 (no FMA, no reassociation), so a
+ * sequential float loop here rounds exactly like the reference's.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define GGO_API __attribute__((visibility("default")))
+
+/* ggml type ids, include/ggnpu/tensor.h:11-42 */
+enum {
+    GGO_F32 = 0, GGO_F16 = 1, GGO_Q4_0 = 2, GGO_Q4_1 = 3, GGO_Q8_0 = 8,
+    GGO_Q2_K = 10, GGO_Q3_K = 11, GGO_Q4_K = 12, GGO_Q5_K = 13, GGO_Q6_K = 14,
+    GGO_IQ4_NL = 20, GGO_IQ4_XS = 23, GGO_BF16 = 30
+};
+
+/* ---- scalar conversions ------------------------------------------------- */
+
+/* include/ggnpu/quant/kquant.h:30-53 and src/utils/bf16.cpp:22-46 (both give
+ * the exact IEEE widening, subnormals included). */
+GGO_API float ggo_f16_to_f32(uint16_t h) {
+    uint32_t s = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 31u, m = h & 1023u, u;
+    if (e == 31u) u = s | 0x7F800000u | (m << 13);
+    else if (e) u = s | ((e + 112u) << 23) | (m << 13);
+    else if (!m) u = s;
+    else {
+        int sh = 0;
+        while (!(m & 1024u)) { m <<= 1; ++sh; }
+        u = s | ((uint32_t)(113 - sh) << 23) | ((m & 1023u) << 13);
+    }
+    float f; memcpy(&f, &u, 4); return f;
+}
+
+/* src/utils/bf16.cpp:15-20 */
+GGO_API float ggo_bf16_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f;
+}
+
+/* src/utils/bf16.cpp:6-13: round-to-nearest-even by bias add, no NaN case. */
+GGO_API uint16_t ggo_f32_to_bf16(float f) {
+    uint32_t u; memcpy(&u, &f, 4);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+static inline float rd_f16(const uint8_t* p) { return ggo_f16_to_f32((uint16_t)(p[0] | (p[1] << 8))); }
+
+/* ---- block geometry: src/gguf/tensor.cpp:18-38 --------------------------- */
+
+GGO_API int ggo_block_elems(uint32_t t) {
+    switch (t) {
+    case GGO_F32: case GGO_F16: case GGO_BF16: return 1;
+    case GGO_Q4_0: case GGO_Q4_1: case GGO_Q8_0: case GGO_IQ4_NL: return 32;
+    case GGO_Q2_K: case GGO_Q3_K: case GGO_Q4_K: case GGO_Q5_K: case GGO_Q6_K: case GGO_IQ4_XS: return 256;
+    default: return 0;
+    }
+}
+
+GGO_API int ggo_block_bytes(uint32_t t) {
+    switch (t) {
+    case GGO_F32: return 4; case GGO_F16: case GGO_BF16: return 2;
+    case GGO_Q4_0: return 18; case GGO_Q4_1: return 20; case GGO_Q8_0: return 34;
+    case GGO_Q2_K: return 84; case GGO_Q3_K: return 110; case GGO_Q4_K: return 144;
+    case GGO_Q5_K: return 176; case GGO_Q6_K: return 210;
+    case GGO_IQ4_NL: return 18; case GGO_IQ4_XS: return 136;
+    default: return 0;
+    }
+}
+
+/* ---- block decoders ------------------------------------------------------ */
+
+/* src/quant/iq4_nl.cpp:16-18 (same table in src/quant/iq4_xs.cpp:14-16) */
+static const int8_t kIq4Codebook[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* src/quant/q4_0.cpp:18-26: (nibble-8)*d, int first then one float multiply. */
+static void dq_q4_0(const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    for (int j = 0; j < 16; ++j) {
+        y[j] = (float)((int)(b[2 + j] & 15) - 8) * d;
+        y[j + 16] = (float)((int)(b[2 + j] >> 4) - 8) * d;
+    }
+}
+
+/* src/quant/q4_1.cpp:20-29: nibble*d + m (product then add, two roundings). */
+static void dq_q4_1(const uint8_t* b, float* y) {
+    const float d = rd_f16(b), m = rd_f16(b + 2);
+    for (int j = 0; j < 16; ++j) {
+        y[j] = (float)(int)(b[4 + j] & 15) * d + m;
+        y[j + 16] = (float)(int)(b[4 + j] >> 4) * d + m;
+    }
+}
+
+/* src/quant/q8_0.cpp:19-25 */
+static void dq_q8_0(const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    for (int j = 0; j < 32; ++j) y[j] = (float)(int8_t)b[2 + j] * d;
+}
+
+/* src/quant/iq4_nl.cpp:24-31 */
+static void dq_iq4_nl(const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    for (int j = 0; j < 16; ++j) {
+        y[j] = d * (float)kIq4Codebook[b[2 + j] & 15];
+        y[j + 16] = d * (float)kIq4Codebook[b[2 + j] >> 4];
+    }
+}
+
+/* src/quant/iq4_xs.cpp:21-39: 8 sub-blocks of 32; 6-bit scale = 4 low bits
+ * from scales_l, 2 high bits from the u16 scales_h; dl = d*(ls-32). */
+static void dq_iq4_xs(const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    const unsigned sh = (unsigned)(b[2] | (b[3] << 8));
+    for (int ib = 0; ib < 8; ++ib) {
+        const int ls = (int)((b[4 + ib / 2] >> (4 * (ib & 1))) & 15) | (int)(((sh >> (2 * ib)) & 3u) << 4);
+        const float dl = d * (float)(ls - 32);
+        const uint8_t* q = b + 8 + 16 * ib;
+        for (int j = 0; j < 16; ++j) {
+            y[32 * ib + j] = dl * (float)kIq4Codebook[q[j] & 15];
+            y[32 * ib + j + 16] = dl * (float)kIq4Codebook[q[j] >> 4];
+        }
+    }
+}
+
+/* include/ggnpu/quant/kquant.h:56-64: 6-bit (scale, min) pair j of a 12-byte pack. */
+static void k4_scale_min(int j, const uint8_t* p, int* sc, int* mn) {
+    if (j < 4) { *sc = p[j] & 63; *mn = p[j + 4] & 63; }
+    else { *sc = (p[j + 4] & 15) | ((p[j - 4] >> 6) << 4); *mn = (p[j + 4] >> 4) | ((p[j] >> 6) << 4); }
+}
+
+/* include/ggnpu/quant/kquant.h:70-91: dl = d*(sc&15), ml = dmin*(sc>>4),
+ * y = dl*q - ml; sub-blocks of 16, two per shift step, 128 values per half. */
+static void dq_q2_k(const uint8_t* b, float* y) {
+    const float d = rd_f16(b + 80), dmin = rd_f16(b + 82);
+    for (int sb = 0; sb < 16; ++sb) {          /* sub-block sb covers y[16*sb .. 16*sb+15] */
+        const int half = sb >> 3, j = (sb >> 1) & 3, odd = sb & 1;
+        const uint8_t s = b[sb];
+        const float dl = d * (float)(s & 15), ml = dmin * (float)(s >> 4);
+        const uint8_t* q = b + 16 + 32 * half + 16 * odd;
+        for (int l = 0; l < 16; ++l) y[16 * sb + l] = dl * (float)((q[l] >> (2 * j)) & 3) - ml;
+    }
+}
+
+/* include/ggnpu/quant/kquant.h:96-130: 16 signed 6-bit scales rebuilt from
+ * 12 bytes; value = dl * (q2 - (hmask bit ? 0 : 4)), dl = d*(scale-32). */
+static void dq_q3_k(const uint8_t* b, float* y) {
+    const float d = rd_f16(b + 108);
+    const uint8_t* s = b + 96;
+    for (int sb = 0; sb < 16; ++sb) {
+        /* scale sb: low 4 bits from bytes 0..7 (nibble), high 2 bits from bytes 8..11 */
+        const int lo = (sb < 8) ? (s[sb] & 15) : (s[sb - 8] >> 4);
+        const int hi = (s[8 + (sb & 3)] >> (2 * (sb >> 2))) & 3;
+        const float dl = d * (float)((int)(int8_t)(lo | (hi << 4)) - 32);
+        const int half = sb >> 3, j = (sb >> 1) & 3, odd = sb & 1;
+        const uint8_t* q = b + 32 + 32 * half + 16 * odd;
+        const uint8_t* hm = b + 16 * odd;
+        const uint8_t mbit = (uint8_t)(1u << (4 * half + j));
+        for (int l = 0; l < 16; ++l)
+            y[16 * sb + l] = dl * (float)((int)((q[l] >> (2 * j)) & 3) - ((hm[l] & mbit) ? 0 : 4));
+    }
+}
+
+/* include/ggnpu/quant/kquant.h:133-151 */
+static void dq_q4_k(const uint8_t* b, float* y) {
+    const float d = rd_f16(b), dmin = rd_f16(b + 2);
+    for (int g = 0; g < 4; ++g) {
+        int s1, m1, s2, m2;
+        k4_scale_min(2 * g, b + 4, &s1, &m1);
+        k4_scale_min(2 * g + 1, b + 4, &s2, &m2);
+        const float d1 = d * (float)s1, n1 = dmin * (float)m1, d2 = d * (float)s2, n2 = dmin * (float)m2;
+        const uint8_t* q = b + 16 + 32 * g;
+        for (int l = 0; l < 32; ++l) {
+            y[64 * g + l] = d1 * (float)(q[l] & 15) - n1;
+            y[64 * g + 32 + l] = d2 * (float)(q[l] >> 4) - n2;
+        }
+    }
+}
+
+/* include/ggnpu/quant/kquant.h:157-179 */
+static void dq_q5_k(const uint8_t* b, float* y) {
+    const float d = rd_f16(b), dmin = rd_f16(b + 2);
+    const uint8_t* qh = b + 16;
+    for (int g = 0; g < 4; ++g) {
+        int s1, m1, s2, m2;
+        k4_scale_min(2 * g, b + 4, &s1, &m1);
+        k4_scale_min(2 * g + 1, b + 4, &s2, &m2);
+        const float d1 = d * (float)s1, n1 = dmin * (float)m1, d2 = d * (float)s2, n2 = dmin * (float)m2;
+        const uint8_t* q = b + 48 + 32 * g;
+        for (int l = 0; l < 32; ++l) {
+            y[64 * g + l] = d1 * (float)((q[l] & 15) + (((qh[l] >> (2 * g)) & 1) ? 16 : 0)) - n1;
+            y[64 * g + 32 + l] = d2 * (float)((q[l] >> 4) + (((qh[l] >> (2 * g + 1)) & 1) ? 16 : 0)) - n2;
+        }
+    }
+}
+
+/* include/ggnpu/quant/kquant.h:182-202: y = (d * sc) * q, left to right. */
+static void dq_q6_k(const uint8_t* b, float* y) {
+    const float d = rd_f16(b + 208);
+    for (int h = 0; h < 2; ++h) {
+        const uint8_t* ql = b + 64 * h;
+        const uint8_t* qh = b + 128 + 32 * h;
+        const int8_t* sc = (const int8_t*)(b + 192 + 8 * h);
+        float* o = y + 128 * h;
+        for (int l = 0; l < 32; ++l) {
+            const int is = l >> 4;
+            const int q1 = (int)((ql[l] & 15) | ((qh[l] & 3) << 4)) - 32;
+            const int q2 = (int)((ql[l + 32] & 15) | (((qh[l] >> 2) & 3) << 4)) - 32;
+            const int q3 = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+            const int q4 = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+            o[l] = d * (float)sc[is] * (float)q1;
+            o[l + 32] = d * (float)sc[is + 2] * (float)q2;
+            o[l + 64] = d * (float)sc[is + 4] * (float)q3;
+            o[l + 96] = d * (float)sc[is + 6] * (float)q4;
+        }
+    }
+}
+
+/* One block of any supported type -> fp32.  Returns 0, or -1 for an
+ * unsupported type. */
+GGO_API int ggo_dequant_block(uint32_t type, const uint8_t* blk, float* out) {
+    switch (type) {
+    case GGO_F32: memcpy(out, blk, 4); return 0;
+    case GGO_F16: out[0] = ggo_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))); return 0;
+    case GGO_BF16: out[0] = ggo_bf16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))); return 0;
+    case GGO_Q4_0: dq_q4_0(blk, out); return 0;
+    case GGO_Q4_1: dq_q4_1(blk, out); return 0;
+    case GGO_Q8_0: dq_q8_0(blk, out); return 0;
+    case GGO_Q2_K: dq_q2_k(blk, out); return 0;
+    case GGO_Q3_K: dq_q3_k(blk, out); return 0;
+    case GGO_Q4_K: dq_q4_k(blk, out); return 0;
+    case GGO_Q5_K: dq_q5_k(blk, out); return 0;
+    case GGO_Q6_K: dq_q6_k(blk, out); return 0;
+    case GGO_IQ4_NL: dq_iq4_nl(blk, out); return 0;
+    case GGO_IQ4_XS: dq_iq4_xs(blk, out); return 0;
+    default: return -1;
+    }
+}
+
+GGO_API int ggo_dequant_blocks(uint32_t type, const uint8_t* data, int64_t n_blocks, float* out) {
+    const int be = ggo_block_elems(type), bb = ggo_block_bytes(type);
+    if (!be) return -1;
+    for (int64_t i = 0; i < n_blocks; ++i) ggo_dequant_block(type, data + i * bb, out + i * be);
+    return 0;
+}
+
+/* src/cli/main.cpp:36-261 (dequant_tensor_row): row `row` of a [N rows][K]
+ * weight; a row is ceil(K/blk) consecutive blocks; values past K are dropped. */
+GGO_API int ggo_dequant_row(uint32_t type, const uint8_t* data, int64_t row, int K, float* out) {
+    const int be = ggo_block_elems(type), bb = ggo_block_bytes(type);
+    if (!be || K <= 0) return -1;
+    const int64_t bpr = ((int64_t)K + be - 1) / be;
+    const uint8_t* r = data + row * bpr * bb;
+    float tmp[256];
+    for (int64_t b = 0; b < bpr; ++b) {
+        ggo_dequant_block(type, r + b * bb, tmp);
+        for (int j = 0; j < be; ++j) { const int64_t k = b * be + j; if (k < K) out[k] = tmp[j]; }
+    }
+    return 0;
+}
+
+/* ---- matmul --------------------------------------------------------------- */
+
+/* src/cli/main.cpp:1379-1388 (GGNPU_FP32_MATMUL path, the exact CPU matmul for
+ * every format) and :270-327 compute_logits' CPU branch: dequantise row n,
+ * one running fp32 sum over k in order.  Applied per activation row m. */
+GGO_API int ggo_matmul_exact(const float* A, int M, int lda, const uint8_t* W, uint32_t type,
+                             int N, int K, float* C, int ldc) {
+    float* w = (float*)malloc(sizeof(float) * (size_t)K);
+    if (!w) return -1;
+    for (int n = 0; n < N; ++n) {
+        if (ggo_dequant_row(type, W, n, K, w)) { free(w); return -1; }
+        for (int m = 0; m < M; ++m) {
+            const float* a = A + (size_t)m * lda;
+            float acc = 0.0f;
+            for (int k = 0; k < K; ++k) acc += a[k] * w[k];
+            C[(size_t)m * ldc + n] = acc;
+        }
+    }
+    free(w);
+    return 0;
+}
+
+/* src/backends/cpu_ref/cpu_ref.cpp:87-117 (Q4_K / Q6_K only): one partial sum
+ * per 256-block, added into C in block order.  lda/ldc are ignored (K, N). */
+GGO_API int ggo_matmul_cpu_ref_k(const float* A, int M, const uint8_t* W, uint32_t type,
+                                 int N, int K, float* C) {
+    if (type != GGO_Q4_K && type != GGO_Q6_K) return -1;
+    const int bb = ggo_block_bytes(type);
+    const int64_t bpr = ((int64_t)K + 255) / 256;
+    memset(C, 0, sizeof(float) * (size_t)M * N);
+    float w[256];
+    for (int n = 0; n < N; ++n)
+        for (int64_t b = 0; b < bpr; ++b) {
+            ggo_dequant_block(type, W + ((int64_t)n * bpr + b) * bb, w);
+            for (int m = 0; m < M; ++m) {
+                float s = 0.0f;
+                for (int j = 0; j < 256; ++j) { const int64_t k = b * 256 + j; if (k < K) s += A[(size_t)m * K + k] * w[j]; }
+                C[(size_t)m * N + n] += s;
+            }
+        }
+    return 0;
+}
+
+/* src/backends/cpu_ref/cpu_ref.cpp:119-133: F32 B is [K][N]. */
+GGO_API void ggo_matmul_f32_kn(const float* A, const float* B, float* C, int M, int N, int K) {
+    for (int m = 0; m < M; ++m)
+        for (int n = 0; n < N; ++n) {
+            float s = 0.0f;
+            for (int k = 0; k < K; ++k) s += A[(size_t)m * K + k] * B[(size_t)k * N + n];
+            C[(size_t)m * N + n] = s;
+        }
+}
+
+/* ---- elementwise / norm / attention: src/backends/cpu_ref/cpu_ref.cpp ----- */
+
+/* cpu_ref.cpp:139-156 */
+GGO_API void ggo_rms_norm(const float* x, float* y, int n, float eps, const float* w) {
+    float v = 0.0f;
+    for (int i = 0; i < n; ++i) v += x[i] * x[i];
+    v /= (float)n;
+    v += eps;
+    const float inv = 1.0f / sqrtf(v);
+    for (int i = 0; i < n; ++i) y[i] = x[i] * inv * (w ? w[i] : 1.0f);
+}
+
+/* src/cli/main.cpp:3294-3299 (per-head QK-norm, sum of squares in double) */
+GGO_API void ggo_rms_norm_head_f64(float* v, int n, float eps, const float* w) {
+    double ss = 0.0;
+    for (int i = 0; i < n; ++i) ss += (double)v[i] * v[i];
+    const float inv = 1.0f / sqrtf((float)(ss / n) + eps);
+    for (int i = 0; i < n; ++i) v[i] = v[i] * inv * w[i];
+}
+
+/* cpu_ref.cpp:200-209 */
+GGO_API void ggo_silu(const float* x, float* y, int n) {
+    for (int i = 0; i < n; ++i) y[i] = x[i] / (1.0f + expf(-x[i]));
+}
+
+/* cpu_ref.cpp:211-221 */
+GGO_API void ggo_gelu(const float* x, float* y, int n) {
+    const float k = 0.7978845608f;
+    for (int i = 0; i < n; ++i) y[i] = 0.5f * x[i] * (1.0f + tanhf(k * (x[i] + 0.044715f * x[i] * x[i] * x[i])));
+}
+
+/* cpu_ref.cpp:176-198 */
+GGO_API void ggo_softmax(const float* x, float* y, int rows, int cols) {
+    for (int r = 0; r < rows; ++r) {
+        const float* xi = x + (size_t)r * cols; float* yo = y + (size_t)r * cols;
+        float mx = -INFINITY, s = 0.0f;
+        for (int c = 0; c < cols; ++c) if (xi[c] > mx) mx = xi[c];
+        for (int c = 0; c < cols; ++c) { yo[c] = expf(xi[c] - mx); s += yo[c]; }
+        for (int c = 0; c < cols; ++c) yo[c] /= s;
+    }
+}
+
+/* cpu_ref.cpp:223-280: Q [nh][hd]; K,V [nh][ctx][hd] already GQA-expanded;
+ * keys j > query_pos masked to -inf; scale 1/sqrt(hd); query_pos<0 => ctx-1. */
+GGO_API int ggo_flash_attn(const float* Q, const float* K, const float* V, float* out,
+                           int nh, int hd, int64_t ctx, int64_t qpos) {
+    if (qpos < 0) qpos = ctx - 1;
+    const float scale = 1.0f / sqrtf((float)hd);
+    float* sc = (float*)malloc(sizeof(float) * (size_t)ctx);
+    if (!sc) return -1;
+    for (int h = 0; h < nh; ++h) {
+        const float* q = Q + (size_t)h * hd;
+        const float* k = K + (size_t)h * ctx * hd;
+        const float* v = V + (size_t)h * ctx * hd;
+        float* o = out + (size_t)h * hd;
+        for (int64_t j = 0; j < ctx; ++j) sc[j] = -INFINITY;
+        for (int64_t j = 0; j <= qpos && j < ctx; ++j) {
+            float s = 0.0f;
+            for (int d = 0; d < hd; ++d) s += q[d] * k[j * hd + d];
+            sc[j] = s * scale;
+        }
+        float mx = -INFINITY, sum = 0.0f;
+        for (int64_t j = 0; j < ctx; ++j) if (sc[j] > mx) mx = sc[j];
+        for (int64_t j = 0; j < ctx; ++j) { sc[j] = expf(sc[j] - mx); sum += sc[j]; }
+        for (int64_t j = 0; j < ctx; ++j) sc[j] /= sum;
+        for (int d = 0; d < hd; ++d) o[d] = 0.0f;
+        for (int64_t j = 0; j < ctx; ++j)
+            for (int d = 0; d < hd; ++d) o[d] += sc[j] * v[j * hd + d];
+    }
+    free(sc);
+    return 0;
+}
+
+/* cpu_ref.cpp:158-174: Backend::rope of the CPU backend (base fixed at 10000,
+ * adjacent pairs, angle = offset * 10000^(-i/n_dims) * freq_scale). */
+GGO_API void ggo_rope_cpu_ref(float* x, int n_dims, int64_t offset, float freq_scale, int64_t rope_dims) {
+    for (int64_t i = 0; i < rope_dims; i += 2) {
+        const float ratio = 1.0f / powf(10000.0f, (float)i / (float)n_dims);
+        const float a = (float)offset * ratio * freq_scale;
+        const float c = cosf(a), s = sinf(a), v0 = x[i], v1 = x[i + 1];
+        x[i] = v0 * c - v1 * s;
+        x[i + 1] = v0 * s + v1 * c;
+    }
+}
+
+/* src/cli/main.cpp:665-692 (RopeCache::build): tables [max_pos][n_dims/2],
+ * angle = scale*pos / (base^(2i/n_dims) * ff_i), all in float; ff 0 => 1. */
+GGO_API void ggo_rope_table(int64_t max_pos, int n_dims, float freq_scale, float freq_base,
+                            const float* ff, int n_ff, float* cos_out, float* sin_out) {
+    const int pairs = n_dims / 2;
+    for (int64_t p = 0; p < max_pos; ++p)
+        for (int i = 0; i < pairs; ++i) {
+            float f = (ff && i < n_ff) ? ff[i] : 1.0f;
+            if (f == 0.0f) f = 1.0f;
+            const float wl = powf(freq_base, 2.0f * (float)i / (float)n_dims);
+            const float a = freq_scale * (float)p / (wl * f);
+            cos_out[p * pairs + i] = cosf(a);
+            sin_out[p * pairs + i] = sinf(a);
+        }
+}
+
+/* src/cli/main.cpp:1294-1308 (adjacent pairs; neox=0) and :3328-3341 (NeoX
+ * split-half; neox=1), both from the table row of position `pos`.
+ * rot_dims <= head_dim rotates only the leading dims (main.cpp:906-920). */
+GGO_API void ggo_rope_apply(float* out, const float* in, int n_heads, int head_dim, int rot_dims,
+                            const float* cos_row, const float* sin_row, int neox) {
+    const int half = rot_dims / 2;
+    for (int h = 0; h < n_heads; ++h) {
+        const float* ih = in + (size_t)h * head_dim; float* oh = out + (size_t)h * head_dim;
+        if (out != in) for (int i = rot_dims; i < head_dim; ++i) oh[i] = ih[i];
+        for (int i = 0; i < half; ++i) {
+            const float c = cos_row[i], s = sin_row[i];
+            const int i0 = neox ? i : 2 * i, i1 = neox ? i + half : 2 * i + 1;
+            const float v0 = ih[i0], v1 = ih[i1];
+            oh[i0] = v0 * c - v1 * s;
+            oh[i1] = v0 * s + v1 * c;
+        }
+    }
+}
+
+/* src/cli/main.cpp:827-838: greedy = first index whose logit is strictly greater. */
+GGO_API int ggo_argmax_first(const float* x, int n) {
+    int best = 0; float bv = -INFINITY;
+    for (int i = 0; i < n; ++i) if (x[i] > bv) { bv = x[i]; best = i; }
+    return best;
+}
+
+/* ---- generic (llama / qwen2 / qwen3) forward: src/cli/main.cpp:2367-2375,
+ * 3235-3512, 3593-3599 ------------------------------------------------------ */
+
+typedef struct { const uint8_t* data; uint32_t type; } ggo_weight;
+
+typedef struct {
+    ggo_weight attn_q, attn_k, attn_v, attn_o, ffn_gate, ffn_up, ffn_down;
+    const float *attn_norm, *ffn_norm;          /* F32 [hidden] */
+    const float *bq, *bk, *bv;                  /* optional F32 biases */
+    const float *q_norm, *k_norm;               /* optional F32 [head_dim] */
+} ggo_layer;
+
+typedef struct {
+    int n_layer, hidden, n_head, n_kv, head_dim, ffn, vocab, ctx;
+    int rope_neox;                               /* 1 for qwen3 */
+    float rms_eps, rope_base, rope_scale;
+    ggo_weight tok_embd, output;                 /* output = tok_embd when tied */
+    const float* output_norm;
+    const float* rope_ff; int n_rope_ff;
+    const ggo_layer* layers;
+    /* state owned by the model object */
+    float *kcache, *vcache;                      /* [L][ctx][n_kv][hd], K post-RoPE (src/runtime/kv_cache.cpp:38-48) */
+    float *rope_cos, *rope_sin;                  /* [ctx][hd/2] */
+} ggo_model;
+
+GGO_API ggo_model* ggo_model_new(int n_layer, int hidden, int n_head, int n_kv, int head_dim, int ffn,
+                                 int vocab, int ctx, float rms_eps, float rope_base, float rope_scale,
+                                 int rope_neox) {
+    ggo_model* m = (ggo_model*)calloc(1, sizeof(ggo_model));
+    if (!m) return NULL;
+    m->n_layer = n_layer; m->hidden = hidden; m->n_head = n_head; m->n_kv = n_kv; m->head_dim = head_dim;
+    m->ffn = ffn; m->vocab = vocab; m->ctx = ctx; m->rms_eps = rms_eps; m->rope_base = rope_base;
+    m->rope_scale = rope_scale; m->rope_neox = rope_neox;
+    m->layers = (ggo_layer*)calloc((size_t)n_layer, sizeof(ggo_layer));
+    const size_t kv = (size_t)n_layer * ctx * n_kv * head_dim;
+    m->kcache = (float*)calloc(kv, sizeof(float));
+    m->vcache = (float*)calloc(kv, sizeof(float));
+    m->rope_cos = (float*)malloc(sizeof(float) * (size_t)ctx * (head_dim / 2));
+    m->rope_sin = (float*)malloc(sizeof(float) * (size_t)ctx * (head_dim / 2));
+    return m;
+}
+
+GGO_API void ggo_model_free(ggo_model* m) {
+    if (!m) return;
+    free((void*)m->layers); free(m->kcache); free(m->vcache); free(m->rope_cos); free(m->rope_sin); free(m);
+}
+
+GGO_API void ggo_model_set_globals(ggo_model* m, const uint8_t* tok_embd, uint32_t tok_type,
+                                   const uint8_t* output, uint32_t out_type, const float* output_norm,
+                                   const float* rope_ff, int n_rope_ff) {
+    m->tok_embd.data = tok_embd; m->tok_embd.type = tok_type;
+    m->output.data = output ? output : tok_embd; m->output.type = output ? out_type : tok_type;
+    m->output_norm = output_norm; m->rope_ff = rope_ff; m->n_rope_ff = n_rope_ff;
+    /* head_dim-wide table built once per run (main.cpp:1272-1273) */
+    ggo_rope_table(m->ctx, m->head_dim, m->rope_scale, m->rope_base, rope_ff, n_rope_ff, m->rope_cos, m->rope_sin);
+}
+
+/* which: 0 q,1 k,2 v,3 o,4 gate,5 up,6 down */
+GGO_API void ggo_model_set_weight(ggo_model* m, int layer, int which, const uint8_t* data, uint32_t type) {
+    ggo_layer* l = (ggo_layer*)&m->layers[layer];
+    ggo_weight* w[7] = {&l->attn_q, &l->attn_k, &l->attn_v, &l->attn_o, &l->ffn_gate, &l->ffn_up, &l->ffn_down};
+    w[which]->data = data; w[which]->type = type;
+}
+
+/* which: 0 attn_norm,1 ffn_norm,2 bq,3 bk,4 bv,5 q_norm,6 k_norm */
+GGO_API void ggo_model_set_vec(ggo_model* m, int layer, int which, const float* v) {
+    ggo_layer* l = (ggo_layer*)&m->layers[layer];
+    const float** p[7] = {&l->attn_norm, &l->ffn_norm, &l->bq, &l->bk, &l->bv, &l->q_norm, &l->k_norm};
+    *p[which] = v;
+}
+
+/* One forward over n_tok tokens at absolute positions pos..pos+n_tok-1,
+ * writing the KV cache and (if logits != NULL) the logits of the LAST row
+ * (main.cpp:3593-3598).  Matmuls follow the exact path (ggo_matmul_exact).
+ * hidden_out (optional) receives the final-normed hidden rows [n_tok][hidden]. */
+GGO_API int ggo_forward(ggo_model* m, const int32_t* tokens, int n_tok, int pos, float* logits, float* hidden_out) {
+    const int H = m->hidden, hd = m->head_dim, qd = m->n_head * hd, kvd = m->n_kv * hd, F = m->ffn;
+    if (pos + n_tok > m->ctx) return -1;
+    const size_t T = (size_t)n_tok;
+    float* x = (float*)malloc(sizeof(float) * T * H);
+    float* xn = (float*)malloc(sizeof(float) * T * H);
+    float* q = (float*)malloc(sizeof(float) * T * qd);
+    float* k = (float*)malloc(sizeof(float) * T * kvd);
+    float* v = (float*)malloc(sizeof(float) * T * kvd);
+    float* qr = (float*)malloc(sizeof(float) * T * qd);
+    float* kr = (float*)malloc(sizeof(float) * T * kvd);
+    float* att = (float*)malloc(sizeof(float) * T * qd);
+    float* proj = (float*)malloc(sizeof(float) * T * H);
+    float* g = (float*)malloc(sizeof(float) * T * F);
+    float* u = (float*)malloc(sizeof(float) * T * F);
+    const int64_t ctx_len = pos + n_tok;
+    float* kexp = (float*)malloc(sizeof(float) * (size_t)m->n_head * ctx_len * hd);
+    float* vexp = (float*)malloc(sizeof(float) * (size_t)m->n_head * ctx_len * hd);
+    const int grp = m->n_head / m->n_kv;
+
+    for (int t = 0; t < n_tok; ++t) ggo_dequant_row(m->tok_embd.type, m->tok_embd.data, tokens[t], H, x + (size_t)t * H);
+
+    for (int L = 0; L < m->n_layer; ++L) {
+        const ggo_layer* l = &m->layers[L];
+        for (int t = 0; t < n_tok; ++t) ggo_rms_norm(x + (size_t)t * H, xn + (size_t)t * H, H, m->rms_eps, l->attn_norm);
+        ggo_matmul_exact(xn, n_tok, H, l->attn_q.data, l->attn_q.type, qd, H, q, qd);
+        ggo_matmul_exact(xn, n_tok, H, l->attn_k.data, l->attn_k.type, kvd, H, k, kvd);
+        ggo_matmul_exact(xn, n_tok, H, l->attn_v.data, l->attn_v.type, kvd, H, v, kvd);
+        for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3274-3284 */
+            if (l->bq) for (int j = 0; j < qd; ++j) q[(size_t)t * qd + j] += l->bq[j];
+            if (l->bk) for (int j = 0; j < kvd; ++j) k[(size_t)t * kvd + j] += l->bk[j];
+            if (l->bv) for (int j = 0; j < kvd; ++j) v[(size_t)t * kvd + j] += l->bv[j];
+        }
+        for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3289-3312 */
+            if (l->q_norm) for (int h = 0; h < m->n_head; ++h) ggo_rms_norm_head_f64(q + (size_t)t * qd + (size_t)h * hd, hd, m->rms_eps, l->q_norm);
+            if (l->k_norm) for (int h = 0; h < m->n_kv; ++h) ggo_rms_norm_head_f64(k + (size_t)t * kvd + (size_t)h * hd, hd, m->rms_eps, l->k_norm);
+        }
+        for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3314-3351 */
+            const float* c = m->rope_cos + (size_t)(pos + t) * (hd / 2);
+            const float* s = m->rope_sin + (size_t)(pos + t) * (hd / 2);
+            ggo_rope_apply(qr + (size_t)t * qd, q + (size_t)t * qd, m->n_head, hd, hd, c, s, m->rope_neox);
+            ggo_rope_apply(kr + (size_t)t * kvd, k + (size_t)t * kvd, m->n_kv, hd, hd, c, s, m->rope_neox);
+        }
+        /* KV write, src/runtime/kv_cache.cpp:76-104 */
+        float* kc = m->kcache + (size_t)L * m->ctx * kvd;
+        float* vc = m->vcache + (size_t)L * m->ctx * kvd;
+        memcpy(kc + (size_t)pos * kvd, kr, sizeof(float) * T * kvd);
+        memcpy(vc + (size_t)pos * kvd, v, sizeof(float) * T * kvd);
+        /* GQA expand, main.cpp:3364-3383 */
+        for (int h = 0; h < m->n_head; ++h)
+            for (int64_t j = 0; j < ctx_len; ++j) {
+                memcpy(kexp + ((size_t)h * ctx_len + j) * hd, kc + (size_t)j * kvd + (size_t)(h / grp) * hd, sizeof(float) * hd);
+                memcpy(vexp + ((size_t)h * ctx_len + j) * hd, vc + (size_t)j * kvd + (size_t)(h / grp) * hd, sizeof(float) * hd);
+            }
+        for (int t = 0; t < n_tok; ++t)                           /* main.cpp:3393-3410 */
+            ggo_flash_attn(qr + (size_t)t * qd, kexp, vexp, att + (size_t)t * qd, m->n_head, hd, ctx_len, pos + t);
+        ggo_matmul_exact(att, n_tok, qd, l->attn_o.data, l->attn_o.type, H, qd, proj, H);
+        for (size_t i = 0; i < T * H; ++i) x[i] += proj[i];
+        for (int t = 0; t < n_tok; ++t) ggo_rms_norm(x + (size_t)t * H, xn + (size_t)t * H, H, m->rms_eps, l->ffn_norm);
+        ggo_matmul_exact(xn, n_tok, H, l->ffn_gate.data, l->ffn_gate.type, F, H, g, F);
+        ggo_matmul_exact(xn, n_tok, H, l->ffn_up.data, l->ffn_up.type, F, H, u, F);
+        for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3461-3479 */
+            ggo_silu(g + (size_t)t * F, g + (size_t)t * F, F);
+            for (int i = 0; i < F; ++i) g[(size_t)t * F + i] *= u[(size_t)t * F + i];
+        }
+        ggo_matmul_exact(g, n_tok, F, l->ffn_down.data, l->ffn_down.type, H, F, proj, H);
+        for (size_t i = 0; i < T * H; ++i) x[i] += proj[i];
+    }
+    for (int t = 0; t < n_tok; ++t) ggo_rms_norm(x + (size_t)t * H, xn + (size_t)t * H, H, m->rms_eps, m->output_norm);
+    if (hidden_out) memcpy(hidden_out, xn, sizeof(float) * T * H);
+    if (logits) ggo_matmul_exact(xn + (T - 1) * H, 1, H, m->output.data, m->output.type, m->vocab, H, logits, m->vocab);
+    free(x); free(xn); free(q); free(k); free(v); free(qr); free(kr); free(att); free(proj); free(g); free(u);
+    free(kexp); free(vexp);
+    return 0;
+}
+
+/* Read access to the oracle KV cache row (layer, position): [n_kv][hd]. */
+GGO_API const float* ggo_model_kv(const ggo_model* m, int layer, int pos, int want_v) {
+    const size_t kvd = (size_t)m->n_kv * m->head_dim;
+    return (want_v ? m->vcache : m->kcache) + ((size_t)layer * m->ctx + pos) * kvd;
+}
