@@ -1,0 +1,341 @@
+"""Host-side mirror of ggnpu's Backend interface over the C ABI of libggb200.so.
+
+`CudaBackend` has the reference's method names, argument meaning and status
+codes (include/ggnpu/backend.h:113-160): mul_mat_q, rms_norm, rope,
+rope_batched, matmul_bf16, softmax, silu, gelu, flash_attn, sync,
+is_available, name, last_error.  Arrays are numpy (host memory), as the
+reference's callers hold every activation in host memory.  `Model` wraps the
+device-resident path (packed weights, paged KV, CUDA-graph decode).
+
+There is no CPU fallback: if the library is missing or no B200 is usable the
+constructors raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libggb200.so")
+
+
+class Status(enum.IntEnum):
+    """ggnpu::Status, include/ggnpu/backend.h:12-19."""
+    OK = 0
+    ERROR = 1
+    NOT_FOUND = 2
+    INVALID_PARAM = 3
+    NPU_UNAVAILABLE = 4
+    OUT_OF_MEMORY = 5
+
+
+class MulMatParams(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+                ("lda", C.c_int), ("ldb", C.c_int), ("ldc", C.c_int), ("n_batches", C.c_int32), ("scales", C.c_void_p),
+                ("n_weight_scales", C.c_int), ("B_type", C.c_uint32)]
+
+
+class RmsNormParams(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("size", C.c_int), ("eps", C.c_float), ("weight", C.c_void_p)]
+
+
+class RopeParams(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("n_dims", C.c_int), ("offset", C.c_int64), ("freq_scale", C.c_float),
+                ("freq_base", C.c_float), ("rope_dims", C.c_int64), ("cos_table", C.c_void_p), ("sin_table", C.c_void_p),
+                ("neox_split_half", C.c_uint8)]
+
+
+class RopeBatchedParams(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("n_heads", C.c_int), ("n_dims", C.c_int), ("offset", C.c_int64),
+                ("freq_scale", C.c_float), ("freq_base", C.c_float), ("rope_dims", C.c_int64), ("cos_table", C.c_void_p),
+                ("sin_table", C.c_void_p), ("neox_split_half", C.c_uint8)]
+
+
+class SoftmaxParams(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("rows", C.c_int), ("cols", C.c_int)]
+
+
+class UnaryParams(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("size", C.c_int)]
+
+
+class AttnParams(C.Structure):
+    _fields_ = [("Q", C.c_void_p), ("K", C.c_void_p), ("V", C.c_void_p), ("output", C.c_void_p), ("batch_size", C.c_int),
+                ("n_head", C.c_int), ("head_dim", C.c_int), ("ctx_len", C.c_int64), ("query_pos", C.c_int64),
+                ("freq_factors", C.c_void_p)]
+
+
+class ModelDesc(C.Structure):
+    _fields_ = [("n_layer", C.c_int), ("hidden", C.c_int), ("n_head", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
+                ("ffn", C.c_int), ("vocab", C.c_int), ("ctx", C.c_int), ("rms_eps", C.c_float), ("rope_base", C.c_float),
+                ("rope_scale", C.c_float), ("rope_neox", C.c_int), ("kv_page", C.c_int)]
+
+
+# every symbol include/ggb200.h declares
+EXPORTS = [
+    "ggb_create", "ggb_destroy", "ggb_mul_mat_q", "ggb_rms_norm", "ggb_rope", "ggb_rope_batched", "ggb_matmul_bf16",
+    "ggb_softmax", "ggb_silu", "ggb_gelu", "ggb_flash_attn", "ggb_sync", "ggb_is_available", "ggb_name", "ggb_last_error",
+    "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
+    "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
+    "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
+    "ggb_model_read_kv", "ggb_model_decode_bytes",
+]
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen libggb200.so and declare the signatures.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m ggnpu_b200.build` (there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH)
+    vp, i32, i64, u32, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_float
+    L.ggb_create.argtypes = [i32, C.POINTER(vp)]
+    L.ggb_destroy.argtypes = [vp]
+    L.ggb_destroy.restype = None
+    for name, st in [("ggb_mul_mat_q", MulMatParams), ("ggb_rms_norm", RmsNormParams), ("ggb_rope", RopeParams),
+                     ("ggb_rope_batched", RopeBatchedParams), ("ggb_softmax", SoftmaxParams), ("ggb_silu", UnaryParams),
+                     ("ggb_gelu", UnaryParams), ("ggb_flash_attn", AttnParams)]:
+        getattr(L, name).argtypes = [vp, C.POINTER(st)]
+    L.ggb_matmul_bf16.argtypes = [vp, vp, vp, vp, i32, i32, i32]
+    L.ggb_sync.argtypes = [vp]
+    L.ggb_sync.restype = None
+    L.ggb_is_available.argtypes = [vp]
+    L.ggb_name.argtypes = [vp]
+    L.ggb_name.restype = C.c_char_p
+    L.ggb_last_error.argtypes = [vp]
+    L.ggb_last_error_message.argtypes = [vp]
+    L.ggb_last_error_message.restype = C.c_char_p
+    L.ggb_dequant_rows.argtypes = [vp, u32, vp, i64, i32, i64, i64, vp]
+    L.ggb_weight_upload.argtypes = [vp, u32, i64, i32, vp, C.POINTER(vp)]
+    L.ggb_weight_free.argtypes = [vp, vp]
+    L.ggb_weight_free.restype = None
+    L.ggb_weight_bytes.argtypes = [vp]
+    L.ggb_weight_bytes.restype = C.c_size_t
+    L.ggb_gemv_device.argtypes = [vp, vp, vp, i32, i32, vp, i32, i32, vp, vp, f32]
+    L.ggb_gemv_swiglu_device.argtypes = [vp, vp, vp, vp, i32, i32, vp, i32, vp, f32]
+    L.ggb_stream.argtypes = [vp]
+    L.ggb_stream.restype = vp
+    L.ggb_launch_count.argtypes = [vp]
+    L.ggb_launch_count.restype = C.c_uint64
+    L.ggb_model_create.argtypes = [vp, C.POINTER(ModelDesc), C.POINTER(vp)]
+    L.ggb_model_destroy.argtypes = [vp]
+    L.ggb_model_destroy.restype = None
+    L.ggb_model_set_tensor.argtypes = [vp, i32, i32, u32, i64, i32, vp]
+    L.ggb_model_finalize.argtypes = [vp]
+    L.ggb_model_prefill.argtypes = [vp, vp, i32, i32, vp, C.POINTER(C.c_int32)]
+    L.ggb_model_decode.argtypes = [vp, C.c_int32, i32, vp, C.POINTER(C.c_int32)]
+    L.ggb_model_generate.argtypes = [vp, C.c_int32, i32, i32, vp]
+    L.ggb_model_read_kv.argtypes = [vp, i32, i32, i32, vp]
+    L.ggb_model_decode_bytes.argtypes = [vp, i32]
+    L.ggb_model_decode_bytes.restype = C.c_uint64
+    _lib = L
+    return L
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class BackendError(RuntimeError):
+    def __init__(self, status: Status, message: str):
+        super().__init__(f"{status.name}: {message}")
+        self.status = status
+
+
+class CudaBackend:
+    """The reference's `Backend` (include/ggnpu/backend.h:113-160), CUDA-backed.
+
+    Methods return a `Status`; outputs are written into the arrays passed in,
+    exactly as the reference writes through the caller's pointers."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load_library()
+        h = C.c_void_p()
+        st = Status(self.lib.ggb_create(device, C.byref(h)))
+        if st != Status.OK:
+            raise BackendError(st, f"ggb_create(device={device}) failed: no usable sm_100 GPU")
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.ggb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- Backend interface ------------------------------------------------
+    def mul_mat_q(self, A, B, C_out, M, N, K, B_type, lda=None, ldb=None, ldc=None) -> Status:
+        p = MulMatParams(_ptr(A), _ptr(B), _ptr(C_out), M, N, K, K if lda is None else lda, K if ldb is None else ldb,
+                         N if ldc is None else ldc, 1, None, 0, int(B_type))
+        return Status(self.lib.ggb_mul_mat_q(self.h, C.byref(p)))
+
+    def rms_norm(self, input, output, size, eps, weight=None) -> Status:
+        p = RmsNormParams(_ptr(input), _ptr(output), size, eps, _ptr(weight))
+        return Status(self.lib.ggb_rms_norm(self.h, C.byref(p)))
+
+    def rope(self, data, n_dims, offset, freq_scale, freq_base, rope_dims, cos_table=None, sin_table=None,
+             neox_split_half=False) -> Status:
+        p = RopeParams(_ptr(data), n_dims, offset, freq_scale, freq_base, rope_dims, _ptr(cos_table), _ptr(sin_table),
+                       int(neox_split_half))
+        return Status(self.lib.ggb_rope(self.h, C.byref(p)))
+
+    def rope_batched(self, data, n_heads, n_dims, offset, freq_scale, freq_base, rope_dims, cos_table=None, sin_table=None,
+                     neox_split_half=False) -> Status:
+        p = RopeBatchedParams(_ptr(data), n_heads, n_dims, offset, freq_scale, freq_base, rope_dims, _ptr(cos_table),
+                              _ptr(sin_table), int(neox_split_half))
+        return Status(self.lib.ggb_rope_batched(self.h, C.byref(p)))
+
+    def matmul_bf16(self, A, B, C_out, M, N, K) -> Status:
+        return Status(self.lib.ggb_matmul_bf16(self.h, _ptr(A), _ptr(B), _ptr(C_out), M, N, K))
+
+    def softmax(self, input, output, rows, cols) -> Status:
+        p = SoftmaxParams(_ptr(input), _ptr(output), rows, cols)
+        return Status(self.lib.ggb_softmax(self.h, C.byref(p)))
+
+    def silu(self, input, output, size) -> Status:
+        p = UnaryParams(_ptr(input), _ptr(output), size)
+        return Status(self.lib.ggb_silu(self.h, C.byref(p)))
+
+    def gelu(self, input, output, size) -> Status:
+        p = UnaryParams(_ptr(input), _ptr(output), size)
+        return Status(self.lib.ggb_gelu(self.h, C.byref(p)))
+
+    def flash_attn(self, Q, K, V, output, n_head, head_dim, ctx_len, query_pos=-1) -> Status:
+        p = AttnParams(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), 1, n_head, head_dim, ctx_len, query_pos, None)
+        return Status(self.lib.ggb_flash_attn(self.h, C.byref(p)))
+
+    def sync(self) -> None:
+        self.lib.ggb_sync(self.h)
+
+    def is_available(self) -> bool:
+        return bool(self.lib.ggb_is_available(self.h))
+
+    def name(self) -> str:
+        return self.lib.ggb_name(self.h).decode()
+
+    def last_error(self) -> Status:
+        return Status(self.lib.ggb_last_error(self.h))
+
+    def last_error_message(self) -> str:
+        return self.lib.ggb_last_error_message(self.h).decode()
+
+    # -- device-resident extras ---------------------------------------------
+    def check(self, st, what=""):
+        st = Status(st)
+        if st != Status.OK:
+            raise BackendError(st, f"{what}: {self.last_error_message()}")
+
+    def dequant_rows(self, type_id, raw, N, K, row0=0, n_rows=None) -> np.ndarray:
+        raw = np.ascontiguousarray(raw, dtype=np.uint8)
+        n_rows = N - row0 if n_rows is None else n_rows
+        out = np.empty((n_rows, K), dtype=np.float32)
+        self.check(self.lib.ggb_dequant_rows(self.h, int(type_id), _ptr(raw), N, K, row0, n_rows, _ptr(out)), "dequant_rows")
+        return out
+
+    def upload_weight(self, type_id, raw, N, K):
+        raw = np.ascontiguousarray(raw, dtype=np.uint8)
+        w = C.c_void_p()
+        self.check(self.lib.ggb_weight_upload(self.h, int(type_id), N, K, _ptr(raw), C.byref(w)), "weight_upload")
+        return w
+
+    def free_weight(self, w):
+        self.lib.ggb_weight_free(self.h, w)
+
+    def gemv_device(self, w, d_x, M, lda, d_y, ldc, epilogue=0, d_extra=None, d_gamma=None, eps=0.0):
+        self.check(self.lib.ggb_gemv_device(self.h, w, d_x, M, lda, d_y, ldc, epilogue, d_extra, d_gamma, eps), "gemv_device")
+
+    def gemv_swiglu_device(self, wg, wu, d_x, M, lda, d_y, ldc, d_gamma=None, eps=0.0):
+        self.check(self.lib.ggb_gemv_swiglu_device(self.h, wg, wu, d_x, M, lda, d_y, ldc, d_gamma, eps), "gemv_swiglu_device")
+
+    def stream(self) -> int:
+        return int(self.lib.ggb_stream(self.h) or 0)
+
+    def launch_count(self) -> int:
+        return int(self.lib.ggb_launch_count(self.h))
+
+
+_SLOTS = {"token_embd.weight": 0, "output.weight": 1, "output_norm.weight": 2, "rope_freqs.weight": 3}
+_LAYER_SLOTS = {"attn_norm.weight": 10, "attn_q.weight": 11, "attn_k.weight": 12, "attn_v.weight": 13,
+                "attn_output.weight": 14, "ffn_norm.weight": 15, "ffn_gate.weight": 16, "ffn_up.weight": 17,
+                "ffn_down.weight": 18, "attn_q.bias": 19, "attn_k.bias": 20, "attn_v.bias": 21, "attn_q_norm.weight": 22,
+                "attn_k_norm.weight": 23}
+
+
+class Model:
+    """A llama / qwen2 / qwen3-style decoder resident in HBM.
+
+    `tensors` maps GGUF tensor names to (ggml type id, dims with dims[0]=K, raw bytes),
+    the form ggnpu_b200.synth.SynthModel.tensors has."""
+
+    def __init__(self, backend: CudaBackend, cfg, tensors: dict):
+        self.b, self.cfg = backend, cfg
+        L = backend.lib
+        desc = ModelDesc(cfg.n_layer, cfg.hidden, cfg.n_head, cfg.n_kv, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.ctx,
+                         cfg.rms_eps, float(np.float32(cfg.rope_base)), 1.0, 1 if cfg.arch == "qwen3" else 0, 0)
+        m = C.c_void_p()
+        backend.check(L.ggb_model_create(backend.h, C.byref(desc), C.byref(m)), "model_create")
+        self.m = m
+        for name, (tid, dims, raw) in tensors.items():
+            raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+            if name in _SLOTS:
+                slot, layer = _SLOTS[name], -1
+            else:
+                parts = name.split(".", 2)
+                if parts[0] != "blk" or parts[2] not in _LAYER_SLOTS:
+                    raise KeyError(f"tensor {name} has no slot in the generic graph")
+                slot, layer = _LAYER_SLOTS[parts[2]], int(parts[1])
+            n, k = (dims[1], dims[0]) if len(dims) == 2 else (dims[0], 1)
+            backend.check(L.ggb_model_set_tensor(m, slot, layer, int(tid), n, k, _ptr(raw)), f"set_tensor({name})")
+        backend.check(L.ggb_model_finalize(m), "model_finalize")
+
+    def prefill(self, tokens, pos0=0, want_logits=True):
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        nxt = C.c_int32()
+        self.b.check(self.b.lib.ggb_model_prefill(self.m, _ptr(toks), toks.size, pos0, _ptr(logits), C.byref(nxt)), "prefill")
+        return logits, nxt.value
+
+    def decode(self, token, pos, want_logits=True, logits_out=None):
+        logits = logits_out if logits_out is not None else (np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None)
+        nxt = C.c_int32()
+        self.b.check(self.b.lib.ggb_model_decode(self.m, int(token), int(pos), _ptr(logits), C.byref(nxt)), "decode")
+        return logits, nxt.value
+
+    def generate(self, first_token, pos0, n):
+        out = np.empty(n, dtype=np.int32)
+        self.b.check(self.b.lib.ggb_model_generate(self.m, int(first_token), int(pos0), n, _ptr(out)), "generate")
+        return out
+
+    def read_kv(self, layer, pos, want_v):
+        out = np.empty((self.cfg.n_kv, self.cfg.head_dim), dtype=np.float32)
+        self.b.check(self.b.lib.ggb_model_read_kv(self.m, layer, pos, int(want_v), _ptr(out)), "read_kv")
+        return out
+
+    def decode_bytes(self, pos) -> int:
+        return int(self.b.lib.ggb_model_decode_bytes(self.m, pos))
+
+    def close(self):
+        if getattr(self, "m", None):
+            self.b.lib.ggb_model_destroy(self.m)
+            self.m = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,272 @@
+// Attention.
+//  * attn_expanded: the Backend::flash_attn contract (src/backends/cpu_ref/cpu_ref.cpp:223-280):
+//    one query token, fp32 K/V already expanded to one copy per query head.
+//  * paged path: bf16 K (stored after RoPE) and V in pages of `page` tokens, laid out
+//    [page][kv_head][slot][head_dim]; grouped-query attention reads each KV head once for all the
+//    query heads that share it (the reference expands K/V per query head instead,
+//    src/cli/main.cpp:3364-3383); long contexts are split across CTAs and merged by a second kernel.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "ggb_internal.h"
+#include "ggb_attn.h"
+
+namespace ggb {
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// ---- Backend::flash_attn ---------------------------------------------------------------------
+// One CTA per head.  scores[j] = scale * q.k_j for j <= query_pos, softmax with max subtraction,
+// out = sum_j w_j v_j.  Scores for the whole context live in shared memory.
+__global__ void attn_expanded_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                     float* __restrict__ out, int hd, int64_t ctx, int64_t qpos) {
+    extern __shared__ float sc[];            // [ctx]
+    __shared__ float red[32];
+    const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* q = Q + static_cast<size_t>(h) * hd;
+    const float* k = K + static_cast<size_t>(h) * ctx * hd;
+    const float* v = V + static_cast<size_t>(h) * ctx * hd;
+    const float scale = 1.0f / sqrtf(static_cast<float>(hd));
+    const int64_t n_keys = (qpos + 1 < ctx) ? qpos + 1 : ctx;
+    for (int64_t j = warp; j < n_keys; j += nw) {
+        float s = 0.0f;
+        for (int d = lane; d < hd; d += 32) s = fmaf(q[d], k[j * hd + d], s);
+        s = wsum(s);
+        if (lane == 0) sc[j] = s * scale;
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int64_t j = threadIdx.x; j < n_keys; j += blockDim.x) mx = fmaxf(mx, sc[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = -INFINITY;
+    for (int i = 0; i < nw; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int64_t j = threadIdx.x; j < n_keys; j += blockDim.x) { const float e = expf(sc[j] - mx); sc[j] = e; sum += e; }
+    sum = wsum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = 0.0f;
+    for (int i = 0; i < nw; ++i) sum += red[i];
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.0f;
+        for (int64_t j = 0; j < n_keys; ++j) o = fmaf(sc[j] / sum, v[j * hd + d], o);
+        out[static_cast<size_t>(h) * hd + d] = o;
+    }
+}
+
+int launch_attn_expanded(Context* c, const float* Q, const float* K, const float* V, float* out, int n_head, int head_dim,
+                         int64_t ctx_len, int64_t query_pos, cudaStream_t s) {
+    const size_t smem = static_cast<size_t>(ctx_len) * sizeof(float);
+    if (smem > 200 * 1024) return set_status(c, GGB_INVALID_PARAM, "flash_attn: ctx_len too large for the host-pointer path");
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_expanded_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return cuda_status(c, e, "flash_attn attr");
+    }
+    if (query_pos < 0) query_pos = ctx_len - 1;
+    attn_expanded_kernel<<<n_head, 256, smem, s>>>(Q, K, V, out, head_dim, ctx_len, query_pos);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "flash_attn");
+}
+
+// ---- RoPE + KV append ---------------------------------------------------------------------------
+// For token t (position p = pos + t): optional per-head RMS norm of q and k (sum of squares in
+// double, src/cli/main.cpp:3294-3299), rotate q in place and k from the table row p
+// (src/cli/main.cpp:1294-1308 / 3328-3341), store k (rotated) and v as bf16 into page p / page,
+// slot p % page (K is cached after RoPE, V raw: src/cli/main.cpp:3354-3356).
+// grid (n_head + n_kv, n_tok); one CTA per head per token; blockDim = head_dim / 2 pairs.
+__global__ void rope_append_kernel(KvAppendArgs a) {
+    const int t = blockIdx.y, hh = blockIdx.x;
+    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int hd = a.head_dim, half = hd >> 1;
+    const bool is_q = hh < a.n_head;
+    const int h = is_q ? hh : hh - a.n_head;
+    float* src = is_q ? a.q + (static_cast<size_t>(t) * a.n_head + h) * hd : a.k + (static_cast<size_t>(t) * a.n_kv + h) * hd;
+    const float* nw = is_q ? a.q_norm : a.k_norm;
+    __shared__ double red[8];
+    __shared__ float inv_s;
+    const int i = threadIdx.x;               // pair index
+    const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+    float v0 = 0.0f, v1 = 0.0f;
+    if (i < half) { v0 = src[i0]; v1 = src[i1]; }
+    if (nw) {
+        double ss = static_cast<double>(v0) * v0 + static_cast<double>(v1) * v1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double tot = 0.0;
+            for (int w = 0; w < (blockDim.x + 31) / 32; ++w) tot += red[w];
+            inv_s = 1.0f / sqrtf(static_cast<float>(tot / hd) + a.eps);
+        }
+        __syncthreads();
+        if (i < half) { v0 = v0 * inv_s * nw[i0]; v1 = v1 * inv_s * nw[i1]; }
+    }
+    if (i < half) {
+        const float cs = a.cos_tab[static_cast<size_t>(pos) * half + i], sn = a.sin_tab[static_cast<size_t>(pos) * half + i];
+        const float r0 = v0 * cs - v1 * sn, r1 = v0 * sn + v1 * cs;
+        if (is_q) { src[i0] = r0; src[i1] = r1; }
+        else {
+            const int page = a.block_table[pos / a.page], slot = pos % a.page;
+            const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * hd;
+            a.k_cache[o + i0] = __float2bfloat16_rn(r0);
+            a.k_cache[o + i1] = __float2bfloat16_rn(r1);
+            const float* vs = a.v + (static_cast<size_t>(t) * a.n_kv + h) * hd;
+            a.v_cache[o + i0] = __float2bfloat16_rn(vs[i0]);
+            a.v_cache[o + i1] = __float2bfloat16_rn(vs[i1]);
+        }
+    }
+}
+
+int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s) {
+    const int threads = ((a.head_dim / 2) + 31) / 32 * 32;
+    dim3 grid(a.n_head + a.n_kv, n_tok);
+    rope_append_kernel<<<grid, threads, 0, s>>>(a);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "rope_append");
+}
+
+// ---- paged GQA attention, split over the context ---------------------------------------------
+// grid (n_kv, n_splits, n_tok), 128 threads.  CTA (h, s, t) handles KV head h, keys of split s that
+// are <= pos_t, for the G = n_head / n_kv query heads sharing h, and writes an un-normalised
+// partial (max, sum, acc[hd]) per query head.  Warps stride over keys; lanes split head_dim.
+template <int EPL>   // elements per lane = head_dim / 32
+__global__ void __launch_bounds__(128) attn_split_kernel(AttnPagedArgs a) {
+    constexpr int MAXG = 8;
+    const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int G = a.n_head / a.n_kv, hd = EPL * 32;
+    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int keys_per_split = a.pages_per_split * a.page;
+    const int j_begin = split * keys_per_split;
+    const int j_end = min(j_begin + keys_per_split, pos + 1);
+    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits + split) * (hd + 2);
+    if (j_begin > pos) return;               // this split holds no visible key (combine skips it too)
+
+    extern __shared__ float sm[];
+    float* qs = sm;                                   // [G][hd]
+    float* wm = qs + G * hd;                          // [4][G] running max per warp
+    float* wl = wm + 4 * MAXG;                        // [4][G] running sum
+    float* wacc = wl + 4 * MAXG;                      // [4][G][hd]
+    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * hd;
+    for (int i = threadIdx.x; i < G * hd; i += blockDim.x) qs[i] = q[i];
+    __syncthreads();
+
+    float m[MAXG], l[MAXG], acc[MAXG][EPL];
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f; }
+    const float scale = 1.0f / sqrtf(static_cast<float>(hd));
+
+    for (int j = j_begin + warp; j < j_end; j += 4) {
+        const int page = a.block_table[j / a.page], slot = j % a.page;
+        const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * hd + lane * EPL;
+        float kf[EPL], vf[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; e += 2) {
+            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(a.k_cache + o + e);
+            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v_cache + o + e);
+            kf[e] = __low2float(k2); kf[e + 1] = __high2float(k2);
+            vf[e] = __low2float(v2); vf[e + 1] = __high2float(v2);
+        }
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+            if (g < G) {
+                float s = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) s = fmaf(qs[g * hd + lane * EPL + e], kf[e], s);
+                s = wsum(s) * scale;
+                const float mn = fmaxf(m[g], s);
+                const float corr = expf(m[g] - mn), p = expf(s - mn);
+                l[g] = l[g] * corr + p;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+                m[g] = mn;
+            }
+        }
+    }
+    // merge the four warps
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+        if (g < G) {
+            if (lane == 0) { wm[warp * MAXG + g] = m[g]; wl[warp * MAXG + g] = l[g]; }
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) wacc[(warp * G + g) * hd + lane * EPL + e] = acc[g][e];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+        const int g = idx / hd, d = idx - g * hd;
+        float mx = -INFINITY;
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wm[w * MAXG + g]);
+        float lsum = 0.0f, o = 0.0f;
+        for (int w = 0; w < 4; ++w) {
+            const float mw = wm[w * MAXG + g];
+            const float f = (mw == -INFINITY) ? 0.0f : expf(mw - mx);
+            lsum += wl[w * MAXG + g] * f;
+            o += wacc[(w * G + g) * hd + d] * f;
+        }
+        float* pg = part + static_cast<size_t>(g) * a.n_splits * (hd + 2);
+        pg[2 + d] = o;
+        if (d == 0) { pg[0] = mx; pg[1] = lsum; }
+    }
+}
+
+// grid (n_head, n_tok): merge the visible splits, normalise, write out[t][head][hd].
+__global__ void attn_combine_kernel(AttnPagedArgs a) {
+    const int head = blockIdx.x, t = blockIdx.y, hd = a.head_dim;
+    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int keys_per_split = a.pages_per_split * a.page;
+    const int n_active = min(a.n_splits, pos / keys_per_split + 1);
+    const float* part = a.partial + (static_cast<size_t>(t) * a.n_head + head) * a.n_splits * (hd + 2);
+    float mx = -INFINITY;
+    for (int s = 0; s < n_active; ++s) mx = fmaxf(mx, part[static_cast<size_t>(s) * (hd + 2)]);
+    float lsum = 0.0f;
+    for (int s = 0; s < n_active; ++s) lsum += part[static_cast<size_t>(s) * (hd + 2) + 1] * expf(part[static_cast<size_t>(s) * (hd + 2)] - mx);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.0f;
+        for (int s = 0; s < n_active; ++s) o += part[static_cast<size_t>(s) * (hd + 2) + 2 + d] * expf(part[static_cast<size_t>(s) * (hd + 2)] - mx);
+        a.out[(static_cast<size_t>(t) * a.n_head + head) * hd + d] = o / lsum;
+    }
+}
+
+size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim) {
+    return static_cast<size_t>(n_tok) * n_head * n_splits * (head_dim + 2);
+}
+
+int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s) {
+    const int G = a.n_head / a.n_kv;
+    if (G < 1 || G > 8 || a.n_head % a.n_kv) return set_status(c, GGB_INVALID_PARAM, "attention: query heads per KV head must be 1..8");
+    const int hd = a.head_dim;
+    const size_t smem = (static_cast<size_t>(G) * hd + 2 * 4 * 8 + static_cast<size_t>(4) * G * hd) * sizeof(float);
+    dim3 grid(a.n_kv, a.n_splits, n_tok);
+    cudaError_t e = cudaSuccess;
+#define GGB_ATTN_CASE(EPL)                                                                                             \
+    {                                                                                                                  \
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(attn_split_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+        if (e == cudaSuccess) attn_split_kernel<EPL><<<grid, 128, smem, s>>>(a);                                       \
+    }
+    if (hd == 64) GGB_ATTN_CASE(2)
+    else if (hd == 128) GGB_ATTN_CASE(4)
+    else if (hd == 256) GGB_ATTN_CASE(8)
+    else return set_status(c, GGB_INVALID_PARAM, "attention: head_dim must be 64, 128 or 256");
+#undef GGB_ATTN_CASE
+    if (e != cudaSuccess) return cuda_status(c, e, "attention attr");
+    c->launches++;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_status(c, e, "attention split");
+    attn_combine_kernel<<<dim3(a.n_head, n_tok), 64, 0, s>>>(a);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "attention combine");
+}
+
+}  // namespace ggb

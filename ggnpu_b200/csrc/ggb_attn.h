@@ -1,0 +1,43 @@
+// Argument blocks of the paged-KV attention kernels (ggb_attn.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace ggb {
+
+struct Context;
+
+struct KvAppendArgs {
+    float* q;                 // [n_tok][n_head][hd]  rotated in place
+    float* k;                 // [n_tok][n_kv][hd]    pre-RoPE keys (read)
+    const float* v;           // [n_tok][n_kv][hd]
+    __nv_bfloat16* k_cache;   // one layer: [pages][n_kv][page][hd]
+    __nv_bfloat16* v_cache;
+    const int32_t* block_table;   // logical page -> physical page
+    const float* cos_tab;     // [ctx][hd/2]
+    const float* sin_tab;
+    const float* q_norm;      // optional [hd]
+    const float* k_norm;
+    const int32_t* d_pos;     // device scalar: position of token 0 (nullptr => pos0)
+    int pos0;
+    int n_head, n_kv, head_dim, page, neox;
+    float eps;
+};
+
+struct AttnPagedArgs {
+    const float* q;           // [n_tok][n_head][hd] post-RoPE
+    const __nv_bfloat16* k_cache;
+    const __nv_bfloat16* v_cache;
+    const int32_t* block_table;
+    float* partial;           // [n_tok][n_head][n_splits][hd + 2] scratch
+    float* out;               // [n_tok][n_head][hd]
+    const int32_t* d_pos;
+    int pos0;
+    int n_head, n_kv, head_dim, page, n_splits, pages_per_split;
+};
+
+int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s);
+int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s);
+size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim);
+
+}  // namespace ggb

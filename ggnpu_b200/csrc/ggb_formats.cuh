@@ -1,0 +1,172 @@
+// GGUF block formats as they live in HBM, and their exact decoders.
+//
+// At upload every weight matrix is re-laid-out ("packed once") from GGUF's
+// array-of-blocks into a few streams, each a dense array over all (row, block)
+// pairs, so that the hot loops issue only naturally aligned 16-byte loads:
+//
+//   Q4_K   144 B : hdr[16] (d, dmin, scales[12]) | qs[128]
+//   Q5_K   176 B : hdr[16]                       | qh[32]  | qs[128]
+//   Q6_K   210 B : ql[128] | qh[64] | scales[16] | d[2]
+//   Q2_K    84 B : scales[16] | qs[64] | d,dmin[4]
+//   Q3_K   110 B : hmask[32] | qs[64] | scales[12] | d[2]
+//   Q8_0    34 B : d[2] | qs[32]
+//   Q4_0/IQ4_NL 18 B : d[2] | qs[16]        Q4_1 20 B : d,m[4] | qs[16]
+//   IQ4_XS 136 B : hdr[8] (d, scales_h, scales_l[4]) | qs[128]
+//   F32 / F16 / BF16 : unchanged
+//
+// Each stream is a slice [off, off+size) of the GGUF block, so the re-layout is
+// a pure permutation of bytes and total bytes equal the GGUF bytes (plus
+// alignment padding between streams).  Decoders below reproduce, value for
+// value and rounding for rounding, the reference decoders of
+// include/ggnpu/quant/kquant.h:70-202, src/quant/q4_0.cpp:18-26,
+// src/quant/q4_1.cpp:20-29, src/quant/q8_0.cpp:19-25, src/quant/iq4_nl.cpp:24-31,
+// src/quant/iq4_xs.cpp:21-39 and src/utils/bf16.cpp:15-46.  All arithmetic is
+// fp32; fp16 scales are widened exactly (subnormals kept), nothing is flushed.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace ggb {
+
+enum : uint32_t {
+    T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12,
+    T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20, T_IQ4_XS = 23, T_BF16 = 30
+};
+
+constexpr int kMaxStreams = 4;
+
+struct FormatInfo {
+    int block_elems;       // 0 => unsupported type
+    int block_bytes;
+    int n_streams;
+    int off[kMaxStreams];  // slice of the GGUF block that forms stream i
+    int size[kMaxStreams];
+};
+
+__host__ __device__ inline FormatInfo format_info(uint32_t t) {
+    switch (t) {
+    case T_F32:    return {1, 4, 1, {0, 0, 0, 0}, {4, 0, 0, 0}};
+    case T_F16:    return {1, 2, 1, {0, 0, 0, 0}, {2, 0, 0, 0}};
+    case T_BF16:   return {1, 2, 1, {0, 0, 0, 0}, {2, 0, 0, 0}};
+    case T_Q4_0:   return {32, 18, 2, {0, 2, 0, 0}, {2, 16, 0, 0}};
+    case T_IQ4_NL: return {32, 18, 2, {0, 2, 0, 0}, {2, 16, 0, 0}};
+    case T_Q4_1:   return {32, 20, 2, {0, 4, 0, 0}, {4, 16, 0, 0}};
+    case T_Q8_0:   return {32, 34, 2, {0, 2, 0, 0}, {2, 32, 0, 0}};
+    case T_Q2_K:   return {256, 84, 3, {0, 16, 80, 0}, {16, 64, 4, 0}};
+    case T_Q3_K:   return {256, 110, 4, {0, 32, 96, 108}, {32, 64, 12, 2}};
+    case T_Q4_K:   return {256, 144, 2, {0, 16, 0, 0}, {16, 128, 0, 0}};
+    case T_Q5_K:   return {256, 176, 3, {0, 16, 48, 0}, {16, 32, 128, 0}};
+    case T_Q6_K:   return {256, 210, 4, {0, 128, 192, 208}, {128, 64, 16, 2}};
+    case T_IQ4_XS: return {256, 136, 2, {0, 8, 0, 0}, {8, 128, 0, 0}};
+    default:       return {0, 0, 0, {0, 0, 0, 0}, {0, 0, 0, 0}};
+    }
+}
+
+// A weight matrix [N rows][K] resident in HBM in the stream layout.
+struct PackedW {
+    const uint8_t* s[kMaxStreams];
+    int64_t N;
+    int K;
+    int nb;          // blocks per row = K / block_elems
+    uint32_t type;
+};
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
+    return __half2float(__ushort_as_half(h));      // exact widening, subnormals included
+}
+__device__ __forceinline__ float ld_f16(const uint8_t* p) {   // p 2-byte aligned
+    return f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(p));
+}
+
+__device__ __constant__ const int8_t kIq4Codebook[16] = {-127, -104, -83, -65, -49, -35, -22, -10,
+                                                         1, 13, 25, 38, 53, 69, 89, 113};
+
+// 6-bit (scale, min) pair j of the 12-byte Q4_K/Q5_K pack.
+__device__ __forceinline__ void k4_scale_min(int j, const uint8_t* p, int& sc, int& mn) {
+    if (j < 4) { sc = p[j] & 63; mn = p[j + 4] & 63; }
+    else { sc = (p[j + 4] & 15) | ((p[j - 4] >> 6) << 4); mn = (p[j + 4] >> 4) | ((p[j] >> 6) << 4); }
+}
+
+// Element j of block `blk` (= row * nb + block-in-row), bit-exact with the
+// reference decoder of its type.  Products are formed in the reference's
+// order; the one rounding of the min-type formats is the final subtract/add
+// (an FMA there yields the same bits because the product is exact).
+__device__ inline float decode_elem(const PackedW& w, int64_t blk, int j) {
+    switch (w.type) {
+    case T_F32: return reinterpret_cast<const float*>(w.s[0])[blk];
+    case T_F16: return f16_bits_to_f32(reinterpret_cast<const uint16_t*>(w.s[0])[blk]);
+    case T_BF16: return __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(w.s[0])[blk]) << 16);
+    case T_Q4_0: {
+        const float d = ld_f16(w.s[0] + blk * 2);
+        const uint8_t b = w.s[1][blk * 16 + (j & 15)];
+        return __int2float_rn(static_cast<int>(j < 16 ? (b & 15) : (b >> 4)) - 8) * d;
+    }
+    case T_Q4_1: {
+        const float d = ld_f16(w.s[0] + blk * 4), m = ld_f16(w.s[0] + blk * 4 + 2);
+        const uint8_t b = w.s[1][blk * 16 + (j & 15)];
+        return __fadd_rn(__fmul_rn(__int2float_rn(j < 16 ? (b & 15) : (b >> 4)), d), m);
+    }
+    case T_Q8_0: {
+        const float d = ld_f16(w.s[0] + blk * 2);
+        return __int2float_rn(static_cast<int8_t>(w.s[1][blk * 32 + j])) * d;
+    }
+    case T_IQ4_NL: {
+        const float d = ld_f16(w.s[0] + blk * 2);
+        const uint8_t b = w.s[1][blk * 16 + (j & 15)];
+        return d * __int2float_rn(kIq4Codebook[j < 16 ? (b & 15) : (b >> 4)]);
+    }
+    case T_IQ4_XS: {
+        const uint8_t* h = w.s[0] + blk * 8;
+        const float d = ld_f16(h);
+        const unsigned sh = h[2] | (h[3] << 8);
+        const int ib = j >> 5, l = j & 31;
+        const int ls = ((h[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15) | (((sh >> (2 * ib)) & 3) << 4);
+        const float dl = d * __int2float_rn(ls - 32);
+        const uint8_t b = w.s[1][blk * 128 + 16 * ib + (l & 15)];
+        return dl * __int2float_rn(kIq4Codebook[l < 16 ? (b & 15) : (b >> 4)]);
+    }
+    case T_Q4_K: case T_Q5_K: {
+        const uint8_t* h = w.s[0] + blk * 16;
+        const float d = ld_f16(h), dmin = ld_f16(h + 2);
+        const int sb = j >> 5, l = j & 31, g = sb >> 1;
+        int sc, mn;
+        k4_scale_min(sb, h + 4, sc, mn);
+        const uint8_t* qs = (w.type == T_Q4_K ? w.s[1] : w.s[2]) + blk * 128;
+        const uint8_t b = qs[32 * g + l];
+        int q = (sb & 1) ? (b >> 4) : (b & 15);
+        if (w.type == T_Q5_K) q += ((w.s[1][blk * 32 + l] >> sb) & 1) ? 16 : 0;
+        return __fsub_rn(__fmul_rn(d * __int2float_rn(sc), __int2float_rn(q)), dmin * __int2float_rn(mn));
+    }
+    case T_Q6_K: {
+        const float d = ld_f16(w.s[3] + blk * 2);
+        const int hf = j >> 7, r = j & 127, quarter = r >> 5, l = r & 31;
+        const uint8_t* ql = w.s[0] + blk * 128 + 64 * hf;
+        const uint8_t qh = w.s[1][blk * 64 + 32 * hf + l];
+        const uint8_t lo = ql[l + 32 * (quarter & 1)];
+        const int q = static_cast<int>(((quarter & 2) ? (lo >> 4) : (lo & 15)) | (((qh >> (2 * quarter)) & 3) << 4)) - 32;
+        const int sc = static_cast<int8_t>(w.s[2][blk * 16 + 8 * hf + 2 * quarter + (l >> 4)]);
+        return __fmul_rn(__fmul_rn(d, __int2float_rn(sc)), __int2float_rn(q));
+    }
+    case T_Q2_K: {
+        const float d = ld_f16(w.s[2] + blk * 4), dmin = ld_f16(w.s[2] + blk * 4 + 2);
+        const int sb = j >> 4, l = j & 15, hf = sb >> 3, sh = (sb >> 1) & 3, odd = sb & 1;
+        const uint8_t s = w.s[0][blk * 16 + sb];
+        const int q = (w.s[1][blk * 64 + 32 * hf + 16 * odd + l] >> (2 * sh)) & 3;
+        return __fsub_rn(__fmul_rn(d * __int2float_rn(s & 15), __int2float_rn(q)), dmin * __int2float_rn(s >> 4));
+    }
+    case T_Q3_K: {
+        const float d = ld_f16(w.s[3] + blk * 2);
+        const int sb = j >> 4, l = j & 15, hf = sb >> 3, sh = (sb >> 1) & 3, odd = sb & 1;
+        const uint8_t* s = w.s[2] + blk * 12;
+        const int lo = (sb < 8) ? (s[sb] & 15) : (s[sb - 8] >> 4);
+        const int hi = (s[8 + (sb & 3)] >> (2 * (sb >> 2))) & 3;
+        const float dl = d * __int2float_rn((lo | (hi << 4)) - 32);
+        const int q = (w.s[1][blk * 64 + 32 * hf + 16 * odd + l] >> (2 * sh)) & 3;
+        const int hbit = (w.s[0][blk * 32 + 16 * odd + l] >> (4 * hf + sh)) & 1;
+        return dl * __int2float_rn(q - (hbit ? 0 : 4));
+    }
+    default: return 0.0f;
+    }
+}
+
+}  // namespace ggb

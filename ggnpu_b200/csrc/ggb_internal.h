@@ -1,0 +1,93 @@
+// Internal declarations shared by the translation units of libggb200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/ggb200.h"
+#include "ggb_formats.cuh"
+
+namespace ggb {
+
+// Epilogue of a GEMV: what happens to y = W x before it is stored.
+enum : int { EPI_STORE = 0, EPI_ADD_BIAS = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+
+struct GemvArgs {
+    PackedW w;            // main weight
+    PackedW w2;           // second weight of the same shape/type (SwiGLU: w = gate, w2 = up)
+    const float* x;       // [M][lda] activations (device)
+    int M, lda;
+    float* y;             // [M][ldc]
+    int ldc;
+    int epi;
+    const float* bias;    // EPI_ADD_BIAS: [N]
+    const float* resid;   // EPI_RESIDUAL: [M][ldc], y = resid + W x (may alias y)
+    // optional fused RMSNorm prologue: x is normalised with gamma before the product
+    const float* gamma;   // nullptr => no norm
+    float eps;
+};
+
+struct DeviceWeight {
+    PackedW w{};
+    void* base = nullptr;     // one allocation holding all streams
+    size_t bytes = 0;
+};
+
+struct Context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    int last_status = GGB_OK;
+    std::string last_message;
+    int sm_count = 148;
+    // scratch buffers for the host-pointer operator path (grown on demand)
+    void* d_scratch[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t d_scratch_bytes[4] = {0, 0, 0, 0};
+    void* h_pinned = nullptr;
+    size_t h_pinned_bytes = 0;
+    // host weight pointer -> packed device copy (first sight uploads)
+    struct Key { const void* p; int64_t n; int k; uint32_t t; bool operator==(const Key& o) const { return p == o.p && n == o.n && k == o.k && t == o.t; } };
+    struct KeyHash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.n * 1315423911u + k.k) << 1) ^ k.t; } };
+    std::unordered_map<Key, DeviceWeight*, KeyHash> weight_cache;
+    uint64_t launches = 0;    // kernels launched by this library on this context
+};
+
+int set_status(Context* c, int status, const char* msg);
+int cuda_status(Context* c, cudaError_t e, const char* what);
+void* scratch(Context* c, int slot, size_t bytes);           // nullptr on failure (status set)
+
+// ggb_pack.cu
+int upload_weight(Context* c, uint32_t type, int64_t N, int K, const void* host_rows, DeviceWeight** out);
+void free_weight(DeviceWeight* w);
+size_t packed_bytes(uint32_t type, int64_t N, int K);
+int launch_dequant_rows(Context* c, const PackedW& w, int64_t row0, int64_t n_rows, float* d_out, cudaStream_t s);
+int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int n_rows, float* d_out, int ld, cudaStream_t s);
+
+// ggb_gemv.cu
+int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
+
+// ggb_ops.cu
+int launch_rms_norm(Context* c, const float* x, float* y, int rows, int n, float eps, const float* gamma, cudaStream_t s);
+int launch_silu(Context* c, const float* x, float* y, int64_t n, cudaStream_t s);
+int launch_gelu(Context* c, const float* x, float* y, int64_t n, cudaStream_t s);
+int launch_softmax(Context* c, const float* x, float* y, int rows, int cols, cudaStream_t s);
+int launch_rope(Context* c, float* x, int n_tok, int n_heads, int head_dim, int rot_dims, const float* cos_tab,
+                const float* sin_tab, const int32_t* d_pos, int pos0, int neox, cudaStream_t s);
+int launch_rope_angles(Context* c, float* x, int n_heads, int n_dims, int64_t rope_dims, int64_t offset, float freq_scale,
+                       float freq_base, int neox, cudaStream_t s);
+int launch_matmul_f32_kn(Context* c, const float* A, const float* B, float* C, int M, int N, int K, int lda, int ldc, cudaStream_t s);
+int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
+
+// ggb_attn.cu
+int launch_attn_expanded(Context* c, const float* Q, const float* K, const float* V, float* out, int n_head, int head_dim,
+                         int64_t ctx_len, int64_t query_pos, cudaStream_t s);
+
+}  // namespace ggb
+
+// The opaque C handles are thin names for the internal structs.
+struct ggb_context : ggb::Context {};
+struct ggb_weight_s : ggb::DeviceWeight {};

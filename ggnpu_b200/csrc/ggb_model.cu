@@ -1,0 +1,415 @@
+// C ABI, part 2: the generic decoder graph of the reference CLI (src/cli/main.cpp:2367-2375 embed,
+// :3235-3500 layer loop, :3504-3512 final norm, :3593-3599 logits, :827-838 greedy) kept entirely in
+// HBM: packed weights, paged bf16 KV cache, f32 activations, one CUDA graph per decode step.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include <cmath>
+#include <memory>
+
+#include "ggb_attn.h"
+#include "ggb_internal.h"
+
+using namespace ggb;
+
+
+namespace {
+
+struct Layer {
+    DeviceWeight *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+};
+
+constexpr int kMaxChunk = 256;   // prompt tokens per forward pass (the reference's kPrefillChunk, main.cpp:2326)
+
+}  // namespace
+
+struct ggb_model_s {
+    Context* c = nullptr;
+    ggb_model_desc d{};
+    DeviceWeight *tok_embd = nullptr, *output = nullptr;
+    float* output_norm = nullptr;
+    std::vector<float> rope_ff;
+    std::vector<Layer> layers;
+    std::vector<void*> owned;            // cudaMalloc'd vectors and buffers
+    bool finalized = false;
+    // KV cache
+    __nv_bfloat16 *k_cache = nullptr, *v_cache = nullptr;
+    int32_t* block_table = nullptr;
+    int page = 64, n_pages = 0, n_splits = 1, pages_per_split = 1;
+    size_t kv_layer_elems = 0;
+    float *cos_tab = nullptr, *sin_tab = nullptr;
+    // activations
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
+    float *partial = nullptr, *amax_partial = nullptr;
+    int32_t *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *d_gen = nullptr, *d_step = nullptr;
+    // pinned host staging
+    int32_t* h_io = nullptr;             // [0]=token [1]=pos [2]=next
+    float* h_logits = nullptr;
+    cudaGraphExec_t decode_graph = nullptr;
+    uint64_t launches_per_step = 0;
+};
+
+namespace {
+
+template <class T>
+int dev_alloc(ggb_model m, T** p, size_t count) {
+    void* v = nullptr;
+    int st = cuda_status(m->c, cudaMalloc(&v, sizeof(T) * std::max<size_t>(count, 1)), "cudaMalloc(model)");
+    if (st != GGB_OK) return st;
+    m->owned.push_back(v);
+    *p = static_cast<T*>(v);
+    return GGB_OK;
+}
+
+__global__ void feedback_kernel(const int32_t* next, int32_t* tokens, int32_t* pos, int32_t* gen, int32_t* step, int gen_cap) {
+    const int s = step[0];
+    if (s < gen_cap) gen[s] = next[0];
+    tokens[0] = next[0];
+    pos[0] += 1;
+    step[0] = s + 1;
+}
+
+GemvArgs gemv_args(const DeviceWeight* w, const float* x, int M, int lda, float* y, int ldc) {
+    GemvArgs a{};
+    a.w = w->w; a.x = x; a.M = M; a.lda = lda; a.y = y; a.ldc = ldc; a.epi = EPI_STORE;
+    return a;
+}
+
+#define M_TRY(expr) do { int _st = (expr); if (_st != GGB_OK) return _st; } while (0)
+
+// Enqueue one forward over n_tok tokens whose ids are in m->d_tokens.  Positions start at
+// d_pos[0] when dev_pos, else at pos0.  Ends with logits of the last row and its argmax in d_next.
+int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
+    Context* c = m->c;
+    cudaStream_t s = c->stream;
+    const ggb_model_desc& d = m->d;
+    const int H = d.hidden, hd = d.head_dim, qd = d.n_head * hd, kvd = d.n_kv * hd, F = d.ffn;
+    const int32_t* dpos = dev_pos ? m->d_pos : nullptr;
+    M_TRY(launch_gather_rows(c, m->tok_embd->w, m->d_tokens, n_tok, m->x, H, s));
+    for (int L = 0; L < d.n_layer; ++L) {
+        const Layer& l = m->layers[L];
+        GemvArgs a = gemv_args(l.q, m->x, n_tok, H, m->q, qd);
+        a.gamma = l.attn_norm; a.eps = d.rms_eps;
+        if (l.bq) { a.epi = EPI_ADD_BIAS; a.bias = l.bq; }
+        M_TRY(launch_gemv(c, a, s));
+        a = gemv_args(l.k, m->x, n_tok, H, m->k, kvd);
+        a.gamma = l.attn_norm; a.eps = d.rms_eps;
+        if (l.bk) { a.epi = EPI_ADD_BIAS; a.bias = l.bk; }
+        M_TRY(launch_gemv(c, a, s));
+        a = gemv_args(l.v, m->x, n_tok, H, m->v, kvd);
+        a.gamma = l.attn_norm; a.eps = d.rms_eps;
+        if (l.bv) { a.epi = EPI_ADD_BIAS; a.bias = l.bv; }
+        M_TRY(launch_gemv(c, a, s));
+
+        KvAppendArgs ka{};
+        ka.q = m->q; ka.k = m->k; ka.v = m->v;
+        ka.k_cache = m->k_cache + static_cast<size_t>(L) * m->kv_layer_elems;
+        ka.v_cache = m->v_cache + static_cast<size_t>(L) * m->kv_layer_elems;
+        ka.block_table = m->block_table; ka.cos_tab = m->cos_tab; ka.sin_tab = m->sin_tab;
+        ka.q_norm = l.q_norm; ka.k_norm = l.k_norm; ka.d_pos = dpos; ka.pos0 = pos0;
+        ka.n_head = d.n_head; ka.n_kv = d.n_kv; ka.head_dim = hd; ka.page = m->page; ka.neox = d.rope_neox; ka.eps = d.rms_eps;
+        M_TRY(launch_rope_append(c, ka, n_tok, s));
+
+        AttnPagedArgs aa{};
+        aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = m->block_table;
+        aa.partial = m->partial; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
+        aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
+        aa.pages_per_split = m->pages_per_split;
+        M_TRY(launch_attn_paged(c, aa, n_tok, s));
+
+        a = gemv_args(l.o, m->att, n_tok, qd, m->x, H);
+        a.epi = EPI_RESIDUAL; a.resid = m->x;
+        M_TRY(launch_gemv(c, a, s));
+
+        a = gemv_args(l.gate, m->x, n_tok, H, m->act, F);
+        a.w2 = l.up->w; a.epi = EPI_SWIGLU; a.gamma = l.ffn_norm; a.eps = d.rms_eps;
+        M_TRY(launch_gemv(c, a, s));
+
+        a = gemv_args(l.down, m->act, n_tok, F, m->x, H);
+        a.epi = EPI_RESIDUAL; a.resid = m->x;
+        M_TRY(launch_gemv(c, a, s));
+    }
+    // final norm fused into the logits GEMV; only the last row feeds sampling (main.cpp:3593-3598)
+    GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H, m->logits, d.vocab);
+    a.gamma = m->output_norm; a.eps = d.rms_eps;
+    M_TRY(launch_gemv(c, a, s));
+    M_TRY(launch_argmax(c, m->logits, d.vocab, m->d_next, m->amax_partial, s));
+    return GGB_OK;
+}
+
+}  // namespace
+
+#define GGB_LOCK(h) std::lock_guard<std::mutex> _lk((h)->mu); cudaSetDevice((h)->device)
+
+extern "C" {
+
+int ggb_model_create(ggb_handle h, const ggb_model_desc* desc, ggb_model* out) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!desc || !out) return set_status(h, GGB_INVALID_PARAM, "model_create: null pointer");
+    const ggb_model_desc& d = *desc;
+    if (d.n_layer <= 0 || d.hidden <= 0 || d.n_head <= 0 || d.n_kv <= 0 || d.head_dim <= 0 || d.ffn <= 0 || d.vocab <= 0 || d.ctx <= 0 ||
+        d.n_head % d.n_kv || (d.head_dim != 64 && d.head_dim != 128 && d.head_dim != 256) || d.hidden % 32 || d.ffn % 32)
+        return set_status(h, GGB_INVALID_PARAM, "model_create: unsupported dimensions");
+    ggb_model m = new ggb_model_s();
+    m->c = h; m->d = d;
+    if (m->d.rope_scale == 0.0f) m->d.rope_scale = 1.0f;
+    m->page = d.kv_page > 0 ? d.kv_page : 64;
+    m->layers.resize(d.n_layer);
+    *out = m;
+    return GGB_OK;
+}
+
+void ggb_model_destroy(ggb_model m) {
+    if (!m) return;
+    {
+        GGB_LOCK(m->c);
+        cudaStreamSynchronize(m->c->stream);
+        if (m->decode_graph) cudaGraphExecDestroy(m->decode_graph);
+        for (void* p : m->owned) cudaFree(p);
+        if (m->h_io) cudaFreeHost(m->h_io);
+        if (m->h_logits) cudaFreeHost(m->h_logits);
+        free_weight(m->tok_embd); free_weight(m->output);
+        for (Layer& l : m->layers) { free_weight(l.q); free_weight(l.k); free_weight(l.v); free_weight(l.o); free_weight(l.gate); free_weight(l.up); free_weight(l.down); }
+    }
+    delete m;
+}
+
+int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_t N, int K, const void* host) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!host) return set_status(c, GGB_INVALID_PARAM, "set_tensor: null data");
+    if (m->finalized) return set_status(c, GGB_INVALID_PARAM, "set_tensor: model already finalized");
+    GGB_LOCK(c);
+    const ggb_model_desc& d = m->d;
+    const int qd = d.n_head * d.head_dim, kvd = d.n_kv * d.head_dim;
+    auto mat = [&](DeviceWeight** dst, int64_t wantN, int wantK) -> int {
+        if (N != wantN || K != wantK) return set_status(c, GGB_INVALID_PARAM, "set_tensor: shape does not match the model description");
+        if (*dst) { free_weight(*dst); *dst = nullptr; }
+        return upload_weight(c, type, N, K, host, dst);
+    };
+    auto vec = [&](float** dst, int64_t wantN) -> int {
+        if (type != GGB_F32 || N != wantN) return set_status(c, GGB_INVALID_PARAM, "set_tensor: vectors must be F32 of the model's size");
+        int st = dev_alloc(m, dst, static_cast<size_t>(N));
+        if (st != GGB_OK) return st;
+        st = cuda_status(c, cudaMemcpyAsync(*dst, host, sizeof(float) * N, cudaMemcpyHostToDevice, c->stream), "vector upload");
+        if (st != GGB_OK) return st;
+        return cuda_status(c, cudaStreamSynchronize(c->stream), "vector upload");
+    };
+    if (slot < 10) {
+        switch (slot) {
+        case GGB_T_TOKEN_EMBD: return mat(&m->tok_embd, d.vocab, d.hidden);
+        case GGB_T_OUTPUT: return mat(&m->output, d.vocab, d.hidden);
+        case GGB_T_OUTPUT_NORM: return vec(&m->output_norm, d.hidden);
+        case GGB_T_ROPE_FREQS:
+            if (type != GGB_F32 || N <= 0) return set_status(c, GGB_INVALID_PARAM, "set_tensor: rope_freqs must be F32");
+            m->rope_ff.assign(static_cast<const float*>(host), static_cast<const float*>(host) + N);
+            return GGB_OK;
+        default: return set_status(c, GGB_NOT_FOUND, "set_tensor: unknown slot");
+        }
+    }
+    if (layer < 0 || layer >= d.n_layer) return set_status(c, GGB_INVALID_PARAM, "set_tensor: layer out of range");
+    Layer& l = m->layers[layer];
+    switch (slot) {
+    case GGB_T_ATTN_NORM: return vec(&l.attn_norm, d.hidden);
+    case GGB_T_FFN_NORM: return vec(&l.ffn_norm, d.hidden);
+    case GGB_T_ATTN_Q: return mat(&l.q, qd, d.hidden);
+    case GGB_T_ATTN_K: return mat(&l.k, kvd, d.hidden);
+    case GGB_T_ATTN_V: return mat(&l.v, kvd, d.hidden);
+    case GGB_T_ATTN_OUT: return mat(&l.o, d.hidden, qd);
+    case GGB_T_FFN_GATE: return mat(&l.gate, d.ffn, d.hidden);
+    case GGB_T_FFN_UP: return mat(&l.up, d.ffn, d.hidden);
+    case GGB_T_FFN_DOWN: return mat(&l.down, d.hidden, d.ffn);
+    case GGB_T_BIAS_Q: return vec(&l.bq, qd);
+    case GGB_T_BIAS_K: return vec(&l.bk, kvd);
+    case GGB_T_BIAS_V: return vec(&l.bv, kvd);
+    case GGB_T_Q_NORM: return vec(&l.q_norm, d.head_dim);
+    case GGB_T_K_NORM: return vec(&l.k_norm, d.head_dim);
+    default: return set_status(c, GGB_NOT_FOUND, "set_tensor: unknown slot");
+    }
+}
+
+int ggb_model_finalize(ggb_model m) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (m->finalized) return GGB_OK;
+    GGB_LOCK(c);
+    const ggb_model_desc& d = m->d;
+    if (!m->tok_embd || !m->output_norm) return set_status(c, GGB_INVALID_PARAM, "finalize: token_embd / output_norm missing");
+    for (const Layer& l : m->layers) {
+        if (!l.q || !l.k || !l.v || !l.o || !l.gate || !l.up || !l.down || !l.attn_norm || !l.ffn_norm)
+            return set_status(c, GGB_INVALID_PARAM, "finalize: a layer tensor is missing");
+        if (l.gate->w.type != l.up->w.type) return set_status(c, GGB_INVALID_PARAM, "finalize: ffn_gate and ffn_up must share a type");
+    }
+    const int hd = d.head_dim, qd = d.n_head * hd, kvd = d.n_kv * hd;
+    // RoPE table exactly as RopeCache::build (src/cli/main.cpp:665-692): float pow/cos/sin on the host.
+    {
+        const int pairs = hd / 2;
+        std::vector<float> cs(static_cast<size_t>(d.ctx) * pairs), sn(cs.size());
+        for (int64_t p = 0; p < d.ctx; ++p)
+            for (int i = 0; i < pairs; ++i) {
+                float ff = i < static_cast<int>(m->rope_ff.size()) ? m->rope_ff[i] : 1.0f;
+                if (ff == 0.0f) ff = 1.0f;
+                const float wavelength = std::pow(d.rope_base, 2.0f * static_cast<float>(i) / static_cast<float>(hd));
+                const float angle = m->d.rope_scale * static_cast<float>(p) / (wavelength * ff);
+                cs[p * pairs + i] = std::cos(angle);
+                sn[p * pairs + i] = std::sin(angle);
+            }
+        M_TRY(dev_alloc(m, &m->cos_tab, cs.size()));
+        M_TRY(dev_alloc(m, &m->sin_tab, sn.size()));
+        M_TRY(cuda_status(c, cudaMemcpy(m->cos_tab, cs.data(), sizeof(float) * cs.size(), cudaMemcpyHostToDevice), "rope table"));
+        M_TRY(cuda_status(c, cudaMemcpy(m->sin_tab, sn.data(), sizeof(float) * sn.size(), cudaMemcpyHostToDevice), "rope table"));
+    }
+    // paged KV
+    m->n_pages = (d.ctx + m->page - 1) / m->page;
+    m->pages_per_split = (m->n_pages + 31) / 32;
+    m->n_splits = (m->n_pages + m->pages_per_split - 1) / m->pages_per_split;
+    m->kv_layer_elems = static_cast<size_t>(m->n_pages) * d.n_kv * m->page * hd;
+    M_TRY(dev_alloc(m, &m->k_cache, m->kv_layer_elems * d.n_layer));
+    M_TRY(dev_alloc(m, &m->v_cache, m->kv_layer_elems * d.n_layer));
+    M_TRY(cuda_status(c, cudaMemset(m->k_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
+    M_TRY(cuda_status(c, cudaMemset(m->v_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
+    {
+        std::vector<int32_t> bt(m->n_pages);
+        for (int i = 0; i < m->n_pages; ++i) bt[i] = i;
+        M_TRY(dev_alloc(m, &m->block_table, bt.size()));
+        M_TRY(cuda_status(c, cudaMemcpy(m->block_table, bt.data(), sizeof(int32_t) * bt.size(), cudaMemcpyHostToDevice), "block table"));
+    }
+    const size_t T = kMaxChunk;
+    M_TRY(dev_alloc(m, &m->x, T * d.hidden));
+    M_TRY(dev_alloc(m, &m->q, T * qd));
+    M_TRY(dev_alloc(m, &m->k, T * kvd));
+    M_TRY(dev_alloc(m, &m->v, T * kvd));
+    M_TRY(dev_alloc(m, &m->att, T * qd));
+    M_TRY(dev_alloc(m, &m->act, T * d.ffn));
+    M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
+    M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kMaxChunk, d.n_head, m->n_splits, hd)));
+    M_TRY(dev_alloc(m, &m->amax_partial, 512));
+    M_TRY(dev_alloc(m, &m->d_tokens, T));
+    M_TRY(dev_alloc(m, &m->d_pos, 1));
+    M_TRY(dev_alloc(m, &m->d_next, 1));
+    M_TRY(dev_alloc(m, &m->d_step, 1));
+    M_TRY(dev_alloc(m, &m->d_gen, static_cast<size_t>(d.ctx)));
+    M_TRY(cuda_status(c, cudaMemset(m->d_pos, 0, 4), "memset"));
+    M_TRY(cuda_status(c, cudaMemset(m->d_step, 0, 4), "memset"));
+    M_TRY(cuda_status(c, cudaMemset(m->d_tokens, 0, 4 * T), "memset"));
+    M_TRY(cuda_status(c, cudaMallocHost(&m->h_io, 64), "pinned alloc"));
+    M_TRY(cuda_status(c, cudaMallocHost(&m->h_logits, sizeof(float) * d.vocab), "pinned alloc"));
+
+    // One eager step first: it sets every kernel's shared-memory attribute outside capture
+    // (and faults early, if anything is wrong, where the error is attributable).
+    M_TRY(enqueue_forward(m, 1, true, 0));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "warm-up step"));
+    // Capture the decode step: forward + token/position feedback.
+    const uint64_t before = c->launches;
+    M_TRY(cuda_status(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "begin capture"));
+    int st = enqueue_forward(m, 1, true, 0);
+    if (st == GGB_OK) {
+        feedback_kernel<<<1, 1, 0, c->stream>>>(m->d_next, m->d_tokens, m->d_pos, m->d_gen, m->d_step, d.ctx);
+        c->launches++;
+        st = cuda_status(c, cudaGetLastError(), "feedback kernel");
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    if (st != GGB_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    M_TRY(cuda_status(c, e, "end capture"));
+    m->launches_per_step = c->launches - before;
+    c->launches = before;    // captured launches are counted when the graph is replayed
+    e = cudaGraphInstantiate(&m->decode_graph, graph, 0);
+    cudaGraphDestroy(graph);
+    M_TRY(cuda_status(c, e, "graph instantiate"));
+    M_TRY(cuda_status(c, cudaMemset(m->k_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
+    M_TRY(cuda_status(c, cudaMemset(m->v_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
+    m->finalized = true;
+    return GGB_OK;
+}
+
+int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int pos0, float* host_logits, int32_t* next_token) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "prefill: model not finalized");
+    if (!host_tokens || n_tok <= 0 || pos0 < 0 || pos0 + n_tok > m->d.ctx) return set_status(c, GGB_INVALID_PARAM, "prefill: bad arguments");
+    GGB_LOCK(c);
+    for (int t0 = 0; t0 < n_tok; t0 += kMaxChunk) {
+        const int n = std::min(kMaxChunk, n_tok - t0);
+        M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, host_tokens + t0, sizeof(int32_t) * n, cudaMemcpyHostToDevice, c->stream), "token upload"));
+        M_TRY(enqueue_forward(m, n, false, pos0 + t0));
+    }
+    if (host_logits) M_TRY(cuda_status(c, cudaMemcpyAsync(host_logits, m->logits, sizeof(float) * m->d.vocab, cudaMemcpyDeviceToHost, c->stream), "logits download"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 2, m->d_next, 4, cudaMemcpyDeviceToHost, c->stream), "token download"));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "prefill"));
+    if (next_token) *next_token = m->h_io[2];
+    return GGB_OK;
+}
+
+int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, int32_t* next_token) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "decode: model not finalized");
+    if (pos < 0 || pos >= m->d.ctx || token < 0 || token >= m->d.vocab) return set_status(c, GGB_INVALID_PARAM, "decode: token or position out of range");
+    GGB_LOCK(c);
+    m->h_io[0] = token; m->h_io[1] = pos;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(cuda_status(c, cudaGraphLaunch(m->decode_graph, c->stream), "graph launch"));
+    c->launches += m->launches_per_step;
+    if (host_logits) M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_logits, m->logits, sizeof(float) * m->d.vocab, cudaMemcpyDeviceToHost, c->stream), "logits download"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 2, m->d_next, 4, cudaMemcpyDeviceToHost, c->stream), "token download"));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "decode"));
+    if (host_logits) memcpy(host_logits, m->h_logits, sizeof(float) * m->d.vocab);
+    if (next_token) *next_token = m->h_io[2];
+    return GGB_OK;
+}
+
+int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_t* host_out) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate: model not finalized");
+    if (n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || first_token < 0 || first_token >= m->d.vocab || !host_out)
+        return set_status(c, GGB_INVALID_PARAM, "generate: bad arguments");
+    GGB_LOCK(c);
+    m->h_io[0] = first_token; m->h_io[1] = pos0; m->h_io[3] = 0;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_step, m->h_io + 3, 4, cudaMemcpyHostToDevice, c->stream), "step upload"));
+    for (int i = 0; i < n; ++i) M_TRY(cuda_status(c, cudaGraphLaunch(m->decode_graph, c->stream), "graph launch"));
+    c->launches += m->launches_per_step * n;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(host_out, m->d_gen, sizeof(int32_t) * n, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
+    return cuda_status(c, cudaStreamSynchronize(c->stream), "generate");
+}
+
+int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized || !host_out || layer < 0 || layer >= m->d.n_layer || pos < 0 || pos >= m->d.ctx) return set_status(c, GGB_INVALID_PARAM, "read_kv: bad arguments");
+    GGB_LOCK(c);
+    const int hd = m->d.head_dim;
+    std::vector<__nv_bfloat16> tmp(hd);
+    const __nv_bfloat16* base = (want_v ? m->v_cache : m->k_cache) + static_cast<size_t>(layer) * m->kv_layer_elems;
+    const int page = pos / m->page, slot = pos % m->page;   // identity block table
+    for (int h = 0; h < m->d.n_kv; ++h) {
+        const size_t o = ((static_cast<size_t>(page) * m->d.n_kv + h) * m->page + slot) * hd;
+        M_TRY(cuda_status(c, cudaMemcpy(tmp.data(), base + o, sizeof(__nv_bfloat16) * hd, cudaMemcpyDeviceToHost), "kv download"));
+        for (int i = 0; i < hd; ++i) host_out[h * hd + i] = __bfloat162float(tmp[i]);
+    }
+    return GGB_OK;
+}
+
+uint64_t ggb_model_decode_bytes(ggb_model m, int pos) {
+    if (!m || !m->finalized) return 0;
+    const ggb_model_desc& d = m->d;
+    auto wb = [](const DeviceWeight* w) -> uint64_t {
+        if (!w) return 0;
+        const FormatInfo f = format_info(w->w.type);
+        return static_cast<uint64_t>(w->w.N) * w->w.nb * f.block_bytes;
+    };
+    uint64_t b = wb(m->output ? m->output : m->tok_embd);
+    for (const Layer& l : m->layers) b += wb(l.q) + wb(l.k) + wb(l.v) + wb(l.o) + wb(l.gate) + wb(l.up) + wb(l.down);
+    b += static_cast<uint64_t>(d.hidden) * 4 * (2 * d.n_layer + 1);                        // norm gammas
+    b += static_cast<uint64_t>(2) * d.n_layer * (pos + 1) * d.n_kv * d.head_dim * 2;       // K and V read, bf16
+    const FormatInfo fe = format_info(m->tok_embd->w.type);
+    b += static_cast<uint64_t>(m->tok_embd->w.nb) * fe.block_bytes;                        // one embedding row
+    return b;
+}
+
+}  // extern "C"

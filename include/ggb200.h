@@ -1,0 +1,235 @@
+/*
+ * ggb200.h -- C ABI of libggb200.so, a CUDA (sm_100a) implementation of the
+ * ggnpu Backend operator set.
+ *
+ * Part 1 mirrors ggnpu's plugin boundary one to one: every function takes the
+ * same parameter block, with the same field order, types and meaning, as the
+ * C++ method it stands in for (include/ggnpu/backend.h), uses HOST pointers
+ * owned by the caller, and returns the integer value of ggnpu::Status.
+ * Part 2 is the device-resident path (weights packed once into HBM, paged bf16
+ * KV cache, whole decode step as one CUDA graph); it has no counterpart in the
+ * reference, whose only caller keeps every activation in host memory.
+ *
+ * No function throws, aborts, or falls back to the CPU.  Every failure is a
+ * status code plus a message kept per handle (ggb_last_error_message).
+ */
+#ifndef GGB200_H
+#define GGB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GGB_API __attribute__((visibility("default")))
+#else
+#define GGB_API
+#endif
+
+/* ggnpu::Status, include/ggnpu/backend.h:12-19 (same integer values). */
+enum ggb_status {
+    GGB_OK = 0,
+    GGB_ERROR = 1,
+    GGB_NOT_FOUND = 2,
+    GGB_INVALID_PARAM = 3,
+    GGB_UNAVAILABLE = 4, /* NPU_UNAVAILABLE: no usable CUDA device */
+    GGB_OUT_OF_MEMORY = 5
+};
+
+/* ggml type ids as in ggnpu::GgmlType, include/ggnpu/tensor.h:11-42. */
+enum ggb_type {
+    GGB_F32 = 0, GGB_F16 = 1, GGB_Q4_0 = 2, GGB_Q4_1 = 3, GGB_Q8_0 = 8, GGB_Q2_K = 10, GGB_Q3_K = 11,
+    GGB_Q4_K = 12, GGB_Q5_K = 13, GGB_Q6_K = 14, GGB_IQ4_NL = 20, GGB_IQ4_XS = 23, GGB_BF16 = 30
+};
+
+typedef struct ggb_context* ggb_handle;
+
+/* ---------------------------------------------------------------------------
+ * Part 1: the Backend operator set (host pointers, f32 activations)
+ * ------------------------------------------------------------------------- */
+
+/* ggnpu::MulMatParams, include/ggnpu/backend.h:21-35.  C[M,N] = A[M,K] * W^T.
+ * For a quantised B_type, B is raw GGUF bytes: N rows of ceil(K/blk) blocks
+ * (what the reference hands any backend whose name is not "amd_xdna",
+ * src/cli/main.cpp:1430-1432).  For F32, B is [K][N] as in
+ * src/backends/cpu_ref/cpu_ref.cpp:119-133.  ldb, scales, n_weight_scales and
+ * n_batches are accepted and ignored, as both reference backends do for
+ * quantised weights.  B is cached by (pointer, N, K, type): the first call
+ * uploads and packs it, later calls reuse the HBM copy, so B must stay valid
+ * and unchanged while the handle lives (the reference passes mmap'd weights). */
+typedef struct ggb_mul_mat_params {
+    const void* A;
+    const void* B;
+    void* C;
+    int M, N, K;
+    int lda, ldb, ldc;
+    int32_t n_batches;
+    const void* scales;
+    int n_weight_scales;
+    uint32_t B_type;
+} ggb_mul_mat_params;
+
+/* ggnpu::RmsNormParams, include/ggnpu/backend.h:37-43. */
+typedef struct ggb_rms_norm_params {
+    const float* input;
+    float* output;
+    int size;
+    float eps;
+    const float* weight; /* may be NULL */
+} ggb_rms_norm_params;
+
+/* ggnpu::RopeParams, include/ggnpu/backend.h:45-62.  Rotates data in place. */
+typedef struct ggb_rope_params {
+    float* data;
+    int n_dims;
+    int64_t offset;
+    float freq_scale;
+    float freq_base;
+    int64_t rope_dims;
+    const float* cos_table; /* optional [rope_dims/2]; with sin_table overrides the angles */
+    const float* sin_table;
+    uint8_t neox_split_half;
+} ggb_rope_params;
+
+/* ggnpu::RopeBatchedParams, include/ggnpu/backend.h:68-79. */
+typedef struct ggb_rope_batched_params {
+    float* data; /* [n_heads][n_dims] */
+    int n_heads;
+    int n_dims;
+    int64_t offset;
+    float freq_scale;
+    float freq_base;
+    int64_t rope_dims;
+    const float* cos_table;
+    const float* sin_table;
+    uint8_t neox_split_half;
+} ggb_rope_batched_params;
+
+/* ggnpu::SoftmaxParams / SiluParams / GeluParams, include/ggnpu/backend.h:81-98. */
+typedef struct ggb_softmax_params { const float* input; float* output; int rows; int cols; } ggb_softmax_params;
+typedef struct ggb_unary_params { const float* input; float* output; int size; } ggb_unary_params;
+
+/* ggnpu::AttnParams, include/ggnpu/backend.h:100-111.  Q [n_head][head_dim];
+ * K,V [n_head][ctx_len][head_dim] already expanded per query head; keys after
+ * query_pos are masked; query_pos < 0 means ctx_len-1; scale 1/sqrt(head_dim). */
+typedef struct ggb_attn_params {
+    const float* Q;
+    const float* K;
+    const float* V;
+    float* output;
+    int batch_size;
+    int n_head;
+    int head_dim;
+    int64_t ctx_len;
+    int64_t query_pos;
+    const float* freq_factors; /* unused, as in the reference */
+} ggb_attn_params;
+
+/* Factory + lifetime.  Replaces ggnpu::create_amd_xdna_backend(int),
+ * include/ggnpu/backend.h:162-165 (defined src/backends/amd_xdna/amd_xdna.cpp:3104-3111).
+ * Returns GGB_UNAVAILABLE when the device cannot be used. */
+GGB_API int ggb_create(int device, ggb_handle* out);
+GGB_API void ggb_destroy(ggb_handle h);
+
+/* Backend::mul_mat_q, include/ggnpu/backend.h:117. */
+GGB_API int ggb_mul_mat_q(ggb_handle h, const ggb_mul_mat_params* p);
+/* Backend::rms_norm, include/ggnpu/backend.h:118. */
+GGB_API int ggb_rms_norm(ggb_handle h, const ggb_rms_norm_params* p);
+/* Backend::rope, include/ggnpu/backend.h:119. */
+GGB_API int ggb_rope(ggb_handle h, const ggb_rope_params* p);
+/* Backend::rope_batched, include/ggnpu/backend.h:123-140. */
+GGB_API int ggb_rope_batched(ggb_handle h, const ggb_rope_batched_params* p);
+/* Backend::matmul_bf16, include/ggnpu/backend.h:146-150: C[M,N] = A[M,K] B[K,N],
+ * f32 host buffers. */
+GGB_API int ggb_matmul_bf16(ggb_handle h, const float* A, const float* B, float* C, int M, int N, int K);
+/* Backend::softmax / silu / gelu / flash_attn, include/ggnpu/backend.h:152-155. */
+GGB_API int ggb_softmax(ggb_handle h, const ggb_softmax_params* p);
+GGB_API int ggb_silu(ggb_handle h, const ggb_unary_params* p);
+GGB_API int ggb_gelu(ggb_handle h, const ggb_unary_params* p);
+GGB_API int ggb_flash_attn(ggb_handle h, const ggb_attn_params* p);
+/* Backend::sync / is_available / name / last_error, include/ggnpu/backend.h:156-160. */
+GGB_API void ggb_sync(ggb_handle h);
+GGB_API int ggb_is_available(ggb_handle h);
+GGB_API const char* ggb_name(ggb_handle h); /* "cuda_b200" */
+GGB_API int ggb_last_error(ggb_handle h);
+GGB_API const char* ggb_last_error_message(ggb_handle h);
+
+/* ---------------------------------------------------------------------------
+ * Part 2: device-resident path
+ * ------------------------------------------------------------------------- */
+
+/* Block decode on the GPU (the role of dequant_*_block, include/ggnpu/quant/kquant.h:70-202
+ * and src/quant/q*.cpp, and of dequant_tensor_row, src/cli/main.cpp:36-261): host bytes of
+ * N rows x K values in, fp32 [n_rows][K] out for rows row0..row0+n_rows-1.  The bytes go
+ * through the same pack-into-HBM step as every weight, so this also checks the re-layout. */
+GGB_API int ggb_dequant_rows(ggb_handle h, uint32_t type, const void* host_bytes, int64_t N, int K,
+                             int64_t row0, int64_t n_rows, float* host_out);
+
+typedef struct ggb_weight_s* ggb_weight;
+
+/* Pack a [N][K] matrix of the given type into HBM (what src/quant's decode_*_for_npu plus the
+ * WeightCache of include/ggnpu/weight_cache.h:34-158 do for the NPU: one-time conversion of
+ * GGUF bytes into the device's layout).  host_rows may be freed after the call returns. */
+GGB_API int ggb_weight_upload(ggb_handle h, uint32_t type, int64_t N, int K, const void* host_rows, ggb_weight* out);
+GGB_API void ggb_weight_free(ggb_handle h, ggb_weight w);
+GGB_API size_t ggb_weight_bytes(ggb_weight w);
+
+/* y[M][ldc] = x[M][lda] * W^T with DEVICE pointers, M <= 16 (decode GEMV), on the handle's
+ * stream.  epilogue: 0 store; 1 + bias[N]; 2 + resid[M][ldc].  gamma != NULL applies RMSNorm
+ * (eps) to each x row first.  Asynchronous. */
+GGB_API int ggb_gemv_device(ggb_handle h, ggb_weight w, const float* d_x, int M, int lda, float* d_y, int ldc,
+                            int epilogue, const float* d_extra, const float* d_gamma, float eps);
+/* Fused SwiGLU pair: y = silu(Wg x) * (Wu x)  (src/cli/main.cpp:3449-3479 in one pass). */
+GGB_API int ggb_gemv_swiglu_device(ggb_handle h, ggb_weight w_gate, ggb_weight w_up, const float* d_x, int M, int lda,
+                                   float* d_y, int ldc, const float* d_gamma, float eps);
+
+/* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
+GGB_API void* ggb_stream(ggb_handle h);
+/* Number of kernels this library has launched on the handle so far. */
+GGB_API uint64_t ggb_launch_count(ggb_handle h);
+
+/* ---- whole-model path (generic llama / qwen2 / qwen3 graph, src/cli/main.cpp:3235-3512) ---- */
+
+typedef struct ggb_model_desc {
+    int n_layer, hidden, n_head, n_kv, head_dim, ffn, vocab, ctx;
+    float rms_eps, rope_base, rope_scale;
+    int rope_neox;   /* 1: split-half pairs (qwen3); 0: adjacent pairs (llama, qwen2) */
+    int kv_page;     /* tokens per KV page; 0 = default (64) */
+} ggb_model_desc;
+
+typedef struct ggb_model_s* ggb_model;
+
+enum ggb_tensor_slot {
+    GGB_T_TOKEN_EMBD = 0, GGB_T_OUTPUT = 1, GGB_T_OUTPUT_NORM = 2, GGB_T_ROPE_FREQS = 3,
+    GGB_T_ATTN_NORM = 10, GGB_T_ATTN_Q = 11, GGB_T_ATTN_K = 12, GGB_T_ATTN_V = 13, GGB_T_ATTN_OUT = 14,
+    GGB_T_FFN_NORM = 15, GGB_T_FFN_GATE = 16, GGB_T_FFN_UP = 17, GGB_T_FFN_DOWN = 18,
+    GGB_T_BIAS_Q = 19, GGB_T_BIAS_K = 20, GGB_T_BIAS_V = 21, GGB_T_Q_NORM = 22, GGB_T_K_NORM = 23
+};
+
+GGB_API int ggb_model_create(ggb_handle h, const ggb_model_desc* desc, ggb_model* out);
+GGB_API void ggb_model_destroy(ggb_model m);
+/* One tensor of the model: matrices as GGUF rows ([N][K] of `type`), vectors as F32. */
+GGB_API int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_t N, int K, const void* host_data);
+/* Allocate KV pages, build the RoPE table (RopeCache::build, src/cli/main.cpp:665-692) and
+ * capture the decode graph.  Call once after all tensors are set. */
+GGB_API int ggb_model_finalize(ggb_model m);
+/* Forward over n_tok prompt tokens at positions pos0.. (writes KV); logits of the LAST row to
+ * host_logits (may be NULL), greedy token to *next_token (may be NULL). */
+GGB_API int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int pos0, float* host_logits, int32_t* next_token);
+/* One decode step from host buffers: token in, logits (optional) and greedy next token out. */
+GGB_API int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, int32_t* next_token);
+/* n greedy decode steps with the token fed back on the device (no host round trip inside);
+ * the n generated ids land in host_out afterwards. */
+GGB_API int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_t* host_out);
+/* Read back one KV row [n_kv][head_dim] as f32 (tests). */
+GGB_API int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out);
+/* Algorithmic HBM bytes one decode step at position pos reads+writes (weights once + KV). */
+GGB_API uint64_t ggb_model_decode_bytes(ggb_model m, int pos);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GGB200_H */

@@ -1,0 +1,116 @@
+"""Regenerate tests/golden/*.npz from the reference's own compiled code.
+
+Run where the reference tree is available:
+
+    make -C oracle ref REF=/path/to/ggnpu && python tests/golden/make_golden.py
+
+Every array stored here is an INPUT (seeded random bytes / floats) or an OUTPUT of
+the reference's functions on that input (oracle/_ref/libggnpu_ref.so, built from
+the unmodified reference sources).  Tests then hold the C restatement and the
+CUDA path to these outputs on machines where the reference tree is absent.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from ggnpu_b200 import synth as S  # noqa: E402
+from oracle.binding import Ref, run_ref_cli  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main():
+    ref = Ref()
+    out = {}
+    # 1. block decoders: 24 random blocks per format + 8 blocks from the quantiser
+    for t in S.QUANT_TYPES:
+        be, bb = S.BLOCK[t]
+        blk = S.random_blocks(t, 24, seed=100 + t)
+        import torch
+        g = torch.Generator().manual_seed(200 + t)
+        x = torch.randn(2, 4 * be if be == 256 else 32 * 4, generator=g) * 0.02
+        qb = S.quantize(x, t).numpy().reshape(-1, bb)
+        allb = np.concatenate([blk, qb])
+        out[f"dq_in_{t}"] = allb
+        out[f"dq_out_{t}"] = ref.dequant_blocks(t, allb)
+    # fp16 / bf16 scalar conversions over every 16-bit pattern (finite or not)
+    h = np.arange(65536, dtype=np.uint32)
+    out["f16_all"] = np.array([ref.lib.ref_f16_to_f32(int(v)) for v in h], dtype=np.float32).view(np.uint32)
+    out["kq_f16_all"] = np.array([ref.lib.ref_kquant_fp16_to_f32(int(v)) for v in h], dtype=np.float32).view(np.uint32)
+    rng = np.random.default_rng(5)
+    fl = rng.standard_normal(4096).astype(np.float32) * np.float32(10.0) ** rng.integers(-6, 6, 4096).astype(np.float32)
+    out["bf16_in"] = fl
+    out["bf16_out"] = np.array([ref.lib.ref_f32_to_bf16(float(v)) for v in fl], dtype=np.uint16)
+    # 2. operators of the CPU backend
+    x = (rng.random(2048).astype(np.float32) - 0.5)
+    w = (1.0 + 0.1 * rng.standard_normal(2048)).astype(np.float32)
+    out["rms_x"], out["rms_w"] = x, w
+    out["rms_y"] = ref.rms_norm(x, 1e-5, w)[1]
+    out["silu_y"] = ref.silu(x)[1]
+    out["gelu_y"] = ref.gelu(x)[1]
+    sm = rng.standard_normal((4, 40)).astype(np.float32)
+    out["softmax_x"], out["softmax_y"] = sm, ref.softmax(sm)[1]
+    Q = rng.standard_normal((4, 64)).astype(np.float32)
+    K = rng.standard_normal((4, 40, 64)).astype(np.float32)
+    V = rng.standard_normal((4, 40, 64)).astype(np.float32)
+    out["attn_q"], out["attn_k"], out["attn_v"] = Q, K, V
+    out["attn_full"] = ref.flash_attn(Q, K, V, -1)[1]
+    out["attn_causal17"] = ref.flash_attn(Q, K, V, 17)[1]
+    r = rng.standard_normal(64).astype(np.float32)
+    out["rope_x"] = r
+    out["rope_y"] = ref.rope(r, 64, 5, 1.0, 10000.0, 64)[1]
+    c, s = ref.rope_table(48, 64, 1.0, 500000.0)
+    out["rope_tab_cos"], out["rope_tab_sin"] = c, s
+    ff = (1.0 + rng.random(32)).astype(np.float32)
+    c2, s2 = ref.rope_table(16, 64, 1.0, 1e6, ff)
+    out["rope_ff"], out["rope_tab_cos_ff"], out["rope_tab_sin_ff"] = ff, c2, s2
+    # 3. matmul: the exact path for every format, and the CPU backend's K-quant path
+    A = rng.standard_normal((3, 512)).astype(np.float32)
+    out["mm_A"] = A
+    for t in S.QUANT_TYPES + [S.BF16, S.F16]:
+        import torch
+        g = torch.Generator().manual_seed(300 + t)
+        wq = S.quantize(torch.randn(24, 512, generator=g) * 0.02, t).numpy()
+        out[f"mm_W_{t}"] = wq
+        out[f"mm_exact_{t}"] = ref.matmul_exact(A, wq, t, 24, 512)
+        if t in (S.Q4_K, S.Q6_K):
+            out[f"mm_cpuref_{t}"] = ref.mul_mat_q(A, wq, t, 24, 512)[1]
+    np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **out)
+
+    # 4. end to end: the reference CLI on two tiny seeded models (top-10 logits after the prompt and
+    #    the greedy continuation), exact fp32 matmul path.
+    e2e = {}
+    cases = {"llama": S.tiny_config(seed=11), "qwen2": S.tiny_config(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12,
+                                                                      rope_base=1e6, tied=False)}
+    for name, cfg in cases.items():
+        m = S.build_model(cfg)
+        path = f"/tmp/ggb_golden_{name}.gguf"
+        m.write(path)
+        ids = np.random.default_rng(42).integers(0, cfg.vocab, 7)
+        r1 = run_ref_cli(path, S.prompt_text(ids), 0, ctx=cfg.ctx, bench_logits=True)
+        top = []
+        for line in (r1.stdout + r1.stderr).splitlines():
+            line = line.strip()
+            if line.startswith("top") and "id=" in line:
+                tid = int(line.split("id=")[1].split()[0])
+                lg = float(line.split("logit=")[1].split()[0])
+                top.append((tid, lg))
+        assert len(top) == 10, (r1.stdout, r1.stderr)
+        r2 = run_ref_cli(path, S.prompt_text(ids), 6, ctx=cfg.ctx)
+        gen = S.text_ids(r2.stdout)
+        assert len(gen) == 6, (r2.stdout, r2.stderr)
+        e2e[f"{name}_prompt"] = ids.astype(np.int32)
+        e2e[f"{name}_top_ids"] = np.array([t for t, _ in top], dtype=np.int32)
+        e2e[f"{name}_top_logits"] = np.array([v for _, v in top], dtype=np.float32)
+        e2e[f"{name}_greedy"] = np.array(gen, dtype=np.int32)
+        os.remove(path)
+    np.savez_compressed(os.path.join(HERE, "ref_cli.npz"), **e2e)
+    print("wrote", os.path.join(HERE, "ref_vectors.npz"), os.path.join(HERE, "ref_cli.npz"))
+
+
+if __name__ == "__main__":
+    main()

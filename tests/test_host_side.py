@@ -1,0 +1,86 @@
+"""CPU-only checks of the host side: the C-ABI library builds, loads and exports every symbol
+the header declares; the synthetic-model tooling produces decodable GGUF files."""
+import os
+import re
+import struct
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, bits
+from ggnpu_b200 import synth as S
+
+
+def test_library_exports_every_declared_symbol():
+    from ggnpu_b200.build import build
+    from ggnpu_b200 import backend as B
+    path = build()
+    assert os.path.exists(path)
+    hdr = open(os.path.join(ROOT, "include", "ggb200.h")).read()
+    declared = set(re.findall(r"GGB_API\s+[\w\s\*]+?\b(ggb_\w+)\s*\(", hdr))
+    assert declared, "no declarations found"
+    lib = B.load_library()
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in ggb200.h but not exported"
+    assert declared == set(B.EXPORTS)
+
+
+def test_struct_layouts_match_reference_field_order():
+    # field order of include/ggnpu/backend.h:21-111
+    from ggnpu_b200 import backend as B
+    assert [f[0] for f in B.MulMatParams._fields_] == ["A", "B", "C", "M", "N", "K", "lda", "ldb", "ldc", "n_batches",
+                                                        "scales", "n_weight_scales", "B_type"]
+    assert [f[0] for f in B.AttnParams._fields_] == ["Q", "K", "V", "output", "batch_size", "n_head", "head_dim",
+                                                      "ctx_len", "query_pos", "freq_factors"]
+    assert [int(s) for s in B.Status] == [0, 1, 2, 3, 4, 5]
+
+
+def test_no_gpu_means_unavailable_not_fallback():
+    """Without a usable device the factory reports NPU_UNAVAILABLE (as create_amd_xdna_backend's
+    caller sees is_available()==false); it never substitutes a CPU path."""
+    import torch
+    from ggnpu_b200 import backend as B
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(B.BackendError) as e:
+        B.CudaBackend(0)
+    assert e.value.status == B.Status.NPU_UNAVAILABLE
+
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES)
+def test_quantiser_emits_valid_blocks(oracle, t):
+    import torch
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(4, 1024, generator=g) * 0.02
+    raw = S.quantize(x, t).numpy()
+    assert raw.shape == (4, S.row_bytes(t, 1024))
+    y = oracle.dequant_blocks(t, raw).reshape(4, 1024)
+    err = np.linalg.norm(y - x.numpy()) / np.linalg.norm(x.numpy())
+    assert err < {S.Q2_K: 0.45, S.Q3_K: 0.25}.get(t, 0.12)
+
+
+def test_gguf_writer_layout(tmp_path):
+    cfg = S.tiny_config(n_layer=1, vocab=64)
+    m = S.build_model(cfg)
+    p = tmp_path / "t.gguf"
+    m.write(str(p))
+    blob = p.read_bytes()
+    magic, ver, n_t, n_kv = struct.unpack_from("<IIQQ", blob, 0)
+    assert magic == 0x46554747 and ver == 3 and n_t == len(m.tensors) and n_kv == len(m.kv())
+    # tensor data is appended in order, 32-byte aligned; the last tensor's bytes end the file
+    last = list(m.tensors.values())[-1][2]
+    tail = blob[len(blob) - ((last.nbytes + 31) // 32 * 32):][:last.nbytes]
+    assert tail == last.tobytes()
+
+
+def test_reference_cli_reads_our_gguf(tmp_path):
+    from oracle.binding import REF_CLI, run_ref_cli
+    if not os.path.exists(REF_CLI):
+        pytest.skip("reference CLI not built")
+    cfg = S.tiny_config(n_layer=1, vocab=96, seed=3)
+    m = S.build_model(cfg)
+    p = tmp_path / "t.gguf"
+    m.write(str(p))
+    r = run_ref_cli(str(p), S.prompt_text([5, 9, 2]), 3, ctx=cfg.ctx, timeout=120)
+    assert r.returncode == 0, r.stderr
+    assert len(S.text_ids(r.stdout)) == 3

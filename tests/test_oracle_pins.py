@@ -1,0 +1,182 @@
+"""Pins the CPU oracle (oracle/ggb_oracle.c) to the reference: against the reference's own
+compiled functions where oracle/_ref exists, against the committed outputs of those functions
+(tests/golden/ref_vectors.npz, ref_cli.npz), and against the known answers written in the
+reference's tests/test_quant.cpp and tests/test_arch.cpp."""
+import numpy as np
+import pytest
+
+from conftest import bits, rel_l2
+from ggnpu_b200 import synth as S
+
+
+def f16_bytes(v):
+    return np.array([v], dtype=np.float16).view(np.uint8)
+
+
+# ---- known answers from the reference's unit tests --------------------------------------------
+
+def test_q4_k_golden_block(oracle):
+    # tests/test_quant.cpp:209-247: d=0.5, dmin=0.25, scales 0..3 = 2, mins 0..3 = 1, qs[0]=0x31
+    b = np.zeros(144, dtype=np.uint8)
+    b[0:2], b[2:4] = f16_bytes(0.5), f16_bytes(0.25)
+    b[4:8], b[8:12] = 2, 1
+    b[16] = 0x31
+    y = oracle.dequant_blocks(S.Q4_K, b)
+    assert y[0] == 0.75 and y[1] == -0.25 and y[32] == 2.75
+
+
+def test_q6_k_golden_block(oracle):
+    # tests/test_quant.cpp:249-288: d=0.25, scales[0]=4, scales[4]=2, ql[0]=0x21
+    b = np.zeros(210, dtype=np.uint8)
+    b[208:210] = f16_bytes(0.25)
+    b[192], b[196], b[0] = 4, 2, 0x21
+    y = oracle.dequant_blocks(S.Q6_K, b)
+    assert y[0] == -31.0 and y[64] == -15.0 and y[1] == -32.0
+
+
+def test_q4_0_q8_0_known_answers(oracle):
+    # tests/test_quant.cpp:105-150: d=1.0; Q4_0 qs[0]=0x11 -> value[0] = -7, value[1] = -8, value[16] = -7
+    b = np.zeros(18, dtype=np.uint8)
+    b[0:2], b[2] = f16_bytes(1.0), 0x11
+    y = oracle.dequant_blocks(S.Q4_0, b)
+    assert y[0] == -7.0 and y[1] == -8.0 and y[16] == -7.0
+    b = np.zeros(34, dtype=np.uint8)
+    b[0:2], b[2], b[33] = f16_bytes(1.0), 3, 1
+    y = oracle.dequant_blocks(S.Q8_0, b)
+    assert y[0] == 3.0 and y[31] == 1.0 and y[1] == 0.0
+
+
+def test_block_geometry(oracle):
+    # tests/test_quant.cpp:194-207, 294-317; tests/test_gguf.cpp:42-73
+    for t, (be, bb) in S.BLOCK.items():
+        assert oracle.block_geom(t) == (be, bb)
+
+
+def test_cpu_ref_op_known_answers(oracle):
+    # tests/test_arch.cpp:95-135, 223-249
+    y = oracle.rms_norm(np.array([3.0, 4.0], np.float32), 1e-5)
+    assert abs(y[0] - 0.8485) < 1e-3 and abs(y[1] - 1.1314) < 1e-3
+    s = oracle.silu(np.array([0.0, 1.0, -1.0], np.float32))
+    assert abs(s[0]) < 1e-3 and abs(s[1] - 0.7311) < 1e-3 and abs(s[2] + 0.2689) < 1e-3
+    sm = oracle.softmax(np.array([[1.0, 2.0, 3.0]], np.float32))
+    assert abs(sm.sum() - 1.0) < 1e-6
+    o = oracle.flash_attn(np.array([[1.0, 0.0]], np.float32), np.array([[[1.0, 0.0], [0.0, 1.0]]], np.float32),
+                          np.array([[[1.0, 0.0], [0.0, 1.0]]], np.float32))
+    assert abs(o[0, 0] - 0.670) < 1e-2 and abs(o[0, 1] - 0.330) < 1e-2
+    # all-ones matmul: C == K (src/cli/main.cpp:809-825)
+    c = oracle.matmul_f32_kn(np.ones((4, 256), np.float32), np.ones((256, 8), np.float32))
+    assert np.all(c == 256.0)
+
+
+# ---- committed outputs of the reference's functions -------------------------------------------
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES)
+def test_dequant_matches_reference_vectors(oracle, vectors, t):
+    got = oracle.dequant_blocks(t, vectors[f"dq_in_{t}"])
+    assert np.array_equal(bits(got), bits(vectors[f"dq_out_{t}"]))
+
+
+def test_scalar_conversions_match_reference_vectors(oracle, vectors):
+    got = np.array([oracle.lib.ggo_f16_to_f32(int(h)) for h in range(65536)], dtype=np.float32).view(np.uint32)
+    assert np.array_equal(got, vectors["f16_all"])
+    assert np.array_equal(got, vectors["kq_f16_all"])
+    got = np.array([oracle.lib.ggo_f32_to_bf16(float(v)) for v in vectors["bf16_in"]], dtype=np.uint16)
+    assert np.array_equal(got, vectors["bf16_out"])
+
+
+def test_ops_match_reference_vectors(oracle, vectors):
+    v = vectors
+    assert np.array_equal(bits(oracle.rms_norm(v["rms_x"], 1e-5, v["rms_w"])), bits(v["rms_y"]))
+    assert np.array_equal(bits(oracle.silu(v["rms_x"])), bits(v["silu_y"]))
+    assert np.array_equal(bits(oracle.gelu(v["rms_x"])), bits(v["gelu_y"]))
+    assert np.array_equal(bits(oracle.softmax(v["softmax_x"])), bits(v["softmax_y"]))
+    assert np.array_equal(bits(oracle.flash_attn(v["attn_q"], v["attn_k"], v["attn_v"], -1)), bits(v["attn_full"]))
+    assert np.array_equal(bits(oracle.flash_attn(v["attn_q"], v["attn_k"], v["attn_v"], 17)), bits(v["attn_causal17"]))
+    assert np.array_equal(bits(oracle.rope_cpu_ref(v["rope_x"], 64, 5, 1.0, 64)), bits(v["rope_y"]))
+    c, s = oracle.rope_table(48, 64, 1.0, 500000.0)
+    assert np.array_equal(bits(c), bits(v["rope_tab_cos"])) and np.array_equal(bits(s), bits(v["rope_tab_sin"]))
+    c, s = oracle.rope_table(16, 64, 1.0, 1e6, v["rope_ff"])
+    assert np.array_equal(bits(c), bits(v["rope_tab_cos_ff"])) and np.array_equal(bits(s), bits(v["rope_tab_sin_ff"]))
+
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES + [S.BF16, S.F16])
+def test_matmul_matches_reference_vectors(oracle, vectors, t):
+    got = oracle.matmul_exact(vectors["mm_A"], vectors[f"mm_W_{t}"], t, 24, 512)
+    assert np.array_equal(bits(got), bits(vectors[f"mm_exact_{t}"]))
+    if t in (S.Q4_K, S.Q6_K):
+        got = oracle.matmul_cpu_ref_k(vectors["mm_A"], vectors[f"mm_W_{t}"], t, 24, 512)
+        assert np.array_equal(bits(got), bits(vectors[f"mm_cpuref_{t}"]))
+
+
+CLI_CASES = {"llama": dict(seed=11), "qwen2": dict(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12,
+                                                    rope_base=1e6, tied=False)}
+
+
+@pytest.mark.parametrize("name", list(CLI_CASES))
+def test_forward_matches_reference_cli(oracle, cli_vectors, name):
+    """The restated layer loop against what the unmodified reference CLI printed for the same
+    seeded model and prompt: top-10 ids in order, logits to the 6 digits it prints, greedy stream."""
+    from oracle.binding import OracleModel
+    cfg = S.tiny_config(**CLI_CASES[name])
+    om = OracleModel(oracle, S.build_model(cfg))
+    ids = cli_vectors[f"{name}_prompt"]
+    pos = 0
+    for tkn in ids[:-1]:          # one token per forward, as GGNPU_NO_PREFILL_BATCH does
+        om.forward([tkn], pos, want_logits=False)
+        pos += 1
+    logits = om.forward([ids[-1]], pos)
+    pos += 1
+    order = np.argsort(-logits, kind="stable")[:10]
+    assert list(order) == list(cli_vectors[f"{name}_top_ids"])
+    assert np.allclose(logits[order], cli_vectors[f"{name}_top_logits"], rtol=2e-6, atol=2e-6)
+    gen, tok = [], oracle.argmax_first(logits)
+    for _ in range(6):
+        gen.append(tok)
+        logits = om.forward([tok], pos)
+        pos += 1
+        tok = oracle.argmax_first(logits)
+    assert gen == list(cli_vectors[f"{name}_greedy"])
+    # batched prompt == token-by-token prompt (same arithmetic per row)
+    om2 = OracleModel(oracle, S.build_model(cfg))
+    l2 = om2.forward(ids, 0)
+    pos2 = len(ids)
+    l1 = OracleModel(oracle, S.build_model(cfg))
+    for i, tkn in enumerate(ids):
+        last = l1.forward([tkn], i)
+    assert np.array_equal(bits(l2), bits(last))
+
+
+# ---- live comparison with the reference's compiled functions ----------------------------------
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES)
+def test_dequant_matches_reference_live(oracle, ref, t):
+    blk = S.random_blocks(t, 4096, seed=t)
+    assert np.array_equal(bits(oracle.dequant_blocks(t, blk)), bits(ref.dequant_blocks(t, blk)))
+
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES + [S.BF16, S.F16, S.F32])
+def test_row_decode_and_matmul_live(oracle, ref, t):
+    import torch
+    g = torch.Generator().manual_seed(t)
+    K, N = 768, 10
+    raw = S.quantize(torch.randn(N, K, generator=g) * 0.02, t).numpy()
+    for row in (0, 7):
+        assert np.array_equal(bits(oracle.dequant_row(t, raw, row, K)), bits(ref.dequant_row(t, raw, row, K)))
+    A = np.random.default_rng(3).standard_normal((2, K)).astype(np.float32)
+    assert np.array_equal(bits(oracle.matmul_exact(A, raw, t, N, K)), bits(ref.matmul_exact(A, raw, t, N, K)))
+
+
+def test_ops_live(oracle, ref):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal(1536).astype(np.float32)
+    w = rng.standard_normal(1536).astype(np.float32)
+    assert np.array_equal(bits(oracle.rms_norm(x, 1e-6, w)), bits(ref.rms_norm(x, 1e-6, w)[1]))
+    assert np.array_equal(bits(oracle.silu(x)), bits(ref.silu(x)[1]))
+    Q = rng.standard_normal((3, 128)).astype(np.float32)
+    K = rng.standard_normal((3, 9, 128)).astype(np.float32)
+    V = rng.standard_normal((3, 9, 128)).astype(np.float32)
+    for qp in (-1, 0, 4):
+        assert np.array_equal(bits(oracle.flash_attn(Q, K, V, qp)), bits(ref.flash_attn(Q, K, V, qp)[1]))
+    assert oracle.argmax_first(np.array([1, 5, 5, 2], np.float32)) == ref.argmax(np.array([1, 5, 5, 2], np.float32)) == 1
+    # error statuses of the reference CPU backend (tests/test_arch.cpp:192-221)
+    assert ref.lib.ref_rms_norm(None, None, 0, 1e-5, None) == 3
