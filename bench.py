@@ -183,6 +183,8 @@ def run_reference(args):
 # GPU side
 # ---------------------------------------------------------------------------------------------
 def run_ours(args):
+    global PROMPT_LEN
+    PROMPT_LEN = args.prompt_len
     import torch
     import torch.distributed as dist
     from ggnpu_b200.backend import CudaBackend, Model
@@ -199,7 +201,7 @@ def run_ours(args):
     synth = build_synth("cuda")
     b = CudaBackend(local)
     model = Model(b, cfg, synth.tensors)
-    ids = prompt_ids(cfg)
+    ids = prompt_ids(cfg, PROMPT_LEN)
     stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
 
     def barrier():
@@ -338,6 +340,68 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """Quantised-matmul microbenchmark (weights N x K in several formats, activation rows M): one JSON
+    line per case with the kernel's average launch time and algorithmic GB/s.  Weight copies rotate
+    through more than 256 MB so every launch reads HBM, not L2.  Used for profiling single kernels:
+        python bench.py --micro --types Q4_K --shapes 8192x2048 --ms 1 --dual --reps 3"""
+    import torch
+    from ggnpu_b200.backend import CudaBackend
+    b = CudaBackend(0)
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", 0))
+    peak, peak_kind = peaks()
+    for tname in args.types.split(","):
+        t = S.TYPE_IDS[tname]
+        for shp in args.shapes.split(","):
+            N, K = (int(v) for v in shp.split("x"))
+            g = torch.Generator(device="cuda").manual_seed(7)
+            wbytes = N * S.row_bytes(t, K) * (2 if args.dual else 1)
+            copies = max(2, min(64, -(-(256 << 20) // wbytes)))
+            raw = S.quantize(torch.randn(N, K, generator=g, device="cuda") * 0.02, t).cpu().numpy()
+            ws = [b.upload_weight(t, raw, N, K) for _ in range(copies * (2 if args.dual else 1))]   # distinct HBM copies
+            for M in (int(v) for v in args.ms.split(",")):
+                x = torch.randn(M, K, device="cuda", dtype=torch.float32)
+                y = torch.empty(M, N, device="cuda", dtype=torch.float32)
+                torch.cuda.synchronize()
+
+                def one(i):
+                    if args.dual:
+                        b.gemv_swiglu_device(ws[2 * i], ws[2 * i + 1], x.data_ptr(), M, K, y.data_ptr(), N)
+                    else:
+                        b.gemv_device(ws[i], x.data_ptr(), M, K, y.data_ptr(), N)
+
+                for i in range(copies):
+                    one(i)
+                b.sync()
+                times = []
+                for _ in range(args.reps):
+                    evs = []
+                    for i in range(copies):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream); one(i); e1.record(stream)
+                        evs.append((e0, e1))
+                    b.sync()
+                    times += [e0.elapsed_time(e1) for e0, e1 in evs]
+                # back-to-back launches (no events in between): launch overhead amortised
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(args.reps):
+                    for i in range(copies):
+                        one(i)
+                e1.record(stream)
+                b.sync()
+                b2b_us = e0.elapsed_time(e1) * 1e3 / (args.reps * copies)
+                alg = wbytes + M * K * 4 + M * N * 4
+                us = float(np.mean(times)) * 1e3
+                print(json.dumps({"micro": "quant_matmul", "type": tname, "N": N, "K": K, "M": M, "dual": bool(args.dual),
+                                  "avg_launch_us": us, "back_to_back_us": b2b_us, "alg_bytes": alg, "gbs": alg / us / 1e3,
+                                  "gbs_back_to_back": alg / b2b_us / 1e3, "frac_of_hbm_peak": alg / b2b_us / 1e3 / peak,
+                                  "peak_source": peak_kind, "copies": copies}), flush=True)
+            for w in ws:
+                b.free_weight(w)
+    b.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -345,8 +409,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=128, help="prompt tokens before the timed decode (128 = the benchmark config)")
+    ap.add_argument("--micro", action="store_true", help="quantised-matmul microbenchmark instead of the decode benchmark")
+    ap.add_argument("--types", default="Q4_0,Q8_0,Q4_K,Q6_K,IQ4_XS")
+    ap.add_argument("--shapes", default="2048x2048,8192x2048,2048x8192,8960x1536")
+    ap.add_argument("--ms", default="1,16")
+    ap.add_argument("--dual", action="store_true")
+    ap.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

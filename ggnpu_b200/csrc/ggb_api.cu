@@ -3,6 +3,7 @@
 // kernels on the handle's stream and returns after the results are back in the caller's buffers,
 // which is what the reference's NPU backend does (run.wait() inside each op,
 // src/backends/amd_xdna/amd_xdna.cpp:865-897); sync() is then only a stream synchronise.
+#include <stdlib.h>
 #include <string.h>
 
 #include "ggb_internal.h"
@@ -39,6 +40,16 @@ static int d2h_sync(Context* c, void* h, const void* d, size_t n) {
     return cuda_status(c, cudaStreamSynchronize(c->stream), "stream sync");
 }
 
+int check_device_error(Context* c) {
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, c->d_err, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_status(c, e, "read device error word");
+    if (v == 0) return GGB_OK;
+    cudaMemset(c->d_err, 0, sizeof(int));
+    return set_status(c, GGB_ERROR, v == 1 ? "device: weight producer timed out waiting for a free ring stage"
+                                           : "device: consumers timed out waiting for a weight tile");
+}
+
 }  // namespace ggb
 
 using namespace ggb;
@@ -61,6 +72,11 @@ int ggb_create(int device, ggb_handle* out) {
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete c; return GGB_UNAVAILABLE; }
+    if (cudaMalloc(&c->d_err, sizeof(int)) != cudaSuccess || cudaMemset(c->d_err, 0, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError(); cudaStreamDestroy(c->stream); delete c; return GGB_OUT_OF_MEMORY;
+    }
+    c->use_pdl = getenv("GGB_NO_PDL") == nullptr;
+    c->use_tma = getenv("GGB_NO_TMA") == nullptr;
     *out = c;
     return GGB_OK;
 }
@@ -72,6 +88,7 @@ void ggb_destroy(ggb_handle h) {
     for (auto& kv : h->weight_cache) free_weight(kv.second);
     for (int i = 0; i < 4; ++i) if (h->d_scratch[i]) cudaFree(h->d_scratch[i]);
     if (h->h_pinned) cudaFreeHost(h->h_pinned);
+    if (h->d_err) cudaFree(h->d_err);
     cudaStreamDestroy(h->stream);
     delete h;
 }
@@ -114,7 +131,8 @@ int ggb_mul_mat_q(ggb_handle h, const ggb_mul_mat_params* p) {
         GGB_TRY(launch_gemv(h, a, h->stream));
     }
     GGB_TRY(cuda_status(h, cudaMemcpy2DAsync(p->C, sizeof(float) * ldc, dC, sizeof(float) * N, sizeof(float) * N, M, cudaMemcpyDeviceToHost, h->stream), "C download"));
-    return cuda_status(h, cudaStreamSynchronize(h->stream), "mul_mat_q");
+    GGB_TRY(cuda_status(h, cudaStreamSynchronize(h->stream), "mul_mat_q"));
+    return check_device_error(h);
 }
 
 int ggb_rms_norm(ggb_handle h, const ggb_rms_norm_params* p) {

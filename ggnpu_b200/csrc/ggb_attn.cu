@@ -269,4 +269,41 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_
     return cuda_status(c, cudaGetLastError(), "attention combine");
 }
 
+// Split geometry shared by every caller: at most 32 splits, each a whole number of pages.
+void attn_split_geometry(int n_pages, int* n_splits, int* pages_per_split) {
+    *pages_per_split = (n_pages + 31) / 32;
+    *n_splits = (n_pages + *pages_per_split - 1) / *pages_per_split;
+}
+
+static int check_paged_params(Context* c, const ggb_attn_paged_params* p) {
+    if (!p || !p->q || !p->k_cache || !p->v_cache || !p->block_table || !p->out) return set_status(c, GGB_INVALID_PARAM, "attn_paged: null pointer");
+    if (p->n_head <= 0 || p->n_kv <= 0 || p->page <= 0 || p->n_pages <= 0 || p->pos < 0 || p->pos >= p->n_pages * p->page)
+        return set_status(c, GGB_INVALID_PARAM, "attn_paged: bad sizes or position");
+    return GGB_OK;
+}
+
+static AttnPagedArgs paged_args(const ggb_attn_paged_params* p, float* partial) {
+    AttnPagedArgs a{};
+    a.q = p->q; a.k_cache = static_cast<const __nv_bfloat16*>(p->k_cache); a.v_cache = static_cast<const __nv_bfloat16*>(p->v_cache);
+    a.block_table = p->block_table; a.partial = partial; a.out = p->out; a.d_pos = nullptr; a.pos0 = p->pos;
+    a.n_head = p->n_head; a.n_kv = p->n_kv; a.head_dim = p->head_dim; a.page = p->page;
+    attn_split_geometry(p->n_pages, &a.n_splits, &a.pages_per_split);
+    return a;
+}
+
 }  // namespace ggb
+
+using namespace ggb;
+
+extern "C" int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* p) {
+    if (!h) return GGB_UNAVAILABLE;
+    int st = check_paged_params(h, p);
+    if (st != GGB_OK) return st;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    int n_splits, pps;
+    attn_split_geometry(p->n_pages, &n_splits, &pps);
+    float* partial = static_cast<float*>(scratch(h, 3, sizeof(float) * attn_partial_floats(1, p->n_head, n_splits, p->head_dim)));
+    if (!partial) return h->last_status;
+    return launch_attn_paged(h, paged_args(p, partial), 1, h->stream);
+}

@@ -538,10 +538,13 @@ static int dispatch(Context* c, const GemvArgs& a, cudaStream_t s) {
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
     if (!a.x || !a.y || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
     if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3)) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
-    if (a.epi == EPI_SWIGLU) {
-        if (a.w2.type != a.w.type || a.w2.N != a.w.N || a.w2.K != a.w.K) return set_status(c, GGB_INVALID_PARAM, "gemv: gate/up mismatch");
-        return dispatch<true>(c, a, s);
+    if (a.epi == EPI_SWIGLU && (a.w2.type != a.w.type || a.w2.N != a.w.N || a.w2.K != a.w.K))
+        return set_status(c, GGB_INVALID_PARAM, "gemv: gate/up mismatch");
+    if (c->use_tma && a.M == 1) {
+        const int st = launch_gemv_tma(c, a, s);
+        if (st != GGB_NOT_FOUND) return st;
     }
+    if (a.epi == EPI_SWIGLU) return dispatch<true>(c, a, s);
     return dispatch<false>(c, a, s);
 }
 

@@ -54,6 +54,9 @@ struct Context {
     struct KeyHash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.n * 1315423911u + k.k) << 1) ^ k.t; } };
     std::unordered_map<Key, DeviceWeight*, KeyHash> weight_cache;
     uint64_t launches = 0;    // kernels launched by this library on this context
+    int* d_err = nullptr;     // device word: non-zero after a bounded device-side wait gave up
+    bool use_pdl = true;      // launch the streaming kernels with programmatic dependent launch
+    bool use_tma = true;      // M == 1 GEMV through the bulk-copy ring kernel
 };
 
 int set_status(Context* c, int status, const char* msg);
@@ -67,8 +70,10 @@ size_t packed_bytes(uint32_t type, int64_t N, int K);
 int launch_dequant_rows(Context* c, const PackedW& w, int64_t row0, int64_t n_rows, float* d_out, cudaStream_t s);
 int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int n_rows, float* d_out, int ld, cudaStream_t s);
 
-// ggb_gemv.cu
+// ggb_gemv.cu / ggb_gemv_tma.cu
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
+int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
+int check_device_error(Context* c);     // after a synchronise: turns the device error word into a status
 
 // ggb_ops.cu
 int launch_rms_norm(Context* c, const float* x, float* y, int rows, int n, float eps, const float* gamma, cudaStream_t s);

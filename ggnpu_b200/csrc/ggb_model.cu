@@ -339,7 +339,7 @@ int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int po
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 2, m->d_next, 4, cudaMemcpyDeviceToHost, c->stream), "token download"));
     M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "prefill"));
     if (next_token) *next_token = m->h_io[2];
-    return GGB_OK;
+    return check_device_error(c);
 }
 
 int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, int32_t* next_token) {
@@ -355,7 +355,9 @@ int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, in
     c->launches += m->launches_per_step;
     if (host_logits) M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_logits, m->logits, sizeof(float) * m->d.vocab, cudaMemcpyDeviceToHost, c->stream), "logits download"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 2, m->d_next, 4, cudaMemcpyDeviceToHost, c->stream), "token download"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 4, c->d_err, 4, cudaMemcpyDeviceToHost, c->stream), "error word download"));
     M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "decode"));
+    if (m->h_io[4] != 0) return check_device_error(c);
     if (host_logits) memcpy(host_logits, m->h_logits, sizeof(float) * m->d.vocab);
     if (next_token) *next_token = m->h_io[2];
     return GGB_OK;
@@ -375,7 +377,8 @@ int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_
     for (int i = 0; i < n; ++i) M_TRY(cuda_status(c, cudaGraphLaunch(m->decode_graph, c->stream), "graph launch"));
     c->launches += m->launches_per_step * n;
     M_TRY(cuda_status(c, cudaMemcpyAsync(host_out, m->d_gen, sizeof(int32_t) * n, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
-    return cuda_status(c, cudaStreamSynchronize(c->stream), "generate");
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate"));
+    return check_device_error(c);
 }
 
 int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out) {

@@ -186,6 +186,28 @@ GGB_API int ggb_gemv_device(ggb_handle h, ggb_weight w, const float* d_x, int M,
 GGB_API int ggb_gemv_swiglu_device(ggb_handle h, ggb_weight w_gate, ggb_weight w_up, const float* d_x, int M, int lda,
                                    float* d_y, int ldc, const float* d_gamma, float eps);
 
+/* Grouped-query attention of ONE query token over a paged bf16 KV cache, DEVICE pointers: the
+ * GPU-native form of Backend::flash_attn (include/ggnpu/backend.h:155) plus the caller's GQA expand
+ * (src/cli/main.cpp:3364-3383), which it makes unnecessary: each KV head is read once for all the
+ * query heads that share it.  q [n_head][head_dim] f32 already rotated; k_cache / v_cache are bf16
+ * [pages][n_kv][page][head_dim] (K stored after RoPE); block_table[logical page] = physical page;
+ * keys 0..pos are attended with scale 1/sqrt(head_dim); out [n_head][head_dim] f32.  The context is
+ * split across CTAs and merged by a second kernel through a scratch buffer owned by the handle
+ * (allocated with cudaMalloc on first need and when it must grow).  Asynchronous on the handle's
+ * stream. */
+typedef struct ggb_attn_paged_params {
+    const float* q;
+    const void* k_cache;
+    const void* v_cache;
+    const int32_t* block_table;
+    float* out;
+    int n_head, n_kv, head_dim;
+    int page;      /* tokens per page */
+    int n_pages;   /* logical pages in block_table */
+    int pos;       /* position of the query token; attends keys 0..pos */
+} ggb_attn_paged_params;
+GGB_API int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* p);
+
 /* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
 GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */

@@ -1,0 +1,63 @@
+"""Paged grouped-query attention (device pointers, bf16 KV pages, split over the context) vs the CPU
+oracle's flash_attn (src/backends/cpu_ref/cpu_ref.cpp:223-280) on the same bf16-rounded K/V expanded
+per query head the way the reference's caller does (src/cli/main.cpp:3364-3383)."""
+import numpy as np
+import pytest
+import torch
+
+from ggnpu_b200.backend import Status
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(n_head, n_kv, hd, page, n_pages, seed):
+    g = torch.Generator().manual_seed(seed)
+    ctx = page * n_pages
+    k = torch.randn(ctx, n_kv, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(ctx, n_kv, hd, generator=g).to(torch.bfloat16)
+    q = torch.randn(n_head, hd, generator=g)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)        # a shuffled block table
+
+    def paged(x):
+        pages = x.reshape(n_pages, page, n_kv, hd).permute(0, 2, 1, 3).contiguous()   # [logical page][kv][slot][hd]
+        phys = torch.empty_like(pages)
+        phys[perm.long()] = pages
+        return phys
+
+    return q, k, v, paged(k), paged(v), perm
+
+
+def expanded(x, n_head, n_kv, upto):
+    grp = n_head // n_kv
+    xf = x[:upto].float().numpy()                                        # [ctx][kv][hd]
+    return np.ascontiguousarray(np.stack([xf[:, h // grp, :] for h in range(n_head)]))
+
+
+@pytest.mark.parametrize("shape", [(32, 8, 64, 64, 8), (12, 2, 128, 64, 5), (16, 2, 256, 16, 40), (4, 4, 64, 32, 3)])
+def test_paged_attention_matches_oracle(backend, oracle, shape):
+    n_head, n_kv, hd, page, n_pages = shape
+    q, k, v, kp, vp, table = make_case(*shape, seed=sum(shape))
+    dev = torch.device("cuda:0")
+    dq, dk, dv, dt = q.to(dev), kp.to(dev), vp.to(dev), table.to(dev)
+    out = torch.empty(n_head, hd, device=dev)
+    ctx = page * n_pages
+    for pos in (0, page - 1, page, ctx // 2 + 3, ctx - 1):
+        torch.cuda.synchronize()
+        st = backend.attn_paged_device(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dt.data_ptr(), out.data_ptr(),
+                                       n_head, n_kv, hd, page, n_pages, pos)
+        assert st == Status.OK, backend.last_error_message()
+        backend.sync()
+        want = oracle.flash_attn(q.numpy(), expanded(k, n_head, n_kv, pos + 1), expanded(v, n_head, n_kv, pos + 1), -1)
+        assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=2e-6), (shape, pos)
+
+
+def test_paged_attention_argument_errors(backend):
+    dev = torch.device("cuda:0")
+    t = torch.zeros(64, device=dev)
+    it = torch.zeros(4, device=dev, dtype=torch.int32)
+    ok = dict(n_head=4, n_kv=2, head_dim=64, page=16, n_pages=4, pos=3)
+    bad = [dict(ok, pos=64), dict(ok, pos=-1), dict(ok, n_head=3), dict(ok, head_dim=96), dict(ok, n_head=32, n_kv=2)]
+    for kw in bad:
+        st = backend.attn_paged_device(t.data_ptr(), t.data_ptr(), t.data_ptr(), it.data_ptr(), t.data_ptr(), **kw)
+        assert st == Status.INVALID_PARAM
+    assert backend.attn_paged_device(0, t.data_ptr(), t.data_ptr(), it.data_ptr(), t.data_ptr(), **ok) == Status.INVALID_PARAM
