@@ -307,3 +307,41 @@ extern "C" int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* 
     if (!partial) return h->last_status;
     return launch_attn_paged(h, paged_args(p, partial), 1, h->stream);
 }
+
+// ---- the same attention without any allocation --------------------------------------------------
+// Scratch for the per-split partial results lives in this fixed array, which every GPU that loads
+// the library holds until the process exits.  64 query heads x 32 context splits x (256 + 2) floats.
+static constexpr size_t kStaticAttnScratchFloats = static_cast<size_t>(64) * 32 * (256 + 2);
+static __device__ __align__(256) float g_attn_static_scratch[kStaticAttnScratchFloats];
+
+// Host code cannot use the array's name as a pointer: on the host it is only a handle for the
+// symbol.  The device address is looked up once per device and kept here.
+static float* g_attn_static_ptr[64];
+static std::mutex g_attn_static_mu;
+
+extern "C" int ggb_attn_paged_static(ggb_handle h, const ggb_attn_paged_params* p) {
+    if (!h) return GGB_UNAVAILABLE;
+    int st = check_paged_params(h, p);
+    if (st != GGB_OK) return st;
+    int n_splits, pps;
+    attn_split_geometry(p->n_pages, &n_splits, &pps);
+    const size_t need = attn_partial_floats(1, p->n_head, n_splits, p->head_dim);
+    if (need > kStaticAttnScratchFloats || p->n_head > 64)
+        return set_status(h, GGB_INVALID_PARAM, "attn_paged_static: n_head * splits * (head_dim + 2) exceeds the built-in scratch "
+                                                "(64 heads x 32 splits x 258 floats); use ggb_attn_paged_device");
+    if (h->device < 0 || h->device >= 64) return set_status(h, GGB_INVALID_PARAM, "attn_paged_static: device index out of range");
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    float* partial = nullptr;
+    {
+        std::lock_guard<std::mutex> g(g_attn_static_mu);
+        if (!g_attn_static_ptr[h->device]) {
+            void* sym = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&sym, g_attn_static_scratch);   // with h->device current
+            if (e != cudaSuccess) return cuda_status(h, e, "attn_paged_static: cudaGetSymbolAddress");
+            g_attn_static_ptr[h->device] = static_cast<float*>(sym);
+        }
+        partial = g_attn_static_ptr[h->device];
+    }
+    return launch_attn_paged(h, paged_args(p, partial), 1, h->stream);
+}

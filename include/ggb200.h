@@ -208,6 +208,22 @@ typedef struct ggb_attn_paged_params {
 } ggb_attn_paged_params;
 GGB_API int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* p);
 
+/* The same computation as ggb_attn_paged_device for callers that must not cause a device
+ * allocation.  (No counterpart in the reference: its backends allocate buffers as they please.)
+ * Who needs it: a host that gave all of the GPU's memory to its own pool at start-up, so a
+ * cudaMalloc made by this library would fail or fight that pool; and a serving loop that cannot
+ * afford the device-wide stall an allocation may bring.  This entry point calls neither cudaMalloc
+ * nor cudaFree nor any routine that does: the per-split partial results go to a fixed array inside
+ * the library (2.1 MB of device memory on every GPU that loads the library, held until the process
+ * exits).  Limits: n_head <= 64 and n_head * splits * (head_dim + 2) <= 64 * 32 * 258 floats, where
+ * splits = min(32, n_pages) rounded to whole pages; larger requests are refused with
+ * GGB_INVALID_PARAM and a message.  The first call on each device looks up the array's device
+ * address (a one-time set-up step): make that first call before any stream capture begins.  All
+ * calls share the one array and it keeps whatever the previous call left; the kernels overwrite
+ * every slot they later read, so nothing has to be cleared, but two calls whose kernels overlap on
+ * the GPU (different handles or streams) would race on it -- keep them ordered. */
+GGB_API int ggb_attn_paged_static(ggb_handle h, const ggb_attn_paged_params* p);
+
 /* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
 GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */
