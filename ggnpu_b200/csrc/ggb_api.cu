@@ -3,6 +3,9 @@
 // kernels on the handle's stream and returns after the results are back in the caller's buffers,
 // which is what the reference's NPU backend does (run.wait() inside each op,
 // src/backends/amd_xdna/amd_xdna.cpp:865-897); sync() is then only a stream synchronise.
+#include <stdio.h>
+
+#include <algorithm>
 #include <stdlib.h>
 #include <string.h>
 
@@ -77,6 +80,8 @@ int ggb_create(int device, ggb_handle* out) {
     }
     c->use_pdl = getenv("GGB_NO_PDL") == nullptr;
     c->use_tma = getenv("GGB_NO_TMA") == nullptr;
+    c->use_mma = getenv("GGB_NO_MMA") == nullptr;
+    if (getenv("GGB_TRACE") && cudaMalloc(&c->d_trace, 4096 * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(c->d_trace, 0, 4096 * sizeof(unsigned long long));
     *out = c;
     return GGB_OK;
 }
@@ -93,7 +98,29 @@ void ggb_destroy(ggb_handle h) {
     delete h;
 }
 
-void ggb_sync(ggb_handle h) { if (h) { GGB_LOCK(h); cuda_status(h, cudaStreamSynchronize(h->stream), "sync"); } }
+void ggb_sync(ggb_handle h) {
+    if (!h) return;
+    GGB_LOCK(h);
+    cuda_status(h, cudaStreamSynchronize(h->stream), "sync");
+    if (h->d_trace) {        // tuning aid: time stamps (ns, relative to the first) left by the last traced kernel
+        static unsigned long long t[4096];
+        if (getenv("GGB_TRACE_DUMP") && cudaMemcpy(t, h->d_trace, sizeof(t), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            std::vector<int> order;
+            for (int i = 0; i < 512; ++i) if (t[8 * i]) order.push_back(i);
+            std::sort(order.begin(), order.end(), [&](int a, int b) { return t[8 * a] < t[8 * b]; });
+            unsigned long long prev_end = 0, t0 = order.empty() ? 0 : t[8 * order[0]];
+            for (int i : order) {
+                const unsigned long long* e = t + 8 * i;
+                fprintf(stderr, "[ggb trace] x3=%lld x4=%lld kind=%llu start=%lld wait=%lld prologue=%lld end=%lld gap_from_prev_end=%lld\n",
+                        e[3] ? static_cast<long long>(e[3] - e[0]) : -1, e[4] ? static_cast<long long>(e[4] - e[0]) : -1, e[6],
+                        static_cast<long long>(e[0] - t0), e[1] ? static_cast<long long>(e[1] - e[0]) : -1, e[2] ? static_cast<long long>(e[2] - e[0]) : -1,
+                        static_cast<long long>(e[7] - e[0]), prev_end ? static_cast<long long>(e[0] - prev_end) : 0);
+                prev_end = e[7];
+            }
+            cudaMemset(h->d_trace, 0, sizeof(t));
+        }
+    }
+}
 int ggb_is_available(ggb_handle h) { return h != nullptr; }
 const char* ggb_name(ggb_handle) { return "cuda_b200"; }
 int ggb_last_error(ggb_handle h) { return h ? h->last_status : GGB_UNAVAILABLE; }

@@ -13,6 +13,29 @@
 
 namespace ggb {
 
+__device__ __forceinline__ void stamp(unsigned long long* tr, int i, int kind) {
+    if (tr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+        unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; tr[6] = kind;
+    }
+}
+// Programmatic dependent launch: a kernel launched with the attribute may start before its
+// predecessor in the stream has finished; it must pass pdl_sync() before reading anything the
+// predecessor wrote.  The trigger right after it lets the successor be scheduled in turn.
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <class... KArgs, class... Args>
+static cudaError_t launch_pdl(Context* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 __device__ __forceinline__ float wsum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
@@ -83,6 +106,9 @@ int launch_attn_expanded(Context* c, const float* Q, const float* K, const float
 // slot p % page (K is cached after RoPE, V raw: src/cli/main.cpp:3354-3356).
 // grid (n_head + n_kv, n_tok); one CTA per head per token; blockDim = head_dim / 2 pairs.
 __global__ void rope_append_kernel(KvAppendArgs a) {
+    stamp(a.trace, 0, 5);
+    pdl_sync();
+    stamp(a.trace, 1, 5);
     const int t = blockIdx.y, hh = blockIdx.x;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int hd = a.head_dim, half = hd >> 1;
@@ -124,105 +150,231 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
             a.v_cache[o + i1] = __float2bfloat16_rn(vs[i1]);
         }
     }
+    stamp(a.trace, 7, 5);
 }
 
-int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s) {
+int launch_rope_append(Context* c, const KvAppendArgs& a_in, int n_tok, cudaStream_t s) {
+    KvAppendArgs a = a_in;
+    a.trace = trace_slot(c);
     const int threads = ((a.head_dim / 2) + 31) / 32 * 32;
     dim3 grid(a.n_head + a.n_kv, n_tok);
-    rope_append_kernel<<<grid, threads, 0, s>>>(a);
+    const cudaError_t e = launch_pdl(c, rope_append_kernel, grid, dim3(threads), 0, s, a);
     c->launches++;
-    return cuda_status(c, cudaGetLastError(), "rope_append");
+    return cuda_status(c, e, "rope_append");
 }
 
 // ---- paged GQA attention, split over the context ---------------------------------------------
-// grid (n_kv, n_splits, n_tok), 128 threads.  CTA (h, s, t) handles KV head h, keys of split s that
-// are <= pos_t, for the G = n_head / n_kv query heads sharing h, and writes an un-normalised
-// partial (max, sum, acc[hd]) per query head.  Warps stride over keys; lanes split head_dim.
-template <int EPL>   // elements per lane = head_dim / 32
-__global__ void __launch_bounds__(128) attn_split_kernel(AttnPagedArgs a) {
-    constexpr int MAXG = 8;
-    const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int G = a.n_head / a.n_kv, hd = EPL * 32;
+// grid (n_kv, n_splits, n_tok), 128 threads.  CTA (h, s, t) handles KV head h, the keys of split s
+// that are <= pos_t, for the G = n_head / n_kv query heads sharing h, and writes an un-normalised
+// partial (max, sum, acc[hd]) per query head.  Keys are processed in chunks of 64: the chunk's K and
+// V rows are first copied into shared memory with every 16-byte load in flight at once (a loop that
+// fetches key after key pays one full memory latency per key), then scores, an online softmax and
+// P*V run out of shared memory in fp32.
+// With a.fuse (single-token decode) the kernel also does the work of rope_append_kernel for its
+// head: q is rotated on the way into shared memory, and the CTA whose split contains pos rotates the
+// new key, stores key and value into the cache and uses them directly.
+template <int HD>
+__global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
+    constexpr int KW = HD / 2;           // 32-bit words (bf16 pairs) per K or V row
+    constexpr int KS = KW + 1;           // padded K row stride: thread-per-key reads hit distinct banks
+    constexpr int TK = 64;               // keys per chunk
+    constexpr int NP = (8 * KW + 127) / 128;   // (head, dim pair) items per thread in P*V
+    stamp(a.trace, 0, 3);
+    pdl_sync();
+    stamp(a.trace, 1, 3);
+    const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int G = a.n_head / a.n_kv;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
     const int j_begin = split * keys_per_split;
     const int j_end = min(j_begin + keys_per_split, pos + 1);
-    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits + split) * (hd + 2);
-    if (j_begin > pos) return;               // this split holds no visible key (combine skips it too)
+    if (j_begin > pos) return;           // no visible key in this split (the merge skips it too)
 
-    extern __shared__ float sm[];
-    float* qs = sm;                                   // [G][hd]
-    float* wm = qs + G * hd;                          // [4][G] running max per warp
-    float* wl = wm + 4 * MAXG;                        // [4][G] running sum
-    float* wacc = wl + 4 * MAXG;                      // [4][G][hd]
-    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * hd;
-    for (int i = threadIdx.x; i < G * hd; i += blockDim.x) qs[i] = q[i];
-    __syncthreads();
+    extern __shared__ __align__(16) uint32_t sm_u[];
+    uint32_t* Vt = sm_u;                                   // [TK][KW]   (16-byte aligned rows)
+    uint32_t* Kt = Vt + TK * KW;                           // [TK][KS]
+    float* qs = reinterpret_cast<float*>(Kt + TK * KS);    // [G][HD], already multiplied by 1/sqrt(HD)
+    float* S = qs + 8 * HD;                                // [8][TK] scores, then probabilities
+    float* mrun = S + 8 * TK;                              // [8] running max, [8] running sum, [8] rescale
+    float* lrun = mrun + 8;
+    float* corr = lrun + 8;
+    float* hinv = corr + 8;                                // [9] per-head norm factors (q heads, then k)
+    __nv_bfloat16* fresh = reinterpret_cast<__nv_bfloat16*>(hinv + 12);   // [2][HD] new key and value
+    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
+    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
+    const bool has_new = a.fuse && pos >= j_begin && pos < j_begin + keys_per_split;
+    const int half = HD >> 1;
 
-    float m[MAXG], l[MAXG], acc[MAXG][EPL];
+    // The first chunk's K and V rows are requested now, into registers, so that their memory latency
+    // overlaps the q / new-key preparation below (head_dim <= 128; larger heads load in the loop).
+    constexpr int NPF = HD <= 128 ? HD / 16 : 0;
+    uint4 kpre[NPF > 0 ? NPF : 1], vpre[NPF > 0 ? NPF : 1];
+    if (NPF > 0) {
+        const int nk0 = min(TK, j_end - j_begin);
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f; }
-    const float scale = 1.0f / sqrtf(static_cast<float>(hd));
-
-    for (int j = j_begin + warp; j < j_end; j += 4) {
-        const int page = a.block_table[j / a.page], slot = j % a.page;
-        const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * hd + lane * EPL;
-        float kf[EPL], vf[EPL];
-#pragma unroll
-        for (int e = 0; e < EPL; e += 2) {
-            const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(a.k_cache + o + e);
-            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(a.v_cache + o + e);
-            kf[e] = __low2float(k2); kf[e + 1] = __high2float(k2);
-            vf[e] = __low2float(v2); vf[e + 1] = __high2float(v2);
-        }
-#pragma unroll
-        for (int g = 0; g < MAXG; ++g) {
-            if (g < G) {
-                float s = 0.0f;
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) s = fmaf(qs[g * hd + lane * EPL + e], kf[e], s);
-                s = wsum(s) * scale;
-                const float mn = fmaxf(m[g], s);
-                const float corr = expf(m[g] - mn), p = expf(s - mn);
-                l[g] = l[g] * corr + p;
-#pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
-                m[g] = mn;
+        for (int u = 0; u < NPF; ++u) {
+            const int i = tid + 128 * u;
+            const int row = i / (HD / 8), part = i - row * (HD / 8);
+            if (row < nk0) {
+                const int j = j_begin + row;
+                const int page = a.block_table[j / a.page], slot = j % a.page;
+                const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
+                kpre[u] = *reinterpret_cast<const uint4*>(a.k_cache + o);
+                vpre[u] = *reinterpret_cast<const uint4*>(a.v_cache + o);
             }
         }
     }
-    // merge the four warps
+    if (tid < 8) { mrun[tid] = -INFINITY; lrun[tid] = 0.0f; }
+    if (a.fuse) {
+        // optional per-head RMS norm of q and k before the rotation, sum of squares in double
+        // (src/cli/main.cpp:3294-3299)
+        for (int hh = warp; hh < G + 1; hh += 4) {
+            const float* nw = hh < G ? a.q_norm : a.k_norm;
+            float inv = 1.0f;
+            if (nw) {
+                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                double ss = 0.0;
+                for (int i = lane; i < HD; i += 32) ss += static_cast<double>(src[i]) * src[i];
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-        if (g < G) {
-            if (lane == 0) { wm[warp * MAXG + g] = m[g]; wl[warp * MAXG + g] = l[g]; }
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                inv = 1.0f / sqrtf(static_cast<float>(ss / HD) + a.eps);
+            }
+            if (lane == 0) hinv[hh] = inv;
+        }
+        __syncthreads();
+        const float* cs = a.cos_tab + static_cast<size_t>(pos) * half;
+        const float* sn = a.sin_tab + static_cast<size_t>(pos) * half;
+        for (int idx = tid; idx < (G + (has_new ? 1 : 0)) * half; idx += 128) {
+            const int hh = idx / half, i = idx - hh * half;
+            const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+            const bool is_q = hh < G;
+            const float* src = is_q ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+            const float* nw = is_q ? a.q_norm : a.k_norm;
+            float v0 = src[i0], v1 = src[i1];
+            if (nw) { v0 = v0 * hinv[hh] * nw[i0]; v1 = v1 * hinv[hh] * nw[i1]; }
+            const float r0 = v0 * cs[i] - v1 * sn[i], r1 = v0 * sn[i] + v1 * cs[i];
+            if (is_q) { qs[hh * HD + i0] = r0 * scale; qs[hh * HD + i1] = r1 * scale; }
+            else { fresh[i0] = __float2bfloat16_rn(r0); fresh[i1] = __float2bfloat16_rn(r1); }
+        }
+        if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(a.v_new[static_cast<size_t>(h) * HD + i]);
+        __syncthreads();
+        if (has_new) {     // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
+            const int page = a.block_table[pos / a.page], slot = pos % a.page;
+            const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD;
+            for (int i = tid; i < HD; i += 128) { a.k_cache_w[o + i] = fresh[i]; a.v_cache_w[o + i] = fresh[HD + i]; }
+        }
+    } else {
+        for (int i = tid; i < G * HD; i += 128) qs[i] = q[i] * scale;
+    }
+
+    float acc[NP][2];
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) wacc[(warp * G + g) * hd + lane * EPL + e] = acc[g][e];
+    for (int p = 0; p < NP; ++p) { acc[p][0] = 0.0f; acc[p][1] = 0.0f; }
+
+    for (int jc = j_begin; jc < j_end; jc += TK) {
+        const int nk = min(TK, j_end - jc);
+        __syncthreads();                                   // previous chunk fully consumed
+        if (NPF > 0 && jc == j_begin) {
+#pragma unroll
+            for (int u = 0; u < NPF; ++u) {
+                const int i = tid + 128 * u;
+                const int row = i / (HD / 8), part = i - row * (HD / 8);
+                if (row < nk) {
+                    uint32_t* kd = Kt + row * KS + part * 4;
+                    kd[0] = kpre[u].x; kd[1] = kpre[u].y; kd[2] = kpre[u].z; kd[3] = kpre[u].w;
+                    *reinterpret_cast<uint4*>(Vt + row * KW + part * 4) = vpre[u];
+                }
+            }
+        } else
+        for (int i = tid; i < nk * (HD / 8); i += 128) {
+            const int row = i / (HD / 8), part = i - row * (HD / 8);
+            const int j = jc + row;
+            const int page = a.block_table[j / a.page], slot = j % a.page;
+            const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
+            const uint4 kv = *reinterpret_cast<const uint4*>(a.k_cache + o);
+            const uint4 vv = *reinterpret_cast<const uint4*>(a.v_cache + o);
+            uint32_t* kd = Kt + row * KS + part * 4;
+            kd[0] = kv.x; kd[1] = kv.y; kd[2] = kv.z; kd[3] = kv.w;
+            *reinterpret_cast<uint4*>(Vt + row * KW + part * 4) = vv;
+        }
+        if (has_new && pos >= jc && pos < jc + nk) {       // the new token's row comes from shared memory
+            __syncthreads();
+            const uint32_t* fk = reinterpret_cast<const uint32_t*>(fresh);
+            for (int w = tid; w < KW; w += 128) { Kt[(pos - jc) * KS + w] = fk[w]; Vt[(pos - jc) * KW + w] = fk[KW + w]; }
+        }
+        __syncthreads();
+        {   // scores: thread = (key, head parity); heads hg, hg+2, hg+4, hg+6 share each K word
+            const int key = tid & 63, hg = tid >> 6;
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+            if (key < nk) {
+                const uint32_t* kr = Kt + key * KS;
+#pragma unroll 8
+                for (int w = 0; w < KW; ++w) {
+                    const uint32_t kw = kr[w];
+                    const float k0 = __uint_as_float(kw << 16), k1 = __uint_as_float(kw & 0xFFFF0000u);
+                    const float2 q0 = *reinterpret_cast<const float2*>(qs + hg * HD + 2 * w);
+                    s0 = fmaf(q0.x, k0, fmaf(q0.y, k1, s0));
+                    if (G > 2) { const float2 q1 = *reinterpret_cast<const float2*>(qs + (hg + 2) * HD + 2 * w); s1 = fmaf(q1.x, k0, fmaf(q1.y, k1, s1)); }
+                    if (G > 4) { const float2 q2 = *reinterpret_cast<const float2*>(qs + (hg + 4) * HD + 2 * w); s2 = fmaf(q2.x, k0, fmaf(q2.y, k1, s2)); }
+                    if (G > 6) { const float2 q3 = *reinterpret_cast<const float2*>(qs + (hg + 6) * HD + 2 * w); s3 = fmaf(q3.x, k0, fmaf(q3.y, k1, s3)); }
+                }
+            } else { s0 = s1 = s2 = s3 = -INFINITY; }
+            if (hg < G) S[hg * TK + key] = s0;
+            if (hg + 2 < G) S[(hg + 2) * TK + key] = s1;
+            if (hg + 4 < G) S[(hg + 4) * TK + key] = s2;
+            if (hg + 6 < G) S[(hg + 6) * TK + key] = s3;
+        }
+        __syncthreads();
+        for (int hh = warp; hh < G; hh += 4) {             // online softmax, one warp per head
+            const float v0 = S[hh * TK + lane], v1 = S[hh * TK + lane + 32];
+            float mx = fmaxf(v0, v1);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            const float mo = mrun[hh], mn = fmaxf(mo, mx);
+            const float p0 = expf(v0 - mn), p1 = expf(v1 - mn);
+            const float sum = wsum(p0 + p1);
+            S[hh * TK + lane] = p0; S[hh * TK + lane + 32] = p1;
+            if (lane == 0) { const float c = expf(mo - mn); corr[hh] = c; lrun[hh] = lrun[hh] * c + sum; mrun[hh] = mn; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {                     // acc = acc * corr + P V
+            const int idx = tid + 128 * p;
+            if (idx < G * KW) {
+                const int gq = idx / KW, w = idx - gq * KW;
+                const float c = corr[gq];
+                float a0 = acc[p][0] * c, a1 = acc[p][1] * c;
+                const float* pr = S + gq * TK;
+                for (int j = 0; j < nk; ++j) {
+                    const uint32_t vw = Vt[j * KW + w];
+                    const float pj = pr[j];
+                    a0 = fmaf(pj, __uint_as_float(vw << 16), a0);
+                    a1 = fmaf(pj, __uint_as_float(vw & 0xFFFF0000u), a1);
+                }
+                acc[p][0] = a0; acc[p][1] = a1;
+            }
         }
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
-        const int g = idx / hd, d = idx - g * hd;
-        float mx = -INFINITY;
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, wm[w * MAXG + g]);
-        float lsum = 0.0f, o = 0.0f;
-        for (int w = 0; w < 4; ++w) {
-            const float mw = wm[w * MAXG + g];
-            const float f = (mw == -INFINITY) ? 0.0f : expf(mw - mx);
-            lsum += wl[w * MAXG + g] * f;
-            o += wacc[(w * G + g) * hd + d] * f;
+    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits + split) * (HD + 2);
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+        const int idx = tid + 128 * p;
+        if (idx < G * KW) {
+            const int gq = idx / KW, w = idx - gq * KW;
+            float* pg = part + static_cast<size_t>(gq) * a.n_splits * (HD + 2);
+            pg[2 + 2 * w] = acc[p][0]; pg[3 + 2 * w] = acc[p][1];
+            if (w == 0) { pg[0] = mrun[gq]; pg[1] = lrun[gq]; }
         }
-        float* pg = part + static_cast<size_t>(g) * a.n_splits * (hd + 2);
-        pg[2 + d] = o;
-        if (d == 0) { pg[0] = mx; pg[1] = lsum; }
     }
+    stamp(a.trace, 7, 3);
 }
 
 // grid (n_head, n_tok): merge the visible splits, normalise, write out[t][head][hd].
 __global__ void attn_combine_kernel(AttnPagedArgs a) {
+    stamp(a.trace2, 0, 4);
+    pdl_sync();
+    stamp(a.trace2, 1, 4);
     const int head = blockIdx.x, t = blockIdx.y, hd = a.head_dim;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
@@ -237,35 +389,44 @@ __global__ void attn_combine_kernel(AttnPagedArgs a) {
         for (int s = 0; s < n_active; ++s) o += part[static_cast<size_t>(s) * (hd + 2) + 2 + d] * expf(part[static_cast<size_t>(s) * (hd + 2)] - mx);
         a.out[(static_cast<size_t>(t) * a.n_head + head) * hd + d] = o / lsum;
     }
+    stamp(a.trace2, 7, 4);
 }
 
 size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim) {
     return static_cast<size_t>(n_tok) * n_head * n_splits * (head_dim + 2);
 }
 
-int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s) {
+int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStream_t s) {
+    AttnPagedArgs a = a_in;
+    a.trace = trace_slot(c);
+    a.trace2 = c->d_trace ? c->d_trace + 8 * ((c->launches + 1) % 512) : nullptr;
     const int G = a.n_head / a.n_kv;
     if (G < 1 || G > 8 || a.n_head % a.n_kv) return set_status(c, GGB_INVALID_PARAM, "attention: query heads per KV head must be 1..8");
     const int hd = a.head_dim;
-    const size_t smem = (static_cast<size_t>(G) * hd + 2 * 4 * 8 + static_cast<size_t>(4) * G * hd) * sizeof(float);
+    if (a.page % 8) return set_status(c, GGB_INVALID_PARAM, "attention: page size must be a multiple of 8");
+    if (a.fuse && n_tok != 1) return set_status(c, GGB_INVALID_PARAM, "attention: fused append is for single-token steps");
     dim3 grid(a.n_kv, a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
-#define GGB_ATTN_CASE(EPL)                                                                                             \
+    size_t smem = 0;
+#define GGB_ATTN_CASE(HD)                                                                                              \
     {                                                                                                                  \
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(attn_split_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-        if (e == cudaSuccess) attn_split_kernel<EPL><<<grid, 128, smem, s>>>(a);                                       \
+        smem = sizeof(uint32_t) * (64 * (HD / 2) + 64 * (HD / 2 + 1)) + sizeof(float) * (8 * HD + 8 * 64 + 24 + 12) + 2 * 2 * HD + 16; \
+        static size_t allowed = 48 * 1024;                                                                              \
+        if (smem > allowed) { e = cudaFuncSetAttribute(attn_tile_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); allowed = smem; } \
+        if (e == cudaSuccess) e = launch_pdl(c, attn_tile_kernel<HD>, grid, dim3(128), smem, s, a);                     \
     }
-    if (hd == 64) GGB_ATTN_CASE(2)
-    else if (hd == 128) GGB_ATTN_CASE(4)
-    else if (hd == 256) GGB_ATTN_CASE(8)
+    if (hd == 64) GGB_ATTN_CASE(64)
+    else if (hd == 128) GGB_ATTN_CASE(128)
+    else if (hd == 256) GGB_ATTN_CASE(256)
     else return set_status(c, GGB_INVALID_PARAM, "attention: head_dim must be 64, 128 or 256");
 #undef GGB_ATTN_CASE
     if (e != cudaSuccess) return cuda_status(c, e, "attention attr");
     c->launches++;
-    e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_status(c, e, "attention split");
-    attn_combine_kernel<<<dim3(a.n_head, n_tok), 64, 0, s>>>(a);
+    if (a.skip_merge) return GGB_OK;
+    e = launch_pdl(c, attn_combine_kernel, dim3(a.n_head, n_tok), dim3(64), 0, s, a);
     c->launches++;
+    if (e != cudaSuccess) return cuda_status(c, e, "attention combine");
     return cuda_status(c, cudaGetLastError(), "attention combine");
 }
 

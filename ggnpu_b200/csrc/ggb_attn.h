@@ -22,6 +22,7 @@ struct KvAppendArgs {
     int pos0;
     int n_head, n_kv, head_dim, page, neox;
     float eps;
+    unsigned long long* trace;   // optional time stamps (tuning aid)
 };
 
 struct AttnPagedArgs {
@@ -34,6 +35,21 @@ struct AttnPagedArgs {
     const int32_t* d_pos;
     int pos0;
     int n_head, n_kv, head_dim, page, n_splits, pages_per_split;
+    // fused RoPE + KV append for a single-token step (fuse != 0): q is then PRE-RoPE, k_new / v_new are
+    // this token's projections [n_kv][hd]; the kernel rotates, stores into the cache and attends.
+    int fuse, neox;
+    int skip_merge;           // 1: leave the per-split partials for the consumer (the output projection merges them)
+    const float* k_new;
+    const float* v_new;
+    __nv_bfloat16* k_cache_w;
+    __nv_bfloat16* v_cache_w;
+    const float* cos_tab;
+    const float* sin_tab;
+    const float* q_norm;
+    const float* k_norm;
+    float eps;
+    unsigned long long* trace;   // optional time stamps (tuning aid)
+    unsigned long long* trace2;
 };
 
 int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s);

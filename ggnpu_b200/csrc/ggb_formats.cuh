@@ -63,13 +63,60 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
 }
 
 // A weight matrix [N rows][K] resident in HBM in the stream layout.
+// layout 0: streams indexed [row][block].  layout 1 ("row-group major", Q4_K and Q6_K; Q4_K shown): rows are taken in
+// groups of 16 (N padded with zero rows), streams indexed [group][block][...] with the quant bytes
+// ordered as the A-operand fragments of an m16n8k32 int8 tensor-core instruction:
+//   hdr : [group][block][row16][16 B]
+//   qs  : [group][block][j = 0..3][lane = 0..31][16 B], lane (g = lane/4, t = lane%4) holding the four
+//         32-bit words  {row g, bytes 32j+4t..}, {row g+8, same}, {row g, bytes 32j+16+4t..}, {row g+8, same}
+//         (low nibbles = sub-block 2j, high nibbles = sub-block 2j+1 of the GGUF block).
+// Any (group, block range) is then one contiguous byte range of each stream.
 struct PackedW {
     const uint8_t* s[kMaxStreams];
     int64_t N;
     int K;
     int nb;          // blocks per row = K / block_elems
     uint32_t type;
+    int layout;
 };
+
+// Byte offsets inside the streams of a Q4_K weight, for either layout.  blk = row * nb + block.
+__host__ __device__ __forceinline__ int64_t q4k_hdr_off(int layout, int nb, int64_t blk) {
+    if (layout == 0) return blk * 16;
+    const int64_t row = blk / nb; const int b = static_cast<int>(blk - row * nb);
+    return (((row >> 4) * nb + b) * 16 + (row & 15)) * 16;
+}
+__host__ __device__ __forceinline__ int64_t q4k_qs_off(int layout, int nb, int64_t blk, int qi) {   // qi = 0..127
+    if (layout == 0) return blk * 128 + qi;
+    const int64_t row = blk / nb; const int b = static_cast<int>(blk - row * nb);
+    const int r = static_cast<int>(row & 15), j = qi >> 5, within = qi & 31;
+    const int word = ((within >> 4) << 1) | (r >> 3), lane = ((r & 7) << 2) | ((within & 15) >> 2);
+    return ((((row >> 4) * nb + b) * 4 + j) * 32 + lane) * 16 + word * 4 + (within & 3);
+}
+
+// Q6_K in layout 1 (row groups of 16, A-operand fragments of m16n8k16 int8 instructions):
+//   s0 : [group][block][combo = 2*half + c][lane][16 B] = words {ql_a row g, ql_b row g, ql_a row g+8, ql_b row g+8}
+//        with ql_a = ql[64*half + 16c + 4t ..+3], ql_b = ql[64*half + 32 + 16c + 4t ..+3]   (lane = 4g + t)
+//   s1 : [group][block][half][lane][16 B] = words {qh(c=0) row g, qh(c=0) row g+8, qh(c=1) row g, qh(c=1) row g+8},
+//        qh(c) = qh[32*half + 16c + 4t ..+3]
+//   s2 : [group][block][row16][16 B] int8 scales      s3 : [group][block][row16][2 B] fp16 d
+__host__ __device__ __forceinline__ int64_t q6k_ql_off(int layout, int nb, int64_t blk, int qi) {      // qi = 0..127
+    if (layout == 0) return blk * 128 + qi;
+    const int64_t row = blk / nb; const int b = static_cast<int>(blk - row * nb);
+    const int r = static_cast<int>(row & 15), hf = qi >> 6, w64 = qi & 63, ab = w64 >> 5, c = (w64 >> 4) & 1, t = (w64 & 15) >> 2;
+    return (((((row >> 4) * nb + b) * 4 + 2 * hf + c) * 32 + ((r & 7) << 2) + t) * 4 + ab + 2 * (r >> 3)) * 4 + (qi & 3);
+}
+__host__ __device__ __forceinline__ int64_t q6k_qh_off(int layout, int nb, int64_t blk, int qi) {      // qi = 0..63
+    if (layout == 0) return blk * 64 + qi;
+    const int64_t row = blk / nb; const int b = static_cast<int>(blk - row * nb);
+    const int r = static_cast<int>(row & 15), hf = qi >> 5, c = (qi >> 4) & 1, t = (qi & 15) >> 2;
+    return (((((row >> 4) * nb + b) * 2 + hf) * 32 + ((r & 7) << 2) + t) * 4 + 2 * c + (r >> 3)) * 4 + (qi & 3);
+}
+__host__ __device__ __forceinline__ int64_t q6k_row_slot(int layout, int nb, int64_t blk) {           // index of (row, block) in s2 / s3
+    if (layout == 0) return blk;
+    const int64_t row = blk / nb; const int b = static_cast<int>(blk - row * nb);
+    return ((row >> 4) * nb + b) * 16 + (row & 15);
+}
 
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
     return __half2float(__ushort_as_half(h));      // exact widening, subnormals included
@@ -126,25 +173,24 @@ __device__ inline float decode_elem(const PackedW& w, int64_t blk, int j) {
         return dl * __int2float_rn(kIq4Codebook[l < 16 ? (b & 15) : (b >> 4)]);
     }
     case T_Q4_K: case T_Q5_K: {
-        const uint8_t* h = w.s[0] + blk * 16;
+        const uint8_t* h = w.s[0] + q4k_hdr_off(w.layout, w.nb, blk);
         const float d = ld_f16(h), dmin = ld_f16(h + 2);
         const int sb = j >> 5, l = j & 31, g = sb >> 1;
         int sc, mn;
         k4_scale_min(sb, h + 4, sc, mn);
-        const uint8_t* qs = (w.type == T_Q4_K ? w.s[1] : w.s[2]) + blk * 128;
-        const uint8_t b = qs[32 * g + l];
+        const uint8_t b = w.type == T_Q4_K ? w.s[1][q4k_qs_off(w.layout, w.nb, blk, 32 * g + l)] : w.s[2][blk * 128 + 32 * g + l];
         int q = (sb & 1) ? (b >> 4) : (b & 15);
         if (w.type == T_Q5_K) q += ((w.s[1][blk * 32 + l] >> sb) & 1) ? 16 : 0;
         return __fsub_rn(__fmul_rn(d * __int2float_rn(sc), __int2float_rn(q)), dmin * __int2float_rn(mn));
     }
     case T_Q6_K: {
-        const float d = ld_f16(w.s[3] + blk * 2);
+        const int64_t slot = q6k_row_slot(w.layout, w.nb, blk);
+        const float d = ld_f16(w.s[3] + slot * 2);
         const int hf = j >> 7, r = j & 127, quarter = r >> 5, l = r & 31;
-        const uint8_t* ql = w.s[0] + blk * 128 + 64 * hf;
-        const uint8_t qh = w.s[1][blk * 64 + 32 * hf + l];
-        const uint8_t lo = ql[l + 32 * (quarter & 1)];
+        const uint8_t qh = w.s[1][q6k_qh_off(w.layout, w.nb, blk, 32 * hf + l)];
+        const uint8_t lo = w.s[0][q6k_ql_off(w.layout, w.nb, blk, 64 * hf + l + 32 * (quarter & 1))];
         const int q = static_cast<int>(((quarter & 2) ? (lo >> 4) : (lo & 15)) | (((qh >> (2 * quarter)) & 3) << 4)) - 32;
-        const int sc = static_cast<int8_t>(w.s[2][blk * 16 + 8 * hf + 2 * quarter + (l >> 4)]);
+        const int sc = static_cast<int8_t>(w.s[2][slot * 16 + 8 * hf + 2 * quarter + (l >> 4)]);
         return __fmul_rn(__fmul_rn(d, __int2float_rn(sc)), __int2float_rn(q));
     }
     case T_Q2_K: {

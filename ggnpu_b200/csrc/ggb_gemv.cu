@@ -98,8 +98,16 @@ struct FQ4K {
     // unit u: block b = u>>3, t8 = u&7, group j = t8>>1, half hf = t8&1:
     //   low nibbles -> values 64j + 16hf + l (sub-block 2j), high nibbles -> +32 (sub-block 2j+1)
     __device__ static void load(const PackedW& w, int64_t rb, int u, Raw& r) {
-        r.q = ldg16(w.s[1] + (rb * 8 + u) * 16);
-        r.h = ldg16(w.s[0] + (rb + (u >> 3)) * 16);
+        if (w.layout == 0) {
+            r.q = ldg16(w.s[1] + (rb * 8 + u) * 16);
+            r.h = ldg16(w.s[0] + (rb + (u >> 3)) * 16);
+        } else {
+            // row-group-major layout: the unit's four words sit in four consecutive lane slots
+            const int64_t blk = rb + (u >> 3);
+            const uint32_t* p = reinterpret_cast<const uint32_t*>(w.s[1] + q4k_qs_off(1, w.nb, blk, (u & 7) * 16));
+            r.q = make_uint4(__ldg(p), __ldg(p + 4), __ldg(p + 8), __ldg(p + 12));
+            r.h = ldg16(w.s[0] + q4k_hdr_off(1, w.nb, blk));
+        }
     }
     __device__ static void load_x(const float4* xs, int u, X& x) {
         const int k0 = (u >> 3) * 256 + ((u & 7) >> 1) * 64 + (u & 1) * 16;
@@ -168,11 +176,20 @@ struct FQ6K {
     __device__ static void load(const PackedW& w, int64_t rb, int u, Raw& r) {
         const int64_t blk = rb + (u >> 3);
         const int t8 = u & 7, hf = t8 >> 2, p = (t8 >> 1) & 1, c = t8 & 1;
-        r.ql = ldg16(w.s[0] + (rb * 8 + u) * 16);
-        r.qh = ldg16(w.s[1] + blk * 64 + hf * 32 + c * 16);
-        const int8_t* sc = reinterpret_cast<const int8_t*>(w.s[2] + blk * 16 + 8 * hf + 2 * p + c);
+        const int64_t slot = q6k_row_slot(w.layout, w.nb, blk);
+        if (w.layout == 0) {
+            r.ql = ldg16(w.s[0] + (rb * 8 + u) * 16);
+            r.qh = ldg16(w.s[1] + blk * 64 + hf * 32 + c * 16);
+        } else {
+            // row-group-major layout: the four words of each 16-byte run sit in four consecutive lane slots
+            const uint32_t* pl = reinterpret_cast<const uint32_t*>(w.s[0] + q6k_ql_off(1, w.nb, blk, 64 * hf + 32 * p + 16 * c));
+            const uint32_t* ph = reinterpret_cast<const uint32_t*>(w.s[1] + q6k_qh_off(1, w.nb, blk, 32 * hf + 16 * c));
+            r.ql = make_uint4(__ldg(pl), __ldg(pl + 4), __ldg(pl + 8), __ldg(pl + 12));
+            r.qh = make_uint4(__ldg(ph), __ldg(ph + 4), __ldg(ph + 8), __ldg(ph + 12));
+        }
+        const int8_t* sc = reinterpret_cast<const int8_t*>(w.s[2] + slot * 16 + 8 * hf + 2 * p + c);
         r.sc_lo = __ldg(sc); r.sc_hi = __ldg(sc + 4);
-        r.d = ldg_f16(w.s[3] + blk * 2);
+        r.d = ldg_f16(w.s[3] + slot * 2);
     }
     __device__ static void load_x(const float4* xs, int u, X& x) {
         const int t8 = u & 7;
@@ -536,10 +553,26 @@ static int dispatch(Context* c, const GemvArgs& a, cudaStream_t s) {
 }
 
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
-    if (!a.x || !a.y || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
-    if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3)) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
+    if ((!a.x && !a.attn_partial) || !a.y || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
+    if (a.attn_partial && (a.w.layout != 1 || a.M != 1)) return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input needs the tensor-core layout and M == 1");
+    if (a.x && ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3))) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
     if (a.epi == EPI_SWIGLU && (a.w2.type != a.w.type || a.w2.N != a.w.N || a.w2.K != a.w.K))
         return set_status(c, GGB_INVALID_PARAM, "gemv: gate/up mismatch");
+    if (a.w.layout == 1) {
+        // tensor-core kernel, two activation rows per pass (each pass streams the weights once)
+        int st = GGB_OK;
+        for (int m0 = 0; m0 < a.M && st == GGB_OK; m0 += 2) {
+            GemvArgs sub = a;
+            sub.M = std::min(2, a.M - m0);
+            sub.x = a.x + static_cast<size_t>(m0) * a.lda;
+            sub.y = a.y + static_cast<size_t>(m0) * a.ldc;
+            if (a.resid) sub.resid = a.resid + static_cast<size_t>(m0) * a.ldc;
+            st = launch_gemv_mma(c, sub, s);
+            if (st == GGB_NOT_FOUND && m0 == 0) break;
+        }
+        if (st != GGB_NOT_FOUND) return st;
+    }
+    if (a.n_cat || a.attn_partial) return set_status(c, GGB_INVALID_PARAM, "gemv: stacked matrices / attention-merge input need the tensor-core kernel");
     if (c->use_tma && a.M == 1) {
         const int st = launch_gemv_tma(c, a, s);
         if (st != GGB_NOT_FOUND) return st;

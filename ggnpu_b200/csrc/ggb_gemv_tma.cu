@@ -30,7 +30,7 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr uint32_t kSpinLimit = 1u << 22;         // ~ tens of ms of polling, far beyond any real wait
+constexpr uint32_t kSpinLimit = 1u << 17;         // each poll can suspend for microseconds: about half a second in all
 constexpr int kMaxStages = 8;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -60,6 +60,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void stamp(unsigned long long* tr, int i) {
+    if (tr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; }
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -204,6 +207,7 @@ struct TmaGemvArgs {
     int wk;               // K slices
     int units_per_slice;
     int* err;
+    unsigned long long* trace;   // optional time stamps of CTA 0
 };
 
 // Shared-memory map (dynamic): [ring: stages * stage_bytes][x limb planes 3*K][x run sums K/16 floats]
@@ -226,6 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
         for (int s = 0; s < a.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x == 0) { stamp(a.trace, 0); if (a.trace && blockIdx.x == 0) a.trace[6] = 2; }
     __syncthreads();
     pdl_launch();       // the next kernel may start streaming its own weights
 
@@ -262,6 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
         // ---------------- consumers ----------------
         const int tid = threadIdx.x;                      // 0 .. 255
         pdl_wait();                                       // x (and resid) come from the previous kernel
+        if (warp == 0) stamp(a.trace, 1);
         // 1. optional RMSNorm scale
         float inv = 1.0f;
         if (a.gamma) {
@@ -317,6 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
             if (lane == 0) xscale[b] = scale * (1.0f / 16384.0f);
         }
         consumer_sync();
+        if (warp == 0) stamp(a.trace, 2);
         // 3. this lane's units: slice wk_i of K, units u = slice_begin + lane + 32 i
         const int wk_i = warp % a.wk, wr_i = warp / a.wk, wr_n = kConsumerWarps / a.wk;
         const int units = K >> 5;
@@ -394,6 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                 }
             }
         }
+        if (warp == 0) stamp(a.trace, 7);
     }
 }
 
@@ -435,6 +443,7 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     a.w = g.w; a.w2 = g.w2; a.x = g.x; a.y = g.y; a.bias = g.bias; a.resid = g.resid; a.gamma = g.gamma; a.eps = g.eps; a.epi = g.epi;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
     a.err = c->d_err;
+    a.trace = trace_slot(c);
 
     auto kern = gemv_tma_kernel<F, DUAL>;
     static size_t smem_allowed = 48 * 1024;
@@ -463,7 +472,7 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
 // M == 1 fast path.  Returns GGB_NOT_FOUND when the shape or format is not covered (the caller then
 // uses the general kernel), GGB_OK or an error otherwise.
 int launch_gemv_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
-    if (g.M != 1 || (reinterpret_cast<uintptr_t>(g.x) & 15)) return GGB_NOT_FOUND;
+    if (g.M != 1 || g.w.layout != 0 || (reinterpret_cast<uintptr_t>(g.x) & 15)) return GGB_NOT_FOUND;
     const bool dual = g.epi == EPI_SWIGLU;
     switch (g.w.type) {
     case T_Q4_K: return dual ? launch_tma<TQ4K, true>(c, g, s) : launch_tma<TQ4K, false>(c, g, s);

@@ -29,6 +29,16 @@ struct GemvArgs {
     // optional fused RMSNorm prologue: x is normalised with gamma before the product
     const float* gamma;   // nullptr => no norm
     float eps;
+    // optional (tensor-core kernel, M == 1): x is the merge of paged-attention split results
+    const float* attn_partial = nullptr;
+    const int32_t* attn_d_pos = nullptr;
+    int attn_pos0 = 0, attn_n_splits = 0, attn_keys_per_split = 0, attn_hd = 0;
+    // optional (tensor-core kernel): up to two more matrices stacked along N sharing x, K, M, epilogue kind
+    int n_cat = 0;
+    PackedW cat_w[2];
+    float* cat_y[2] = {nullptr, nullptr};
+    const float* cat_bias[2] = {nullptr, nullptr};
+    int cat_ldc[2] = {0, 0};
 };
 
 struct DeviceWeight {
@@ -57,6 +67,8 @@ struct Context {
     int* d_err = nullptr;     // device word: non-zero after a bounded device-side wait gave up
     bool use_pdl = true;      // launch the streaming kernels with programmatic dependent launch
     bool use_tma = true;      // M == 1 GEMV through the bulk-copy ring kernel
+    unsigned long long* d_trace = nullptr;   // tuning aid (GGB_TRACE=1): %globaltimer stamps of CTA 0, printed by ggb_sync
+    bool use_mma = true;      // Q4_K in the row-group-major layout + int8 tensor-core GEMV (M <= 2)
 };
 
 int set_status(Context* c, int status, const char* msg);
@@ -73,7 +85,10 @@ int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int 
 // ggb_gemv.cu / ggb_gemv_tma.cu
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
 int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
-int check_device_error(Context* c);     // after a synchronise: turns the device error word into a status
+int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
+int check_device_error(Context* c);
+// tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
+inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
 
 // ggb_ops.cu
 int launch_rms_norm(Context* c, const float* x, float* y, int rows, int n, float eps, const float* gamma, cudaStream_t s);

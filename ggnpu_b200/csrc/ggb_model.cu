@@ -92,15 +92,24 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         GemvArgs a = gemv_args(l.q, m->x, n_tok, H, m->q, qd);
         a.gamma = l.attn_norm; a.eps = d.rms_eps;
         if (l.bq) { a.epi = EPI_ADD_BIAS; a.bias = l.bq; }
-        M_TRY(launch_gemv(c, a, s));
-        a = gemv_args(l.k, m->x, n_tok, H, m->k, kvd);
-        a.gamma = l.attn_norm; a.eps = d.rms_eps;
-        if (l.bk) { a.epi = EPI_ADD_BIAS; a.bias = l.bk; }
-        M_TRY(launch_gemv(c, a, s));
-        a = gemv_args(l.v, m->x, n_tok, H, m->v, kvd);
-        a.gamma = l.attn_norm; a.eps = d.rms_eps;
-        if (l.bv) { a.epi = EPI_ADD_BIAS; a.bias = l.bv; }
-        M_TRY(launch_gemv(c, a, s));
+        const bool biases_agree = (l.bq != nullptr) == (l.bk != nullptr) && (l.bq != nullptr) == (l.bv != nullptr);
+        if (n_tok <= 2 && biases_agree && l.q->w.layout == 1 && l.k->w.layout == 1 && l.v->w.layout == 1) {
+            // q, k and v in one launch: three matrices stacked along N share the normalised x
+            a.n_cat = 2;
+            a.cat_w[0] = l.k->w; a.cat_y[0] = m->k; a.cat_bias[0] = l.bk; a.cat_ldc[0] = kvd;
+            a.cat_w[1] = l.v->w; a.cat_y[1] = m->v; a.cat_bias[1] = l.bv; a.cat_ldc[1] = kvd;
+            M_TRY(launch_gemv(c, a, s));
+        } else {
+            M_TRY(launch_gemv(c, a, s));
+            a = gemv_args(l.k, m->x, n_tok, H, m->k, kvd);
+            a.gamma = l.attn_norm; a.eps = d.rms_eps;
+            if (l.bk) { a.epi = EPI_ADD_BIAS; a.bias = l.bk; }
+            M_TRY(launch_gemv(c, a, s));
+            a = gemv_args(l.v, m->x, n_tok, H, m->v, kvd);
+            a.gamma = l.attn_norm; a.eps = d.rms_eps;
+            if (l.bv) { a.epi = EPI_ADD_BIAS; a.bias = l.bv; }
+            M_TRY(launch_gemv(c, a, s));
+        }
 
         KvAppendArgs ka{};
         ka.q = m->q; ka.k = m->k; ka.v = m->v;
@@ -109,17 +118,29 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         ka.block_table = m->block_table; ka.cos_tab = m->cos_tab; ka.sin_tab = m->sin_tab;
         ka.q_norm = l.q_norm; ka.k_norm = l.k_norm; ka.d_pos = dpos; ka.pos0 = pos0;
         ka.n_head = d.n_head; ka.n_kv = d.n_kv; ka.head_dim = hd; ka.page = m->page; ka.neox = d.rope_neox; ka.eps = d.rms_eps;
-        M_TRY(launch_rope_append(c, ka, n_tok, s));
+        if (n_tok > 1) M_TRY(launch_rope_append(c, ka, n_tok, s));   // single-token steps fuse this into attention
 
         AttnPagedArgs aa{};
+        if (n_tok == 1) {
+            aa.fuse = 1; aa.neox = d.rope_neox; aa.k_new = m->k; aa.v_new = m->v;
+            aa.k_cache_w = ka.k_cache; aa.v_cache_w = ka.v_cache; aa.cos_tab = m->cos_tab; aa.sin_tab = m->sin_tab;
+            aa.q_norm = l.q_norm; aa.k_norm = l.k_norm; aa.eps = d.rms_eps;
+        }
         aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = m->block_table;
         aa.partial = m->partial; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
         aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
         aa.pages_per_split = m->pages_per_split;
+        // single-token steps: the output projection merges the attention splits itself
+        const bool merge_in_gemv = n_tok == 1 && l.o->w.layout == 1;
+        aa.skip_merge = merge_in_gemv ? 1 : 0;
         M_TRY(launch_attn_paged(c, aa, n_tok, s));
 
         a = gemv_args(l.o, m->att, n_tok, qd, m->x, H);
         a.epi = EPI_RESIDUAL; a.resid = m->x;
+        if (merge_in_gemv) {
+            a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = m->n_splits;
+            a.attn_keys_per_split = m->pages_per_split * m->page; a.attn_hd = hd;
+        }
         M_TRY(launch_gemv(c, a, s));
 
         a = gemv_args(l.gate, m->x, n_tok, H, m->act, F);

@@ -28,10 +28,122 @@ __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restri
     }
 }
 
+// Q4_K into the row-group-major layout (layout 1 of ggb_formats.cuh).  `raw` holds `rows` GGUF rows
+// starting at the first row of group `g0`; groups g0 .. g0+groups-1 are written; rows past the end
+// of the matrix become zero blocks (d = dmin = 0 decodes to 0).
+__global__ void repack_q4k_rg16_kernel(const uint8_t* __restrict__ raw, int64_t rows, int nb, int64_t groups,
+                                       uint8_t* __restrict__ hdr, uint8_t* __restrict__ qs) {
+    const int64_t n_hdr = groups * nb * 16 * 4;          // 32-bit words of the header stream
+    const int64_t n_qs = groups * nb * 4 * 32 * 4;       // 32-bit words of the quant stream
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_hdr + n_qs;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int64_t row; int b, src_byte; uint8_t* dst;
+        if (i < n_hdr) {
+            const int word = static_cast<int>(i & 3);
+            const int64_t e = i >> 2;                     // (group * nb + b) * 16 + r
+            const int r = static_cast<int>(e & 15);
+            const int64_t gb = e >> 4;
+            b = static_cast<int>(gb % nb); row = (gb / nb) * 16 + r;
+            src_byte = word * 4; dst = hdr + i * 4;
+        } else {
+            const int64_t k = i - n_hdr;
+            const int word = static_cast<int>(k & 3), lane = static_cast<int>((k >> 2) & 31), j = static_cast<int>((k >> 7) & 3);
+            const int64_t gb = k >> 9;
+            b = static_cast<int>(gb % nb); row = (gb / nb) * 16 + (lane >> 2) + 8 * (word & 1);
+            src_byte = 16 + 32 * j + 16 * (word >> 1) + 4 * (lane & 3); dst = qs + k * 4;
+        }
+        uchar4 v = make_uchar4(0, 0, 0, 0);
+        if (row < rows) {
+            const uint8_t* sp = raw + (row * nb + b) * 144 + src_byte;
+            v = make_uchar4(sp[0], sp[1], sp[2], sp[3]);
+        }
+        *reinterpret_cast<uchar4*>(dst) = v;
+    }
+}
+
+// Q6_K into its row-group-major layout (ggb_formats.cuh).  Same contract as the Q4_K kernel.
+__global__ void repack_q6k_rg16_kernel(const uint8_t* __restrict__ raw, int64_t rows, int nb, int64_t groups,
+                                       uint8_t* __restrict__ s0, uint8_t* __restrict__ s1, uint8_t* __restrict__ s2, uint8_t* __restrict__ s3) {
+    const int64_t gbs = groups * nb;
+    const int64_t n0 = gbs * 512, n1 = gbs * 256, n2 = gbs * 64, n3 = gbs * 16;   // 32-bit words (s3: 16-bit)
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n0 + n1 + n2 + n3;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int64_t gb, row; int src_byte, nbytes = 4; uint8_t* dst;
+        if (i < n0) {
+            const int word = static_cast<int>(i & 3), lane = static_cast<int>((i >> 2) & 31), combo = static_cast<int>((i >> 7) & 3);
+            gb = i >> 9;
+            row = (lane >> 2) + 8 * (word >> 1);
+            src_byte = 64 * (combo >> 1) + 32 * (word & 1) + 16 * (combo & 1) + 4 * (lane & 3); dst = s0 + i * 4;
+        } else if (i < n0 + n1) {
+            const int64_t k = i - n0;
+            const int word = static_cast<int>(k & 3), lane = static_cast<int>((k >> 2) & 31), hf = static_cast<int>((k >> 7) & 1);
+            gb = k >> 8;
+            row = (lane >> 2) + 8 * (word & 1);
+            src_byte = 128 + 32 * hf + 16 * (word >> 1) + 4 * (lane & 3); dst = s1 + k * 4;
+        } else if (i < n0 + n1 + n2) {
+            const int64_t k = i - n0 - n1;
+            gb = k >> 6; row = (k >> 2) & 15; src_byte = 192 + 4 * static_cast<int>(k & 3); dst = s2 + k * 4;
+        } else {
+            const int64_t k = i - n0 - n1 - n2;
+            gb = k >> 4; row = k & 15; src_byte = 208; nbytes = 2; dst = s3 + k * 2;
+        }
+        const int b = static_cast<int>(gb % nb);
+        row += (gb / nb) * 16;
+        const bool ok = row < rows;
+        const uint8_t* sp = raw + (row * nb + b) * 210 + src_byte;
+        for (int q = 0; q < nbytes; ++q) dst[q] = ok ? sp[q] : 0;
+    }
+}
+
+// Q4_K / Q6_K in the row-group-major layouts: stage whole row groups, permute on the device.
+static int upload_rg16(Context* c, uint32_t type, int64_t N, int K, const void* host_rows, DeviceWeight** out) {
+    const int nb = K / 256;
+    const int64_t groups = (N + 15) / 16;
+    const bool q4 = type == T_Q4_K;
+    // bytes of each stream per (group, block)
+    const int per_gb[4] = {q4 ? 256 : 2048, q4 ? 2048 : 1024, q4 ? 0 : 256, q4 ? 0 : 32};
+    const int block_bytes = q4 ? 144 : 210;
+    DeviceWeight* dw = new DeviceWeight();
+    size_t off[4], acc = 0;
+    for (int i = 0; i < 4; ++i) { off[i] = acc; acc += align_up(static_cast<size_t>(groups) * nb * per_gb[i], 256); }
+    dw->bytes = acc;
+    cudaError_t e = cudaMalloc(&dw->base, dw->bytes);
+    if (e != cudaSuccess) { delete dw; return cuda_status(c, e, "cudaMalloc(weight)"); }
+    uint8_t* p = static_cast<uint8_t*>(dw->base);
+    dw->w.N = N; dw->w.K = K; dw->w.nb = nb; dw->w.type = type; dw->w.layout = 1;
+    for (int i = 0; i < 4; ++i) dw->w.s[i] = per_gb[i] ? p + off[i] : nullptr;
+    const size_t row_bytes = static_cast<size_t>(nb) * block_bytes;
+    const int64_t chunk_groups = std::max<int64_t>(1, static_cast<int64_t>((size_t(256) << 20) / (16 * row_bytes)));
+    void* staging = nullptr;
+    e = cudaMalloc(&staging, static_cast<size_t>(std::min(groups, chunk_groups)) * 16 * row_bytes);
+    if (e != cudaSuccess) { free_weight(dw); return cuda_status(c, e, "cudaMalloc(staging)"); }
+    for (int64_t g0 = 0; g0 < groups && e == cudaSuccess; g0 += chunk_groups) {
+        const int64_t ng = std::min(chunk_groups, groups - g0);
+        const int64_t rows = std::min<int64_t>(ng * 16, N - g0 * 16);
+        e = cudaMemcpyAsync(staging, static_cast<const uint8_t*>(host_rows) + static_cast<size_t>(g0) * 16 * row_bytes,
+                            static_cast<size_t>(rows) * row_bytes, cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) break;
+        const int64_t items = ng * nb * (q4 ? (16 * 4 + 4 * 32 * 4) : (512 + 256 + 64 + 16));
+        const int grid = static_cast<int>(std::min<int64_t>((items + 255) / 256, 148 * 16));
+        uint8_t* d[4];
+        for (int i = 0; i < 4; ++i) d[i] = p + off[i] + static_cast<size_t>(g0) * nb * per_gb[i];
+        if (q4) repack_q4k_rg16_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(staging), rows, nb, ng, d[0], d[1]);
+        else repack_q6k_rg16_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const uint8_t*>(staging), rows, nb, ng, d[0], d[1], d[2], d[3]);
+        c->launches++;
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    }
+    cudaFree(staging);
+    if (e != cudaSuccess) { free_weight(dw); return cuda_status(c, e, "weight pack (row groups)"); }
+    *out = dw;
+    return GGB_OK;
+}
+
 int upload_weight(Context* c, uint32_t type, int64_t N, int K, const void* host_rows, DeviceWeight** out) {
     const FormatInfo f = format_info(type);
     if (!f.block_elems) return set_status(c, GGB_INVALID_PARAM, "unsupported weight type");
     if (!host_rows || N <= 0 || K <= 0 || K % f.block_elems) return set_status(c, GGB_INVALID_PARAM, "bad weight shape");
+    if ((type == T_Q4_K || type == T_Q6_K) && c->use_mma) return upload_rg16(c, type, N, K, host_rows, out);
     const int nb = K / f.block_elems;
     const size_t blocks = static_cast<size_t>(N) * nb;
     const size_t raw_bytes = blocks * f.block_bytes;
