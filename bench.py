@@ -396,6 +396,7 @@ def run_micro(args):
                 print(json.dumps({"micro": "quant_matmul", "type": tname, "N": N, "K": K, "M": M, "dual": bool(args.dual),
                                   "avg_launch_us": us, "back_to_back_us": b2b_us, "alg_bytes": alg, "gbs": alg / us / 1e3,
                                   "gbs_back_to_back": alg / b2b_us / 1e3, "frac_of_hbm_peak": alg / b2b_us / 1e3 / peak,
+                                  "tflops_back_to_back": 2.0 * M * N * K * (2 if args.dual else 1) / b2b_us / 1e6,
                                   "peak_source": peak_kind, "copies": copies}), flush=True)
             for w in ws:
                 b.free_weight(w)

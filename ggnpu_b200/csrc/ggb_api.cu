@@ -81,6 +81,8 @@ int ggb_create(int device, ggb_handle* out) {
     c->use_pdl = getenv("GGB_NO_PDL") == nullptr;
     c->use_tma = getenv("GGB_NO_TMA") == nullptr;
     c->use_mma = getenv("GGB_NO_MMA") == nullptr;
+    c->use_tc = getenv("GGB_NO_TC") == nullptr;
+    if (const char* m = getenv("GGB_TC_MIN_M")) c->tc_min_m = std::max(1, atoi(m));
     if (getenv("GGB_TRACE") && cudaMalloc(&c->d_trace, 4096 * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(c->d_trace, 0, 4096 * sizeof(unsigned long long));
     *out = c;
     return GGB_OK;
@@ -92,6 +94,7 @@ void ggb_destroy(ggb_handle h) {
     cudaStreamSynchronize(h->stream);
     for (auto& kv : h->weight_cache) free_weight(kv.second);
     for (int i = 0; i < 4; ++i) if (h->d_scratch[i]) cudaFree(h->d_scratch[i]);
+    if (h->d_xb) cudaFree(h->d_xb);
     if (h->h_pinned) cudaFreeHost(h->h_pinned);
     if (h->d_err) cudaFree(h->d_err);
     cudaStreamDestroy(h->stream);

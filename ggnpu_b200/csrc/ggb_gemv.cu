@@ -558,6 +558,18 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
     if (a.x && ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3))) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
     if (a.epi == EPI_SWIGLU && (a.w2.type != a.w.type || a.w2.N != a.w.N || a.w2.K != a.w.K))
         return set_status(c, GGB_INVALID_PARAM, "gemv: gate/up mismatch");
+    if (c->use_tc && a.M >= c->tc_min_m && a.x && !a.n_cat && !a.attn_partial) {
+        const size_t need = gemm_tc_xb_elems(a);
+        if (need > c->d_xb_elems) {
+            cudaStreamSynchronize(s);
+            if (c->d_xb) cudaFree(c->d_xb);
+            c->d_xb = nullptr; c->d_xb_elems = 0;
+            if (cuda_status(c, cudaMalloc(&c->d_xb, need * 2), "cudaMalloc(bf16 activations)") != GGB_OK) return c->last_status;
+            c->d_xb_elems = need;
+        }
+        const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
     if (a.w.layout == 1) {
         // tensor-core kernel, two activation rows per pass (each pass streams the weights once)
         int st = GGB_OK;

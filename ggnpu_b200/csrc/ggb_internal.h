@@ -69,6 +69,10 @@ struct Context {
     bool use_tma = true;      // M == 1 GEMV through the bulk-copy ring kernel
     unsigned long long* d_trace = nullptr;   // tuning aid (GGB_TRACE=1): %globaltimer stamps of CTA 0, printed by ggb_sync
     bool use_mma = true;      // Q4_K in the row-group-major layout + int8 tensor-core GEMV (M <= 2)
+    bool use_tc = true;       // M >= tc_min_m through the tcgen05 GEMM (bf16 operands, fp32 accumulation in TMEM)
+    int tc_min_m = 32;
+    void* d_xb = nullptr;     // bf16 activations of the tcgen05 GEMM (grown on demand, never during graph capture)
+    size_t d_xb_elems = 0;
 };
 
 int set_status(Context* c, int status, const char* msg);
@@ -87,6 +91,9 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
 int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 int check_device_error(Context* c);
+// ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
+int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, cudaStream_t s);
+size_t gemm_tc_xb_elems(const GemvArgs& a);
 // tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
 inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
 

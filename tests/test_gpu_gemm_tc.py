@@ -1,0 +1,136 @@
+"""Prefill GEMM on the tcgen05 tensor cores (M >= 32 through Backend::mul_mat_q and the device-pointer
+entry points) vs the CPU oracle.
+
+Two bars, both written here:
+  * "bf16 model": the kernel rounds the exactly dequantised weights and the activations to bf16 once
+    and accumulates in fp32.  Against the oracle's dequantised rows with the SAME two roundings
+    applied (float64 accumulation) only the summation order differs: rel-L2 <= 1e-5,
+    max-abs <= 2e-5 * max|ref|.  This pins tile layout, swizzle, descriptors and the epilogue.
+  * "reference": against the exact fp32 matmul of the reference's CPU path (dequant_tensor_row +
+    sequential dot, src/cli/main.cpp:1379-1388) the operand rounding leaves rel-L2 <= 5e-3 (two
+    roundings of relative size 2^-9, uncorrelated over K)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from ggnpu_b200 import synth as S
+from ggnpu_b200.backend import Status
+
+pytestmark = pytest.mark.gpu
+
+TYPES = [S.Q4_K, S.Q6_K, S.Q8_0, S.Q4_0, S.IQ4_XS, S.Q5_K, S.Q2_K, S.Q3_K, S.Q4_1, S.IQ4_NL, S.F16, S.BF16]
+
+
+def bf16(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float64).numpy()
+
+
+def make(t, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    return S.quantize(torch.randn(N, K, generator=g) * 0.02, t).numpy()
+
+
+def dequant(oracle, t, raw, N, K):
+    return np.stack([oracle.dequant_row(t, raw, r, K) for r in range(N)])
+
+
+def check_model(got, A, Wd, extra=None):
+    want = bf16(A) @ bf16(Wd).T
+    if extra is not None:
+        want = want + extra
+    assert np.isfinite(got).all()
+    assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_all_formats_bf16_model_and_reference(backend, oracle, t):
+    N, K, M = 200, 512, 100            # N not a multiple of the 128-row tile, M not a multiple of 64
+    raw = make(t, N, K, 3)
+    A = np.random.default_rng(3).standard_normal((M, K)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    before = backend.launch_count()
+    assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+    assert backend.launch_count() > before
+    check_model(C, A, dequant(oracle, t, raw, N, K))
+    assert rel_l2(C, oracle.matmul_exact(A, raw, t, N, K)) <= 5e-3
+
+
+@pytest.mark.parametrize("M", [32, 64, 257, 600])
+@pytest.mark.parametrize("t", [S.Q4_K, S.Q6_K])
+def test_token_tiles(backend, oracle, t, M):
+    """One tile, exactly one tile, one tile + 1 row, several tiles; K with several 64-steps per stage parity."""
+    N, K = 256, 1024
+    raw = make(t, N, K, 5)
+    A = np.random.default_rng(M).standard_normal((M, K)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+    check_model(C, A, dequant(oracle, t, raw, N, K))
+
+
+def test_k_of_one_and_two_steps(backend, oracle):
+    """K = 256 with a 32-wide format has four 64-steps; K = 64 (one step, no stage reuse) and K = 128."""
+    for K in (64, 128, 256):
+        t, N, M = S.Q8_0, 130, 40
+        raw = make(t, N, K, K)
+        A = np.random.default_rng(K).standard_normal((M, K)).astype(np.float32)
+        C = np.full((M, N), np.nan, np.float32)
+        assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+        check_model(C, A, dequant(oracle, t, raw, N, K))
+
+
+def test_benchmark_shapes_sampled_rows(backend, oracle):
+    """Llama-3.2-1B projection shapes at a 256-token chunk; a sample of weight rows is checked."""
+    M = 256
+    for (N, K), t in (((8192, 2048), S.Q4_K), ((2048, 8192), S.Q6_K), ((2048, 2048), S.Q4_K)):
+        raw = make(t, N, K, 9)
+        A = np.random.default_rng(9).standard_normal((M, K)).astype(np.float32)
+        C = np.full((M, N), np.nan, np.float32)
+        assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+        assert np.isfinite(C).all()
+        rows = np.unique(np.concatenate([np.arange(4), np.arange(N - 4, N), np.random.default_rng(1).integers(0, N, 40)]))
+        rb = S.row_bytes(t, K)
+        sub = np.ascontiguousarray(raw.reshape(N, rb)[rows])
+        check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K))
+
+
+def test_fused_epilogues(backend, oracle):
+    """RMSNorm prologue, bias, residual (aliasing y) and the SwiGLU pair at M = 70 on device pointers."""
+    t, N, K, M = S.Q4_K, 192, 512, 70
+    wg, wu = make(t, N, K, 1), make(t, N, K, 2)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    gamma = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    resid = rng.standard_normal((M, N)).astype(np.float32)
+    dev = torch.device("cuda:0")
+    dx, dg, db = torch.from_numpy(x).to(dev), torch.from_numpy(gamma).to(dev), torch.from_numpy(bias).to(dev)
+    dy = torch.empty((M, N), device=dev, dtype=torch.float32)
+    hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
+    # the kernel normalises in fp32 (x * inv * gamma) and then rounds to bf16
+    inv = 1.0 / np.sqrt((x.astype(np.float32) ** 2).sum(1, dtype=np.float32) / np.float32(K) + np.float32(1e-5))
+    xn = (x * inv[:, None].astype(np.float32) * gamma).astype(np.float32)
+    Wg, Wu = dequant(oracle, t, wg, N, K), dequant(oracle, t, wu, N, K)
+    g_ref, u_ref = bf16(xn) @ bf16(Wg).T, bf16(xn) @ bf16(Wu).T
+
+    def run(fn):
+        torch.cuda.synchronize()
+        fn()
+        backend.sync()
+        return dy.cpu().numpy()
+
+    got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 1, db.data_ptr(), dg.data_ptr(), 1e-5))
+    assert rel_l2(got, g_ref + bias) <= 1e-4
+    dy.copy_(torch.from_numpy(resid))
+    got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 2, dy.data_ptr(), dg.data_ptr(), 1e-5))
+    assert rel_l2(got, g_ref + resid) <= 1e-4
+    got = run(lambda: backend.gemv_swiglu_device(hg, hu, dx.data_ptr(), M, K, dy.data_ptr(), N, dg.data_ptr(), 1e-5))
+    want = g_ref / (1.0 + np.exp(-g_ref)) * u_ref
+    assert rel_l2(got, want) <= 1e-4
+    # against the reference's exact arithmetic: bf16 operand tolerance
+    xo = np.stack([oracle.rms_norm(r, 1e-5, gamma) for r in x])
+    ge, ue = oracle.matmul_exact(xo, wg, t, N, K), oracle.matmul_exact(xo, wu, t, N, K)
+    assert rel_l2(got, np.stack([oracle.silu(r) for r in ge]) * ue) <= 8e-3
+    backend.free_weight(hg)
+    backend.free_weight(hu)
