@@ -83,6 +83,8 @@ int ggb_create(int device, ggb_handle* out) {
     c->use_mma = getenv("GGB_NO_MMA") == nullptr;
     c->use_tc = getenv("GGB_NO_TC") == nullptr;
     if (const char* m = getenv("GGB_TC_MIN_M")) c->tc_min_m = std::max(1, atoi(m));
+    c->tc_generic = getenv("GGB_TC_GENERIC") != nullptr;
+    if (const char* m = getenv("GGB_TC_RT")) c->tc_rt = atoi(m);
     if (getenv("GGB_TRACE") && cudaMalloc(&c->d_trace, 4096 * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(c->d_trace, 0, 4096 * sizeof(unsigned long long));
     *out = c;
     return GGB_OK;

@@ -1,21 +1,30 @@
 // Prefill GEMM on the 5th-generation tensor cores: Y[M tokens][N] = X[M][K] * W[N][K]^T with W a
-// quantised GGUF matrix (any supported format) and M >= 17 (smaller M uses the GEMV kernels).
+// quantised GGUF matrix (any supported format) and M >= 32 (smaller M uses the GEMV kernels).
 // Replaces the batched-prefill use of mul_mat_weight (src/cli/main.cpp:3256-3267, M <= 256 chunks).
 //
-// Computed as D^T: the weight rows are the UMMA "M" operand (128 per CTA), the tokens the "N" operand
-// (up to 256 per CTA), the accumulator D[128 rows][tokens] lives in tensor memory (TMEM, fp32).
-// Per K step of 64:
-//   * all 8 warps dequantise the CTA's 128 x 64 weight tile with the same exact fp32 decoder the
-//     dequant kernel uses (decode_elem), round to bf16 and store it into shared memory in the K-major
-//     128-byte-swizzled layout tcgen05.mma reads; they also copy the 64-wide bf16 activation slice
-//     (prepared once per call by x_to_bf16_kernel, RMS norm fused) in the same layout;
-//   * after fence.proxy.async + a CTA barrier one thread issues four tcgen05.mma (K = 16 each) that
-//     accumulate into TMEM, then tcgen05.commit to the stage's mbarrier; the MMAs run asynchronously,
-//     so the tensor cores work on stage s while the warps dequantise stage s^1.
-// Epilogue: tcgen05.ld brings the accumulator to registers (one weight row per lane), bias / residual
-// / SwiGLU are applied and rows are stored so that 32 lanes write 32 consecutive n of one token.
+// Computed as D^T: weight rows are the UMMA "M" operand (one or two 128-row tiles per CTA), tokens
+// the "N" operand (up to 256 per CTA); the accumulators D[128 rows][tokens] live in tensor memory
+// (TMEM, fp32).  Operands are fp16: the quantised formats carry fp16 block scales, so Q8_0 / Q4_0
+// weights are reproduced exactly and K-quant sub-block scales lose 2^-12; activations are rounded to
+// fp16 once (clamped to the finite range).  Warp roles, K step 64, ring of `stages` stages:
+//   * warps 0-7 (dequant): read the quantised fragments with 128-bit loads, expand them with byte
+//     permutes + packed half arithmetic (integer -> fp16 through the 0x6400 | q trick, exact), scale,
+//     and store the 128 x 64 tiles into shared memory in the K-major 128-byte-swizzled layout
+//     tcgen05.mma reads; fence.proxy.async, then one arrive per warp on the stage's `a_full` barrier;
+//   * warp 9 lane 0 (activation producer): one cp.async.bulk per stage brings the token tile, which
+//     x_prep_kernel wrote once per call already in the swizzled tile image (RMS norm fused there);
+//   * warp 8 lane 0 (MMA issuer): waits for both, issues four tcgen05.mma (K = 16) per weight tile
+//     accumulating in TMEM, and tcgen05.commit to the stage's `free` barrier, so the tensor cores run
+//     stage s while the other warps fill the next stages.
+// Inside every 32-run of K both operands use the same permutation (position 8t + 4h + i holds
+// element 16h + 4t + i): a dot product does not depend on the order of its terms, and this order is
+// the one in which the row-group-major Q4_K / Q6_K fragments deliver 16-byte chunks.
+// Epilogue: tcgen05.ld brings the accumulators to registers (one weight row per lane); bias /
+// residual / SwiGLU are applied and 32 lanes store 32 consecutive n of one token.
 // No cluster launch and no multicast copy is used.  Every mbarrier wait is bounded.
-#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
 
 #include "ggb_internal.h"
 
@@ -23,14 +32,22 @@ namespace ggb {
 
 namespace {
 
-constexpr int kTileN = 128;            // weight rows per CTA (UMMA M)
-constexpr int kBK = 64;                // K per pipeline step (128 bytes of bf16: one swizzle row)
-constexpr int kThreadsG = 256;
+constexpr int kBK = 64;                // K per pipeline step (128 bytes of fp16: one swizzle row)
+constexpr int kDequantThreads = 256;
+constexpr int kThreadsG = 320;         // 8 dequant warps + MMA warp + producer warp
+constexpr int kMaxStagesG = 6;
 constexpr uint32_t kSpin = 1u << 17;
+enum : int { F_GEN = 0, F_Q4K = 1, F_Q6K = 2, F_Q80 = 3 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -44,8 +61,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     atomicExch(err, 4);
     return false;
 }
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
+}
 
-// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, swizzled in
+// Shared-memory matrix descriptor of a K-major 16-bit tile whose rows are 128 bytes, swizzled in
 // 8-row / 1024-byte atoms (tile base 1024-byte aligned): start address, stride between 8-row groups
 // 1024 bytes, descriptor version 1 (sm_100), swizzle mode 2 (128 bytes).
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -57,11 +78,12 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                               // bits 61-63: 128-byte swizzle
     return d;
 }
-// Instruction descriptor, kind::f16: D fp32, A and B bf16, both K-major, shape M x N.
+// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (format 0), both K-major,
+// N / 8 in bits 17-22, M / 16 in bits 24-28.
 __device__ __forceinline__ uint32_t umma_idesc(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+    return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
@@ -84,28 +106,36 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 
 struct GemmArgs {
     PackedW w, w2;                // w2: second matrix of the fused gate/up pair (dual)
-    const __nv_bfloat16* xb;      // [M_pad][K] activations in bf16
+    const __half* xb;             // activation tile images, see x_prep_kernel
     float* y;                     // [M][ldc]
     const float* bias;
     const float* resid;
     int M, K, ldc, epi, dual;
-    int tn;                       // tokens per CTA tile (multiple of 16, <= 256)
-    int tmem_cols;                // power of two >= tn * (dual ? 2 : 1), >= 32
+    int tn;                       // tokens per CTA tile (multiple of 64, <= 256)
+    int tmem_cols;                // power of two >= accumulator columns, >= 32
+    int stages;
     int* err;
 };
 
-// ---- activations: fp32 -> bf16 with the fused RMS norm ------------------------------------------
-// One CTA per token row; rows M .. M_pad-1 are zero.  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma
-// (src/backends/cpu_ref/cpu_ref.cpp:139-156), then round to nearest even bf16.
-__global__ void x_to_bf16_kernel(const float* __restrict__ x, int lda, int M, int K, const float* __restrict__ gamma, float eps,
-                                 __nv_bfloat16* __restrict__ out) {
+// byte offset of 16-byte chunk c (0..7) of row r inside a K-major 128-byte-swizzled tile
+__host__ __device__ __forceinline__ uint32_t swz_off(int r, int c) { return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(c ^ (r & 7)) << 4); }
+// element of a 64-wide K step held by slot e (0..7) of chunk c (0..7)
+__host__ __device__ __forceinline__ int perm_k(int c, int e) { return 32 * (c >> 2) + 16 * (e >> 2) + 4 * (c & 3) + (e & 3); }
+
+// ---- activations: fp32 -> fp16 tile images with the fused RMS norm -------------------------------
+// out[m_tile][k_step][tn rows x 128 B] is exactly the shared-memory image of the activation tile of
+// one pipeline step (swizzled, K permuted), so the GEMM fetches it with one bulk copy.  Rows >= M are
+// zero.  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma (src/backends/cpu_ref/cpu_ref.cpp:139-156).
+__global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K, int tn, const float* __restrict__ gamma, float eps,
+                              __half* __restrict__ out) {
     __shared__ float red[32];
-    const int row = blockIdx.x;
-    __nv_bfloat16* o = out + static_cast<size_t>(row) * K;
-    if (row >= M) { for (int i = threadIdx.x; i < K; i += blockDim.x) o[i] = __float2bfloat16_rn(0.0f); return; }
-    const float* xr = x + static_cast<size_t>(row) * lda;
+    const int row = blockIdx.x, mt = row / tn, r = row - mt * tn;
+    const int n_steps = K / kBK;
+    uint8_t* tile0 = reinterpret_cast<uint8_t*>(out) + static_cast<size_t>(mt) * n_steps * tn * 128;
+    const bool live = row < M;
+    const float* xr = x + static_cast<size_t>(live ? row : 0) * lda;
     float inv = 1.0f;
-    if (gamma) {
+    if (gamma && live) {
         float ss = 0.0f;
         for (int i = threadIdx.x; i < K; i += blockDim.x) ss += xr[i] * xr[i];
 #pragma unroll
@@ -116,49 +146,131 @@ __global__ void x_to_bf16_kernel(const float* __restrict__ x, int lda, int M, in
         for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
         inv = 1.0f / sqrtf(tot / static_cast<float>(K) + eps);
     }
-    for (int i = threadIdx.x; i < K; i += blockDim.x) o[i] = __float2bfloat16_rn(gamma ? xr[i] * inv * gamma[i] : xr[i]);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {          // one 16-byte chunk per iteration
+        const int ks = i >> 3, c = i & 7;
+        uint32_t p[4] = {0u, 0u, 0u, 0u};
+        if (live) {
+#pragma unroll
+            for (int hv = 0; hv < 2; ++hv) {
+                const int k = ks * kBK + perm_k(c, 4 * hv);
+                float4 v = *reinterpret_cast<const float4*>(xr + k);
+                if (gamma) {
+                    const float4 gm = *reinterpret_cast<const float4*>(gamma + k);
+                    v.x = v.x * inv * gm.x; v.y = v.y * inv * gm.y; v.z = v.z * inv * gm.z; v.w = v.w * inv * gm.w;
+                }
+                const float lim = 65504.0f;
+                const __half2 a = __floats2half2_rn(fminf(fmaxf(v.x, -lim), lim), fminf(fmaxf(v.y, -lim), lim));
+                const __half2 b = __floats2half2_rn(fminf(fmaxf(v.z, -lim), lim), fminf(fmaxf(v.w, -lim), lim));
+                p[2 * hv] = *reinterpret_cast<const uint32_t*>(&a);
+                p[2 * hv + 1] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+        }
+        *reinterpret_cast<uint4*>(tile0 + static_cast<size_t>(ks) * tn * 128 + swz_off(r, c)) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
 }
 
-// byte offset of 16-byte chunk c (0..7) of row r inside a K-major 128-byte-swizzled tile
-__device__ __forceinline__ uint32_t swz_off(int r, int c) { return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(c ^ (r & 7)) << 4); }
+// ---- dequantisation into fp16 --------------------------------------------------------------------
+__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) { return as_u32(__floats2half2_rn(a, b)); }
+// The four bytes of n (each <= 255) as exact halves minus `bias`: 0x6400 | b is the half 1024 + b.
+__device__ __forceinline__ void bytes_to_half(uint32_t n, __half2 bias, __half2& p01, __half2& p23) {
+    p01 = __hsub2(as_h2(__byte_perm(n, 0x64646464u, 0x4140)), bias);
+    p23 = __hsub2(as_h2(__byte_perm(n, 0x64646464u, 0x4342)), bias);
+}
 
-// Dequantise 8 consecutive weights k0..k0+7 of `row` to bf16 (exact fp32 decode, then one rounding).
-__device__ __forceinline__ uint4 dequant8_bf16(const PackedW& w, int64_t row, int k0, int block_elems) {
+// Q4_K, row-group-major layout.  Table row (8 words): word sb = half(d * sc_sb) | half(-dmin * m_sb) << 16.
+__device__ __forceinline__ void q4k_table_words(const uint4 h, uint32_t* dst) {     // h: the row's 16-byte block header
+    const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(h.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(h.x >> 16)));
+    auto B = [&](int i) -> int { const uint32_t wd = i < 4 ? h.y : (i < 8 ? h.z : h.w); return static_cast<int>((wd >> (8 * (i & 3))) & 0xFFu); };
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb) {
+        int sc, mn;
+        if (sb < 4) { sc = B(sb) & 63; mn = B(sb + 4) & 63; }
+        else { sc = (B(sb + 4) & 15) | ((B(sb - 4) >> 6) << 4); mn = (B(sb + 4) >> 4) | ((B(sb) >> 6) << 4); }
+        dst[sb] = pack_h2(d * static_cast<float>(sc), -(dmin * static_cast<float>(mn)));
+    }
+}
+// one 16-byte chunk: slots 0-3 from the nibbles in na, 4-7 from nb_; e = scale | offset << 16
+__device__ __forceinline__ uint4 q4k_chunk(uint32_t na, uint32_t nb_, uint32_t e) {
+    const __half2 k1024 = as_h2(0x64006400u);
+    const __half2 ss = as_h2(__byte_perm(e, e, 0x1010)), oo = as_h2(__byte_perm(e, e, 0x3232));
+    __half2 p0, p1, p2, p3;
+    bytes_to_half(na, k1024, p0, p1);
+    bytes_to_half(nb_, k1024, p2, p3);
+    return make_uint4(as_u32(__hfma2(p0, ss, oo)), as_u32(__hfma2(p1, ss, oo)), as_u32(__hfma2(p2, ss, oo)), as_u32(__hfma2(p3, ss, oo)));
+}
+
+// Q6_K, row-group-major layout.  Table row (8 words = 16 halves): half(d * sc_i), i = 0..15.
+__device__ __forceinline__ void q6k_table_words(const uint4 sc, const float d, uint32_t* dst) {     // sc: the row's 16 int8 scales
+    const uint32_t wd[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int a = static_cast<int8_t>((wd[i >> 1] >> (16 * (i & 1))) & 0xFFu), c = static_cast<int8_t>((wd[i >> 1] >> (16 * (i & 1) + 8)) & 0xFFu);
+        dst[i] = pack_h2(d * static_cast<float>(a), d * static_cast<float>(c));
+    }
+}
+// one chunk: slots 0-3 = 6-bit values (nib0 | hb0 << 4) with scale lo16(e), slots 4-7 = (nib1 | hb1 << 4) with hi16(e)
+__device__ __forceinline__ uint4 q6k_chunk(uint32_t nib0, uint32_t hb0, uint32_t nib1, uint32_t hb1, uint32_t e) {
+    const __half2 k1056 = as_h2(0x64206420u);     // 1024 + 32
+    const __half2 s0 = as_h2(__byte_perm(e, e, 0x1010)), s1 = as_h2(__byte_perm(e, e, 0x3232));
+    __half2 p0, p1, p2, p3;
+    bytes_to_half(nib0 + (hb0 << 4), k1056, p0, p1);
+    bytes_to_half(nib1 + (hb1 << 4), k1056, p2, p3);
+    return make_uint4(as_u32(__hmul2(p0, s0)), as_u32(__hmul2(p1, s0)), as_u32(__hmul2(p2, s1)), as_u32(__hmul2(p3, s1)));
+}
+// Q8_0 (stream layout): signed bytes wa (slots 0-3) and wb (4-7) times the block's fp16 scale -- exact up to the final rounding
+__device__ __forceinline__ uint4 q80_chunk(uint32_t wa, uint32_t wb, __half2 dd) {
+    const __half2 k1152 = as_h2(0x64806480u);     // 1024 + 128
+    __half2 p0, p1, p2, p3;
+    bytes_to_half(wa ^ 0x80808080u, k1152, p0, p1);
+    bytes_to_half(wb ^ 0x80808080u, k1152, p2, p3);
+    return make_uint4(as_u32(__hmul2(p0, dd)), as_u32(__hmul2(p1, dd)), as_u32(__hmul2(p2, dd)), as_u32(__hmul2(p3, dd)));
+}
+// any format: exact fp32 decode (the decoder the dequant kernel uses), one rounding to fp16
+__device__ __forceinline__ uint4 generic_chunk(const PackedW& w, int64_t row, int k0, int c, int block_elems) {
     uint32_t p[4];
-    const bool valid = row < w.N;
-    const int64_t blk = row * w.nb + k0 / block_elems;
-    const int j0 = k0 % block_elems;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float a = 0.0f, b = 0.0f;
-        if (valid) {
-            if (block_elems == 1) { a = decode_elem(w, row * w.nb + k0 + 2 * i, 0); b = decode_elem(w, row * w.nb + k0 + 2 * i + 1, 0); }
-            else { a = decode_elem(w, blk, j0 + 2 * i); b = decode_elem(w, blk, j0 + 2 * i + 1); }
+        float v[2] = {0.0f, 0.0f};
+        if (row < w.N) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int k = k0 + perm_k(c, 2 * i + u);
+                v[u] = block_elems == 1 ? decode_elem(w, row * w.nb + k, 0) : decode_elem(w, row * w.nb + k / block_elems, k % block_elems);
+            }
         }
-        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        p[i] = *reinterpret_cast<const uint32_t*>(&h);
+        p[i] = pack_h2(v[0], v[1]);
     }
     return make_uint4(p[0], p[1], p[2], p[3]);
 }
 
-// dynamic shared memory (1024-byte aligned): 2 stages x [A: 128 x 128 B][A2 (dual): 16 KB][B: tn x 128 B]
+// ---- the GEMM --------------------------------------------------------------------------------------
+// RT = weight tiles of 128 rows per CTA.  Non-dual: tile i covers rows n0 + 128 i of w.  Dual (RT == 2):
+// tile 0 = rows n0.. of w (gate), tile 1 = the same rows of w2 (up); the epilogue combines them.
+// Dynamic shared memory (1024-byte aligned): stages x { RT weight tiles of 16 KB, token tile tn x 128 B },
+// then the scale table RT x 128 rows x 32 B (Q4_K / Q6_K; each warp owns the rows it fills).
+template <int FMT, int RT>
 __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t free_bar[2], done_bar;
+    __shared__ __align__(8) uint64_t a_full[kMaxStagesG], b_full[kMaxStagesG], free_bar[kMaxStagesG], done_bar;
     __shared__ uint32_t tmem_base_s;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int a_bytes = kTileN * 128, b_bytes = a.tn * 128;
-    const int stage_bytes = a_bytes * (a.dual ? 2 : 1) + b_bytes;
-    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kTileN;
-    const int t0 = blockIdx.y * a.tn;
-    const FormatInfo fi = format_info(a.w.type);
+    const int S = a.stages;
+    const int b_bytes = a.tn * 128;
+    const int stage_bytes = RT * 16384 + b_bytes;
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + static_cast<size_t>(S) * stage_bytes);      // [RT][128][8]
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * (a.dual ? 128 : 128 * RT);
+    const int n_steps = a.K / kBK;
 
     if (tid == 0) {
-        mbar_init(&free_bar[0], 1); mbar_init(&free_bar[1], 1); mbar_init(&done_bar, 1);
+        for (int s = 0; s < S; ++s) { mbar_init(&a_full[s], 8); mbar_init(&b_full[s], 1); mbar_init(&free_bar[s], 1); }
+        mbar_init(&done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {       // one warp allocates the accumulator columns in tensor memory
+    if (warp == 8) {       // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(&tmem_base_s)), "r"(static_cast<uint32_t>(a.tmem_cols)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -166,124 +278,294 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = tmem_base_s;
-    const uint32_t idesc = umma_idesc(kTileN, a.tn);
-
-    const int n_steps = a.K / kBK;
     bool ok = true;
-    for (int ks = 0; ks < n_steps; ++ks) {
-        const int s = ks & 1;
-        // the MMAs that last read this stage (step ks-2) must have finished
-        if (ks >= 2 && ok) ok = mbar_wait(&free_bar[s], ((ks >> 1) - 1) & 1, a.err);
-        uint8_t* As = smem + static_cast<size_t>(s) * stage_bytes;
-        uint8_t* A2s = As + a_bytes;
-        uint8_t* Bs = As + a_bytes * (a.dual ? 2 : 1);
-        const int k0 = ks * kBK;
-        // weights: 128 rows x 8 chunks of 8 values
-        for (int i = tid; i < kTileN * 8; i += kThreadsG) {
-            const int r = i >> 3, c = i & 7;
-            *reinterpret_cast<uint4*>(As + swz_off(r, c)) = dequant8_bf16(a.w, n0 + r, k0 + 8 * c, fi.block_elems);
-            if (a.dual) *reinterpret_cast<uint4*>(A2s + swz_off(r, c)) = dequant8_bf16(a.w2, n0 + r, k0 + 8 * c, fi.block_elems);
-        }
-        // activations: tn token rows x 8 chunks
-        for (int i = tid; i < a.tn * 8; i += kThreadsG) {
-            const int r = i >> 3, c = i & 7;
-            *reinterpret_cast<uint4*>(Bs + swz_off(r, c)) =
-                __ldg(reinterpret_cast<const uint4*>(a.xb + static_cast<size_t>(t0 + r) * a.K + k0 + 8 * c));
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0 && ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = umma_desc(s_u32(As)), da2 = umma_desc(s_u32(A2s)), db = umma_desc(s_u32(Bs));
-#pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk) {
-                const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
-                umma_bf16(tmem_d, da + 2 * kk, db + 2 * kk, idesc, acc);                   // +32 bytes along K per step
-                if (a.dual) umma_bf16(tmem_d + a.tn, da2 + 2 * kk, db + 2 * kk, idesc, acc);
+
+    if (warp == 9) {
+        // ---------------- activation producer ----------------
+        if (lane == 0) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * n_steps * b_bytes;
+            for (int ks = 0; ks < n_steps; ++ks) {
+                const int s = ks % S, u = ks / S;
+                if (u >= 1 && ok) ok = mbar_wait(&free_bar[s], (u - 1) & 1, a.err);
+                mbar_expect_tx(&b_full[s], static_cast<uint32_t>(b_bytes));
+                bulk_g2s(smem + static_cast<size_t>(s) * stage_bytes + RT * 16384, src + static_cast<size_t>(ks) * b_bytes, static_cast<uint32_t>(b_bytes), &b_full[s]);
             }
-            umma_commit(ks == n_steps - 1 ? &done_bar : &free_bar[s]);
         }
-    }
-    // ---- epilogue: warp w reads lane quarter (w & 3), column half (w >> 2) ----
-    if (ok) ok = mbar_wait(&done_bar, 0, a.err);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-        const int q = warp & 3, half = warp >> 2;
-        const int64_t n = n0 + q * 32 + lane;
-        const int c_begin = half * (a.tn / 2), c_end = c_begin + a.tn / 2;
-        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-            float v[32], v2[32];
-            const uint32_t taddr = tmem_d + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c0);
-            tmem_ld32(taddr, v);
-            if (a.dual) tmem_ld32(taddr + a.tn, v2);
+    } else if (warp == 8) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(128, a.tn);
+            for (int ks = 0; ks < n_steps; ++ks) {
+                const int s = ks % S, u = ks / S;
+                if (ok) ok = mbar_wait(&a_full[s], u & 1, a.err);
+                if (ok) ok = mbar_wait(&b_full[s], u & 1, a.err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = s_u32(smem + static_cast<size_t>(s) * stage_bytes);
+                const uint64_t db = umma_desc(st + RT * 16384);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int tok = t0 + c0 + i;
-                if (c0 + i < c_end && tok < a.M && n < a.w.N) {
-                    const size_t o = static_cast<size_t>(tok) * a.ldc + n;
-                    float r = v[i];
-                    if (a.dual) r = (r / (1.0f + expf(-r))) * v2[i];
-                    else if (a.epi == EPI_ADD_BIAS) r += __ldg(a.bias + n);
-                    else if (a.epi == EPI_RESIDUAL) r += a.resid[o];
-                    a.y[o] = r;
+                for (int i = 0; i < RT; ++i) {
+                    const uint64_t da = umma_desc(st + i * 16384);
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; ++kk)
+                        umma_f16(tmem_d + i * a.tn, da + 2 * kk, db + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);     // +32 bytes along K per instruction
+                }
+                umma_commit(&free_bar[s]);
+            }
+            if (ok) umma_commit(&done_bar);
+        }
+    } else {
+        // ---------------- dequant warps ----------------
+        // Warp w fills rows 16 w .. 16 w + 15 of every weight tile.  Fragments are fetched two steps
+        // ahead into a rotating register queue (DRAM latency is longer than one step); K-quant
+        // sub-block scales are expanded once per 256-block into a warp-private table.
+        const int g = lane >> 2, t = lane & 3;
+        const FormatInfo fi = format_info(a.w.type);
+        auto tile_w = [&](int i) -> const PackedW& { return (a.dual && i == 1) ? a.w2 : a.w; };
+        auto tile_row0 = [&](int i) -> int64_t { return a.dual ? n0 : n0 + 128 * i; };
+        constexpr int NQ = FMT == F_Q6K ? 3 : (FMT == F_Q80 ? 2 : 1);
+        struct Frag { uint4 v[NQ]; uint32_t d; };
+        struct Hdr { uint4 v; float d; };
+        auto load_frag = [&](int ks, Frag (&f)[RT]) {
+#pragma unroll
+            for (int i = 0; i < RT; ++i) {
+                const PackedW& w = tile_w(i);
+#pragma unroll
+                for (int j = 0; j < NQ; ++j) f[i].v[j] = make_uint4(0u, 0u, 0u, 0u);
+                f[i].d = 0u;
+                if (FMT == F_Q4K || FMT == F_Q6K) {
+                    const int64_t grp = (tile_row0(i) >> 4) + warp;
+                    if (grp < ((w.N + 15) >> 4)) {
+                        const int64_t gb = grp * w.nb + (ks >> 2);
+                        if (FMT == F_Q4K) {
+                            f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + ((gb * 4 + (ks & 3)) * 32 + lane) * 16));
+                        } else {
+                            const int hf = (ks & 3) >> 1;
+                            f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[0] + ((gb * 4 + 2 * hf) * 32 + lane) * 16));
+                            f[i].v[1] = __ldg(reinterpret_cast<const uint4*>(w.s[0] + ((gb * 4 + 2 * hf + 1) * 32 + lane) * 16));
+                            f[i].v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + ((gb * 2 + hf) * 32 + lane) * 16));
+                        }
+                    }
+                } else if (FMT == F_Q80) {
+                    // two lanes per row, each one 32-element block = chunks 4 hh .. 4 hh + 3
+                    const int64_t row = tile_row0(i) + (tid >> 1);
+                    if (row < w.N) {
+                        const int64_t blk = row * w.nb + 2 * ks + (tid & 1);
+                        f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + blk * 32));
+                        f[i].v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + blk * 32 + 16));
+                        f[i].d = __ldg(reinterpret_cast<const unsigned short*>(w.s[0] + blk * 2));
+                    }
+                }
+            }
+        };
+        // K-quant header of (tile lane / 16, row 16 w + lane % 16), block b
+        auto load_hdr = [&](int b) -> Hdr {
+            Hdr h; h.v = make_uint4(0u, 0u, 0u, 0u); h.d = 0.0f;
+            const int i = lane >> 4;
+            if ((FMT == F_Q4K || FMT == F_Q6K) && i < RT && b < a.w.nb) {
+                const PackedW& w = tile_w(i);
+                const int64_t row = tile_row0(i) + warp * 16 + (lane & 15);
+                if (row < ((w.N + 15) >> 4) * 16) {
+                    const int64_t slot = ((row >> 4) * w.nb + b) * 16 + (row & 15);
+                    if (FMT == F_Q4K) h.v = __ldg(reinterpret_cast<const uint4*>(w.s[0] + slot * 16));
+                    else { h.v = __ldg(reinterpret_cast<const uint4*>(w.s[2] + slot * 16)); h.d = ld_f16(w.s[3] + slot * 2); }
+                }
+            }
+            return h;
+        };
+        Frag f0[RT], f1[RT], f2[RT];
+        Hdr h0 = load_hdr(0), h1 = load_hdr(1);
+        load_frag(0, f0);
+        if (n_steps > 1) load_frag(1, f1);
+        for (int ks = 0; ks < n_steps; ++ks) {
+            const int s = ks % S, u = ks / S;
+            const int k0 = ks * kBK;
+            uint8_t* As = smem + static_cast<size_t>(s) * stage_bytes;
+            if (FMT != F_GEN && ks + 2 < n_steps) load_frag(ks + 2, f2);
+            if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == 0) {
+                // the previous block's readers are past their __syncwarp; expand this block's scales
+                if ((lane >> 4) < RT) {
+                    uint32_t* dst = table + ((lane >> 4) * 128 + warp * 16 + (lane & 15)) * 8;
+                    if (FMT == F_Q4K) q4k_table_words(h0.v, dst); else q6k_table_words(h0.v, h0.d, dst);
+                }
+                h0 = h1;
+                h1 = load_hdr((ks >> 2) + 2);
+                __syncwarp();
+            }
+            if (u >= 1 && ok) ok = mbar_wait(&free_bar[s], (u - 1) & 1, a.err);
+            if (FMT == F_Q4K || FMT == F_Q6K) {
+#pragma unroll
+                for (int i = 0; i < RT; ++i) {
+                    uint8_t* At = As + i * 16384;
+                    const uint32_t* tb = table + i * 128 * 8;
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {                 // rows g and g + 8 of the group
+                        const int r = warp * 16 + g + 8 * hi;
+                        const uint2 e = *reinterpret_cast<const uint2*>(tb + r * 8 + 2 * (ks & 3));
+                        if (FMT == F_Q4K) {
+                            const uint32_t wa = hi ? f0[i].v[0].y : f0[i].v[0].x, wb = hi ? f0[i].v[0].w : f0[i].v[0].z;
+                            *reinterpret_cast<uint4*>(At + swz_off(r, t)) = q4k_chunk(wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, e.x);
+                            *reinterpret_cast<uint4*>(At + swz_off(r, 4 + t)) = q4k_chunk((wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu, e.y);
+                        } else {
+                            const uint4 c0 = f0[i].v[0], c1 = f0[i].v[1], qh = f0[i].v[NQ - 1];
+                            const uint32_t a0 = hi ? c0.z : c0.x, b0 = hi ? c0.w : c0.y;      // c = 0: ql_a, ql_b
+                            const uint32_t a1 = hi ? c1.z : c1.x, b1 = hi ? c1.w : c1.y;      // c = 1
+                            const uint32_t q0 = hi ? qh.y : qh.x, q1 = hi ? qh.w : qh.z;      // qh of c = 0, 1
+                            const int sh = 4 * (ks & 1);
+                            *reinterpret_cast<uint4*>(At + swz_off(r, t)) =
+                                q6k_chunk((a0 >> sh) & 0x0F0F0F0Fu, (q0 >> sh) & 0x03030303u, (a1 >> sh) & 0x0F0F0F0Fu, (q1 >> sh) & 0x03030303u, e.x);
+                            *reinterpret_cast<uint4*>(At + swz_off(r, 4 + t)) =
+                                q6k_chunk((b0 >> sh) & 0x0F0F0F0Fu, (q0 >> (sh + 2)) & 0x03030303u, (b1 >> sh) & 0x0F0F0F0Fu, (q1 >> (sh + 2)) & 0x03030303u, e.y);
+                        }
+                    }
+                }
+            } else if (FMT == F_Q80) {
+                const int r = tid >> 1, hh = tid & 1;
+#pragma unroll
+                for (int i = 0; i < RT; ++i) {
+                    uint8_t* At = As + i * 16384;
+                    const uint4 lo = f0[i].v[0], hi4 = f0[i].v[NQ - 1];
+                    const __half2 dd = __half2half2(__ushort_as_half(static_cast<unsigned short>(f0[i].d)));
+                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 0)) = q80_chunk(lo.x, hi4.x, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 1)) = q80_chunk(lo.y, hi4.y, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 2)) = q80_chunk(lo.z, hi4.z, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 3)) = q80_chunk(lo.w, hi4.w, dd);
+                }
+            } else {
+                for (int it = tid; it < RT * 128 * 8; it += kDequantThreads) {
+                    const int i = it >> 10, r = (it >> 3) & 127, c = it & 7;
+                    *reinterpret_cast<uint4*>(As + i * 16384 + swz_off(r, c)) = generic_chunk(tile_w(i), tile_row0(i) + r, k0, c, fi.block_elems);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&a_full[s]);
+#pragma unroll
+            for (int i = 0; i < RT; ++i) { f0[i] = f1[i]; f1[i] = f2[i]; }
+        }
+        // ---------------- epilogue (the same 8 warps) ----------------
+        if (ok) ok = mbar_wait(&done_bar, 0, a.err);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int q = warp & 3, half = warp >> 2;
+            const int t0 = blockIdx.y * a.tn;
+            // non-dual RT == 2: warp half = weight tile, all columns; otherwise the halves split the columns
+            const bool by_tile = (RT == 2 && !a.dual);
+            const int tile = by_tile ? half : 0;
+            const int64_t n = n0 + 128 * tile + q * 32 + lane;
+            const int c_begin = by_tile ? 0 : half * (a.tn / 2), c_end = by_tile ? a.tn : c_begin + a.tn / 2;
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+                float v[32], v2[32];
+                const uint32_t taddr = tmem_d + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(tile * a.tn + c0);
+                tmem_ld32(taddr, v);
+                if (a.dual) tmem_ld32(taddr + a.tn, v2);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int tok = t0 + c0 + i;
+                    if (tok < a.M && n < a.w.N) {
+                        const size_t o = static_cast<size_t>(tok) * a.ldc + n;
+                        float r = v[i];
+                        if (a.dual) r = (r / (1.0f + expf(-r))) * v2[i];
+                        else if (a.epi == EPI_ADD_BIAS) r += __ldg(a.bias + n);
+                        else if (a.epi == EPI_RESIDUAL) r += a.resid[o];
+                        a.y[o] = r;
+                    }
                 }
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(static_cast<uint32_t>(a.tmem_cols)) : "memory");
     }
 }
 
+template <int FMT, int RT>
+int launch_one(Context* c, const GemmArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return cuda_status(c, e, "gemm_tc attr");
+        allowed = smem;
+    }
+    gemm_tc_kernel<FMT, RT><<<grid, kThreadsG, smem, s>>>(a);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "gemm_tc launch");
+}
+
+// tokens per CTA tile: a multiple of 64 (the epilogue reads column halves 32 at a time), at most 256.
+// The largest of 256 / 128 / 64 that still yields about one CTA per SM (every token tile repeats the
+// dequantisation of its weight rows, so bigger is cheaper when the grid is full anyway).
+int tile_tokens(const GemvArgs& g) {
+    const int cap = std::min(256, (g.M + 63) / 64 * 64);
+    const int64_t row_tiles = (g.w.N + 127) / 128;
+    for (int tn = 256; tn > 64; tn >>= 1)
+        if (tn <= cap && row_tiles * ((g.M + tn - 1) / tn) >= 118) return tn;
+    return std::min(cap, 64);
+}
+
 }  // namespace
 
-// tokens per CTA tile: a multiple of 64 (the epilogue reads two column halves 32 at a time), at most
-// 256 (one accumulator) or 128 (gate and up accumulators side by side)
-static int tile_tokens(const GemvArgs& g) {
-    const int cap = g.epi == EPI_SWIGLU ? 128 : 256;
-    return std::min(cap, (g.M + 63) / 64 * 64);
-}
 size_t gemm_tc_xb_elems(const GemvArgs& g) {
     const int tn = tile_tokens(g);
     return static_cast<size_t>((g.M + tn - 1) / tn) * tn * g.w.K;
 }
 
 // Prefill GEMM.  Returns GGB_NOT_FOUND when the shape is not covered (caller falls back).
-// d_xb_v: scratch for the bf16 activations, at least gemm_tc_xb_elems(g) elements.
+// d_xb_v: scratch for the fp16 activation tile images, at least gemm_tc_xb_elems(g) elements.
 int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems, cudaStream_t s) {
-    __nv_bfloat16* d_xb = static_cast<__nv_bfloat16*>(d_xb_v);
+    __half* d_xb = static_cast<__half*>(d_xb_v);
     const int K = g.w.K;
     const FormatInfo fi = format_info(g.w.type);
     if (!fi.block_elems || K % kBK || g.M < 1 || !g.x || g.n_cat || g.attn_partial) return GGB_NOT_FOUND;
     const bool dual = g.epi == EPI_SWIGLU;
+    if (dual && g.w2.layout != g.w.layout) return GGB_NOT_FOUND;
     const int tn = tile_tokens(g);
     const int m_tiles = (g.M + tn - 1) / tn;
-    if (static_cast<size_t>(m_tiles) * tn * K > xb_elems) return GGB_NOT_FOUND;
-    int cols = 32;
-    while (cols < tn * (dual ? 2 : 1)) cols <<= 1;
+    if (gemm_tc_xb_elems(g) > xb_elems) return GGB_NOT_FOUND;
 
-    x_to_bf16_kernel<<<m_tiles * tn, 256, 0, s>>>(g.x, g.lda, g.M, K, g.gamma, g.eps, d_xb);
+    int fmt = F_GEN;
+    if (!c->tc_generic) {
+        if (g.w.type == T_Q4_K && g.w.layout == 1) fmt = F_Q4K;
+        else if (g.w.type == T_Q6_K && g.w.layout == 1) fmt = F_Q6K;
+        else if (g.w.type == T_Q8_0 && g.w.layout == 0) fmt = F_Q80;
+    }
+    // two weight tiles per CTA halve the activation traffic per flop; one tile doubles the CTA count
+    int rt = 2;
+    if (!dual) {
+        const int64_t ctas2 = (g.w.N + 255) / 256 * m_tiles;
+        if (g.w.N <= 128 || ctas2 < (c->sm_count * 3) / 4) rt = 1;
+        if (c->tc_rt == 1 || c->tc_rt == 2) rt = g.w.N <= 128 ? 1 : c->tc_rt;
+    }
+    int cols = 32;
+    while (cols < tn * rt) cols <<= 1;
+    const size_t stage_bytes = static_cast<size_t>(rt) * 16384 + static_cast<size_t>(tn) * 128;
+    const size_t table_bytes = static_cast<size_t>(rt) * 128 * 32;
+    const size_t budget = 227 * 1024 - 1024 - table_bytes - 2048;      // alignment slack, table, static barriers
+    const int stages = static_cast<int>(std::min<size_t>(kMaxStagesG, budget / stage_bytes));
+    if (stages < 2) return GGB_NOT_FOUND;
+    const size_t smem = stages * stage_bytes + table_bytes + 1024;
+
+    x_prep_kernel<<<m_tiles * tn, 256, 0, s>>>(g.x, g.lda, g.M, K, tn, g.gamma, g.eps, d_xb);
     c->launches++;
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_status(c, e, "x_to_bf16");
+    if (e != cudaSuccess) return cuda_status(c, e, "x_prep");
 
     GemmArgs a{};
     a.w = g.w; a.w2 = g.w2; a.xb = d_xb; a.y = g.y; a.bias = g.bias; a.resid = g.resid;
-    a.M = g.M; a.K = K; a.ldc = g.ldc; a.epi = g.epi; a.dual = dual ? 1 : 0; a.tn = tn; a.tmem_cols = cols; a.err = c->d_err;
-    const size_t smem = 2 * (static_cast<size_t>(kTileN) * 128 * (dual ? 2 : 1) + static_cast<size_t>(tn) * 128) + 1024;
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return cuda_status(c, e, "gemm_tc attr");
-        allowed = smem;
+    a.M = g.M; a.K = K; a.ldc = g.ldc; a.epi = g.epi; a.dual = dual ? 1 : 0; a.tn = tn; a.tmem_cols = cols; a.stages = stages; a.err = c->d_err;
+    dim3 grid(static_cast<unsigned>((g.w.N + (dual ? 128 : 128 * rt) - 1) / (dual ? 128 : 128 * rt)), static_cast<unsigned>(m_tiles));
+    switch (fmt * 2 + (rt - 1)) {
+    case F_GEN * 2 + 0: return launch_one<F_GEN, 1>(c, a, grid, smem, s);
+    case F_GEN * 2 + 1: return launch_one<F_GEN, 2>(c, a, grid, smem, s);
+    case F_Q4K * 2 + 0: return launch_one<F_Q4K, 1>(c, a, grid, smem, s);
+    case F_Q4K * 2 + 1: return launch_one<F_Q4K, 2>(c, a, grid, smem, s);
+    case F_Q6K * 2 + 0: return launch_one<F_Q6K, 1>(c, a, grid, smem, s);
+    case F_Q6K * 2 + 1: return launch_one<F_Q6K, 2>(c, a, grid, smem, s);
+    case F_Q80 * 2 + 0: return launch_one<F_Q80, 1>(c, a, grid, smem, s);
+    default: return launch_one<F_Q80, 2>(c, a, grid, smem, s);
     }
-    dim3 grid(static_cast<unsigned>((g.w.N + kTileN - 1) / kTileN), static_cast<unsigned>(m_tiles));
-    gemm_tc_kernel<<<grid, kThreadsG, smem, s>>>(a);
-    c->launches++;
-    return cuda_status(c, cudaGetLastError(), "gemm_tc launch");
 }
 
 }  // namespace ggb

@@ -564,7 +564,7 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
             cudaStreamSynchronize(s);
             if (c->d_xb) cudaFree(c->d_xb);
             c->d_xb = nullptr; c->d_xb_elems = 0;
-            if (cuda_status(c, cudaMalloc(&c->d_xb, need * 2), "cudaMalloc(bf16 activations)") != GGB_OK) return c->last_status;
+            if (cuda_status(c, cudaMalloc(&c->d_xb, need * 2), "cudaMalloc(fp16 activations)") != GGB_OK) return c->last_status;
             c->d_xb_elems = need;
         }
         const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, s);

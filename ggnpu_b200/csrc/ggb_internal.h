@@ -69,9 +69,11 @@ struct Context {
     bool use_tma = true;      // M == 1 GEMV through the bulk-copy ring kernel
     unsigned long long* d_trace = nullptr;   // tuning aid (GGB_TRACE=1): %globaltimer stamps of CTA 0, printed by ggb_sync
     bool use_mma = true;      // Q4_K in the row-group-major layout + int8 tensor-core GEMV (M <= 2)
-    bool use_tc = true;       // M >= tc_min_m through the tcgen05 GEMM (bf16 operands, fp32 accumulation in TMEM)
+    bool use_tc = true;       // M >= tc_min_m through the tcgen05 GEMM (fp16 operands, fp32 accumulation in TMEM)
     int tc_min_m = 32;
-    void* d_xb = nullptr;     // bf16 activations of the tcgen05 GEMM (grown on demand, never during graph capture)
+    bool tc_generic = false;  // tuning aid: every format through the generic (exact fp32 decode) tile filler
+    int tc_rt = 0;            // tuning aid: force 1 or 2 weight tiles per CTA (0: heuristic)
+    void* d_xb = nullptr;     // fp16 activation tile images of the tcgen05 GEMM (grown on demand, never during graph capture)
     size_t d_xb_elems = 0;
 };
 

@@ -1,14 +1,15 @@
 """Prefill GEMM on the tcgen05 tensor cores (M >= 32 through Backend::mul_mat_q and the device-pointer
 entry points) vs the CPU oracle.
 
-Two bars, both written here:
-  * "bf16 model": the kernel rounds the exactly dequantised weights and the activations to bf16 once
-    and accumulates in fp32.  Against the oracle's dequantised rows with the SAME two roundings
-    applied (float64 accumulation) only the summation order differs: rel-L2 <= 1e-5,
-    max-abs <= 2e-5 * max|ref|.  This pins tile layout, swizzle, descriptors and the epilogue.
+Operands are fp16 (weights dequantised to fp16, activations rounded to fp16 once), sums fp32.  Bars:
+  * "fp16 model", tight: formats filled by the exact decoder (and Q8_0, whose fast filler is exact)
+    equal the oracle's dequantised rows with the SAME two roundings applied (float64 accumulation)
+    up to summation order: rel-L2 <= 1e-5, max-abs <= 2e-5 * max|ref|.  This pins tile layout,
+    swizzle, K permutation, descriptors and the epilogue.
+  * "fp16 model", loose: the fast Q4_K / Q6_K fillers round the sub-block scale (and min term) to
+    fp16 before the multiply: rel-L2 <= 1.5e-3 against the same model.
   * "reference": against the exact fp32 matmul of the reference's CPU path (dequant_tensor_row +
-    sequential dot, src/cli/main.cpp:1379-1388) the operand rounding leaves rel-L2 <= 5e-3 (two
-    roundings of relative size 2^-9, uncorrelated over K)."""
+    sequential dot, src/cli/main.cpp:1379-1388): rel-L2 <= 2e-3."""
 import numpy as np
 import pytest
 import torch
@@ -22,8 +23,11 @@ pytestmark = pytest.mark.gpu
 TYPES = [S.Q4_K, S.Q6_K, S.Q8_0, S.Q4_0, S.IQ4_XS, S.Q5_K, S.Q2_K, S.Q3_K, S.Q4_1, S.IQ4_NL, S.F16, S.BF16]
 
 
-def bf16(a):
-    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float64).numpy()
+def f16(a):
+    return np.ascontiguousarray(a, dtype=np.float32).astype(np.float16).astype(np.float64)
+
+
+LOOSE_TYPES = (S.Q4_K, S.Q6_K)      # fast fillers that round the scales to fp16
 
 
 def make(t, N, K, seed):
@@ -35,17 +39,18 @@ def dequant(oracle, t, raw, N, K):
     return np.stack([oracle.dequant_row(t, raw, r, K) for r in range(N)])
 
 
-def check_model(got, A, Wd, extra=None):
-    want = bf16(A) @ bf16(Wd).T
-    if extra is not None:
-        want = want + extra
+def check_model(got, A, Wd, t):
+    want = f16(A) @ f16(Wd).T
     assert np.isfinite(got).all()
-    assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
-    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+    if t in LOOSE_TYPES:
+        assert rel_l2(got, want) <= 1.5e-3, rel_l2(got, want)
+    else:
+        assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
+        assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
 
 
 @pytest.mark.parametrize("t", TYPES)
-def test_all_formats_bf16_model_and_reference(backend, oracle, t):
+def test_all_formats_fp16_model_and_reference(backend, oracle, t):
     N, K, M = 200, 512, 100            # N not a multiple of the 128-row tile, M not a multiple of 64
     raw = make(t, N, K, 3)
     A = np.random.default_rng(3).standard_normal((M, K)).astype(np.float32)
@@ -53,8 +58,8 @@ def test_all_formats_bf16_model_and_reference(backend, oracle, t):
     before = backend.launch_count()
     assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
     assert backend.launch_count() > before
-    check_model(C, A, dequant(oracle, t, raw, N, K))
-    assert rel_l2(C, oracle.matmul_exact(A, raw, t, N, K)) <= 5e-3
+    check_model(C, A, dequant(oracle, t, raw, N, K), t)
+    assert rel_l2(C, oracle.matmul_exact(A, raw, t, N, K)) <= 2e-3
 
 
 @pytest.mark.parametrize("M", [32, 64, 257, 600])
@@ -66,7 +71,7 @@ def test_token_tiles(backend, oracle, t, M):
     A = np.random.default_rng(M).standard_normal((M, K)).astype(np.float32)
     C = np.full((M, N), np.nan, np.float32)
     assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
-    check_model(C, A, dequant(oracle, t, raw, N, K))
+    check_model(C, A, dequant(oracle, t, raw, N, K), t)
 
 
 def test_k_of_one_and_two_steps(backend, oracle):
@@ -77,13 +82,14 @@ def test_k_of_one_and_two_steps(backend, oracle):
         A = np.random.default_rng(K).standard_normal((M, K)).astype(np.float32)
         C = np.full((M, N), np.nan, np.float32)
         assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
-        check_model(C, A, dequant(oracle, t, raw, N, K))
+        check_model(C, A, dequant(oracle, t, raw, N, K), t)
 
 
 def test_benchmark_shapes_sampled_rows(backend, oracle):
-    """Llama-3.2-1B projection shapes at a 256-token chunk; a sample of weight rows is checked."""
-    M = 256
-    for (N, K), t in (((8192, 2048), S.Q4_K), ((2048, 8192), S.Q6_K), ((2048, 2048), S.Q4_K)):
+    """Llama-3.2-1B projection shapes at a 256-token chunk (one weight tile per CTA) and at 1024 tokens
+    (two weight tiles per CTA), Qwen2.5-1.5B's Q8_0 FFN shape; a sample of weight rows is checked."""
+    for (N, K), t, M in (((8192, 2048), S.Q4_K, 256), ((2048, 8192), S.Q6_K, 256), ((2048, 2048), S.Q4_K, 256),
+                         ((8192, 2048), S.Q4_K, 1024), ((8192, 2048), S.Q6_K, 1024), ((8960, 1536), S.Q8_0, 1000)):
         raw = make(t, N, K, 9)
         A = np.random.default_rng(9).standard_normal((M, K)).astype(np.float32)
         C = np.full((M, N), np.nan, np.float32)
@@ -92,7 +98,7 @@ def test_benchmark_shapes_sampled_rows(backend, oracle):
         rows = np.unique(np.concatenate([np.arange(4), np.arange(N - 4, N), np.random.default_rng(1).integers(0, N, 40)]))
         rb = S.row_bytes(t, K)
         sub = np.ascontiguousarray(raw.reshape(N, rb)[rows])
-        check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K))
+        check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
 
 
 def test_fused_epilogues(backend, oracle):
@@ -108,11 +114,11 @@ def test_fused_epilogues(backend, oracle):
     dx, dg, db = torch.from_numpy(x).to(dev), torch.from_numpy(gamma).to(dev), torch.from_numpy(bias).to(dev)
     dy = torch.empty((M, N), device=dev, dtype=torch.float32)
     hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
-    # the kernel normalises in fp32 (x * inv * gamma) and then rounds to bf16
+    # the kernel normalises in fp32 (x * inv * gamma) and then rounds to fp16
     inv = 1.0 / np.sqrt((x.astype(np.float32) ** 2).sum(1, dtype=np.float32) / np.float32(K) + np.float32(1e-5))
     xn = (x * inv[:, None].astype(np.float32) * gamma).astype(np.float32)
     Wg, Wu = dequant(oracle, t, wg, N, K), dequant(oracle, t, wu, N, K)
-    g_ref, u_ref = bf16(xn) @ bf16(Wg).T, bf16(xn) @ bf16(Wu).T
+    g_ref, u_ref = f16(xn) @ f16(Wg).T, f16(xn) @ f16(Wu).T
 
     def run(fn):
         torch.cuda.synchronize()
@@ -121,16 +127,16 @@ def test_fused_epilogues(backend, oracle):
         return dy.cpu().numpy()
 
     got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 1, db.data_ptr(), dg.data_ptr(), 1e-5))
-    assert rel_l2(got, g_ref + bias) <= 1e-4
+    assert rel_l2(got, g_ref + bias) <= 1.5e-3
     dy.copy_(torch.from_numpy(resid))
     got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 2, dy.data_ptr(), dg.data_ptr(), 1e-5))
-    assert rel_l2(got, g_ref + resid) <= 1e-4
+    assert rel_l2(got, g_ref + resid) <= 1.5e-3
     got = run(lambda: backend.gemv_swiglu_device(hg, hu, dx.data_ptr(), M, K, dy.data_ptr(), N, dg.data_ptr(), 1e-5))
     want = g_ref / (1.0 + np.exp(-g_ref)) * u_ref
-    assert rel_l2(got, want) <= 1e-4
-    # against the reference's exact arithmetic: bf16 operand tolerance
+    assert rel_l2(got, want) <= 2e-3
+    # against the reference's exact arithmetic
     xo = np.stack([oracle.rms_norm(r, 1e-5, gamma) for r in x])
     ge, ue = oracle.matmul_exact(xo, wg, t, N, K), oracle.matmul_exact(xo, wu, t, N, K)
-    assert rel_l2(got, np.stack([oracle.silu(r) for r in ge]) * ue) <= 8e-3
+    assert rel_l2(got, np.stack([oracle.silu(r) for r in ge]) * ue) <= 3e-3
     backend.free_weight(hg)
     backend.free_weight(hu)
