@@ -7,13 +7,13 @@
 // (TMEM, fp32).  Operands are fp16: the quantised formats carry fp16 block scales, so Q8_0 / Q4_0
 // weights are reproduced exactly and K-quant sub-block scales lose 2^-12; activations are rounded to
 // fp16 once (clamped to the finite range).  Warp roles, K step 64, ring of `stages` stages:
-//   * warps 0-7 (dequant): read the quantised fragments with 128-bit loads, expand them with byte
+//   * warps 0-15 (dequant): read the quantised fragments with 128-bit loads, expand them with byte
 //     permutes + packed half arithmetic (integer -> fp16 through the 0x6400 | q trick, exact), scale,
 //     and store the 128 x 64 tiles into shared memory in the K-major 128-byte-swizzled layout
 //     tcgen05.mma reads; fence.proxy.async, then one arrive per warp on the stage's `a_full` barrier;
-//   * warp 9 lane 0 (activation producer): one cp.async.bulk per stage brings the token tile, which
+//   * warp 17 lane 0 (activation producer): one cp.async.bulk per stage brings the token tile, which
 //     x_prep_kernel wrote once per call already in the swizzled tile image (RMS norm fused there);
-//   * warp 8 lane 0 (MMA issuer): waits for both, issues four tcgen05.mma (K = 16) per weight tile
+//   * warp 16 lane 0 (MMA issuer): waits for both, issues four tcgen05.mma (K = 16) per weight tile
 //     accumulating in TMEM, and tcgen05.commit to the stage's `free` barrier, so the tensor cores run
 //     stage s while the other warps fill the next stages.
 // Inside every 32-run of K both operands use the same permutation (position 8t + 4h + i holds
@@ -33,8 +33,8 @@ namespace ggb {
 namespace {
 
 constexpr int kBK = 64;                // K per pipeline step (128 bytes of fp16: one swizzle row)
-constexpr int kDequantThreads = 256;
-constexpr int kThreadsG = 320;         // 8 dequant warps + MMA warp + producer warp
+constexpr int kDequantWarps = 16;
+constexpr int kThreadsG = (kDequantWarps + 2) * 32;      // dequant warps + MMA warp + producer warp
 constexpr int kMaxStagesG = 6;
 constexpr uint32_t kSpin = 1u << 17;
 enum : int { F_GEN = 0, F_Q4K = 1, F_Q6K = 2, F_Q80 = 3 };
@@ -90,18 +90,15 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint6
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 struct GemmArgs {
@@ -179,7 +176,7 @@ __device__ __forceinline__ void bytes_to_half(uint32_t n, __half2 bias, __half2&
     p23 = __hsub2(as_h2(__byte_perm(n, 0x64646464u, 0x4342)), bias);
 }
 
-// Q4_K, row-group-major layout.  Table row (8 words): word sb = half(d * sc_sb) | half(-dmin * m_sb) << 16.
+// Q4_K, row-group-major layout.  Table row (16 words): words 2 sb, 2 sb + 1 = half2(d * sc_sb) x 2, half2(-dmin * m_sb) x 2.
 __device__ __forceinline__ void q4k_table_words(const uint4 h, uint32_t* dst) {     // h: the row's 16-byte block header
     const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(h.x & 0xFFFFu)));
     const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(h.x >> 16)));
@@ -189,32 +186,33 @@ __device__ __forceinline__ void q4k_table_words(const uint4 h, uint32_t* dst) { 
         int sc, mn;
         if (sb < 4) { sc = B(sb) & 63; mn = B(sb + 4) & 63; }
         else { sc = (B(sb + 4) & 15) | ((B(sb - 4) >> 6) << 4); mn = (B(sb + 4) >> 4) | ((B(sb) >> 6) << 4); }
-        dst[sb] = pack_h2(d * static_cast<float>(sc), -(dmin * static_cast<float>(mn)));
+        const float sv = d * static_cast<float>(sc), ov = -(dmin * static_cast<float>(mn));
+        dst[2 * sb] = pack_h2(sv, sv);
+        dst[2 * sb + 1] = pack_h2(ov, ov);
     }
 }
-// one 16-byte chunk: slots 0-3 from the nibbles in na, 4-7 from nb_; e = scale | offset << 16
-__device__ __forceinline__ uint4 q4k_chunk(uint32_t na, uint32_t nb_, uint32_t e) {
+// one 16-byte chunk: slots 0-3 from the nibbles in na, 4-7 from nb_; w = q * ss + oo
+__device__ __forceinline__ uint4 q4k_chunk(uint32_t na, uint32_t nb_, const __half2 ss, const __half2 oo) {
     const __half2 k1024 = as_h2(0x64006400u);
-    const __half2 ss = as_h2(__byte_perm(e, e, 0x1010)), oo = as_h2(__byte_perm(e, e, 0x3232));
     __half2 p0, p1, p2, p3;
     bytes_to_half(na, k1024, p0, p1);
     bytes_to_half(nb_, k1024, p2, p3);
     return make_uint4(as_u32(__hfma2(p0, ss, oo)), as_u32(__hfma2(p1, ss, oo)), as_u32(__hfma2(p2, ss, oo)), as_u32(__hfma2(p3, ss, oo)));
 }
 
-// Q6_K, row-group-major layout.  Table row (8 words = 16 halves): half(d * sc_i), i = 0..15.
+// Q6_K, row-group-major layout.  Table row (16 words): word i = half2(d * sc_i) x 2, i = 0..15.
 __device__ __forceinline__ void q6k_table_words(const uint4 sc, const float d, uint32_t* dst) {     // sc: the row's 16 int8 scales
     const uint32_t wd[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int a = static_cast<int8_t>((wd[i >> 1] >> (16 * (i & 1))) & 0xFFu), c = static_cast<int8_t>((wd[i >> 1] >> (16 * (i & 1) + 8)) & 0xFFu);
-        dst[i] = pack_h2(d * static_cast<float>(a), d * static_cast<float>(c));
+        dst[2 * i] = pack_h2(d * static_cast<float>(a), d * static_cast<float>(a));
+        dst[2 * i + 1] = pack_h2(d * static_cast<float>(c), d * static_cast<float>(c));
     }
 }
-// one chunk: slots 0-3 = 6-bit values (nib0 | hb0 << 4) with scale lo16(e), slots 4-7 = (nib1 | hb1 << 4) with hi16(e)
-__device__ __forceinline__ uint4 q6k_chunk(uint32_t nib0, uint32_t hb0, uint32_t nib1, uint32_t hb1, uint32_t e) {
+// one chunk: slots 0-3 = 6-bit values (nib0 | hb0 << 4) with scale s0, slots 4-7 = (nib1 | hb1 << 4) with s1
+__device__ __forceinline__ uint4 q6k_chunk(uint32_t nib0, uint32_t hb0, uint32_t nib1, uint32_t hb1, const __half2 s0, const __half2 s1) {
     const __half2 k1056 = as_h2(0x64206420u);     // 1024 + 32
-    const __half2 s0 = as_h2(__byte_perm(e, e, 0x1010)), s1 = as_h2(__byte_perm(e, e, 0x3232));
     __half2 p0, p1, p2, p3;
     bytes_to_half(nib0 + (hb0 << 4), k1056, p0, p1);
     bytes_to_half(nib1 + (hb1 << 4), k1056, p2, p3);
@@ -227,6 +225,13 @@ __device__ __forceinline__ uint4 q80_chunk(uint32_t wa, uint32_t wb, __half2 dd)
     bytes_to_half(wa ^ 0x80808080u, k1152, p0, p1);
     bytes_to_half(wb ^ 0x80808080u, k1152, p2, p3);
     return make_uint4(as_u32(__hmul2(p0, dd)), as_u32(__hmul2(p1, dd)), as_u32(__hmul2(p2, dd)), as_u32(__hmul2(p3, dd)));
+}
+// Store chunks t (lo) and 4 + t (hi) of row r.  A quarter warp (lanes g, g + 1; t = 0..3) stores in one
+// wavefront when its eight 16-byte slots differ: even g writes lo first, odd g hi first.
+__device__ __forceinline__ void store_pair(uint8_t* tile, int r, int t, int odd, const uint4 lo, const uint4 hi) {
+    const uint4 first = odd ? hi : lo, second = odd ? lo : hi;
+    *reinterpret_cast<uint4*>(tile + swz_off(r, t + 4 * odd)) = first;
+    *reinterpret_cast<uint4*>(tile + swz_off(r, t + 4 * (odd ^ 1))) = second;
 }
 // any format: exact fp32 decode (the decoder the dequant kernel uses), one rounding to fp16
 __device__ __forceinline__ uint4 generic_chunk(const PackedW& w, int64_t row, int k0, int c, int block_elems) {
@@ -250,7 +255,9 @@ __device__ __forceinline__ uint4 generic_chunk(const PackedW& w, int64_t row, in
 // RT = weight tiles of 128 rows per CTA.  Non-dual: tile i covers rows n0 + 128 i of w.  Dual (RT == 2):
 // tile 0 = rows n0.. of w (gate), tile 1 = the same rows of w2 (up); the epilogue combines them.
 // Dynamic shared memory (1024-byte aligned): stages x { RT weight tiles of 16 KB, token tile tn x 128 B },
-// then the scale table RT x 128 rows x 32 B (Q4_K / Q6_K; each warp owns the rows it fills).
+// then the scale table RT x 128 rows x 64 B (Q4_K / Q6_K; each warp owns the rows it fills).
+// 16 dequant warps: warp w works on row group w % 8 (16 rows) of tile w / 8 (RT == 2) or on the
+// row half w / 8 of that group (RT == 1).  Warp 16 issues the MMAs, warp 17 the activation copies.
 template <int FMT, int RT>
 __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -261,16 +268,16 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     const int S = a.stages;
     const int b_bytes = a.tn * 128;
     const int stage_bytes = RT * 16384 + b_bytes;
-    uint32_t* table = reinterpret_cast<uint32_t*>(smem + static_cast<size_t>(S) * stage_bytes);      // [RT][128][8]
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem + static_cast<size_t>(S) * stage_bytes);      // [RT][128][16]
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * (a.dual ? 128 : 128 * RT);
     const int n_steps = a.K / kBK;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&a_full[s], 8); mbar_init(&b_full[s], 1); mbar_init(&free_bar[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&a_full[s], kDequantWarps); mbar_init(&b_full[s], 1); mbar_init(&free_bar[s], 1); }
         mbar_init(&done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {       // the MMA warp owns the tensor-memory allocation
+    if (warp == kDequantWarps) {       // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(&tmem_base_s)), "r"(static_cast<uint32_t>(a.tmem_cols)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -280,25 +287,26 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     const uint32_t tmem_d = tmem_base_s;
     bool ok = true;
 
-    if (warp == 9) {
+    if (warp == kDequantWarps + 1) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * n_steps * b_bytes;
+            int s = 0; uint32_t par = 1;          // parity of the `free` phase that releases the stage (first round: none)
             for (int ks = 0; ks < n_steps; ++ks) {
-                const int s = ks % S, u = ks / S;
-                if (u >= 1 && ok) ok = mbar_wait(&free_bar[s], (u - 1) & 1, a.err);
+                if (ks >= S && ok) ok = mbar_wait(&free_bar[s], par, a.err);
                 mbar_expect_tx(&b_full[s], static_cast<uint32_t>(b_bytes));
                 bulk_g2s(smem + static_cast<size_t>(s) * stage_bytes + RT * 16384, src + static_cast<size_t>(ks) * b_bytes, static_cast<uint32_t>(b_bytes), &b_full[s]);
+                if (++s == S) { s = 0; par ^= 1; }
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == kDequantWarps) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(128, a.tn);
+            int s = 0; uint32_t par = 0;
             for (int ks = 0; ks < n_steps; ++ks) {
-                const int s = ks % S, u = ks / S;
-                if (ok) ok = mbar_wait(&a_full[s], u & 1, a.err);
-                if (ok) ok = mbar_wait(&b_full[s], u & 1, a.err);
+                if (ok) ok = mbar_wait(&a_full[s], par, a.err);
+                if (ok) ok = mbar_wait(&b_full[s], par, a.err);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t st = s_u32(smem + static_cast<size_t>(s) * stage_bytes);
@@ -311,161 +319,178 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                         umma_f16(tmem_d + i * a.tn, da + 2 * kk, db + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);     // +32 bytes along K per instruction
                 }
                 umma_commit(&free_bar[s]);
+                if (++s == S) { s = 0; par ^= 1; }
             }
             if (ok) umma_commit(&done_bar);
         }
     } else {
         // ---------------- dequant warps ----------------
-        // Warp w fills rows 16 w .. 16 w + 15 of every weight tile.  Fragments are fetched two steps
-        // ahead into a rotating register queue (DRAM latency is longer than one step); K-quant
-        // sub-block scales are expanded once per 256-block into a warp-private table.
+        // Fragments are fetched two steps ahead into three register sets that rotate by name (DRAM
+        // latency is longer than one step); K-quant sub-block scales are expanded once per 256-block
+        // into the warp's own rows of the scale table.
         const int g = lane >> 2, t = lane & 3;
+        const int grp_w = warp & 7;
+        const int tile = RT == 2 ? (warp >> 3) : 0;
+        const int hi_first = RT == 2 ? 0 : (warp >> 3), hi_count = RT == 2 ? 2 : 1;      // row halves (g, g + 8) this warp fills
+        const PackedW& w = (a.dual && tile == 1) ? a.w2 : a.w;
+        const int64_t row0 = a.dual ? n0 : n0 + 128 * tile;
         const FormatInfo fi = format_info(a.w.type);
-        auto tile_w = [&](int i) -> const PackedW& { return (a.dual && i == 1) ? a.w2 : a.w; };
-        auto tile_row0 = [&](int i) -> int64_t { return a.dual ? n0 : n0 + 128 * i; };
         constexpr int NQ = FMT == F_Q6K ? 3 : (FMT == F_Q80 ? 2 : 1);
         struct Frag { uint4 v[NQ]; uint32_t d; };
         struct Hdr { uint4 v; float d; };
-        auto load_frag = [&](int ks, Frag (&f)[RT]) {
+        // per-thread stream positions
+        const int64_t grp = (row0 >> 4) + grp_w;
+        const bool grp_live = grp < ((w.N + 15) >> 4);
+        const uint8_t* q_base = nullptr;      // Q4_K: qs fragments; Q6_K: ql fragments; Q8_0: qs of this thread's row
+        const uint8_t* q_base2 = nullptr;     // Q6_K: qh fragments; Q8_0: block scales
+        int q80_r = 0, q80_hh = 0, q80_part = 0;
+        bool q80_live = false;
+        if (FMT == F_Q4K) q_base = w.s[1] + (grp * w.nb * 4 * 32 + lane) * 16;
+        if (FMT == F_Q6K) { q_base = w.s[0] + (grp * w.nb * 4 * 32 + lane) * 16; q_base2 = w.s[1] + (grp * w.nb * 2 * 32 + lane) * 16; }
+        if (FMT == F_Q80) {
+            const int lt = tid & 255;
+            if (RT == 2) { q80_r = lt >> 1; q80_hh = lt & 1; }
+            else { q80_r = tid >> 2; q80_hh = (tid >> 1) & 1; q80_part = tid & 1; }
+            const int64_t row = row0 + q80_r;
+            q80_live = row < w.N;
+            q_base = w.s[1] + (row * w.nb + q80_hh) * 32 + 8 * q80_part;
+            q_base2 = w.s[0] + (row * w.nb + q80_hh) * 2;
+        }
+        auto load_frag = [&](int ks, Frag& f) {
 #pragma unroll
-            for (int i = 0; i < RT; ++i) {
-                const PackedW& w = tile_w(i);
-#pragma unroll
-                for (int j = 0; j < NQ; ++j) f[i].v[j] = make_uint4(0u, 0u, 0u, 0u);
-                f[i].d = 0u;
-                if (FMT == F_Q4K || FMT == F_Q6K) {
-                    const int64_t grp = (tile_row0(i) >> 4) + warp;
-                    if (grp < ((w.N + 15) >> 4)) {
-                        const int64_t gb = grp * w.nb + (ks >> 2);
-                        if (FMT == F_Q4K) {
-                            f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + ((gb * 4 + (ks & 3)) * 32 + lane) * 16));
-                        } else {
-                            const int hf = (ks & 3) >> 1;
-                            f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[0] + ((gb * 4 + 2 * hf) * 32 + lane) * 16));
-                            f[i].v[1] = __ldg(reinterpret_cast<const uint4*>(w.s[0] + ((gb * 4 + 2 * hf + 1) * 32 + lane) * 16));
-                            f[i].v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + ((gb * 2 + hf) * 32 + lane) * 16));
-                        }
+            for (int j = 0; j < NQ; ++j) f.v[j] = make_uint4(0u, 0u, 0u, 0u);
+            f.d = 0u;
+            if (FMT == F_Q4K) {
+                if (grp_live) f.v[0] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>(ks) * 512));
+            } else if (FMT == F_Q6K) {
+                if (grp_live) {
+                    f.v[0] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>(ks & ~1) * 512));
+                    f.v[1] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>((ks & ~1) + 1) * 512));
+                    f.v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(q_base2 + static_cast<size_t>(ks >> 1) * 512));
+                }
+            } else if (FMT == F_Q80) {
+                if (q80_live) {
+                    const uint8_t* p = q_base + static_cast<size_t>(ks) * 64;
+                    if (RT == 2) {
+                        f.v[0] = __ldg(reinterpret_cast<const uint4*>(p));
+                        f.v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(p + 16));
+                    } else {
+                        const uint2 lo = __ldg(reinterpret_cast<const uint2*>(p)), hi = __ldg(reinterpret_cast<const uint2*>(p + 16));
+                        f.v[0].x = lo.x; f.v[0].y = lo.y; f.v[NQ - 1].x = hi.x; f.v[NQ - 1].y = hi.y;
                     }
-                } else if (FMT == F_Q80) {
-                    // two lanes per row, each one 32-element block = chunks 4 hh .. 4 hh + 3
-                    const int64_t row = tile_row0(i) + (tid >> 1);
-                    if (row < w.N) {
-                        const int64_t blk = row * w.nb + 2 * ks + (tid & 1);
-                        f[i].v[0] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + blk * 32));
-                        f[i].v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(w.s[1] + blk * 32 + 16));
-                        f[i].d = __ldg(reinterpret_cast<const unsigned short*>(w.s[0] + blk * 2));
-                    }
+                    f.d = __ldg(reinterpret_cast<const unsigned short*>(q_base2 + static_cast<size_t>(ks) * 4));
                 }
             }
         };
-        // K-quant header of (tile lane / 16, row 16 w + lane % 16), block b
+        // K-quant header of this lane's table row (row r16 of the group), block b
+        const int hdr_lanes = RT == 2 ? 16 : 8;
+        const int r16 = RT == 2 ? (lane & 15) : 8 * hi_first + (lane & 7);
         auto load_hdr = [&](int b) -> Hdr {
             Hdr h; h.v = make_uint4(0u, 0u, 0u, 0u); h.d = 0.0f;
-            const int i = lane >> 4;
-            if ((FMT == F_Q4K || FMT == F_Q6K) && i < RT && b < a.w.nb) {
-                const PackedW& w = tile_w(i);
-                const int64_t row = tile_row0(i) + warp * 16 + (lane & 15);
-                if (row < ((w.N + 15) >> 4) * 16) {
-                    const int64_t slot = ((row >> 4) * w.nb + b) * 16 + (row & 15);
-                    if (FMT == F_Q4K) h.v = __ldg(reinterpret_cast<const uint4*>(w.s[0] + slot * 16));
-                    else { h.v = __ldg(reinterpret_cast<const uint4*>(w.s[2] + slot * 16)); h.d = ld_f16(w.s[3] + slot * 2); }
-                }
+            if ((FMT == F_Q4K || FMT == F_Q6K) && lane < hdr_lanes && b < w.nb && grp_live) {
+                const int64_t slot = (grp * w.nb + b) * 16 + r16;
+                if (FMT == F_Q4K) h.v = __ldg(reinterpret_cast<const uint4*>(w.s[0] + slot * 16));
+                else { h.v = __ldg(reinterpret_cast<const uint4*>(w.s[2] + slot * 16)); h.d = ld_f16(w.s[3] + slot * 2); }
             }
             return h;
         };
-        Frag f0[RT], f1[RT], f2[RT];
+        uint32_t* tb = table + tile * 128 * 16;
+        uint8_t* stage_ptr = smem + tile * 16384;
+        int s_cur = 0; uint32_t par_free = 1;
+        Frag f0, f1, f2;
         Hdr h0 = load_hdr(0), h1 = load_hdr(1);
         load_frag(0, f0);
         if (n_steps > 1) load_frag(1, f1);
-        for (int ks = 0; ks < n_steps; ++ks) {
-            const int s = ks % S, u = ks / S;
-            const int k0 = ks * kBK;
-            uint8_t* As = smem + static_cast<size_t>(s) * stage_bytes;
-            if (FMT != F_GEN && ks + 2 < n_steps) load_frag(ks + 2, f2);
+        // one pipeline step: fetch the fragments of step ks + 2 into `ahead`, fill stage s_cur from `cur`
+        auto step = [&](const int ks, const Frag& cur, Frag& ahead) {
+            uint8_t* At = stage_ptr + static_cast<size_t>(s_cur) * stage_bytes;
+            if (FMT != F_GEN && ks + 2 < n_steps) load_frag(ks + 2, ahead);
             if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == 0) {
                 // the previous block's readers are past their __syncwarp; expand this block's scales
-                if ((lane >> 4) < RT) {
-                    uint32_t* dst = table + ((lane >> 4) * 128 + warp * 16 + (lane & 15)) * 8;
+                if (lane < hdr_lanes) {
+                    uint32_t* dst = tb + (grp_w * 16 + r16) * 16;
                     if (FMT == F_Q4K) q4k_table_words(h0.v, dst); else q6k_table_words(h0.v, h0.d, dst);
                 }
                 h0 = h1;
                 h1 = load_hdr((ks >> 2) + 2);
                 __syncwarp();
             }
-            if (u >= 1 && ok) ok = mbar_wait(&free_bar[s], (u - 1) & 1, a.err);
+            if (ks >= S && ok) ok = mbar_wait(&free_bar[s_cur], par_free, a.err);
             if (FMT == F_Q4K || FMT == F_Q6K) {
 #pragma unroll
-                for (int i = 0; i < RT; ++i) {
-                    uint8_t* At = As + i * 16384;
-                    const uint32_t* tb = table + i * 128 * 8;
-#pragma unroll
-                    for (int hi = 0; hi < 2; ++hi) {                 // rows g and g + 8 of the group
-                        const int r = warp * 16 + g + 8 * hi;
-                        const uint2 e = *reinterpret_cast<const uint2*>(tb + r * 8 + 2 * (ks & 3));
-                        if (FMT == F_Q4K) {
-                            const uint32_t wa = hi ? f0[i].v[0].y : f0[i].v[0].x, wb = hi ? f0[i].v[0].w : f0[i].v[0].z;
-                            *reinterpret_cast<uint4*>(At + swz_off(r, t)) = q4k_chunk(wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, e.x);
-                            *reinterpret_cast<uint4*>(At + swz_off(r, 4 + t)) = q4k_chunk((wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu, e.y);
-                        } else {
-                            const uint4 c0 = f0[i].v[0], c1 = f0[i].v[1], qh = f0[i].v[NQ - 1];
-                            const uint32_t a0 = hi ? c0.z : c0.x, b0 = hi ? c0.w : c0.y;      // c = 0: ql_a, ql_b
-                            const uint32_t a1 = hi ? c1.z : c1.x, b1 = hi ? c1.w : c1.y;      // c = 1
-                            const uint32_t q0 = hi ? qh.y : qh.x, q1 = hi ? qh.w : qh.z;      // qh of c = 0, 1
-                            const int sh = 4 * (ks & 1);
-                            *reinterpret_cast<uint4*>(At + swz_off(r, t)) =
-                                q6k_chunk((a0 >> sh) & 0x0F0F0F0Fu, (q0 >> sh) & 0x03030303u, (a1 >> sh) & 0x0F0F0F0Fu, (q1 >> sh) & 0x03030303u, e.x);
-                            *reinterpret_cast<uint4*>(At + swz_off(r, 4 + t)) =
-                                q6k_chunk((b0 >> sh) & 0x0F0F0F0Fu, (q0 >> (sh + 2)) & 0x03030303u, (b1 >> sh) & 0x0F0F0F0Fu, (q1 >> (sh + 2)) & 0x03030303u, e.y);
-                        }
+                for (int hq = 0; hq < 2; ++hq) {
+                    if (hq >= hi_count) break;
+                    const int hi = hi_first + hq;                      // 0: row g, 1: row g + 8
+                    const int r = grp_w * 16 + g + 8 * hi;
+                    const uint4 e = *reinterpret_cast<const uint4*>(tb + r * 16 + 4 * (ks & 3));
+                    if (FMT == F_Q4K) {
+                        const uint32_t wa = hi ? cur.v[0].y : cur.v[0].x, wb = hi ? cur.v[0].w : cur.v[0].z;
+                        store_pair(At, r, t, g & 1, q4k_chunk(wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, as_h2(e.x), as_h2(e.y)),
+                                   q4k_chunk((wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu, as_h2(e.z), as_h2(e.w)));
+                    } else {
+                        const uint4 c0 = cur.v[0], c1 = cur.v[1], qh = cur.v[NQ - 1];
+                        const uint32_t a0 = hi ? c0.z : c0.x, b0 = hi ? c0.w : c0.y;      // c = 0: ql_a, ql_b
+                        const uint32_t a1 = hi ? c1.z : c1.x, b1 = hi ? c1.w : c1.y;      // c = 1
+                        const uint32_t q0 = hi ? qh.y : qh.x, q1 = hi ? qh.w : qh.z;      // qh of c = 0, 1
+                        const int sh = 4 * (ks & 1);
+                        store_pair(At, r, t, g & 1,
+                                   q6k_chunk((a0 >> sh) & 0x0F0F0F0Fu, (q0 >> sh) & 0x03030303u, (a1 >> sh) & 0x0F0F0F0Fu, (q1 >> sh) & 0x03030303u, as_h2(e.x), as_h2(e.y)),
+                                   q6k_chunk((b0 >> sh) & 0x0F0F0F0Fu, (q0 >> (sh + 2)) & 0x03030303u, (b1 >> sh) & 0x0F0F0F0Fu, (q1 >> (sh + 2)) & 0x03030303u, as_h2(e.z), as_h2(e.w)));
                     }
                 }
             } else if (FMT == F_Q80) {
-                const int r = tid >> 1, hh = tid & 1;
-#pragma unroll
-                for (int i = 0; i < RT; ++i) {
-                    uint8_t* At = As + i * 16384;
-                    const uint4 lo = f0[i].v[0], hi4 = f0[i].v[NQ - 1];
-                    const __half2 dd = __half2half2(__ushort_as_half(static_cast<unsigned short>(f0[i].d)));
-                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 0)) = q80_chunk(lo.x, hi4.x, dd);
-                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 1)) = q80_chunk(lo.y, hi4.y, dd);
-                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 2)) = q80_chunk(lo.z, hi4.z, dd);
-                    *reinterpret_cast<uint4*>(At + swz_off(r, 4 * hh + 3)) = q80_chunk(lo.w, hi4.w, dd);
+                const uint4 lo = cur.v[0], hi4 = cur.v[NQ - 1];
+                const __half2 dd = __half2half2(__ushort_as_half(static_cast<unsigned short>(cur.d)));
+                const int c0 = 4 * q80_hh + 2 * q80_part;
+                *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 0)) = q80_chunk(lo.x, hi4.x, dd);
+                *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 1)) = q80_chunk(lo.y, hi4.y, dd);
+                if (RT == 2) {
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = q80_chunk(lo.z, hi4.z, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = q80_chunk(lo.w, hi4.w, dd);
                 }
             } else {
-                for (int it = tid; it < RT * 128 * 8; it += kDequantThreads) {
+                uint8_t* As = smem + static_cast<size_t>(s_cur) * stage_bytes;
+                for (int it = tid; it < RT * 128 * 8; it += kDequantWarps * 32) {
                     const int i = it >> 10, r = (it >> 3) & 127, c = it & 7;
-                    *reinterpret_cast<uint4*>(As + i * 16384 + swz_off(r, c)) = generic_chunk(tile_w(i), tile_row0(i) + r, k0, c, fi.block_elems);
+                    *reinterpret_cast<uint4*>(As + i * 16384 + swz_off(r, c)) =
+                        generic_chunk((a.dual && i == 1) ? a.w2 : a.w, (a.dual ? n0 : n0 + 128 * i) + r, ks * kBK, c, fi.block_elems);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&a_full[s]);
-#pragma unroll
-            for (int i = 0; i < RT; ++i) { f0[i] = f1[i]; f1[i] = f2[i]; }
+            if (lane == 0) mbar_arrive(&a_full[s_cur]);
+            if (++s_cur == S) { s_cur = 0; par_free ^= 1; }
+        };
+        for (int ks = 0; ks < n_steps; ks += 3) {
+            step(ks, f0, f2);
+            if (ks + 1 < n_steps) step(ks + 1, f1, f0);
+            if (ks + 2 < n_steps) step(ks + 2, f2, f1);
         }
-        // ---------------- epilogue (the same 8 warps) ----------------
+        // ---------------- epilogue (the same 16 warps) ----------------
         if (ok) ok = mbar_wait(&done_bar, 0, a.err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            const int q = warp & 3, half = warp >> 2;
+            const int q = warp & 3, part = warp >> 2;
             const int t0 = blockIdx.y * a.tn;
-            // non-dual RT == 2: warp half = weight tile, all columns; otherwise the halves split the columns
+            // non-dual RT == 2: two warps per weight tile and lane quarter, each half the columns;
+            // otherwise four warps per lane quarter, each a quarter of the columns
             const bool by_tile = (RT == 2 && !a.dual);
-            const int tile = by_tile ? half : 0;
-            const int64_t n = n0 + 128 * tile + q * 32 + lane;
-            const int c_begin = by_tile ? 0 : half * (a.tn / 2), c_end = by_tile ? a.tn : c_begin + a.tn / 2;
-            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                float v[32], v2[32];
-                const uint32_t taddr = tmem_d + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(tile * a.tn + c0);
-                tmem_ld32(taddr, v);
-                if (a.dual) tmem_ld32(taddr + a.tn, v2);
+            const int tile_e = by_tile ? (part & 1) : 0;
+            const int c_len = by_tile ? a.tn / 2 : a.tn / 4;
+            const int c_begin = (by_tile ? (part >> 1) : part) * c_len;
+            const int64_t n = n0 + 128 * tile_e + q * 32 + lane;
+            for (int c0 = c_begin; c0 < c_begin + c_len; c0 += 16) {
+                float v[16], v2[16];
+                const uint32_t taddr = tmem_d + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(tile_e * a.tn + c0);
+                tmem_ld16(taddr, v);
+                if (a.dual) tmem_ld16(taddr + a.tn, v2);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     const int tok = t0 + c0 + i;
                     if (tok < a.M && n < a.w.N) {
                         const size_t o = static_cast<size_t>(tok) * a.ldc + n;
                         float r = v[i];
-                        if (a.dual) r = (r / (1.0f + expf(-r))) * v2[i];
+                        if (a.dual) r = __fdividef(r, 1.0f + __expf(-r)) * v2[i];
                         else if (a.epi == EPI_ADD_BIAS) r += __ldg(a.bias + n);
                         else if (a.epi == EPI_RESIDUAL) r += a.resid[o];
                         a.y[o] = r;
@@ -476,7 +501,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kDequantWarps) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(static_cast<uint32_t>(a.tmem_cols)) : "memory");
     }
 }
@@ -541,7 +566,7 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     int cols = 32;
     while (cols < tn * rt) cols <<= 1;
     const size_t stage_bytes = static_cast<size_t>(rt) * 16384 + static_cast<size_t>(tn) * 128;
-    const size_t table_bytes = static_cast<size_t>(rt) * 128 * 32;
+    const size_t table_bytes = static_cast<size_t>(rt) * 128 * 64;
     const size_t budget = 227 * 1024 - 1024 - table_bytes - 2048;      // alignment slack, table, static barriers
     const int stages = static_cast<int>(std::min<size_t>(kMaxStagesG, budget / stage_bytes));
     if (stages < 2) return GGB_NOT_FOUND;
