@@ -85,7 +85,7 @@ EXPORTS = [
     "ggb_create", "ggb_destroy", "ggb_mul_mat_q", "ggb_rms_norm", "ggb_rope", "ggb_rope_batched", "ggb_matmul_bf16",
     "ggb_softmax", "ggb_silu", "ggb_gelu", "ggb_flash_attn", "ggb_sync", "ggb_is_available", "ggb_name", "ggb_last_error",
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
-    "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
+    "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
     "ggb_model_read_kv", "ggb_model_decode_bytes",
 ]
@@ -127,6 +127,7 @@ def load_library() -> C.CDLL:
     L.ggb_gemv_device.argtypes = [vp, vp, vp, i32, i32, vp, i32, i32, vp, vp, f32]
     L.ggb_gemv_swiglu_device.argtypes = [vp, vp, vp, vp, i32, i32, vp, i32, vp, f32]
     L.ggb_attn_paged_device.argtypes = [vp, C.POINTER(AttnPagedParams)]
+    L.ggb_attn_prefill_device.argtypes = [vp, C.POINTER(AttnPagedParams), i32]
     L.ggb_attn_paged_static.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_stream.argtypes = [vp]
     L.ggb_stream.restype = vp
@@ -274,6 +275,11 @@ class CudaBackend:
         """All pointer arguments are device addresses (ints)."""
         p = AttnPagedParams(q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos)
         return Status(self.lib.ggb_attn_paged_device(self.h, C.byref(p)))
+
+    def attn_prefill_device(self, q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos, n_tok) -> Status:
+        """Causal attention of n_tok query tokens starting at position pos (device pointers)."""
+        p = AttnPagedParams(q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos)
+        return Status(self.lib.ggb_attn_prefill_device(self.h, C.byref(p), n_tok))
 
     def attn_paged_static(self, q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos) -> Status:
         """attn_paged_device without any device allocation (fixed scratch inside the library)."""

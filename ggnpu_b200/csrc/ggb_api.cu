@@ -26,6 +26,17 @@ int cuda_status(Context* c, cudaError_t e, const char* what) {
     return set_status(c, e == cudaErrorMemoryAllocation ? GGB_OUT_OF_MEMORY : GGB_ERROR, m.c_str());
 }
 
+// FNV-1a over 64 evenly spaced 64-byte samples (the whole buffer when it is small)
+static uint64_t weight_fingerprint(const void* data, size_t bytes) {
+    const uint8_t* b = static_cast<const uint8_t*>(data);
+    uint64_t h = 1469598103934665603ull;
+    auto eat = [&](size_t from, size_t n) { for (size_t i = 0; i < n; ++i) { h ^= b[from + i]; h *= 1099511628211ull; } };
+    if (bytes <= 64 * 64) { eat(0, bytes); return h; }
+    const size_t stride = (bytes - 64) / 63;
+    for (int i = 0; i < 64; ++i) eat(static_cast<size_t>(i) * stride, 64);
+    return h;
+}
+
 void* scratch(Context* c, int slot, size_t bytes) {
     if (bytes <= c->d_scratch_bytes[slot]) return c->d_scratch[slot];
     if (c->d_scratch[slot]) { cudaStreamSynchronize(c->stream); cudaFree(c->d_scratch[slot]); c->d_scratch[slot] = nullptr; c->d_scratch_bytes[slot] = 0; }
@@ -154,10 +165,20 @@ int ggb_mul_mat_q(ggb_handle h, const ggb_mul_mat_params* p) {
         if (!f.block_elems) return set_status(h, GGB_INVALID_PARAM, "mul_mat_q: unsupported B_type");
         if (K % f.block_elems) return set_status(h, GGB_INVALID_PARAM, "mul_mat_q: K is not a multiple of the block length");
         Context::Key key{p->B, N, K, p->B_type};
+        const uint64_t fp = weight_fingerprint(p->B, static_cast<size_t>(N) * (K / f.block_elems) * f.block_bytes);
         DeviceWeight* dw = nullptr;
         auto it = h->weight_cache.find(key);
-        if (it != h->weight_cache.end()) dw = it->second;
-        else { GGB_TRY(upload_weight(h, p->B_type, N, K, p->B, &dw)); h->weight_cache[key] = dw; }
+        if (it != h->weight_cache.end() && it->second->fingerprint == fp) dw = it->second;
+        else {
+            if (it != h->weight_cache.end()) {            // same address and shape, other contents: replace
+                cudaStreamSynchronize(h->stream);
+                free_weight(it->second);
+                h->weight_cache.erase(it);
+            }
+            GGB_TRY(upload_weight(h, p->B_type, N, K, p->B, &dw));
+            dw->fingerprint = fp;
+            h->weight_cache[key] = dw;
+        }
         GemvArgs a{};
         a.w = dw->w; a.x = dA; a.M = M; a.lda = K; a.y = dC; a.ldc = N; a.epi = EPI_STORE;
         GGB_TRY(launch_gemv(h, a, h->stream));

@@ -405,6 +405,10 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     const int hd = a.head_dim;
     if (a.page % 8) return set_status(c, GGB_INVALID_PARAM, "attention: page size must be a multiple of 8");
     if (a.fuse && n_tok != 1) return set_status(c, GGB_INVALID_PARAM, "attention: fused append is for single-token steps");
+    if (c->use_tc && n_tok >= c->tc_min_m && !a.fuse) {      // prompt chunks: tensor-core flash attention
+        const int st = launch_attn_prefill(c, a, n_tok, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
     dim3 grid(a.n_kv, a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
     size_t smem = 0;
@@ -467,6 +471,20 @@ extern "C" int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* 
     float* partial = static_cast<float*>(scratch(h, 3, sizeof(float) * attn_partial_floats(1, p->n_head, n_splits, p->head_dim)));
     if (!partial) return h->last_status;
     return launch_attn_paged(h, paged_args(p, partial), 1, h->stream);
+}
+
+extern "C" int ggb_attn_prefill_device(ggb_handle h, const ggb_attn_paged_params* p, int n_tok) {
+    if (!h) return GGB_UNAVAILABLE;
+    int st = check_paged_params(h, p);
+    if (st != GGB_OK) return st;
+    if (n_tok <= 0 || p->pos + n_tok > p->n_pages * p->page) return set_status(h, GGB_INVALID_PARAM, "attn_prefill: chunk runs past the cache");
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    int n_splits, pps;
+    attn_split_geometry(p->n_pages, &n_splits, &pps);
+    float* partial = static_cast<float*>(scratch(h, 3, sizeof(float) * attn_partial_floats(n_tok, p->n_head, n_splits, p->head_dim)));
+    if (!partial) return h->last_status;
+    return launch_attn_paged(h, paged_args(p, partial), n_tok, h->stream);
 }
 
 // ---- the same attention without any allocation --------------------------------------------------

@@ -54,6 +54,7 @@ struct AttnPagedArgs {
 
 int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s);
 int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s);
+int launch_attn_prefill(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s);   // ggb_attn_prefill.cu; GGB_NOT_FOUND: geometry not covered
 size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim);
 void attn_split_geometry(int n_pages, int* n_splits, int* pages_per_split);
 

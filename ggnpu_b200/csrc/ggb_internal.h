@@ -45,6 +45,9 @@ struct DeviceWeight {
     PackedW w{};
     void* base = nullptr;     // one allocation holding all streams
     size_t bytes = 0;
+    // fingerprint of sampled host bytes (weight cache): a freed host buffer whose address is reused
+    // for other weights of the same shape must not hit the stale copy
+    uint64_t fingerprint = 0;
 };
 
 struct Context {

@@ -208,6 +208,14 @@ typedef struct ggb_attn_paged_params {
 } ggb_attn_paged_params;
 GGB_API int ggb_attn_paged_device(ggb_handle h, const ggb_attn_paged_params* p);
 
+/* Causal attention of a prompt chunk: n_tok query tokens at positions p->pos .. p->pos + n_tok - 1,
+ * q and out are [n_tok][n_head][head_dim]; token t attends keys 0 .. p->pos + t, all of which must
+ * already be in the cache (p->pos + n_tok <= n_pages * page).  Replaces the per-token loop GQA expand
+ * -> Backend::flash_attn (src/cli/main.cpp:3364-3383 -> cpu_ref.cpp:223-280) over the chunk.  With
+ * page == 64 and head_dim 64 or 128 this is a tensor-core flash-attention kernel (Q and the softmax
+ * weights rounded to bf16, fp32 accumulation); other geometries run the per-token kernel. */
+GGB_API int ggb_attn_prefill_device(ggb_handle h, const ggb_attn_paged_params* p, int n_tok);
+
 /* The same computation as ggb_attn_paged_device for callers that must not cause a device
  * allocation.  (No counterpart in the reference: its backends allocate buffers as they please.)
  * Who needs it: a host that gave all of the GPU's memory to its own pool at start-up, so a

@@ -51,6 +51,41 @@ def test_paged_attention_matches_oracle(backend, oracle, shape):
         assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=2e-6), (shape, pos)
 
 
+@pytest.mark.parametrize("shape", [(32, 8, 64, 64, 8), (12, 2, 128, 64, 5), (8, 2, 64, 16, 12)])
+def test_prefill_attention_matches_oracle(backend, oracle, shape):
+    """A chunk of query tokens, causal: every token against the oracle's single-query flash_attn.
+    page 64 with head_dim 64 / 128 runs the tensor-core kernel (Q and the softmax weights rounded to
+    bf16: rel-L2 <= 5e-3, max-abs <= 2e-2 of the largest output); page 16 runs the per-token kernel
+    (fp32 queries: 2e-5)."""
+    n_head, n_kv, hd, page, n_pages = shape
+    _, k, v, kp, vp, table = make_case(*shape, seed=sum(shape) + 1)
+    dev = torch.device("cuda:0")
+    dk, dv, dt = kp.to(dev), vp.to(dev), table.to(dev)
+    ctx = page * n_pages
+    tensor_path = page == 64
+    for pos0, n_tok in ((0, 70), (page + 5, 100), (ctx - 130, 130), (3, 32)):
+        g = torch.Generator().manual_seed(pos0 + n_tok)
+        q = torch.randn(n_tok, n_head, hd, generator=g)
+        dq = q.to(dev)
+        out = torch.full((n_tok, n_head, hd), float("nan"), device=dev)
+        torch.cuda.synchronize()
+        st = backend.attn_prefill_device(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dt.data_ptr(), out.data_ptr(),
+                                         n_head, n_kv, hd, page, n_pages, pos0, n_tok)
+        assert st == Status.OK, backend.last_error_message()
+        backend.sync()
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        for t in (0, 1, n_tok // 2, n_tok - 2, n_tok - 1):
+            upto = pos0 + t + 1
+            want = oracle.flash_attn(q[t].numpy(), expanded(k, n_head, n_kv, upto), expanded(v, n_head, n_kv, upto), -1)
+            if tensor_path:
+                err = got[t] - want
+                assert np.linalg.norm(err) <= 5e-3 * np.linalg.norm(want), (shape, pos0, t, np.linalg.norm(err) / np.linalg.norm(want))
+                assert np.abs(err).max() <= 2e-2 * np.abs(want).max()
+            else:
+                assert np.allclose(got[t], want, rtol=2e-5, atol=2e-6), (shape, pos0, t)
+
+
 def test_paged_attention_argument_errors(backend):
     dev = torch.device("cuda:0")
     t = torch.zeros(64, device=dev)
