@@ -104,39 +104,41 @@ int launch_attn_expanded(Context* c, const float* Q, const float* K, const float
 // double, src/cli/main.cpp:3294-3299), rotate q in place and k from the table row p
 // (src/cli/main.cpp:1294-1308 / 3328-3341), store k (rotated) and v as bf16 into page p / page,
 // slot p % page (K is cached after RoPE, V raw: src/cli/main.cpp:3354-3356).
-// grid (n_head + n_kv, n_tok); one CTA per head per token; blockDim = head_dim / 2 pairs.
+// grid (ceil((n_head + n_kv) / blockDim.y), n_tok); blockDim.x = head_dim / 2 pairs rounded up to a warp,
+// blockDim.y heads per CTA (256 threads in all).
 __global__ void rope_append_kernel(KvAppendArgs a) {
     stamp(a.trace, 0, 5);
     pdl_sync();
     stamp(a.trace, 1, 5);
-    const int t = blockIdx.y, hh = blockIdx.x;
+    const int t = blockIdx.y, hh = blockIdx.x * blockDim.y + threadIdx.y;
+    const bool active = hh < a.n_head + a.n_kv;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int hd = a.head_dim, half = hd >> 1;
     const bool is_q = hh < a.n_head;
     const int h = is_q ? hh : hh - a.n_head;
-    float* src = is_q ? a.q + (static_cast<size_t>(t) * a.n_head + h) * hd : a.k + (static_cast<size_t>(t) * a.n_kv + h) * hd;
+    float* src = !active ? nullptr : (is_q ? a.q + (static_cast<size_t>(t) * a.n_head + h) * hd : a.k + (static_cast<size_t>(t) * a.n_kv + h) * hd);
     const float* nw = is_q ? a.q_norm : a.k_norm;
-    __shared__ double red[8];
-    __shared__ float inv_s;
+    __shared__ double red[8][8];
+    __shared__ float inv_s[8];
     const int i = threadIdx.x;               // pair index
     const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
     float v0 = 0.0f, v1 = 0.0f;
-    if (i < half) { v0 = src[i0]; v1 = src[i1]; }
-    if (nw) {
+    if (active && i < half) { v0 = src[i0]; v1 = src[i1]; }
+    if (a.q_norm || a.k_norm) {              // uniform over the CTA: every thread reaches the barriers
         double ss = static_cast<double>(v0) * v0 + static_cast<double>(v1) * v1;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        if ((threadIdx.x & 31) == 0) red[threadIdx.y][threadIdx.x >> 5] = ss;
         __syncthreads();
         if (threadIdx.x == 0) {
             double tot = 0.0;
-            for (int w = 0; w < (blockDim.x + 31) / 32; ++w) tot += red[w];
-            inv_s = 1.0f / sqrtf(static_cast<float>(tot / hd) + a.eps);
+            for (int w = 0; w < (blockDim.x + 31) / 32; ++w) tot += red[threadIdx.y][w];
+            inv_s[threadIdx.y] = 1.0f / sqrtf(static_cast<float>(tot / hd) + a.eps);
         }
         __syncthreads();
-        if (i < half) { v0 = v0 * inv_s * nw[i0]; v1 = v1 * inv_s * nw[i1]; }
+        if (nw && active && i < half) { v0 = v0 * inv_s[threadIdx.y] * nw[i0]; v1 = v1 * inv_s[threadIdx.y] * nw[i1]; }
     }
-    if (i < half) {
+    if (active && i < half) {
         const float cs = a.cos_tab[static_cast<size_t>(pos) * half + i], sn = a.sin_tab[static_cast<size_t>(pos) * half + i];
         const float r0 = v0 * cs - v1 * sn, r1 = v0 * sn + v1 * cs;
         if (is_q) { src[i0] = r0; src[i1] = r1; }
@@ -156,9 +158,11 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
 int launch_rope_append(Context* c, const KvAppendArgs& a_in, int n_tok, cudaStream_t s) {
     KvAppendArgs a = a_in;
     a.trace = trace_slot(c);
-    const int threads = ((a.head_dim / 2) + 31) / 32 * 32;
-    dim3 grid(a.n_head + a.n_kv, n_tok);
-    const cudaError_t e = launch_pdl(c, rope_append_kernel, grid, dim3(threads), 0, s, a);
+    const int tx = ((a.head_dim / 2) + 31) / 32 * 32;
+    if (tx > 256) return set_status(c, GGB_INVALID_PARAM, "rope_append: head_dim must be at most 512");
+    const int ty = std::max(1, std::min(8, 256 / tx));
+    dim3 grid((a.n_head + a.n_kv + ty - 1) / ty, n_tok);
+    const cudaError_t e = launch_pdl(c, rope_append_kernel, grid, dim3(tx, ty), 0, s, a);
     c->launches++;
     return cuda_status(c, e, "rope_append");
 }

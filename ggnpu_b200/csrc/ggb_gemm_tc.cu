@@ -10,7 +10,7 @@
 //   * warps 0-15 (dequant): read the quantised fragments with 128-bit loads, expand them with byte
 //     permutes + packed half arithmetic (integer -> fp16 through the 0x6400 | q trick, exact), scale,
 //     and store the 128 x 64 tiles into shared memory in the K-major 128-byte-swizzled layout
-//     tcgen05.mma reads; fence.proxy.async, then one arrive per warp on the stage's `a_full` barrier;
+//     tcgen05.mma reads; fence.proxy.async, then one arrive per warp on the stage's `full` barrier;
 //   * warp 17 lane 0 (activation producer): one cp.async.bulk per stage brings the token tile, which
 //     x_prep_kernel wrote once per call already in the swizzled tile image (RMS norm fused there);
 //   * warp 16 lane 0 (MMA issuer): waits for both, issues four tcgen05.mma (K = 16) per weight tile
@@ -24,6 +24,9 @@
 // No cluster launch and no multicast copy is used.  Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
+#include <stdio.h>
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "ggb_internal.h"
@@ -35,7 +38,7 @@ namespace {
 constexpr int kBK = 64;                // K per pipeline step (128 bytes of fp16: one swizzle row)
 constexpr int kDequantWarps = 16;
 constexpr int kThreadsG = (kDequantWarps + 2) * 32;      // dequant warps + MMA warp + producer warp
-constexpr int kMaxStagesG = 6;
+constexpr int kMaxStagesG = 8;
 constexpr uint32_t kSpin = 1u << 17;
 enum : int { F_GEN = 0, F_Q4K = 1, F_Q6K = 2, F_Q80 = 3 };
 
@@ -67,17 +70,10 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 
 // Shared-memory matrix descriptor of a K-major 16-bit tile whose rows are 128 bytes, swizzled in
-// 8-row / 1024-byte atoms (tile base 1024-byte aligned): start address, stride between 8-row groups
-// 1024 bytes, descriptor version 1 (sm_100), swizzle mode 2 (128 bytes).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // bits 0-13: address / 16
-    d |= static_cast<uint64_t>(1) << 16;                               // bits 16-29: leading byte offset / 16 (unused for swizzled K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;                       // bits 32-45: stride byte offset / 16
-    d |= static_cast<uint64_t>(1) << 46;                               // bits 46-47: descriptor version
-    d |= static_cast<uint64_t>(2) << 61;                               // bits 61-63: 128-byte swizzle
-    return d;
-}
+// 8-row / 1024-byte atoms (tile base 1024-byte aligned): bits 0-13 address / 16, bits 16-29 leading
+// byte offset / 16 (unused for swizzled K-major, set to 1), bits 32-45 stride between 8-row groups / 16
+// (1024 B -> 64), bits 46-47 descriptor version 1 (sm_100), bits 61-63 swizzle mode 2 (128 bytes).
+// The MMA thread keeps the constant high word (0x40004040) and advances the low word.
 // Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (format 0), both K-major,
 // N / 8 in bits 17-22, M / 16 in bits 24-28.
 __device__ __forceinline__ uint32_t umma_idesc(int M, int N) {
@@ -101,6 +97,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// tuning aid (GGB_TC_TRACE=1): %globaltimer stamps of CTA (0,0): [0..63] MMA thread (4 per step: a ready,
+// b ready, issued, -), [64..127] dequant warp 0 (4 per step: start, stage free, arrived, -)
+__device__ unsigned long long g_tc_trace[128];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
 struct GemmArgs {
     PackedW w, w2;                // w2: second matrix of the fused gate/up pair (dual)
     const __half* xb;             // activation tile images, see x_prep_kernel
@@ -111,6 +112,8 @@ struct GemmArgs {
     int tn;                       // tokens per CTA tile (multiple of 64, <= 256)
     int tmem_cols;                // power of two >= accumulator columns, >= 32
     int stages;
+    int trace;
+    __half* y_img;                // dual only: write silu(gate) * up as the fp16 tile image of the next GEMM (K = N) instead of y
     int* err;
 };
 
@@ -120,15 +123,15 @@ __host__ __device__ __forceinline__ uint32_t swz_off(int r, int c) { return stat
 __host__ __device__ __forceinline__ int perm_k(int c, int e) { return 32 * (c >> 2) + 16 * (e >> 2) + 4 * (c & 3) + (e & 3); }
 
 // ---- activations: fp32 -> fp16 tile images with the fused RMS norm -------------------------------
-// out[m_tile][k_step][tn rows x 128 B] is exactly the shared-memory image of the activation tile of
-// one pipeline step (swizzled, K permuted), so the GEMM fetches it with one bulk copy.  Rows >= M are
-// zero.  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma (src/backends/cpu_ref/cpu_ref.cpp:139-156).
-__global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K, int tn, const float* __restrict__ gamma, float eps,
+// out[m64][k_step][64 rows x 128 B]: each 8 KB piece is exactly the shared-memory image of 64 token
+// rows of one pipeline step (swizzled, K permuted), so the GEMM fetches a token tile with tn / 64 bulk
+// copies whatever its tile size.  Rows >= M are zero (they only feed output columns nobody stores).  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma (src/backends/cpu_ref/cpu_ref.cpp:139-156).
+__global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K, const float* __restrict__ gamma, float eps,
                               __half* __restrict__ out) {
     __shared__ float red[32];
-    const int row = blockIdx.x, mt = row / tn, r = row - mt * tn;
+    const int row = blockIdx.x, mt = row >> 6, r = row & 63;
     const int n_steps = K / kBK;
-    uint8_t* tile0 = reinterpret_cast<uint8_t*>(out) + static_cast<size_t>(mt) * n_steps * tn * 128;
+    uint8_t* tile0 = reinterpret_cast<uint8_t*>(out) + static_cast<size_t>(mt) * n_steps * 8192;
     const bool live = row < M;
     const float* xr = x + static_cast<size_t>(live ? row : 0) * lda;
     float inv = 1.0f;
@@ -162,7 +165,7 @@ __global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K
                 p[2 * hv + 1] = *reinterpret_cast<const uint32_t*>(&b);
             }
         }
-        *reinterpret_cast<uint4*>(tile0 + static_cast<size_t>(ks) * tn * 128 + swz_off(r, c)) = make_uint4(p[0], p[1], p[2], p[3]);
+        *reinterpret_cast<uint4*>(tile0 + static_cast<size_t>(ks) * 8192 + swz_off(r, c)) = make_uint4(p[0], p[1], p[2], p[3]);
     }
 }
 
@@ -254,26 +257,33 @@ __device__ __forceinline__ uint4 generic_chunk(const PackedW& w, int64_t row, in
 // ---- the GEMM --------------------------------------------------------------------------------------
 // RT = weight tiles of 128 rows per CTA.  Non-dual: tile i covers rows n0 + 128 i of w.  Dual (RT == 2):
 // tile 0 = rows n0.. of w (gate), tile 1 = the same rows of w2 (up); the epilogue combines them.
-// Dynamic shared memory (1024-byte aligned): stages x { RT weight tiles of 16 KB, token tile tn x 128 B },
-// then the scale table RT x 128 rows x 64 B (Q4_K / Q6_K; each warp owns the rows it fills).
-// 16 dequant warps: warp w works on row group w % 8 (16 rows) of tile w / 8 (RT == 2) or on the
-// row half w / 8 of that group (RT == 1).  Warp 16 issues the MMAs, warp 17 the activation copies.
+// Dynamic shared memory (1024-byte aligned): stages x RT weight tiles of 16 KB, stages token tiles of tn x 128 B,
+// then the scale table 2 x 128 rows x 64 B (Q4_K / Q6_K; each warp owns the rows it fills).
+// 16 dequant warps, warp w on row group w % 8 (16 rows): with RT == 2 warp w fills tile w / 8 at every
+// step; with RT == 1 the warps form two sets (w / 8) that fill alternate steps, so that one set's
+// load / convert / fence / arrive chain overlaps the other's.  Warp 16 issues the MMAs, warp 17 the
+// activation copies.
 template <int FMT, int RT>
 __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t a_full[kMaxStagesG], b_full[kMaxStagesG], free_bar[kMaxStagesG], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kMaxStagesG], free_bar[kMaxStagesG], done_bar;
     __shared__ uint32_t tmem_base_s;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // One ring of S stages.  Stage s = weight tiles at smem + s * a_bytes and the token tile at
+    // smem_b + s * b_bytes.  full_bar[s] completes when the stage's dequant warps have arrived AND the
+    // activation copy's bytes have landed (one wait for the MMA thread); free_bar[s] by tcgen05.commit.
     const int S = a.stages;
     const int b_bytes = a.tn * 128;
-    const int stage_bytes = RT * 16384 + b_bytes;
-    uint32_t* table = reinterpret_cast<uint32_t*>(smem + static_cast<size_t>(S) * stage_bytes);      // [RT][128][16]
+    constexpr int a_bytes = RT * 16384;
+    constexpr int kFillWarps = RT == 2 ? kDequantWarps : kDequantWarps / 2;      // warps that fill one stage
+    uint8_t* smem_b = smem + static_cast<size_t>(S) * a_bytes;
+    uint32_t* table = reinterpret_cast<uint32_t*>(smem_b + static_cast<size_t>(S) * b_bytes);      // [2][128][16]
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * (a.dual ? 128 : 128 * RT);
     const int n_steps = a.K / kBK;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&a_full[s], kDequantWarps); mbar_init(&b_full[s], 1); mbar_init(&free_bar[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], kFillWarps + 1); mbar_init(&free_bar[s], 1); }
         mbar_init(&done_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -290,36 +300,47 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     if (warp == kDequantWarps + 1) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * n_steps * b_bytes;
+            const int subs = a.tn >> 6;           // 64-row pieces of the token tile
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * subs * n_steps * 8192;
             int s = 0; uint32_t par = 1;          // parity of the `free` phase that releases the stage (first round: none)
             for (int ks = 0; ks < n_steps; ++ks) {
                 if (ks >= S && ok) ok = mbar_wait(&free_bar[s], par, a.err);
-                mbar_expect_tx(&b_full[s], static_cast<uint32_t>(b_bytes));
-                bulk_g2s(smem + static_cast<size_t>(s) * stage_bytes + RT * 16384, src + static_cast<size_t>(ks) * b_bytes, static_cast<uint32_t>(b_bytes), &b_full[s]);
+                mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(b_bytes));
+                uint8_t* dst = smem_b + static_cast<size_t>(s) * b_bytes;
+                for (int i = 0; i < subs; ++i)
+                    bulk_g2s(dst + i * 8192, src + (static_cast<size_t>(i) * n_steps + ks) * 8192, 8192u, &full_bar[s]);
                 if (++s == S) { s = 0; par ^= 1; }
             }
         }
     } else if (warp == kDequantWarps) {
         // ---------------- MMA issuer ----------------
+        // This one thread's instruction chain paces the whole CTA (its warp shares a scheduler with
+        // dequant warps), so the loop is kept to one wait, the MMAs and one commit: descriptors are a
+        // constant high word and a low word that advances by a fixed amount per stage.
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(128, a.tn);
+            const uint64_t desc_hi = static_cast<uint64_t>(0x40004040u) << 32;       // stride 1024 B, version 1, 128-byte swizzle
+            const uint32_t a_lo0 = ((s_u32(smem) & 0x3FFFFu) >> 4) | 0x10000u, b_lo0 = ((s_u32(smem_b) & 0x3FFFFu) >> 4) | 0x10000u;
+            const uint32_t a_step = a_bytes >> 4, b_step = static_cast<uint32_t>(b_bytes) >> 4;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0, accumulate = 0u;
             int s = 0; uint32_t par = 0;
             for (int ks = 0; ks < n_steps; ++ks) {
-                if (ok) ok = mbar_wait(&a_full[s], par, a.err);
-                if (ok) ok = mbar_wait(&b_full[s], par, a.err);
+                const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && ks >= 8 && ks < 24;
+                ok = mbar_wait(&full_bar[s], par, a.err);
+                if (tr) g_tc_trace[4 * (ks - 8)] = gtime();
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t st = s_u32(smem + static_cast<size_t>(s) * stage_bytes);
-                const uint64_t db = umma_desc(st + RT * 16384);
 #pragma unroll
                 for (int i = 0; i < RT; ++i) {
-                    const uint64_t da = umma_desc(st + i * 16384);
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; ++kk)
-                        umma_f16(tmem_d + i * a.tn, da + 2 * kk, db + 2 * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);     // +32 bytes along K per instruction
+                    for (int kk = 0; kk < kBK / 16; ++kk)      // +32 bytes along K per instruction, +16 KB per weight tile
+                        umma_f16(tmem_d + i * a.tn, desc_hi | (a_lo + i * 1024 + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, (kk == 0) ? accumulate : 1u);
                 }
                 umma_commit(&free_bar[s]);
-                if (++s == S) { s = 0; par ^= 1; }
+                if (tr) g_tc_trace[4 * (ks - 8) + 2] = gtime();
+                accumulate = 1u;
+                a_lo += a_step; b_lo += b_step;
+                if (++s == S) { s = 0; par ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
             }
             if (ok) umma_commit(&done_bar);
         }
@@ -330,8 +351,9 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         // into the warp's own rows of the scale table.
         const int g = lane >> 2, t = lane & 3;
         const int grp_w = warp & 7;
-        const int tile = RT == 2 ? (warp >> 3) : 0;
-        const int hi_first = RT == 2 ? 0 : (warp >> 3), hi_count = RT == 2 ? 2 : 1;      // row halves (g, g + 8) this warp fills
+        const int set = warp >> 3;                       // RT == 2: weight tile; RT == 1: which alternate steps
+        const int tile = RT == 2 ? set : 0;
+        const int stride = RT == 2 ? 1 : 2, ks_first = RT == 2 ? 0 : set;
         const PackedW& w = (a.dual && tile == 1) ? a.w2 : a.w;
         const int64_t row0 = a.dual ? n0 : n0 + 128 * tile;
         const FormatInfo fi = format_info(a.w.type);
@@ -343,17 +365,16 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         const bool grp_live = grp < ((w.N + 15) >> 4);
         const uint8_t* q_base = nullptr;      // Q4_K: qs fragments; Q6_K: ql fragments; Q8_0: qs of this thread's row
         const uint8_t* q_base2 = nullptr;     // Q6_K: qh fragments; Q8_0: block scales
-        int q80_r = 0, q80_hh = 0, q80_part = 0;
+        int q80_r = 0, q80_hh = 0;
         bool q80_live = false;
         if (FMT == F_Q4K) q_base = w.s[1] + (grp * w.nb * 4 * 32 + lane) * 16;
         if (FMT == F_Q6K) { q_base = w.s[0] + (grp * w.nb * 4 * 32 + lane) * 16; q_base2 = w.s[1] + (grp * w.nb * 2 * 32 + lane) * 16; }
         if (FMT == F_Q80) {
             const int lt = tid & 255;
-            if (RT == 2) { q80_r = lt >> 1; q80_hh = lt & 1; }
-            else { q80_r = tid >> 2; q80_hh = (tid >> 1) & 1; q80_part = tid & 1; }
+            q80_r = lt >> 1; q80_hh = lt & 1;
             const int64_t row = row0 + q80_r;
             q80_live = row < w.N;
-            q_base = w.s[1] + (row * w.nb + q80_hh) * 32 + 8 * q80_part;
+            q_base = w.s[1] + (row * w.nb + q80_hh) * 32;
             q_base2 = w.s[0] + (row * w.nb + q80_hh) * 2;
         }
         auto load_frag = [&](int ks, Frag& f) {
@@ -371,20 +392,15 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             } else if (FMT == F_Q80) {
                 if (q80_live) {
                     const uint8_t* p = q_base + static_cast<size_t>(ks) * 64;
-                    if (RT == 2) {
-                        f.v[0] = __ldg(reinterpret_cast<const uint4*>(p));
-                        f.v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(p + 16));
-                    } else {
-                        const uint2 lo = __ldg(reinterpret_cast<const uint2*>(p)), hi = __ldg(reinterpret_cast<const uint2*>(p + 16));
-                        f.v[0].x = lo.x; f.v[0].y = lo.y; f.v[NQ - 1].x = hi.x; f.v[NQ - 1].y = hi.y;
-                    }
+                    f.v[0] = __ldg(reinterpret_cast<const uint4*>(p));
+                    f.v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(p + 16));
                     f.d = __ldg(reinterpret_cast<const unsigned short*>(q_base2 + static_cast<size_t>(ks) * 4));
                 }
             }
         };
         // K-quant header of this lane's table row (row r16 of the group), block b
-        const int hdr_lanes = RT == 2 ? 16 : 8;
-        const int r16 = RT == 2 ? (lane & 15) : 8 * hi_first + (lane & 7);
+        const int hdr_lanes = 16;
+        const int r16 = lane & 15;
         auto load_hdr = [&](int b) -> Hdr {
             Hdr h; h.v = make_uint4(0u, 0u, 0u, 0u); h.d = 0.0f;
             if ((FMT == F_Q4K || FMT == F_Q6K) && lane < hdr_lanes && b < w.nb && grp_live) {
@@ -394,18 +410,20 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             }
             return h;
         };
-        uint32_t* tb = table + tile * 128 * 16;
+        uint32_t* tb = table + set * 128 * 16;          // this warp set's own copy of the scale table
         uint8_t* stage_ptr = smem + tile * 16384;
-        int s_cur = 0; uint32_t par_free = 1;
+        int s_cur = ks_first; uint32_t par_free = 1;
         Frag f0, f1, f2;
         Hdr h0 = load_hdr(0), h1 = load_hdr(1);
-        load_frag(0, f0);
-        if (n_steps > 1) load_frag(1, f1);
-        // one pipeline step: fetch the fragments of step ks + 2 into `ahead`, fill stage s_cur from `cur`
+        if (ks_first < n_steps) load_frag(ks_first, f0);
+        if (ks_first + stride < n_steps) load_frag(ks_first + stride, f1);
+        // one pipeline step: fetch the fragments two of this warp's steps ahead into `ahead`, fill stage s_cur from `cur`
         auto step = [&](const int ks, const Frag& cur, Frag& ahead) {
-            uint8_t* At = stage_ptr + static_cast<size_t>(s_cur) * stage_bytes;
-            if (FMT != F_GEN && ks + 2 < n_steps) load_frag(ks + 2, ahead);
-            if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == 0) {
+            uint8_t* At = stage_ptr + static_cast<size_t>(s_cur) * a_bytes;
+            const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && ks >= 8 && ks < 24;
+            if (tr) g_tc_trace[64 + 4 * (ks - 8)] = gtime();
+            if (FMT != F_GEN && ks + 2 * stride < n_steps) load_frag(ks + 2 * stride, ahead);
+            if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == ks_first) {
                 // the previous block's readers are past their __syncwarp; expand this block's scales
                 if (lane < hdr_lanes) {
                     uint32_t* dst = tb + (grp_w * 16 + r16) * 16;
@@ -416,11 +434,10 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                 __syncwarp();
             }
             if (ks >= S && ok) ok = mbar_wait(&free_bar[s_cur], par_free, a.err);
+            if (tr) g_tc_trace[64 + 4 * (ks - 8) + 1] = gtime();
             if (FMT == F_Q4K || FMT == F_Q6K) {
 #pragma unroll
-                for (int hq = 0; hq < 2; ++hq) {
-                    if (hq >= hi_count) break;
-                    const int hi = hi_first + hq;                      // 0: row g, 1: row g + 8
+                for (int hi = 0; hi < 2; ++hi) {                       // 0: row g, 1: row g + 8
                     const int r = grp_w * 16 + g + 8 * hi;
                     const uint4 e = *reinterpret_cast<const uint4*>(tb + r * 16 + 4 * (ks & 3));
                     if (FMT == F_Q4K) {
@@ -441,16 +458,14 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             } else if (FMT == F_Q80) {
                 const uint4 lo = cur.v[0], hi4 = cur.v[NQ - 1];
                 const __half2 dd = __half2half2(__ushort_as_half(static_cast<unsigned short>(cur.d)));
-                const int c0 = 4 * q80_hh + 2 * q80_part;
+                const int c0 = 4 * q80_hh;
                 *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 0)) = q80_chunk(lo.x, hi4.x, dd);
                 *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 1)) = q80_chunk(lo.y, hi4.y, dd);
-                if (RT == 2) {
-                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = q80_chunk(lo.z, hi4.z, dd);
-                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = q80_chunk(lo.w, hi4.w, dd);
-                }
+                *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = q80_chunk(lo.z, hi4.z, dd);
+                *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = q80_chunk(lo.w, hi4.w, dd);
             } else {
-                uint8_t* As = smem + static_cast<size_t>(s_cur) * stage_bytes;
-                for (int it = tid; it < RT * 128 * 8; it += kDequantWarps * 32) {
+                uint8_t* As = smem + static_cast<size_t>(s_cur) * a_bytes;
+                for (int it = (RT == 2 ? tid : (tid & 255)); it < RT * 128 * 8; it += RT * 256) {
                     const int i = it >> 10, r = (it >> 3) & 127, c = it & 7;
                     *reinterpret_cast<uint4*>(As + i * 16384 + swz_off(r, c)) =
                         generic_chunk((a.dual && i == 1) ? a.w2 : a.w, (a.dual ? n0 : n0 + 128 * i) + r, ks * kBK, c, fi.block_elems);
@@ -458,13 +473,15 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&a_full[s_cur]);
-            if (++s_cur == S) { s_cur = 0; par_free ^= 1; }
+            if (lane == 0) mbar_arrive(&full_bar[s_cur]);
+            if (tr) g_tc_trace[64 + 4 * (ks - 8) + 2] = gtime();
+            s_cur += stride;
+            if (s_cur >= S) { s_cur -= S; par_free ^= 1; }
         };
-        for (int ks = 0; ks < n_steps; ks += 3) {
+        for (int ks = ks_first; ks < n_steps; ks += 3 * stride) {
             step(ks, f0, f2);
-            if (ks + 1 < n_steps) step(ks + 1, f1, f0);
-            if (ks + 2 < n_steps) step(ks + 2, f2, f1);
+            if (ks + stride < n_steps) step(ks + stride, f1, f0);
+            if (ks + 2 * stride < n_steps) step(ks + 2 * stride, f2, f1);
         }
         // ---------------- epilogue (the same 16 warps) ----------------
         if (ok) ok = mbar_wait(&done_bar, 0, a.err);
@@ -493,7 +510,12 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                         if (a.dual) r = __fdividef(r, 1.0f + __expf(-r)) * v2[i];
                         else if (a.epi == EPI_ADD_BIAS) r += __ldg(a.bias + n);
                         else if (a.epi == EPI_RESIDUAL) r += a.resid[o];
-                        a.y[o] = r;
+                        if (a.y_img) {
+                            // element (token tok, k = n) of an image with N / 64 steps; kl = 32 h + 16 hi + 4 t + i -> chunk 4 h + t, slot 4 hi + i
+                            const int kl = static_cast<int>(n & 63), ch = ((kl >> 5) << 2) | ((kl >> 2) & 3), sl = (((kl >> 4) & 1) << 2) | (kl & 3);
+                            uint8_t* img = reinterpret_cast<uint8_t*>(a.y_img) + ((static_cast<size_t>(tok >> 6) * (a.w.N >> 6)) + (n >> 6)) * 8192;
+                            *reinterpret_cast<__half*>(img + swz_off(tok & 63, ch) + 2 * sl) = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
+                        } else a.y[o] = r;
                     }
                 }
             }
@@ -543,12 +565,13 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     __half* d_xb = static_cast<__half*>(d_xb_v);
     const int K = g.w.K;
     const FormatInfo fi = format_info(g.w.type);
-    if (!fi.block_elems || K % kBK || g.M < 1 || !g.x || g.n_cat || g.attn_partial) return GGB_NOT_FOUND;
+    if (!fi.block_elems || K % kBK || g.M < 1 || (!g.x && !g.x_img) || g.n_cat || g.attn_partial) return GGB_NOT_FOUND;
+    if (g.y_img && (g.epi != EPI_SWIGLU || g.w.N % 64)) return GGB_NOT_FOUND;
     const bool dual = g.epi == EPI_SWIGLU;
     if (dual && g.w2.layout != g.w.layout) return GGB_NOT_FOUND;
     const int tn = tile_tokens(g);
     const int m_tiles = (g.M + tn - 1) / tn;
-    if (gemm_tc_xb_elems(g) > xb_elems) return GGB_NOT_FOUND;
+    if (!g.x_img && gemm_tc_xb_elems(g) > xb_elems) return GGB_NOT_FOUND;
 
     int fmt = F_GEN;
     if (!c->tc_generic) {
@@ -565,22 +588,38 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     }
     int cols = 32;
     while (cols < tn * rt) cols <<= 1;
-    const size_t stage_bytes = static_cast<size_t>(rt) * 16384 + static_cast<size_t>(tn) * 128;
-    const size_t table_bytes = static_cast<size_t>(rt) * 128 * 64;
+    const size_t a_stage = static_cast<size_t>(rt) * 16384, b_stage = static_cast<size_t>(tn) * 128;
+    const size_t table_bytes = static_cast<size_t>(2) * 128 * 64;      // one copy per weight tile (two tiles) or per warp set (one tile)
     const size_t budget = 227 * 1024 - 1024 - table_bytes - 2048;      // alignment slack, table, static barriers
-    const int stages = static_cast<int>(std::min<size_t>(kMaxStagesG, budget / stage_bytes));
+    // (a shallower weight ring with a deeper, separate token ring measured slower than one ring)
+    const int stages = static_cast<int>(std::min<size_t>(kMaxStagesG, budget / (a_stage + b_stage)));
     if (stages < 2) return GGB_NOT_FOUND;
-    const size_t smem = stages * stage_bytes + table_bytes + 1024;
+    const size_t smem = stages * (a_stage + b_stage) + table_bytes + 1024;
 
-    x_prep_kernel<<<m_tiles * tn, 256, 0, s>>>(g.x, g.lda, g.M, K, tn, g.gamma, g.eps, d_xb);
-    c->launches++;
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_status(c, e, "x_prep");
+    if (!g.x_img) {
+        x_prep_kernel<<<m_tiles * tn, 256, 0, s>>>(g.x, g.lda, g.M, K, g.gamma, g.eps, d_xb);
+        c->launches++;
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_status(c, e, "x_prep");
+    }
 
     GemmArgs a{};
-    a.w = g.w; a.w2 = g.w2; a.xb = d_xb; a.y = g.y; a.bias = g.bias; a.resid = g.resid;
+    a.w = g.w; a.w2 = g.w2; a.xb = g.x_img ? static_cast<const __half*>(g.x_img) : d_xb; a.y = g.y; a.y_img = static_cast<__half*>(g.y_img); a.bias = g.bias; a.resid = g.resid;
     a.M = g.M; a.K = K; a.ldc = g.ldc; a.epi = g.epi; a.dual = dual ? 1 : 0; a.tn = tn; a.tmem_cols = cols; a.stages = stages; a.err = c->d_err;
     dim3 grid(static_cast<unsigned>((g.w.N + (dual ? 128 : 128 * rt) - 1) / (dual ? 128 : 128 * rt)), static_cast<unsigned>(m_tiles));
+    static const bool trace = getenv("GGB_TC_TRACE") != nullptr;
+    a.trace = trace ? 1 : 0;
+    struct Dump { Context* c; cudaStream_t s; int sa, tn, rt; ~Dump() {
+        if (!trace) return;
+        unsigned long long t[128];
+        cudaStreamSynchronize(s);
+        if (cudaMemcpyFromSymbol(t, g_tc_trace, sizeof(t)) != cudaSuccess) return;
+        fprintf(stderr, "[tc trace] stages %d tn %d rt %d\n", sa, tn, rt);
+        for (int i = 0; i < 16; ++i)
+            fprintf(stderr, "[tc trace] step %2d mma: a_ready %6lld b_ready %6lld issued %6lld | warp0: start %6lld free %6lld arrived %6lld\n", i + 8,
+                    (long long)(t[4 * i] - t[0]), (long long)(t[4 * i + 1] - t[0]), (long long)(t[4 * i + 2] - t[0]),
+                    (long long)(t[64 + 4 * i] - t[0]), (long long)(t[64 + 4 * i + 1] - t[0]), (long long)(t[64 + 4 * i + 2] - t[0]));
+    } } dump{c, s, stages, tn, rt};
     switch (fmt * 2 + (rt - 1)) {
     case F_GEN * 2 + 0: return launch_one<F_GEN, 1>(c, a, grid, smem, s);
     case F_GEN * 2 + 1: return launch_one<F_GEN, 2>(c, a, grid, smem, s);

@@ -553,13 +553,13 @@ static int dispatch(Context* c, const GemvArgs& a, cudaStream_t s) {
 }
 
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
-    if ((!a.x && !a.attn_partial) || !a.y || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
+    if ((!a.x && !a.attn_partial && !a.x_img) || (!a.y && !a.y_img) || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
     if (a.attn_partial && (a.w.layout != 1 || a.M != 1)) return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input needs the tensor-core layout and M == 1");
     if (a.x && ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3))) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
     if (a.epi == EPI_SWIGLU && (a.w2.type != a.w.type || a.w2.N != a.w.N || a.w2.K != a.w.K))
         return set_status(c, GGB_INVALID_PARAM, "gemv: gate/up mismatch");
-    if (c->use_tc && a.M >= c->tc_min_m && a.x && !a.n_cat && !a.attn_partial) {
-        const size_t need = gemm_tc_xb_elems(a);
+    if (c->use_tc && a.M >= c->tc_min_m && (a.x || a.x_img) && !a.n_cat && !a.attn_partial) {
+        const size_t need = a.x_img ? 0 : gemm_tc_xb_elems(a);
         if (need > c->d_xb_elems) {
             cudaStreamSynchronize(s);
             if (c->d_xb) cudaFree(c->d_xb);
@@ -570,6 +570,7 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, s);
         if (st != GGB_NOT_FOUND) return st;
     }
+    if (a.x_img || a.y_img) return set_status(c, GGB_INVALID_PARAM, "gemv: tile-image operands need the tensor-core GEMM");
     if (a.w.layout == 1) {
         // tensor-core kernel, two activation rows per pass (each pass streams the weights once)
         int st = GGB_OK;

@@ -39,6 +39,11 @@ struct GemvArgs {
     float* cat_y[2] = {nullptr, nullptr};
     const float* cat_bias[2] = {nullptr, nullptr};
     int cat_ldc[2] = {0, 0};
+    // optional (tcgen05 GEMM, M >= tc_min_m): x_img = activations already in the fp16 tile-image form
+    // (x, gamma are then ignored); y_img (SwiGLU pair only) = write the result in that form, for a
+    // following GEMM whose K is this N, instead of fp32 y.  gemm_tc_image_elems gives the buffer size.
+    const void* x_img = nullptr;
+    void* y_img = nullptr;
 };
 
 struct DeviceWeight {
@@ -99,6 +104,7 @@ int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
 int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, cudaStream_t s);
 size_t gemm_tc_xb_elems(const GemvArgs& a);
+inline size_t gemm_tc_image_elems(int M, int K) { return static_cast<size_t>((M + 255) / 256) * 256 * K; }
 // tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
 inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
 

@@ -20,11 +20,16 @@ struct Layer {
     float *attn_norm = nullptr, *ffn_norm = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr, *q_norm = nullptr, *k_norm = nullptr;
 };
 
-constexpr int kMaxChunk = 256;   // prompt tokens per forward pass (the reference's kPrefillChunk, main.cpp:2326)
+// Prompt tokens per forward pass.  The reference chunks at 256 (main.cpp:2326); results do not depend
+// on the chunking.  With the tensor-core attention available a chunk is up to 2048 tokens (each GEMM
+// then dequantises its weights once per 2048 tokens); otherwise 256, which bounds the per-token
+// attention kernel's split scratch.
+constexpr int kSmallChunk = 256, kLargeChunk = 2048;
 
 }  // namespace
 
 struct ggb_model_s {
+    int chunk = kSmallChunk;
     Context* c = nullptr;
     ggb_model_desc d{};
     DeviceWeight *tok_embd = nullptr, *output = nullptr;
@@ -42,6 +47,8 @@ struct ggb_model_s {
     // activations
     float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
     float *partial = nullptr, *amax_partial = nullptr;
+    uint16_t* act_img = nullptr;         // SwiGLU output of a prompt chunk as the down projection's fp16 tile image
+    bool tc_images = false;              // prompt chunks pass activations between GEMMs as tile images
     int32_t *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *d_gen = nullptr, *d_step = nullptr;
     // pinned host staging
     int32_t* h_io = nullptr;             // [0]=token [1]=pos [2]=next
@@ -100,14 +107,19 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
             a.cat_w[1] = l.v->w; a.cat_y[1] = m->v; a.cat_bias[1] = l.bv; a.cat_ldc[1] = kvd;
             M_TRY(launch_gemv(c, a, s));
         } else {
+            // prompt chunk on the tensor-core GEMM: the q projection prepares the normalised fp16 tile
+            // image of x, the k and v projections read the same image
+            const bool img = m->tc_images && n_tok >= c->tc_min_m;
             M_TRY(launch_gemv(c, a, s));
             a = gemv_args(l.k, m->x, n_tok, H, m->k, kvd);
             a.gamma = l.attn_norm; a.eps = d.rms_eps;
             if (l.bk) { a.epi = EPI_ADD_BIAS; a.bias = l.bk; }
+            if (img) a.x_img = c->d_xb;
             M_TRY(launch_gemv(c, a, s));
             a = gemv_args(l.v, m->x, n_tok, H, m->v, kvd);
             a.gamma = l.attn_norm; a.eps = d.rms_eps;
             if (l.bv) { a.epi = EPI_ADD_BIAS; a.bias = l.bv; }
+            if (img) a.x_img = c->d_xb;
             M_TRY(launch_gemv(c, a, s));
         }
 
@@ -143,12 +155,16 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         }
         M_TRY(launch_gemv(c, a, s));
 
+        // prompt chunks: silu(gate) * up goes straight into the down projection's fp16 tile image
+        const bool act_as_image = m->tc_images && n_tok >= c->tc_min_m;
         a = gemv_args(l.gate, m->x, n_tok, H, m->act, F);
         a.w2 = l.up->w; a.epi = EPI_SWIGLU; a.gamma = l.ffn_norm; a.eps = d.rms_eps;
+        if (act_as_image) a.y_img = m->act_img;
         M_TRY(launch_gemv(c, a, s));
 
         a = gemv_args(l.down, m->act, n_tok, F, m->x, H);
         a.epi = EPI_RESIDUAL; a.resid = m->x;
+        if (act_as_image) a.x_img = m->act_img;
         M_TRY(launch_gemv(c, a, s));
     }
     // final norm fused into the logits GEMV; only the last row feeds sampling (main.cpp:3593-3598)
@@ -296,15 +312,19 @@ int ggb_model_finalize(ggb_model m) {
         M_TRY(dev_alloc(m, &m->block_table, bt.size()));
         M_TRY(cuda_status(c, cudaMemcpy(m->block_table, bt.data(), sizeof(int32_t) * bt.size(), cudaMemcpyHostToDevice), "block table"));
     }
-    const size_t T = kMaxChunk;
+    const bool tensor_attn = c->use_tc && c->tc_min_m <= kSmallChunk && m->page == 64 && (hd == 64 || hd == 128);
+    m->chunk = tensor_attn ? std::min(kLargeChunk, std::max(d.ctx, kSmallChunk)) : kSmallChunk;
+    const size_t T = m->chunk;
     M_TRY(dev_alloc(m, &m->x, T * d.hidden));
     M_TRY(dev_alloc(m, &m->q, T * qd));
     M_TRY(dev_alloc(m, &m->k, T * kvd));
     M_TRY(dev_alloc(m, &m->v, T * kvd));
     M_TRY(dev_alloc(m, &m->att, T * qd));
     M_TRY(dev_alloc(m, &m->act, T * d.ffn));
+    m->tc_images = tensor_attn && d.hidden % 64 == 0 && d.ffn % 64 == 0;
+    if (m->tc_images) M_TRY(dev_alloc(m, &m->act_img, gemm_tc_image_elems(m->chunk, d.ffn)));
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
-    M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kMaxChunk, d.n_head, m->n_splits, hd)));
+    M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd)));
     M_TRY(dev_alloc(m, &m->amax_partial, 512));
     M_TRY(dev_alloc(m, &m->d_tokens, T));
     M_TRY(dev_alloc(m, &m->d_pos, 1));
@@ -351,8 +371,8 @@ int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int po
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "prefill: model not finalized");
     if (!host_tokens || n_tok <= 0 || pos0 < 0 || pos0 + n_tok > m->d.ctx) return set_status(c, GGB_INVALID_PARAM, "prefill: bad arguments");
     GGB_LOCK(c);
-    for (int t0 = 0; t0 < n_tok; t0 += kMaxChunk) {
-        const int n = std::min(kMaxChunk, n_tok - t0);
+    for (int t0 = 0; t0 < n_tok; t0 += m->chunk) {
+        const int n = std::min(m->chunk, n_tok - t0);
         M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, host_tokens + t0, sizeof(int32_t) * n, cudaMemcpyHostToDevice, c->stream), "token upload"));
         M_TRY(enqueue_forward(m, n, false, pos0 + t0));
     }
