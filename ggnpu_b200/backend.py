@@ -87,7 +87,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device",
 ]
 
 _lib = None
@@ -128,6 +128,9 @@ def load_library() -> C.CDLL:
     L.ggb_gemv_swiglu_device.argtypes = [vp, vp, vp, vp, i32, i32, vp, i32, vp, f32]
     L.ggb_attn_paged_device.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_attn_prefill_device.argtypes = [vp, C.POINTER(AttnPagedParams), i32]
+    L.ggb_tp_unique_id.argtypes = [vp]
+    L.ggb_tp_init.argtypes = [vp, vp, i32, i32]
+    L.ggb_tp_all_reduce_device.argtypes = [vp, vp, i64]
     L.ggb_attn_paged_static.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_stream.argtypes = [vp]
     L.ggb_stream.restype = vp
@@ -286,6 +289,24 @@ class CudaBackend:
         p = AttnPagedParams(q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos)
         return Status(self.lib.ggb_attn_paged_static(self.h, C.byref(p)))
 
+    # ---- tensor-parallel group (one process per GPU, NCCL underneath) ----
+    tp_rank, tp_size = 0, 1
+
+    def tp_unique_id(self) -> bytes:
+        """Rank 0: the 128-byte id every rank passes to tp_init."""
+        buf = C.create_string_buffer(128)
+        self.check(self.lib.ggb_tp_unique_id(buf), "tp_unique_id")
+        return buf.raw
+
+    def tp_init(self, unique_id: bytes, rank: int, size: int) -> None:
+        """Collective: returns when all `size` ranks have joined."""
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        self.check(self.lib.ggb_tp_init(self.h, buf, rank, size), "tp_init")
+        self.tp_rank, self.tp_size = rank, size
+
+    def tp_all_reduce_device(self, d_buf: int, count: int) -> Status:
+        return Status(self.lib.ggb_tp_all_reduce_device(self.h, d_buf, count))
+
     def stream(self) -> int:
         return int(self.lib.ggb_stream(self.h) or 0)
 
@@ -309,6 +330,11 @@ class Model:
     def __init__(self, backend: CudaBackend, cfg, tensors: dict):
         self.b, self.cfg = backend, cfg
         L = backend.lib
+        if backend.tp_size > 1:          # this process holds one shard; `cfg` and `tensors` describe the full model
+            from . import tp
+            tensors = tp.shard_tensors(cfg, tensors, backend.tp_rank, backend.tp_size)
+            cfg = tp.shard_config(cfg, backend.tp_size)
+        self.cfg_local = cfg
         desc = ModelDesc(cfg.n_layer, cfg.hidden, cfg.n_head, cfg.n_kv, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.ctx,
                          cfg.rms_eps, float(np.float32(cfg.rope_base)), 1.0, 1 if cfg.arch == "qwen3" else 0, 0)
         m = C.c_void_p()
@@ -346,7 +372,7 @@ class Model:
         return out
 
     def read_kv(self, layer, pos, want_v):
-        out = np.empty((self.cfg.n_kv, self.cfg.head_dim), dtype=np.float32)
+        out = np.empty((self.cfg_local.n_kv, self.cfg_local.head_dim), dtype=np.float32)
         self.b.check(self.b.lib.ggb_model_read_kv(self.m, layer, pos, int(want_v), _ptr(out)), "read_kv")
         return out
 

@@ -49,7 +49,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, sources()))
-    cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-Xcompiler", "-fPIC"]
+    cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-Xcompiler", "-fPIC", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

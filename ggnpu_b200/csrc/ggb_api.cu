@@ -105,6 +105,7 @@ void ggb_destroy(ggb_handle h) {
     if (!h) return;
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->stream);
+    tp_destroy(h);
     for (auto& kv : h->weight_cache) free_weight(kv.second);
     for (int i = 0; i < 4; ++i) if (h->d_scratch[i]) cudaFree(h->d_scratch[i]);
     if (h->d_xb) cudaFree(h->d_xb);

@@ -30,6 +30,9 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kThreads = (kWarps + 1) * 32;
 constexpr int kMaxStages = 32;
+#ifndef GGB_MMA_MIN_BLOCKS
+#define GGB_MMA_MIN_BLOCKS 1
+#endif
 constexpr uint32_t kSpinLimit = 1u << 17;         // each poll can suspend for microseconds: about half a second in all
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -173,7 +176,7 @@ struct MmaArgs {
 //
 // dynamic shared memory map: [ring: 8 * P * stage_bytes][limb planes: 3*M * (K + 16) bytes]
 //   [asum: M * K/32 floats][xs: M * K/256 floats][comb: 2 * 8 * nmat * 16 * M floats]
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const MmaArgs a) {
+__global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_kernel(const MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ float red[2 * kWarps];

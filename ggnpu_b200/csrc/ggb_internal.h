@@ -81,6 +81,9 @@ struct Context {
     int tc_min_m = 32;
     bool tc_generic = false;  // tuning aid: every format through the generic (exact fp32 decode) tile filler
     int tc_rt = 0;            // tuning aid: force 1 or 2 weight tiles per CTA (0: heuristic)
+    // tensor-parallel group (ggb_tp.cu); tp_size == 1: none
+    void* tp_comm = nullptr;
+    int tp_rank = 0, tp_size = 1;
     void* d_xb = nullptr;     // fp16 activation tile images of the tcgen05 GEMM (grown on demand, never during graph capture)
     size_t d_xb_elems = 0;
 };
@@ -107,6 +110,11 @@ size_t gemm_tc_xb_elems(const GemvArgs& a);
 inline size_t gemm_tc_image_elems(int M, int K) { return static_cast<size_t>((M + 255) / 256) * 256 * K; }
 // tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
 inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
+
+// ggb_tp.cu: collectives over the handle's tensor-parallel group, on stream s (no-ops for a single rank)
+int tp_all_reduce(Context* c, float* d_buf, size_t count, cudaStream_t s);               // sum, in place
+int tp_all_gather_in_place(Context* c, float* d_recv, size_t count, cudaStream_t s);     // rank r's piece sits at d_recv + r * count
+void tp_destroy(Context* c);
 
 // ggb_ops.cu
 int launch_rms_norm(Context* c, const float* x, float* y, int rows, int n, float eps, const float* gamma, cudaStream_t s);

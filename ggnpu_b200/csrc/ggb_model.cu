@@ -147,13 +147,19 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         aa.skip_merge = merge_in_gemv ? 1 : 0;
         M_TRY(launch_attn_paged(c, aa, n_tok, s));
 
+        // Tensor parallel: attn_output and ffn_down are row parallel (this rank's K range), so their
+        // results are partial sums.  Rank 0 adds the residual stream, the other ranks overwrite their
+        // copy of it with the bare partial product, and the all-reduce leaves resid + sum on every rank.
+        const bool tp = c->tp_size > 1;
+        const int resid_epi = (!tp || c->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
         a = gemv_args(l.o, m->att, n_tok, qd, m->x, H);
-        a.epi = EPI_RESIDUAL; a.resid = m->x;
+        a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (merge_in_gemv) {
             a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = m->n_splits;
             a.attn_keys_per_split = m->pages_per_split * m->page; a.attn_hd = hd;
         }
         M_TRY(launch_gemv(c, a, s));
+        if (tp) M_TRY(tp_all_reduce(c, m->x, static_cast<size_t>(n_tok) * H, s));
 
         // prompt chunks: silu(gate) * up goes straight into the down projection's fp16 tile image
         const bool act_as_image = m->tc_images && n_tok >= c->tc_min_m;
@@ -163,14 +169,19 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         M_TRY(launch_gemv(c, a, s));
 
         a = gemv_args(l.down, m->act, n_tok, F, m->x, H);
-        a.epi = EPI_RESIDUAL; a.resid = m->x;
+        a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (act_as_image) a.x_img = m->act_img;
         M_TRY(launch_gemv(c, a, s));
+        if (tp) M_TRY(tp_all_reduce(c, m->x, static_cast<size_t>(n_tok) * H, s));
     }
     // final norm fused into the logits GEMV; only the last row feeds sampling (main.cpp:3593-3598)
-    GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H, m->logits, d.vocab);
+    // tensor parallel: each rank computes its slice of the vocabulary, then the slices are gathered
+    const int vocab_l = d.vocab / c->tp_size;
+    GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H,
+                           m->logits + static_cast<size_t>(c->tp_rank) * vocab_l, vocab_l);
     a.gamma = m->output_norm; a.eps = d.rms_eps;
     M_TRY(launch_gemv(c, a, s));
+    M_TRY(tp_all_gather_in_place(c, m->logits, static_cast<size_t>(vocab_l), s));
     M_TRY(launch_argmax(c, m->logits, d.vocab, m->d_next, m->amax_partial, s));
     return GGB_OK;
 }
@@ -236,7 +247,7 @@ int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_
     if (slot < 10) {
         switch (slot) {
         case GGB_T_TOKEN_EMBD: return mat(&m->tok_embd, d.vocab, d.hidden);
-        case GGB_T_OUTPUT: return mat(&m->output, d.vocab, d.hidden);
+        case GGB_T_OUTPUT: return mat(&m->output, d.vocab / c->tp_size, d.hidden);
         case GGB_T_OUTPUT_NORM: return vec(&m->output_norm, d.hidden);
         case GGB_T_ROPE_FREQS:
             if (type != GGB_F32 || N <= 0) return set_status(c, GGB_INVALID_PARAM, "set_tensor: rope_freqs must be F32");
@@ -273,6 +284,8 @@ int ggb_model_finalize(ggb_model m) {
     GGB_LOCK(c);
     const ggb_model_desc& d = m->d;
     if (!m->tok_embd || !m->output_norm) return set_status(c, GGB_INVALID_PARAM, "finalize: token_embd / output_norm missing");
+    if (c->tp_size > 1 && (!m->output || d.vocab % c->tp_size))
+        return set_status(c, GGB_INVALID_PARAM, "finalize: a tensor-parallel shard needs its slice of the output matrix (vocab divisible by the group size)");
     for (const Layer& l : m->layers) {
         if (!l.q || !l.k || !l.v || !l.o || !l.gate || !l.up || !l.down || !l.attn_norm || !l.ffn_norm)
             return set_status(c, GGB_INVALID_PARAM, "finalize: a layer tensor is missing");

@@ -237,6 +237,16 @@ GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */
 GGB_API uint64_t ggb_launch_count(ggb_handle h);
 
+/* ---- tensor parallel group (no counterpart in the reference, which drives one device) ----
+ * One process per GPU.  Rank 0 obtains a 128-byte id with ggb_tp_unique_id and hands it to the other
+ * ranks by any host channel; every rank then calls ggb_tp_init on its handle (a collective call: it
+ * returns when all `size` ranks have joined; NCCL over NVLink / NVSwitch underneath).  A model created
+ * on such a handle is one shard of a tensor-parallel model: see ggb_model_desc. */
+GGB_API int ggb_tp_unique_id(void* id128);
+GGB_API int ggb_tp_init(ggb_handle h, const void* id128, int rank, int size);
+/* Sum of d_buf[0..count) over the group, in place, asynchronous on the handle's stream. */
+GGB_API int ggb_tp_all_reduce_device(ggb_handle h, float* d_buf, int64_t count);
+
 /* ---- whole-model path (generic llama / qwen2 / qwen3 graph, src/cli/main.cpp:3235-3512) ---- */
 
 typedef struct ggb_model_desc {
@@ -245,6 +255,15 @@ typedef struct ggb_model_desc {
     int rope_neox;   /* 1: split-half pairs (qwen3); 0: adjacent pairs (llama, qwen2) */
     int kv_page;     /* tokens per KV page; 0 = default (64) */
 } ggb_model_desc;
+/* On a handle that belongs to a tensor-parallel group of `size` ranks the description and the tensors
+ * are those of ONE SHARD (Megatron-style): n_head, n_kv and ffn are the full model's divided by size;
+ * attn_q/k/v, ffn_gate/up and their biases hold this rank's rows (column parallel); attn_output and
+ * ffn_down hold this rank's K range of every row (row parallel, a whole number of quant blocks);
+ * GGB_T_OUTPUT holds rows [rank * vocab / size, (rank + 1) * vocab / size) of the output matrix and must
+ * be given explicitly (also for tied embeddings); token_embd, the norms, hidden, vocab and ctx are the
+ * full model's.  The library sums the partial results of attn_output and ffn_down over the group
+ * (all-reduce) and gathers the logits slices (all-gather), so every rank ends a step with the full
+ * logits and the same next token.  ggnpu_b200/tp.py cuts a full GGUF tensor set into such shards. */
 
 typedef struct ggb_model_s* ggb_model;
 

@@ -1,0 +1,90 @@
+"""One rank of the 2-GPU tensor-parallel test (spawned by test_gpu_tp.py).
+
+usage: python tests/tp_worker.py RANK SIZE PORT
+Each rank owns GPU RANK, joins the group, builds the same seeded tiny model, keeps its shard, runs a
+prefill and a few decode steps; rank 0 checks logits and tokens against the CPU oracle's full model."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, size, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200 import synth as S
+    from ggnpu_b200.backend import CudaBackend, Model
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=size)
+    b = CudaBackend(rank)
+    box = [b.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    b.tp_init(box[0], rank, size)
+
+    # the group sums: every rank contributes rank + 1
+    t = torch.full((1000,), float(rank + 1), device=f"cuda:{rank}")
+    assert int(b.tp_all_reduce_device(t.data_ptr(), t.numel())) == 0
+    b.sync()
+    assert torch.all(t == size * (size + 1) / 2)
+
+    worst = 0.0
+    for name, kw in {"llama_q4k_q6k": dict(seed=11, n_head=8, n_kv=2, ffn=1024),
+                     "qwen2_q8_0_bias": dict(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12, rope_base=1e6,
+                                             tied=False, n_head=8, n_kv=2, ffn=1024)}.items():
+        cfg = S.tiny_config(**kw)
+        synth = S.build_model(cfg)
+        gm = Model(b, cfg, synth.tensors)
+        ids = np.random.default_rng(42).integers(0, cfg.vocab, 40).astype(np.int32)     # >= 32: the tcgen05 GEMM path
+        got, nxt = gm.prefill(ids, 0)
+        steps = [(got.copy(), nxt)]
+        if rank == 0:
+            from oracle.binding import Oracle, OracleModel
+            oracle = Oracle()
+            om = OracleModel(oracle, synth)
+            want = om.forward(ids, 0)
+            tok = oracle.argmax_first(want)
+        else:
+            want, tok = None, None
+        # teacher forcing on the oracle's stream: rank 0 tells the others the token
+        box = [tok]
+        dist.broadcast_object_list(box, src=0)
+        tok, pos = box[0], len(ids)
+        wants = [want]
+        for _ in range(4):
+            got, nxt = gm.decode(tok, pos)
+            steps.append((got.copy(), nxt))
+            if rank == 0:
+                want = om.forward([tok], pos)
+                wants.append(want)
+                box = [oracle.argmax_first(want)]
+            dist.broadcast_object_list(box, src=0)
+            tok, pos = box[0], pos + 1
+        if rank == 0:
+            for (got, nxt), want in zip(steps, wants):
+                err = float(np.abs(got - want).max())
+                rng = float(want.max() - want.min())
+                assert err <= 0.15 and err <= 0.02 * rng, (name, err, rng)
+                worst = max(worst, err / rng)
+                srt = np.sort(want)
+                if srt[-1] - srt[-2] > 2 * err:
+                    assert nxt == oracle.argmax_first(want), name
+                assert nxt == int(np.argmax(got))
+        # every rank ends a step with the same full logits and token
+        mine = torch.from_numpy(np.concatenate([steps[-1][0], [float(steps[-1][1])]]))
+        both = [torch.empty_like(mine) for _ in range(size)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(both[0], x) for x in both[1:]), name
+        gm.close()
+    dist.barrier()
+    b.close()
+    dist.destroy_process_group()
+    print(f"TP_WORKER_OK rank {rank} worst_rel_err {worst:.2e}", flush=True)
+
+
+if __name__ == "__main__":
+    main()
