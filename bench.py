@@ -449,6 +449,86 @@ def run_micro(args):
     b.close()
 
 
+def run_tp(args):
+    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model (BASELINE config 4) over all ranks
+    of this launch (torchrun: one process per GPU; a single process is the TP = 1 point).  Strong
+    scaling: the model is fixed, each rank holds 1 / N of the heads, FFN rows and vocabulary.
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench.py --tp --gpus 8"""
+    import dataclasses
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200.backend import CudaBackend, Model
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = args.tp_ctx
+    cfg = dataclasses.replace(S.LLAMA_8B, ctx=ctx, n_layer=args.tp_layers or S.LLAMA_8B.n_layer)
+    b = CudaBackend(local)
+    if world > 1:
+        box = [b.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        b.tp_init(box[0], rank, world)
+    t0 = time.perf_counter()
+    synth = S.build_model(cfg, device="cuda")
+    model = Model(b, cfg, synth.tensors)
+    build_s = time.perf_counter() - t0
+    del synth
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    n_prompt = min(args.tp_prompt, ctx - args.steps - args.warmup - 1)
+    ids = prompt_ids(cfg, n_prompt)
+    model.prefill(ids, 0, want_logits=False)                      # untimed pass sizes the scratch
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    _, first = model.prefill(ids, 0, want_logits=False)
+    e1.record(stream)
+    barrier()
+    prefill_ms = e0.elapsed_time(e1)
+    K, W = args.steps, max(args.warmup, 3)
+    toks = model.generate(int(first), n_prompt, W)
+    barrier()
+    launches0 = b.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    toks = model.generate(int(toks[-1]), n_prompt + W, K)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = b.launch_count() - launches0
+    t = torch.tensor([ms, prefill_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, prefill_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        peak, peak_kind = peaks()
+        bytes_step = model.decode_bytes(n_prompt + W + K // 2)        # this rank's shard
+        print(json.dumps({
+            "metric": METRIC, "value": K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"llama-3-8b-shape Q4_K_M-style ({cfg.n_layer} layers), tensor parallel over {world} GPU(s), batch-1 greedy decode after a {n_prompt}-token prompt, ctx {ctx}",
+                       "parallelism": f"tp{world}", "collectives": "NCCL all-reduce after attn_output and ffn_down (16 KB at batch 1), all-gather of the logits slices",
+                       "l2": "each step streams this rank's weight shard (> 126 MB L2 up to tp8)"},
+            "gpu_launches": launches, "prefill": {"tokens": n_prompt, "tok_per_s": n_prompt / (prefill_ms * 1e-3)},
+            "decode_step": {"algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
+                            "frac_of_hbm_peak": bytes_step / (ms / K * 1e-3) / 1e9 / peak, "peak_source": peak_kind},
+            "model_build_s": build_s}), flush=True)
+    model.close()
+    b.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -458,6 +538,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=128, help="prompt tokens before the timed decode (128 = the benchmark config)")
     ap.add_argument("--prefill-long", type=int, default=2048, help="token count of the long-prompt prefill figure")
+    ap.add_argument("--tp", action="store_true", help="tensor-parallel benchmark of the 8B-shape model over the ranks of this launch")
+    ap.add_argument("--tp-ctx", type=int, default=4352)
+    ap.add_argument("--tp-prompt", type=int, default=4096)
+    ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
     ap.add_argument("--micro", action="store_true", help="quantised-matmul microbenchmark instead of the decode benchmark")
     ap.add_argument("--types", default="Q4_0,Q8_0,Q4_K,Q6_K,IQ4_XS")
     ap.add_argument("--shapes", default="2048x2048,8192x2048,2048x8192,8960x1536")
@@ -465,6 +549,9 @@ def main():
     ap.add_argument("--dual", action="store_true")
     ap.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
+    if args.tp:
+        run_tp(args)
+        return
     if args.micro:
         run_micro(args)
     elif args.impl == "reference":
