@@ -64,6 +64,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     atomicExch(err, 4);
     return false;
 }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(s_u32(dst)), "l"(src), "r"(bytes), "r"(s_u32(bar)) : "memory");
@@ -112,6 +114,8 @@ struct GemmArgs {
     int tn;                       // tokens per CTA tile (multiple of 64, <= 256)
     int tmem_cols;                // power of two >= accumulator columns, >= 32
     int stages;
+    int steps_per_split;          // K steps per CTA (= K / 64 without split-K)
+    float* ws;                    // split-K partial sums, nullptr without split-K
     int trace;
     __half* y_img;                // dual only: write silu(gate) * up as the fp16 tile image of the next GEMM (K = N) instead of y
     int* err;
@@ -129,6 +133,8 @@ __host__ __device__ __forceinline__ int perm_k(int c, int e) { return 32 * (c >>
 __global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K, const float* __restrict__ gamma, float eps,
                               __half* __restrict__ out) {
     __shared__ float red[32];
+    pdl_wait();          // x comes from the previous kernel; the image may still be read by the GEMM before it
+    pdl_trigger();       // the GEMM may start: its dequant warps need nothing from this kernel
     const int row = blockIdx.x, mt = row >> 6, r = row & 63;
     const int n_steps = K / kBK;
     uint8_t* tile0 = reinterpret_cast<uint8_t*>(out) + static_cast<size_t>(mt) * n_steps * 8192;
@@ -281,6 +287,8 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     uint32_t* table = reinterpret_cast<uint32_t*>(smem_b + static_cast<size_t>(S) * b_bytes);      // [2][128][16]
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * (a.dual ? 128 : 128 * RT);
     const int n_steps = a.K / kBK;
+    // split-K: this CTA covers K steps [kw0, kw1) (a multiple of 4 steps, so K-quant blocks stay whole)
+    const int kw0 = blockIdx.z * a.steps_per_split, kw1 = kw0 + a.steps_per_split;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], kFillWarps + 1); mbar_init(&free_bar[s], 1); }
@@ -303,8 +311,9 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             const int subs = a.tn >> 6;           // 64-row pieces of the token tile
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * subs * n_steps * 8192;
             int s = 0; uint32_t par = 1;          // parity of the `free` phase that releases the stage (first round: none)
-            for (int ks = 0; ks < n_steps; ++ks) {
-                if (ks >= S && ok) ok = mbar_wait(&free_bar[s], par, a.err);
+            pdl_wait();                           // the activation image is the predecessor's output
+            for (int ks = kw0; ks < kw1; ++ks) {
+                if (ks - kw0 >= S && ok) ok = mbar_wait(&free_bar[s], par, a.err);
                 mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(b_bytes));
                 uint8_t* dst = smem_b + static_cast<size_t>(s) * b_bytes;
                 for (int i = 0; i < subs; ++i)
@@ -324,7 +333,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             const uint32_t a_step = a_bytes >> 4, b_step = static_cast<uint32_t>(b_bytes) >> 4;
             uint32_t a_lo = a_lo0, b_lo = b_lo0, accumulate = 0u;
             int s = 0; uint32_t par = 0;
-            for (int ks = 0; ks < n_steps; ++ks) {
+            for (int ks = kw0; ks < kw1; ++ks) {
                 const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && ks >= 8 && ks < 24;
                 ok = mbar_wait(&full_bar[s], par, a.err);
                 if (tr) g_tc_trace[4 * (ks - 8)] = gtime();
@@ -344,6 +353,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             }
             if (ok) umma_commit(&done_bar);
         }
+        pdl_trigger();                            // main loop issued: the next kernel in the stream may be scheduled
     } else {
         // ---------------- dequant warps ----------------
         // Fragments are fetched two steps ahead into three register sets that rotate by name (DRAM
@@ -353,7 +363,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         const int grp_w = warp & 7;
         const int set = warp >> 3;                       // RT == 2: weight tile; RT == 1: which alternate steps
         const int tile = RT == 2 ? set : 0;
-        const int stride = RT == 2 ? 1 : 2, ks_first = RT == 2 ? 0 : set;
+        const int stride = RT == 2 ? 1 : 2, ks_first = RT == 2 ? 0 : set;      // ks_first: relative to kw0
         const PackedW& w = (a.dual && tile == 1) ? a.w2 : a.w;
         const int64_t row0 = a.dual ? n0 : n0 + 128 * tile;
         const FormatInfo fi = format_info(a.w.type);
@@ -414,15 +424,15 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         uint8_t* stage_ptr = smem + tile * 16384;
         int s_cur = ks_first; uint32_t par_free = 1;
         Frag f0, f1, f2;
-        Hdr h0 = load_hdr(0), h1 = load_hdr(1);
-        if (ks_first < n_steps) load_frag(ks_first, f0);
-        if (ks_first + stride < n_steps) load_frag(ks_first + stride, f1);
+        Hdr h0 = load_hdr(kw0 >> 2), h1 = load_hdr((kw0 >> 2) + 1);
+        if (kw0 + ks_first < kw1) load_frag(kw0 + ks_first, f0);
+        if (kw0 + ks_first + stride < kw1) load_frag(kw0 + ks_first + stride, f1);
         // one pipeline step: fetch the fragments two of this warp's steps ahead into `ahead`, fill stage s_cur from `cur`
         auto step = [&](const int ks, const Frag& cur, Frag& ahead) {
             uint8_t* At = stage_ptr + static_cast<size_t>(s_cur) * a_bytes;
             const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && ks >= 8 && ks < 24;
             if (tr) g_tc_trace[64 + 4 * (ks - 8)] = gtime();
-            if (FMT != F_GEN && ks + 2 * stride < n_steps) load_frag(ks + 2 * stride, ahead);
+            if (FMT != F_GEN && ks + 2 * stride < kw1) load_frag(ks + 2 * stride, ahead);
             if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == ks_first) {
                 // the previous block's readers are past their __syncwarp; expand this block's scales
                 if (lane < hdr_lanes) {
@@ -433,7 +443,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                 h1 = load_hdr((ks >> 2) + 2);
                 __syncwarp();
             }
-            if (ks >= S && ok) ok = mbar_wait(&free_bar[s_cur], par_free, a.err);
+            if (ks - kw0 >= S && ok) ok = mbar_wait(&free_bar[s_cur], par_free, a.err);
             if (tr) g_tc_trace[64 + 4 * (ks - 8) + 1] = gtime();
             if (FMT == F_Q4K || FMT == F_Q6K) {
 #pragma unroll
@@ -478,14 +488,16 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             s_cur += stride;
             if (s_cur >= S) { s_cur -= S; par_free ^= 1; }
         };
-        for (int ks = ks_first; ks < n_steps; ks += 3 * stride) {
+        for (int ks = kw0 + ks_first; ks < kw1; ks += 3 * stride) {
             step(ks, f0, f2);
-            if (ks + stride < n_steps) step(ks + stride, f1, f0);
-            if (ks + 2 * stride < n_steps) step(ks + 2 * stride, f2, f1);
+            if (ks + stride < kw1) step(ks + stride, f1, f0);
+            if (ks + 2 * stride < kw1) step(ks + 2 * stride, f2, f1);
         }
         // ---------------- epilogue (the same 16 warps) ----------------
+        pdl_trigger();
         if (ok) ok = mbar_wait(&done_bar, 0, a.err);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_wait();                               // first global write / residual read of this kernel
         if (ok) {
             const int q = warp & 3, part = warp >> 2;
             const int t0 = blockIdx.y * a.tn;
@@ -504,7 +516,13 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int tok = t0 + c0 + i;
-                    if (tok < a.M && n < a.w.N) {
+                    if (tok < a.M && n < a.w.N && a.ws) {
+                        // split-K: bare partial sums [split][gate | up][M][N]; splitk_reduce_kernel applies the epilogue
+                        const size_t plane = static_cast<size_t>(a.M) * a.w.N, o = static_cast<size_t>(tok) * a.w.N + n;
+                        float* wsz = a.ws + static_cast<size_t>(blockIdx.z) * plane * (a.dual ? 2 : 1);
+                        wsz[o] = v[i];
+                        if (a.dual) wsz[plane + o] = v2[i];
+                    } else if (tok < a.M && n < a.w.N) {
                         const size_t o = static_cast<size_t>(tok) * a.ldc + n;
                         float r = v[i];
                         if (a.dual) r = __fdividef(r, 1.0f + __expf(-r)) * v2[i];
@@ -528,6 +546,34 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     }
 }
 
+// Split-K tail: y = epilogue(sum over splits of the partial sums).  One thread per output element.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int64_t N, int dual, int epi,
+                                     const float* __restrict__ bias, const float* resid, float* y, int ldc, __half* y_img) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t plane = static_cast<size_t>(M) * N;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < plane; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int tok = static_cast<int>(i / N);
+        const int64_t n = static_cast<int64_t>(i - static_cast<size_t>(tok) * N);
+        float g = 0.0f, u = 0.0f;
+        for (int z = 0; z < splits; ++z) {
+            const float* p = ws + static_cast<size_t>(z) * plane * (dual ? 2 : 1);
+            g += p[i];
+            if (dual) u += p[plane + i];
+        }
+        const size_t o = static_cast<size_t>(tok) * ldc + n;
+        float r = g;
+        if (dual) r = __fdividef(g, 1.0f + __expf(-g)) * u;
+        else if (epi == EPI_ADD_BIAS) r += __ldg(bias + n);
+        else if (epi == EPI_RESIDUAL) r += resid[o];
+        if (y_img) {
+            const int kl = static_cast<int>(n & 63), ch = ((kl >> 5) << 2) | ((kl >> 2) & 3), sl = (((kl >> 4) & 1) << 2) | (kl & 3);
+            uint8_t* img = reinterpret_cast<uint8_t*>(y_img) + ((static_cast<size_t>(tok >> 6) * (N >> 6)) + (n >> 6)) * 8192;
+            *reinterpret_cast<__half*>(img + swz_off(tok & 63, ch) + 2 * sl) = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
+        } else y[o] = r;
+    }
+}
+
 template <int FMT, int RT>
 int launch_one(Context* c, const GemmArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
     static size_t allowed = 48 * 1024;
@@ -536,24 +582,40 @@ int launch_one(Context* c, const GemmArgs& a, dim3 grid, size_t smem, cudaStream
         if (e != cudaSuccess) return cuda_status(c, e, "gemm_tc attr");
         allowed = smem;
     }
-    gemm_tc_kernel<FMT, RT><<<grid, kThreadsG, smem, s>>>(a);
+    const cudaError_t e = launch_pdl(c, gemm_tc_kernel<FMT, RT>, grid, dim3(kThreadsG), smem, s, a);
     c->launches++;
-    return cuda_status(c, cudaGetLastError(), "gemm_tc launch");
+    return cuda_status(c, e != cudaSuccess ? e : cudaGetLastError(), "gemm_tc launch");
 }
 
-// tokens per CTA tile: a multiple of 64 (the epilogue reads column halves 32 at a time), at most 256.
-// The largest of 256 / 128 / 64 that still yields about one CTA per SM (every token tile repeats the
-// dequantisation of its weight rows, so bigger is cheaper when the grid is full anyway).
+// How many ways K is split when the (row tile x token tile) grid would leave most SMs idle: each CTA
+// then takes a K window that is a whole number of 256-blocks and writes bare partial sums; a small
+// kernel adds them and applies the epilogue.  1 = no split.
+int k_splits(const GemvArgs& g, int tn) {
+    const int64_t ctas = (g.w.N + 127) / 128 * ((g.M + tn - 1) / tn);
+    const int n_steps = g.w.K / kBK;
+    if (ctas >= 96 || n_steps % 4) return 1;
+    int best = 1;
+    for (int sp = 2; sp <= 16; ++sp)
+        if (n_steps % (4 * sp) == 0 && n_steps / sp >= 16 && ctas * sp <= 160) best = sp;
+    return best;
+}
+// tokens per CTA tile: a multiple of 64 (the epilogue reads the columns 16 at a time per warp), at most
+// 256.  The largest tile whose grid (with split-K) covers about one CTA per SM; every token tile repeats
+// the dequantisation of its weight rows, so bigger is cheaper.
 int tile_tokens(const GemvArgs& g) {
     const int cap = std::min(256, (g.M + 63) / 64 * 64);
     const int64_t row_tiles = (g.w.N + 127) / 128;
     for (int tn = 256; tn > 64; tn >>= 1)
-        if (tn <= cap && row_tiles * ((g.M + tn - 1) / tn) >= 118) return tn;
+        if (tn <= cap && row_tiles * ((g.M + tn - 1) / tn) * k_splits(g, tn) >= 96) return tn;
     return std::min(cap, 64);
 }
 
 }  // namespace
 
+size_t gemm_tc_ws_floats(const GemvArgs& g) {
+    const int sp = k_splits(g, tile_tokens(g));
+    return sp > 1 ? static_cast<size_t>(sp) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N : 0;
+}
 size_t gemm_tc_xb_elems(const GemvArgs& g) {
     const int tn = tile_tokens(g);
     return static_cast<size_t>((g.M + tn - 1) / tn) * tn * g.w.K;
@@ -561,7 +623,7 @@ size_t gemm_tc_xb_elems(const GemvArgs& g) {
 
 // Prefill GEMM.  Returns GGB_NOT_FOUND when the shape is not covered (caller falls back).
 // d_xb_v: scratch for the fp16 activation tile images, at least gemm_tc_xb_elems(g) elements.
-int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems, cudaStream_t s) {
+int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems, float* d_ws, size_t ws_floats, cudaStream_t s) {
     __half* d_xb = static_cast<__half*>(d_xb_v);
     const int K = g.w.K;
     const FormatInfo fi = format_info(g.w.type);
@@ -573,6 +635,9 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     const int m_tiles = (g.M + tn - 1) / tn;
     if (!g.x_img && gemm_tc_xb_elems(g) > xb_elems) return GGB_NOT_FOUND;
 
+    const int splits = k_splits(g, tn);
+    if (splits > 1 && gemm_tc_ws_floats(g) > ws_floats) return GGB_NOT_FOUND;
+
     int fmt = F_GEN;
     if (!c->tc_generic) {
         if (g.w.type == T_Q4_K && g.w.layout == 1) fmt = F_Q4K;
@@ -582,7 +647,7 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     // two weight tiles per CTA halve the activation traffic per flop; one tile doubles the CTA count
     int rt = 2;
     if (!dual) {
-        const int64_t ctas2 = (g.w.N + 255) / 256 * m_tiles;
+        const int64_t ctas2 = (g.w.N + 255) / 256 * m_tiles * splits;
         if (g.w.N <= 128 || ctas2 < (c->sm_count * 3) / 4) rt = 1;
         if (c->tc_rt == 1 || c->tc_rt == 2) rt = g.w.N <= 128 ? 1 : c->tc_rt;
     }
@@ -597,16 +662,17 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     const size_t smem = stages * (a_stage + b_stage) + table_bytes + 1024;
 
     if (!g.x_img) {
-        x_prep_kernel<<<m_tiles * tn, 256, 0, s>>>(g.x, g.lda, g.M, K, g.gamma, g.eps, d_xb);
+        cudaError_t e = launch_pdl(c, x_prep_kernel, dim3(m_tiles * tn), dim3(256), 0, s, g.x, g.lda, g.M, K, g.gamma, g.eps, d_xb);
         c->launches++;
-        const cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_status(c, e, "x_prep");
     }
 
     GemmArgs a{};
     a.w = g.w; a.w2 = g.w2; a.xb = g.x_img ? static_cast<const __half*>(g.x_img) : d_xb; a.y = g.y; a.y_img = static_cast<__half*>(g.y_img); a.bias = g.bias; a.resid = g.resid;
     a.M = g.M; a.K = K; a.ldc = g.ldc; a.epi = g.epi; a.dual = dual ? 1 : 0; a.tn = tn; a.tmem_cols = cols; a.stages = stages; a.err = c->d_err;
-    dim3 grid(static_cast<unsigned>((g.w.N + (dual ? 128 : 128 * rt) - 1) / (dual ? 128 : 128 * rt)), static_cast<unsigned>(m_tiles));
+    a.steps_per_split = K / kBK / splits; a.ws = splits > 1 ? d_ws : nullptr;
+    dim3 grid(static_cast<unsigned>((g.w.N + (dual ? 128 : 128 * rt) - 1) / (dual ? 128 : 128 * rt)), static_cast<unsigned>(m_tiles), static_cast<unsigned>(splits));
     static const bool trace = getenv("GGB_TC_TRACE") != nullptr;
     a.trace = trace ? 1 : 0;
     struct Dump { Context* c; cudaStream_t s; int sa, tn, rt; ~Dump() {
@@ -620,16 +686,23 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
                     (long long)(t[4 * i] - t[0]), (long long)(t[4 * i + 1] - t[0]), (long long)(t[4 * i + 2] - t[0]),
                     (long long)(t[64 + 4 * i] - t[0]), (long long)(t[64 + 4 * i + 1] - t[0]), (long long)(t[64 + 4 * i + 2] - t[0]));
     } } dump{c, s, stages, tn, rt};
+    int st;
     switch (fmt * 2 + (rt - 1)) {
-    case F_GEN * 2 + 0: return launch_one<F_GEN, 1>(c, a, grid, smem, s);
-    case F_GEN * 2 + 1: return launch_one<F_GEN, 2>(c, a, grid, smem, s);
-    case F_Q4K * 2 + 0: return launch_one<F_Q4K, 1>(c, a, grid, smem, s);
-    case F_Q4K * 2 + 1: return launch_one<F_Q4K, 2>(c, a, grid, smem, s);
-    case F_Q6K * 2 + 0: return launch_one<F_Q6K, 1>(c, a, grid, smem, s);
-    case F_Q6K * 2 + 1: return launch_one<F_Q6K, 2>(c, a, grid, smem, s);
-    case F_Q80 * 2 + 0: return launch_one<F_Q80, 1>(c, a, grid, smem, s);
-    default: return launch_one<F_Q80, 2>(c, a, grid, smem, s);
+    case F_GEN * 2 + 0: st = launch_one<F_GEN, 1>(c, a, grid, smem, s); break;
+    case F_GEN * 2 + 1: st = launch_one<F_GEN, 2>(c, a, grid, smem, s); break;
+    case F_Q4K * 2 + 0: st = launch_one<F_Q4K, 1>(c, a, grid, smem, s); break;
+    case F_Q4K * 2 + 1: st = launch_one<F_Q4K, 2>(c, a, grid, smem, s); break;
+    case F_Q6K * 2 + 0: st = launch_one<F_Q6K, 1>(c, a, grid, smem, s); break;
+    case F_Q6K * 2 + 1: st = launch_one<F_Q6K, 2>(c, a, grid, smem, s); break;
+    case F_Q80 * 2 + 0: st = launch_one<F_Q80, 1>(c, a, grid, smem, s); break;
+    default: st = launch_one<F_Q80, 2>(c, a, grid, smem, s); break;
     }
+    if (st != GGB_OK || splits == 1) return st;
+    const size_t elems = static_cast<size_t>(g.M) * g.w.N;
+    const cudaError_t e = launch_pdl(c, splitk_reduce_kernel, dim3(static_cast<unsigned>(std::min<size_t>((elems + 255) / 256, 148 * 8))), dim3(256), 0, s,
+                                     static_cast<const float*>(d_ws), splits, g.M, g.w.N, dual ? 1 : 0, g.epi, g.bias, g.resid, g.y, g.ldc, static_cast<__half*>(g.y_img));
+    c->launches++;
+    return cuda_status(c, e != cudaSuccess ? e : cudaGetLastError(), "gemm_tc split-K reduce");
 }
 
 }  // namespace ggb

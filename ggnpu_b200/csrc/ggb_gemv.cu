@@ -567,7 +567,15 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
             if (cuda_status(c, cudaMalloc(&c->d_xb, need * 2), "cudaMalloc(fp16 activations)") != GGB_OK) return c->last_status;
             c->d_xb_elems = need;
         }
-        const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, s);
+        const size_t need_ws = gemm_tc_ws_floats(a);
+        if (need_ws > c->d_ws_floats) {
+            cudaStreamSynchronize(s);
+            if (c->d_ws) cudaFree(c->d_ws);
+            c->d_ws = nullptr; c->d_ws_floats = 0;
+            if (cuda_status(c, cudaMalloc(&c->d_ws, need_ws * sizeof(float)), "cudaMalloc(split-K partial sums)") != GGB_OK) return c->last_status;
+            c->d_ws_floats = need_ws;
+        }
+        const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, c->d_ws, c->d_ws_floats, s);
         if (st != GGB_NOT_FOUND) return st;
     }
     if (a.x_img || a.y_img) return set_status(c, GGB_INVALID_PARAM, "gemv: tile-image operands need the tensor-core GEMM");

@@ -86,6 +86,8 @@ struct Context {
     int tp_rank = 0, tp_size = 1;
     void* d_xb = nullptr;     // fp16 activation tile images of the tcgen05 GEMM (grown on demand, never during graph capture)
     size_t d_xb_elems = 0;
+    float* d_ws = nullptr;    // split-K partial sums of the tcgen05 GEMM (grown on demand)
+    size_t d_ws_floats = 0;
 };
 
 int set_status(Context* c, int status, const char* msg);
@@ -105,8 +107,9 @@ int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT
 int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
-int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, cudaStream_t s);
+int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, float* d_ws, size_t ws_floats, cudaStream_t s);
 size_t gemm_tc_xb_elems(const GemvArgs& a);
+size_t gemm_tc_ws_floats(const GemvArgs& a);       // split-K partial sums (0: no split)
 inline size_t gemm_tc_image_elems(int M, int K) { return static_cast<size_t>((M + 255) / 256) * 256 * K; }
 // tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
 inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
@@ -115,6 +118,21 @@ inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_tra
 int tp_all_reduce(Context* c, float* d_buf, size_t count, cudaStream_t s);               // sum, in place
 int tp_all_gather_in_place(Context* c, float* d_recv, size_t count, cudaStream_t s);     // rank r's piece sits at d_recv + r * count
 void tp_destroy(Context* c);
+
+// Launch with programmatic dependent launch (when enabled on the context): the kernel may begin while its
+// predecessor in the stream drains, and must execute griddepcontrol.wait before it touches anything
+// an earlier kernel wrote or still reads.
+template <class... KArgs, class... Args>
+static inline cudaError_t launch_pdl(Context* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 
 // ggb_ops.cu
 int launch_rms_norm(Context* c, const float* x, float* y, int rows, int n, float eps, const float* gamma, cudaStream_t s);

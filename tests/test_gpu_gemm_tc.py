@@ -101,9 +101,11 @@ def test_benchmark_shapes_sampled_rows(backend, oracle):
         check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
 
 
-def test_fused_epilogues(backend, oracle):
-    """RMSNorm prologue, bias, residual (aliasing y) and the SwiGLU pair at M = 70 on device pointers."""
-    t, N, K, M = S.Q4_K, 192, 512, 70
+@pytest.mark.parametrize("K", [512, 2048])
+def test_fused_epilogues(backend, oracle, K):
+    """RMSNorm prologue, bias, residual (aliasing y) and the SwiGLU pair at M = 70 on device pointers.
+    K = 2048 with so few output tiles runs split-K: partial sums, then the epilogue in the reduce kernel."""
+    t, N, M = S.Q4_K, 192, 70
     wg, wu = make(t, N, K, 1), make(t, N, K, 2)
     rng = np.random.default_rng(5)
     x = rng.standard_normal((M, K)).astype(np.float32)
