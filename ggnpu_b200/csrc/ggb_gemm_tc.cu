@@ -123,21 +123,28 @@ struct GemmArgs {
 
 // byte offset of 16-byte chunk c (0..7) of row r inside a K-major 128-byte-swizzled tile
 __host__ __device__ __forceinline__ uint32_t swz_off(int r, int c) { return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(c ^ (r & 7)) << 4); }
+// Byte offset, inside an activation image with n_steps K steps, of the 8 KB piece that holds the 64 tokens
+// starting at `tok` (a multiple of 64) of K step ks: [256-token block][K step][4 pieces of 64 tokens], so
+// that a token tile of 64 / 128 / 256 tokens (aligned to its size) is one contiguous range per K step.
+__host__ __device__ __forceinline__ size_t img_piece(int tok, int ks, int n_steps) {
+    return ((static_cast<size_t>(tok >> 8) * n_steps + ks) * 4 + ((tok >> 6) & 3)) * 8192;
+}
 // element of a 64-wide K step held by slot e (0..7) of chunk c (0..7)
 __host__ __device__ __forceinline__ int perm_k(int c, int e) { return 32 * (c >> 2) + 16 * (e >> 2) + 4 * (c & 3) + (e & 3); }
 
 // ---- activations: fp32 -> fp16 tile images with the fused RMS norm -------------------------------
-// out[m64][k_step][64 rows x 128 B]: each 8 KB piece is exactly the shared-memory image of 64 token
-// rows of one pipeline step (swizzled, K permuted), so the GEMM fetches a token tile with tn / 64 bulk
-// copies whatever its tile size.  Rows >= M are zero (they only feed output columns nobody stores).  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma (src/backends/cpu_ref/cpu_ref.cpp:139-156).
+// out[256-token block][k_step][4 x (64 rows x 128 B)]: each 8 KB piece is exactly the shared-memory image
+// of 64 token rows of one pipeline step (swizzled, K permuted), and the pieces of a token tile of 64,
+// 128 or 256 tokens are adjacent, so the GEMM fetches its tile with one bulk copy whatever the tile
+// size.  Rows >= M are zero (they only feed output columns nobody stores).  v = sum(x^2)/K + eps, y = x * (1/sqrt(v)) * gamma (src/backends/cpu_ref/cpu_ref.cpp:139-156).
 __global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K, const float* __restrict__ gamma, float eps,
                               __half* __restrict__ out) {
     __shared__ float red[32];
     pdl_wait();          // x comes from the previous kernel; the image may still be read by the GEMM before it
     pdl_trigger();       // the GEMM may start: its dequant warps need nothing from this kernel
-    const int row = blockIdx.x, mt = row >> 6, r = row & 63;
+    const int row = blockIdx.x, r = row & 63;
     const int n_steps = K / kBK;
-    uint8_t* tile0 = reinterpret_cast<uint8_t*>(out) + static_cast<size_t>(mt) * n_steps * 8192;
+    uint8_t* img = reinterpret_cast<uint8_t*>(out);
     const bool live = row < M;
     const float* xr = x + static_cast<size_t>(live ? row : 0) * lda;
     float inv = 1.0f;
@@ -171,7 +178,7 @@ __global__ void x_prep_kernel(const float* __restrict__ x, int lda, int M, int K
                 p[2 * hv + 1] = *reinterpret_cast<const uint32_t*>(&b);
             }
         }
-        *reinterpret_cast<uint4*>(tile0 + static_cast<size_t>(ks) * 8192 + swz_off(r, c)) = make_uint4(p[0], p[1], p[2], p[3]);
+        *reinterpret_cast<uint4*>(img + img_piece(row & ~63, ks, n_steps) + swz_off(r, c)) = make_uint4(p[0], p[1], p[2], p[3]);
     }
 }
 
@@ -308,16 +315,14 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
     if (warp == kDequantWarps + 1) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
-            const int subs = a.tn >> 6;           // 64-row pieces of the token tile
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb) + static_cast<size_t>(blockIdx.y) * subs * n_steps * 8192;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.xb);
+            const int tok0 = blockIdx.y * a.tn;
             int s = 0; uint32_t par = 1;          // parity of the `free` phase that releases the stage (first round: none)
             pdl_wait();                           // the activation image is the predecessor's output
             for (int ks = kw0; ks < kw1; ++ks) {
                 if (ks - kw0 >= S && ok) ok = mbar_wait(&free_bar[s], par, a.err);
                 mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(b_bytes));
-                uint8_t* dst = smem_b + static_cast<size_t>(s) * b_bytes;
-                for (int i = 0; i < subs; ++i)
-                    bulk_g2s(dst + i * 8192, src + (static_cast<size_t>(i) * n_steps + ks) * 8192, 8192u, &full_bar[s]);
+                bulk_g2s(smem_b + static_cast<size_t>(s) * b_bytes, src + img_piece(tok0, ks, n_steps), static_cast<uint32_t>(b_bytes), &full_bar[s]);
                 if (++s == S) { s = 0; par ^= 1; }
             }
         }
@@ -531,7 +536,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                         if (a.y_img) {
                             // element (token tok, k = n) of an image with N / 64 steps; kl = 32 h + 16 hi + 4 t + i -> chunk 4 h + t, slot 4 hi + i
                             const int kl = static_cast<int>(n & 63), ch = ((kl >> 5) << 2) | ((kl >> 2) & 3), sl = (((kl >> 4) & 1) << 2) | (kl & 3);
-                            uint8_t* img = reinterpret_cast<uint8_t*>(a.y_img) + ((static_cast<size_t>(tok >> 6) * (a.w.N >> 6)) + (n >> 6)) * 8192;
+                            uint8_t* img = reinterpret_cast<uint8_t*>(a.y_img) + img_piece(tok & ~63, static_cast<int>(n >> 6), static_cast<int>(a.w.N >> 6));
                             *reinterpret_cast<__half*>(img + swz_off(tok & 63, ch) + 2 * sl) = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
                         } else a.y[o] = r;
                     }
@@ -568,7 +573,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, i
         else if (epi == EPI_RESIDUAL) r += resid[o];
         if (y_img) {
             const int kl = static_cast<int>(n & 63), ch = ((kl >> 5) << 2) | ((kl >> 2) & 3), sl = (((kl >> 4) & 1) << 2) | (kl & 3);
-            uint8_t* img = reinterpret_cast<uint8_t*>(y_img) + ((static_cast<size_t>(tok >> 6) * (N >> 6)) + (n >> 6)) * 8192;
+            uint8_t* img = reinterpret_cast<uint8_t*>(y_img) + img_piece(tok & ~63, static_cast<int>(n >> 6), static_cast<int>(N >> 6));
             *reinterpret_cast<__half*>(img + swz_off(tok & 63, ch) + 2 * sl) = __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
         } else y[o] = r;
     }
@@ -616,10 +621,7 @@ size_t gemm_tc_ws_floats(const GemvArgs& g) {
     const int sp = k_splits(g, tile_tokens(g));
     return sp > 1 ? static_cast<size_t>(sp) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N : 0;
 }
-size_t gemm_tc_xb_elems(const GemvArgs& g) {
-    const int tn = tile_tokens(g);
-    return static_cast<size_t>((g.M + tn - 1) / tn) * tn * g.w.K;
-}
+size_t gemm_tc_xb_elems(const GemvArgs& g) { return static_cast<size_t>((g.M + 255) / 256) * 256 * g.w.K; }
 
 // Prefill GEMM.  Returns GGB_NOT_FOUND when the shape is not covered (caller falls back).
 // d_xb_v: scratch for the fp16 activation tile images, at least gemm_tc_xb_elems(g) elements.
