@@ -74,6 +74,14 @@ class AttnPagedParams(C.Structure):
                 ("n_pages", C.c_int), ("pos", C.c_int)]
 
 
+class MoeParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("resid", C.c_void_p), ("y", C.c_void_p), ("router", C.c_void_p),
+                ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
+                ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p), ("sh_gate_inp", C.c_void_p),
+                ("hidden", C.c_int), ("eff", C.c_int), ("eff_sh", C.c_int), ("n_expert", C.c_int), ("top_k", C.c_int),
+                ("sel_out", C.c_void_p), ("w_out", C.c_void_p)]
+
+
 class ModelDesc(C.Structure):
     _fields_ = [("n_layer", C.c_int), ("hidden", C.c_int), ("n_head", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
                 ("ffn", C.c_int), ("vocab", C.c_int), ("ctx", C.c_int), ("rms_eps", C.c_float), ("rope_base", C.c_float),
@@ -87,7 +95,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_moe_ffn_device",
 ]
 
 _lib = None
@@ -128,6 +136,7 @@ def load_library() -> C.CDLL:
     L.ggb_gemv_swiglu_device.argtypes = [vp, vp, vp, vp, i32, i32, vp, i32, vp, f32]
     L.ggb_attn_paged_device.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_attn_prefill_device.argtypes = [vp, C.POINTER(AttnPagedParams), i32]
+    L.ggb_moe_ffn_device.argtypes = [vp, C.POINTER(MoeParams)]
     L.ggb_tp_unique_id.argtypes = [vp]
     L.ggb_tp_init.argtypes = [vp, vp, i32, i32]
     L.ggb_tp_all_reduce_device.argtypes = [vp, vp, i64]
@@ -288,6 +297,11 @@ class CudaBackend:
         """attn_paged_device without any device allocation (fixed scratch inside the library)."""
         p = AttnPagedParams(q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos)
         return Status(self.lib.ggb_attn_paged_static(self.h, C.byref(p)))
+
+    def moe_ffn_device(self, **kw) -> Status:
+        """Mixture-of-experts FFN of one token; keyword arguments are the fields of ggb_moe_params (device pointers / weights)."""
+        p = MoeParams(**{k: (v if v is not None else None) for k, v in kw.items()})
+        return Status(self.lib.ggb_moe_ffn_device(self.h, C.byref(p)))
 
     # ---- tensor-parallel group (one process per GPU, NCCL underneath) ----
     tp_rank, tp_size = 0, 1

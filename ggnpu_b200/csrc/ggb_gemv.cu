@@ -593,7 +593,8 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         }
         if (st != GGB_NOT_FOUND) return st;
     }
-    if (a.n_cat || a.attn_partial) return set_status(c, GGB_INVALID_PARAM, "gemv: stacked matrices / attention-merge input need the tensor-core kernel");
+    if (a.n_cat || a.attn_partial || a.sel || a.xscale)
+        return set_status(c, GGB_INVALID_PARAM, "gemv: stacked matrices, attention-merge input, routed experts and scaled activations need the tensor-core kernel (Q4_K / Q6_K)");
     if (c->use_tma && a.M == 1) {
         const int st = launch_gemv_tma(c, a, s);
         if (st != GGB_NOT_FOUND) return st;

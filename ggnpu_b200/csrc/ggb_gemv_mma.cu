@@ -162,6 +162,14 @@ struct MmaArgs {
     int ws;            // consumer warps that share one row group (1, 2, 4 or 8)
     int P;             // ring stages per consumer warp
     int stage_bytes;
+    // routed experts (MoE): the weight holds all experts stacked along N, `sel` (device) names the chosen ones
+    const int* sel;    // nullptr: none
+    int sel_mode;      // 1: output rows = the chosen experts' row ranges (gate / up);  2: K = the chosen experts' K ranges side by side (down)
+    int sel_groups;    // row groups of one expert's matrix
+    int klog, nblog;   // logical K and blocks per row the kernel iterates over (mode 2: n_sel * the expert's)
+    int64_t nlog;      // logical number of output rows
+    const float* xscale;   // optional: x[i] is multiplied by xscale[i / xscale_run] (router weights folded into the activations)
+    int xscale_run;
     int* err;
     unsigned long long* trace;   // optional time stamps of CTA 0
 };
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ float red[2 * kWarps];
     __shared__ int x_ready;        // consumer warps that have pulled their part of x into registers
-    const int K = a.w.K, nb = a.w.nb, M = a.M;
+    const int K = a.klog, nb = a.nblog, M = a.M;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tprg = a.nmat * a.spr;
     const int plane_stride = K + 16;
@@ -218,11 +226,16 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
             // Only the first stage of each ring is requested before the activations are in: a full
             // ring of weight traffic queued ahead of the x loads would delay them by microseconds.
             bool throttled = true;
+            if (a.sel) pdl_wait();                 // the expert ids are the predecessor's output
             for (int rg = team; rg < n_rg && ok; rg += n_teams) {
                 const int mi = which(g_begin + rg);
                 const PackedW& w0 = mi == 0 ? a.w : a.cat[mi - 1].w;
                 const bool is_q6 = w0.type == T_Q6_K;
-                const int64_t blk0 = (g_begin + rg - (mi == 0 ? 0 : a.cat[mi - 1].g_start)) * nb;
+                int64_t blk0 = (g_begin + rg - (mi == 0 ? 0 : a.cat[mi - 1].g_start)) * nb;
+                if (a.sel_mode == 1) {             // gathered rows: logical group -> (chosen expert, group inside it)
+                    const int64_t lg = g_begin + rg;
+                    blk0 = (static_cast<int64_t>(a.sel[lg / a.sel_groups]) * a.sel_groups + lg % a.sel_groups) * a.w.nb;
+                }
                 for (int ti = member; ti < tprg; ti += a.ws) {
                     const int s = lane * a.P + st;
                     if (throttled && (rg != team || ti != member)) {
@@ -236,7 +249,9 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
                     const int b0 = sl * a.sb, nbk = min(a.sb, nb - b0);
                     uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
                     const PackedW& w = mat ? a.w2 : w0;
-                    const int64_t gb = blk0 + b0;
+                    int64_t gb = blk0 + b0;
+                    if (a.sel_mode == 2)           // K ranges side by side: tile sl = all a.w.nb blocks of chosen expert sl, same row group
+                        gb = (static_cast<int64_t>(a.sel[sl]) * a.sel_groups + (g_begin + rg)) * a.w.nb;
                     if (!is_q6) {
                         mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 2304u);
                         bulk_g2s(dst, w.s[1] + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, &full_bar[s]);
@@ -287,6 +302,11 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
                     else {
                         const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr + k0)), p1 = __ldg(reinterpret_cast<const float4*>(xr + k0 + 4));
                         v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+                    }
+                    if (a.xscale) {
+                        const float sc = a.xscale[k0 / a.xscale_run];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[u][i] *= sc;
                     }
                     if (a.gamma) {
                         const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4));
@@ -527,7 +547,7 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
                 va[mat][m] = pa * inv[m]; vb[mat][m] = pb * inv[m];
             }
         const int64_t row_base = (g_begin + rg - (mi == 0 ? 0 : a.cat[mi - 1].g_start)) * 16;
-        const int64_t n_rows = mi == 0 ? a.w.N : a.cat[mi - 1].w.N;
+        const int64_t n_rows = mi == 0 ? a.nlog : a.cat[mi - 1].w.N;
         float* const yb = mi == 0 ? a.y : a.cat[mi - 1].y;
         const float* const bb = mi == 0 ? a.bias : a.cat[mi - 1].bias;
         const int ldc = mi == 0 ? a.ldc : a.cat[mi - 1].ldc;
@@ -580,8 +600,12 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
     if (g.attn_partial && (g.M != 1 || g.attn_hd % 8 || g.attn_hd <= 0)) return GGB_NOT_FOUND;
     const bool dual = g.epi == EPI_SWIGLU;
     if (dual && (g.w2.layout != 1 || g.w2.type != g.w.type)) return GGB_NOT_FOUND;
-    const int K = g.w.K, nb = g.w.nb, M = g.M;
-    int groups = static_cast<int>((g.w.N + 15) / 16);
+    if (g.sel && (g.n_cat || g.attn_partial || g.sel_count < 1 || g.sel_rows < 16 || g.sel_rows % 16 || (g.sel_mode != 1 && g.sel_mode != 2))) return GGB_NOT_FOUND;
+    if (g.sel && g.sel_mode == 2 && (dual || g.w.nb > 8)) return GGB_NOT_FOUND;
+    // logical shape: with routed experts the kernel sees the chosen experts' rows (mode 1) or K ranges (mode 2)
+    const int K = g.sel && g.sel_mode == 2 ? g.sel_count * g.w.K : g.w.K, nb = g.sel && g.sel_mode == 2 ? g.sel_count * g.w.nb : g.w.nb, M = g.M;
+    const int64_t n_log = !g.sel ? g.w.N : (g.sel_mode == 1 ? static_cast<int64_t>(g.sel_count) * g.sel_rows : g.sel_rows);
+    int groups = static_cast<int>((n_log + 15) / 16);
     bool any_q6 = g.w.type == T_Q6_K;
     if (g.n_cat < 0 || g.n_cat > 2 || (g.n_cat && dual)) return GGB_NOT_FOUND;
     int cat_start[2] = {0, 0};
@@ -603,6 +627,7 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
     int sb = 4;
     while (sb > 1 && nmat * ((nb + sb - 1) / sb) < ws) sb >>= 1;
     sb = std::min(sb, nb);
+    if (g.sel && g.sel_mode == 2) sb = g.w.nb;            // one tile = one chosen expert's blocks of the row group
     const int spr = (nb + sb - 1) / sb;
     const int stage_bytes = sb * gb_bytes;
     const size_t fixed = static_cast<size_t>(3 * M) * (K + 16) + sizeof(float) * M * (K / 32 + K / 16 + K / 256) + sizeof(float) * 2 * kWarps * 2 * 32 + 64;
@@ -625,6 +650,8 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
     a.attn.partial = g.attn_partial; a.attn.d_pos = g.attn_d_pos; a.attn.pos0 = g.attn_pos0; a.attn.n_splits = g.attn_n_splits;
     a.attn.keys_per_split = g.attn_keys_per_split; a.attn.hd = g.attn_hd;
     a.sb = sb; a.spr = spr; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
+    a.sel = g.sel; a.sel_mode = g.sel ? g.sel_mode : 0; a.sel_groups = g.sel ? g.sel_rows / 16 : 0;
+    a.klog = K; a.nblog = nb; a.nlog = n_log; a.xscale = g.xscale; a.xscale_run = g.xscale_run > 0 ? g.xscale_run : 1;
     a.err = c->d_err;
     a.trace = trace_slot(c);
 

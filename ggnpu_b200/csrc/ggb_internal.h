@@ -39,6 +39,14 @@ struct GemvArgs {
     float* cat_y[2] = {nullptr, nullptr};
     const float* cat_bias[2] = {nullptr, nullptr};
     int cat_ldc[2] = {0, 0};
+    // optional (tensor-core GEMV, Q4_K / Q6_K): routed experts.  w (and w2) hold all experts stacked along N
+    // ([n_expert * sel_rows][K]); sel (device, sel_count ids) names the chosen ones.  sel_mode 1: the output
+    // is the chosen experts' rows one after the other (gate / up);  sel_mode 2: K is the chosen experts' K
+    // ranges side by side, x has sel_count * K values (down).  xscale multiplies x in runs of xscale_run.
+    const int* sel = nullptr;
+    int sel_mode = 0, sel_count = 0, sel_rows = 0;
+    const float* xscale = nullptr;
+    int xscale_run = 0;
     // optional (tcgen05 GEMM, M >= tc_min_m): x_img = activations already in the fp16 tile-image form
     // (x, gamma are then ignored); y_img (SwiGLU pair only) = write the result in that form, for a
     // following GEMM whose K is this N, instead of fp32 y.  gemm_tc_image_elems gives the buffer size.

@@ -1,0 +1,152 @@
+// Mixture-of-experts FFN of one token on device pointers: router, top-k, softmax over the chosen
+// experts, routed SwiGLU experts, sigmoid-gated shared expert.  Replaces the qwen35moe branch of the
+// reference's layer loop, src/cli/main.cpp:3110-3193, which runs 9 experts x 3 host-pointer matmuls
+// with a sync after each.
+//
+// Four launches, no host round trip (the chosen expert ids never leave the GPU):
+//   1. moe_router_kernel: logits = router[n_expert][hidden] . x, k rounds of block-wide arg-max (lowest
+//      index wins a tie), weights exp(l - max) / sum over the chosen, shared-expert gate sigmoid(g . x);
+//   2. gate/up of the k chosen experts as ONE tensor-core GEMV over gathered row ranges (the expert
+//      tensors are uploaded whole, [n_expert * eff][hidden]; the kernel's producer maps its row groups
+//      through the id list) with the SwiGLU epilogue -> act[k][eff];
+//   3. down of the k experts as ONE GEMV whose K axis is the k experts' K ranges side by side, the
+//      router weights folded into the activations (x scale per run of eff), residual added in the
+//      epilogue;
+//   4. the shared expert: the ordinary fused gate/up GEMV and a down GEMV that accumulates onto y.
+#include "ggb_internal.h"
+
+namespace ggb {
+
+namespace {
+
+constexpr int kMaxTopK = 16;
+
+// grid 1, block 256.  logits in shared memory (n_expert <= 1024).
+__global__ void moe_router_kernel(const float* __restrict__ x, const float* __restrict__ router, int hidden, int n_expert, int top_k,
+                                  const float* __restrict__ sh_gate_inp, int32_t* __restrict__ sel, float* __restrict__ w) {
+    __shared__ float logit[1024];
+    __shared__ float red_v[8];
+    __shared__ int red_i[8];
+    __shared__ float chosen[kMaxTopK];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e <= n_expert; e += 8) {          // e == n_expert: the shared expert's gate row
+        const float* wr = e < n_expert ? router + static_cast<size_t>(e) * hidden : sh_gate_inp;
+        if (!wr) continue;
+        float acc = 0.0f;
+        for (int i = lane * 4; i < hidden; i += 128) {
+            const float4 a = *reinterpret_cast<const float4*>(x + i), b = __ldg(reinterpret_cast<const float4*>(wr + i));
+            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (lane == 0) {
+            if (e < n_expert) logit[e] = acc;
+            else w[top_k] = 1.0f / (1.0f + expf(-acc));
+        }
+    }
+    if (!sh_gate_inp && threadIdx.x == 0) w[top_k] = 1.0f;
+    __syncthreads();
+    for (int j = 0; j < top_k; ++j) {
+        float bv = -INFINITY; int bi = 0x7FFFFFFF;
+        for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+            const float v = logit[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int q = 1; q < 8; ++q)
+                if (red_v[q] > red_v[0] || (red_v[q] == red_v[0] && red_i[q] < red_i[0])) { red_v[0] = red_v[q]; red_i[0] = red_i[q]; }
+            sel[j] = red_i[0];
+            chosen[j] = red_v[0];
+            logit[red_i[0]] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float mx = chosen[0];
+        float sum = 0.0f;
+        for (int j = 0; j < top_k; ++j) { chosen[j] = expf(chosen[j] - mx); sum += chosen[j]; }
+        for (int j = 0; j < top_k; ++j) w[j] = chosen[j] / sum;
+    }
+}
+
+}  // namespace
+
+}  // namespace ggb
+
+using namespace ggb;
+
+extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!p || !p->x || !p->y || !p->router || !p->gate_exps || !p->up_exps || !p->down_exps)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: null pointer");
+    if (p->hidden <= 0 || p->hidden % 256 || p->eff <= 0 || p->eff % 256 || p->n_expert < 1 || p->n_expert > 1024 || p->top_k < 1 ||
+        p->top_k > kMaxTopK || p->top_k > p->n_expert)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden and eff must be multiples of 256, n_expert <= 1024, top_k <= 16");
+    const DeviceWeight *ge = reinterpret_cast<const DeviceWeight*>(p->gate_exps), *ue = reinterpret_cast<const DeviceWeight*>(p->up_exps),
+                       *de = reinterpret_cast<const DeviceWeight*>(p->down_exps);
+    if (ge->w.N != static_cast<int64_t>(p->n_expert) * p->eff || ue->w.N != ge->w.N || ge->w.K != p->hidden || ue->w.K != p->hidden ||
+        de->w.N != static_cast<int64_t>(p->n_expert) * p->hidden || de->w.K != p->eff || ge->w.type != ue->w.type)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be [n_expert * eff][hidden] (gate, up) and [n_expert * hidden][eff] (down)");
+    if (ge->w.layout != 1 || ue->w.layout != 1 || de->w.layout != 1)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be Q4_K or Q6_K in the tensor-core layout");
+    const bool shared = p->sh_gate && p->sh_up && p->sh_down;
+    const DeviceWeight *sg = reinterpret_cast<const DeviceWeight*>(p->sh_gate), *su = reinterpret_cast<const DeviceWeight*>(p->sh_up),
+                       *sd = reinterpret_cast<const DeviceWeight*>(p->sh_down);
+    if (shared && (sg->w.N != p->eff_sh || su->w.N != p->eff_sh || sg->w.K != p->hidden || su->w.K != p->hidden || sd->w.N != p->hidden ||
+                   sd->w.K != p->eff_sh || p->eff_sh <= 0 || p->eff_sh % 256))
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: shared expert shapes do not match");
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    cudaStream_t s = h->stream;
+    // scratch: [sel: 16 ints][w: 17 floats][act: top_k * eff][act_sh: eff_sh]
+    const size_t floats = 64 + static_cast<size_t>(p->top_k) * p->eff + (shared ? p->eff_sh : 0);
+    float* scr = static_cast<float*>(scratch(h, 3, sizeof(float) * floats));
+    if (!scr) return h->last_status;
+    int32_t* sel = reinterpret_cast<int32_t*>(scr);
+    float* w = scr + 16;
+    float* act = scr + 64;
+    float* act_sh = act + static_cast<size_t>(p->top_k) * p->eff;
+
+    cudaError_t e = launch_pdl(h, moe_router_kernel, dim3(1), dim3(256), 0, s, p->x, p->router, p->hidden, p->n_expert, p->top_k,
+                               shared ? p->sh_gate_inp : static_cast<const float*>(nullptr), sel, w);
+    h->launches++;
+    if (e != cudaSuccess) return cuda_status(h, e, "moe router");
+    if (p->sel_out) cudaMemcpyAsync(p->sel_out, sel, sizeof(int32_t) * p->top_k, cudaMemcpyDeviceToDevice, s);
+    if (p->w_out) cudaMemcpyAsync(p->w_out, w, sizeof(float) * (p->top_k + 1), cudaMemcpyDeviceToDevice, s);
+
+    GemvArgs a{};
+    a.w = ge->w; a.w2 = ue->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act; a.ldc = p->top_k * p->eff; a.epi = EPI_SWIGLU;
+    a.sel = sel; a.sel_mode = 1; a.sel_count = p->top_k; a.sel_rows = p->eff;
+    int st = launch_gemv_mma(h, a, s);
+    if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert gate/up shape not covered") : st;
+
+    a = GemvArgs{};
+    a.w = de->w; a.x = act; a.M = 1; a.lda = p->top_k * p->eff; a.y = p->y; a.ldc = p->hidden;
+    a.epi = p->resid ? EPI_RESIDUAL : EPI_STORE; a.resid = p->resid;
+    a.sel = sel; a.sel_mode = 2; a.sel_count = p->top_k; a.sel_rows = p->hidden; a.xscale = w; a.xscale_run = p->eff;
+    st = launch_gemv_mma(h, a, s);
+    if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert down shape not covered") : st;
+
+    if (shared) {
+        a = GemvArgs{};
+        a.w = sg->w; a.w2 = su->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act_sh; a.ldc = p->eff_sh; a.epi = EPI_SWIGLU;
+        st = launch_gemv(h, a, s);
+        if (st != GGB_OK) return st;
+        a = GemvArgs{};
+        a.w = sd->w; a.x = act_sh; a.M = 1; a.lda = p->eff_sh; a.y = p->y; a.ldc = p->hidden; a.epi = EPI_RESIDUAL; a.resid = p->y;
+        a.xscale = w + p->top_k; a.xscale_run = p->eff_sh;
+        st = launch_gemv(h, a, s);
+        if (st != GGB_OK) return st;
+    }
+    return GGB_OK;
+}

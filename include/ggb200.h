@@ -232,6 +232,29 @@ GGB_API int ggb_attn_prefill_device(ggb_handle h, const ggb_attn_paged_params* p
  * the GPU (different handles or streams) would race on it -- keep them ordered. */
 GGB_API int ggb_attn_paged_static(ggb_handle h, const ggb_attn_paged_params* p);
 
+/* Mixture-of-experts FFN of ONE token (the qwen35moe branch of the reference's layer loop,
+ * src/cli/main.cpp:3110-3193): router logits = router[n_expert][hidden] . x; the top_k experts by logit;
+ * weights = softmax over just those; y = (resid +) sum_j w_j * down_j(silu(gate_j x) * up_j x)
+ * (+ sigmoid(sh_gate_inp . x) * shared expert).  x is the FFN-normed hidden row.  The expert tensors are
+ * the GGUF 3-D tensors uploaded whole with ggb_weight_upload as 2-D matrices: gate_exps / up_exps as
+ * [n_expert * eff][hidden], down_exps as [n_expert * hidden][eff] (Q4_K or Q6_K).  The chosen ids stay on
+ * the device: four kernels, no host round trip.  All pointers are device memory; asynchronous on the
+ * handle's stream.  sel_out / w_out (optional) receive the chosen ids [top_k] and weights [top_k + 1,
+ * the last one the shared expert's gate]. */
+typedef struct ggb_moe_params {
+    const float* x;
+    const float* resid;          /* optional [hidden]; may alias y */
+    float* y;
+    const float* router;         /* F32 [n_expert][hidden] */
+    ggb_weight gate_exps, up_exps, down_exps;
+    ggb_weight sh_gate, sh_up, sh_down;     /* shared expert: all three or none */
+    const float* sh_gate_inp;    /* optional F32 [hidden] */
+    int hidden, eff, eff_sh, n_expert, top_k;
+    int32_t* sel_out;
+    float* w_out;
+} ggb_moe_params;
+GGB_API int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p);
+
 /* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
 GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */

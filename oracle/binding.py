@@ -60,6 +60,8 @@ class Oracle:
         L.ggo_dequant_blocks.argtypes = [C.c_uint32, _u8p, C.c_int64, _f32p]
         L.ggo_dequant_row.argtypes = [C.c_uint32, _u8p, C.c_int64, C.c_int, _f32p]
         L.ggo_matmul_exact.argtypes = [_f32p, C.c_int, C.c_int, _u8p, C.c_uint32, C.c_int, C.c_int, _f32p, C.c_int]
+        L.ggo_moe_ffn.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, _u8p, _u8p, C.c_uint32, _u8p, C.c_uint32,
+                                  _u8p, _u8p, C.c_uint32, _u8p, C.c_uint32, C.c_int, _f32p, _f32p, C.c_void_p, _f32p]
         L.ggo_matmul_cpu_ref_k.argtypes = [_f32p, C.c_int, _u8p, C.c_uint32, C.c_int, C.c_int, _f32p]
         L.ggo_matmul_f32_kn.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
         L.ggo_rms_norm.argtypes = [_f32p, _f32p, C.c_int, C.c_float, _f32p]
@@ -164,6 +166,32 @@ class Oracle:
         out = np.empty_like(Q)
         assert self.lib.ggo_flash_attn(_fp(Q), _fp(K), _fp(V), _fp(out), nh, hd, ctx, qpos) == 0
         return out
+
+    def moe_ffn(self, x, router, top_k, eff, gate_exps, up_exps, type_gu, down_exps, type_d,
+                shared=None, sh_gate_inp=None):
+        """MoE FFN of one token (src/cli/main.cpp:3110-3193).  shared = (gate, up, type_gu, down, type_d, eff_sh) or None.
+        Returns (moe_out[hidden], chosen ids[top_k], weights[top_k (+1 with a shared expert)])."""
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+        router = np.ascontiguousarray(router, dtype=np.float32)
+        n_expert, hidden = router.shape
+        out = np.empty(hidden, np.float32)
+        ids = np.empty(top_k, np.int32)
+        w = np.zeros(top_k + 1, np.float32)
+        u8 = lambda a: np.ascontiguousarray(a, dtype=np.uint8).reshape(-1)
+        ge, ue, de = u8(gate_exps), u8(up_exps), u8(down_exps)
+        if shared is not None:
+            sg, su, stgu, sd, std, eff_sh = shared
+            sg, su, sd = u8(sg), u8(su), u8(sd)
+            sgp, sup, sdp = _bp(sg), _bp(su), _bp(sd)
+        else:
+            sgp = sup = sdp = None
+            stgu = std = eff_sh = 0
+        gi = np.ascontiguousarray(sh_gate_inp, dtype=np.float32) if sh_gate_inp is not None else None
+        rc = self.lib.ggo_moe_ffn(_fp(x), hidden, _fp(router), n_expert, top_k, eff, _bp(ge), _bp(ue), type_gu, _bp(de), type_d,
+                                  sgp, sup, stgu, sdp, std, eff_sh, _fp(gi) if gi is not None else None, _fp(out),
+                                  ids.ctypes.data_as(C.c_void_p), _fp(w))
+        assert rc == 0
+        return out, ids, (w if shared is not None else w[:top_k])
 
     def rope_cpu_ref(self, x, n_dims, offset, freq_scale, rope_dims):
         v = np.array(x, dtype=np.float32, copy=True)

@@ -521,6 +521,81 @@ GGO_API void ggo_model_set_vec(ggo_model* m, int layer, int which, const float* 
     *p[which] = v;
 }
 
+/* Mixture-of-experts FFN of one token, src/cli/main.cpp:3110-3193 (qwen35moe branch).
+ * PARITY UNPINNED at unit level: the reference keeps this block inside main(), so it cannot be called
+ * from the reference-built checker; it is restated line by line from the cited source.
+ *   router logits  :3117-3125  F32 [n_expert][hidden] . x, one running fp32 sum per expert
+ *   top-k          :3128-3131  std::partial_sort by logit, descending (ties: unspecified there; lowest index here)
+ *   weights        :3132-3135  exp(l - max) / sum over the k chosen
+ *   expert e       :3140-3170  slice e of the 3-D tensors; act = silu(gate x) * up x; out = down act; moe += w * out
+ *   shared expert  :3177-3191  the same with its own matrices, weight = sigmoid(gate_inp_shexp . x) (1 if absent)
+ * x is the FFN-normed hidden row; moe_out (hidden floats) is what the caller adds to the residual stream.
+ * Expert tensors: gate / up [n_expert][eff][hidden], down [n_expert][hidden][eff], GGUF rows of their type. */
+GGO_API int ggo_moe_ffn(const float* x, int hidden, const float* router, int n_expert, int top_k, int eff,
+                        const uint8_t* gate_exps, const uint8_t* up_exps, uint32_t type_gu,
+                        const uint8_t* down_exps, uint32_t type_d,
+                        const uint8_t* sh_gate, const uint8_t* sh_up, uint32_t sh_type_gu, const uint8_t* sh_down, uint32_t sh_type_d,
+                        int eff_sh, const float* sh_gate_inp, float* moe_out, int32_t* sel_ids, float* sel_w) {
+    if (top_k < 1 || top_k > n_expert) return -1;
+    float* rl = (float*)malloc(sizeof(float) * (size_t)n_expert);
+    char* used = (char*)calloc((size_t)n_expert, 1);
+    int maxeff = eff > eff_sh ? eff : eff_sh;
+    float* eg = (float*)malloc(sizeof(float) * (size_t)maxeff);
+    float* eu = (float*)malloc(sizeof(float) * (size_t)maxeff);
+    float* ea = (float*)malloc(sizeof(float) * (size_t)maxeff);
+    float* ed = (float*)malloc(sizeof(float) * (size_t)hidden);
+    int rc = 0;
+    for (int e = 0; e < n_expert; ++e) {
+        const float* wr = router + (size_t)e * hidden;
+        float acc = 0.0f;
+        for (int i = 0; i < hidden; ++i) acc += x[i] * wr[i];
+        rl[e] = acc;
+    }
+    for (int j = 0; j < top_k; ++j) {
+        int best = -1;
+        for (int e = 0; e < n_expert; ++e)
+            if (!used[e] && (best < 0 || rl[e] > rl[best])) best = e;
+        used[best] = 1;
+        sel_ids[j] = best;
+    }
+    {
+        const float mx = rl[sel_ids[0]];
+        float wsum = 0.0f;
+        for (int j = 0; j < top_k; ++j) { sel_w[j] = expf(rl[sel_ids[j]] - mx); wsum += sel_w[j]; }
+        for (int j = 0; j < top_k; ++j) sel_w[j] /= wsum;
+    }
+    for (int i = 0; i < hidden; ++i) moe_out[i] = 0.0f;
+    const size_t gu_bytes = (size_t)eff * ((size_t)hidden / ggo_block_elems(type_gu)) * ggo_block_bytes(type_gu);
+    const size_t d_bytes = (size_t)hidden * ((size_t)eff / ggo_block_elems(type_d)) * ggo_block_bytes(type_d);
+    for (int j = 0; j <= top_k && rc == 0; ++j) {
+        const uint8_t *g, *u, *d;
+        uint32_t tgu, td;
+        int f;
+        float weight;
+        if (j < top_k) {
+            g = gate_exps + gu_bytes * sel_ids[j]; u = up_exps + gu_bytes * sel_ids[j]; d = down_exps + d_bytes * sel_ids[j];
+            tgu = type_gu; td = type_d; f = eff; weight = sel_w[j];
+        } else {
+            if (!sh_gate || !sh_up || !sh_down) break;
+            weight = 1.0f;
+            if (sh_gate_inp) {
+                float acc = 0.0f;
+                for (int i = 0; i < hidden; ++i) acc += x[i] * sh_gate_inp[i];
+                weight = 1.0f / (1.0f + expf(-acc));
+            }
+            sel_w[top_k] = weight;
+            g = sh_gate; u = sh_up; d = sh_down; tgu = sh_type_gu; td = sh_type_d; f = eff_sh;
+        }
+        rc |= ggo_matmul_exact(x, 1, hidden, g, tgu, f, hidden, eg, f);
+        rc |= ggo_matmul_exact(x, 1, hidden, u, tgu, f, hidden, eu, f);
+        for (int i = 0; i < f; ++i) ea[i] = (eg[i] / (1.0f + expf(-eg[i]))) * eu[i];
+        rc |= ggo_matmul_exact(ea, 1, f, d, td, hidden, f, ed, hidden);
+        for (int i = 0; i < hidden; ++i) moe_out[i] += weight * ed[i];
+    }
+    free(rl); free(used); free(eg); free(eu); free(ea); free(ed);
+    return rc;
+}
+
 /* One forward over n_tok tokens at absolute positions pos..pos+n_tok-1,
  * writing the KV cache and (if logits != NULL) the logits of the LAST row
  * (main.cpp:3593-3598).  Matmuls follow the exact path (ggo_matmul_exact).
