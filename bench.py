@@ -449,6 +449,57 @@ def run_micro(args):
     b.close()
 
 
+def run_micro_moe(args):
+    """Decode-side MoE FFN microbenchmark at the qwen35moe expert shapes (BASELINE config 5): hidden 2048,
+    256 routed experts of FFN 512 (Q4_K gate/up, Q6_K down), top-8 + shared expert.  64 different tokens
+    are routed in turn, so successive calls touch different experts of the 0.4 GB expert set (> L2).
+        python bench.py --micro-moe"""
+    import torch
+    from ggnpu_b200.backend import CudaBackend
+    b = CudaBackend(0)
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", 0))
+    peak, peak_kind = peaks()
+    H, eff, nE, k, eff_sh = 2048, 512, args.moe_experts, 8, 512
+    g = torch.Generator(device="cuda").manual_seed(7)
+
+    def up(n, kdim, t):
+        raw = S.quantize(torch.randn(n, kdim, generator=g, device="cuda") * 0.02, t).cpu().numpy()
+        return b.upload_weight(t, raw, n, kdim)
+
+    hg, hu, hd = up(nE * eff, H, S.Q4_K), up(nE * eff, H, S.Q4_K), up(nE * H, eff, S.Q6_K)
+    sg, su, sd = up(eff_sh, H, S.Q4_K), up(eff_sh, H, S.Q4_K), up(H, eff_sh, S.Q6_K)
+    router = (torch.randn(nE, H, generator=g, device="cuda") * 0.05).contiguous()
+    sgi = (torch.randn(H, generator=g, device="cuda") * 0.05).contiguous()
+    xs = torch.randn(64, H, generator=g, device="cuda").contiguous()
+    y = torch.empty(H, device="cuda")
+    torch.cuda.synchronize()
+
+    def one(i):
+        x = xs[i % 64]
+        b.moe_ffn_device(x=x.data_ptr(), resid=x.data_ptr(), y=y.data_ptr(), router=router.data_ptr(), gate_exps=hg, up_exps=hu,
+                         down_exps=hd, sh_gate=sg, sh_up=su, sh_down=sd, sh_gate_inp=sgi.data_ptr(), hidden=H, eff=eff, eff_sh=eff_sh,
+                         n_expert=nE, top_k=k, sel_out=None, w_out=None)
+
+    for i in range(64):
+        one(i)
+    b.sync()
+    l0 = b.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 64 * args.reps
+    e0.record(stream)
+    for i in range(n):
+        one(i)
+    e1.record(stream)
+    b.sync()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    alg = nE * H * 4 + H * 4 + (k + 1) * (2 * eff * (H // 256) * 144 + H * (eff // 256) * 210) + H * 12
+    print(json.dumps({"micro": "moe_ffn_decode", "hidden": H, "eff": eff, "n_expert": nE, "top_k": k, "shared_eff": eff_sh,
+                      "us_per_token_layer": us, "launches_per_call": (b.launch_count() - l0) / n, "alg_bytes": alg,
+                      "gbs": alg / us / 1e3, "frac_of_hbm_peak": alg / us / 1e3 / peak, "peak_source": peak_kind,
+                      "reference_equivalent": "9 experts x 3 host-pointer matmuls + sync each (src/cli/main.cpp:3152-3191)"}), flush=True)
+    b.close()
+
+
 def run_tp(args):
     """Tensor-parallel decode + prefill of the Llama-3-8B-shape model (BASELINE config 4) over all ranks
     of this launch (torchrun: one process per GPU; a single process is the TP = 1 point).  Strong
@@ -538,6 +589,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=128, help="prompt tokens before the timed decode (128 = the benchmark config)")
     ap.add_argument("--prefill-long", type=int, default=2048, help="token count of the long-prompt prefill figure")
+    ap.add_argument("--micro-moe", action="store_true", help="MoE FFN decode microbenchmark (qwen35moe expert shapes)")
+    ap.add_argument("--moe-experts", type=int, default=256)
     ap.add_argument("--tp", action="store_true", help="tensor-parallel benchmark of the 8B-shape model over the ranks of this launch")
     ap.add_argument("--tp-ctx", type=int, default=4352)
     ap.add_argument("--tp-prompt", type=int, default=4096)
@@ -551,6 +604,9 @@ def main():
     args = ap.parse_args()
     if args.tp:
         run_tp(args)
+        return
+    if args.micro_moe:
+        run_micro_moe(args)
         return
     if args.micro:
         run_micro(args)

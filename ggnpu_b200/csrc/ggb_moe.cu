@@ -3,9 +3,10 @@
 // reference's layer loop, src/cli/main.cpp:3110-3193, which runs 9 experts x 3 host-pointer matmuls
 // with a sync after each.
 //
-// Four launches, no host round trip (the chosen expert ids never leave the GPU):
-//   1. moe_router_kernel: logits = router[n_expert][hidden] . x, k rounds of block-wide arg-max (lowest
-//      index wins a tie), weights exp(l - max) / sum over the chosen, shared-expert gate sigmoid(g . x);
+// Six launches, no host round trip (the chosen expert ids never leave the GPU):
+//   1. moe_logits_kernel: logits = router[n_expert][hidden] . x (a warp per expert); moe_topk_kernel: k
+//      rounds of block-wide arg-max (lowest index wins a tie), weights exp(l - max) / sum over the
+//      chosen, shared-expert gate sigmoid(g . x);
 //   2. gate/up of the k chosen experts as ONE tensor-core GEMV over gathered row ranges (the expert
 //      tensors are uploaded whole, [n_expert * eff][hidden]; the kernel's producer maps its row groups
 //      through the id list) with the SwiGLU epilogue -> act[k][eff];
@@ -21,9 +22,31 @@ namespace {
 
 constexpr int kMaxTopK = 16;
 
-// grid 1, block 256.  logits in shared memory (n_expert <= 1024).
-__global__ void moe_router_kernel(const float* __restrict__ x, const float* __restrict__ router, int hidden, int n_expert, int top_k,
-                                  const float* __restrict__ sh_gate_inp, int32_t* __restrict__ sel, float* __restrict__ w) {
+// Router logits: one warp per expert row (row n_expert = the shared expert's gate vector), 8 rows per CTA,
+// so the 2 MB router matrix is read by dozens of SMs rather than one.
+__global__ void moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ router, int hidden, int n_expert,
+                                  const float* __restrict__ sh_gate_inp, float* __restrict__ logits) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    if (e > n_expert) return;
+    const float* wr = e < n_expert ? router + static_cast<size_t>(e) * hidden : sh_gate_inp;
+    if (!wr) return;
+    float acc = 0.0f;
+    for (int i = lane * 4; i < hidden; i += 128) {
+        const float4 a = *reinterpret_cast<const float4*>(x + i), b = __ldg(reinterpret_cast<const float4*>(wr + i));
+        acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if (lane == 0) logits[e] = acc;
+}
+
+// grid 1, block 256: k rounds of block-wide arg-max over the logits (n_expert <= 1024), softmax over the chosen,
+// shared-expert gate.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, int top_k, int has_gate,
+                                int32_t* __restrict__ sel, float* __restrict__ w) {
     __shared__ float logit[1024];
     __shared__ float red_v[8];
     __shared__ int red_i[8];
@@ -31,22 +54,8 @@ __global__ void moe_router_kernel(const float* __restrict__ x, const float* __re
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = warp; e <= n_expert; e += 8) {          // e == n_expert: the shared expert's gate row
-        const float* wr = e < n_expert ? router + static_cast<size_t>(e) * hidden : sh_gate_inp;
-        if (!wr) continue;
-        float acc = 0.0f;
-        for (int i = lane * 4; i < hidden; i += 128) {
-            const float4 a = *reinterpret_cast<const float4*>(x + i), b = __ldg(reinterpret_cast<const float4*>(wr + i));
-            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-        if (lane == 0) {
-            if (e < n_expert) logit[e] = acc;
-            else w[top_k] = 1.0f / (1.0f + expf(-acc));
-        }
-    }
-    if (!sh_gate_inp && threadIdx.x == 0) w[top_k] = 1.0f;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) logit[e] = logits[e];
+    if (threadIdx.x == 0) w[top_k] = has_gate ? 1.0f / (1.0f + expf(-logits[n_expert])) : 1.0f;
     __syncthreads();
     for (int j = 0; j < top_k; ++j) {
         float bv = -INFINITY; int bi = 0x7FFFFFFF;
@@ -108,19 +117,24 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     std::lock_guard<std::mutex> lk(h->mu);
     cudaSetDevice(h->device);
     cudaStream_t s = h->stream;
-    // scratch: [sel: 16 ints][w: 17 floats][act: top_k * eff][act_sh: eff_sh]
-    const size_t floats = 64 + static_cast<size_t>(p->top_k) * p->eff + (shared ? p->eff_sh : 0);
+    // scratch: [sel: 16 ints][w: 17 floats][act: top_k * eff][act_sh: eff_sh][logits: n_expert + 1]
+    const size_t floats = 64 + static_cast<size_t>(p->top_k) * p->eff + (shared ? p->eff_sh : 0) + p->n_expert + 1;
     float* scr = static_cast<float*>(scratch(h, 3, sizeof(float) * floats));
     if (!scr) return h->last_status;
     int32_t* sel = reinterpret_cast<int32_t*>(scr);
     float* w = scr + 16;
     float* act = scr + 64;
     float* act_sh = act + static_cast<size_t>(p->top_k) * p->eff;
+    float* logits = act_sh + (shared ? p->eff_sh : 0);
+    const float* gate_vec = shared ? p->sh_gate_inp : static_cast<const float*>(nullptr);
 
-    cudaError_t e = launch_pdl(h, moe_router_kernel, dim3(1), dim3(256), 0, s, p->x, p->router, p->hidden, p->n_expert, p->top_k,
-                               shared ? p->sh_gate_inp : static_cast<const float*>(nullptr), sel, w);
+    cudaError_t e = launch_pdl(h, moe_logits_kernel, dim3((p->n_expert + 1 + 7) / 8), dim3(256), 0, s, p->x, p->router, p->hidden, p->n_expert,
+                               gate_vec, logits);
     h->launches++;
-    if (e != cudaSuccess) return cuda_status(h, e, "moe router");
+    if (e != cudaSuccess) return cuda_status(h, e, "moe router logits");
+    e = launch_pdl(h, moe_topk_kernel, dim3(1), dim3(256), 0, s, static_cast<const float*>(logits), p->n_expert, p->top_k, gate_vec ? 1 : 0, sel, w);
+    h->launches++;
+    if (e != cudaSuccess) return cuda_status(h, e, "moe top-k");
     if (p->sel_out) cudaMemcpyAsync(p->sel_out, sel, sizeof(int32_t) * p->top_k, cudaMemcpyDeviceToDevice, s);
     if (p->w_out) cudaMemcpyAsync(p->w_out, w, sizeof(float) * (p->top_k + 1), cudaMemcpyDeviceToDevice, s);
 
