@@ -500,6 +500,46 @@ def run_micro_moe(args):
     b.close()
 
 
+def run_micro_allreduce(args):
+    """Latency of the tensor-parallel all-reduce at decode message sizes, peer-memory one-shot kernel vs
+    NCCL, back to back on the compute stream (run under torchrun, one process per GPU)."""
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200.backend import CudaBackend
+    rank, local, world = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    b = CudaBackend(local)
+    box = [b.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    b.tp_init(box[0], rank, world)
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
+    res = {}
+    for mode in ("nccl", "one_shot"):
+        if mode == "one_shot":
+            handles = [None] * world
+            dist.all_gather_object(handles, b.tp_ipc_handle())
+            b.tp_attach_peers(handles)
+        for n in (1024, 4096, 16384):
+            t = torch.ones(n, device="cuda")
+            for _ in range(20):
+                b.tp_all_reduce_device(t.data_ptr(), n)
+                t.fill_(1.0)
+            b.sync(); dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(200):
+                b.tp_all_reduce_device(t.data_ptr(), n)
+            e1.record(stream)
+            b.sync()
+            res[f"{mode}_{n * 4}B_us"] = e0.elapsed_time(e1) * 1e3 / 200
+    if rank == 0:
+        print(json.dumps({"micro": "tp_all_reduce", "ranks": world, **res}), flush=True)
+    dist.barrier()
+    b.close()
+    dist.destroy_process_group()
+
+
 def run_tp(args):
     """Tensor-parallel decode + prefill of the Llama-3-8B-shape model (BASELINE config 4) over all ranks
     of this launch (torchrun: one process per GPU; a single process is the TP = 1 point).  Strong
@@ -523,6 +563,10 @@ def run_tp(args):
         box = [b.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         b.tp_init(box[0], rank, world)
+        if not args.tp_nccl_only:                      # one-shot peer-memory all-reduce for the 16 KB decode messages
+            handles = [None] * world
+            dist.all_gather_object(handles, b.tp_ipc_handle())
+            b.tp_attach_peers(handles)
     t0 = time.perf_counter()
     synth = S.build_model(cfg, device="cuda")
     model = Model(b, cfg, synth.tensors)
@@ -567,7 +611,7 @@ def run_tp(args):
             "metric": METRIC, "value": K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"llama-3-8b-shape Q4_K_M-style ({cfg.n_layer} layers), tensor parallel over {world} GPU(s), batch-1 greedy decode after a {n_prompt}-token prompt, ctx {ctx}",
-                       "parallelism": f"tp{world}", "collectives": "NCCL all-reduce after attn_output and ffn_down (16 KB at batch 1), all-gather of the logits slices",
+                       "parallelism": f"tp{world}", "collectives": ("NCCL all-reduce" if args.tp_nccl_only or world == 1 else "one-shot peer-memory all-reduce (decode), NCCL (prefill)") + " after attn_output and ffn_down, NCCL all-gather of the logits slices",
                        "l2": "each step streams this rank's weight shard (> 126 MB L2 up to tp8)"},
             "gpu_launches": launches, "prefill": {"tokens": n_prompt, "tok_per_s": n_prompt / (prefill_ms * 1e-3)},
             "decode_step": {"algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
@@ -591,7 +635,9 @@ def main():
     ap.add_argument("--prefill-long", type=int, default=2048, help="token count of the long-prompt prefill figure")
     ap.add_argument("--micro-moe", action="store_true", help="MoE FFN decode microbenchmark (qwen35moe expert shapes)")
     ap.add_argument("--moe-experts", type=int, default=256)
+    ap.add_argument("--micro-allreduce", action="store_true", help="latency of the tensor-parallel all-reduce (torchrun)")
     ap.add_argument("--tp", action="store_true", help="tensor-parallel benchmark of the 8B-shape model over the ranks of this launch")
+    ap.add_argument("--tp-nccl-only", action="store_true", help="keep every all-reduce on NCCL (no peer-memory one-shot kernel)")
     ap.add_argument("--tp-ctx", type=int, default=4352)
     ap.add_argument("--tp-prompt", type=int, default=4096)
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
@@ -604,6 +650,9 @@ def main():
     args = ap.parse_args()
     if args.tp:
         run_tp(args)
+        return
+    if args.micro_allreduce:
+        run_micro_allreduce(args)
         return
     if args.micro_moe:
         run_micro_moe(args)

@@ -95,7 +95,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_moe_ffn_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device",
 ]
 
 _lib = None
@@ -140,6 +140,8 @@ def load_library() -> C.CDLL:
     L.ggb_tp_unique_id.argtypes = [vp]
     L.ggb_tp_init.argtypes = [vp, vp, i32, i32]
     L.ggb_tp_all_reduce_device.argtypes = [vp, vp, i64]
+    L.ggb_tp_ipc_handle.argtypes = [vp, vp]
+    L.ggb_tp_attach_peers.argtypes = [vp, vp]
     L.ggb_attn_paged_static.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_stream.argtypes = [vp]
     L.ggb_stream.restype = vp
@@ -317,6 +319,18 @@ class CudaBackend:
         buf = C.create_string_buffer(bytes(unique_id), 128)
         self.check(self.lib.ggb_tp_init(self.h, buf, rank, size), "tp_init")
         self.tp_rank, self.tp_size = rank, size
+
+    def tp_ipc_handle(self) -> bytes:
+        """This rank's exchange region for the one-shot all-reduce, as a 64-byte CUDA IPC handle."""
+        buf = C.create_string_buffer(64)
+        self.check(self.lib.ggb_tp_ipc_handle(self.h, buf), "tp_ipc_handle")
+        return buf.raw
+
+    def tp_attach_peers(self, handles) -> None:
+        """handles: the `size` IPC handles in rank order (every rank's tp_ipc_handle())."""
+        blob = b"".join(bytes(x) for x in handles)
+        assert len(blob) == 64 * self.tp_size
+        self.check(self.lib.ggb_tp_attach_peers(self.h, C.create_string_buffer(blob, len(blob))), "tp_attach_peers")
 
     def tp_all_reduce_device(self, d_buf: int, count: int) -> Status:
         return Status(self.lib.ggb_tp_all_reduce_device(self.h, d_buf, count))

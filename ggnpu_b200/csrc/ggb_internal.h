@@ -92,6 +92,8 @@ struct Context {
     // tensor-parallel group (ggb_tp.cu); tp_size == 1: none
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
+    void* tp_region[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // peer-mapped exchange regions (own at tp_rank)
+    bool tp_peers_attached = false;
     void* d_xb = nullptr;     // fp16 activation tile images of the tcgen05 GEMM (grown on demand, never during graph capture)
     size_t d_xb_elems = 0;
     float* d_ws = nullptr;    // split-K partial sums of the tcgen05 GEMM (grown on demand)

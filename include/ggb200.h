@@ -267,6 +267,15 @@ GGB_API uint64_t ggb_launch_count(ggb_handle h);
  * on such a handle is one shard of a tensor-parallel model: see ggb_model_desc. */
 GGB_API int ggb_tp_unique_id(void* id128);
 GGB_API int ggb_tp_init(ggb_handle h, const void* id128, int rank, int size);
+/* Optional, after ggb_tp_init: a one-shot all-reduce over peer memory for small messages (the 16 KB partial
+ * rows of a decode step, where NCCL's latency dominates).  Every rank calls ggb_tp_ipc_handle (allocates
+ * its exchange region, returns a 64-byte CUDA IPC handle), the ranks exchange the handles over the host
+ * channel, and every rank calls ggb_tp_attach_peers with all `size` handles in rank order (its own entry is
+ * ignored).  From then on, in groups of 4 or more ranks (where it is faster than NCCL; GGB_TP_ONE_SHOT=1 in the
+ * environment lowers that to 2), sums of up to 16384 floats use the peer-memory kernel, larger ones NCCL.
+ * All ranks of a group must be processes on one machine whose GPUs can reach each other (NVLink / NVSwitch). */
+GGB_API int ggb_tp_ipc_handle(ggb_handle h, void* handle64);
+GGB_API int ggb_tp_attach_peers(ggb_handle h, const void* handles);
 /* Sum of d_buf[0..count) over the group, in place, asynchronous on the handle's stream. */
 GGB_API int ggb_tp_all_reduce_device(ggb_handle h, float* d_buf, int64_t count);
 

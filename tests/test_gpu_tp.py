@@ -16,7 +16,8 @@ def test_two_rank_model_matches_oracle():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     port = 29500 + os.getpid() % 2000
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # GGB_TP_ONE_SHOT: take the peer-memory all-reduce also at 2 ranks (by default it starts at 4, where it wins)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", GGB_TP_ONE_SHOT="1")
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(r), "2", str(port)],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
     outs = []

@@ -26,11 +26,31 @@ def main():
     dist.broadcast_object_list(box, src=0)
     b.tp_init(box[0], rank, size)
 
-    # the group sums: every rank contributes rank + 1
+    # the group sums over NCCL: every rank contributes rank + 1
     t = torch.full((1000,), float(rank + 1), device=f"cuda:{rank}")
     assert int(b.tp_all_reduce_device(t.data_ptr(), t.numel())) == 0
     b.sync()
     assert torch.all(t == size * (size + 1) / 2)
+    # peer-memory exchange regions: small sums now take the one-shot kernel, large ones stay on NCCL
+    handles = [None] * size
+    dist.all_gather_object(handles, b.tp_ipc_handle())
+    b.tp_attach_peers(handles)
+    g = torch.Generator().manual_seed(100 + rank)
+    for it in range(40):                                   # many epochs, both halves of the exchange buffer, three sizes
+        for n in (4096, 1024, 16384, 100000):
+            mine = torch.randn(n, generator=g)
+            parts = [torch.empty(n) for _ in range(size)]
+            dist.all_gather(parts, mine)
+            t = mine.to(f"cuda:{rank}")
+            assert int(b.tp_all_reduce_device(t.data_ptr(), n)) == 0
+            b.sync()
+            if n <= 16384:                                 # one-shot: slices added in rank order, bit-identical on every rank
+                want = parts[0].clone()
+                for p in parts[1:]:
+                    want += p
+                assert torch.equal(t.cpu(), want), (it, n)
+            else:
+                assert torch.allclose(t.cpu(), torch.stack(parts).sum(0), rtol=1e-6, atol=1e-6)
 
     worst = 0.0
     for name, kw in {"llama_q4k_q6k": dict(seed=11, n_head=8, n_kv=2, ffn=1024),
