@@ -317,7 +317,10 @@ def run_ours(args):
         alg_bytes = 2 * N * (Kd // 256) * 144 + Kd * 4 + Kd * 4 + N * 4
         achieved = alg_bytes / (avg_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "kernel": "gemv_mma_q4k_kernel (dual gate/up 8192x2048 Q4_K + SwiGLU + RMSNorm prologue, M = 1)", "achieved": achieved, "peak": peak,
-                "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind, "traffic": None,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the ncu capture
+                # summarised in profiles/gemv_mma_q4k_dual_8192x2048_m1.md (1.002 x the algorithmic bytes)
+                "traffic": 18969600, "traffic_source": "ncu capture, profiles/gemv_mma_q4k_dual_8192x2048_m1.md",
                 "bytes_per_launch": alg_bytes, "avg_launch_us": avg_ms * 1e3, "launches_timed": len(times)}
         # ---- tensor roofline of the prefill GEMM: the same gate/up pairs at a 2048-token chunk ----
         Mg = 2048
@@ -351,7 +354,8 @@ def run_ours(args):
             tpeak, tkind = 1590.0, "fallback"
         gemm_roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (dual gate/up 8192x2048 Q4_K + SwiGLU, 2048 tokens; includes the fp16 activation preparation kernel)",
                      "achieved": flops / (g_ms * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s", "frac": flops / (g_ms * 1e-3) / 1e12 / tpeak,
-                     "peak_source": tkind, "traffic": None, "flops_per_launch": flops, "avg_launch_us": g_ms * 1e3, "launches_timed": len(gtimes)}
+                     "peak_source": tkind, "traffic": 44704768, "traffic_source": "ncu capture (DRAM bytes; the fp32 result mostly stays in L2), profiles/gemm_tc_q4k_dual_8192x2048_m2048.md",
+                     "flops_per_launch": flops, "avg_launch_us": g_ms * 1e3, "launches_timed": len(gtimes)}
         for wg, wu in copies:
             b.free_weight(wg); b.free_weight(wu)
 
