@@ -192,6 +192,8 @@ class CudaBackend:
 
     def close(self):
         if getattr(self, "h", None):
+            for m in list(getattr(self, "_models", ())):      # models hold pointers into the handle: they go first
+                m.close()
             self.lib.ggb_destroy(self.h)
             self.h = None
 
@@ -368,6 +370,10 @@ class Model:
         m = C.c_void_p()
         backend.check(L.ggb_model_create(backend.h, C.byref(desc), C.byref(m)), "model_create")
         self.m = m
+        if not hasattr(backend, "_models"):
+            import weakref
+            backend._models = weakref.WeakSet()
+        backend._models.add(self)
         for name, (tid, dims, raw) in tensors.items():
             raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
             if name in _SLOTS:
@@ -409,8 +415,13 @@ class Model:
 
     def close(self):
         if getattr(self, "m", None):
-            self.b.lib.ggb_model_destroy(self.m)
+            if getattr(self.b, "h", None):                    # a destroyed handle took its models' memory with the context
+                self.b.lib.ggb_model_destroy(self.m)
             self.m = None
+            try:
+                self.b._models.discard(self)
+            except Exception:
+                pass
 
     def __del__(self):
         try:

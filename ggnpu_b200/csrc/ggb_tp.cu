@@ -174,8 +174,8 @@ void tp_destroy(Context* c) {
         c->tp_region[q] = nullptr;
     }
     c->tp_peers_attached = false;
-    Nccl* n = nccl();
-    if (n && c->tp_comm) n->comm_destroy(c->tp_comm);
+    // NCCL is only touched by handles that joined a group (no dlopen from a destructor otherwise)
+    if (c->tp_comm) { Nccl* n = nccl(); if (n) n->comm_destroy(c->tp_comm); }
     c->tp_comm = nullptr; c->tp_size = 1; c->tp_rank = 0;
 }
 
