@@ -363,224 +363,6 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
     stamp(a.trace, 7, 3);
 }
 
-// ---- the same attention, one warp per query head, no block-wide barrier -------------------------------
-// grid (n_kv, n_splits, n_tok), block 32 * G threads (G = query heads per KV head <= 8), head_dim 64 or 128.
-// At decode contexts a split is one or two 64-key chunks: the work is tiny and attn_tile_kernel's eight
-// __syncthreads phases are its whole duration.  Here warp w owns query head h * G + w end to end: lane l
-// holds dims l * D .. l * D + D - 1 of q (D = head_dim / 32: adjacent RoPE pairs stay inside a lane, NeoX
-// pairs sit 16 lanes apart), scores its own keys (lane = key, the K row read straight from the cache
-// with 128-bit loads, q broadcast from the warp's shared-memory copy), reduces max / sum with shuffles,
-// and accumulates P V with lane = output dims, one coalesced V row per key.  With a.fuse every warp
-// rotates the new key itself (identical bits, no exchange needed); warp 0 stores it to the cache.
-// The first chunk's K rows and V words are requested BEFORE griddepcontrol.wait: cache rows below `pos`
-// were written by kernels that finished long ago (every kernel triggers its successor only after its own
-// wait), so their memory latency hides behind the predecessor's tail; q and the new key come after it.
-template <int HD>
-__global__ void __launch_bounds__(256) attn_warp_kernel(AttnPagedArgs a) {
-    constexpr int D = HD / 32;               // dims per lane
-    constexpr int KW = HD / 2;               // 32-bit words (bf16 pairs) per K or V row
-    constexpr int NVP = D == 2 ? 64 : 16;    // keys of the first chunk whose V words are prefetched into registers
-    __shared__ __align__(16) float qs_all[8][HD];
-    __shared__ __align__(16) uint32_t fresh_all[8][HD];     // per warp: rotated new key [KW words], new value [KW words]
-    stamp(a.trace, 0, 3);
-    const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int G = a.n_head / a.n_kv;
-    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
-    const int keys_per_split = a.pages_per_split * a.page;
-    const int j_begin = split * keys_per_split;
-    const int j_end = min(j_begin + keys_per_split, pos + 1);
-    if (j_begin > pos) return;               // no visible key in this split (the merge skips it too)
-    const int head = h * G + w;
-    float* qs = qs_all[w];
-    uint32_t* fresh = fresh_all[w];
-    const bool has_new = a.fuse && pos >= j_begin && pos < j_begin + keys_per_split;
-    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
-    const int half = HD >> 1;
-    const int d0 = lane * D;
-
-    // element offset of a key's row inside the layer's cache (fits 32 bits: pages * n_kv * page * HD elements)
-    auto row_off = [&](int key) -> uint32_t {
-        const int page = a.block_table[key / a.page], slot = key % a.page;
-        return static_cast<uint32_t>(((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD);
-    };
-    uint32_t off[2];
-    bool live[2], is_new[2];
-    uint4 kw[2][HD / 8];
-    // this lane's two keys of chunk jc: row offsets (two independent table look-ups), then both K rows in flight
-    auto load_keys = [&](int jc, int nk) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int key = jc + lane + 32 * u;
-            live[u] = lane + 32 * u < nk;
-            is_new[u] = has_new && key == pos;
-            off[u] = live[u] && !is_new[u] ? row_off(key) : 0u;
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const uint4* kr = reinterpret_cast<const uint4*>(a.k_cache + off[u]);
-#pragma unroll
-            for (int c = 0; c < HD / 8; ++c) kw[u][c] = live[u] && !is_new[u] ? kr[c] : make_uint4(0u, 0u, 0u, 0u);
-        }
-    };
-    // V words of this lane's dims for 16 keys j0 .. j0 + 15 of chunk jc (offsets arrive by shuffle, the loads go out together)
-    auto load_v16 = [&](int jc, int nk, int j0, uint32_t (&vlo)[16], uint32_t (&vhi)[16]) {
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const int j = j0 + u;                           // warp-uniform
-            const uint32_t o = __shfl_sync(0xFFFFFFFFu, j < 32 ? off[0] : off[1], j & 31);
-            vlo[u] = 0u; vhi[u] = 0u;
-            if (j < nk && !(has_new && jc + j == pos)) {
-                const uint32_t* vr = reinterpret_cast<const uint32_t*>(a.v_cache + o);
-                if (D == 2) vlo[u] = vr[lane];
-                else { const uint2 v2 = *reinterpret_cast<const uint2*>(vr + 2 * lane); vlo[u] = v2.x; vhi[u] = v2.y; }
-            }
-        }
-    };
-    uint32_t vplo[NVP / 16][16], vphi[NVP / 16][16];
-    {   // first chunk, before the dependency wait
-        const int nk0 = min(64, j_end - j_begin);
-        load_keys(j_begin, nk0);
-#pragma unroll
-        for (int b = 0; b < NVP / 16; ++b) load_v16(j_begin, nk0, 16 * b, vplo[b], vphi[b]);
-    }
-    pdl_sync();
-    stamp(a.trace, 1, 3);
-
-    // rotate D values held by this lane (dims d0 ..): optional RMS norm with gamma nw, then RoPE at `pos`
-    auto norm_rope = [&](float (&v)[D], const float* nw) {
-        if (nw) {                            // per-head RMS norm, sum of squares in double (src/cli/main.cpp:3294-3299)
-            double ss = 0.0;
-#pragma unroll
-            for (int i = 0; i < D; ++i) ss += static_cast<double>(v[i]) * v[i];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-            const float inv = 1.0f / sqrtf(static_cast<float>(ss / HD) + a.eps);
-#pragma unroll
-            for (int i = 0; i < D; ++i) v[i] = v[i] * inv * nw[d0 + i];
-        }
-        const float* cs = a.cos_tab + static_cast<size_t>(pos) * half;
-        const float* sn = a.sin_tab + static_cast<size_t>(pos) * half;
-        if (!a.neox) {                       // pairs (2 i, 2 i + 1): both in this lane
-#pragma unroll
-            for (int i = 0; i < D; i += 2) {
-                const int pi = (d0 + i) >> 1;
-                const float c = cs[pi], sv = sn[pi], v0 = v[i], v1 = v[i + 1];
-                v[i] = v0 * c - v1 * sv; v[i + 1] = v0 * sv + v1 * c;
-            }
-        } else {                             // pairs (i, i + half): the partner dims live 16 lanes away
-#pragma unroll
-            for (int i = 0; i < D; ++i) {
-                const float other = __shfl_xor_sync(0xFFFFFFFFu, v[i], 16);
-                const int pi = (d0 + i) & (half - 1);
-                const float c = cs[pi], sv = sn[pi];
-                v[i] = lane < 16 ? v[i] * c - other * sv : other * sv + v[i] * c;
-            }
-        }
-    };
-
-    {   // q of this warp's head
-        const float* q = a.q + (static_cast<size_t>(t) * a.n_head + head) * HD + d0;
-        float v[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) v[i] = q[i];
-        if (a.fuse) norm_rope(v, a.q_norm);
-#pragma unroll
-        for (int i = 0; i < D; ++i) qs[d0 + i] = v[i] * scale;
-    }
-    if (has_new) {
-        float kv[D], vv[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) { kv[i] = a.k_new[static_cast<size_t>(h) * HD + d0 + i]; vv[i] = a.v_new[static_cast<size_t>(h) * HD + d0 + i]; }
-        norm_rope(kv, a.k_norm);
-        const int page = a.block_table[pos / a.page], slot = pos % a.page;
-        const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + d0;
-#pragma unroll
-        for (int i = 0; i < D; i += 2) {
-            const __nv_bfloat162 kb = __floats2bfloat162_rn(kv[i], kv[i + 1]), vb = __floats2bfloat162_rn(vv[i], vv[i + 1]);
-            fresh[(d0 + i) >> 1] = *reinterpret_cast<const uint32_t*>(&kb);
-            fresh[KW + ((d0 + i) >> 1)] = *reinterpret_cast<const uint32_t*>(&vb);
-            if (w == 0) {                    // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
-                *reinterpret_cast<__nv_bfloat162*>(a.k_cache_w + o + i) = kb;
-                *reinterpret_cast<__nv_bfloat162*>(a.v_cache_w + o + i) = vb;
-            }
-        }
-    }
-    __syncwarp();
-    stamp(a.trace, 2, 3);
-
-    float m = -INFINITY, l = 0.0f, acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.0f;
-    // acc += p_j * V[j] for 16 keys whose V words are in vlo / vhi (the new token's row comes from `fresh`)
-    auto pv16 = [&](int jc, int nk, int j0, const uint32_t (&vlo)[16], const uint32_t (&vhi)[16], float p0, float p1) {
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const int j = j0 + u;
-            const float pj = j < nk ? __shfl_sync(0xFFFFFFFFu, j < 32 ? p0 : p1, j & 31) : 0.0f;
-            uint32_t lo = vlo[u], hi = vhi[u];
-            if (has_new && jc + j == pos) { lo = fresh[KW + (d0 >> 1)]; hi = D == 4 ? fresh[KW + (d0 >> 1) + 1] : 0u; }
-            acc[0] = fmaf(pj, __uint_as_float(lo << 16), acc[0]);
-            acc[1] = fmaf(pj, __uint_as_float(lo & 0xFFFF0000u), acc[1]);
-            if (D == 4) {
-                acc[D - 2] = fmaf(pj, __uint_as_float(hi << 16), acc[D - 2]);
-                acc[D - 1] = fmaf(pj, __uint_as_float(hi & 0xFFFF0000u), acc[D - 1]);
-            }
-        }
-    };
-    for (int jc = j_begin; jc < j_end; jc += 64) {
-        const int nk = min(64, j_end - jc);
-        if (jc != j_begin) load_keys(jc, nk);
-        float sc[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (is_new[u]) {                 // the new token's key is in shared memory, not yet in the cache
-#pragma unroll
-                for (int c = 0; c < HD / 8; ++c) kw[u][c] = reinterpret_cast<const uint4*>(fresh)[c];
-            }
-            float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                const uint4 k4 = kw[u][c];
-                const float4 qa = *reinterpret_cast<const float4*>(qs + 8 * c), qb = *reinterpret_cast<const float4*>(qs + 8 * c + 4);
-                s0 = fmaf(qa.x, __uint_as_float(k4.x << 16), fmaf(qa.y, __uint_as_float(k4.x & 0xFFFF0000u), s0));
-                s1 = fmaf(qa.z, __uint_as_float(k4.y << 16), fmaf(qa.w, __uint_as_float(k4.y & 0xFFFF0000u), s1));
-                s0 = fmaf(qb.x, __uint_as_float(k4.z << 16), fmaf(qb.y, __uint_as_float(k4.z & 0xFFFF0000u), s0));
-                s1 = fmaf(qb.z, __uint_as_float(k4.w << 16), fmaf(qb.w, __uint_as_float(k4.w & 0xFFFF0000u), s1));
-            }
-            sc[u] = live[u] ? s0 + s1 : -INFINITY;
-        }
-        stamp(a.trace, 3, 3);
-        float mx = fmaxf(sc[0], sc[1]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        const float mn = fmaxf(m, mx);
-        const float p0 = expf(sc[0] - mn), p1 = expf(sc[1] - mn);
-        const float sum = wsum(p0 + p1);
-        const float corr = expf(m - mn);
-        stamp(a.trace, 4, 3);
-        l = l * corr + sum; m = mn;
-#pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] *= corr;
-        int j0 = 0;
-        if (jc == j_begin) {                 // prefetched part of the first chunk
-#pragma unroll
-            for (int b = 0; b < NVP / 16; ++b) pv16(jc, nk, 16 * b, vplo[b], vphi[b], p0, p1);
-            j0 = NVP;
-        }
-        for (; j0 < nk; j0 += 16) {
-            uint32_t vlo[16], vhi[16];
-            load_v16(jc, nk, j0, vlo, vhi);
-            pv16(jc, nk, j0, vlo, vhi, p0, p1);
-        }
-    }
-    float* pg = a.partial + ((static_cast<size_t>(t) * a.n_head + head) * a.n_splits + split) * (HD + 2);
-    if (lane == 0) { pg[0] = m; pg[1] = l; }
-#pragma unroll
-    for (int i = 0; i < D; ++i) pg[2 + d0 + i] = acc[i];
-    stamp(a.trace, 7, 3);
-}
-
 // grid (n_head, n_tok): merge the visible splits, normalise, write out[t][head][hd].
 __global__ void attn_combine_kernel(AttnPagedArgs a) {
     stamp(a.trace2, 0, 4);
@@ -623,10 +405,6 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     dim3 grid(a.n_kv, a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
     size_t smem = 0;
-    static const bool use_warp_kernel = getenv("GGB_ATTN_WARP") != nullptr;     // GGB_ATTN_WARP=1: the warp-per-head kernel (being validated)
-    if (use_warp_kernel && (hd == 64 || hd == 128)) {
-        e = hd == 64 ? launch_pdl(c, attn_warp_kernel<64>, grid, dim3(32 * G), 0, s, a) : launch_pdl(c, attn_warp_kernel<128>, grid, dim3(32 * G), 0, s, a);
-    } else
 #define GGB_ATTN_CASE(HD)                                                                                              \
     {                                                                                                                  \
         smem = sizeof(uint32_t) * (64 * (HD / 2) + 64 * (HD / 2 + 1)) + sizeof(float) * (8 * HD + 8 * 64 + 24 + 12) + 2 * 2 * HD + 16; \
