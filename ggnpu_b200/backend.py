@@ -82,6 +82,12 @@ class MoeParams(C.Structure):
                 ("sel_out", C.c_void_p), ("w_out", C.c_void_p)]
 
 
+class DeltaNetParams(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("mixed", "zgate", "araw", "braw", "conv_w", "ssm_a", "dt_bias", "ssm_norm",
+                                           "conv_state", "rec_state", "out")] + \
+               [("n_khead", C.c_int), ("n_vhead", C.c_int), ("sk", C.c_int), ("conv_k", C.c_int), ("rms_eps", C.c_float)]
+
+
 class ModelDesc(C.Structure):
     _fields_ = [("n_layer", C.c_int), ("hidden", C.c_int), ("n_head", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
                 ("ffn", C.c_int), ("vocab", C.c_int), ("ctx", C.c_int), ("rms_eps", C.c_float), ("rope_base", C.c_float),
@@ -95,7 +101,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device",
 ]
 
 _lib = None
@@ -137,6 +143,7 @@ def load_library() -> C.CDLL:
     L.ggb_attn_paged_device.argtypes = [vp, C.POINTER(AttnPagedParams)]
     L.ggb_attn_prefill_device.argtypes = [vp, C.POINTER(AttnPagedParams), i32]
     L.ggb_moe_ffn_device.argtypes = [vp, C.POINTER(MoeParams)]
+    L.ggb_deltanet_step_device.argtypes = [vp, C.POINTER(DeltaNetParams)]
     L.ggb_tp_unique_id.argtypes = [vp]
     L.ggb_tp_init.argtypes = [vp, vp, i32, i32]
     L.ggb_tp_all_reduce_device.argtypes = [vp, vp, i64]
@@ -306,6 +313,11 @@ class CudaBackend:
         """Mixture-of-experts FFN of one token; keyword arguments are the fields of ggb_moe_params (device pointers / weights)."""
         p = MoeParams(**{k: (v if v is not None else None) for k, v in kw.items()})
         return Status(self.lib.ggb_moe_ffn_device(self.h, C.byref(p)))
+
+    def deltanet_step_device(self, **kw) -> Status:
+        """One token of a Gated DeltaNet layer; keyword arguments are the fields of ggb_deltanet_params (device pointers)."""
+        p = DeltaNetParams(**kw)
+        return Status(self.lib.ggb_deltanet_step_device(self.h, C.byref(p)))
 
     # ---- tensor-parallel group (one process per GPU, NCCL underneath) ----
     tp_rank, tp_size = 0, 1

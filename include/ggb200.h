@@ -255,6 +255,31 @@ typedef struct ggb_moe_params {
 } ggb_moe_params;
 GGB_API int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p);
 
+/* One token of a Gated DeltaNet (linear attention) layer after its projections, the qwen35 / qwen35moe
+ * branch of the reference's layer loop, src/cli/main.cpp:2925-3023: causal depthwise conv (conv_k taps) +
+ * SiLU over mixed = [q: n_khead*sk | k: n_khead*sk | v: n_vhead*sk] with a rolling state of the previous
+ * conv_k - 1 inputs; per key head L2 norm of q and k (q also / sqrt(sk)); per value head h (key head
+ * h % n_khead): beta = sigmoid(braw), g = exp(ssm_a * softplus(araw + dt_bias)), S *= g, pred = S^T k,
+ * delta = beta (v - pred), S += k (x) delta, o = S^T q; out = rms_norm(o) * ssm_norm * silu(zgate).
+ * All pointers are device memory (F32); conv_state [(conv_k-1)][conv_dim] and rec_state
+ * [n_vhead][sk][sk] are updated in place; asynchronous on the handle's stream.  sk is 64 or 128. */
+typedef struct ggb_deltanet_params {
+    const float* mixed;
+    const float* zgate;
+    const float* araw;
+    const float* braw;
+    const float* conv_w;     /* [conv_dim][conv_k], newest tap last */
+    const float* ssm_a;      /* [n_vhead], stored as -exp(A_log) */
+    const float* dt_bias;
+    const float* ssm_norm;   /* [sk] */
+    float* conv_state;
+    float* rec_state;
+    float* out;              /* [n_vhead * sk] */
+    int n_khead, n_vhead, sk, conv_k;
+    float rms_eps;
+} ggb_deltanet_params;
+GGB_API int ggb_deltanet_step_device(ggb_handle h, const ggb_deltanet_params* p);
+
 /* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
 GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */

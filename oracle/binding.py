@@ -62,6 +62,7 @@ class Oracle:
         L.ggo_matmul_exact.argtypes = [_f32p, C.c_int, C.c_int, _u8p, C.c_uint32, C.c_int, C.c_int, _f32p, C.c_int]
         L.ggo_moe_ffn.argtypes = [_f32p, C.c_int, _f32p, C.c_int, C.c_int, C.c_int, _u8p, _u8p, C.c_uint32, _u8p, C.c_uint32,
                                   _u8p, _u8p, C.c_uint32, _u8p, C.c_uint32, C.c_int, _f32p, _f32p, C.c_void_p, _f32p]
+        L.ggo_deltanet_step.argtypes = [_f32p] * 11 + [C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]
         L.ggo_matmul_cpu_ref_k.argtypes = [_f32p, C.c_int, _u8p, C.c_uint32, C.c_int, C.c_int, _f32p]
         L.ggo_matmul_f32_kn.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
         L.ggo_rms_norm.argtypes = [_f32p, _f32p, C.c_int, C.c_float, _f32p]
@@ -192,6 +193,19 @@ class Oracle:
                                   ids.ctypes.data_as(C.c_void_p), _fp(w))
         assert rc == 0
         return out, ids, (w if shared is not None else w[:top_k])
+
+    def deltanet_step(self, mixed, zgate, araw, braw, conv_w, ssm_a, dt_bias, ssm_norm, conv_state, rec_state,
+                      n_khead, n_vhead, sk, conv_k, rms_eps):
+        """One token of a Gated DeltaNet layer (src/cli/main.cpp:2925-3023); conv_state and rec_state (float32,
+        C-contiguous) are updated in place.  Returns out[n_vhead * sk]."""
+        f = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+        assert conv_state.dtype == np.float32 and conv_state.flags.c_contiguous and rec_state.dtype == np.float32 and rec_state.flags.c_contiguous
+        out = np.empty(n_vhead * sk, np.float32)
+        args = [f(mixed), f(zgate), f(araw), f(braw), f(conv_w), f(ssm_a), f(dt_bias), f(ssm_norm)]
+        rc = self.lib.ggo_deltanet_step(*[_fp(a) for a in args], _fp(conv_state), _fp(rec_state), _fp(out),
+                                        n_khead, n_vhead, sk, conv_k, rms_eps)
+        assert rc == 0
+        return out
 
     def rope_cpu_ref(self, x, n_dims, offset, freq_scale, rope_dims):
         v = np.array(x, dtype=np.float32, copy=True)

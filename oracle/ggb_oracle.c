@@ -596,6 +596,74 @@ GGO_API int ggo_moe_ffn(const float* x, int hidden, const float* router, int n_e
     return rc;
 }
 
+/* One token of a Gated DeltaNet (linear attention) layer after its projections,
+ * src/cli/main.cpp:2925-3023 (qwen35 / qwen35moe branch).  PARITY UNPINNED at unit level, like
+ * ggo_moe_ffn: the reference keeps the block inside main().
+ *   conv      :2925-2941  causal depthwise conv1d (conv_k taps, newest = this token) + SiLU; the state
+ *                         holds the previous conv_k - 1 inputs [tap][channel] and is rolled
+ *   q, k      :2956-2968  per key head L2-normalised over sk (eps 1e-6); q also scaled by 1/sqrt(sk)
+ *   per V head:2976-3011  key head = h % n_khead; beta = sigmoid(b); g = exp(ssm_a * softplus(a + dt_bias));
+ *                         S *= g; pred = S^T k; delta = beta (v - pred); S += k (x) delta; o = S^T q
+ *   output    :3016-3023  rms_norm(o) * ssm_norm * silu(z)
+ * mixed = [q: n_khead*sk | k: n_khead*sk | v: n_vhead*sk] of this token (the attn_qkv projection). */
+GGO_API int ggo_deltanet_step(const float* mixed, const float* zgate, const float* araw, const float* braw,
+                              const float* conv_w, const float* ssm_a, const float* dt_bias, const float* ssm_norm,
+                              float* conv_state, float* rec_state, float* out,
+                              int n_khead, int n_vhead, int sk, int conv_k, float rms_eps) {
+    const int key_dim = n_khead * sk, value_dim = n_vhead * sk, conv_dim = 2 * key_dim + value_dim, ckm1 = conv_k - 1;
+    float* conv = (float*)malloc(sizeof(float) * (size_t)conv_dim);
+    float* qn = (float*)malloc(sizeof(float) * (size_t)key_dim);
+    float* kn = (float*)malloc(sizeof(float) * (size_t)key_dim);
+    float* pred = (float*)malloc(sizeof(float) * (size_t)sk);
+    float* delta = (float*)malloc(sizeof(float) * (size_t)sk);
+    float* oh = (float*)malloc(sizeof(float) * (size_t)sk);
+    for (int ch = 0; ch < conv_dim; ++ch) {
+        float acc = conv_w[ch * conv_k + ckm1] * mixed[ch];
+        for (int t = 0; t < ckm1; ++t) acc += conv_w[ch * conv_k + t] * conv_state[(size_t)t * conv_dim + ch];
+        conv[ch] = acc / (1.0f + expf(-acc));
+        for (int t = 0; t < ckm1 - 1; ++t) conv_state[(size_t)t * conv_dim + ch] = conv_state[(size_t)(t + 1) * conv_dim + ch];
+        if (ckm1 > 0) conv_state[(size_t)(ckm1 - 1) * conv_dim + ch] = mixed[ch];
+    }
+    const float *qc = conv, *kc = conv + key_dim, *vc = conv + 2 * key_dim;
+    for (int h = 0; h < n_khead; ++h) {
+        const float *qh = qc + h * sk, *kh = kc + h * sk;
+        float sq = 0.0f, s2 = 0.0f;
+        for (int i = 0; i < sk; ++i) { sq += qh[i] * qh[i]; s2 += kh[i] * kh[i]; }
+        const float rq = (1.0f / sqrtf(sq + 1e-6f)) / sqrtf((float)sk);
+        const float rk = 1.0f / sqrtf(s2 + 1e-6f);
+        for (int i = 0; i < sk; ++i) { qn[h * sk + i] = qh[i] * rq; kn[h * sk + i] = kh[i] * rk; }
+    }
+    for (int h = 0; h < n_vhead; ++h) {
+        const int kh = h % n_khead;
+        const float *qh = qn + kh * sk, *khp = kn + kh * sk, *vh = vc + h * sk;
+        const float beta = 1.0f / (1.0f + expf(-braw[h]));
+        const float a = araw[h] + dt_bias[h];
+        const float sp = (a > 20.0f) ? a : log1pf(expf(a));
+        const float g = expf(ssm_a[h] * sp);
+        float* Sh = rec_state + (size_t)h * sk * sk;
+        for (int v = 0; v < sk; ++v) { pred[v] = 0.0f; oh[v] = 0.0f; }
+        for (int kk = 0; kk < sk; ++kk) {
+            const float kval = khp[kk];
+            float* row = Sh + (size_t)kk * sk;
+            for (int v = 0; v < sk; ++v) { row[v] *= g; pred[v] += row[v] * kval; }
+        }
+        for (int v = 0; v < sk; ++v) delta[v] = beta * (vh[v] - pred[v]);
+        for (int kk = 0; kk < sk; ++kk) {
+            const float kval = khp[kk], qval = qh[kk];
+            float* row = Sh + (size_t)kk * sk;
+            for (int v = 0; v < sk; ++v) { row[v] += kval * delta[v]; oh[v] += row[v] * qval; }
+        }
+        const float* zh = zgate + h * sk;
+        float ss = 0.0f;
+        for (int v = 0; v < sk; ++v) ss += oh[v] * oh[v];
+        const float r = 1.0f / sqrtf(ss / (float)sk + rms_eps);
+        float* od = out + h * sk;
+        for (int v = 0; v < sk; ++v) od[v] = (oh[v] * r * ssm_norm[v]) * (zh[v] / (1.0f + expf(-zh[v])));
+    }
+    free(conv); free(qn); free(kn); free(pred); free(delta); free(oh);
+    return 0;
+}
+
 /* One forward over n_tok tokens at absolute positions pos..pos+n_tok-1,
  * writing the KV cache and (if logits != NULL) the logits of the LAST row
  * (main.cpp:3593-3598).  Matmuls follow the exact path (ggo_matmul_exact).
