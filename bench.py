@@ -504,6 +504,49 @@ def run_micro_moe(args):
     b.close()
 
 
+def run_micro_deltanet(args):
+    """Gated DeltaNet step at the qwen35moe shape (16 key / 32 value heads of 128, conv 4): per layer and token the
+    4 MB recurrent state is read and written once.  30 layers' states (60 MB read + 60 MB written per pass) are
+    stepped in turn, so the state comes from HBM rather than L2 only partly (126 MB L2).
+        python bench.py --micro-deltanet"""
+    import torch
+    from ggnpu_b200.backend import CudaBackend
+    b = CudaBackend(0)
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", 0))
+    peak, peak_kind = peaks()
+    nK, nV, sk, ck, layers = 16, 32, 128, 4, 30
+    cd = 2 * nK * sk + nV * sk
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *shape: torch.randn(*shape, generator=g, device="cuda")
+    conv_w, ssm_a, dt, norm = 0.3 * rn(cd, ck), -torch.exp(0.5 * rn(nV)), rn(nV), 1 + 0.1 * rn(sk)
+    cs = [torch.zeros(ck - 1, cd, device="cuda") for _ in range(layers)]
+    S = [torch.zeros(nV, sk, sk, device="cuda") for _ in range(layers)]
+    mixed, z, ar, br, out = rn(cd), rn(nV * sk), rn(nV), rn(nV), torch.empty(nV * sk, device="cuda")
+    torch.cuda.synchronize()
+
+    def one(l):
+        b.deltanet_step_device(mixed=mixed.data_ptr(), zgate=z.data_ptr(), araw=ar.data_ptr(), braw=br.data_ptr(), conv_w=conv_w.data_ptr(),
+                               ssm_a=ssm_a.data_ptr(), dt_bias=dt.data_ptr(), ssm_norm=norm.data_ptr(), conv_state=cs[l].data_ptr(),
+                               rec_state=S[l].data_ptr(), out=out.data_ptr(), n_khead=nK, n_vhead=nV, sk=sk, conv_k=ck, rms_eps=1e-6)
+
+    for l in range(layers):
+        one(l)
+    b.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = layers * args.reps
+    e0.record(stream)
+    for i in range(n):
+        one(i % layers)
+    e1.record(stream)
+    b.sync()
+    us = e0.elapsed_time(e1) * 1e3 / n
+    alg = 2 * nV * sk * sk * 4 + 2 * (ck - 1) * cd * 4 + cd * (ck + 2) * 4 + 2 * nV * sk * 4
+    print(json.dumps({"micro": "deltanet_step", "n_khead": nK, "n_vhead": nV, "sk": sk, "conv_k": ck, "us_per_token_layer": us,
+                      "launches_per_call": 2, "alg_bytes": alg, "gbs": alg / us / 1e3, "frac_of_hbm_peak": alg / us / 1e3 / peak,
+                      "peak_source": peak_kind}), flush=True)
+    b.close()
+
+
 def run_micro_allreduce(args):
     """Latency of the tensor-parallel all-reduce at decode message sizes, peer-memory one-shot kernel vs
     NCCL, back to back on the compute stream (run under torchrun, one process per GPU)."""
@@ -637,6 +680,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=128, help="prompt tokens before the timed decode (128 = the benchmark config)")
     ap.add_argument("--prefill-long", type=int, default=2048, help="token count of the long-prompt prefill figure")
+    ap.add_argument("--micro-deltanet", action="store_true", help="Gated DeltaNet step microbenchmark (qwen35moe shape)")
     ap.add_argument("--micro-moe", action="store_true", help="MoE FFN decode microbenchmark (qwen35moe expert shapes)")
     ap.add_argument("--moe-experts", type=int, default=256)
     ap.add_argument("--micro-allreduce", action="store_true", help="latency of the tensor-parallel all-reduce (torchrun)")
@@ -657,6 +701,9 @@ def main():
         return
     if args.micro_allreduce:
         run_micro_allreduce(args)
+        return
+    if args.micro_deltanet:
+        run_micro_deltanet(args)
         return
     if args.micro_moe:
         run_micro_moe(args)
