@@ -234,9 +234,12 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
                 int64_t blk0 = (g_begin + rg - (mi == 0 ? 0 : a.cat[mi - 1].g_start)) * nb;
                 if (a.sel_mode == 1) {             // gathered rows: logical group -> (chosen expert, group inside it)
                     const int64_t lg = g_begin + rg;
-                    blk0 = (static_cast<int64_t>(a.sel[lg / a.sel_groups]) * a.sel_groups + lg % a.sel_groups) * a.w.nb;
+                    const int e = a.sel[lg / a.sel_groups];
+                    if (e < 0) continue;           // expert held by another rank (expert parallel): nothing to stream, the consumers skip it too
+                    blk0 = (static_cast<int64_t>(e) * a.sel_groups + lg % a.sel_groups) * a.w.nb;
                 }
                 for (int ti = member; ti < tprg; ti += a.ws) {
+                    if (a.sel_mode == 2 && a.sel[ti - (ti >= a.spr) * a.spr] < 0) continue;       // K range of an expert on another rank
                     const int s = lane * a.P + st;
                     if (throttled && (rg != team || ti != member)) {
                         uint32_t spins = 0;
@@ -401,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
     bool ok = true;
     int parity = 0;
     for (int rg = team; rg < n_rg; rg += n_teams, parity ^= 1) {
+        if (a.sel_mode == 1 && a.sel[(g_begin + rg) / a.sel_groups] < 0) continue;      // rows of an expert on another rank: left unwritten
         const int mi = which(g_begin + rg);
         const bool is_q6 = (mi == 0 ? a.w.type : a.cat[mi - 1].w.type) == T_Q6_K;
         // accumulators in the C-fragment layout: [matrix][row g / g+8][column 2t / 2t+1], and this
@@ -409,6 +413,7 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
         float F0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, F1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         float MN0[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, MN1[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};   // [row g / g+8][activation row]
         for (int ti = member; ti < tprg; ti += a.ws) {
+            if (a.sel_mode == 2 && a.sel[ti - (ti >= a.spr) * a.spr] < 0) continue;
             const int s = warp * a.P + st;
             if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
             if (++st == a.P) { st = 0; ph ^= 1; }

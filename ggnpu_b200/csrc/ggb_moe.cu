@@ -45,8 +45,10 @@ __global__ void moe_logits_kernel(const float* __restrict__ x, const float* __re
 
 // grid 1, block 256: k rounds of block-wide arg-max over the logits (n_expert <= 1024), softmax over the chosen,
 // shared-expert gate.
-__global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, int top_k, int has_gate,
-                                int32_t* __restrict__ sel, float* __restrict__ w) {
+// Expert parallel: sel / w describe this rank's share -- experts outside [ep_first, ep_first + ep_local) get
+// id -1 (the GEMV kernels skip them) and weight 0; sel_glob / w_glob (optional) keep the global choice.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, int top_k, int has_gate, int ep_first, int ep_local,
+                                int32_t* __restrict__ sel, float* __restrict__ w, int32_t* __restrict__ sel_glob, float* __restrict__ w_glob) {
     __shared__ float logit[1024];
     __shared__ float red_v[8];
     __shared__ int red_i[8];
@@ -74,7 +76,9 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
         if (threadIdx.x == 0) {
             for (int q = 1; q < 8; ++q)
                 if (red_v[q] > red_v[0] || (red_v[q] == red_v[0] && red_i[q] < red_i[0])) { red_v[0] = red_v[q]; red_i[0] = red_i[q]; }
-            sel[j] = red_i[0];
+            const int e = red_i[0];
+            if (sel_glob) sel_glob[j] = e;
+            sel[j] = (e >= ep_first && e < ep_first + ep_local) ? e - ep_first : -1;
             chosen[j] = red_v[0];
             logit[red_i[0]] = -INFINITY;
         }
@@ -84,7 +88,12 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
         const float mx = chosen[0];
         float sum = 0.0f;
         for (int j = 0; j < top_k; ++j) { chosen[j] = expf(chosen[j] - mx); sum += chosen[j]; }
-        for (int j = 0; j < top_k; ++j) w[j] = chosen[j] / sum;
+        for (int j = 0; j < top_k; ++j) {
+            const float wj = chosen[j] / sum;
+            if (w_glob) w_glob[j] = wj;
+            w[j] = sel[j] >= 0 ? wj : 0.0f;
+        }
+        if (w_glob) w_glob[top_k] = w[top_k];
     }
 }
 
@@ -101,14 +110,21 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     if (p->hidden <= 0 || p->hidden % 256 || p->eff <= 0 || p->eff % 256 || p->n_expert < 1 || p->n_expert > 1024 || p->top_k < 1 ||
         p->top_k > kMaxTopK || p->top_k > p->n_expert)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden and eff must be multiples of 256, n_expert <= 1024, top_k <= 16");
+    // expert parallel: this rank holds experts [ep_first, ep_first + ep_local) of the n_expert the router knows
+    const bool ep = p->ep_local > 0;
+    const int n_local = ep ? p->ep_local : p->n_expert, ep_first = ep ? p->ep_first : 0;
+    if (ep && (p->ep_first < 0 || p->ep_first + p->ep_local > p->n_expert || h->tp_size < 2))
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert-parallel range outside the router's experts, or the handle is not in a group");
     const DeviceWeight *ge = reinterpret_cast<const DeviceWeight*>(p->gate_exps), *ue = reinterpret_cast<const DeviceWeight*>(p->up_exps),
                        *de = reinterpret_cast<const DeviceWeight*>(p->down_exps);
-    if (ge->w.N != static_cast<int64_t>(p->n_expert) * p->eff || ue->w.N != ge->w.N || ge->w.K != p->hidden || ue->w.K != p->hidden ||
-        de->w.N != static_cast<int64_t>(p->n_expert) * p->hidden || de->w.K != p->eff || ge->w.type != ue->w.type)
+    if (ge->w.N != static_cast<int64_t>(n_local) * p->eff || ue->w.N != ge->w.N || ge->w.K != p->hidden || ue->w.K != p->hidden ||
+        de->w.N != static_cast<int64_t>(n_local) * p->hidden || de->w.K != p->eff || ge->w.type != ue->w.type)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be [n_expert * eff][hidden] (gate, up) and [n_expert * hidden][eff] (down)");
     if (ge->w.layout != 1 || ue->w.layout != 1 || de->w.layout != 1)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be Q4_K or Q6_K in the tensor-core layout");
-    const bool shared = p->sh_gate && p->sh_up && p->sh_down;
+    // expert parallel: rank 0 alone adds the residual and the shared expert; the all-reduce spreads them
+    const bool lead = !ep || h->tp_rank == 0;
+    const bool shared = p->sh_gate && p->sh_up && p->sh_down && lead;
     const DeviceWeight *sg = reinterpret_cast<const DeviceWeight*>(p->sh_gate), *su = reinterpret_cast<const DeviceWeight*>(p->sh_up),
                        *sd = reinterpret_cast<const DeviceWeight*>(p->sh_down);
     if (shared && (sg->w.N != p->eff_sh || su->w.N != p->eff_sh || sg->w.K != p->hidden || su->w.K != p->hidden || sd->w.N != p->hidden ||
@@ -132,11 +148,10 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
                                gate_vec, logits);
     h->launches++;
     if (e != cudaSuccess) return cuda_status(h, e, "moe router logits");
-    e = launch_pdl(h, moe_topk_kernel, dim3(1), dim3(256), 0, s, static_cast<const float*>(logits), p->n_expert, p->top_k, gate_vec ? 1 : 0, sel, w);
+    e = launch_pdl(h, moe_topk_kernel, dim3(1), dim3(256), 0, s, static_cast<const float*>(logits), p->n_expert, p->top_k, gate_vec ? 1 : 0,
+                   ep_first, n_local, sel, w, p->sel_out, p->w_out);
     h->launches++;
     if (e != cudaSuccess) return cuda_status(h, e, "moe top-k");
-    if (p->sel_out) cudaMemcpyAsync(p->sel_out, sel, sizeof(int32_t) * p->top_k, cudaMemcpyDeviceToDevice, s);
-    if (p->w_out) cudaMemcpyAsync(p->w_out, w, sizeof(float) * (p->top_k + 1), cudaMemcpyDeviceToDevice, s);
 
     GemvArgs a{};
     a.w = ge->w; a.w2 = ue->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act; a.ldc = p->top_k * p->eff; a.epi = EPI_SWIGLU;
@@ -146,7 +161,7 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
 
     a = GemvArgs{};
     a.w = de->w; a.x = act; a.M = 1; a.lda = p->top_k * p->eff; a.y = p->y; a.ldc = p->hidden;
-    a.epi = p->resid ? EPI_RESIDUAL : EPI_STORE; a.resid = p->resid;
+    a.epi = (p->resid && lead) ? EPI_RESIDUAL : EPI_STORE; a.resid = lead ? p->resid : nullptr;
     a.sel = sel; a.sel_mode = 2; a.sel_count = p->top_k; a.sel_rows = p->hidden; a.xscale = w; a.xscale_run = p->eff;
     st = launch_gemv_mma(h, a, s);
     if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert down shape not covered") : st;
@@ -162,5 +177,6 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
         st = launch_gemv(h, a, s);
         if (st != GGB_OK) return st;
     }
+    if (ep) return tp_all_reduce(h, p->y, static_cast<size_t>(p->hidden), s);      // sum of the ranks' expert shares (+ rank 0's residual, shared expert)
     return GGB_OK;
 }

@@ -252,6 +252,12 @@ typedef struct ggb_moe_params {
     int hidden, eff, eff_sh, n_expert, top_k;
     int32_t* sel_out;
     float* w_out;
+    /* Expert parallel (ep_local > 0; the handle must belong to a group, ggb_tp_init): this rank's expert tensors
+     * hold experts [ep_first, ep_first + ep_local) only; the router (replicated) still scores all n_expert.  Each
+     * rank streams just the chosen experts it holds, rank 0 adds the residual and the shared expert, and the
+     * partial rows are summed over the group (the batch-1 form of dispatch / combine), so every rank ends with
+     * the same y.  sel_out / w_out report the global choice on every rank. */
+    int ep_first, ep_local;
 } ggb_moe_params;
 GGB_API int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p);
 

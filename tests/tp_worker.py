@@ -100,6 +100,47 @@ def main():
         dist.all_gather(both, mine)
         assert all(torch.equal(both[0], x) for x in both[1:]), name
         gm.close()
+    # ---- expert parallel MoE FFN: each rank holds half of the experts, the router is replicated ----
+    from ggnpu_b200.backend import Status
+    H, eff, nE, k, eff_sh = 512, 256, 64, 8, 512
+    qz = lambda shape, t, seed: S.quantize(torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * 0.05, t).numpy()
+    ge, ue, de = qz((nE * eff, H), S.Q4_K, 1), qz((nE * eff, H), S.Q4_K, 2), qz((nE * H, eff), S.Q6_K, 3)
+    sg, su, sd = qz((eff_sh, H), S.Q4_K, 4), qz((eff_sh, H), S.Q4_K, 5), qz((H, eff_sh), S.Q6_K, 6)
+    rng = np.random.default_rng(77)
+    router = (0.05 * rng.standard_normal((nE, H))).astype(np.float32)
+    sgi = (0.05 * rng.standard_normal(H)).astype(np.float32)
+    nl = nE // size
+    cut = lambda raw, rows_per_expert: np.ascontiguousarray(raw.reshape(nE, -1)[rank * nl:(rank + 1) * nl]).reshape(-1)
+    hg, hu, hd = (b.upload_weight(S.Q4_K, cut(ge, eff), nl * eff, H), b.upload_weight(S.Q4_K, cut(ue, eff), nl * eff, H),
+                  b.upload_weight(S.Q6_K, cut(de, H), nl * H, eff))
+    hs = [b.upload_weight(S.Q4_K, sg, eff_sh, H), b.upload_weight(S.Q4_K, su, eff_sh, H), b.upload_weight(S.Q6_K, sd, H, eff_sh)]
+    dev = f"cuda:{rank}"
+    drt, dgi = torch.from_numpy(router).to(dev), torch.from_numpy(sgi).to(dev)
+    if rank == 0:
+        from oracle.binding import Oracle
+        oracle = Oracle()
+    for trial in range(6):
+        x = rng.standard_normal(H).astype(np.float32)
+        resid = rng.standard_normal(H).astype(np.float32)
+        dx, dr = torch.from_numpy(x).to(dev), torch.from_numpy(resid).to(dev)
+        dy = torch.full((H,), float("nan"), device=dev)
+        dsel = torch.full((k,), -1, device=dev, dtype=torch.int32)
+        torch.cuda.synchronize()
+        st = b.moe_ffn_device(x=dx.data_ptr(), resid=dr.data_ptr(), y=dy.data_ptr(), router=drt.data_ptr(), gate_exps=hg, up_exps=hu,
+                              down_exps=hd, sh_gate=hs[0], sh_up=hs[1], sh_down=hs[2], sh_gate_inp=dgi.data_ptr(), hidden=H, eff=eff,
+                              eff_sh=eff_sh, n_expert=nE, top_k=k, sel_out=dsel.data_ptr(), w_out=None, ep_first=rank * nl, ep_local=nl)
+        assert st == Status.OK, b.last_error_message()
+        b.sync()
+        got = dy.cpu().numpy()
+        if rank == 0:
+            want, ids, w = oracle.moe_ffn(x, router, k, eff, ge, ue, S.Q4_K, de, S.Q6_K, shared=(sg, su, S.Q4_K, sd, S.Q6_K, eff_sh), sh_gate_inp=sgi)
+            assert np.array_equal(dsel.cpu().numpy(), ids)
+            rel = np.linalg.norm(got - (want + resid)) / np.linalg.norm(want + resid)
+            assert rel <= 2e-5, ("expert parallel", trial, rel)
+        mine = torch.from_numpy(got)
+        both = [torch.empty_like(mine) for _ in range(size)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(both[0], t) for t in both[1:]) or size < 4, "ranks disagree"      # NCCL at 2 ranks: same sum on both
     dist.barrier()
     b.close()
     dist.destroy_process_group()
