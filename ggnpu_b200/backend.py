@@ -101,7 +101,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
 ]
 
 _lib = None
@@ -144,6 +144,8 @@ def load_library() -> C.CDLL:
     L.ggb_attn_prefill_device.argtypes = [vp, C.POINTER(AttnPagedParams), i32]
     L.ggb_moe_ffn_device.argtypes = [vp, C.POINTER(MoeParams)]
     L.ggb_deltanet_step_device.argtypes = [vp, C.POINTER(DeltaNetParams)]
+    L.ggb_qgate_split_device.argtypes = [vp, vp, vp, i32, i32]
+    L.ggb_attn_gate_device.argtypes = [vp, vp, vp, i32, i32]
     L.ggb_tp_unique_id.argtypes = [vp]
     L.ggb_tp_init.argtypes = [vp, vp, i32, i32]
     L.ggb_tp_all_reduce_device.argtypes = [vp, vp, i64]
@@ -313,6 +315,12 @@ class CudaBackend:
         """Mixture-of-experts FFN of one token; keyword arguments are the fields of ggb_moe_params (device pointers / weights)."""
         p = MoeParams(**{k: (v if v is not None else None) for k, v in kw.items()})
         return Status(self.lib.ggb_moe_ffn_device(self.h, C.byref(p)))
+
+    def qgate_split_device(self, d_qg, d_q, n_head, head_dim) -> Status:
+        return Status(self.lib.ggb_qgate_split_device(self.h, d_qg, d_q, n_head, head_dim))
+
+    def attn_gate_device(self, d_out, d_qg, n_head, head_dim) -> Status:
+        return Status(self.lib.ggb_attn_gate_device(self.h, d_out, d_qg, n_head, head_dim))
 
     def deltanet_step_device(self, **kw) -> Status:
         """One token of a Gated DeltaNet layer; keyword arguments are the fields of ggb_deltanet_params (device pointers)."""

@@ -368,4 +368,18 @@ int ggb_gemv_swiglu_device(ggb_handle h, ggb_weight wg, ggb_weight wu, const flo
     return launch_gemv(h, a, h->stream);
 }
 
+int ggb_qgate_split_device(ggb_handle h, const float* d_qg, float* d_q, int n_head, int head_dim) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!d_qg || !d_q || n_head <= 0 || head_dim <= 0) return set_status(h, GGB_INVALID_PARAM, "qgate_split: bad arguments");
+    GGB_LOCK(h);
+    return launch_qgate_split(h, d_qg, d_q, n_head, head_dim, h->stream);
+}
+
+int ggb_attn_gate_device(ggb_handle h, float* d_out, const float* d_qg, int n_head, int head_dim) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!d_out || !d_qg || n_head <= 0 || head_dim <= 0) return set_status(h, GGB_INVALID_PARAM, "attn_gate: bad arguments");
+    GGB_LOCK(h);
+    return launch_attn_gate(h, d_out, d_qg, n_head, head_dim, h->stream);
+}
+
 }  // extern "C"

@@ -154,6 +154,8 @@ int launch_rope(Context* c, float* x, int n_tok, int n_heads, int head_dim, int 
 int launch_rope_angles(Context* c, float* x, int n_heads, int n_dims, int64_t rope_dims, int64_t offset, float freq_scale,
                        float freq_base, int neox, cudaStream_t s);
 int launch_matmul_f32_kn(Context* c, const float* A, const float* B, float* C, int M, int N, int K, int lda, int ldc, cudaStream_t s);
+int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, int hd, cudaStream_t s);
+int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s);
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
 
 // ggb_attn.cu

@@ -227,4 +227,31 @@ int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_pa
     return cuda_status(c, cudaGetLastError(), "argmax");
 }
 
+// ---- gated attention (qwen35 full-attention layers) -----------------------------------------------
+// The attn_q projection emits, per query head, [query(hd) | gate(hd)] (src/cli/main.cpp:3054-3060).
+// qgate_split: q_out[h][i] = qg[h][i] (contiguous heads for the attention kernels; the gate stays in qg).
+// attn_gate:   out[h][i] *= sigmoid(qg[h][hd + i])  (main.cpp:3098), read in place from the projection.
+__global__ void qgate_split_kernel(const float* __restrict__ qg, float* __restrict__ q_out, int n, int hd) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int h = i / hd, d = i - h * hd;
+        q_out[i] = qg[static_cast<size_t>(h) * 2 * hd + d];
+    }
+}
+__global__ void attn_gate_kernel(float* __restrict__ out, const float* __restrict__ qg, int n, int hd) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int h = i / hd, d = i - h * hd;
+        out[i] *= 1.0f / (1.0f + expf(-qg[static_cast<size_t>(h) * 2 * hd + hd + d]));
+    }
+}
+int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, int hd, cudaStream_t s) {
+    qgate_split_kernel<<<ew_grid(static_cast<int64_t>(n_head) * hd), 256, 0, s>>>(qg, q_out, n_head * hd, hd);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "qgate_split");
+}
+int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s) {
+    attn_gate_kernel<<<ew_grid(static_cast<int64_t>(n_head) * hd), 256, 0, s>>>(out, qg, n_head * hd, hd);
+    c->launches++;
+    return cuda_status(c, cudaGetLastError(), "attn_gate");
+}
+
 }  // namespace ggb

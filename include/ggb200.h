@@ -286,6 +286,15 @@ typedef struct ggb_deltanet_params {
 } ggb_deltanet_params;
 GGB_API int ggb_deltanet_step_device(ggb_handle h, const ggb_deltanet_params* p);
 
+/* Gated full attention (qwen35 / qwen35moe attention layers, src/cli/main.cpp:3035-3105): the attn_q projection
+ * emits per query head [query(head_dim) | gate(head_dim)].  ggb_qgate_split_device copies the query halves into
+ * contiguous heads d_q[n_head][head_dim] for the attention entry points (:3054-3060; the gate halves stay where
+ * they are); ggb_attn_gate_device multiplies the attention output by sigmoid(gate), reading the gate in place
+ * from the projection (:3098).  QK-norm, the partial NeoX rotation and head_dim 256 are covered by ggb_rms_norm,
+ * ggb_rope (rope_dims < n_dims) and the paged attention entry points.  Device pointers, asynchronous. */
+GGB_API int ggb_qgate_split_device(ggb_handle h, const float* d_qg, float* d_q, int n_head, int head_dim);
+GGB_API int ggb_attn_gate_device(ggb_handle h, float* d_out, const float* d_qg, int n_head, int head_dim);
+
 /* The handle's CUDA stream (a cudaStream_t), for callers that time or order work on it. */
 GGB_API void* ggb_stream(ggb_handle h);
 /* Number of kernels this library has launched on the handle so far. */

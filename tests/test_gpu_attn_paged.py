@@ -86,6 +86,34 @@ def test_prefill_attention_matches_oracle(backend, oracle, shape):
                 assert np.allclose(got[t], want, rtol=2e-5, atol=2e-6), (shape, pos0, t)
 
 
+def test_gated_attention_head_256(backend, oracle):
+    """qwen35 full-attention layer core (src/cli/main.cpp:3054-3060, 3098): the q projection holds per head
+    [query(256) | gate(256)]; the query halves feed the paged attention (16 Q / 2 KV heads of 256), the output is
+    multiplied by sigmoid(gate).  vs the oracle's flash_attn on the gathered query times the same gate."""
+    n_head, n_kv, hd, page, n_pages = 16, 2, 256, 64, 4
+    _, k, v, kp, vp, table = make_case(n_head, n_kv, hd, page, n_pages, seed=99)
+    g = torch.Generator().manual_seed(5)
+    qg = torch.randn(n_head, 2 * hd, generator=g)
+    dev = torch.device("cuda:0")
+    dqg, dk, dv, dt = qg.to(dev), kp.to(dev), vp.to(dev), table.to(dev)
+    dq = torch.full((n_head, hd), float("nan"), device=dev)
+    out = torch.empty(n_head, hd, device=dev)
+    pos = 150
+    torch.cuda.synchronize()
+    assert backend.qgate_split_device(dqg.data_ptr(), dq.data_ptr(), n_head, hd) == Status.OK
+    assert backend.attn_paged_device(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dt.data_ptr(), out.data_ptr(),
+                                     n_head, n_kv, hd, page, n_pages, pos) == Status.OK, backend.last_error_message()
+    assert backend.attn_gate_device(out.data_ptr(), dqg.data_ptr(), n_head, hd) == Status.OK
+    backend.sync()
+    q = qg[:, :hd].contiguous().numpy()
+    gate = qg[:, hd:].numpy().astype(np.float32)
+    assert np.array_equal(dq.cpu().numpy(), q)
+    want = oracle.flash_attn(q, expanded(k, n_head, n_kv, pos + 1), expanded(v, n_head, n_kv, pos + 1), -1)
+    want = want * (np.float32(1.0) / (np.float32(1.0) + np.exp(-gate)))
+    assert np.allclose(out.cpu().numpy(), want, rtol=3e-5, atol=3e-6)
+    assert backend.attn_gate_device(0, dqg.data_ptr(), n_head, hd) == Status.INVALID_PARAM
+
+
 def test_paged_attention_argument_errors(backend):
     dev = torch.device("cuda:0")
     t = torch.zeros(64, device=dev)
