@@ -21,7 +21,7 @@
 // the one in which the row-group-major Q4_K / Q6_K fragments deliver 16-byte chunks.
 // Epilogue: tcgen05.ld brings the accumulators to registers (one weight row per lane); bias /
 // residual / SwiGLU are applied and 32 lanes store 32 consecutive n of one token.
-// No cluster launch and no multicast copy is used.  Every mbarrier wait is bounded.
+// No cluster launch is used and every copy targets one CTA.  Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include <stdio.h>
