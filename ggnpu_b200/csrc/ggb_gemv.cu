@@ -593,11 +593,22 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         }
         if (st != GGB_NOT_FOUND) return st;
     }
-    if (a.n_cat || a.attn_partial || a.sel || a.xscale)
-        return set_status(c, GGB_INVALID_PARAM, "gemv: stacked matrices, attention-merge input, routed experts and scaled activations need the tensor-core kernel (Q4_K / Q6_K)");
+    if (a.attn_partial || a.sel || a.xscale)
+        return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input, routed experts and scaled activations need the tensor-core kernel (Q4_K / Q6_K)");
     if (c->use_tma && a.M == 1) {
         const int st = launch_gemv_tma(c, a, s);
         if (st != GGB_NOT_FOUND) return st;
+    }
+    if (a.n_cat) {
+        // no kernel took the stack: one launch per matrix
+        GemvArgs one = a;
+        one.n_cat = 0;
+        int st = launch_gemv(c, one, s);
+        for (int i = 0; i < a.n_cat && st == GGB_OK; ++i) {
+            one.w = a.cat_w[i]; one.y = a.cat_y[i]; one.bias = a.cat_bias[i]; one.ldc = a.cat_ldc[i];
+            st = launch_gemv(c, one, s);
+        }
+        return st;
     }
     if (a.epi == EPI_SWIGLU) return dispatch<true>(c, a, s);
     return dispatch<false>(c, a, s);

@@ -208,7 +208,34 @@ struct TmaGemvArgs {
     int units_per_slice;
     int* err;
     unsigned long long* trace;   // optional time stamps of CTA 0
+    // stacked matrices (q, k, v of one layer): tiles [tile_first[i], tile_first[i + 1]) belong to matrix
+    // i + 1, which has its own streams, row count, output and bias; all share K, the format and x
+    int n_cat;
+    int tile_first[2];
+    const uint8_t* cat_s[2][kMaxStreams];
+    int64_t cat_N[2];
+    float* cat_y[2];
+    const float* cat_bias[2];
 };
+
+// Matrix and first row of tile t.
+struct TileRef {
+    const uint8_t* const* s;
+    int64_t N, row0;
+    float* y;
+    const float* bias;
+};
+__device__ __forceinline__ TileRef tile_ref(const TmaGemvArgs& a, int t) {
+    TileRef r;
+    if (a.n_cat == 0 || t < a.tile_first[0]) {
+        r.s = a.w.s; r.N = a.w.N; r.y = a.y; r.bias = a.bias; r.row0 = static_cast<int64_t>(t) * a.tile_rows;
+    } else {
+        const int i = (a.n_cat > 1 && t >= a.tile_first[1]) ? 1 : 0;
+        r.s = a.cat_s[i]; r.N = a.cat_N[i]; r.y = a.cat_y[i]; r.bias = a.cat_bias[i];
+        r.row0 = static_cast<int64_t>(t - a.tile_first[i]) * a.tile_rows;
+    }
+    return r;
+}
 
 // Shared-memory map (dynamic): [ring: stages * stage_bytes][x limb planes 3*K][x run sums K/16 floats]
 // [block scales K/256 floats][slice partials 2 * tile_rows * wk * (dual ? 2 : 1) floats]
@@ -250,15 +277,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                 const int s = n % a.stages;
                 const uint32_t ph = (n / a.stages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1, a.err, 1)) break;
-                const int64_t row0 = static_cast<int64_t>(t) * a.tile_rows;
-                const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), a.w.N - row0));
+                const TileRef tr = tile_ref(a, t);
+                const int64_t row0 = tr.row0;
+                const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), tr.N - row0));
                 uint32_t bytes = 0;
                 for (int i = 0; i < F::NS; ++i) bytes += rows * nb * fi.size[i];
                 mbar_expect_tx(&full_bar[s], DUAL ? 2 * bytes : bytes);
                 uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
                 for (int i = 0; i < F::NS; ++i) {
                     const uint32_t sz = rows * nb * fi.size[i];
-                    bulk_g2s(dst + soff[i], a.w.s[i] + row0 * nb * fi.size[i], sz, &full_bar[s]);
+                    bulk_g2s(dst + soff[i], tr.s[i] + row0 * nb * fi.size[i], sz, &full_bar[s]);
                     if (DUAL) bulk_g2s(dst + soff[kMaxStreams + i], a.w2.s[i] + row0 * nb * fi.size[i], sz, &full_bar[s]);
                 }
             }
@@ -356,8 +384,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
             const int s = n % a.stages;
             const uint32_t ph = (n / a.stages) & 1;
             if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
-            const int64_t row0 = static_cast<int64_t>(t) * a.tile_rows;
-            const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), a.w.N - row0));
+            const TileRef tr = tile_ref(a, t);
+            const int64_t row0 = tr.row0;
+            const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), tr.N - row0));
             const uint8_t* base = ring + static_cast<size_t>(s) * a.stage_bytes;
             // stream bases of this tile (a partial last tile fills only the head of each stream slot)
             const uint8_t* sa[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -381,9 +410,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                     const int64_t nrow = row0 + r;
                     float v = acc;
                     if constexpr (DUAL) v = (v / (1.0f + expf(-v))) * acc2;
-                    else if (a.epi == EPI_ADD_BIAS) v += __ldg(a.bias + nrow);
+                    else if (a.epi == EPI_ADD_BIAS) v += __ldg(tr.bias + nrow);
                     else if (a.epi == EPI_RESIDUAL) v += a.resid[nrow];
-                    a.y[nrow] = v;
+                    tr.y[nrow] = v;
                 }
             }
             __syncwarp();
@@ -395,9 +424,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                     for (int k = 0; k < a.wk; ++k) { v += pp[r * a.wk + k]; if constexpr (DUAL) v2 += pp[(a.tile_rows + r) * a.wk + k]; }
                     const int64_t nrow = row0 + r;
                     if constexpr (DUAL) v = (v / (1.0f + expf(-v))) * v2;
-                    else if (a.epi == EPI_ADD_BIAS) v += __ldg(a.bias + nrow);
+                    else if (a.epi == EPI_ADD_BIAS) v += __ldg(tr.bias + nrow);
                     else if (a.epi == EPI_RESIDUAL) v += a.resid[nrow];
-                    a.y[nrow] = v;
+                    tr.y[nrow] = v;
                 }
             }
         }
@@ -412,6 +441,13 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     const int64_t N = g.w.N;
     const int units = K / 32;
     if (K % 256 || N % 8 || units > 8 * 64) return GGB_NOT_FOUND;
+    if (g.n_cat && (DUAL || g.n_cat > 2 || (g.epi != EPI_STORE && g.epi != EPI_ADD_BIAS))) return GGB_NOT_FOUND;
+    int64_t n_all = N;
+    for (int i = 0; i < g.n_cat; ++i) {
+        const PackedW& w = g.cat_w[i];
+        if (w.type != g.w.type || w.K != K || w.layout != 0 || w.N % 8 || !g.cat_y[i] || (g.epi == EPI_ADD_BIAS && !g.cat_bias[i])) return GGB_NOT_FOUND;
+        n_all += w.N;
+    }
     int wk = 1;
     while (wk < kConsumerWarps && (units + wk - 1) / wk > 64) wk *= 2;
     const int ups = (units + wk - 1) / wk;
@@ -421,11 +457,13 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     int gran = 1;
     for (int i = 0; i < fi.n_streams; ++i) while ((gran * nb * fi.size[i]) % 16) ++gran;
     if (N % gran) return GGB_NOT_FOUND;
+    for (int i = 0; i < g.n_cat; ++i) if (g.cat_w[i].N % gran) return GGB_NOT_FOUND;
     const int G = c->sm_count;
     int tile_rows = gran;
     double best = 1e30;
     for (int tr = gran; tr <= 512 && static_cast<int64_t>(tr) * row_bytes <= 24 * 1024 + (tr == gran ? (1 << 30) : 0); tr += gran) {
-        const int64_t nt = (N + tr - 1) / tr;
+        int64_t nt = (N + tr - 1) / tr;
+        for (int i = 0; i < g.n_cat; ++i) nt += (g.cat_w[i].N + tr - 1) / tr;
         const double cost = static_cast<double>((nt + G - 1) / G) * (static_cast<double>(tr) * row_bytes + 3072.0);
         if (cost < best * 0.999) { best = cost; tile_rows = tr; }
     }
@@ -435,7 +473,9 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     if (fixed + 2 * static_cast<size_t>(stage_bytes) > 200 * 1024) return GGB_NOT_FOUND;
     int stages = static_cast<int>((std::max(budget, fixed + 2 * stage_bytes) - fixed) / stage_bytes);
     stages = std::max(2, std::min(stages, kMaxStages));
-    const int n_tiles = static_cast<int>((N + tile_rows - 1) / tile_rows);
+    int n_tiles = static_cast<int>((N + tile_rows - 1) / tile_rows);
+    int tile_first[2] = {0, 0};
+    for (int i = 0; i < g.n_cat; ++i) { tile_first[i] = n_tiles; n_tiles += static_cast<int>((g.cat_w[i].N + tile_rows - 1) / tile_rows); }
     stages = std::min(stages, std::max(2, (n_tiles + c->sm_count - 1) / c->sm_count));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + fixed;
 
@@ -444,6 +484,12 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
     a.err = c->d_err;
     a.trace = trace_slot(c);
+    a.n_cat = g.n_cat;
+    for (int i = 0; i < g.n_cat; ++i) {
+        a.tile_first[i] = tile_first[i];
+        for (int j = 0; j < kMaxStreams; ++j) a.cat_s[i][j] = g.cat_w[i].s[j];
+        a.cat_N[i] = g.cat_w[i].N; a.cat_y[i] = g.cat_y[i]; a.cat_bias[i] = g.cat_bias[i];
+    }
 
     auto kern = gemv_tma_kernel<F, DUAL>;
     static size_t smem_allowed = 48 * 1024;

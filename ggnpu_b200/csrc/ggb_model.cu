@@ -100,7 +100,8 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
         a.gamma = l.attn_norm; a.eps = d.rms_eps;
         if (l.bq) { a.epi = EPI_ADD_BIAS; a.bias = l.bq; }
         const bool biases_agree = (l.bq != nullptr) == (l.bk != nullptr) && (l.bq != nullptr) == (l.bv != nullptr);
-        if (n_tok <= 2 && biases_agree && l.q->w.layout == 1 && l.k->w.layout == 1 && l.v->w.layout == 1) {
+        const bool same_kind = l.q->w.type == l.k->w.type && l.q->w.type == l.v->w.type && l.q->w.layout == l.k->w.layout && l.q->w.layout == l.v->w.layout;
+        if (biases_agree && ((n_tok <= 2 && l.q->w.layout == 1 && l.k->w.layout == 1 && l.v->w.layout == 1) || (n_tok == 1 && same_kind))) {
             // q, k and v in one launch: three matrices stacked along N share the normalised x
             a.n_cat = 2;
             a.cat_w[0] = l.k->w; a.cat_y[0] = m->k; a.cat_bias[0] = l.bk; a.cat_ldc[0] = kvd;
