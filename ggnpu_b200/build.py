@@ -27,7 +27,8 @@ def sources() -> list[str]:
 
 
 def _deps_mtime() -> float:
-    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "ggb200.h")]
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "ggb200.h"),
+                                                                 os.path.join(HERE, "iq_tables.py")]
     return max(os.path.getmtime(f) for f in files)
 
 
@@ -36,6 +37,11 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
         return OUT
     os.makedirs(OBJ, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose_ptxas else []
+    # codebooks of the grid-coded formats, generated from the gguf package (absent: built without them)
+    from .iq_tables import write_include
+    if not write_include(os.path.join(OBJ, "ggb_iq_grids.inc")):
+        sys.stderr.write("ggnpu_b200.build: gguf package not found, IQ1/IQ2/IQ3 formats left out\n")
+    extra += ["-I", OBJ]
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")

@@ -30,8 +30,18 @@ namespace ggb {
 
 enum : uint32_t {
     T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12,
-    T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20, T_IQ4_XS = 23, T_BF16 = 30
+    T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20, T_IQ4_XS = 23, T_BF16 = 30,
+    // grid-coded formats (their codebooks are generated at build time, see GGB_HAVE_IQ_GRIDS below)
+    T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ1_S = 19, T_IQ3_S = 21, T_IQ2_S = 22, T_IQ1_M = 29
 };
+
+// The codebooks of the grid-coded formats come from a file generated at build time (iq_tables.py writes
+// it from the gguf package).  Where it is absent the library is built without these formats.
+#if defined(__has_include)
+#if __has_include("ggb_iq_grids.inc")
+#define GGB_HAVE_IQ_GRIDS 1
+#endif
+#endif
 
 constexpr int kMaxStreams = 4;
 
@@ -58,6 +68,16 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     case T_Q5_K:   return {256, 176, 3, {0, 16, 48, 0}, {16, 32, 128, 0}};
     case T_Q6_K:   return {256, 210, 4, {0, 128, 192, 208}, {128, 64, 16, 2}};
     case T_IQ4_XS: return {256, 136, 2, {0, 8, 0, 0}, {8, 128, 0, 0}};
+#ifdef GGB_HAVE_IQ_GRIDS
+    // one stream: the block as it is in the file (include/ggnpu/quant/iquants.h:40-46 for the sizes)
+    case T_IQ2_XXS: return {256, 66, 1, {0, 0, 0, 0}, {66, 0, 0, 0}};
+    case T_IQ2_XS:  return {256, 74, 1, {0, 0, 0, 0}, {74, 0, 0, 0}};
+    case T_IQ2_S:   return {256, 82, 1, {0, 0, 0, 0}, {82, 0, 0, 0}};
+    case T_IQ3_XXS: return {256, 98, 1, {0, 0, 0, 0}, {98, 0, 0, 0}};
+    case T_IQ3_S:   return {256, 110, 1, {0, 0, 0, 0}, {110, 0, 0, 0}};
+    case T_IQ1_S:   return {256, 50, 1, {0, 0, 0, 0}, {50, 0, 0, 0}};
+    case T_IQ1_M:   return {256, 56, 1, {0, 0, 0, 0}, {56, 0, 0, 0}};
+#endif
     default:       return {0, 0, 0, {0, 0, 0, 0}, {0, 0, 0, 0}};
     }
 }
@@ -127,6 +147,112 @@ __device__ __forceinline__ float ld_f16(const uint8_t* p) {   // p 2-byte aligne
 
 __device__ __constant__ const int8_t kIq4Codebook[16] = {-127, -104, -83, -65, -49, -35, -22, -10,
                                                          1, 13, 25, 38, 53, 69, 89, 113};
+
+__host__ __device__ constexpr bool is_grid_type(uint32_t t) {
+    return t == T_IQ2_XXS || t == T_IQ2_XS || t == T_IQ2_S || t == T_IQ3_XXS || t == T_IQ3_S || t == T_IQ1_S || t == T_IQ1_M;
+}
+
+#ifdef GGB_HAVE_IQ_GRIDS
+#define GGB_IQ_TABLE(ctype, name, rows, cols) static __device__ const ctype name[rows][cols]
+#include "ggb_iq_grids.inc"
+#undef GGB_IQ_TABLE
+
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t* p) { return p[0] | (static_cast<uint32_t>(p[1]) << 8); }
+__device__ __forceinline__ uint32_t ld_u32(const uint8_t* p) { return ld_u16(p) | (ld_u16(p + 2) << 16); }
+
+// Values 8*g8 .. 8*g8+7 of the 256-value block at p (a block is only 2-byte aligned), bit-exact with
+// the reference decoders src/quant/iquants.cpp:37-203: eight values share one codebook row (two rows
+// of four for the IQ3 formats) and one sign byte; the scale is formed with the reference's roundings
+// ((d * (0.5 + s)) * 0.25 etc.), then scale * grid value, then the sign.
+template <uint32_t TYPE>
+__device__ __forceinline__ void iq_decode8(const uint8_t* p, int g8, float (&out)[8]) {
+    const int ib = g8 >> 2, l = g8 & 3;
+    if constexpr (TYPE == T_IQ1_S || TYPE == T_IQ1_M) {
+        float dl, delta;
+        uint32_t idx;
+        if constexpr (TYPE == T_IQ1_S) {
+            const float d = ld_f16(p);
+            const uint32_t qh = ld_u16(p + 34 + 2 * ib);
+            dl = __fmul_rn(d, __int2float_rn(2 * static_cast<int>((qh >> 12) & 7) + 1));
+            delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+            idx = p[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8);
+        } else {
+            const uint32_t s0 = ld_u16(p + 48), s1 = ld_u16(p + 50), s2 = ld_u16(p + 52), s3 = ld_u16(p + 54);
+            const float d = f16_bits_to_f32(static_cast<uint16_t>((s0 >> 12) | ((s1 >> 8) & 0x00F0u) | ((s2 >> 4) & 0x0F00u) | (s3 & 0xF000u)));
+            const uint32_t sc = ld_u16(p + 48 + 2 * (ib >> 1));
+            dl = __fmul_rn(d, __int2float_rn(2 * static_cast<int>((sc >> (6 * (ib & 1) + 3 * (l >> 1))) & 7) + 1));
+            const uint32_t qh = p[32 + 2 * ib + (l >> 1)];
+            delta = (qh & ((l & 1) ? 0x80u : 0x08u)) ? -0.125f : 0.125f;
+            idx = p[4 * ib + l] | ((qh << ((l & 1) ? 4 : 8)) & 0x700u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[j] = __fmul_rn(dl, __int2float_rn(kIq1sGrid[idx][j]) + delta);
+    } else if constexpr (TYPE == T_IQ2_XXS || TYPE == T_IQ2_XS || TYPE == T_IQ2_S) {
+        const float d = ld_f16(p);
+        float db;
+        uint32_t signs;
+        const uint8_t* grid;
+        if constexpr (TYPE == T_IQ2_XXS) {
+            const uint32_t aux = ld_u32(p + 2 + 8 * ib + 4);
+            db = __fmul_rn(__fmul_rn(d, 0.5f + __uint2float_rn(aux >> 28)), 0.25f);
+            signs = kIqSigns[0][(aux >> (7 * l)) & 127];
+            grid = kIq2xxsGrid[p[2 + 8 * ib + l]];
+        } else {
+            const uint32_t sc = p[(TYPE == T_IQ2_XS ? 66 : 74) + ib];
+            db = __fmul_rn(__fmul_rn(d, 0.5f + __uint2float_rn(l < 2 ? (sc & 15) : (sc >> 4))), 0.25f);
+            if constexpr (TYPE == T_IQ2_XS) {
+                const uint32_t q = ld_u16(p + 2 + 2 * (4 * ib + l));
+                signs = kIqSigns[0][q >> 9];
+                grid = kIq2xsGrid[q & 511];
+            } else {
+                signs = p[2 + 32 + 4 * ib + l];
+                grid = kIq2sGrid[p[2 + 4 * ib + l] | ((static_cast<uint32_t>(p[66 + ib]) << (8 - 2 * l)) & 0x300u)];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = __fmul_rn(db, __uint2float_rn(grid[j]));
+            out[j] = (signs >> j) & 1 ? -v : v;
+        }
+    } else {
+        const float d = ld_f16(p);
+        float db;
+        uint32_t signs;
+        const uint8_t* g1;
+        const uint8_t* g2;
+        if constexpr (TYPE == T_IQ3_XXS) {
+            const uint32_t aux = ld_u32(p + 66 + 4 * ib);
+            db = __fmul_rn(__fmul_rn(d, 0.5f + __uint2float_rn(aux >> 28)), 0.5f);
+            signs = kIqSigns[0][(aux >> (7 * l)) & 127];
+            g1 = kIq3xxsGrid[p[2 + 8 * ib + 2 * l]];
+            g2 = kIq3xxsGrid[p[2 + 8 * ib + 2 * l + 1]];
+        } else {
+            const uint32_t sc = p[106 + (ib >> 1)];
+            db = __fmul_rn(d, __int2float_rn(1 + 2 * static_cast<int>((ib & 1) ? (sc >> 4) : (sc & 15))));
+            const uint32_t qh = p[66 + ib];
+            signs = p[74 + 4 * ib + l];
+            g1 = kIq3sGrid[p[2 + 8 * ib + 2 * l] | ((qh << (8 - 2 * l)) & 256u)];
+            g2 = kIq3sGrid[p[2 + 8 * ib + 2 * l + 1] | ((qh << (7 - 2 * l)) & 256u)];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float v1 = __fmul_rn(db, __uint2float_rn(g1[j])), v2 = __fmul_rn(db, __uint2float_rn(g2[j]));
+            out[j] = (signs >> j) & 1 ? -v1 : v1;
+            out[j + 4] = (signs >> (j + 4)) & 1 ? -v2 : v2;
+        }
+    }
+}
+
+template <uint32_t TYPE>
+__device__ __forceinline__ float iq_decode_one(const uint8_t* p, int j) {
+    float v[8];
+    iq_decode8<TYPE>(p, j >> 3, v);
+    float r = v[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) r = (j & 7) == i ? v[i] : r;
+    return r;
+}
+#endif  // GGB_HAVE_IQ_GRIDS
 
 // 6-bit (scale, min) pair j of the 12-byte Q4_K/Q5_K pack.
 __device__ __forceinline__ void k4_scale_min(int j, const uint8_t* p, int& sc, int& mn) {
@@ -211,6 +337,15 @@ __device__ inline float decode_elem(const PackedW& w, int64_t blk, int j) {
         const int hbit = (w.s[0][blk * 32 + 16 * odd + l] >> (4 * hf + sh)) & 1;
         return dl * __int2float_rn(q - (hbit ? 0 : 4));
     }
+#ifdef GGB_HAVE_IQ_GRIDS
+    case T_IQ2_XXS: return iq_decode_one<T_IQ2_XXS>(w.s[0] + blk * 66, j);
+    case T_IQ2_XS: return iq_decode_one<T_IQ2_XS>(w.s[0] + blk * 74, j);
+    case T_IQ2_S: return iq_decode_one<T_IQ2_S>(w.s[0] + blk * 82, j);
+    case T_IQ3_XXS: return iq_decode_one<T_IQ3_XXS>(w.s[0] + blk * 98, j);
+    case T_IQ3_S: return iq_decode_one<T_IQ3_S>(w.s[0] + blk * 110, j);
+    case T_IQ1_S: return iq_decode_one<T_IQ1_S>(w.s[0] + blk * 50, j);
+    case T_IQ1_M: return iq_decode_one<T_IQ1_M>(w.s[0] + blk * 56, j);
+#endif
     default: return 0.0f;
     }
 }

@@ -271,6 +271,34 @@ struct FIQ4XS {
     }
 };
 
+#ifdef GGB_HAVE_IQ_GRIDS
+// Grid-coded formats: a unit is one 32-value sub-block, decoded eight values at a time through the
+// codebook (iq_decode8).  Correct for every one of them; not tuned (none is in a benchmark configuration).
+template <uint32_t TYPE>
+struct FIQGrid {
+    static constexpr int UNIT = 32;
+    struct Raw { const uint8_t* p; };
+    typedef FQ4K::X X;
+    __device__ static void load(const PackedW& w, int64_t rb, int u, Raw& r) {
+        r.p = w.s[0] + (rb + (u >> 3)) * format_info(TYPE).block_bytes;
+    }
+    __device__ static void load_x(const float4* xs, int u, X& x) {
+        load_run16(xs, u * 32, x.lo); load_run16(xs, u * 32 + 16, x.hi);
+        x.slo = 0.0f; x.shi = 0.0f;
+    }
+    __device__ static float dot(const Raw& r, const X& x, int u) {
+        float s = 0.0f, v[8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            iq_decode8<TYPE>(r.p, (u & 7) * 4 + g, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(g < 2 ? x.lo[8 * g + i] : x.hi[8 * (g - 2) + i], v[i], s);
+        }
+        return s;
+    }
+};
+#endif
+
 struct FQ80 {
     static constexpr int UNIT = 32;
     struct Raw { uint4 q0, q1; float d; };
@@ -542,6 +570,15 @@ static int dispatch(Context* c, const GemvArgs& a, cudaStream_t s) {
     case T_Q4_1: return launch_fmt<FQ4Small<T_Q4_1>, DUAL>(c, a, s);
     case T_IQ4_NL: return launch_fmt<FQ4Small<T_IQ4_NL>, DUAL>(c, a, s);
     case T_IQ4_XS: return launch_fmt<FIQ4XS, DUAL>(c, a, s);
+#ifdef GGB_HAVE_IQ_GRIDS
+    case T_IQ2_XXS: return launch_fmt<FIQGrid<T_IQ2_XXS>, DUAL>(c, a, s);
+    case T_IQ2_XS: return launch_fmt<FIQGrid<T_IQ2_XS>, DUAL>(c, a, s);
+    case T_IQ2_S: return launch_fmt<FIQGrid<T_IQ2_S>, DUAL>(c, a, s);
+    case T_IQ3_XXS: return launch_fmt<FIQGrid<T_IQ3_XXS>, DUAL>(c, a, s);
+    case T_IQ3_S: return launch_fmt<FIQGrid<T_IQ3_S>, DUAL>(c, a, s);
+    case T_IQ1_S: return launch_fmt<FIQGrid<T_IQ1_S>, DUAL>(c, a, s);
+    case T_IQ1_M: return launch_fmt<FIQGrid<T_IQ1_M>, DUAL>(c, a, s);
+#endif
     case T_Q8_0: return launch_fmt<FQ80, DUAL>(c, a, s);
     case T_Q2_K: return launch_fmt<FQ2K, DUAL>(c, a, s);
     case T_Q3_K: return launch_fmt<FQ3K, DUAL>(c, a, s);

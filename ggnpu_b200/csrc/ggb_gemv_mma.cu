@@ -27,9 +27,10 @@ namespace ggb {
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = (kWarps + 1) * 32;
-constexpr int kMaxStages = 32;
+// The kernel is compiled for 8 and for 16 consumer warps (template parameter kWarps; one more warp
+// produces).  Sixteen warps halve the per-warp instruction stream of a small matrix, whose time is the
+// latency of that stream rather than bandwidth; eight leave each warp 166 registers and deeper rings.
+constexpr int kMaxStages = 64;
 #ifndef GGB_MMA_MIN_BLOCKS
 #define GGB_MMA_MIN_BLOCKS 1
 #endif
@@ -66,6 +67,7 @@ __device__ __forceinline__ void stamp(unsigned long long* tr, int i) {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <int kWarps>
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); }
 
 // C[16x8] = A[16x32] * B[32x8], int8 in, int32 out (C starts from zero).
@@ -184,7 +186,8 @@ struct MmaArgs {
 //
 // dynamic shared memory map: [ring: 8 * P * stage_bytes][limb planes: 3*M * (K + 16) bytes]
 //   [asum: M * K/32 floats][xs: M * K/256 floats][comb: 2 * 8 * nmat * 16 * M floats]
-__global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_kernel(const MmaArgs a) {
+template <int kWarps>
+__global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_kernel(const MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ float red[2 * kWarps];
@@ -384,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
     __syncwarp();
     if (warp == 0) stamp(a.trace, 4);                                                        // warp 0 done converting
     if (lane == 0) atomicAdd(&x_ready, 1);      // this warp's x values have arrived: weight streaming may go deep
-    consumer_sync();
+    consumer_sync<kWarps>();
     float inv[2] = {1.0f, 1.0f};
     if (a.gamma) {
 #pragma unroll
@@ -597,9 +600,9 @@ __global__ void __launch_bounds__(kThreads, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_ker
     if (warp == 0) stamp(a.trace, 7);
 }
 
-}  // namespace
-
-int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
+template <int kWarps>
+int launch_mma_t(Context* c, const GemvArgs& g, cudaStream_t s) {
+    constexpr int kThreads = (kWarps + 1) * 32;
     if ((g.w.type != T_Q4_K && g.w.type != T_Q6_K) || g.w.layout != 1 || g.M < 1 || g.M > 2) return GGB_NOT_FOUND;
     if (!g.attn_partial && ((reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3))) return GGB_NOT_FOUND;
     if (g.attn_partial && (g.M != 1 || g.attn_hd % 8 || g.attn_hd <= 0)) return GGB_NOT_FOUND;
@@ -633,17 +636,23 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
     while (sb > 1 && nmat * ((nb + sb - 1) / sb) < ws) sb >>= 1;
     sb = std::min(sb, nb);
     if (g.sel && g.sel_mode == 2) sb = g.w.nb;            // one tile = one chosen expert's blocks of the row group
-    const int spr = (nb + sb - 1) / sb;
-    const int stage_bytes = sb * gb_bytes;
     const size_t fixed = static_cast<size_t>(3 * M) * (K + 16) + sizeof(float) * M * (K / 32 + K / 16 + K / 256) + sizeof(float) * 2 * kWarps * 2 * 32 + 64;
     static const size_t budget = [] {
         const char* e = getenv("GGB_MMA_SMEM_KB");          // tuning knob: shared memory per CTA
         const long kb = e ? atol(e) : 0;
         return static_cast<size_t>(kb >= 32 && kb <= 220 ? kb : 200) * 1024;
     }();
-    const int tiles_per_warp = ((gpc + kWarps / ws - 1) / (kWarps / ws)) * ((nmat * spr + ws - 1) / ws);
-    int P = std::min(kMaxStages / kWarps, std::max(1, tiles_per_warp));
-    while (P > 1 && static_cast<size_t>(kWarps) * P * stage_bytes + fixed > budget) --P;
+    int spr, stage_bytes, P;
+    for (;;) {
+        spr = (nb + sb - 1) / sb;
+        stage_bytes = sb * gb_bytes;
+        const int tiles_per_warp = ((gpc + kWarps / ws - 1) / (kWarps / ws)) * ((nmat * spr + ws - 1) / ws);
+        P = std::min(kMaxStages / kWarps, std::max(1, tiles_per_warp));
+        while (P > 1 && static_cast<size_t>(kWarps) * P * stage_bytes + fixed > budget) --P;
+        // a warp with a single stage cannot overlap copy and use: shallower tiles, more stages
+        if (P > 1 || tiles_per_warp <= 1 || sb == 1 || (g.sel && g.sel_mode == 2)) break;
+        sb >>= 1;
+    }
     const size_t smem = static_cast<size_t>(kWarps) * P * stage_bytes + fixed;
     if (smem > 220 * 1024) return GGB_NOT_FOUND;
 
@@ -662,7 +671,7 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
 
     static size_t smem_allowed = 48 * 1024;
     if (smem > smem_allowed) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_q4k_kernel<kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma attr");
         smem_allowed = smem;
     }
@@ -676,9 +685,20 @@ int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = c->use_pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_q4k_kernel<kWarps>, a);
     c->launches++;
     return cuda_status(c, e, "gemv_mma launch");
+}
+
+}  // namespace
+
+int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
+    static const int warps = [] { const char* e = getenv("GGB_MMA_WARPS"); return e ? atoi(e) : 8; }();
+    if (warps == 16) {
+        const int st = launch_mma_t<16>(c, g, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
+    return launch_mma_t<8>(c, g, s);
 }
 
 }  // namespace ggb

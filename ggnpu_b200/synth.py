@@ -23,14 +23,22 @@ import torch
 F32, F16, Q4_0, Q4_1, Q8_0 = 0, 1, 2, 3, 8
 Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14
 IQ4_NL, IQ4_XS, BF16 = 20, 23, 30
+# grid-coded formats: decoded everywhere, never produced by quantize() (tests use random block bytes)
+IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ1_M = 16, 17, 18, 19, 21, 22, 29
+GRID_TYPES = [IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M]
 
 TYPE_NAMES = {F32: "F32", F16: "F16", Q4_0: "Q4_0", Q4_1: "Q4_1", Q8_0: "Q8_0", Q2_K: "Q2_K", Q3_K: "Q3_K",
-              Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS", BF16: "BF16"}
+              Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS", BF16: "BF16",
+              IQ2_XXS: "IQ2_XXS", IQ2_XS: "IQ2_XS", IQ2_S: "IQ2_S", IQ3_XXS: "IQ3_XXS", IQ3_S: "IQ3_S",
+              IQ1_S: "IQ1_S", IQ1_M: "IQ1_M"}
 TYPE_IDS = {v: k for k, v in TYPE_NAMES.items()}
 # (elements per block, bytes per block): src/gguf/tensor.cpp:18-38
 BLOCK = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q4_0: (32, 18), Q4_1: (32, 20), Q8_0: (32, 34),
          Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
-         IQ4_NL: (32, 18), IQ4_XS: (256, 136)}
+         IQ4_NL: (32, 18), IQ4_XS: (256, 136),
+         # include/ggnpu/quant/iquants.h:40-46
+         IQ2_XXS: (256, 66), IQ2_XS: (256, 74), IQ2_S: (256, 82), IQ3_XXS: (256, 98), IQ3_S: (256, 110),
+         IQ1_S: (256, 50), IQ1_M: (256, 56)}
 QUANT_TYPES = [Q4_0, Q4_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS]
 IQ4_CODEBOOK = [-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113]
 
@@ -198,11 +206,16 @@ def random_blocks(type_id: int, n_blocks: int, seed: int) -> np.ndarray:
     rng = np.random.default_rng(seed)
     raw = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
     f16_at = {Q4_0: [0], Q4_1: [0, 2], Q8_0: [0], Q2_K: [80, 82], Q3_K: [108], Q4_K: [0, 2], Q5_K: [0, 2],
-              Q6_K: [208], IQ4_NL: [0], IQ4_XS: [0], F16: [0], BF16: [], F32: []}[type_id]
+              Q6_K: [208], IQ4_NL: [0], IQ4_XS: [0], F16: [0], BF16: [], F32: [],
+              IQ2_XXS: [0], IQ2_XS: [0], IQ2_S: [0], IQ3_XXS: [0], IQ3_S: [0], IQ1_S: [0], IQ1_M: []}[type_id]
     for off in f16_at:
         hi = raw[:, off + 1]
         inf_nan = (hi & 0x7C) == 0x7C
         raw[:, off + 1] = np.where(inf_nan, hi & 0xBF, hi)      # clear one exponent bit
+    if type_id == IQ1_M:
+        # the fp16 scale is spread over the top nibbles of the four scale words (bytes 49, 51, 53, 55);
+        # its exponent's top bits sit in byte 55: clear one so that the scale is finite
+        raw[:, 55] &= 0xBF
     if type_id == F32:
         f = rng.standard_normal(n_blocks).astype(np.float32)
         raw = f.view(np.uint8).reshape(n_blocks, 4).copy()
@@ -210,6 +223,22 @@ def random_blocks(type_id: int, n_blocks: int, seed: int) -> np.ndarray:
         hi = raw[:, 1]
         raw[:, 1] = np.where((hi & 0x7F) == 0x7F, hi & 0xBF, hi)
     return raw
+
+
+def set_grid_block_scales(raw: np.ndarray, type_id: int, d: np.ndarray) -> np.ndarray:
+    """Overwrites the fp16 block scale of grid-coded blocks ([n_blocks][block bytes]) with d (one value
+    per block), leaving every other field as it is: random bytes then give weights of a chosen size."""
+    bits16 = np.asarray(d, dtype=np.float16).view(np.uint16).astype(np.uint16)
+    out = raw.copy()
+    if type_id == IQ1_M:
+        # the scale's four nibbles are the top nibbles of the four 16-bit scale words (src/quant/iquants.cpp:183-184)
+        for i in range(4):
+            nib = ((bits16 >> (4 * i)) & 15).astype(np.uint8)
+            out[:, 49 + 2 * i] = (out[:, 49 + 2 * i] & 0x0F) | (nib << 4)
+    else:
+        out[:, 0] = (bits16 & 0xFF).astype(np.uint8)
+        out[:, 1] = (bits16 >> 8).astype(np.uint8)
+    return out
 
 
 # ---------------------------------------------------------------------------

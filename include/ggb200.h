@@ -42,7 +42,11 @@ enum ggb_status {
 /* ggml type ids as in ggnpu::GgmlType, include/ggnpu/tensor.h:11-42. */
 enum ggb_type {
     GGB_F32 = 0, GGB_F16 = 1, GGB_Q4_0 = 2, GGB_Q4_1 = 3, GGB_Q8_0 = 8, GGB_Q2_K = 10, GGB_Q3_K = 11,
-    GGB_Q4_K = 12, GGB_Q5_K = 13, GGB_Q6_K = 14, GGB_IQ4_NL = 20, GGB_IQ4_XS = 23, GGB_BF16 = 30
+    GGB_Q4_K = 12, GGB_Q5_K = 13, GGB_Q6_K = 14, GGB_IQ4_NL = 20, GGB_IQ4_XS = 23, GGB_BF16 = 30,
+    /* grid-coded formats (src/quant/iquants.cpp:37-203).  Their codebooks are generated when the library
+     * is built (ggnpu_b200/iq_tables.py, from the gguf package); a library built without them answers
+     * GGB_INVALID_PARAM for these ids. */
+    GGB_IQ2_XXS = 16, GGB_IQ2_XS = 17, GGB_IQ3_XXS = 18, GGB_IQ1_S = 19, GGB_IQ3_S = 21, GGB_IQ2_S = 22, GGB_IQ1_M = 29
 };
 
 typedef struct ggb_context* ggb_handle;

@@ -33,7 +33,15 @@ def _bp(a):
 
 
 def build_oracle() -> str:
-    if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(HERE, "ggb_oracle.c")):
+    # the codebooks of the grid-coded formats are generated (from the gguf package) next to the CUDA objects
+    inc = os.path.join(HERE, "..", "ggnpu_b200", "build", "ggb_iq_grids.inc")
+    try:
+        from ggnpu_b200.iq_tables import write_include
+        write_include(inc)
+    except Exception:
+        pass
+    deps = [os.path.join(HERE, "ggb_oracle.c")] + ([inc] if os.path.exists(inc) else [])
+    if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < max(os.path.getmtime(d) for d in deps):
         subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
     return ORACLE_SO
 

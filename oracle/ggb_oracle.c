@@ -24,8 +24,20 @@
 enum {
     GGO_F32 = 0, GGO_F16 = 1, GGO_Q4_0 = 2, GGO_Q4_1 = 3, GGO_Q8_0 = 8,
     GGO_Q2_K = 10, GGO_Q3_K = 11, GGO_Q4_K = 12, GGO_Q5_K = 13, GGO_Q6_K = 14,
-    GGO_IQ4_NL = 20, GGO_IQ4_XS = 23, GGO_BF16 = 30
+    GGO_IQ4_NL = 20, GGO_IQ4_XS = 23, GGO_BF16 = 30,
+    GGO_IQ2_XXS = 16, GGO_IQ2_XS = 17, GGO_IQ3_XXS = 18, GGO_IQ1_S = 19, GGO_IQ3_S = 21, GGO_IQ2_S = 22, GGO_IQ1_M = 29
 };
+
+/* Codebooks of the grid-coded formats: generated at build time from the gguf package (the file
+ * ggnpu_b200/iq_tables.py writes).  Without it those formats are reported as unsupported. */
+#if defined(__has_include)
+#if __has_include("ggb_iq_grids.inc")
+#define GGO_HAVE_IQ_GRIDS 1
+#define GGB_IQ_TABLE(ctype, name, rows, cols) static const ctype name[rows][cols]
+#include "ggb_iq_grids.inc"
+#undef GGB_IQ_TABLE
+#endif
+#endif
 
 /* ---- scalar conversions ------------------------------------------------- */
 
@@ -65,6 +77,9 @@ GGO_API int ggo_block_elems(uint32_t t) {
     case GGO_F32: case GGO_F16: case GGO_BF16: return 1;
     case GGO_Q4_0: case GGO_Q4_1: case GGO_Q8_0: case GGO_IQ4_NL: return 32;
     case GGO_Q2_K: case GGO_Q3_K: case GGO_Q4_K: case GGO_Q5_K: case GGO_Q6_K: case GGO_IQ4_XS: return 256;
+#ifdef GGO_HAVE_IQ_GRIDS
+    case GGO_IQ2_XXS: case GGO_IQ2_XS: case GGO_IQ2_S: case GGO_IQ3_XXS: case GGO_IQ3_S: case GGO_IQ1_S: case GGO_IQ1_M: return 256;
+#endif
     default: return 0;
     }
 }
@@ -76,6 +91,11 @@ GGO_API int ggo_block_bytes(uint32_t t) {
     case GGO_Q2_K: return 84; case GGO_Q3_K: return 110; case GGO_Q4_K: return 144;
     case GGO_Q5_K: return 176; case GGO_Q6_K: return 210;
     case GGO_IQ4_NL: return 18; case GGO_IQ4_XS: return 136;
+#ifdef GGO_HAVE_IQ_GRIDS
+    /* include/ggnpu/quant/iquants.h:40-46 */
+    case GGO_IQ2_XXS: return 66; case GGO_IQ2_XS: return 74; case GGO_IQ2_S: return 82;
+    case GGO_IQ3_XXS: return 98; case GGO_IQ3_S: return 110; case GGO_IQ1_S: return 50; case GGO_IQ1_M: return 56;
+#endif
     default: return 0;
     }
 }
@@ -227,6 +247,95 @@ static void dq_q6_k(const uint8_t* b, float* y) {
     }
 }
 
+#ifdef GGO_HAVE_IQ_GRIDS
+/* Grid-coded formats, src/quant/iquants.cpp:37-203.  A 256-value block is 8 sub-blocks of 32; a
+ * sub-block is 4 runs of 8 values that share one codebook row (IQ3: two rows of 4) and one byte of
+ * signs.  Value = (sub-block scale * codebook entry), negated where the sign bit is set; the scale
+ * roundings follow the reference: (d * (0.5 + s)) * 0.25 for IQ2, * 0.5 for IQ3_XXS, d * (2 s + 1)
+ * for IQ3_S and IQ1; IQ1 adds a sub-block offset of +-1/8 to the ternary codebook entry first. */
+static uint32_t rd_u16(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8); }
+static uint32_t rd_u32(const uint8_t* p) { return rd_u16(p) | (rd_u16(p + 2) << 16); }
+
+static void put8(float* y, float scale, const uint8_t* row, int n, int first_bit, uint32_t signs) {
+    for (int j = 0; j < n; ++j) {
+        const float v = scale * (float)row[j];
+        y[j] = ((signs >> (first_bit + j)) & 1) ? -v : v;
+    }
+}
+
+static void dq_iq2(uint32_t type, const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    for (int ib = 0; ib < 8; ++ib) {
+        for (int l = 0; l < 4; ++l, y += 8) {
+            if (type == GGO_IQ2_XXS) {                            /* iquants.cpp:37-54 */
+                const uint8_t* q = b + 2 + 8 * ib;
+                const uint32_t aux = rd_u32(q + 4);
+                const float db = d * (0.5f + (float)(aux >> 28)) * 0.25f;
+                put8(y, db, kIq2xxsGrid[q[l]], 8, 0, kIqSigns[0][(aux >> (7 * l)) & 127]);
+            } else {
+                const uint32_t sc = b[(type == GGO_IQ2_XS ? 66 : 74) + ib];
+                const float db = d * (0.5f + (float)(l < 2 ? (sc & 15) : (sc >> 4))) * 0.25f;
+                if (type == GGO_IQ2_XS) {                         /* iquants.cpp:56-73 */
+                    const uint32_t q = rd_u16(b + 2 + 2 * (4 * ib + l));
+                    put8(y, db, kIq2xsGrid[q & 511], 8, 0, kIqSigns[0][q >> 9]);
+                } else {                                          /* iquants.cpp:75-97 */
+                    const uint32_t idx = b[2 + 4 * ib + l] | (((uint32_t)b[66 + ib] << (8 - 2 * l)) & 0x300u);
+                    put8(y, db, kIq2sGrid[idx], 8, 0, b[34 + 4 * ib + l]);
+                }
+            }
+        }
+    }
+}
+
+static void dq_iq3(uint32_t type, const uint8_t* b, float* y) {
+    const float d = rd_f16(b);
+    for (int ib = 0; ib < 8; ++ib) {
+        for (int l = 0; l < 4; ++l, y += 8) {
+            const uint8_t* q = b + 2 + 8 * ib + 2 * l;
+            if (type == GGO_IQ3_XXS) {                            /* iquants.cpp:99-121 */
+                const uint32_t aux = rd_u32(b + 66 + 4 * ib);
+                const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+                const uint32_t signs = kIqSigns[0][(aux >> (7 * l)) & 127];
+                put8(y, db, kIq3xxsGrid[q[0]], 4, 0, signs);
+                put8(y + 4, db, kIq3xxsGrid[q[1]], 4, 4, signs);
+            } else {                                              /* iquants.cpp:123-159 */
+                const uint32_t sc = b[106 + (ib >> 1)], qh = b[66 + ib], signs = b[74 + 4 * ib + l];
+                const float db = d * (float)(1 + 2 * (int)((ib & 1) ? (sc >> 4) : (sc & 15)));
+                put8(y, db, kIq3sGrid[q[0] | ((qh << (8 - 2 * l)) & 256u)], 4, 0, signs);
+                put8(y + 4, db, kIq3sGrid[q[1] | ((qh << (7 - 2 * l)) & 256u)], 4, 4, signs);
+            }
+        }
+    }
+}
+
+static void dq_iq1(uint32_t type, const uint8_t* b, float* y) {
+    float d;
+    if (type == GGO_IQ1_S) d = rd_f16(b);                         /* iquants.cpp:161-178 */
+    else {                                                        /* iquants.cpp:180-203: d is spread over the scale words */
+        const uint32_t s0 = rd_u16(b + 48), s1 = rd_u16(b + 50), s2 = rd_u16(b + 52), s3 = rd_u16(b + 54);
+        d = ggo_f16_to_f32((uint16_t)((s0 >> 12) | ((s1 >> 8) & 0x00F0u) | ((s2 >> 4) & 0x0F00u) | (s3 & 0xF000u)));
+    }
+    for (int ib = 0; ib < 8; ++ib) {
+        for (int l = 0; l < 4; ++l, y += 8) {
+            float dl, delta;
+            uint32_t idx;
+            if (type == GGO_IQ1_S) {
+                const uint32_t qh = rd_u16(b + 34 + 2 * ib);
+                dl = d * (float)(2 * (int)((qh >> 12) & 7) + 1);
+                delta = (qh & 0x8000u) ? -0.125f : 0.125f;
+                idx = b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8);
+            } else {
+                const uint32_t sc = rd_u16(b + 48 + 2 * (ib >> 1)), qh = b[32 + 2 * ib + (l >> 1)];
+                dl = d * (float)(2 * (int)((sc >> (6 * (ib & 1) + 3 * (l >> 1))) & 7) + 1);
+                delta = (qh & ((l & 1) ? 0x80u : 0x08u)) ? -0.125f : 0.125f;
+                idx = b[4 * ib + l] | ((qh << ((l & 1) ? 4 : 8)) & 0x700u);
+            }
+            for (int j = 0; j < 8; ++j) y[j] = dl * ((float)kIq1sGrid[idx][j] + delta);
+        }
+    }
+}
+#endif  /* GGO_HAVE_IQ_GRIDS */
+
 /* One block of any supported type -> fp32.  Returns 0, or -1 for an
  * unsupported type. */
 GGO_API int ggo_dequant_block(uint32_t type, const uint8_t* blk, float* out) {
@@ -244,6 +353,11 @@ GGO_API int ggo_dequant_block(uint32_t type, const uint8_t* blk, float* out) {
     case GGO_Q6_K: dq_q6_k(blk, out); return 0;
     case GGO_IQ4_NL: dq_iq4_nl(blk, out); return 0;
     case GGO_IQ4_XS: dq_iq4_xs(blk, out); return 0;
+#ifdef GGO_HAVE_IQ_GRIDS
+    case GGO_IQ2_XXS: case GGO_IQ2_XS: case GGO_IQ2_S: dq_iq2(type, blk, out); return 0;
+    case GGO_IQ3_XXS: case GGO_IQ3_S: dq_iq3(type, blk, out); return 0;
+    case GGO_IQ1_S: case GGO_IQ1_M: dq_iq1(type, blk, out); return 0;
+#endif
     default: return -1;
     }
 }

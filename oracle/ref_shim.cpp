@@ -56,6 +56,13 @@ int ref_dequant_block(uint32_t type, const uint8_t* blk, float* out) {
     case GgmlType::Q6_K: dequant_q6_k_block(blk, out); return 0;
     case GgmlType::IQ4_NL: dequant_iq4_nl_block(blk, out); return 0;
     case GgmlType::IQ4_XS: dequant_iq4_xs_block(blk, out); return 0;
+    case GgmlType::IQ2_XXS: dequant_iq2_xxs_block(blk, out); return 0;
+    case GgmlType::IQ2_XS: dequant_iq2_xs_block(blk, out); return 0;
+    case GgmlType::IQ2_S: dequant_iq2_s_block(blk, out); return 0;
+    case GgmlType::IQ3_XXS: dequant_iq3_xxs_block(blk, out); return 0;
+    case GgmlType::IQ3_S: dequant_iq3_s_block(blk, out); return 0;
+    case GgmlType::IQ1_S: dequant_iq1_s_block(blk, out); return 0;
+    case GgmlType::IQ1_M: dequant_iq1_m_block(blk, out); return 0;
     default: return -1;
     }
 }

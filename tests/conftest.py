@@ -40,6 +40,11 @@ def vectors():
 
 
 @pytest.fixture(scope="session")
+def grid_vectors():
+    return np.load(os.path.join(GOLDEN, "ref_grid_vectors.npz"))
+
+
+@pytest.fixture(scope="session")
 def cli_vectors():
     return np.load(os.path.join(GOLDEN, "ref_cli.npz"))
 

@@ -112,5 +112,28 @@ def main():
     print("wrote", os.path.join(HERE, "ref_vectors.npz"), os.path.join(HERE, "ref_cli.npz"))
 
 
+def grid_vectors(ref=None):
+    """Grid-coded formats (IQ1 / IQ2 / IQ3): outputs of the reference's block decoders
+    (src/quant/iquants.cpp:37-203) and of its exact matmul on random block bytes -> ref_grid_vectors.npz.
+    There is no quantiser for these formats here, so random bytes (finite scales) stand in for weights."""
+    ref = ref or Ref()
+    out = {}
+    A = np.random.default_rng(21).standard_normal((3, 512)).astype(np.float32)
+    out["mm_A"] = A
+    for t in S.GRID_TYPES:
+        blk = S.random_blocks(t, 32, seed=100 + t)
+        out[f"dq_in_{t}"] = blk
+        out[f"dq_out_{t}"] = ref.dequant_blocks(t, blk)
+        w = S.random_blocks(t, 8 * 2, seed=300 + t)               # 8 rows x 512
+        out[f"mm_W_{t}"] = w
+        out[f"mm_exact_{t}"] = ref.matmul_exact(A, w, t, 8, 512)
+    np.savez_compressed(os.path.join(HERE, "ref_grid_vectors.npz"), **out)
+    print("wrote", os.path.join(HERE, "ref_grid_vectors.npz"))
+
+
 if __name__ == "__main__":
-    main()
+    if "--grid-only" in sys.argv:
+        grid_vectors()
+    else:
+        main()
+        grid_vectors()
