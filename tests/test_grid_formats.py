@@ -15,6 +15,13 @@ GGUF_NAMES = {S.IQ2_XXS: "IQ2_XXS", S.IQ2_XS: "IQ2_XS", S.IQ2_S: "IQ2_S", S.IQ3_
               S.IQ1_S: "IQ1_S", S.IQ1_M: "IQ1_M"}
 
 
+@pytest.fixture(autouse=True)
+def _needs_codebooks(oracle):
+    # the codebooks are generated at build time from the gguf package; a build without it leaves these formats out
+    if oracle.lib.ggo_block_elems(S.IQ2_XXS) == 0:
+        pytest.skip("library built without the grid-coded formats (gguf package absent at build time)")
+
+
 def test_block_geometry(oracle):
     # include/ggnpu/quant/iquants.h:40-46, tests/test_quant.cpp:294-317
     want = {S.IQ2_XXS: 66, S.IQ2_XS: 74, S.IQ2_S: 82, S.IQ3_XXS: 98, S.IQ3_S: 110, S.IQ1_S: 50, S.IQ1_M: 56}
