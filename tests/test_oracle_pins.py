@@ -180,3 +180,19 @@ def test_ops_live(oracle, ref):
     assert oracle.argmax_first(np.array([1, 5, 5, 2], np.float32)) == ref.argmax(np.array([1, 5, 5, 2], np.float32)) == 1
     # error statuses of the reference CPU backend (tests/test_arch.cpp:192-221)
     assert ref.lib.ref_rms_norm(None, None, 0, 1e-5, None) == 3
+
+
+# ---- second, independent pin: the gguf package's numpy decoders ---------------------------------
+
+_GGUF_NAMES = {S.Q4_0: "Q4_0", S.Q4_1: "Q4_1", S.Q8_0: "Q8_0", S.Q2_K: "Q2_K", S.Q3_K: "Q3_K", S.Q4_K: "Q4_K",
+               S.Q5_K: "Q5_K", S.Q6_K: "Q6_K", S.IQ4_NL: "IQ4_NL", S.IQ4_XS: "IQ4_XS"}
+
+
+@pytest.mark.parametrize("t", S.QUANT_TYPES)
+def test_dequant_matches_gguf_package(oracle, t):
+    """4096 random blocks per format (every bit pattern of the packed fields, finite scales) decoded
+    by the restatement and by gguf.quants.dequantize: bit-equal."""
+    gguf = pytest.importorskip("gguf")
+    raw = S.random_blocks(t, 4096, seed=700 + t)
+    want = gguf.quants.dequantize(raw.reshape(-1), getattr(gguf.GGMLQuantizationType, _GGUF_NAMES[t])).astype(np.float32)
+    assert np.array_equal(bits(oracle.dequant_blocks(t, raw)).reshape(-1), bits(want).reshape(-1))
