@@ -116,20 +116,29 @@ __device__ __forceinline__ void attn_merge8(const AttnMerge& am, int k0, float (
     const int pos = am.d_pos ? am.d_pos[0] : am.pos0;
     const int n_active = min(am.n_splits, pos / am.keys_per_split + 1);
     const float* base = am.partial + static_cast<size_t>(head) * am.n_splits * (am.hd + 2);
-    float mx = -INFINITY;
-    for (int s = 0; s < n_active; ++s) mx = fmaxf(mx, __ldg(base + static_cast<size_t>(s) * (am.hd + 2)));
-    float lsum = 0.0f;
+    // One pass with a running maximum: every load of a split is independent of the state carried
+    // from the splits before it, so the splits' loads overlap and the prologue's chain of dependent
+    // round trips to L2 is position -> split data, not position -> maxima -> split data.
+    float mx = -INFINITY, lsum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+#pragma unroll 2
     for (int s = 0; s < n_active; ++s) {
         const float* ps = base + static_cast<size_t>(s) * (am.hd + 2);
-        const float f = expf(__ldg(ps) - mx);
-        lsum = fmaf(__ldg(ps + 1), f, lsum);
+        const float m_s = __ldg(ps), l_s = __ldg(ps + 1);
+        float2 p[4];
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            const float2 p = __ldg(reinterpret_cast<const float2*>(ps + 2 + d0 + i));
-            v[i] = fmaf(p.x, f, v[i]); v[i + 1] = fmaf(p.y, f, v[i + 1]);
+        for (int i = 0; i < 4; ++i) p[i] = __ldg(reinterpret_cast<const float2*>(ps + 2 + d0 + 2 * i));
+        const float nm = fmaxf(mx, m_s);
+        // first split: fa = exp(-inf) = 0; a split without keys (max = -inf) contributes nothing
+        const float fa = mx == -INFINITY ? 0.0f : expf(mx - nm), fb = m_s == -INFINITY ? 0.0f : expf(m_s - nm);
+        lsum = fmaf(l_s, fb, lsum * fa);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = fmaf(p[i].x, fb, v[2 * i] * fa);
+            v[2 * i + 1] = fmaf(p[i].y, fb, v[2 * i + 1] * fa);
         }
+        mx = nm;
     }
     const float r = 1.0f / lsum;
 #pragma unroll
@@ -290,6 +299,14 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
     const int mshift = 16 * (t & 1);                             // this lane's two min bytes: sub-blocks 2t, 2t+1
     pdl_wait();
     if (warp == 0) stamp(a.trace, 1);
+    // Residual epilogue of a team: the lanes that will store the first row group's rows fetch their
+    // residual values now, so that the load's latency passes under the prologue and the main loop.
+    const bool resid_pre = a.epi == EPI_RESIDUAL && a.ws > 1 && member == 0 && lane < 16 * M && team < n_rg && a.ncat == 0 && !a.sel;
+    float resid_first = 0.0f;
+    if (resid_pre) {
+        const int64_t row = (g_begin + team) * 16 + (lane & 15);
+        if (row < a.nlog) resid_first = a.resid[static_cast<size_t>(lane >> 4) * a.ldc + row];
+    }
     // One pass over x: y = W (x * gamma) is linear in x, so the RMS factor 1/sqrt(mean(x^2)+eps) is a
     // scalar that can be applied to the finished dot products; the limbs are taken from x * gamma.
     // A warp converts 256-blocks warp, warp+8, ...; four blocks are loaded before any is converted so
@@ -559,12 +576,12 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
         float* const yb = mi == 0 ? a.y : a.cat[mi - 1].y;
         const float* const bb = mi == 0 ? a.bias : a.cat[mi - 1].bias;
         const int ldc = mi == 0 ? a.ldc : a.cat[mi - 1].ldc;
-        auto finish = [&](float v, float v2, int64_t row, int m) {
+        auto finish = [&](float v, float v2, int64_t row, int m, bool have_resid = false, float resid_v = 0.0f) {
             if (row >= n_rows) return;
             const size_t o = static_cast<size_t>(m) * ldc + row;
             if (a.nmat == 2) v = (v / (1.0f + expf(-v))) * v2;      // silu(gate) * up
             else if (a.epi == EPI_ADD_BIAS && bb) v += __ldg(bb + row);
-            else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
+            else if (a.epi == EPI_RESIDUAL) v += have_resid ? resid_v : a.resid[o];
             yb[o] = v;
         };
         if (a.ws == 1) {
@@ -591,7 +608,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
                         const float* cj = comb + static_cast<size_t>((parity * kWarps + team * a.ws + j) * 2) * 32;
                         v += cj[r * 2 + m]; v2 += cj[(16 + r) * 2 + m];
                     }
-                    finish(v, v2, row_base + r, m);
+                    finish(v, v2, row_base + r, m, resid_pre && rg == team, resid_first);      // idx == lane on the first pass
                 }
             }
         }
