@@ -398,7 +398,7 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     const int hd = a.head_dim;
     if (a.page % 8) return set_status(c, GGB_INVALID_PARAM, "attention: page size must be a multiple of 8");
     if (a.fuse && n_tok != 1) return set_status(c, GGB_INVALID_PARAM, "attention: fused append is for single-token steps");
-    if (c->use_tc && n_tok >= c->tc_min_m && !a.fuse) {      // prompt chunks: tensor-core flash attention
+    if (c->use_tc && n_tok >= std::max(c->tc_min_m, 32) && !a.fuse) {      // prompt chunks: tensor-core flash attention
         const int st = launch_attn_prefill(c, a, n_tok, s);
         if (st != GGB_NOT_FOUND) return st;
     }

@@ -1,5 +1,5 @@
 // Prefill GEMM on the 5th-generation tensor cores: Y[M tokens][N] = X[M][K] * W[N][K]^T with W a
-// quantised GGUF matrix (any supported format) and M >= 32 (smaller M uses the GEMV kernels).
+// quantised GGUF matrix (any supported format) and M >= 17 (smaller M uses the GEMV kernels).
 // Replaces the batched-prefill use of mul_mat_weight (src/cli/main.cpp:3256-3267, M <= 256 chunks).
 //
 // Computed as D^T: weight rows are the UMMA "M" operand (one or two 128-row tiles per CTA), tokens

@@ -86,7 +86,10 @@ struct Context {
     unsigned long long* d_trace = nullptr;   // tuning aid (GGB_TRACE=1): %globaltimer stamps of CTA 0, printed by ggb_sync
     bool use_mma = true;      // Q4_K in the row-group-major layout + int8 tensor-core GEMV (M <= 2)
     bool use_tc = true;       // M >= tc_min_m through the tcgen05 GEMM (fp16 operands, fp32 accumulation in TMEM)
-    int tc_min_m = 32;
+    // 17: up to 16 rows keep fp32 activations (two rows per GEMV pass, rel-L2 1e-5 against the exact
+    // product); from 17 rows on one pass of the tensor-core GEMM (~19 us for a 9-14 MB matrix whatever
+    // M <= 64) beats nine and more GEMV passes (~3.5 us per row)
+    int tc_min_m = 17;
     bool tc_generic = false;  // tuning aid: every format through the generic (exact fp32 decode) tile filler
     int tc_rt = 0;            // tuning aid: force 1 or 2 weight tiles per CTA (0: heuristic)
     // tensor-parallel group (ggb_tp.cu); tp_size == 1: none

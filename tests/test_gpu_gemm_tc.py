@@ -1,4 +1,4 @@
-"""Prefill GEMM on the tcgen05 tensor cores (M >= 32 through Backend::mul_mat_q and the device-pointer
+"""Prefill GEMM on the tcgen05 tensor cores (M >= 17 through Backend::mul_mat_q and the device-pointer
 entry points) vs the CPU oracle.
 
 Operands are fp16 (weights dequantised to fp16, activations rounded to fp16 once), sums fp32.  Bars:
@@ -62,10 +62,11 @@ def test_all_formats_fp16_model_and_reference(backend, oracle, t):
     assert rel_l2(C, oracle.matmul_exact(A, raw, t, N, K)) <= 2e-3
 
 
-@pytest.mark.parametrize("M", [32, 64, 257, 600])
+@pytest.mark.parametrize("M", [17, 24, 32, 64, 257, 600])
 @pytest.mark.parametrize("t", [S.Q4_K, S.Q6_K])
 def test_token_tiles(backend, oracle, t, M):
-    """One tile, exactly one tile, one tile + 1 row, several tiles; K with several 64-steps per stage parity."""
+    """The smallest M that takes this path, a partly filled tile, exactly one tile, one tile + 1 row,
+    several tiles; K with several 64-steps per stage parity."""
     N, K = 256, 1024
     raw = make(t, N, K, 5)
     A = np.random.default_rng(M).standard_normal((M, K)).astype(np.float32)
