@@ -178,6 +178,23 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
     const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int G = a.n_head / a.n_kv;
+    // Fused step: the values the rotation below needs (the G query heads and the new key) do not depend
+    // on the position, so their loads are issued before the position is looked at; the position's own
+    // round trip to memory then overlaps theirs instead of preceding it.
+    constexpr int NQ = HD <= 128 ? (9 * (HD / 2) + 127) / 128 : 0;       // rotation items per thread, G <= 8
+    float qpre0[NQ > 0 ? NQ : 1], qpre1[NQ > 0 ? NQ : 1];
+    if (NQ > 0 && a.fuse) {
+        const float* qb = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
+#pragma unroll
+        for (int u = 0; u < NQ; ++u) {
+            const int idx = tid + 128 * u, hh = idx / (HD / 2), i = idx - hh * (HD / 2);
+            if (hh <= G) {
+                const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + HD / 2 : 2 * i + 1;
+                const float* src = hh < G ? qb + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                qpre0[u] = src[i0]; qpre1[u] = src[i1];
+            }
+        }
+    }
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
     const int j_begin = split * keys_per_split;
@@ -238,17 +255,28 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
         __syncthreads();
         const float* cs = a.cos_tab + static_cast<size_t>(pos) * half;
         const float* sn = a.sin_tab + static_cast<size_t>(pos) * half;
-        for (int idx = tid; idx < (G + (has_new ? 1 : 0)) * half; idx += 128) {
+        auto rotate = [&](int idx, float v0, float v1) {
             const int hh = idx / half, i = idx - hh * half;
             const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
             const bool is_q = hh < G;
-            const float* src = is_q ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
             const float* nw = is_q ? a.q_norm : a.k_norm;
-            float v0 = src[i0], v1 = src[i1];
             if (nw) { v0 = v0 * hinv[hh] * nw[i0]; v1 = v1 * hinv[hh] * nw[i1]; }
             const float r0 = v0 * cs[i] - v1 * sn[i], r1 = v0 * sn[i] + v1 * cs[i];
             if (is_q) { qs[hh * HD + i0] = r0 * scale; qs[hh * HD + i1] = r1 * scale; }
             else { fresh[i0] = __float2bfloat16_rn(r0); fresh[i1] = __float2bfloat16_rn(r1); }
+        };
+        const int n_items = (G + (has_new ? 1 : 0)) * half;
+        if (NQ > 0) {
+#pragma unroll
+            for (int u = 0; u < NQ; ++u)
+                if (tid + 128 * u < n_items) rotate(tid + 128 * u, qpre0[u], qpre1[u]);
+        } else {
+            for (int idx = tid; idx < n_items; idx += 128) {
+                const int hh = idx / half, i = idx - hh * half;
+                const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                rotate(idx, src[i0], src[i1]);
+            }
         }
         if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(a.v_new[static_cast<size_t>(h) * HD + i]);
         __syncthreads();
