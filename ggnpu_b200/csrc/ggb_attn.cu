@@ -367,13 +367,30 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
                 const float c = corr[gq];
                 float a0 = acc[p][0] * c, a1 = acc[p][1] * c;
                 const float* pr = S + gq * TK;
-                for (int j = 0; j < nk; ++j) {
-                    const uint32_t vw = Vt[j * KW + w];
-                    const float pj = pr[j];
-                    a0 = fmaf(pj, __uint_as_float(vw << 16), a0);
-                    a1 = fmaf(pj, __uint_as_float(vw & 0xFFFF0000u), a1);
+                // two partial sums per output and eight keys per pass: the shared-memory loads of a pass are
+                // all in flight before the first multiply-add needs one
+                float b0 = 0.0f, b1 = 0.0f;
+                int j = 0;
+                for (; j + 8 <= nk; j += 8) {
+                    uint32_t vw[8];
+                    float pj[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { vw[u] = Vt[(j + u) * KW + w]; pj[u] = pr[j + u]; }
+#pragma unroll
+                    for (int u = 0; u < 8; u += 2) {
+                        a0 = fmaf(pj[u], __uint_as_float(vw[u] << 16), a0);
+                        a1 = fmaf(pj[u], __uint_as_float(vw[u] & 0xFFFF0000u), a1);
+                        b0 = fmaf(pj[u + 1], __uint_as_float(vw[u + 1] << 16), b0);
+                        b1 = fmaf(pj[u + 1], __uint_as_float(vw[u + 1] & 0xFFFF0000u), b1);
+                    }
                 }
-                acc[p][0] = a0; acc[p][1] = a1;
+                for (; j < nk; ++j) {
+                    const uint32_t v1 = Vt[j * KW + w];
+                    const float p1 = pr[j];
+                    a0 = fmaf(p1, __uint_as_float(v1 << 16), a0);
+                    a1 = fmaf(p1, __uint_as_float(v1 & 0xFFFF0000u), a1);
+                }
+                acc[p][0] = a0 + b0; acc[p][1] = a1 + b1;
             }
         }
     }
