@@ -454,7 +454,7 @@ def run_micro(args):
 
 
 def run_micro_moe(args):
-    """Decode-side MoE FFN microbenchmark at the qwen35moe expert shapes (BASELINE config 5): hidden 2048,
+    """Decode-side MoE FFN microbenchmark at the qwen35moe expert shapes: hidden 2048,
     256 routed experts of FFN 512 (Q4_K gate/up, Q6_K down), top-8 + shared expert.  64 different tokens
     are routed in turn, so successive calls touch different experts of the 0.4 GB expert set (> L2).
         python bench.py --micro-moe"""
@@ -588,7 +588,7 @@ def run_micro_allreduce(args):
 
 
 def run_tp(args):
-    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model (BASELINE config 4) over all ranks
+    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model over all ranks
     of this launch (torchrun: one process per GPU; a single process is the TP = 1 point).  Strong
     scaling: the model is fixed, each rank holds 1 / N of the heads, FFN rows and vocabulary.
         python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench.py --tp --gpus 8"""

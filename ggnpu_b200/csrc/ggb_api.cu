@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <algorithm>
+#include <map>
 #include <stdlib.h>
 #include <string.h>
 
@@ -54,14 +55,38 @@ static int d2h_sync(Context* c, void* h, const void* d, size_t n) {
     return cuda_status(c, cudaStreamSynchronize(c->stream), "stream sync");
 }
 
+cudaError_t ensure_dynamic_smem(Context* c, const void* func, size_t smem) {
+    if (smem <= 48 * 1024) return cudaSuccess;
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> granted;
+    std::lock_guard<std::mutex> lk(mu);
+    size_t& have = granted[{c->device, func}];
+    if (smem <= have) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) have = smem;
+    return e;
+}
+
+// Device error word -> status.  Each bounded device-side wait records its own code when it gives up.
+static const char* device_error_text(int v) {
+    switch (v) {
+    case 1: return "device: weight producer timed out waiting for a free ring stage";
+    case 2: return "device: consumers timed out waiting for a weight tile";
+    case 3: return "device: weight producer timed out waiting for the activations (x_ready)";
+    case 4: return "device: tcgen05 GEMM timed out on an mbarrier (operand stage or accumulator)";
+    case 5: return "device: one-shot all-reduce timed out waiting for a peer rank's flag; the buffer was left unsummed";
+    case 6: return "device: decode step kernel timed out at a grid-wide phase barrier";
+    default: return "device: a bounded wait gave up (unknown code)";
+    }
+}
+
 int check_device_error(Context* c) {
     int v = 0;
     cudaError_t e = cudaMemcpy(&v, c->d_err, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_status(c, e, "read device error word");
     if (v == 0) return GGB_OK;
     cudaMemset(c->d_err, 0, sizeof(int));
-    return set_status(c, GGB_ERROR, v == 1 ? "device: weight producer timed out waiting for a free ring stage"
-                                           : "device: consumers timed out waiting for a weight tile");
+    return set_status(c, GGB_ERROR, device_error_text(v));
 }
 
 }  // namespace ggb
@@ -93,10 +118,6 @@ int ggb_create(int device, ggb_handle* out) {
     c->use_tma = getenv("GGB_NO_TMA") == nullptr;
     c->use_mma = getenv("GGB_NO_MMA") == nullptr;
     c->use_tc = getenv("GGB_NO_TC") == nullptr;
-    if (const char* m = getenv("GGB_TC_MIN_M")) c->tc_min_m = std::max(1, atoi(m));
-    c->tc_generic = getenv("GGB_TC_GENERIC") != nullptr;
-    if (const char* m = getenv("GGB_TC_RT")) c->tc_rt = atoi(m);
-    if (getenv("GGB_TRACE") && cudaMalloc(&c->d_trace, 4096 * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(c->d_trace, 0, 4096 * sizeof(unsigned long long));
     *out = c;
     return GGB_OK;
 }
@@ -119,25 +140,9 @@ void ggb_destroy(ggb_handle h) {
 void ggb_sync(ggb_handle h) {
     if (!h) return;
     GGB_LOCK(h);
-    cuda_status(h, cudaStreamSynchronize(h->stream), "sync");
-    if (h->d_trace) {        // tuning aid: time stamps (ns, relative to the first) left by the last traced kernel
-        static unsigned long long t[4096];
-        if (getenv("GGB_TRACE_DUMP") && cudaMemcpy(t, h->d_trace, sizeof(t), cudaMemcpyDeviceToHost) == cudaSuccess) {
-            std::vector<int> order;
-            for (int i = 0; i < 512; ++i) if (t[8 * i]) order.push_back(i);
-            std::sort(order.begin(), order.end(), [&](int a, int b) { return t[8 * a] < t[8 * b]; });
-            unsigned long long prev_end = 0, t0 = order.empty() ? 0 : t[8 * order[0]];
-            for (int i : order) {
-                const unsigned long long* e = t + 8 * i;
-                fprintf(stderr, "[ggb trace] x3=%lld x4=%lld kind=%llu start=%lld wait=%lld prologue=%lld end=%lld gap_from_prev_end=%lld\n",
-                        e[3] ? static_cast<long long>(e[3] - e[0]) : -1, e[4] ? static_cast<long long>(e[4] - e[0]) : -1, e[6],
-                        static_cast<long long>(e[0] - t0), e[1] ? static_cast<long long>(e[1] - e[0]) : -1, e[2] ? static_cast<long long>(e[2] - e[0]) : -1,
-                        static_cast<long long>(e[7] - e[0]), prev_end ? static_cast<long long>(e[0] - prev_end) : 0);
-                prev_end = e[7];
-            }
-            cudaMemset(h->d_trace, 0, sizeof(t));
-        }
-    }
+    // Backend::sync returns nothing: a failure (CUDA error, or a device-side wait that gave up in any
+    // kernel launched through the asynchronous entry points) lands in last_error / last_error_message.
+    if (cuda_status(h, cudaStreamSynchronize(h->stream), "sync") == GGB_OK) check_device_error(h);
 }
 int ggb_is_available(ggb_handle h) { return h != nullptr; }
 const char* ggb_name(ggb_handle) { return "cuda_b200"; }

@@ -13,11 +13,6 @@
 
 namespace ggb {
 
-__device__ __forceinline__ void stamp(unsigned long long* tr, int i, int kind) {
-    if (tr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
-        unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; tr[6] = kind;
-    }
-}
 // Programmatic dependent launch: a kernel launched with the attribute may start before its
 // predecessor in the stream has finished; it must pass pdl_sync() before reading anything the
 // predecessor wrote.  The trigger right after it lets the successor be scheduled in turn.
@@ -96,9 +91,7 @@ int launch_attn_expanded(Context* c, const float* Q, const float* K, const float
 // grid (ceil((n_head + n_kv) / blockDim.y), n_tok); blockDim.x = head_dim / 2 pairs rounded up to a warp,
 // blockDim.y heads per CTA (256 threads in all).
 __global__ void rope_append_kernel(KvAppendArgs a) {
-    stamp(a.trace, 0, 5);
     pdl_sync();
-    stamp(a.trace, 1, 5);
     const int t = blockIdx.y, hh = blockIdx.x * blockDim.y + threadIdx.y;
     const bool active = hh < a.n_head + a.n_kv;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
@@ -141,12 +134,10 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
             a.v_cache[o + i1] = __float2bfloat16_rn(vs[i1]);
         }
     }
-    stamp(a.trace, 7, 5);
 }
 
 int launch_rope_append(Context* c, const KvAppendArgs& a_in, int n_tok, cudaStream_t s) {
     KvAppendArgs a = a_in;
-    a.trace = trace_slot(c);
     const int tx = ((a.head_dim / 2) + 31) / 32 * 32;
     if (tx > 256) return set_status(c, GGB_INVALID_PARAM, "rope_append: head_dim must be at most 512");
     const int ty = std::max(1, std::min(8, 256 / tx));
@@ -172,9 +163,7 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
     constexpr int KS = KW + 1;           // padded K row stride: thread-per-key reads hit distinct banks
     constexpr int TK = 64;               // keys per chunk
     constexpr int NP = (8 * KW + 127) / 128;   // (head, dim pair) items per thread in P*V
-    stamp(a.trace, 0, 3);
     pdl_sync();
-    stamp(a.trace, 1, 3);
     const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int G = a.n_head / a.n_kv;
@@ -405,14 +394,11 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
             if (w == 0) { pg[0] = mrun[gq]; pg[1] = lrun[gq]; }
         }
     }
-    stamp(a.trace, 7, 3);
 }
 
 // grid (n_head, n_tok): merge the visible splits, normalise, write out[t][head][hd].
 __global__ void attn_combine_kernel(AttnPagedArgs a) {
-    stamp(a.trace2, 0, 4);
     pdl_sync();
-    stamp(a.trace2, 1, 4);
     const int head = blockIdx.x, t = blockIdx.y, hd = a.head_dim;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
@@ -427,7 +413,6 @@ __global__ void attn_combine_kernel(AttnPagedArgs a) {
         for (int s = 0; s < n_active; ++s) o += part[static_cast<size_t>(s) * (hd + 2) + 2 + d] * expf(part[static_cast<size_t>(s) * (hd + 2)] - mx);
         a.out[(static_cast<size_t>(t) * a.n_head + head) * hd + d] = o / lsum;
     }
-    stamp(a.trace2, 7, 4);
 }
 
 size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim) {
@@ -436,8 +421,6 @@ size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim) {
 
 int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStream_t s) {
     AttnPagedArgs a = a_in;
-    a.trace = trace_slot(c);
-    a.trace2 = c->d_trace ? c->d_trace + 8 * ((c->launches + 1) % 512) : nullptr;
     const int G = a.n_head / a.n_kv;
     if (G < 1 || G > 8 || a.n_head % a.n_kv) return set_status(c, GGB_INVALID_PARAM, "attention: query heads per KV head must be 1..8");
     const int hd = a.head_dim;
@@ -447,14 +430,15 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
         const int st = launch_attn_prefill(c, a, n_tok, s);
         if (st != GGB_NOT_FOUND) return st;
     }
+    if (a.partial_tok_cap > 0 && n_tok > a.partial_tok_cap)
+        return set_status(c, GGB_INVALID_PARAM, "attention: prompt chunk larger than the split scratch and not covered by the tensor-core kernel");
     dim3 grid(a.n_kv, a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
     size_t smem = 0;
 #define GGB_ATTN_CASE(HD)                                                                                              \
     {                                                                                                                  \
         smem = sizeof(uint32_t) * (64 * (HD / 2) + 64 * (HD / 2 + 1)) + sizeof(float) * (8 * HD + 8 * 64 + 24 + 12) + 2 * 2 * HD + 16; \
-        static size_t allowed = 48 * 1024;                                                                              \
-        if (smem > allowed) { e = cudaFuncSetAttribute(attn_tile_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); allowed = smem; } \
+        e = ensure_dynamic_smem(c, attn_tile_kernel<HD>, smem);                                                        \
         if (e == cudaSuccess) e = launch_pdl(c, attn_tile_kernel<HD>, grid, dim3(128), smem, s, a);                     \
     }
     if (hd == 64) GGB_ATTN_CASE(64)

@@ -22,7 +22,6 @@ struct KvAppendArgs {
     int pos0;
     int n_head, n_kv, head_dim, page, neox;
     float eps;
-    unsigned long long* trace;   // optional time stamps (tuning aid)
 };
 
 struct AttnPagedArgs {
@@ -31,6 +30,7 @@ struct AttnPagedArgs {
     const __nv_bfloat16* v_cache;
     const int32_t* block_table;
     float* partial;           // [n_tok][n_head][n_splits][hd + 2] scratch
+    int partial_tok_cap;      // tokens `partial` has room for (0: the caller sized it for this call)
     float* out;               // [n_tok][n_head][hd]
     const int32_t* d_pos;
     int pos0;
@@ -48,8 +48,6 @@ struct AttnPagedArgs {
     const float* q_norm;
     const float* k_norm;
     float eps;
-    unsigned long long* trace;   // optional time stamps (tuning aid)
-    unsigned long long* trace2;
 };
 
 int launch_rope_append(Context* c, const KvAppendArgs& a, int n_tok, cudaStream_t s);

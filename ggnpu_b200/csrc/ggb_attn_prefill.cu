@@ -188,8 +188,7 @@ int launch_attn_prefill(Context* c, const AttnPagedArgs& a, int n_tok, cudaStrea
     if (a.head_dim == 64) {
         attn_prefill_kernel<64><<<grid, 128, smem, s>>>(a, n_tok);
     } else {
-        static bool attr = false;
-        if (!attr) { e = cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); attr = true; }
+        e = ensure_dynamic_smem(c, attn_prefill_kernel<128>, smem);
         if (e == cudaSuccess) attn_prefill_kernel<128><<<grid, 128, smem, s>>>(a, n_tok);
     }
     if (e != cudaSuccess) return cuda_status(c, e, "attention prefill attr");

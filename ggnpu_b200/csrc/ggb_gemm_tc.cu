@@ -99,11 +99,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// tuning aid (GGB_TC_TRACE=1): %globaltimer stamps of CTA (0,0): [0..63] MMA thread (4 per step: a ready,
-// b ready, issued, -), [64..127] dequant warp 0 (4 per step: start, stage free, arrived, -)
-__device__ unsigned long long g_tc_trace[128];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
 struct GemmArgs {
     PackedW w, w2;                // w2: second matrix of the fused gate/up pair (dual)
     const __half* xb;             // activation tile images, see x_prep_kernel
@@ -116,7 +111,6 @@ struct GemmArgs {
     int stages;
     int steps_per_split;          // K steps per CTA (= K / 64 without split-K)
     float* ws;                    // split-K partial sums, nullptr without split-K
-    int trace;
     __half* y_img;                // dual only: write silu(gate) * up as the fp16 tile image of the next GEMM (K = N) instead of y
     int* err;
 };
@@ -339,9 +333,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             uint32_t a_lo = a_lo0, b_lo = b_lo0, accumulate = 0u;
             int s = 0; uint32_t par = 0;
             for (int ks = kw0; ks < kw1; ++ks) {
-                const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && ks >= 8 && ks < 24;
                 ok = mbar_wait(&full_bar[s], par, a.err);
-                if (tr) g_tc_trace[4 * (ks - 8)] = gtime();
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -351,7 +343,6 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                         umma_f16(tmem_d + i * a.tn, desc_hi | (a_lo + i * 1024 + 2 * kk), desc_hi | (b_lo + 2 * kk), idesc, (kk == 0) ? accumulate : 1u);
                 }
                 umma_commit(&free_bar[s]);
-                if (tr) g_tc_trace[4 * (ks - 8) + 2] = gtime();
                 accumulate = 1u;
                 a_lo += a_step; b_lo += b_step;
                 if (++s == S) { s = 0; par ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
@@ -435,8 +426,6 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         // one pipeline step: fetch the fragments two of this warp's steps ahead into `ahead`, fill stage s_cur from `cur`
         auto step = [&](const int ks, const Frag& cur, Frag& ahead) {
             uint8_t* At = stage_ptr + static_cast<size_t>(s_cur) * a_bytes;
-            const bool tr = a.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && ks >= 8 && ks < 24;
-            if (tr) g_tc_trace[64 + 4 * (ks - 8)] = gtime();
             if (FMT != F_GEN && ks + 2 * stride < kw1) load_frag(ks + 2 * stride, ahead);
             if ((FMT == F_Q4K || FMT == F_Q6K) && (ks & 3) == ks_first) {
                 // the previous block's readers are past their __syncwarp; expand this block's scales
@@ -449,7 +438,6 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                 __syncwarp();
             }
             if (ks - kw0 >= S && ok) ok = mbar_wait(&free_bar[s_cur], par_free, a.err);
-            if (tr) g_tc_trace[64 + 4 * (ks - 8) + 1] = gtime();
             if (FMT == F_Q4K || FMT == F_Q6K) {
 #pragma unroll
                 for (int hi = 0; hi < 2; ++hi) {                       // 0: row g, 1: row g + 8
@@ -489,7 +477,6 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy stores -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full_bar[s_cur]);
-            if (tr) g_tc_trace[64 + 4 * (ks - 8) + 2] = gtime();
             s_cur += stride;
             if (s_cur >= S) { s_cur -= S; par_free ^= 1; }
         };
@@ -581,12 +568,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, i
 
 template <int FMT, int RT>
 int launch_one(Context* c, const GemmArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return cuda_status(c, e, "gemm_tc attr");
-        allowed = smem;
-    }
+    const cudaError_t ea = ensure_dynamic_smem(c, gemm_tc_kernel<FMT, RT>, smem);
+    if (ea != cudaSuccess) return cuda_status(c, ea, "gemm_tc attr");
     const cudaError_t e = launch_pdl(c, gemm_tc_kernel<FMT, RT>, grid, dim3(kThreadsG), smem, s, a);
     c->launches++;
     return cuda_status(c, e != cudaSuccess ? e : cudaGetLastError(), "gemm_tc launch");
@@ -641,17 +624,14 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     if (splits > 1 && gemm_tc_ws_floats(g) > ws_floats) return GGB_NOT_FOUND;
 
     int fmt = F_GEN;
-    if (!c->tc_generic) {
-        if (g.w.type == T_Q4_K && g.w.layout == 1) fmt = F_Q4K;
-        else if (g.w.type == T_Q6_K && g.w.layout == 1) fmt = F_Q6K;
-        else if (g.w.type == T_Q8_0 && g.w.layout == 0) fmt = F_Q80;
-    }
+    if (g.w.type == T_Q4_K && g.w.layout == 1) fmt = F_Q4K;
+    else if (g.w.type == T_Q6_K && g.w.layout == 1) fmt = F_Q6K;
+    else if (g.w.type == T_Q8_0 && g.w.layout == 0) fmt = F_Q80;
     // two weight tiles per CTA halve the activation traffic per flop; one tile doubles the CTA count
     int rt = 2;
     if (!dual) {
         const int64_t ctas2 = (g.w.N + 255) / 256 * m_tiles * splits;
         if (g.w.N <= 128 || ctas2 < (c->sm_count * 3) / 4) rt = 1;
-        if (c->tc_rt == 1 || c->tc_rt == 2) rt = g.w.N <= 128 ? 1 : c->tc_rt;
     }
     int cols = 32;
     while (cols < tn * rt) cols <<= 1;
@@ -675,19 +655,6 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     a.M = g.M; a.K = K; a.ldc = g.ldc; a.epi = g.epi; a.dual = dual ? 1 : 0; a.tn = tn; a.tmem_cols = cols; a.stages = stages; a.err = c->d_err;
     a.steps_per_split = K / kBK / splits; a.ws = splits > 1 ? d_ws : nullptr;
     dim3 grid(static_cast<unsigned>((g.w.N + (dual ? 128 : 128 * rt) - 1) / (dual ? 128 : 128 * rt)), static_cast<unsigned>(m_tiles), static_cast<unsigned>(splits));
-    static const bool trace = getenv("GGB_TC_TRACE") != nullptr;
-    a.trace = trace ? 1 : 0;
-    struct Dump { Context* c; cudaStream_t s; int sa, tn, rt; ~Dump() {
-        if (!trace) return;
-        unsigned long long t[128];
-        cudaStreamSynchronize(s);
-        if (cudaMemcpyFromSymbol(t, g_tc_trace, sizeof(t)) != cudaSuccess) return;
-        fprintf(stderr, "[tc trace] stages %d tn %d rt %d\n", sa, tn, rt);
-        for (int i = 0; i < 16; ++i)
-            fprintf(stderr, "[tc trace] step %2d mma: a_ready %6lld b_ready %6lld issued %6lld | warp0: start %6lld free %6lld arrived %6lld\n", i + 8,
-                    (long long)(t[4 * i] - t[0]), (long long)(t[4 * i + 1] - t[0]), (long long)(t[4 * i + 2] - t[0]),
-                    (long long)(t[64 + 4 * i] - t[0]), (long long)(t[64 + 4 * i + 1] - t[0]), (long long)(t[64 + 4 * i + 2] - t[0]));
-    } } dump{c, s, stages, tn, rt};
     int st;
     switch (fmt * 2 + (rt - 1)) {
     case F_GEN * 2 + 0: st = launch_one<F_GEN, 1>(c, a, grid, smem, s); break;

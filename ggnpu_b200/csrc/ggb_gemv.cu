@@ -523,11 +523,9 @@ template <class F, int MT, int RW, bool DUAL>
 static cudaError_t launch_one(Context* c, const GemvArgs& a, int m0, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(MT) * a.w.K * sizeof(float);
     auto kern = gemv_kernel<F, MT, RW, DUAL>;
-    static size_t smem_allowed = 48 * 1024;      // per instantiation; raised on first need, outside any capture
-    if (smem > smem_allowed) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    {   // raised on first need, outside any capture
+        const cudaError_t e = ensure_dynamic_smem(c, kern, smem);
         if (e != cudaSuccess) return e;
-        smem_allowed = smem;
     }
     const int64_t groups = (a.w.N + RW - 1) / RW;
     const int wpc = 4;

@@ -27,13 +27,8 @@ namespace ggb {
 
 namespace {
 
-// The kernel is compiled for 8 and for 16 consumer warps (template parameter kWarps; one more warp
-// produces).  Sixteen warps halve the per-warp instruction stream of a small matrix, whose time is the
-// latency of that stream rather than bandwidth; eight leave each warp 166 registers and deeper rings.
+// kWarps consumer warps (8: each keeps 166 registers and a deep private ring) plus one producer warp.
 constexpr int kMaxStages = 64;
-#ifndef GGB_MMA_MIN_BLOCKS
-#define GGB_MMA_MIN_BLOCKS 1
-#endif
 constexpr uint32_t kSpinLimit = 1u << 17;         // each poll can suspend for microseconds: about half a second in all
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -61,9 +56,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void stamp(unsigned long long* tr, int i) {
-    if (tr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; }
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -182,7 +174,6 @@ struct MmaArgs {
     const float* xscale;   // optional: x[i] is multiplied by xscale[i / xscale_run] (router weights folded into the activations)
     int xscale_run;
     int* err;
-    unsigned long long* trace;   // optional time stamps of CTA 0
 };
 
 // Work split inside a CTA.  The CTA owns a contiguous range of row groups (16 rows each).  Its 8
@@ -196,7 +187,7 @@ struct MmaArgs {
 // dynamic shared memory map: [ring: 8 * P * stage_bytes][limb planes: 3*M * (K + 16) bytes]
 //   [asum: M * K/32 floats][xs: M * K/256 floats][comb: 2 * 8 * nmat * 16 * M floats]
 template <int kWarps>
-__global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mma_q4k_kernel(const MmaArgs a) {
+__global__ void __launch_bounds__((kWarps + 1) * 32, 1) gemv_mma_q4k_kernel(const MmaArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ float red[2 * kWarps];
@@ -222,8 +213,6 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
         for (int s = 0; s < kWarps * a.P; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         x_ready = 0;
-        stamp(a.trace, 0);
-        if (a.trace && blockIdx.x == 0) a.trace[6] = 1;
     }
     __syncthreads();
     pdl_launch();
@@ -298,7 +287,6 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
     const int team = warp / a.ws, member = warp % a.ws;
     const int mshift = 16 * (t & 1);                             // this lane's two min bytes: sub-blocks 2t, 2t+1
     pdl_wait();
-    if (warp == 0) stamp(a.trace, 1);
     // Residual epilogue of a team: the lanes that will store the first row group's rows fetch their
     // residual values now, so that the load's latency passes under the prologue and the main loop.
     const bool resid_pre = a.epi == EPI_RESIDUAL && a.ws > 1 && member == 0 && lane < 16 * M && team < n_rg && a.ncat == 0 && !a.sel;
@@ -353,7 +341,6 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
             for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) am[u] = fmaxf(am[u], __shfl_xor_sync(0xFFFFFFFFu, am[u], o));
-            if (warp == 0 && m == 0 && bb == warp) stamp(a.trace, 3);      // first values have arrived
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int b = bb + u * kWarps;
@@ -402,7 +389,6 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
         if (lane == 0) red[m * kWarps + warp] = ss;
     }
     __syncwarp();
-    if (warp == 0) stamp(a.trace, 4);                                                        // warp 0 done converting
     if (lane == 0) atomicAdd(&x_ready, 1);      // this warp's x values have arrived: weight streaming may go deep
     consumer_sync<kWarps>();
     float inv[2] = {1.0f, 1.0f};
@@ -417,7 +403,6 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
             }
         }
     }
-    if (warp == 0) stamp(a.trace, 2);
 
     int st = 0;
     uint32_t ph = 0;
@@ -612,9 +597,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, GGB_MMA_MIN_BLOCKS) gemv_mm
                 }
             }
         }
-        if (rg == 0) stamp(a.trace, 5);
     }
-    if (warp == 0) stamp(a.trace, 7);
 }
 
 template <int kWarps>
@@ -654,11 +637,7 @@ int launch_mma_t(Context* c, const GemvArgs& g, cudaStream_t s) {
     sb = std::min(sb, nb);
     if (g.sel && g.sel_mode == 2) sb = g.w.nb;            // one tile = one chosen expert's blocks of the row group
     const size_t fixed = static_cast<size_t>(3 * M) * (K + 16) + sizeof(float) * M * (K / 32 + K / 16 + K / 256) + sizeof(float) * 2 * kWarps * 2 * 32 + 64;
-    static const size_t budget = [] {
-        const char* e = getenv("GGB_MMA_SMEM_KB");          // tuning knob: shared memory per CTA
-        const long kb = e ? atol(e) : 0;
-        return static_cast<size_t>(kb >= 32 && kb <= 220 ? kb : 200) * 1024;
-    }();
+    const size_t budget = 200 * 1024;                       // shared memory per CTA given to rings + activations
     int spr, stage_bytes, P;
     for (;;) {
         spr = (nb + sb - 1) / sb;
@@ -684,13 +663,10 @@ int launch_mma_t(Context* c, const GemvArgs& g, cudaStream_t s) {
     a.sel = g.sel; a.sel_mode = g.sel ? g.sel_mode : 0; a.sel_groups = g.sel ? g.sel_rows / 16 : 0;
     a.klog = K; a.nblog = nb; a.nlog = n_log; a.xscale = g.xscale; a.xscale_run = g.xscale_run > 0 ? g.xscale_run : 1;
     a.err = c->d_err;
-    a.trace = trace_slot(c);
 
-    static size_t smem_allowed = 48 * 1024;
-    if (smem > smem_allowed) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_q4k_kernel<kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    {
+        const cudaError_t e = ensure_dynamic_smem(c, gemv_mma_q4k_kernel<kWarps>, smem);
         if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma attr");
-        smem_allowed = smem;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(G));
@@ -709,13 +685,6 @@ int launch_mma_t(Context* c, const GemvArgs& g, cudaStream_t s) {
 
 }  // namespace
 
-int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) {
-    static const int warps = [] { const char* e = getenv("GGB_MMA_WARPS"); return e ? atoi(e) : 8; }();
-    if (warps == 16) {
-        const int st = launch_mma_t<16>(c, g, s);
-        if (st != GGB_NOT_FOUND) return st;
-    }
-    return launch_mma_t<8>(c, g, s);
-}
+int launch_gemv_mma(Context* c, const GemvArgs& g, cudaStream_t s) { return launch_mma_t<8>(c, g, s); }
 
 }  // namespace ggb

@@ -61,9 +61,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void stamp(unsigned long long* tr, int i) {
-    if (tr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); tr[i] = t; }
-}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
@@ -207,7 +204,6 @@ struct TmaGemvArgs {
     int wk;               // K slices
     int units_per_slice;
     int* err;
-    unsigned long long* trace;   // optional time stamps of CTA 0
     // stacked matrices (q, k, v of one layer): tiles [tile_first[i], tile_first[i + 1]) belong to matrix
     // i + 1, which has its own streams, row count, output and bias; all share K, the format and x
     int n_cat;
@@ -257,7 +253,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
         for (int s = 0; s < a.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x == 0) { stamp(a.trace, 0); if (a.trace && blockIdx.x == 0) a.trace[6] = 2; }
     __syncthreads();
     pdl_launch();       // the next kernel may start streaming its own weights
 
@@ -295,7 +290,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
         // ---------------- consumers ----------------
         const int tid = threadIdx.x;                      // 0 .. 255
         pdl_wait();                                       // x (and resid) come from the previous kernel
-        if (warp == 0) stamp(a.trace, 1);
         // 1. optional RMSNorm scale
         float inv = 1.0f;
         if (a.gamma) {
@@ -351,7 +345,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
             if (lane == 0) xscale[b] = scale * (1.0f / 16384.0f);
         }
         consumer_sync();
-        if (warp == 0) stamp(a.trace, 2);
         // 3. this lane's units: slice wk_i of K, units u = slice_begin + lane + 32 i
         const int wk_i = warp % a.wk, wr_i = warp / a.wk, wr_n = kConsumerWarps / a.wk;
         const int units = K >> 5;
@@ -430,7 +423,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                 }
             }
         }
-        if (warp == 0) stamp(a.trace, 7);
     }
 }
 
@@ -483,7 +475,6 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     a.w = g.w; a.w2 = g.w2; a.x = g.x; a.y = g.y; a.bias = g.bias; a.resid = g.resid; a.gamma = g.gamma; a.eps = g.eps; a.epi = g.epi;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
     a.err = c->d_err;
-    a.trace = trace_slot(c);
     a.n_cat = g.n_cat;
     for (int i = 0; i < g.n_cat; ++i) {
         a.tile_first[i] = tile_first[i];
@@ -492,11 +483,9 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     }
 
     auto kern = gemv_tma_kernel<F, DUAL>;
-    static size_t smem_allowed = 48 * 1024;
-    if (smem > smem_allowed) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    {
+        const cudaError_t e = ensure_dynamic_smem(c, kern, smem);
         if (e != cudaSuccess) return cuda_status(c, e, "gemv_tma attr");
-        smem_allowed = smem;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(std::min(n_tiles, c->sm_count)));

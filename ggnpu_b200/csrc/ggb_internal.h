@@ -83,15 +83,12 @@ struct Context {
     int* d_err = nullptr;     // device word: non-zero after a bounded device-side wait gave up
     bool use_pdl = true;      // launch the streaming kernels with programmatic dependent launch
     bool use_tma = true;      // M == 1 GEMV through the bulk-copy ring kernel
-    unsigned long long* d_trace = nullptr;   // tuning aid (GGB_TRACE=1): %globaltimer stamps of CTA 0, printed by ggb_sync
     bool use_mma = true;      // Q4_K in the row-group-major layout + int8 tensor-core GEMV (M <= 2)
     bool use_tc = true;       // M >= tc_min_m through the tcgen05 GEMM (fp16 operands, fp32 accumulation in TMEM)
     // 17: up to 16 rows keep fp32 activations (two rows per GEMV pass, rel-L2 1e-5 against the exact
     // product); from 17 rows on one pass of the tensor-core GEMM (~19 us for a 9-14 MB matrix whatever
     // M <= 64) beats nine and more GEMV passes (~3.5 us per row)
     int tc_min_m = 17;
-    bool tc_generic = false;  // tuning aid: every format through the generic (exact fp32 decode) tile filler
-    int tc_rt = 0;            // tuning aid: force 1 or 2 weight tiles per CTA (0: heuristic)
     // tensor-parallel group (ggb_tp.cu); tp_size == 1: none
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
@@ -124,8 +121,15 @@ int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, f
 size_t gemm_tc_xb_elems(const GemvArgs& a);
 size_t gemm_tc_ws_floats(const GemvArgs& a);       // split-K partial sums (0: no split)
 inline size_t gemm_tc_image_elems(int M, int K) { return static_cast<size_t>((M + 255) / 256) * 256 * K; }
-// tuning aid: 8 time-stamp words for the next launch (nullptr unless GGB_TRACE is set)
-inline unsigned long long* trace_slot(Context* c) { return c->d_trace ? c->d_trace + 8 * (c->launches % 512) : nullptr; }     // after a synchronise: turns the device error word into a status
+
+// Opt a kernel into `smem` bytes of dynamic shared memory (above the 48 KB default) on the context's
+// device.  The attribute belongs to the (device, function) pair, so the bytes already granted are kept
+// per pair behind one process-wide mutex: a second handle on another GPU gets its own call.
+cudaError_t ensure_dynamic_smem(Context* c, const void* func, size_t smem);
+template <class... KArgs>
+static inline cudaError_t ensure_dynamic_smem(Context* c, void (*kern)(KArgs...), size_t smem) {
+    return ensure_dynamic_smem(c, reinterpret_cast<const void*>(kern), smem);
+}
 
 // ggb_tp.cu: collectives over the handle's tensor-parallel group, on stream s (no-ops for a single rank)
 int tp_all_reduce(Context* c, float* d_buf, size_t count, cudaStream_t s);               // sum, in place

@@ -140,7 +140,7 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
             aa.q_norm = l.q_norm; aa.k_norm = l.k_norm; aa.eps = d.rms_eps;
         }
         aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = m->block_table;
-        aa.partial = m->partial; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
+        aa.partial = m->partial; aa.partial_tok_cap = kSmallChunk; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
         aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
         aa.pages_per_split = m->pages_per_split;
         // single-token steps: the output projection merges the attention splits itself

@@ -53,6 +53,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
     __shared__ float red_v[8];
     __shared__ int red_i[8];
     __shared__ float chosen[kMaxTopK];
+    __shared__ int picked[kMaxTopK];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,11 +77,27 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
         if (threadIdx.x == 0) {
             for (int q = 1; q < 8; ++q)
                 if (red_v[q] > red_v[0] || (red_v[q] == red_v[0] && red_i[q] < red_i[0])) { red_v[0] = red_v[q]; red_i[0] = red_i[q]; }
-            const int e = red_i[0];
+            int e = red_i[0];
+            float ev = red_v[0];
+            bool none = e < 0 || e >= n_expert;
+            for (int r = 0; r < j && !none; ++r) none = picked[r] == e;      // an exhausted (-inf) entry won the tie
+            if (none) {
+                // no candidate compared greater or equal (every remaining logit is NaN): take the lowest
+                // index not chosen yet, so that the ids stay valid rows of the expert tensors and the NaN
+                // reaches the output through the weights instead of through a wild index
+                e = 0;
+                for (int q = 0; q < n_expert; ++q) {
+                    bool taken = false;
+                    for (int r = 0; r < j; ++r) taken = taken || picked[r] == q;
+                    if (!taken) { e = q; break; }
+                }
+                ev = logit[e];
+            }
+            picked[j] = e;
             if (sel_glob) sel_glob[j] = e;
             sel[j] = (e >= ep_first && e < ep_first + ep_local) ? e - ep_first : -1;
-            chosen[j] = red_v[0];
-            logit[red_i[0]] = -INFINITY;
+            chosen[j] = ev;
+            logit[e] = -INFINITY;
         }
         __syncthreads();
     }

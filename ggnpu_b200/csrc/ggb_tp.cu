@@ -80,7 +80,7 @@ int nccl_status(Context* c, int rc, const char* what) {
 constexpr int kCap = 16384;            // floats per slot (64 KB)
 constexpr int kMaxBlocks = kCap / 1024;
 constexpr int kMaxRanks = 8;
-constexpr unsigned long long kWaitNs = 4000000000ull;     // 4 s: a peer's kernel may start late, never this late
+constexpr unsigned long long kWaitNs = 4000000000ull;     // 4 s: a peer's kernel may start late, never this late (GGB_TP_WAIT_MS overrides)
 
 struct PeerRegion {                    // device layout of one rank's region
     float buf[2][kMaxRanks][kCap];
@@ -93,6 +93,7 @@ struct OneShotArgs {
     int count, rank, size;
     PeerRegion* region[kMaxRanks];     // region[rank] is this rank's own
     int* err;
+    unsigned long long wait_ns;        // how long to wait for a peer's flag before giving up
 };
 
 __global__ void __launch_bounds__(256) tp_oneshot_allreduce_kernel(const OneShotArgs a) {
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(256) tp_oneshot_allreduce_kernel(const OneShot
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         while (static_cast<int>(*f - epoch) < 0) {
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            if (t - t0 > kWaitNs) { failed = 1; atomicExch(a.err, 5); break; }
+            if (t - t0 > a.wait_ns) { failed = 1; atomicExch(a.err, 5); break; }
         }
     }
     __threadfence_system();
@@ -147,6 +148,8 @@ int tp_all_reduce(Context* c, float* d_buf, size_t count, cudaStream_t s) {
         !(reinterpret_cast<uintptr_t>(d_buf) & 15)) {
         OneShotArgs a{};
         a.x = d_buf; a.count = static_cast<int>(count); a.rank = c->tp_rank; a.size = c->tp_size; a.err = c->d_err;
+        a.wait_ns = kWaitNs;
+        if (const char* w = getenv("GGB_TP_WAIT_MS")) { const long ms = atol(w); if (ms > 0 && ms <= 60000) a.wait_ns = static_cast<unsigned long long>(ms) * 1000000ull; }
         for (int q = 0; q < c->tp_size; ++q) a.region[q] = static_cast<PeerRegion*>(c->tp_region[q]);
         const cudaError_t e = launch_pdl(c, tp_oneshot_allreduce_kernel, dim3(static_cast<unsigned>((count + 1023) / 1024)), dim3(256), 0, s, a);
         c->launches++;

@@ -409,6 +409,142 @@ def build_model(cfg: ModelConfig, device: str = "cpu") -> SynthModel:
     return m
 
 
+@dataclass
+class Qwen35MoeConfig:
+    """qwen35moe: Gated DeltaNet layers with a gated full-attention layer every `attn_every` layers, MoE FFN in
+    every layer (metadata keys and tensor names as src/cli/main.cpp:2181-2218, 2894-3193 reads them)."""
+    arch: str = "qwen35moe"
+    n_layer: int = 40
+    hidden: int = 2048
+    n_head: int = 16            # full-attention query heads
+    n_kv: int = 2
+    head_dim: int = 256         # attention.key_length
+    rope_dim: int = 64          # rope.dimension_count: rotated leading dims of each head
+    rope_base: float = 1e7
+    conv_k: int = 4
+    sk: int = 128               # ssm.state_size: DeltaNet head size (keys and values)
+    n_vhead: int = 32           # ssm.inner_size / sk
+    n_khead: int = 16           # ssm.group_count
+    n_expert: int = 256
+    top_k: int = 8
+    eff: int = 512              # expert_feed_forward_length (routed and shared experts)
+    attn_every: int = 4         # layers L with (L + 1) % attn_every == 0 are full attention
+    vocab: int = 248320
+    ctx: int = 2048
+    rms_eps: float = 1e-6
+    tied: bool = True
+    wtype: int = Q4_K
+    wtype_alt: int = Q6_K       # attention output and expert down projections
+    norm_jitter: float = 0.1
+    seed: int = 4321
+
+    @property
+    def ffn(self) -> int:       # the loader wants feed_forward_length; the MoE path never uses it
+        return self.eff
+
+    def is_ssm(self, layer: int) -> bool:
+        return (layer + 1) % self.attn_every != 0
+
+
+QWEN35MOE = Qwen35MoeConfig()
+
+
+def tiny_q35_config(**kw) -> Qwen35MoeConfig:
+    base = dict(n_layer=4, hidden=256, n_head=2, n_kv=1, head_dim=256, rope_dim=64, sk=64, n_vhead=4, n_khead=2,
+                n_expert=8, top_k=2, eff=256, vocab=320, ctx=64)
+    base.update(kw)
+    return Qwen35MoeConfig(**base)
+
+
+def q35_kv(cfg: Qwen35MoeConfig) -> dict:
+    a = cfg.arch
+    return {
+        "general.architecture": a,
+        f"{a}.context_length": cfg.ctx, f"{a}.embedding_length": cfg.hidden, f"{a}.block_count": cfg.n_layer,
+        f"{a}.feed_forward_length": cfg.ffn, f"{a}.attention.head_count": cfg.n_head,
+        f"{a}.attention.head_count_kv": cfg.n_kv, f"{a}.attention.layer_norm_rms_epsilon": float(cfg.rms_eps),
+        f"{a}.rope.freq_base": float(cfg.rope_base), f"{a}.rope.dimension_count": cfg.rope_dim,
+        f"{a}.attention.key_length": cfg.head_dim, f"{a}.ssm.conv_kernel": cfg.conv_k, f"{a}.ssm.state_size": cfg.sk,
+        f"{a}.ssm.inner_size": cfg.n_vhead * cfg.sk, f"{a}.ssm.group_count": cfg.n_khead,
+        f"{a}.expert_count": cfg.n_expert, f"{a}.expert_used_count": cfg.top_k,
+        f"{a}.expert_feed_forward_length": cfg.eff, f"{a}.nextn_predict_layers": 0,
+        "tokenizer.ggml.model": "llama",
+        "tokenizer.ggml.tokens": [chr(0x10000 + i) for i in range(cfg.vocab)],
+        "tokenizer.ggml.scores": [0.0] * cfg.vocab,
+        "tokenizer.ggml.add_space_prefix": False,
+    }
+
+
+def build_q35_model(cfg: Qwen35MoeConfig, device: str = "cpu") -> SynthModel:
+    """Random-init qwen35moe tensors: matrices N(0, 0.02) quantised (Q4_K; Q6_K for attention output and expert
+    down), F32 router / alpha / beta / conv / decay vectors, norm gammas 1 + jitter N(0,1)."""
+    m = SynthModel(cfg)
+    m.kv = lambda: q35_kv(cfg)
+    dev = torch.device(device)
+
+    def randn(name, *shape, scale=1.0):
+        g = torch.Generator(device=dev)
+        g.manual_seed(_name_seed(cfg.seed, name))
+        return torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale
+
+    def mat(name, n, k, tid, n_exp=0):
+        rows = n * max(n_exp, 1)
+        rows_per = max(1, (64 << 20) // max(k, 1))
+        g = torch.Generator(device=dev)
+        g.manual_seed(_name_seed(cfg.seed, name))
+        parts = []
+        for r0 in range(0, rows, rows_per):
+            w = torch.randn(min(rows_per, rows - r0), k, generator=g, device=dev, dtype=torch.float32) * 0.02
+            parts.append(quantize(w, tid).cpu())
+        m.add(name, tid, [k, n, n_exp] if n_exp else [k, n], torch.cat(parts).numpy())
+
+    def f32(name, dims, t):
+        m.add(name, F32, list(dims), t.cpu().contiguous().numpy().view(np.uint8).copy())
+
+    def norm(name, n):
+        f32(name, [n], 1.0 + cfg.norm_jitter * randn(name, n))
+
+    H, sk = cfg.hidden, cfg.sk
+    key_dim, value_dim = cfg.n_khead * sk, cfg.n_vhead * sk
+    conv_dim = 2 * key_dim + value_dim
+    qdim, kvdim = cfg.n_head * cfg.head_dim, cfg.n_kv * cfg.head_dim
+    mat("token_embd.weight", cfg.vocab, H, cfg.wtype)
+    norm("output_norm.weight", H)
+    if not cfg.tied:
+        mat("output.weight", cfg.vocab, H, cfg.wtype_alt)
+    for l in range(cfg.n_layer):
+        p = f"blk.{l}."
+        norm(p + "attn_norm.weight", H)
+        norm(p + "post_attention_norm.weight", H)
+        if cfg.is_ssm(l):
+            mat(p + "attn_qkv.weight", conv_dim, H, cfg.wtype)
+            mat(p + "attn_gate.weight", value_dim, H, cfg.wtype)
+            f32(p + "ssm_alpha.weight", [H, cfg.n_vhead], randn(p + "ssm_alpha.weight", cfg.n_vhead, H, scale=0.05))
+            f32(p + "ssm_beta.weight", [H, cfg.n_vhead], randn(p + "ssm_beta.weight", cfg.n_vhead, H, scale=0.05))
+            # conv taps: [channel][tap], newest tap last (main.cpp:2927-2935)
+            f32(p + "ssm_conv1d.weight", [cfg.conv_k, conv_dim], randn(p + "ssm_conv1d.weight", conv_dim, cfg.conv_k, scale=0.5))
+            f32(p + "ssm_a", [cfg.n_vhead], -torch.exp(randn(p + "ssm_a", cfg.n_vhead, scale=0.5)))   # stored as -exp(A_log)
+            f32(p + "ssm_dt.bias", [cfg.n_vhead], randn(p + "ssm_dt.bias", cfg.n_vhead, scale=0.5))
+            norm(p + "ssm_norm.weight", sk)
+            mat(p + "ssm_out.weight", H, value_dim, cfg.wtype)
+        else:
+            mat(p + "attn_q.weight", 2 * qdim, H, cfg.wtype)
+            mat(p + "attn_k.weight", kvdim, H, cfg.wtype)
+            mat(p + "attn_v.weight", kvdim, H, cfg.wtype)
+            mat(p + "attn_output.weight", H, qdim, cfg.wtype_alt)
+            norm(p + "attn_q_norm.weight", cfg.head_dim)
+            norm(p + "attn_k_norm.weight", cfg.head_dim)
+        f32(p + "ffn_gate_inp.weight", [H, cfg.n_expert], randn(p + "ffn_gate_inp.weight", cfg.n_expert, H, scale=0.05))
+        mat(p + "ffn_gate_exps.weight", cfg.eff, H, cfg.wtype, cfg.n_expert)
+        mat(p + "ffn_up_exps.weight", cfg.eff, H, cfg.wtype, cfg.n_expert)
+        mat(p + "ffn_down_exps.weight", H, cfg.eff, cfg.wtype_alt, cfg.n_expert)
+        mat(p + "ffn_gate_shexp.weight", cfg.eff, H, cfg.wtype)
+        mat(p + "ffn_up_shexp.weight", cfg.eff, H, cfg.wtype)
+        mat(p + "ffn_down_shexp.weight", H, cfg.eff, cfg.wtype_alt)
+        f32(p + "ffn_gate_inp_shexp.weight", [H], randn(p + "ffn_gate_inp_shexp.weight", H, scale=0.05))
+    return m
+
+
 def prompt_text(ids) -> str:
     """Token ids -> the prompt string the code-point tokenizer maps back to them."""
     return "".join(chr(0x10000 + int(i)) for i in ids)

@@ -46,11 +46,24 @@ def build_oracle() -> str:
     return ORACLE_SO
 
 
-def build_ref(ref_root: str = "/root/reference") -> str | None:
+def reference_root() -> str | None:
+    """Where the reference tree lies: $GGNPU_REFERENCE, else a `reference` directory next to this
+    checkout.  None when neither holds the reference's CLI sources."""
+    for cand in (os.environ.get("GGNPU_REFERENCE"), os.path.join(HERE, "..", "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "cli")):
+            return os.path.abspath(cand)
+    return None
+
+
+def build_ref(ref_root: str | None = None) -> str | None:
     """Build oracle/_ref from the reference tree when it is present; otherwise
     use a prebuilt copy if there is one."""
-    if os.path.isdir(os.path.join(ref_root, "src", "cli")):
+    ref_root = ref_root or reference_root()
+    if ref_root:
         subprocess.check_call(["make", "-s", "-j8", "-C", HERE, "ref", f"REF={ref_root}"])
+        # the unmodified reference CLI linked against the CUDA backend (the drop-in check)
+        if os.path.exists(os.path.join(HERE, "..", "ggnpu_b200", "libggb200.so")):
+            subprocess.check_call(["make", "-s", "-j8", "-C", HERE, "dropin", f"REF={ref_root}"])
     return REF_SO if os.path.exists(REF_SO) else None
 
 
@@ -94,6 +107,19 @@ class Oracle:
         L.ggo_model_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.ggo_block_elems.argtypes = [C.c_uint32]
         L.ggo_block_bytes.argtypes = [C.c_uint32]
+        L.ggo_q35_new.restype = C.c_void_p
+        L.ggo_q35_new.argtypes = [C.c_int] * 15 + [C.c_float] * 2
+        L.ggo_q35_free.argtypes = [C.c_void_p]
+        L.ggo_q35_set_globals.argtypes = [C.c_void_p, _u8p, C.c_uint32, _u8p, C.c_uint32, _f32p]
+        L.ggo_q35_set_kind.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.ggo_q35_set_weight.argtypes = [C.c_void_p, C.c_int, C.c_int, _u8p, C.c_uint32]
+        L.ggo_q35_set_vec.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p]
+        L.ggo_q35_rope_table.argtypes = [C.c_int64, C.c_int, C.c_float, _f32p, _f32p]
+        L.ggo_q35_forward.argtypes = [C.c_void_p, C.c_int32, C.c_int, _f32p, _f32p]
+        L.ggo_q35_kv.restype = _f32p
+        L.ggo_q35_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.ggo_q35_rec_state.restype = _f32p
+        L.ggo_q35_rec_state.argtypes = [C.c_void_p, C.c_int]
 
     def block_geom(self, t):
         return self.lib.ggo_block_elems(t), self.lib.ggo_block_bytes(t)
@@ -299,6 +325,85 @@ class OracleModel:
     def close(self):
         if self.h:
             self.o.lib.ggo_model_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_Q35_W = {"attn_qkv": 0, "attn_gate": 1, "ssm_alpha": 2, "ssm_beta": 3, "ssm_out": 4, "attn_q": 5, "attn_k": 6, "attn_v": 7,
+          "attn_output": 8, "ffn_gate_exps": 9, "ffn_up_exps": 10, "ffn_down_exps": 11, "ffn_gate_shexp": 12,
+          "ffn_up_shexp": 13, "ffn_down_shexp": 14}
+_Q35_V = {"attn_norm.weight": 0, "post_attention_norm.weight": 1, "ssm_conv1d.weight": 2, "ssm_a": 3, "ssm_dt.bias": 4,
+          "ssm_norm.weight": 5, "attn_q_norm.weight": 6, "attn_k_norm.weight": 7, "ffn_gate_inp.weight": 8,
+          "ffn_gate_inp_shexp.weight": 9}
+
+
+class OracleQ35Model:
+    """The qwen35moe forward of the reference CLI, restated (ggo_q35_forward), over the tensors of
+    ggnpu_b200.synth.build_q35_model.  One token per call, like the reference."""
+
+    def __init__(self, oracle: Oracle, synth):
+        self.o, self.cfg = oracle, synth.cfg
+        c = synth.cfg
+        L = oracle.lib
+        self._keep = []
+        self.h = L.ggo_q35_new(c.n_layer, c.hidden, c.n_head, c.n_kv, c.head_dim, c.rope_dim, c.conv_k, c.sk, c.n_vhead,
+                               c.n_khead, c.n_expert, c.top_k, c.eff, c.vocab, c.ctx, c.rms_eps, float(np.float32(c.rope_base)))
+        t = synth.tensors
+
+        def raw(name):
+            tid, _, b = t[name]
+            b = np.ascontiguousarray(b).view(np.uint8).reshape(-1)
+            self._keep.append(b)
+            return b, tid
+
+        emb, et = raw("token_embd.weight")
+        out, ot = raw("output.weight") if "output.weight" in t else (None, 0)
+        L.ggo_q35_set_globals(self.h, _bp(emb), et, _bp(out), ot, _fp(raw("output_norm.weight")[0].view(np.float32)))
+        for l in range(c.n_layer):
+            L.ggo_q35_set_kind(self.h, l, 1 if f"blk.{l}.ssm_conv1d.weight" in t else 0)
+            for nm, slot in _Q35_W.items():
+                key = f"blk.{l}.{nm}.weight"
+                if key in t:
+                    b, tid = raw(key)
+                    L.ggo_q35_set_weight(self.h, l, slot, _bp(b), tid)
+            for nm, slot in _Q35_V.items():
+                key = f"blk.{l}.{nm}"
+                if key in t:
+                    L.ggo_q35_set_vec(self.h, l, slot, _fp(raw(key)[0].view(np.float32)))
+
+    def forward(self, token, pos, want_hidden=False):
+        c = self.cfg
+        logits = np.empty(c.vocab, dtype=np.float32)
+        hid = np.empty(c.hidden, dtype=np.float32) if want_hidden else None
+        rc = self.o.lib.ggo_q35_forward(self.h, int(token), int(pos), _fp(logits), _fp(hid))
+        assert rc == 0
+        return (logits, hid) if want_hidden else logits
+
+    def feed(self, tokens, pos0=0):
+        """Run the tokens one by one from position pos0; returns the logits after the last."""
+        out = None
+        for i, tk in enumerate(tokens):
+            out = self.forward(tk, pos0 + i)
+        return out
+
+    def kv_row(self, layer, pos, want_v):
+        c = self.cfg
+        p = self.o.lib.ggo_q35_kv(self.h, layer, pos, int(want_v))
+        return np.ctypeslib.as_array(p, shape=(c.n_kv, c.head_dim)).copy()
+
+    def rec_state(self, layer):
+        c = self.cfg
+        p = self.o.lib.ggo_q35_rec_state(self.h, layer)
+        return np.ctypeslib.as_array(p, shape=(c.n_vhead, c.sk, c.sk)).copy()
+
+    def close(self):
+        if self.h:
+            self.o.lib.ggo_q35_free(self.h)
             self.h = None
 
     def __del__(self):

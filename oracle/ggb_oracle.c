@@ -636,8 +636,9 @@ GGO_API void ggo_model_set_vec(ggo_model* m, int layer, int which, const float* 
 }
 
 /* Mixture-of-experts FFN of one token, src/cli/main.cpp:3110-3193 (qwen35moe branch).
- * PARITY UNPINNED at unit level: the reference keeps this block inside main(), so it cannot be called
- * from the reference-built checker; it is restated line by line from the cited source.
+ * The reference keeps this block inside main(), so it cannot be called from the reference-built checker;
+ * it is restated line by line from the cited source and pinned end to end through ggo_q35_forward against
+ * the unmodified reference CLI's logits and greedy stream on synthetic qwen35moe models.
  *   router logits  :3117-3125  F32 [n_expert][hidden] . x, one running fp32 sum per expert
  *   top-k          :3128-3131  std::partial_sort by logit, descending (ties: unspecified there; lowest index here)
  *   weights        :3132-3135  exp(l - max) / sum over the k chosen
@@ -711,8 +712,8 @@ GGO_API int ggo_moe_ffn(const float* x, int hidden, const float* router, int n_e
 }
 
 /* One token of a Gated DeltaNet (linear attention) layer after its projections,
- * src/cli/main.cpp:2925-3023 (qwen35 / qwen35moe branch).  PARITY UNPINNED at unit level, like
- * ggo_moe_ffn: the reference keeps the block inside main().
+ * src/cli/main.cpp:2925-3023 (qwen35 / qwen35moe branch).  Pinned like ggo_moe_ffn: end to end through
+ * ggo_q35_forward against the reference CLI (the reference keeps the block inside main()).
  *   conv      :2925-2941  causal depthwise conv1d (conv_k taps, newest = this token) + SiLU; the state
  *                         holds the previous conv_k - 1 inputs [tap][channel] and is rolled
  *   q, k      :2956-2968  per key head L2-normalised over sk (eps 1e-6); q also scaled by 1/sqrt(sk)
@@ -863,3 +864,218 @@ GGO_API const float* ggo_model_kv(const ggo_model* m, int layer, int pos, int wa
     const size_t kvd = (size_t)m->n_kv * m->head_dim;
     return (want_v ? m->vcache : m->kcache) + ((size_t)layer * m->ctx + pos) * kvd;
 }
+
+/* ---- qwen35 / qwen35moe forward: src/cli/main.cpp:2859-3232 -------------------------------------
+ * One token per call, as the reference runs this architecture (no prompt batching, main.cpp:2327).
+ * Per layer: attn_norm -> Gated DeltaNet mixer (layers that have ssm_conv1d, :2900-3034, restated in
+ * ggo_deltanet_step) or gated full attention (:3035-3105) -> residual -> post_attention_norm ->
+ * MoE FFN (:3110-3193, restated in ggo_moe_ffn) -> residual; then output_norm and logits (:3504-3512,
+ * :3593-3598).  Every matmul is the exact path (M == 1 under GGNPU_FP32_MATMUL, :1379-1388), F32
+ * weights included (ssm_alpha / ssm_beta).
+ * Parity of this block (and through it of ggo_moe_ffn and ggo_deltanet_step) is pinned by the
+ * unmodified reference CLI's top-10 logits and greedy stream on a synthetic qwen35moe GGUF
+ * (tests/golden/ref_cli.npz, written by tests/golden/make_golden.py). */
+
+typedef struct {
+    int is_ssm;
+    const float *attn_norm, *post_norm;
+    /* DeltaNet layers */
+    ggo_weight qkv, zgate, alpha, beta, ssm_out;
+    const float *conv_w, *ssm_a, *dt_bias, *ssm_norm;
+    float *conv_state, *rec_state;
+    /* full-attention layers */
+    ggo_weight q, k, v, o;
+    const float *q_norm, *k_norm;
+    float *k_store, *v_store;                   /* [ctx][n_kv * head_dim], K after norm + RoPE (main.cpp:3070-3071) */
+    /* MoE FFN */
+    const float* router;
+    ggo_weight gate_exps, up_exps, down_exps, sh_gate, sh_up, sh_down;
+    const float* sh_gate_inp;
+} ggo_q35_layer;
+
+typedef struct {
+    int n_layer, hidden, n_head, n_kv, head_dim, rope_dim, conv_k, sk, n_vhead, n_khead, n_expert, top_k, eff, vocab, ctx;
+    float rms_eps, rope_base;
+    ggo_weight tok_embd, output;
+    const float* output_norm;
+    ggo_q35_layer* layers;
+} ggo_q35_model;
+
+GGO_API ggo_q35_model* ggo_q35_new(int n_layer, int hidden, int n_head, int n_kv, int head_dim, int rope_dim, int conv_k,
+                                   int sk, int n_vhead, int n_khead, int n_expert, int top_k, int eff, int vocab, int ctx,
+                                   float rms_eps, float rope_base) {
+    ggo_q35_model* m = (ggo_q35_model*)calloc(1, sizeof(ggo_q35_model));
+    if (!m) return NULL;
+    m->n_layer = n_layer; m->hidden = hidden; m->n_head = n_head; m->n_kv = n_kv; m->head_dim = head_dim; m->rope_dim = rope_dim;
+    m->conv_k = conv_k; m->sk = sk; m->n_vhead = n_vhead; m->n_khead = n_khead; m->n_expert = n_expert; m->top_k = top_k;
+    m->eff = eff; m->vocab = vocab; m->ctx = ctx; m->rms_eps = rms_eps; m->rope_base = rope_base;
+    m->layers = (ggo_q35_layer*)calloc((size_t)n_layer, sizeof(ggo_q35_layer));
+    return m;
+}
+
+GGO_API void ggo_q35_free(ggo_q35_model* m) {
+    if (!m) return;
+    for (int l = 0; l < m->n_layer; ++l) {
+        free(m->layers[l].conv_state); free(m->layers[l].rec_state); free(m->layers[l].k_store); free(m->layers[l].v_store);
+    }
+    free(m->layers); free(m);
+}
+
+GGO_API void ggo_q35_set_globals(ggo_q35_model* m, const uint8_t* tok_embd, uint32_t tok_type, const uint8_t* output,
+                                 uint32_t out_type, const float* output_norm) {
+    m->tok_embd.data = tok_embd; m->tok_embd.type = tok_type;
+    m->output.data = output ? output : tok_embd; m->output.type = output ? out_type : tok_type;   /* main.cpp:2065-2067 */
+    m->output_norm = output_norm;
+}
+
+/* A layer is a DeltaNet layer iff it has ssm_conv1d.weight (main.cpp:2207-2213). */
+GGO_API void ggo_q35_set_kind(ggo_q35_model* m, int layer, int is_ssm) {
+    ggo_q35_layer* l = &m->layers[layer];
+    l->is_ssm = is_ssm;
+    const size_t conv_dim = (size_t)2 * m->n_khead * m->sk + (size_t)m->n_vhead * m->sk;
+    if (is_ssm) {
+        l->conv_state = (float*)calloc((size_t)(m->conv_k - 1) * conv_dim + 1, sizeof(float));
+        l->rec_state = (float*)calloc((size_t)m->n_vhead * m->sk * m->sk, sizeof(float));
+    } else {
+        l->k_store = (float*)calloc((size_t)m->ctx * m->n_kv * m->head_dim, sizeof(float));
+        l->v_store = (float*)calloc((size_t)m->ctx * m->n_kv * m->head_dim, sizeof(float));
+    }
+}
+
+/* which: 0 attn_qkv, 1 attn_gate, 2 ssm_alpha, 3 ssm_beta, 4 ssm_out, 5 attn_q, 6 attn_k, 7 attn_v, 8 attn_output,
+ *        9 ffn_gate_exps, 10 ffn_up_exps, 11 ffn_down_exps, 12 ffn_gate_shexp, 13 ffn_up_shexp, 14 ffn_down_shexp */
+GGO_API void ggo_q35_set_weight(ggo_q35_model* m, int layer, int which, const uint8_t* data, uint32_t type) {
+    ggo_q35_layer* l = &m->layers[layer];
+    ggo_weight* w[15] = {&l->qkv, &l->zgate, &l->alpha, &l->beta, &l->ssm_out, &l->q, &l->k, &l->v, &l->o,
+                         &l->gate_exps, &l->up_exps, &l->down_exps, &l->sh_gate, &l->sh_up, &l->sh_down};
+    w[which]->data = data; w[which]->type = type;
+}
+
+/* which: 0 attn_norm, 1 post_attention_norm, 2 ssm_conv1d, 3 ssm_a, 4 ssm_dt.bias, 5 ssm_norm, 6 attn_q_norm,
+ *        7 attn_k_norm, 8 ffn_gate_inp (router), 9 ffn_gate_inp_shexp */
+GGO_API void ggo_q35_set_vec(ggo_q35_model* m, int layer, int which, const float* v) {
+    ggo_q35_layer* l = &m->layers[layer];
+    const float** p[10] = {&l->attn_norm, &l->post_norm, &l->conv_w, &l->ssm_a, &l->dt_bias, &l->ssm_norm, &l->q_norm,
+                           &l->k_norm, &l->router, &l->sh_gate_inp};
+    *p[which] = v;
+}
+
+/* src/cli/main.cpp:896-901 (host_rmsnorm): sum of squares in float. */
+static void q35_host_rmsnorm(float* dst, const float* src, int n, const float* w, float eps) {
+    float ss = 0.0f;
+    for (int i = 0; i < n; ++i) ss += src[i] * src[i];
+    const float r = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = 0; i < n; ++i) dst[i] = src[i] * r * (w ? w[i] : 1.0f);
+}
+
+/* src/cli/main.cpp:906-920 (rope_neox_partial): theta = pos * base^(-2i/rope_dim) in float, pairs (i, i + rope_dim/2). */
+static void q35_rope_neox_partial(float* vec, int n_heads, int head_dim, int rope_dim, int64_t pos, float base) {
+    const int half = rope_dim / 2;
+    for (int h = 0; h < n_heads; ++h) {
+        float* p = vec + (size_t)h * head_dim;
+        for (int i = 0; i < half; ++i) {
+            const float theta = (float)pos * powf(base, -2.0f * (float)i / (float)rope_dim);
+            const float c = cosf(theta), s = sinf(theta);
+            const float x0 = p[i], x1 = p[i + half];
+            p[i] = x0 * c - x1 * s;
+            p[i + half] = x0 * s + x1 * c;
+        }
+    }
+}
+
+/* The cos / sin rows the device path uploads, computed exactly as q35_rope_neox_partial does. */
+GGO_API void ggo_q35_rope_table(int64_t max_pos, int rope_dim, float base, float* cos_out, float* sin_out) {
+    const int half = rope_dim / 2;
+    for (int64_t p = 0; p < max_pos; ++p)
+        for (int i = 0; i < half; ++i) {
+            const float theta = (float)p * powf(base, -2.0f * (float)i / (float)rope_dim);
+            cos_out[p * half + i] = cosf(theta);
+            sin_out[p * half + i] = sinf(theta);
+        }
+}
+
+/* One token at position pos.  logits (optional) [vocab]; hidden_out (optional) the final-normed row. */
+GGO_API int ggo_q35_forward(ggo_q35_model* m, int32_t token, int pos, float* logits, float* hidden_out) {
+    const int H = m->hidden, Hd = m->head_dim, nQ = m->n_head, nKV = m->n_kv, qdim = nQ * Hd, kvdim = nKV * Hd;
+    const int sk = m->sk, nVH = m->n_vhead, nKH = m->n_khead, key_dim = nKH * sk, value_dim = nVH * sk, conv_dim = 2 * key_dim + value_dim;
+    if (pos < 0 || pos >= m->ctx) return -1;
+    int rc = 0;
+    float* x = (float*)malloc(sizeof(float) * (size_t)H);
+    float* xn = (float*)malloc(sizeof(float) * (size_t)H);
+    float* mixed = (float*)malloc(sizeof(float) * (size_t)conv_dim);
+    float* zgate = (float*)malloc(sizeof(float) * (size_t)value_dim);
+    float* araw = (float*)malloc(sizeof(float) * (size_t)nVH);
+    float* braw = (float*)malloc(sizeof(float) * (size_t)nVH);
+    float* o_all = (float*)malloc(sizeof(float) * (size_t)value_dim);
+    float* proj = (float*)malloc(sizeof(float) * (size_t)H);
+    float* qg = (float*)malloc(sizeof(float) * (size_t)2 * qdim);
+    float* q = (float*)malloc(sizeof(float) * (size_t)qdim);
+    float* fgate = (float*)malloc(sizeof(float) * (size_t)qdim);
+    float* kbuf = (float*)malloc(sizeof(float) * (size_t)kvdim);
+    float* vbuf = (float*)malloc(sizeof(float) * (size_t)kvdim);
+    float* attn_in = (float*)malloc(sizeof(float) * (size_t)qdim);
+    const int64_t ctx_len = (int64_t)pos + 1;
+    float* kexp = (float*)malloc(sizeof(float) * (size_t)nQ * ctx_len * Hd);
+    float* vexp = (float*)malloc(sizeof(float) * (size_t)nQ * ctx_len * Hd);
+    int32_t sel_ids[64]; float sel_w[65];
+
+    ggo_dequant_row(m->tok_embd.type, m->tok_embd.data, token, H, x);               /* main.cpp:2367-2375 */
+    for (int L = 0; L < m->n_layer && rc == 0; ++L) {
+        ggo_q35_layer* l = &m->layers[L];
+        ggo_rms_norm(x, xn, H, m->rms_eps, l->attn_norm);                            /* :2896 */
+        if (l->is_ssm) {
+            rc |= ggo_matmul_exact(xn, 1, H, l->qkv.data, l->qkv.type, conv_dim, H, mixed, conv_dim);      /* :2916-2923 */
+            rc |= ggo_matmul_exact(xn, 1, H, l->zgate.data, l->zgate.type, value_dim, H, zgate, value_dim);
+            rc |= ggo_matmul_exact(xn, 1, H, l->alpha.data, l->alpha.type, nVH, H, araw, nVH);
+            rc |= ggo_matmul_exact(xn, 1, H, l->beta.data, l->beta.type, nVH, H, braw, nVH);
+            rc |= ggo_deltanet_step(mixed, zgate, araw, braw, l->conv_w, l->ssm_a, l->dt_bias, l->ssm_norm, l->conv_state,
+                                    l->rec_state, o_all, nKH, nVH, sk, m->conv_k, m->rms_eps);             /* :2925-3024 */
+            rc |= ggo_matmul_exact(o_all, 1, value_dim, l->ssm_out.data, l->ssm_out.type, H, value_dim, proj, H);   /* :3028 */
+            for (int i = 0; i < H; ++i) x[i] += proj[i];                             /* :3033 */
+        } else {
+            rc |= ggo_matmul_exact(xn, 1, H, l->q.data, l->q.type, 2 * qdim, H, qg, 2 * qdim);             /* :3047-3052 */
+            rc |= ggo_matmul_exact(xn, 1, H, l->k.data, l->k.type, kvdim, H, kbuf, kvdim);
+            rc |= ggo_matmul_exact(xn, 1, H, l->v.data, l->v.type, kvdim, H, vbuf, kvdim);
+            for (int h = 0; h < nQ; ++h) {                                            /* :3056-3060 */
+                memcpy(q + (size_t)h * Hd, qg + (size_t)h * 2 * Hd, sizeof(float) * Hd);
+                memcpy(fgate + (size_t)h * Hd, qg + (size_t)h * 2 * Hd + Hd, sizeof(float) * Hd);
+            }
+            for (int h = 0; h < nQ; ++h) q35_host_rmsnorm(q + (size_t)h * Hd, q + (size_t)h * Hd, Hd, l->q_norm, m->rms_eps);      /* :3063-3066 */
+            for (int h = 0; h < nKV; ++h) q35_host_rmsnorm(kbuf + (size_t)h * Hd, kbuf + (size_t)h * Hd, Hd, l->k_norm, m->rms_eps);
+            q35_rope_neox_partial(q, nQ, Hd, m->rope_dim, pos, m->rope_base);        /* :3067-3068 */
+            q35_rope_neox_partial(kbuf, nKV, Hd, m->rope_dim, pos, m->rope_base);
+            memcpy(l->k_store + (size_t)pos * kvdim, kbuf, sizeof(float) * kvdim);   /* :3070-3071 */
+            memcpy(l->v_store + (size_t)pos * kvdim, vbuf, sizeof(float) * kvdim);
+            const int group = nQ / nKV;                                               /* :3073-3086 */
+            for (int h = 0; h < nQ; ++h)
+                for (int64_t j = 0; j < ctx_len; ++j) {
+                    memcpy(kexp + ((size_t)h * ctx_len + j) * Hd, l->k_store + ((size_t)j * nKV + h / group) * Hd, sizeof(float) * Hd);
+                    memcpy(vexp + ((size_t)h * ctx_len + j) * Hd, l->v_store + ((size_t)j * nKV + h / group) * Hd, sizeof(float) * Hd);
+                }
+            rc |= ggo_flash_attn(q, kexp, vexp, attn_in, nQ, Hd, ctx_len, pos);      /* :3088-3096 */
+            for (int i = 0; i < qdim; ++i) attn_in[i] *= 1.0f / (1.0f + expf(-fgate[i]));                   /* :3098 */
+            rc |= ggo_matmul_exact(attn_in, 1, qdim, l->o.data, l->o.type, H, qdim, proj, H);               /* :3100 */
+            for (int i = 0; i < H; ++i) x[i] += proj[i];                             /* :3104 */
+        }
+        ggo_rms_norm(x, xn, H, m->rms_eps, l->post_norm);                            /* :3109 */
+        rc |= ggo_moe_ffn(xn, H, l->router, m->n_expert, m->top_k, m->eff, l->gate_exps.data, l->up_exps.data, l->gate_exps.type,
+                          l->down_exps.data, l->down_exps.type, l->sh_gate.data, l->sh_up.data, l->sh_gate.type, l->sh_down.data,
+                          l->sh_down.type, m->eff, l->sh_gate_inp, proj, sel_ids, sel_w);                  /* :3110-3192 */
+        for (int i = 0; i < H; ++i) x[i] += proj[i];                                 /* :3193 */
+    }
+    ggo_rms_norm(x, xn, H, m->rms_eps, m->output_norm);                              /* :3504-3512 */
+    if (hidden_out) memcpy(hidden_out, xn, sizeof(float) * (size_t)H);
+    if (logits && rc == 0) rc |= ggo_matmul_exact(xn, 1, H, m->output.data, m->output.type, m->vocab, H, logits, m->vocab);
+    free(x); free(xn); free(mixed); free(zgate); free(araw); free(braw); free(o_all); free(proj); free(qg); free(q); free(fgate);
+    free(kbuf); free(vbuf); free(attn_in); free(kexp); free(vexp);
+    return rc;
+}
+
+/* Read access for tests: the K or V row [n_kv][head_dim] a full-attention layer stored at `pos`; the recurrent state
+ * [n_vhead][sk][sk] of a DeltaNet layer. */
+GGO_API const float* ggo_q35_kv(const ggo_q35_model* m, int layer, int pos, int want_v) {
+    const ggo_q35_layer* l = &m->layers[layer];
+    if (l->is_ssm) return NULL;
+    return (want_v ? l->v_store : l->k_store) + (size_t)pos * m->n_kv * m->head_dim;
+}
+GGO_API const float* ggo_q35_rec_state(const ggo_q35_model* m, int layer) { return m->layers[layer].rec_state; }

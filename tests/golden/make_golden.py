@@ -2,7 +2,7 @@
 
 Run where the reference tree is available:
 
-    make -C oracle ref REF=/path/to/ggnpu && python tests/golden/make_golden.py
+    make -C oracle ref REF=/path/to/ggnpu && python tests/golden/make_golden.py [--cli-only | --grid-only]
 
 Every array stored here is an INPUT (seeded random bytes / floats) or an OUTPUT of
 the reference's functions on that input (oracle/_ref/libggnpu_ref.so, built from
@@ -81,16 +81,32 @@ def main():
             out[f"mm_cpuref_{t}"] = ref.mul_mat_q(A, wq, t, 24, 512)[1]
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **out)
 
-    # 4. end to end: the reference CLI on two tiny seeded models (top-10 logits after the prompt and
-    #    the greedy continuation), exact fp32 matmul path.
+    print("wrote", os.path.join(HERE, "ref_vectors.npz"))
+
+
+def cli_cases():
+    """name -> (config, builder, prompt length, greedy tokens).  The same table drives the tests."""
+    return {
+        "llama": (S.tiny_config(seed=11), S.build_model, 7, 6),
+        "qwen2": (S.tiny_config(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12, rope_base=1e6, tied=False),
+                  S.build_model, 7, 6),
+        # the full Llama-3.2-1B shape (16 layers, hidden 2048, vocab 128256, Q4_K / Q6_K, tied embeddings)
+        "llama1b": (S.LLAMA_1B, S.build_model, 8, 4),
+        # qwen35moe: 3 Gated DeltaNet layers + 1 gated full-attention layer, 8 experts top-2 + shared expert
+        "qwen35moe": (S.tiny_q35_config(), S.build_q35_model, 7, 6),
+        "qwen35moe_sk128": (S.tiny_q35_config(sk=128, seed=77), S.build_q35_model, 9, 6),
+    }
+
+
+def cli_vectors():
+    """End to end: the unmodified reference CLI (exact fp32 matmul path) on seeded synthetic models:
+    top-10 logits after the prompt and the greedy continuation -> ref_cli.npz."""
     e2e = {}
-    cases = {"llama": S.tiny_config(seed=11), "qwen2": S.tiny_config(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12,
-                                                                      rope_base=1e6, tied=False)}
-    for name, cfg in cases.items():
-        m = S.build_model(cfg)
+    for name, (cfg, builder, n_prompt, n_gen) in cli_cases().items():
+        m = builder(cfg)
         path = f"/tmp/ggb_golden_{name}.gguf"
         m.write(path)
-        ids = np.random.default_rng(42).integers(0, cfg.vocab, 7)
+        ids = np.random.default_rng(42).integers(0, cfg.vocab, n_prompt)
         r1 = run_ref_cli(path, S.prompt_text(ids), 0, ctx=cfg.ctx, bench_logits=True)
         top = []
         for line in (r1.stdout + r1.stderr).splitlines():
@@ -100,16 +116,17 @@ def main():
                 lg = float(line.split("logit=")[1].split()[0])
                 top.append((tid, lg))
         assert len(top) == 10, (r1.stdout, r1.stderr)
-        r2 = run_ref_cli(path, S.prompt_text(ids), 6, ctx=cfg.ctx)
+        r2 = run_ref_cli(path, S.prompt_text(ids), n_gen, ctx=cfg.ctx)
         gen = S.text_ids(r2.stdout)
-        assert len(gen) == 6, (r2.stdout, r2.stderr)
+        assert len(gen) == n_gen, (r2.stdout, r2.stderr)
         e2e[f"{name}_prompt"] = ids.astype(np.int32)
         e2e[f"{name}_top_ids"] = np.array([t for t, _ in top], dtype=np.int32)
         e2e[f"{name}_top_logits"] = np.array([v for _, v in top], dtype=np.float32)
         e2e[f"{name}_greedy"] = np.array(gen, dtype=np.int32)
         os.remove(path)
+        print(name, "top-1", top[0], "greedy", gen)
     np.savez_compressed(os.path.join(HERE, "ref_cli.npz"), **e2e)
-    print("wrote", os.path.join(HERE, "ref_vectors.npz"), os.path.join(HERE, "ref_cli.npz"))
+    print("wrote", os.path.join(HERE, "ref_cli.npz"))
 
 
 def grid_vectors(ref=None):
@@ -134,6 +151,9 @@ def grid_vectors(ref=None):
 if __name__ == "__main__":
     if "--grid-only" in sys.argv:
         grid_vectors()
+    elif "--cli-only" in sys.argv:
+        cli_vectors()
     else:
         main()
+        cli_vectors()
         grid_vectors()

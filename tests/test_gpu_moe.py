@@ -86,3 +86,38 @@ def test_moe_argument_errors(backend):
     assert backend.moe_ffn_device(**dict(base, hidden=128)) == Status.INVALID_PARAM
     backend.free_weight(w)
     backend.free_weight(d)
+
+
+def test_moe_nan_input_returns_normally(backend):
+    """An x that holds a NaN makes every router logit NaN, so no expert wins a comparison.  The call must
+    still return OK with valid expert ids (the NaN travels through the weights into y) and leave the
+    device usable, as the argmax path does (src/cli/main.cpp:3128-3135 has no guard either; it sorts NaNs
+    into some order and carries on)."""
+    H, eff, nE, k = 256, 256, 8, 2
+    ge, ue, de = q((nE * eff, H), S.Q4_K, 1), q((nE * eff, H), S.Q4_K, 2), q((nE * H, eff), S.Q6_K, 3)
+    dev = torch.device("cuda:0")
+    hg, hu, hd = (backend.upload_weight(S.Q4_K, ge, nE * eff, H), backend.upload_weight(S.Q4_K, ue, nE * eff, H),
+                  backend.upload_weight(S.Q6_K, de, nE * H, eff))
+    x = torch.randn(H, device=dev)
+    x[7] = float("nan")
+    router = torch.randn(nE, H, device=dev) * 0.05
+    y = torch.zeros(H, device=dev)
+    dsel = torch.full((k,), -7, device=dev, dtype=torch.int32)
+    dw = torch.zeros(k + 1, device=dev)
+    st = backend.moe_ffn_device(x=x.data_ptr(), resid=None, y=y.data_ptr(), router=router.data_ptr(), gate_exps=hg, up_exps=hu,
+                                down_exps=hd, sh_gate=None, sh_up=None, sh_down=None, sh_gate_inp=None, hidden=H, eff=eff, eff_sh=0,
+                                n_expert=nE, top_k=k, sel_out=dsel.data_ptr(), w_out=dw.data_ptr())
+    assert st == Status.OK, backend.last_error_message()
+    backend.sync()
+    ids = dsel.cpu().numpy()
+    assert ((ids >= 0) & (ids < nE)).all() and len(set(ids.tolist())) == k, ids
+    # the device still works afterwards
+    x2 = torch.randn(H, device=dev)
+    st = backend.moe_ffn_device(x=x2.data_ptr(), resid=None, y=y.data_ptr(), router=router.data_ptr(), gate_exps=hg, up_exps=hu,
+                                down_exps=hd, sh_gate=None, sh_up=None, sh_down=None, sh_gate_inp=None, hidden=H, eff=eff, eff_sh=0,
+                                n_expert=nE, top_k=k, sel_out=dsel.data_ptr(), w_out=dw.data_ptr())
+    assert st == Status.OK
+    backend.sync()
+    assert torch.isfinite(y).all()
+    for hw in (hg, hu, hd):
+        backend.free_weight(hw)

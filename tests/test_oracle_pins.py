@@ -146,6 +146,77 @@ def test_forward_matches_reference_cli(oracle, cli_vectors, name):
     assert np.array_equal(bits(l2), bits(last))
 
 
+Q35_CASES = {"qwen35moe": dict(), "qwen35moe_sk128": dict(sk=128, seed=77)}
+
+
+@pytest.mark.parametrize("name", list(Q35_CASES))
+def test_qwen35moe_forward_matches_reference_cli(oracle, cli_vectors, name):
+    """The restated qwen35moe forward -- Gated DeltaNet layers (ggo_deltanet_step), the gated full-attention
+    layer and the MoE FFN (ggo_moe_ffn) -- against what the unmodified reference CLI printed for the same
+    seeded synthetic model: top-10 ids in order, logits to the 6 digits it prints, greedy stream.  This is
+    what pins those three restatements: the reference keeps the blocks inside main() (src/cli/main.cpp:2859-3232),
+    so its CLI output is the only form in which they can be observed."""
+    from oracle.binding import OracleQ35Model
+    cfg = S.tiny_q35_config(**Q35_CASES[name])
+    om = OracleQ35Model(oracle, S.build_q35_model(cfg))
+    ids = cli_vectors[f"{name}_prompt"]
+    logits = om.feed(ids)
+    pos = len(ids)
+    order = np.argsort(-logits, kind="stable")[:10]
+    assert list(order) == list(cli_vectors[f"{name}_top_ids"])
+    assert np.allclose(logits[order], cli_vectors[f"{name}_top_logits"], rtol=6e-6, atol=0)     # six printed digits
+    gen, tok = [], oracle.argmax_first(logits)
+    for _ in range(len(cli_vectors[f"{name}_greedy"])):
+        gen.append(tok)
+        logits = om.forward(tok, pos)
+        pos += 1
+        tok = oracle.argmax_first(logits)
+    assert gen == list(cli_vectors[f"{name}_greedy"])
+
+
+def test_qwen35moe_forward_matches_reference_cli_live(oracle, ref):
+    """The same pin taken live (where the reference tree was available to build oracle/_ref): another seed,
+    a longer prompt, 8 experts top-3."""
+    import os
+    from oracle.binding import REF_CLI, OracleQ35Model, run_ref_cli
+    if not os.path.exists(REF_CLI):
+        pytest.skip("reference CLI not built")
+    cfg = S.tiny_q35_config(seed=5, top_k=3, n_layer=8)
+    m = S.build_q35_model(cfg)
+    path = "/tmp/ggb_pin_q35.gguf"
+    m.write(path)
+    try:
+        ids = np.random.default_rng(3).integers(0, cfg.vocab, 12)
+        r = run_ref_cli(path, S.prompt_text(ids), 8, ctx=cfg.ctx)
+        want = S.text_ids(r.stdout)
+    finally:
+        os.remove(path)
+    assert len(want) == 8, r.stderr[-500:]
+    om = OracleQ35Model(oracle, m)
+    logits = om.feed(ids)
+    gen, tok, pos = [], oracle.argmax_first(logits), len(ids)
+    for _ in range(8):
+        gen.append(tok)
+        logits = om.forward(tok, pos)
+        pos += 1
+        tok = oracle.argmax_first(logits)
+    assert gen == want
+
+
+def test_llama_1b_shape_top10_matches_reference_cli(oracle, cli_vectors):
+    """The full Llama-3.2-1B shape (16 layers, hidden 2048, 32/8 heads of 64, FFN 8192, vocab 128256, Q4_K with
+    Q6_K for attn_v / ffn_down, tied embeddings): the restated layer loop against the reference CLI's top-10
+    logits after an 8-token prompt."""
+    from oracle.binding import OracleModel
+    om = OracleModel(oracle, S.build_model(S.LLAMA_1B))
+    ids = cli_vectors["llama1b_prompt"]
+    logits = om.forward(ids, 0)
+    order = np.argsort(-logits, kind="stable")[:10]
+    assert list(order) == list(cli_vectors["llama1b_top_ids"])
+    assert np.allclose(logits[order], cli_vectors["llama1b_top_logits"], rtol=6e-6, atol=0)     # six printed digits
+    assert oracle.argmax_first(logits) == cli_vectors["llama1b_greedy"][0]
+
+
 # ---- live comparison with the reference's compiled functions ----------------------------------
 
 @pytest.mark.parametrize("t", S.QUANT_TYPES)

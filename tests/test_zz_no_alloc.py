@@ -46,3 +46,33 @@ def test_static_scratch_rejects_oversize_requests(backend):
     st = backend.attn_paged_static(t.data_ptr(), t.data_ptr(), t.data_ptr(), it.data_ptr(), t.data_ptr(), 128, 16, 64, 16, 64, 0)
     assert st == Status.INVALID_PARAM
     assert "built-in scratch" in backend.last_error_message()
+
+
+def test_static_scratch_entry_point_allocates_no_device_memory(oracle):
+    """The property the entry point exists for.  On a handle of its own, which never ran the allocating
+    entry point (so no scratch buffer of the handle exists that a regression could quietly borrow), the
+    first call does the one-time set-up (symbol address, kernel image); across the next two calls the
+    device's free memory, as the driver reports it, must not move by a byte."""
+    from ggnpu_b200.backend import CudaBackend
+    shape = (32, 8, 64, 64, 8)
+    n_head, n_kv, hd, page, n_pages = shape
+    q, k, v, kp, vp, table = make_case(*shape, seed=7)
+    dev = torch.device("cuda:0")
+    dq, dk, dv, dt = q.to(dev), kp.to(dev), vp.to(dev), table.to(dev)
+    out = torch.full((n_head, hd), float("nan"), device=dev)
+    fresh = CudaBackend(0)
+    try:
+        args = (dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dt.data_ptr(), out.data_ptr())
+        assert fresh.attn_paged_static(*args, n_head, n_kv, hd, page, n_pages, 17) == Status.OK      # set-up call
+        fresh.sync()
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(0)
+        for pos in (page * n_pages - 1, 3):
+            assert fresh.attn_paged_static(*args, n_head, n_kv, hd, page, n_pages, pos) == Status.OK, fresh.last_error_message()
+            fresh.sync()
+        free_after, _ = torch.cuda.mem_get_info(0)
+        assert free_after == free_before, (free_before, free_after)
+        cpu = oracle.flash_attn(q.numpy(), expanded(k, n_head, n_kv, 4), expanded(v, n_head, n_kv, 4), -1)
+        assert np.allclose(out.cpu().numpy(), cpu, rtol=2e-5, atol=2e-6)
+    finally:
+        fresh.close()

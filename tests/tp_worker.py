@@ -141,6 +141,31 @@ def main():
         both = [torch.empty_like(mine) for _ in range(size)]
         dist.all_gather(both, mine)
         assert all(torch.equal(both[0], t) for t in both[1:]) or size < 4, "ranks disagree"      # NCCL at 2 ranks: same sum on both
+    # ---- a peer that never arrives (made on the host: rank 1 simply skips one call) ----
+    # Rank 0's kernel waits for rank 1's flag, gives up after the shortened limit, records the error and
+    # returns by itself; sync() turns the device error word into Status.ERROR naming the all-reduce.  Rank 1
+    # then makes the call it skipped (rank 0's slice and flag of that epoch are already in its region), which
+    # realigns the epochs, and a further sum over the group is exact again: the context stayed usable.
+    if size == 2 and os.environ.get("GGB_TP_ONE_SHOT"):
+        os.environ["GGB_TP_WAIT_MS"] = "300"
+        t = torch.full((1024,), float(rank + 1), device=dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            assert int(b.tp_all_reduce_device(t.data_ptr(), 1024)) == 0
+            b.sync()
+            assert b.last_error() == Status.ERROR and "all-reduce" in b.last_error_message(), b.last_error_message()
+        dist.barrier()
+        if rank == 1:
+            assert int(b.tp_all_reduce_device(t.data_ptr(), 1024)) == 0
+            b.sync()
+            assert torch.all(t == 3.0)
+        del os.environ["GGB_TP_WAIT_MS"]
+        dist.barrier()
+        t = torch.full((1024,), float(rank + 1), device=dev)
+        assert int(b.tp_all_reduce_device(t.data_ptr(), 1024)) == 0
+        b.sync()
+        assert torch.all(t == 3.0), "group did not recover after the timed-out call"
     dist.barrier()
     b.close()
     dist.destroy_process_group()
