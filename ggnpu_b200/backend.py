@@ -79,7 +79,8 @@ class MoeParams(C.Structure):
                 ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
                 ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p), ("sh_gate_inp", C.c_void_p),
                 ("hidden", C.c_int), ("eff", C.c_int), ("eff_sh", C.c_int), ("n_expert", C.c_int), ("top_k", C.c_int),
-                ("sel_out", C.c_void_p), ("w_out", C.c_void_p), ("ep_first", C.c_int), ("ep_local", C.c_int)]
+                ("sel_out", C.c_void_p), ("w_out", C.c_void_p), ("ep_first", C.c_int), ("ep_local", C.c_int),
+                ("gamma", C.c_void_p), ("eps", C.c_float)]
 
 
 class DeltaNetParams(C.Structure):

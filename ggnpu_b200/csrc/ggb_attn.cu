@@ -96,18 +96,21 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
     const bool active = hh < a.n_head + a.n_kv;
     const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int hd = a.head_dim, half = hd >> 1;
+    const int rot = a.rot_dims > 0 ? a.rot_dims : hd, rh = rot >> 1;       // rotated dims and pairs
     const bool is_q = hh < a.n_head;
     const int h = is_q ? hh : hh - a.n_head;
     float* src = !active ? nullptr : (is_q ? a.q + (static_cast<size_t>(t) * a.n_head + h) * hd : a.k + (static_cast<size_t>(t) * a.n_kv + h) * hd);
     const float* nw = is_q ? a.q_norm : a.k_norm;
     __shared__ double red[8][8];
     __shared__ float inv_s[8];
-    const int i = threadIdx.x;               // pair index
-    const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
+    const int i = threadIdx.x;               // thread i < rh owns rotation pair i; the others own two pass-through dims
+    int i0, i1;
+    if (i < rh) { i0 = a.neox ? i : 2 * i; i1 = a.neox ? i + rh : 2 * i + 1; }
+    else { i0 = rot + 2 * (i - rh); i1 = i0 + 1; }
     float v0 = 0.0f, v1 = 0.0f;
     if (active && i < half) { v0 = src[i0]; v1 = src[i1]; }
     if (a.q_norm || a.k_norm) {              // uniform over the CTA: every thread reaches the barriers
-        double ss = static_cast<double>(v0) * v0 + static_cast<double>(v1) * v1;
+        double ss = a.norm_f32 ? static_cast<double>(v0 * v0 + v1 * v1) : static_cast<double>(v0) * v0 + static_cast<double>(v1) * v1;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
         if ((threadIdx.x & 31) == 0) red[threadIdx.y][threadIdx.x >> 5] = ss;
@@ -121,8 +124,11 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
         if (nw && active && i < half) { v0 = v0 * inv_s[threadIdx.y] * nw[i0]; v1 = v1 * inv_s[threadIdx.y] * nw[i1]; }
     }
     if (active && i < half) {
-        const float cs = a.cos_tab[static_cast<size_t>(pos) * half + i], sn = a.sin_tab[static_cast<size_t>(pos) * half + i];
-        const float r0 = v0 * cs - v1 * sn, r1 = v0 * sn + v1 * cs;
+        float r0 = v0, r1 = v1;
+        if (i < rh) {
+            const float cs = a.cos_tab[static_cast<size_t>(pos) * rh + i], sn = a.sin_tab[static_cast<size_t>(pos) * rh + i];
+            r0 = v0 * cs - v1 * sn; r1 = v0 * sn + v1 * cs;
+        }
         if (is_q) { src[i0] = r0; src[i1] = r1; }
         else {
             const int page = a.block_table[pos / a.page], slot = pos % a.page;

@@ -22,6 +22,8 @@ struct KvAppendArgs {
     int pos0;
     int n_head, n_kv, head_dim, page, neox;
     float eps;
+    int rot_dims;             // leading dims of each head that rotate (0: all head_dim); tables hold rot_dims / 2 entries per position
+    int norm_f32;             // 1: QK-norm sum of squares in float (qwen35: src/cli/main.cpp:896-901) instead of double
 };
 
 struct AttnPagedArgs {

@@ -136,23 +136,14 @@ __global__ void __launch_bounds__(8 * SK) dn_step_kernel(const StepArgs a) {
 
 }  // namespace
 
-}  // namespace ggb
-
-using namespace ggb;
-
-extern "C" int ggb_deltanet_step_device(ggb_handle h, const ggb_deltanet_params* p) {
-    if (!h) return GGB_UNAVAILABLE;
+// Validates and enqueues on stream s; `conv` holds 2 * n_khead * sk + n_vhead * sk floats.  The caller holds the handle's lock.
+int deltanet_step_enqueue(Context* h, const ggb_deltanet_params* p, float* conv, cudaStream_t s) {
     if (!p || !p->mixed || !p->zgate || !p->araw || !p->braw || !p->conv_w || !p->ssm_a || !p->dt_bias || !p->ssm_norm ||
         !p->conv_state || !p->rec_state || !p->out)
         return set_status(h, GGB_INVALID_PARAM, "deltanet_step: null pointer");
     if ((p->sk != 64 && p->sk != 128) || p->n_khead < 1 || p->n_vhead < 1 || p->conv_k < 1 || p->conv_k > 8)
         return set_status(h, GGB_INVALID_PARAM, "deltanet_step: head size must be 64 or 128, conv_k 1..8");
-    std::lock_guard<std::mutex> lk(h->mu);
-    cudaSetDevice(h->device);
-    cudaStream_t s = h->stream;
     const int conv_dim = 2 * p->n_khead * p->sk + p->n_vhead * p->sk;
-    float* conv = static_cast<float*>(scratch(h, 3, sizeof(float) * conv_dim));
-    if (!conv) return h->last_status;
     cudaError_t e = launch_pdl(h, dn_conv_kernel, dim3((conv_dim + 255) / 256), dim3(256), 0, s, p->mixed, p->conv_w, p->conv_state, conv, conv_dim, p->conv_k);
     h->launches++;
     if (e != cudaSuccess) return cuda_status(h, e, "deltanet conv");
@@ -163,4 +154,19 @@ extern "C" int ggb_deltanet_step_device(ggb_handle h, const ggb_deltanet_params*
     else e = launch_pdl(h, dn_step_kernel<64>, dim3(p->n_vhead), dim3(512), 0, s, a);
     h->launches++;
     return cuda_status(h, e, "deltanet step");
+}
+
+}  // namespace ggb
+
+using namespace ggb;
+
+extern "C" int ggb_deltanet_step_device(ggb_handle h, const ggb_deltanet_params* p) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!p || p->n_khead < 1 || p->n_vhead < 1 || p->sk < 1) return set_status(h, GGB_INVALID_PARAM, "deltanet_step: bad arguments");
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    const size_t conv_dim = static_cast<size_t>(2) * p->n_khead * p->sk + static_cast<size_t>(p->n_vhead) * p->sk;
+    float* conv = static_cast<float*>(scratch(h, 3, sizeof(float) * conv_dim));
+    if (!conv) return h->last_status;
+    return deltanet_step_enqueue(h, p, conv, h->stream);
 }

@@ -165,6 +165,13 @@ int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, in
 int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s);
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
 
+// ggb_moe.cu / ggb_deltanet.cu: the operators of the qwen35moe layers with caller-owned scratch
+size_t moe_scratch_floats(const ggb_moe_params* p);
+int moe_ffn_enqueue(Context* c, const ggb_moe_params* p, float* scr, cudaStream_t s);
+int deltanet_step_enqueue(Context* c, const ggb_deltanet_params* p, float* conv, cudaStream_t s);
+// y[n] = (rms_norm(x) * gamma) . W[n][:] for small F32 matrices (a warp per row); gamma may be nullptr
+int launch_f32_rows(Context* c, const float* x, const float* gamma, float eps, const float* W, int N, int K, float* y, cudaStream_t s);
+
 // ggb_attn.cu
 int launch_attn_expanded(Context* c, const float* Q, const float* K, const float* V, float* out, int n_head, int head_dim,
                          int64_t ctx_len, int64_t query_pos, cudaStream_t s);

@@ -24,8 +24,8 @@ constexpr int kMaxTopK = 16;
 
 // Router logits: one warp per expert row (row n_expert = the shared expert's gate vector), 8 rows per CTA,
 // so the 2 MB router matrix is read by dozens of SMs rather than one.
-__global__ void moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ router, int hidden, int n_expert,
-                                  const float* __restrict__ sh_gate_inp, float* __restrict__ logits) {
+__global__ void moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float eps, const float* __restrict__ router,
+                                  int hidden, int n_expert, const float* __restrict__ sh_gate_inp, float* __restrict__ logits) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -33,13 +33,21 @@ __global__ void moe_logits_kernel(const float* __restrict__ x, const float* __re
     if (e > n_expert) return;
     const float* wr = e < n_expert ? router + static_cast<size_t>(e) * hidden : sh_gate_inp;
     if (!wr) return;
-    float acc = 0.0f;
+    // with gamma: the logit of rms_norm(x) * gamma, formed as (x * gamma) . w times the row's 1 / rms
+    float acc = 0.0f, ss = 0.0f;
     for (int i = lane * 4; i < hidden; i += 128) {
-        const float4 a = *reinterpret_cast<const float4*>(x + i), b = __ldg(reinterpret_cast<const float4*>(wr + i));
+        float4 a = *reinterpret_cast<const float4*>(x + i);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(wr + i));
+        if (gamma) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + i));
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            a.x *= g.x; a.y *= g.y; a.z *= g.z; a.w *= g.w;
+        }
         acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }
+    if (gamma) acc *= 1.0f / sqrtf(ss / static_cast<float>(hidden) + eps);
     if (lane == 0) logits[e] = acc;
 }
 
@@ -116,12 +124,12 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
 
 }  // namespace
 
-}  // namespace ggb
+size_t moe_scratch_floats(const ggb_moe_params* p) {
+    return 64 + static_cast<size_t>(p->top_k) * p->eff + static_cast<size_t>(p->eff_sh > 0 ? p->eff_sh : 0) + p->n_expert + 1;
+}
 
-using namespace ggb;
-
-extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
-    if (!h) return GGB_UNAVAILABLE;
+// Validates and enqueues on stream s; `scr` holds moe_scratch_floats(p) floats.  The caller holds the handle's lock.
+int moe_ffn_enqueue(Context* h, const ggb_moe_params* p, float* scr, cudaStream_t s) {
     if (!p || !p->x || !p->y || !p->router || !p->gate_exps || !p->up_exps || !p->down_exps)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: null pointer");
     if (p->hidden <= 0 || p->hidden % 256 || p->eff <= 0 || p->eff % 256 || p->n_expert < 1 || p->n_expert > 1024 || p->top_k < 1 ||
@@ -147,13 +155,7 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     if (shared && (sg->w.N != p->eff_sh || su->w.N != p->eff_sh || sg->w.K != p->hidden || su->w.K != p->hidden || sd->w.N != p->hidden ||
                    sd->w.K != p->eff_sh || p->eff_sh <= 0 || p->eff_sh % 256))
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: shared expert shapes do not match");
-    std::lock_guard<std::mutex> lk(h->mu);
-    cudaSetDevice(h->device);
-    cudaStream_t s = h->stream;
     // scratch: [sel: 16 ints][w: 17 floats][act: top_k * eff][act_sh: eff_sh][logits: n_expert + 1]
-    const size_t floats = 64 + static_cast<size_t>(p->top_k) * p->eff + (shared ? p->eff_sh : 0) + p->n_expert + 1;
-    float* scr = static_cast<float*>(scratch(h, 3, sizeof(float) * floats));
-    if (!scr) return h->last_status;
     int32_t* sel = reinterpret_cast<int32_t*>(scr);
     float* w = scr + 16;
     float* act = scr + 64;
@@ -161,8 +163,8 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     float* logits = act_sh + (shared ? p->eff_sh : 0);
     const float* gate_vec = shared ? p->sh_gate_inp : static_cast<const float*>(nullptr);
 
-    cudaError_t e = launch_pdl(h, moe_logits_kernel, dim3((p->n_expert + 1 + 7) / 8), dim3(256), 0, s, p->x, p->router, p->hidden, p->n_expert,
-                               gate_vec, logits);
+    cudaError_t e = launch_pdl(h, moe_logits_kernel, dim3((p->n_expert + 1 + 7) / 8), dim3(256), 0, s, p->x, p->gamma, p->eps, p->router, p->hidden,
+                               p->n_expert, gate_vec, logits);
     h->launches++;
     if (e != cudaSuccess) return cuda_status(h, e, "moe router logits");
     e = launch_pdl(h, moe_topk_kernel, dim3(1), dim3(256), 0, s, static_cast<const float*>(logits), p->n_expert, p->top_k, gate_vec ? 1 : 0,
@@ -172,6 +174,7 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
 
     GemvArgs a{};
     a.w = ge->w; a.w2 = ue->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act; a.ldc = p->top_k * p->eff; a.epi = EPI_SWIGLU;
+    a.gamma = p->gamma; a.eps = p->eps;
     a.sel = sel; a.sel_mode = 1; a.sel_count = p->top_k; a.sel_rows = p->eff;
     int st = launch_gemv_mma(h, a, s);
     if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert gate/up shape not covered") : st;
@@ -186,6 +189,7 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     if (shared) {
         a = GemvArgs{};
         a.w = sg->w; a.w2 = su->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act_sh; a.ldc = p->eff_sh; a.epi = EPI_SWIGLU;
+        a.gamma = p->gamma; a.eps = p->eps;
         st = launch_gemv(h, a, s);
         if (st != GGB_OK) return st;
         a = GemvArgs{};
@@ -196,4 +200,18 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     }
     if (ep) return tp_all_reduce(h, p->y, static_cast<size_t>(p->hidden), s);      // sum of the ranks' expert shares (+ rank 0's residual, shared expert)
     return GGB_OK;
+}
+
+}  // namespace ggb
+
+using namespace ggb;
+
+extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
+    if (!h) return GGB_UNAVAILABLE;
+    if (!p) return set_status(h, GGB_INVALID_PARAM, "moe_ffn: null pointer");
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaSetDevice(h->device);
+    float* scr = static_cast<float*>(scratch(h, 3, sizeof(float) * moe_scratch_floats(p)));
+    if (!scr) return h->last_status;
+    return moe_ffn_enqueue(h, p, scr, h->stream);
 }

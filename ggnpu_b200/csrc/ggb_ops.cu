@@ -119,6 +119,35 @@ __global__ void rope_kernel(float* __restrict__ x, int n_heads, int head_dim, in
         xh[i1] = v0 * sn + v1 * cs;
     }
 }
+// Small F32 matrices applied to a (normalised) row: y[n] = (rms_norm(x) * gamma) . W[n][:].  The reference computes
+// F32 weight matrices on the host in fp32 (src/cli/main.cpp:1390-1406: qwen35moe's ssm_alpha / ssm_beta).  One warp per
+// output row, eight rows per CTA; each warp forms the row statistic itself (K is a few thousand floats, in L2).
+__global__ void f32_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float eps, const float* __restrict__ W,
+                                int N, int K, float* __restrict__ y) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const float* wr = W + static_cast<size_t>(n) * K;
+    float acc = 0.0f, ss = 0.0f;
+    for (int i = lane; i < K; i += 32) {
+        float v = x[i];
+        if (gamma) { ss = fmaf(v, v, ss); v *= gamma[i]; }
+        acc = fmaf(v, __ldg(wr + i), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }
+    if (gamma) acc *= 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
+    if (lane == 0) y[n] = acc;
+}
+
+int launch_f32_rows(Context* c, const float* x, const float* gamma, float eps, const float* W, int N, int K, float* y, cudaStream_t s) {
+    const cudaError_t e = launch_pdl(c, f32_rows_kernel, dim3((N + 7) / 8), dim3(256), 0, s, x, gamma, eps, W, N, K, y);
+    c->launches++;
+    return cuda_status(c, e, "f32 rows");
+}
+
 int launch_rope(Context* c, float* x, int n_tok, int n_heads, int head_dim, int rot_dims, const float* cos_tab,
                 const float* sin_tab, const int32_t* d_pos, int pos0, int neox, cudaStream_t s) {
     const int total = n_heads * (rot_dims / 2);

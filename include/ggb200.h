@@ -262,6 +262,11 @@ typedef struct ggb_moe_params {
      * partial rows are summed over the group (the batch-1 form of dispatch / combine), so every rank ends with
      * the same y.  sel_out / w_out report the global choice on every rank. */
     int ep_first, ep_local;
+    /* Optional fused FFN norm: with gamma != NULL, x is the RAW hidden row and the operator works on
+     * rms_norm(x, eps) * gamma (src/cli/main.cpp:3109), applied inside the router and expert kernels.  x must not
+     * alias y when a shared expert is given (the shared expert reads x after the routed experts wrote y). */
+    const float* gamma;
+    float eps;
 } ggb_moe_params;
 GGB_API int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p);
 

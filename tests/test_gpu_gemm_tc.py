@@ -102,6 +102,32 @@ def test_benchmark_shapes_sampled_rows(backend, oracle):
         check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
 
 
+MICRO_SHAPES = [(2048, 2048), (8192, 2048), (2048, 8192), (8960, 1536)]
+MICRO_TYPES = [S.Q4_0, S.Q8_0, S.Q4_K, S.Q6_K, S.IQ4_XS]
+
+
+@pytest.mark.parametrize("t", MICRO_TYPES, ids=lambda t: S.TYPE_NAMES[t])
+@pytest.mark.parametrize("shape", MICRO_SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+def test_microbench_grid_m512(backend, oracle, shape, t):
+    """The quantised-matmul microbenchmark grid at M = 512: every one of the four weight shapes in every one
+    of the five formats through Backend::mul_mat_q.  A sample of weight rows (first, last and 40 random ones)
+    is checked against the fp16-operand model and against the reference's exact fp32 matmul (src/cli/main.cpp:
+    1379-1388) within the tensor-core tolerance; every output must be finite."""
+    N, K = shape
+    M = 512
+    if K % S.BLOCK[t][0]:
+        pytest.skip("K is not a whole number of blocks of this format")
+    raw = make(t, N, K, 31)
+    A = np.random.default_rng(7).standard_normal((M, K)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+    assert np.isfinite(C).all()
+    rows = np.unique(np.concatenate([np.arange(4), np.arange(N - 4, N), np.random.default_rng(1).integers(0, N, 40)]))
+    sub = np.ascontiguousarray(raw.reshape(N, S.row_bytes(t, K))[rows])
+    check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
+    assert rel_l2(C[:8, rows], oracle.matmul_exact(A[:8], sub, t, len(rows), K)) <= 2e-3
+
+
 @pytest.mark.parametrize("K", [512, 2048])
 def test_fused_epilogues(backend, oracle, K):
     """RMSNorm prologue, bias, residual (aliasing y) and the SwiGLU pair at M = 70 on device pointers.
