@@ -95,6 +95,12 @@ class ModelDesc(C.Structure):
                 ("rope_scale", C.c_float), ("rope_neox", C.c_int), ("kv_page", C.c_int)]
 
 
+class Q35Desc(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("n_layer", "hidden", "n_head", "n_kv", "head_dim", "rope_dim", "conv_k", "sk", "n_vhead",
+                                        "n_khead", "n_expert", "top_k", "eff", "vocab", "ctx")] + \
+               [("rms_eps", C.c_float), ("rope_base", C.c_float), ("kv_page", C.c_int)]
+
+
 # every symbol include/ggb200.h declares
 EXPORTS = [
     "ggb_create", "ggb_destroy", "ggb_mul_mat_q", "ggb_rms_norm", "ggb_rope", "ggb_rope_batched", "ggb_matmul_bf16",
@@ -103,6 +109,8 @@ EXPORTS = [
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
     "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
+    "ggb_q35_create", "ggb_q35_destroy", "ggb_q35_set_tensor", "ggb_q35_finalize", "ggb_q35_reset", "ggb_q35_prefill", "ggb_q35_decode",
+    "ggb_q35_generate", "ggb_q35_read_state", "ggb_q35_decode_bytes",
 ]
 
 _lib = None
@@ -168,6 +176,18 @@ def load_library() -> C.CDLL:
     L.ggb_model_read_kv.argtypes = [vp, i32, i32, i32, vp]
     L.ggb_model_decode_bytes.argtypes = [vp, i32]
     L.ggb_model_decode_bytes.restype = C.c_uint64
+    L.ggb_q35_create.argtypes = [vp, vp, C.POINTER(vp)]
+    L.ggb_q35_destroy.argtypes = [vp]
+    L.ggb_q35_destroy.restype = None
+    L.ggb_q35_set_tensor.argtypes = [vp, i32, i32, u32, i64, i32, vp]
+    L.ggb_q35_finalize.argtypes = [vp]
+    L.ggb_q35_reset.argtypes = [vp]
+    L.ggb_q35_prefill.argtypes = [vp, vp, i32, i32, vp, C.POINTER(C.c_int32)]
+    L.ggb_q35_decode.argtypes = [vp, C.c_int32, i32, vp, C.POINTER(C.c_int32)]
+    L.ggb_q35_generate.argtypes = [vp, C.c_int32, i32, i32, vp]
+    L.ggb_q35_read_state.argtypes = [vp, i32, vp]
+    L.ggb_q35_decode_bytes.argtypes = [vp, i32]
+    L.ggb_q35_decode_bytes.restype = C.c_uint64
     _lib = L
     return L
 
@@ -438,6 +458,110 @@ class Model:
         if getattr(self, "m", None):
             if getattr(self.b, "h", None):                    # a destroyed handle took its models' memory with the context
                 self.b.lib.ggb_model_destroy(self.m)
+            self.m = None
+            try:
+                self.b._models.discard(self)
+            except Exception:
+                pass
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_Q35_SLOTS = {"token_embd.weight": 0, "output.weight": 1, "output_norm.weight": 2}
+_Q35_LAYER_SLOTS = {
+    "attn_norm.weight": 10, "post_attention_norm.weight": 11,
+    "attn_qkv.weight": 20, "attn_gate.weight": 21, "ssm_alpha.weight": 22, "ssm_beta.weight": 23, "ssm_conv1d.weight": 24,
+    "ssm_a": 25, "ssm_dt.bias": 26, "ssm_norm.weight": 27, "ssm_out.weight": 28,
+    "attn_q.weight": 30, "attn_k.weight": 31, "attn_v.weight": 32, "attn_output.weight": 33, "attn_q_norm.weight": 34,
+    "attn_k_norm.weight": 35,
+    "ffn_gate_inp.weight": 40, "ffn_gate_exps.weight": 41, "ffn_up_exps.weight": 42, "ffn_down_exps.weight": 43,
+    "ffn_gate_shexp.weight": 44, "ffn_up_shexp.weight": 45, "ffn_down_shexp.weight": 46, "ffn_gate_inp_shexp.weight": 47,
+}
+_Q35_EXPERT = ("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight")
+
+
+class Q35Model:
+    """A qwen35moe decoder (Gated DeltaNet + gated full attention + mixture-of-experts FFN, the reference's
+    src/cli/main.cpp:2859-3232) resident in HBM.  `tensors` as ggnpu_b200.synth.build_q35_model makes them.
+    On a backend that joined a group the model is expert parallel: this process keeps its slice of the
+    experts (a contiguous range along the expert axis), everything else is replicated."""
+
+    def __init__(self, backend: CudaBackend, cfg, tensors: dict):
+        self.b, self.cfg = backend, cfg
+        L = backend.lib
+        desc = Q35Desc(cfg.n_layer, cfg.hidden, cfg.n_head, cfg.n_kv, cfg.head_dim, cfg.rope_dim, cfg.conv_k, cfg.sk, cfg.n_vhead,
+                       cfg.n_khead, cfg.n_expert, cfg.top_k, cfg.eff, cfg.vocab, cfg.ctx, cfg.rms_eps,
+                       float(np.float32(cfg.rope_base)), 0)
+        m = C.c_void_p()
+        backend.check(L.ggb_q35_create(backend.h, C.byref(desc), C.byref(m)), "q35_create")
+        self.m = m
+        if not hasattr(backend, "_models"):
+            import weakref
+            backend._models = weakref.WeakSet()
+        backend._models.add(self)
+        rank, size = backend.tp_rank, backend.tp_size
+        for name, (tid, dims, raw) in tensors.items():
+            raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+            if name in _Q35_SLOTS:
+                slot, layer, key = _Q35_SLOTS[name], -1, name
+            else:
+                parts = name.split(".", 2)
+                if parts[0] != "blk" or parts[2] not in _Q35_LAYER_SLOTS:
+                    raise KeyError(f"tensor {name} has no slot in the qwen35moe graph")
+                slot, layer, key = _Q35_LAYER_SLOTS[parts[2]], int(parts[1]), parts[2]
+            if len(dims) == 3:                      # expert tensor [K, N, n_expert]: experts stacked along N
+                k, n_exp = dims[0], dims[2]
+                n = dims[1] * n_exp
+                if size > 1 and key in _Q35_EXPERT:
+                    per = raw.size // n_exp
+                    nl = n_exp // size
+                    raw = np.ascontiguousarray(raw[rank * nl * per:(rank + 1) * nl * per])
+                    n = dims[1] * nl
+            elif len(dims) == 2:
+                n, k = dims[1], dims[0]
+            else:
+                n, k = dims[0], 1
+            backend.check(L.ggb_q35_set_tensor(m, slot, layer, int(tid), n, k, _ptr(raw)), f"q35_set_tensor({name})")
+        backend.check(L.ggb_q35_finalize(m), "q35_finalize")
+
+    def reset(self):
+        self.b.check(self.b.lib.ggb_q35_reset(self.m), "q35_reset")
+
+    def prefill(self, tokens, pos0=0, want_logits=True):
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        nxt = C.c_int32()
+        self.b.check(self.b.lib.ggb_q35_prefill(self.m, _ptr(toks), toks.size, pos0, _ptr(logits), C.byref(nxt)), "q35_prefill")
+        return logits, nxt.value
+
+    def decode(self, token, pos, want_logits=True):
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        nxt = C.c_int32()
+        self.b.check(self.b.lib.ggb_q35_decode(self.m, int(token), int(pos), _ptr(logits), C.byref(nxt)), "q35_decode")
+        return logits, nxt.value
+
+    def generate(self, first_token, pos0, n):
+        out = np.empty(n, dtype=np.int32)
+        self.b.check(self.b.lib.ggb_q35_generate(self.m, int(first_token), int(pos0), n, _ptr(out)), "q35_generate")
+        return out
+
+    def rec_state(self, layer):
+        c = self.cfg
+        out = np.empty((c.n_vhead, c.sk, c.sk), dtype=np.float32)
+        self.b.check(self.b.lib.ggb_q35_read_state(self.m, layer, _ptr(out)), "q35_read_state")
+        return out
+
+    def decode_bytes(self, pos) -> int:
+        return int(self.b.lib.ggb_q35_decode_bytes(self.m, pos))
+
+    def close(self):
+        if getattr(self, "m", None):
+            if getattr(self.b, "h", None):
+                self.b.lib.ggb_q35_destroy(self.m)
             self.m = None
             try:
                 self.b._models.discard(self)

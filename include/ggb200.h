@@ -375,6 +375,59 @@ GGB_API int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float
 /* Algorithmic HBM bytes one decode step at position pos reads+writes (weights once + KV). */
 GGB_API uint64_t ggb_model_decode_bytes(ggb_model m, int pos);
 
+/* ---- whole-model path, qwen35 / qwen35moe graph (src/cli/main.cpp:2859-3232) ----
+ * Gated DeltaNet layers (those given an ssm_conv1d tensor, :2207-2213) and gated full-attention layers, a
+ * mixture-of-experts FFN in every layer.  The architecture is a recurrence, so the reference feeds it one token
+ * per forward, the prompt included (:2327); so does this path: one CUDA graph per token, a prompt being the graph
+ * replayed over a device-resident token list (no host round trip between tokens).  Metadata as the reference
+ * reads it (:2181-2200): head_dim = attention.key_length, rope_dim = rope.dimension_count (leading dims of a head
+ * that rotate, NeoX pairs), sk = ssm.state_size, n_vhead = ssm.inner_size / sk, n_khead = ssm.group_count,
+ * eff = expert_feed_forward_length (routed and shared experts alike). */
+typedef struct ggb_q35_desc {
+    int n_layer, hidden, n_head, n_kv, head_dim, rope_dim, conv_k, sk, n_vhead, n_khead, n_expert, top_k, eff, vocab, ctx;
+    float rms_eps, rope_base;
+    int kv_page;     /* tokens per KV page; 0 = default (64) */
+} ggb_q35_desc;
+/* On a handle that belongs to a group of `size` ranks (ggb_tp_init) the model is EXPERT parallel: the three
+ * *_exps tensors hold this rank's n_expert / size experts, rank r owning experts [r n_expert / size, ...); every
+ * other tensor is replicated and n_expert in the description stays the full count.  Each rank runs the mixers,
+ * streams only the chosen experts it owns, and the partial FFN rows are summed over the group, so every rank ends
+ * a step with the same logits and token. */
+typedef struct ggb_q35_model_s* ggb_q35_model;
+enum ggb_q35_slot {
+    GGB_Q35_TOKEN_EMBD = 0, GGB_Q35_OUTPUT = 1, GGB_Q35_OUTPUT_NORM = 2,
+    GGB_Q35_ATTN_NORM = 10, GGB_Q35_POST_NORM = 11,
+    /* DeltaNet layers: attn_qkv [2 n_khead sk + n_vhead sk][hidden], attn_gate [n_vhead sk][hidden], ssm_alpha / ssm_beta
+     * F32 [n_vhead][hidden], ssm_conv1d F32 [conv_dim][conv_k] (newest tap last), ssm_a / ssm_dt.bias F32 [n_vhead],
+     * ssm_norm F32 [sk], ssm_out [hidden][n_vhead sk] */
+    GGB_Q35_SSM_QKV = 20, GGB_Q35_SSM_GATE = 21, GGB_Q35_SSM_ALPHA = 22, GGB_Q35_SSM_BETA = 23, GGB_Q35_SSM_CONV = 24,
+    GGB_Q35_SSM_A = 25, GGB_Q35_SSM_DT_BIAS = 26, GGB_Q35_SSM_NORM = 27, GGB_Q35_SSM_OUT = 28,
+    /* attention layers: attn_q [2 n_head head_dim][hidden] (per head query | gate), attn_k / attn_v, attn_output, QK norms */
+    GGB_Q35_ATTN_Q = 30, GGB_Q35_ATTN_K = 31, GGB_Q35_ATTN_V = 32, GGB_Q35_ATTN_OUT = 33, GGB_Q35_Q_NORM = 34, GGB_Q35_K_NORM = 35,
+    /* every layer: ffn_gate_inp F32 [n_expert][hidden], ffn_{gate,up}_exps [n_expert eff][hidden], ffn_down_exps
+     * [n_expert hidden][eff], the shared expert's three matrices and its gate vector F32 [hidden] */
+    GGB_Q35_ROUTER = 40, GGB_Q35_GATE_EXPS = 41, GGB_Q35_UP_EXPS = 42, GGB_Q35_DOWN_EXPS = 43, GGB_Q35_SH_GATE = 44,
+    GGB_Q35_SH_UP = 45, GGB_Q35_SH_DOWN = 46, GGB_Q35_SH_GATE_INP = 47
+};
+GGB_API int ggb_q35_create(ggb_handle h, const ggb_q35_desc* desc, ggb_q35_model* out);
+GGB_API void ggb_q35_destroy(ggb_q35_model m);
+/* Matrices as GGUF rows ([N][K] of `type`; expert tensors whole, experts stacked along N); F32 tensors with N * K
+ * equal to their element count (vectors: K = 1). */
+GGB_API int ggb_q35_set_tensor(ggb_q35_model m, int slot, int layer, uint32_t type, int64_t N, int K, const void* host_data);
+GGB_API int ggb_q35_finalize(ggb_q35_model m);
+/* Zero the recurrent and convolution states (a new sequence; the KV cache needs no clearing). */
+GGB_API int ggb_q35_reset(ggb_q35_model m);
+/* n_tok prompt tokens at positions pos0.., one graph replay each; logits of the last (optional) and the greedy token. */
+GGB_API int ggb_q35_prefill(ggb_q35_model m, const int32_t* host_tokens, int n_tok, int pos0, float* host_logits, int32_t* next_token);
+GGB_API int ggb_q35_decode(ggb_q35_model m, int32_t token, int pos, float* host_logits, int32_t* next_token);
+/* n greedy steps with the token fed back on the device. */
+GGB_API int ggb_q35_generate(ggb_q35_model m, int32_t first_token, int pos0, int n, int32_t* host_out);
+/* Recurrent state [n_vhead][sk][sk] of a DeltaNet layer (tests). */
+GGB_API int ggb_q35_read_state(ggb_q35_model m, int layer, float* host_out);
+/* Algorithmic HBM bytes of one decode step at position pos (mixer weights, router, the top_k + shared experts,
+ * recurrent and conv states read and written, KV of the attention layers, logits matrix). */
+GGB_API uint64_t ggb_q35_decode_bytes(ggb_q35_model m, int pos);
+
 #ifdef __cplusplus
 }
 #endif
