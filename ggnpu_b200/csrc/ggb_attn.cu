@@ -10,6 +10,7 @@
 
 #include "ggb_internal.h"
 #include "ggb_attn.h"
+#include "ggb_attn_tile.cuh"
 
 namespace ggb {
 
@@ -165,241 +166,9 @@ int launch_rope_append(Context* c, const KvAppendArgs& a_in, int n_tok, cudaStre
 // new key, stores key and value into the cache and uses them directly.
 template <int HD>
 __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
-    constexpr int KW = HD / 2;           // 32-bit words (bf16 pairs) per K or V row
-    constexpr int KS = KW + 1;           // padded K row stride: thread-per-key reads hit distinct banks
-    constexpr int TK = 64;               // keys per chunk
-    constexpr int NP = (8 * KW + 127) / 128;   // (head, dim pair) items per thread in P*V
-    pdl_sync();
-    const int h = blockIdx.x, split = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
-    const int lane = tid & 31, warp = tid >> 5;
-    const int G = a.n_head / a.n_kv;
-    // Fused step: the values the rotation below needs (the G query heads and the new key) do not depend
-    // on the position, so their loads are issued before the position is looked at; the position's own
-    // round trip to memory then overlaps theirs instead of preceding it.
-    constexpr int NQ = HD <= 128 ? (9 * (HD / 2) + 127) / 128 : 0;       // rotation items per thread, G <= 8
-    float qpre0[NQ > 0 ? NQ : 1], qpre1[NQ > 0 ? NQ : 1];
-    if (NQ > 0 && a.fuse) {
-        const float* qb = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
-#pragma unroll
-        for (int u = 0; u < NQ; ++u) {
-            const int idx = tid + 128 * u, hh = idx / (HD / 2), i = idx - hh * (HD / 2);
-            if (hh <= G) {
-                const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + HD / 2 : 2 * i + 1;
-                const float* src = hh < G ? qb + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
-                qpre0[u] = src[i0]; qpre1[u] = src[i1];
-            }
-        }
-    }
-    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
-    const int keys_per_split = a.pages_per_split * a.page;
-    const int j_begin = split * keys_per_split;
-    const int j_end = min(j_begin + keys_per_split, pos + 1);
-    if (j_begin > pos) return;           // no visible key in this split (the merge skips it too)
-
     extern __shared__ __align__(16) uint32_t sm_u[];
-    uint32_t* Vt = sm_u;                                   // [TK][KW]   (16-byte aligned rows)
-    uint32_t* Kt = Vt + TK * KW;                           // [TK][KS]
-    float* qs = reinterpret_cast<float*>(Kt + TK * KS);    // [G][HD], already multiplied by 1/sqrt(HD)
-    float* S = qs + 8 * HD;                                // [8][TK] scores, then probabilities
-    float* mrun = S + 8 * TK;                              // [8] running max, [8] running sum, [8] rescale
-    float* lrun = mrun + 8;
-    float* corr = lrun + 8;
-    float* hinv = corr + 8;                                // [9] per-head norm factors (q heads, then k)
-    __nv_bfloat16* fresh = reinterpret_cast<__nv_bfloat16*>(hinv + 12);   // [2][HD] new key and value
-    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
-    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
-    const bool has_new = a.fuse && pos >= j_begin && pos < j_begin + keys_per_split;
-    const int half = HD >> 1;
-
-    // The first chunk's K and V rows are requested now, into registers, so that their memory latency
-    // overlaps the q / new-key preparation below (head_dim <= 128; larger heads load in the loop).
-    constexpr int NPF = HD <= 128 ? HD / 16 : 0;
-    uint4 kpre[NPF > 0 ? NPF : 1], vpre[NPF > 0 ? NPF : 1];
-    if (NPF > 0) {
-        const int nk0 = min(TK, j_end - j_begin);
-#pragma unroll
-        for (int u = 0; u < NPF; ++u) {
-            const int i = tid + 128 * u;
-            const int row = i / (HD / 8), part = i - row * (HD / 8);
-            if (row < nk0) {
-                const int j = j_begin + row;
-                const int page = a.block_table[j / a.page], slot = j % a.page;
-                const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
-                kpre[u] = *reinterpret_cast<const uint4*>(a.k_cache + o);
-                vpre[u] = *reinterpret_cast<const uint4*>(a.v_cache + o);
-            }
-        }
-    }
-    if (tid < 8) { mrun[tid] = -INFINITY; lrun[tid] = 0.0f; }
-    if (a.fuse) {
-        // optional per-head RMS norm of q and k before the rotation, sum of squares in double
-        // (src/cli/main.cpp:3294-3299)
-        for (int hh = warp; hh < G + 1; hh += 4) {
-            const float* nw = hh < G ? a.q_norm : a.k_norm;
-            float inv = 1.0f;
-            if (nw) {
-                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
-                double ss = 0.0;
-                for (int i = lane; i < HD; i += 32) ss += static_cast<double>(src[i]) * src[i];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-                inv = 1.0f / sqrtf(static_cast<float>(ss / HD) + a.eps);
-            }
-            if (lane == 0) hinv[hh] = inv;
-        }
-        __syncthreads();
-        const float* cs = a.cos_tab + static_cast<size_t>(pos) * half;
-        const float* sn = a.sin_tab + static_cast<size_t>(pos) * half;
-        auto rotate = [&](int idx, float v0, float v1) {
-            const int hh = idx / half, i = idx - hh * half;
-            const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
-            const bool is_q = hh < G;
-            const float* nw = is_q ? a.q_norm : a.k_norm;
-            if (nw) { v0 = v0 * hinv[hh] * nw[i0]; v1 = v1 * hinv[hh] * nw[i1]; }
-            const float r0 = v0 * cs[i] - v1 * sn[i], r1 = v0 * sn[i] + v1 * cs[i];
-            if (is_q) { qs[hh * HD + i0] = r0 * scale; qs[hh * HD + i1] = r1 * scale; }
-            else { fresh[i0] = __float2bfloat16_rn(r0); fresh[i1] = __float2bfloat16_rn(r1); }
-        };
-        const int n_items = (G + (has_new ? 1 : 0)) * half;
-        if (NQ > 0) {
-#pragma unroll
-            for (int u = 0; u < NQ; ++u)
-                if (tid + 128 * u < n_items) rotate(tid + 128 * u, qpre0[u], qpre1[u]);
-        } else {
-            for (int idx = tid; idx < n_items; idx += 128) {
-                const int hh = idx / half, i = idx - hh * half;
-                const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
-                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
-                rotate(idx, src[i0], src[i1]);
-            }
-        }
-        if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(a.v_new[static_cast<size_t>(h) * HD + i]);
-        __syncthreads();
-        if (has_new) {     // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
-            const int page = a.block_table[pos / a.page], slot = pos % a.page;
-            const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD;
-            for (int i = tid; i < HD; i += 128) { a.k_cache_w[o + i] = fresh[i]; a.v_cache_w[o + i] = fresh[HD + i]; }
-        }
-    } else {
-        for (int i = tid; i < G * HD; i += 128) qs[i] = q[i] * scale;
-    }
-
-    float acc[NP][2];
-#pragma unroll
-    for (int p = 0; p < NP; ++p) { acc[p][0] = 0.0f; acc[p][1] = 0.0f; }
-
-    for (int jc = j_begin; jc < j_end; jc += TK) {
-        const int nk = min(TK, j_end - jc);
-        __syncthreads();                                   // previous chunk fully consumed
-        if (NPF > 0 && jc == j_begin) {
-#pragma unroll
-            for (int u = 0; u < NPF; ++u) {
-                const int i = tid + 128 * u;
-                const int row = i / (HD / 8), part = i - row * (HD / 8);
-                if (row < nk) {
-                    uint32_t* kd = Kt + row * KS + part * 4;
-                    kd[0] = kpre[u].x; kd[1] = kpre[u].y; kd[2] = kpre[u].z; kd[3] = kpre[u].w;
-                    *reinterpret_cast<uint4*>(Vt + row * KW + part * 4) = vpre[u];
-                }
-            }
-        } else
-        for (int i = tid; i < nk * (HD / 8); i += 128) {
-            const int row = i / (HD / 8), part = i - row * (HD / 8);
-            const int j = jc + row;
-            const int page = a.block_table[j / a.page], slot = j % a.page;
-            const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
-            const uint4 kv = *reinterpret_cast<const uint4*>(a.k_cache + o);
-            const uint4 vv = *reinterpret_cast<const uint4*>(a.v_cache + o);
-            uint32_t* kd = Kt + row * KS + part * 4;
-            kd[0] = kv.x; kd[1] = kv.y; kd[2] = kv.z; kd[3] = kv.w;
-            *reinterpret_cast<uint4*>(Vt + row * KW + part * 4) = vv;
-        }
-        if (has_new && pos >= jc && pos < jc + nk) {       // the new token's row comes from shared memory
-            __syncthreads();
-            const uint32_t* fk = reinterpret_cast<const uint32_t*>(fresh);
-            for (int w = tid; w < KW; w += 128) { Kt[(pos - jc) * KS + w] = fk[w]; Vt[(pos - jc) * KW + w] = fk[KW + w]; }
-        }
-        __syncthreads();
-        {   // scores: thread = (key, head parity); heads hg, hg+2, hg+4, hg+6 share each K word
-            const int key = tid & 63, hg = tid >> 6;
-            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-            if (key < nk) {
-                const uint32_t* kr = Kt + key * KS;
-#pragma unroll 8
-                for (int w = 0; w < KW; ++w) {
-                    const uint32_t kw = kr[w];
-                    const float k0 = __uint_as_float(kw << 16), k1 = __uint_as_float(kw & 0xFFFF0000u);
-                    const float2 q0 = *reinterpret_cast<const float2*>(qs + hg * HD + 2 * w);
-                    s0 = fmaf(q0.x, k0, fmaf(q0.y, k1, s0));
-                    if (G > 2) { const float2 q1 = *reinterpret_cast<const float2*>(qs + (hg + 2) * HD + 2 * w); s1 = fmaf(q1.x, k0, fmaf(q1.y, k1, s1)); }
-                    if (G > 4) { const float2 q2 = *reinterpret_cast<const float2*>(qs + (hg + 4) * HD + 2 * w); s2 = fmaf(q2.x, k0, fmaf(q2.y, k1, s2)); }
-                    if (G > 6) { const float2 q3 = *reinterpret_cast<const float2*>(qs + (hg + 6) * HD + 2 * w); s3 = fmaf(q3.x, k0, fmaf(q3.y, k1, s3)); }
-                }
-            } else { s0 = s1 = s2 = s3 = -INFINITY; }
-            if (hg < G) S[hg * TK + key] = s0;
-            if (hg + 2 < G) S[(hg + 2) * TK + key] = s1;
-            if (hg + 4 < G) S[(hg + 4) * TK + key] = s2;
-            if (hg + 6 < G) S[(hg + 6) * TK + key] = s3;
-        }
-        __syncthreads();
-        for (int hh = warp; hh < G; hh += 4) {             // online softmax, one warp per head
-            const float v0 = S[hh * TK + lane], v1 = S[hh * TK + lane + 32];
-            float mx = fmaxf(v0, v1);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-            const float mo = mrun[hh], mn = fmaxf(mo, mx);
-            const float p0 = expf(v0 - mn), p1 = expf(v1 - mn);
-            const float sum = wsum(p0 + p1);
-            S[hh * TK + lane] = p0; S[hh * TK + lane + 32] = p1;
-            if (lane == 0) { const float c = expf(mo - mn); corr[hh] = c; lrun[hh] = lrun[hh] * c + sum; mrun[hh] = mn; }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int p = 0; p < NP; ++p) {                     // acc = acc * corr + P V
-            const int idx = tid + 128 * p;
-            if (idx < G * KW) {
-                const int gq = idx / KW, w = idx - gq * KW;
-                const float c = corr[gq];
-                float a0 = acc[p][0] * c, a1 = acc[p][1] * c;
-                const float* pr = S + gq * TK;
-                // two partial sums per output and eight keys per pass: the shared-memory loads of a pass are
-                // all in flight before the first multiply-add needs one
-                float b0 = 0.0f, b1 = 0.0f;
-                int j = 0;
-                for (; j + 8 <= nk; j += 8) {
-                    uint32_t vw[8];
-                    float pj[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) { vw[u] = Vt[(j + u) * KW + w]; pj[u] = pr[j + u]; }
-#pragma unroll
-                    for (int u = 0; u < 8; u += 2) {
-                        a0 = fmaf(pj[u], __uint_as_float(vw[u] << 16), a0);
-                        a1 = fmaf(pj[u], __uint_as_float(vw[u] & 0xFFFF0000u), a1);
-                        b0 = fmaf(pj[u + 1], __uint_as_float(vw[u + 1] << 16), b0);
-                        b1 = fmaf(pj[u + 1], __uint_as_float(vw[u + 1] & 0xFFFF0000u), b1);
-                    }
-                }
-                for (; j < nk; ++j) {
-                    const uint32_t v1 = Vt[j * KW + w];
-                    const float p1 = pr[j];
-                    a0 = fmaf(p1, __uint_as_float(v1 << 16), a0);
-                    a1 = fmaf(p1, __uint_as_float(v1 & 0xFFFF0000u), a1);
-                }
-                acc[p][0] = a0 + b0; acc[p][1] = a1 + b1;
-            }
-        }
-    }
-    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits + split) * (HD + 2);
-#pragma unroll
-    for (int p = 0; p < NP; ++p) {
-        const int idx = tid + 128 * p;
-        if (idx < G * KW) {
-            const int gq = idx / KW, w = idx - gq * KW;
-            float* pg = part + static_cast<size_t>(gq) * a.n_splits * (HD + 2);
-            pg[2 + 2 * w] = acc[p][0]; pg[3 + 2 * w] = acc[p][1];
-            if (w == 0) { pg[0] = mrun[gq]; pg[1] = lrun[gq]; }
-        }
-    }
+    pdl_sync();
+    attn_tile_body<HD, false>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, sm_u, [] { __syncthreads(); });
 }
 
 // grid (n_head, n_tok): merge the visible splits, normalise, write out[t][head][hd].
@@ -443,7 +212,7 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     size_t smem = 0;
 #define GGB_ATTN_CASE(HD)                                                                                              \
     {                                                                                                                  \
-        smem = sizeof(uint32_t) * (64 * (HD / 2) + 64 * (HD / 2 + 1)) + sizeof(float) * (8 * HD + 8 * 64 + 24 + 12) + 2 * 2 * HD + 16; \
+        smem = attn_tile_smem(HD);                                                                                     \
         e = ensure_dynamic_smem(c, attn_tile_kernel<HD>, smem);                                                        \
         if (e == cudaSuccess) e = launch_pdl(c, attn_tile_kernel<HD>, grid, dim3(128), smem, s, a);                     \
     }

@@ -4,10 +4,13 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <stdlib.h>
+
 #include <cmath>
 #include <memory>
 
 #include "ggb_attn.h"
+#include "ggb_decode_step.h"
 #include "ggb_internal.h"
 
 using namespace ggb;
@@ -55,6 +58,11 @@ struct ggb_model_s {
     float* h_logits = nullptr;
     cudaGraphExec_t decode_graph = nullptr;
     uint64_t launches_per_step = 0;
+    // persistent decode-step kernel (single-token steps of an all-Q4_K / Q6_K model on one GPU)
+    bool use_step = false;
+    StepArgs step{};
+    StepLayer* d_step_layers = nullptr;
+    unsigned* d_step_bar = nullptr;
 };
 
 namespace {
@@ -94,6 +102,12 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
     const int H = d.hidden, hd = d.head_dim, qd = d.n_head * hd, kvd = d.n_kv * hd, F = d.ffn;
     const int32_t* dpos = dev_pos ? m->d_pos : nullptr;
     M_TRY(launch_gather_rows(c, m->tok_embd->w, m->d_tokens, n_tok, m->x, H, s));
+    if (m->use_step && n_tok == 1) {
+        // all layers and the logits in one persistent kernel
+        m->step.attn.d_pos = dpos; m->step.attn.pos0 = pos0;
+        M_TRY(launch_decode_step(c, m->step, hd, s));
+        return launch_argmax(c, m->logits, d.vocab, m->d_next, m->amax_partial, s);
+    }
     for (int L = 0; L < d.n_layer; ++L) {
         const Layer& l = m->layers[L];
         GemvArgs a = gemv_args(l.q, m->x, n_tok, H, m->q, qd);
@@ -351,28 +365,95 @@ int ggb_model_finalize(ggb_model m) {
     M_TRY(cuda_status(c, cudaMallocHost(&m->h_io, 64), "pinned alloc"));
     M_TRY(cuda_status(c, cudaMallocHost(&m->h_logits, sizeof(float) * d.vocab), "pinned alloc"));
 
+    // Persistent decode-step kernel: every layer matrix and the logits matrix Q4_K / Q6_K in the tensor-core layout,
+    // no biases or QK norms, head_dim 64 / 128, one GPU.  Anything else keeps the kernel-per-matrix graph.
+    {
+        bool ok = c->use_mma && c->tp_size == 1 && (hd == 64 || hd == 128) && m->page % 8 == 0 && getenv("GGB_NO_STEP_KERNEL") == nullptr &&
+                  d.hidden % 256 == 0 && d.ffn % 256 == 0 && qd % 256 == 0;
+        const DeviceWeight* outw = m->output ? m->output : m->tok_embd;
+        ok = ok && step_mat_ok(outw->w);
+        for (const Layer& l : m->layers)
+            ok = ok && step_mat_ok(l.q->w) && step_mat_ok(l.k->w) && step_mat_ok(l.v->w) && step_mat_ok(l.o->w) && step_mat_ok(l.gate->w) &&
+                 step_mat_ok(l.up->w) && step_mat_ok(l.down->w) && l.gate->w.type == l.up->w.type && !l.bq && !l.bk && !l.bv && !l.q_norm && !l.k_norm;
+        if (ok) {
+            const int n_cta = c->sm_count;
+            std::vector<StepLayer> hl(d.n_layer);
+            for (int L = 0; L < d.n_layer; ++L) {
+                const Layer& l = m->layers[L];
+                StepLayer& t = hl[L];
+                t.q = step_mat(l.q->w, m->q); t.k = step_mat(l.k->w, m->k); t.v = step_mat(l.v->w, m->v); t.o = step_mat(l.o->w, m->x);
+                t.gate = step_mat(l.gate->w, m->act); t.up = step_mat(l.up->w, m->act); t.down = step_mat(l.down->w, m->x);
+                t.attn_norm = l.attn_norm; t.ffn_norm = l.ffn_norm;
+                t.k_cache = m->k_cache + static_cast<size_t>(L) * m->kv_layer_elems;
+                t.v_cache = m->v_cache + static_cast<size_t>(L) * m->kv_layer_elems;
+            }
+            M_TRY(dev_alloc(m, &m->d_step_layers, hl.size()));
+            M_TRY(dev_alloc(m, &m->d_step_bar, 1));
+            M_TRY(cuda_status(c, cudaMemcpy(m->d_step_layers, hl.data(), sizeof(StepLayer) * hl.size(), cudaMemcpyHostToDevice), "step layers"));
+            StepArgs& a = m->step;
+            a.layers = m->d_step_layers; a.n_layer = d.n_layer;
+            a.out = step_mat(outw->w, m->logits); a.out_norm = m->output_norm;
+            step_shape_init(a.shape[kPhaseQkv], d.hidden, qd, kvd, kvd, false, n_cta);
+            step_shape_init(a.shape[kPhaseO], qd, d.hidden, 0, 0, false, n_cta);
+            step_shape_init(a.shape[kPhaseGateUp], d.hidden, d.ffn, 0, 0, true, n_cta);
+            step_shape_init(a.shape[kPhaseDown], d.ffn, d.hidden, 0, 0, false, n_cta);
+            step_shape_init(a.shape[kPhaseLogits], d.hidden, outw->w.N, 0, 0, false, n_cta);
+            a.x = m->x; a.act = m->act; a.eps = d.rms_eps; a.n_cta = n_cta;
+            a.k_max = std::max(std::max(d.hidden, qd), d.ffn);
+            a.bar = m->d_step_bar; a.err = c->d_err;
+            AttnPagedArgs& aa = a.attn;
+            aa = AttnPagedArgs{};
+            aa.q = m->q; aa.block_table = m->block_table; aa.partial = m->partial; aa.out = m->att;
+            aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
+            aa.pages_per_split = m->pages_per_split;
+            aa.fuse = 1; aa.neox = d.rope_neox; aa.skip_merge = 1; aa.k_new = m->k; aa.v_new = m->v;
+            aa.cos_tab = m->cos_tab; aa.sin_tab = m->sin_tab; aa.eps = d.rms_eps;
+            m->use_step = true;
+        }
+    }
     // One eager step first: it sets every kernel's shared-memory attribute outside capture
     // (and faults early, if anything is wrong, where the error is attributable).
-    M_TRY(enqueue_forward(m, 1, true, 0));
-    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "warm-up step"));
-    // Capture the decode step: forward + token/position feedback.
-    const uint64_t before = c->launches;
-    M_TRY(cuda_status(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "begin capture"));
-    int st = enqueue_forward(m, 1, true, 0);
-    if (st == GGB_OK) {
-        feedback_kernel<<<1, 1, 0, c->stream>>>(m->d_next, m->d_tokens, m->d_pos, m->d_gen, m->d_step, d.ctx);
-        c->launches++;
-        st = cuda_status(c, cudaGetLastError(), "feedback kernel");
+    {
+        int st = enqueue_forward(m, 1, true, 0);
+        if (st == GGB_OK) st = cuda_status(c, cudaStreamSynchronize(c->stream), "warm-up step");
+        if (st != GGB_OK && m->use_step) {      // shapes outside the step kernel's shared memory, or no cooperative launch
+            m->use_step = false;
+            cudaStreamSynchronize(c->stream);
+            M_TRY(enqueue_forward(m, 1, true, 0));
+            M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "warm-up step"));
+        } else if (st != GGB_OK) return st;
+        M_TRY(check_device_error(c));
     }
-    cudaGraph_t graph = nullptr;
-    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
-    if (st != GGB_OK) { if (graph) cudaGraphDestroy(graph); return st; }
-    M_TRY(cuda_status(c, e, "end capture"));
-    m->launches_per_step = c->launches - before;
-    c->launches = before;    // captured launches are counted when the graph is replayed
-    e = cudaGraphInstantiate(&m->decode_graph, graph, 0);
-    cudaGraphDestroy(graph);
-    M_TRY(cuda_status(c, e, "graph instantiate"));
+    // Capture the decode step: forward + token/position feedback.  Should the capture refuse the cooperative launch of
+    // the persistent kernel, the kernel-per-matrix graph is captured instead.
+    auto capture = [&]() -> int {
+        const uint64_t before = c->launches;
+        M_TRY(cuda_status(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "begin capture"));
+        int st = enqueue_forward(m, 1, true, 0);
+        if (st == GGB_OK) {
+            feedback_kernel<<<1, 1, 0, c->stream>>>(m->d_next, m->d_tokens, m->d_pos, m->d_gen, m->d_step, d.ctx);
+            c->launches++;
+            st = cuda_status(c, cudaGetLastError(), "feedback kernel");
+        }
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+        m->launches_per_step = c->launches - before;
+        c->launches = before;    // captured launches are counted when the graph is replayed
+        if (st != GGB_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        M_TRY(cuda_status(c, e, "end capture"));
+        e = cudaGraphInstantiate(&m->decode_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        return cuda_status(c, e, "graph instantiate");
+    };
+    {
+        int st = capture();
+        if (st != GGB_OK && m->use_step) {
+            m->use_step = false;
+            cudaGetLastError();
+            st = capture();
+        }
+        if (st != GGB_OK) return st;
+    }
     M_TRY(cuda_status(c, cudaMemset(m->k_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
     M_TRY(cuda_status(c, cudaMemset(m->v_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
     m->finalized = true;
