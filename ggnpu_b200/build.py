@@ -42,6 +42,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
     if not write_include(os.path.join(OBJ, "ggb_iq_grids.inc")):
         sys.stderr.write("ggnpu_b200.build: gguf package not found, IQ1/IQ2/IQ3 formats left out\n")
     extra += ["-I", OBJ]
+    extra += os.environ.get("GGB_NVCC_FLAGS", "").split()        # e.g. -DGGB_STEP_TRACE (time stamps in the decode-step kernel)
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")

@@ -5,11 +5,14 @@
 // Why one kernel: at batch 1 every matrix of a 1B..8B model streams in 1-5 us, so a step made of one launch per
 // matrix spends most of its time in launch gaps, prologues and pipeline ramps with the HBM idle.  Here one CTA per
 // SM lives for the whole step:
-//   * a producer warp streams the packed Q4_K / Q6_K weights of ALL phases, in schedule order, through per-warp
-//     rings of shared memory (cp.async.bulk -> mbarrier).  It needs no activations, so it runs ahead of the
-//     consumers across phase boundaries and layers (up to the rings' ~166 KB per SM, 24 MB over the GPU), and the
-//     weight stream never waits for a dependency;
-//   * eight consumer warps run the phases.  A phase = wait at a grid-wide barrier for the previous phase's output,
+//   * every warp owns a ring of shared-memory stages and a fixed sequence of weight tiles that runs through ALL
+//     phases and layers in schedule order.  When a warp has consumed a tile it requests, into the stage it just
+//     freed, the tile that lies one ring length ahead in its sequence (cp.async.bulk -> mbarrier).  Weights need no
+//     activations, so the requests run ahead of the computation across phase boundaries and layers (the rings hold
+//     ~166 KB per SM, 24 MB over the GPU) and the weight stream does not wait for a dependency.  (A dedicated
+//     producer warp whose lanes poll one "stage free" barrier per ring was measured first: the polls of one lane held
+//     up the refills of the others and every phase ran about twice as long.)
+//   * the eight warps run the phases.  A phase = wait at a grid-wide barrier for the previous phase's output,
 //     read the activation vector (L2), split it into int8 limbs, run the int8 tensor-core tiles that are already in
 //     shared memory, reduce, apply the epilogue, store, arrive at the next barrier;
 //   * the attention phase (the split-KV kernel's body, four warps per (KV head, split)) runs inside the same kernel;
@@ -30,7 +33,7 @@ namespace ggb {
 
 namespace {
 
-constexpr int kWarps = 8;                        // consumer warps (one more warp produces)
+constexpr int kWarps = 8;                        // warps per CTA
 constexpr int kStageBytes = 6912;                // 3 Q4_K (row group, block) units of 2304 B, or 2 Q6_K units of 3360 B
 constexpr int kMaxP = 4;
 constexpr uint32_t kSpinLimit = 1u << 17;        // mbarrier polls (each can suspend for microseconds)
@@ -86,6 +89,24 @@ __device__ __forceinline__ float wsum(float v) {
     return v;
 }
 
+// Optional time stamps (compile with -DGGB_STEP_TRACE): CTA 1, thread 0 writes %globaltimer into a device array that
+// ggb_step_trace_read hands to the host.  Compiled out otherwise.
+#ifdef GGB_STEP_TRACE
+__device__ unsigned long long g_step_trace[4096];
+__device__ int g_step_trace_n;
+__device__ __forceinline__ void stamp(int tag) {
+    __shared__ int n_s;                          // written by thread 0 only; stores are fire-and-forget, no load on the path
+    if (blockIdx.x == 1 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const int i = tag == 0 ? 0 : n_s;
+        if (i < 2047) { g_step_trace[2 * i] = t; g_step_trace[2 * i + 1] = static_cast<unsigned long long>(tag); n_s = i + 1; g_step_trace_n = i + 1; }
+    }
+}
+#else
+__device__ __forceinline__ void stamp(int) {}
+#endif
+
 // Shared-memory views of one CTA.
 struct Smem {
     uint8_t* ring;       // [kWarps][P][kStageBytes]
@@ -97,53 +118,110 @@ struct Smem {
     int plane_stride;
 };
 
-// ---- producer: the tiles of one GEMV phase for consumer warp `w` ---------------------------------------------------
-struct Ring { int st; uint32_t ph; bool ok; };
+// ---- the weight-tile sequence of one warp ---------------------------------------------------------------------------
+// Layer descriptors live in a window of four shared-memory slots (layer L in slot L & 3), refreshed as the computation
+// advances; a request that runs further ahead than the window reads its descriptor from global memory.
+constexpr int kLayerSlots = 4;
 
-__device__ __noinline__ Ring produce_phase(const StepShape* shp, const StepMat* m0, const StepMat* m1, const StepMat* m2, const Smem* smp,
-                                           uint64_t* full_bar, uint64_t* empty_bar, int P, int w, Ring r, int* err) {
-    const StepShape sh = *shp;
-    const Smem sm = *smp;
-    const StepMat* const mats[3] = {m0, m1, m2};
-    const int64_t g_begin = static_cast<int64_t>(blockIdx.x) * sh.groups / gridDim.x;
-    const int n_rg = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * sh.groups / gridDim.x - g_begin);
-    const int n_teams = kWarps / sh.ws, team = w / sh.ws, member = w % sh.ws;
-    for (int rg = team; rg < n_rg && r.ok; rg += n_teams) {
-        const int64_t G_rg = g_begin + rg;
-        const int mi = sh.nmat == 2 ? 0 : (sh.ncat > 1 && G_rg >= sh.g_start[1]) + (sh.ncat > 2 && G_rg >= sh.g_start[2]);
-        const StepMat* w0 = mats[mi];
-        const bool is_q6 = w0->type == T_Q6_K;
-        const int sb = is_q6 ? sh.sb6 : sh.sb4, nb = sh.nb, spr = (nb + sb - 1) / sb;
-        const int64_t blk0 = (G_rg - (sh.nmat == 2 ? 0 : sh.g_start[mi])) * nb;
-        for (int ti = member; ti < sh.nmat * spr; ti += sh.ws) {
-            const int s = w * P + r.st;
-            if (!(r.ok = mbar_wait(&empty_bar[s], r.ph, err, 1))) break;
-            const int mat = ti >= spr, sl = ti - mat * spr;
-            const int b0 = sl * sb, nbk = min(sb, nb - b0);
-            uint8_t* dst = sm.ring + static_cast<size_t>(s) * kStageBytes;
-            const StepMat* wm = mat ? mats[1] : w0;
-            const int64_t gb = blk0 + b0;
-            if (!is_q6) {
-                mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 2304u);
-                bulk_g2s(dst, wm->s[1] + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, &full_bar[s]);
-                bulk_g2s(dst + sb * 2048, wm->s[0] + gb * 256, static_cast<uint32_t>(nbk) * 256u, &full_bar[s]);
-            } else {
-                mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 3360u);
-                bulk_g2s(dst, wm->s[0] + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, &full_bar[s]);
-                bulk_g2s(dst + sb * 2048, wm->s[1] + gb * 1024, static_cast<uint32_t>(nbk) * 1024u, &full_bar[s]);
-                bulk_g2s(dst + sb * 3072, wm->s[2] + gb * 256, static_cast<uint32_t>(nbk) * 256u, &full_bar[s]);
-                bulk_g2s(dst + sb * 3328, wm->s[3] + gb * 32, static_cast<uint32_t>(nbk) * 32u, &full_bar[s]);
+struct Desc {                                    // what the sequence and the phases need to find their matrices
+    const StepLayer* slots;                      // shared memory, kLayerSlots entries
+    const StepLayer* global;                     // device array of all layers
+    const StepMat* out;                          // logits matrix (shared memory)
+    const StepShape* shapes;                     // shared memory, kPhaseCount entries
+    int n_layer;
+};
+
+// Position in the sequence: layer L (n_layer: the logits phase), GEMV phase p (0 q/k/v, 1 o, 2 gate/up, 3 down, 4 logits),
+// row group rg of this CTA's range (team-strided), tile ti of the row group (member-strided).  All warp-uniform.
+struct TileIt {
+    int L, p, rg, ti;
+    int n_rg, n_teams, member, ws, ntiles;       // of the current phase / row group
+    int g_begin;
+    const StepMat* w0;                           // matrix of the current row group (gate for the pair)
+    const StepMat* w1;                           // up matrix of the pair
+    int is_q6, sb, spr, nb;
+    int64_t blk0;
+    bool rg_ready, end;
+};
+
+__device__ __forceinline__ const StepMat* phase_mat(const StepLayer* l, const StepMat* out, int p, int mi) {
+    switch (p) {
+    case kPhaseQkv: return mi == 0 ? &l->q : (mi == 1 ? &l->k : &l->v);
+    case kPhaseO: return &l->o;
+    case kPhaseGateUp: return mi == 0 ? &l->gate : &l->up;
+    case kPhaseDown: return &l->down;
+    default: return out;
+    }
+}
+
+__device__ __forceinline__ void it_begin_phase(TileIt& it, const Desc& d, int warp) {
+    const StepShape& sh = d.shapes[it.p];
+    it.g_begin = sh.g_begin; it.n_rg = sh.n_rg;
+    it.ws = sh.ws; it.n_teams = kWarps >> sh.log_ws; it.member = warp & (sh.ws - 1); it.nb = sh.nb;
+    it.rg = warp >> sh.log_ws; it.ti = it.member; it.rg_ready = false;
+}
+
+// Moves `it` to the next existing tile at or after its position; false at the end of the step.  `window_max` = the
+// highest layer whose descriptor is valid in the shared-memory window.
+__device__ __noinline__ bool it_seek(TileIt& it, const Desc& d, int warp, int window_max) {
+    while (!it.end) {
+        if (it.rg < it.n_rg) {
+            if (!it.rg_ready) {
+                const StepShape& sh = d.shapes[it.p];
+                const int G_rg = it.g_begin + it.rg;
+                const int mi = sh.nmat == 2 ? 0 : (sh.ncat > 1 && G_rg >= sh.g_start[1]) + (sh.ncat > 2 && G_rg >= sh.g_start[2]);
+                const StepLayer* l = it.L <= window_max ? d.slots + (it.L & (kLayerSlots - 1)) : d.global + it.L;
+                it.w0 = phase_mat(l, d.out, it.p, mi);
+                it.w1 = sh.nmat == 2 ? phase_mat(l, d.out, it.p, 1) : it.w0;
+                it.is_q6 = it.w0->type == T_Q6_K;
+                it.sb = it.is_q6 ? sh.sb6 : sh.sb4;
+                it.spr = it.is_q6 ? sh.spr6 : sh.spr4;
+                it.ntiles = sh.nmat * it.spr;
+                it.blk0 = static_cast<int64_t>(G_rg - (sh.nmat == 2 ? 0 : sh.g_start[mi])) * sh.nb;
+                it.rg_ready = true;
             }
-            if (++r.st == P) { r.st = 0; r.ph ^= 1; }
+            if (it.ti < it.ntiles) return true;
+            it.rg += it.n_teams; it.ti = it.member; it.rg_ready = false;
+            continue;
+        }
+        // next phase
+        if (it.p == kPhaseLogits) { it.end = true; break; }
+        if (it.p == kPhaseDown) { it.p = kPhaseQkv; if (++it.L >= d.n_layer) it.p = kPhaseLogits; }
+        else ++it.p;
+        it_begin_phase(it, d, warp);
+    }
+    return false;
+}
+
+// Requests the tile `it` points at into ring stage s of this warp (lane 0 issues), then steps past it.
+__device__ __forceinline__ void it_issue(TileIt& it, uint8_t* stage, uint64_t* full, int lane) {
+    const int mat = it.ti >= it.spr, sl = it.ti - mat * it.spr;
+    const int b0 = sl * it.sb, nbk = min(it.sb, it.nb - b0);
+    if (lane == 0) {
+        const StepMat* wm = mat ? it.w1 : it.w0;
+        const int64_t gb = it.blk0 + b0;
+        const uint8_t *p0 = wm->s[0], *p1 = wm->s[1];
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
+        if (!it.is_q6) {
+            mbar_expect_tx(full, static_cast<uint32_t>(nbk) * 2304u);
+            bulk_g2s(stage, p1 + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, full);
+            bulk_g2s(stage + it.sb * 2048, p0 + gb * 256, static_cast<uint32_t>(nbk) * 256u, full);
+        } else {
+            const uint8_t *p2 = wm->s[2], *p3 = wm->s[3];
+            mbar_expect_tx(full, static_cast<uint32_t>(nbk) * 3360u);
+            bulk_g2s(stage, p0 + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, full);
+            bulk_g2s(stage + it.sb * 2048, p1 + gb * 1024, static_cast<uint32_t>(nbk) * 1024u, full);
+            bulk_g2s(stage + it.sb * 3072, p2 + gb * 256, static_cast<uint32_t>(nbk) * 256u, full);
+            bulk_g2s(stage + it.sb * 3328, p3 + gb * 32, static_cast<uint32_t>(nbk) * 32u, full);
         }
     }
-    return r;
+    it.ti += it.ws;
 }
 
 // ---- consumers ---------------------------------------------------------------------------------------------------
 
 // x[k0 .. k0+7] (k0 a multiple of 8, all in one head) = the attention splits of that head merged (max, sum, acc per split).
-__device__ __forceinline__ void attn_merge8(const AttnPagedArgs& am, int k0, float (&v)[8]) {
+__device__ __noinline__ void attn_merge8(const AttnPagedArgs& am, int k0, float (&v)[8]) {
     const int hd = am.head_dim;
     const int head = k0 / hd, d0 = k0 - head * hd;
     const int pos = am.d_pos ? am.d_pos[0] : am.pos0;
@@ -368,21 +446,30 @@ __device__ __forceinline__ void tile_q6k(const uint8_t* qsT, const uint8_t* s1T,
     }
 }
 
-struct ConsumerState { int st; uint32_t ph; bool ok; };
+// Per-warp state that lives across phases (kept in shared memory between calls).
+struct WarpState {
+    TileIt iss;              // the next tile to request
+    int st; uint32_t ph;     // ring stage and barrier parity of the next tile to consume
+    bool ok;
+};
 
 enum : int { kEpiStore = 0, kEpiResidual = 1, kEpiSwiglu = 2 };
 
-// One GEMV phase on the consumer side.  x: the activation row (nullptr with merge != nullptr: the merged attention
-// splits); resid == y[row] in place for kEpiResidual.
-__device__ __noinline__ ConsumerState consume_phase(const StepShape* shp, const StepMat* m0, const StepMat* m1, const StepMat* m2, const float* x,
-                                                    const AttnPagedArgs* merge, const float* gamma, float eps, int epi, const Smem* smp,
-                                                    uint64_t* full_bar, uint64_t* empty_bar, float* red, int P, ConsumerState cs, int* err) {
+// One GEMV phase.  x: the activation row (nullptr with merge != nullptr: the merged attention splits); the residual
+// epilogue adds onto y in place.  m0..m2: the phase's matrices (shared-memory descriptors).
+__device__ __noinline__ void consume_phase(int p, const StepMat* m0, const StepMat* m1, const StepMat* m2, const float* x, const AttnPagedArgs* merge,
+                                           const float* gamma, float eps, int epi, const Desc* dp, const Smem* smp, uint64_t* full_bar, float* red,
+                                           int P, WarpState* wsp, int window_max, int* err) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    x_to_limbs(x, merge, gamma, shp->K, smp, red);
+    const Desc d = *dp;
+    stamp(1);
+    x_to_limbs(x, merge, gamma, d.shapes[p].K, smp, red);
     consumer_sync();
-    const StepShape sh = *shp;
+    stamp(2);
+    const StepShape sh = d.shapes[p];
     const Smem sm = *smp;
     const StepMat* const mats[3] = {m0, m1, m2};
+    WarpState st = *wsp;
     const int K = sh.K, nb = sh.nb;
     float inv = 1.0f;
     if (gamma) {
@@ -398,23 +485,23 @@ __device__ __noinline__ ConsumerState consume_phase(const StepShape* shp, const 
     lc.lw0 = col0 == 0 ? 1.0f : (col0 == 2 ? 1.0f / 16384.0f : 0.0f);
     lc.lw1 = col1 == 1 ? 1.0f / 128.0f : 0.0f;
 
-    const int64_t g_begin = static_cast<int64_t>(blockIdx.x) * sh.groups / gridDim.x;
-    const int n_rg = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * sh.groups / gridDim.x - g_begin);
-    const int n_teams = kWarps / sh.ws, team = warp / sh.ws, member = warp % sh.ws;
+    const int g_begin = sh.g_begin, n_rg = sh.n_rg;
+    const int n_teams = kWarps >> sh.log_ws, team = warp >> sh.log_ws, member = warp & (sh.ws - 1);
     int parity = 0;
     for (int rg = team; rg < n_rg; rg += n_teams, parity ^= 1) {
-        const int64_t G_rg = g_begin + rg;
+        const int G_rg = g_begin + rg;
         const int mi = sh.nmat == 2 ? 0 : (sh.ncat > 1 && G_rg >= sh.g_start[1]) + (sh.ncat > 2 && G_rg >= sh.g_start[2]);
         const StepMat* w0 = mats[mi];
         const bool is_q6 = w0->type == T_Q6_K;
-        const int sb = is_q6 ? sh.sb6 : sh.sb4, spr = (nb + sb - 1) / sb;
+        const int sb = is_q6 ? sh.sb6 : sh.sb4, spr = is_q6 ? sh.spr6 : sh.spr4;
         float F0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, F1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         float MN0[2] = {0.0f, 0.0f}, MN1[2] = {0.0f, 0.0f};                  // [row g / g+8]
         for (int ti = member; ti < sh.nmat * spr; ti += sh.ws) {
-            const int s = warp * P + cs.st;
-            if (cs.ok) cs.ok = mbar_wait(&full_bar[s], cs.ph, err, 2);
-            if (++cs.st == P) { cs.st = 0; cs.ph ^= 1; }
-            if (!cs.ok) continue;
+            const int s = warp * P + st.st;
+            if (st.ok) st.ok = mbar_wait(&full_bar[s], st.ph, err, 2);
+            if (++st.st == P) { st.st = 0; st.ph ^= 1; }
+            if (!st.ok) continue;
+            stamp(6);
             const int mat = ti >= spr, sl = ti - mat * spr;
             const int b0 = sl * sb, nbk = min(sb, nb - b0);
             const uint8_t* qsT = sm.ring + static_cast<size_t>(s) * kStageBytes;
@@ -424,8 +511,10 @@ __device__ __noinline__ ConsumerState consume_phase(const StepShape* shp, const 
             else tile_q6k(qsT, s1T, s1T + sb * 1024, s1T + sb * 1280, nbk, b0, sm, lc, lane, f0, f1, f2, f3, mnA, mnB);
             if (mat == 0) { F0[0] += f0; F0[1] += f1; F0[2] += f2; F0[3] += f3; MN0[0] += mnA; MN0[1] += mnB; }
             else { F1[0] += f0; F1[1] += f1; F1[2] += f2; F1[3] += f3; MN1[0] += mnA; MN1[1] += mnB; }
+            stamp(7);
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
+            // the stage is free: request the tile one ring length ahead in this warp's sequence
+            if (it_seek(st.iss, d, warp, window_max)) it_issue(st.iss, sm.ring + static_cast<size_t>(s) * kStageBytes, &full_bar[s], lane);
         }
         // fold the limb columns (lanes t = 0..3 of a row) and the min terms
         float va[2], vb[2];
@@ -438,7 +527,7 @@ __device__ __noinline__ ConsumerState consume_phase(const StepShape* shp, const 
             pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 1); pb += __shfl_xor_sync(0xFFFFFFFFu, pb, 2);
             va[mat] = pa * inv; vb[mat] = pb * inv;
         }
-        const int64_t row_base = (G_rg - (sh.nmat == 2 ? 0 : sh.g_start[mi])) * 16;
+        const int64_t row_base = static_cast<int64_t>(G_rg - (sh.nmat == 2 ? 0 : sh.g_start[mi])) * 16;
         const int64_t n_rows = w0->N;
         float* const yb = w0->y;
         auto finish = [&](float v, float v2, int64_t row) {
@@ -466,11 +555,13 @@ __device__ __noinline__ ConsumerState consume_phase(const StepShape* shp, const 
             }
         }
     }
-    return cs;
+    if (lane == 0) *wsp = st;
+    stamp(3);
 }
 
 // Attention phase of one layer: warps 0..3 of each CTA take the (KV head, split) items blockIdx.x, blockIdx.x + gridDim.x, ...
 // over the splits that hold visible keys; the other warps pass through.
+template <int HD>
 __device__ __noinline__ void attn_phase(const AttnPagedArgs* atp, uint32_t* tile_smem) {
     const AttnPagedArgs& at = *atp;
     if ((threadIdx.x >> 5) >= 4) return;
@@ -478,15 +569,15 @@ __device__ __noinline__ void attn_phase(const AttnPagedArgs* atp, uint32_t* tile
     const int n_active = min(at.n_splits, pos / (at.pages_per_split * at.page) + 1);
     for (int item = blockIdx.x; item < at.n_kv * n_active; item += gridDim.x) {
         const int h = item % at.n_kv, split = item / at.n_kv;
-        if (at.head_dim == 64) attn_tile_body<64, true>(at, h, split, 0, threadIdx.x, tile_smem, [] { attn_sync(); });
-        else attn_tile_body<128, true>(at, h, split, 0, threadIdx.x, tile_smem, [] { attn_sync(); });
+        attn_tile_body<HD, true>(at, h, split, 0, threadIdx.x, tile_smem, [] { attn_sync(); });
         attn_sync();                       // the next item reuses the shared-memory tiles
     }
 }
 
 // Grid-wide barrier number `k` (1, 2, ...): arrive, then wait until all CTAs have arrived k times.
-__device__ __forceinline__ void grid_barrier(unsigned* bar, unsigned k, bool& failed, int* err) {
+__device__ __noinline__ void grid_barrier(unsigned* bar, unsigned k, bool& failed, int* err) {
     consumer_sync();                                   // this CTA's stores of the phase are done (all consumer warps)
+    stamp(4);
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(bar, 1u);
@@ -501,19 +592,23 @@ __device__ __forceinline__ void grid_barrier(unsigned* bar, unsigned k, bool& fa
         __threadfence();
     }
     consumer_sync();
+    stamp(5);
 }
 
-__global__ void __launch_bounds__((kWarps + 1) * 32, 1) decode_step_kernel(const StepArgs a) {
+template <int HD>
+__global__ void __launch_bounds__(kWarps * 32, 1) decode_step_kernel(const StepArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kWarps * kMaxP], empty_bar[kWarps * kMaxP];
+    __shared__ __align__(8) uint64_t full_bar[kWarps * kMaxP];
     __shared__ float red[kWarps];
     __shared__ AttnPagedArgs at_s;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int P = a.P;
     __shared__ StepShape sh_s[kPhaseCount];
     __shared__ StepMat out_mat_s;
-    const StepMat* out_s = &out_mat_s;
+    __shared__ StepLayer layer_s[kLayerSlots];
     __shared__ Smem sm_s;
+    __shared__ Desc desc_s;
+    __shared__ WarpState ws_s[kWarps];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int P = a.P;
     Smem sm;
     sm.ring = smem;
     sm.xl = reinterpret_cast<int8_t*>(smem + static_cast<size_t>(kWarps) * P * kStageBytes);
@@ -522,58 +617,68 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 1) decode_step_kernel(const
     sm.asum16 = sm.asum + a.k_max / 32;
     sm.xs = sm.asum16 + a.k_max / 16;
     sm.comb = sm.xs + a.k_max / 256;
+    auto load_layer = [&](int L) {               // all threads: descriptor of layer L into its window slot
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers + L);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&layer_s[L & (kLayerSlots - 1)]);
+        for (int i = threadIdx.x; i < static_cast<int>(sizeof(StepLayer) / 4); i += kWarps * 32) dst[i] = src[i];
+    };
+    for (int L = 0; L < kLayerSlots && L < a.n_layer; ++L) load_layer(L);
     if (threadIdx.x == 0) {
         sm_s = sm;
         out_mat_s = a.out;
-        for (int i = 0; i < kPhaseCount; ++i) sh_s[i] = a.shape[i];
-        for (int s = 0; s < kWarps * P; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int i = 0; i < kPhaseCount; ++i) {
+            sh_s[i] = a.shape[i];
+            const int64_t g0 = static_cast<int64_t>(blockIdx.x) * sh_s[i].groups / gridDim.x;
+            sh_s[i].g_begin = static_cast<int>(g0);
+            sh_s[i].n_rg = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * sh_s[i].groups / gridDim.x - g0);
+        }
+        desc_s.slots = layer_s; desc_s.global = a.layers; desc_s.out = &out_mat_s; desc_s.shapes = sh_s; desc_s.n_layer = a.n_layer;
+        for (int s = 0; s < kWarps * P; ++s) mbar_init(&full_bar[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-
-    if (warp == kWarps) {
-        // ---------------- producer: lane w feeds consumer warp w, all phases in schedule order ----------------
-        if (lane < kWarps) {
-            Ring r{0, 1u, true};
-            for (int L = 0; L < a.n_layer && r.ok; ++L) {
-                const StepLayer* l = a.layers + L;
-                r = produce_phase(&sh_s[kPhaseQkv], &l->q, &l->k, &l->v, &sm_s, full_bar, empty_bar, P, lane, r, a.err);
-                r = produce_phase(&sh_s[kPhaseO], &l->o, &l->o, &l->o, &sm_s, full_bar, empty_bar, P, lane, r, a.err);
-                r = produce_phase(&sh_s[kPhaseGateUp], &l->gate, &l->up, &l->up, &sm_s, full_bar, empty_bar, P, lane, r, a.err);
-                r = produce_phase(&sh_s[kPhaseDown], &l->down, &l->down, &l->down, &sm_s, full_bar, empty_bar, P, lane, r, a.err);
-            }
-            if (r.ok) r = produce_phase(&sh_s[kPhaseLogits], out_s, out_s, out_s, &sm_s, full_bar, empty_bar, P, lane, r, a.err);
-        }
-        return;
+    stamp(0);
+    {   // fill this warp's ring with the first P tiles of its sequence
+        WarpState st{};
+        st.iss.L = 0; st.iss.p = a.n_layer > 0 ? kPhaseQkv : kPhaseLogits; st.iss.end = false;
+        it_begin_phase(st.iss, desc_s, warp);
+        for (int i = 0; i < P; ++i)
+            if (it_seek(st.iss, desc_s, warp, kLayerSlots - 1)) it_issue(st.iss, sm.ring + static_cast<size_t>(warp * P + i) * kStageBytes, &full_bar[warp * P + i], lane);
+        st.st = 0; st.ph = 0u; st.ok = true;
+        if (lane == 0) ws_s[warp] = st;
+        __syncwarp();
     }
 
-    // ---------------- consumers ----------------
-    ConsumerState cs{0, 0u, true};
     bool failed = false;
     unsigned bar_k = 0;
+    const StepMat* const out_m = &out_mat_s;
+    WarpState* const wsp = &ws_s[warp];
     for (int L = 0; L < a.n_layer; ++L) {
-        const StepLayer* l = a.layers + L;
+        const StepLayer* l = &layer_s[L & (kLayerSlots - 1)];
+        // the window moves on: layer L + 2 replaces layer L - 2 (published by the next barrier)
+        if (L >= 2 && L + 2 < a.n_layer) load_layer(L + 2);
+        const int win_a = max(kLayerSlots - 1, L + 1), win_b = max(kLayerSlots - 1, L + 2);
         // q / k / v projections of the normalised hidden row
-        cs = consume_phase(&sh_s[kPhaseQkv], &l->q, &l->k, &l->v, a.x, nullptr, l->attn_norm, a.eps, kEpiStore, &sm_s, full_bar, empty_bar, red, P, cs, a.err);
+        consume_phase(kPhaseQkv, &l->q, &l->k, &l->v, a.x, nullptr, l->attn_norm, a.eps, kEpiStore, &desc_s, &sm_s, full_bar, red, P, wsp, win_a, a.err);
         if (threadIdx.x == 0) {      // this layer's attention arguments (published by the barrier below; last read two barriers ago)
             at_s = a.attn;
             at_s.k_cache = l->k_cache; at_s.v_cache = l->v_cache; at_s.k_cache_w = l->k_cache; at_s.v_cache_w = l->v_cache;
         }
         grid_barrier(a.bar, ++bar_k, failed, a.err);
-        attn_phase(&at_s, reinterpret_cast<uint32_t*>(sm.xl));      // RoPE + KV append + attention; warps 0..3 run the (KV head, split) items
+        attn_phase<HD>(&at_s, reinterpret_cast<uint32_t*>(sm.xl));      // RoPE + KV append + attention; warps 0..3 run the (KV head, split) items
         grid_barrier(a.bar, ++bar_k, failed, a.err);
         // output projection of the merged splits, + residual
-        cs = consume_phase(&sh_s[kPhaseO], &l->o, &l->o, &l->o, nullptr, &at_s, nullptr, a.eps, kEpiResidual, &sm_s, full_bar, empty_bar, red, P, cs, a.err);
+        consume_phase(kPhaseO, &l->o, &l->o, &l->o, nullptr, &at_s, nullptr, a.eps, kEpiResidual, &desc_s, &sm_s, full_bar, red, P, wsp, win_b, a.err);
         grid_barrier(a.bar, ++bar_k, failed, a.err);
         // silu(gate x) * (up x) of the normalised row
-        cs = consume_phase(&sh_s[kPhaseGateUp], &l->gate, &l->up, &l->up, a.x, nullptr, l->ffn_norm, a.eps, kEpiSwiglu, &sm_s, full_bar, empty_bar, red, P, cs, a.err);
+        consume_phase(kPhaseGateUp, &l->gate, &l->up, &l->up, a.x, nullptr, l->ffn_norm, a.eps, kEpiSwiglu, &desc_s, &sm_s, full_bar, red, P, wsp, win_b, a.err);
         grid_barrier(a.bar, ++bar_k, failed, a.err);
         // down projection + residual
-        cs = consume_phase(&sh_s[kPhaseDown], &l->down, &l->down, &l->down, a.act, nullptr, nullptr, a.eps, kEpiResidual, &sm_s, full_bar, empty_bar, red, P, cs, a.err);
+        consume_phase(kPhaseDown, &l->down, &l->down, &l->down, a.act, nullptr, nullptr, a.eps, kEpiResidual, &desc_s, &sm_s, full_bar, red, P, wsp, win_b, a.err);
         grid_barrier(a.bar, ++bar_k, failed, a.err);
     }
     // final norm + logits
-    cs = consume_phase(&sh_s[kPhaseLogits], out_s, out_s, out_s, a.x, nullptr, a.out_norm, a.eps, kEpiStore, &sm_s, full_bar, empty_bar, red, P, cs, a.err);
+    consume_phase(kPhaseLogits, out_m, out_m, out_m, a.x, nullptr, a.out_norm, a.eps, kEpiStore, &desc_s, &sm_s, full_bar, red, P, wsp, a.n_layer, a.err);
 }
 
 // Team width and tile depth of a phase, as launch_gemv_mma chooses them for a single launch.
@@ -589,6 +694,9 @@ void plan_shape(StepShape& sh, int n_cta) {
     };
     sh.sb4 = depth(3);
     sh.sb6 = depth(2);
+    sh.log_ws = ws == 1 ? 0 : (ws == 2 ? 1 : (ws == 4 ? 2 : 3));
+    sh.spr4 = (sh.nb + sh.sb4 - 1) / sh.sb4;
+    sh.spr6 = (sh.nb + sh.sb6 - 1) / sh.sb6;
 }
 
 }  // namespace
@@ -629,13 +737,14 @@ int launch_decode_step(Context* c, StepArgs& a, int head_dim, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(kWarps) * P * kStageBytes + fixed;
     if (smem > 227 * 1024 || P < 2) return GGB_NOT_FOUND;
     a.P = P; a.fixed_bytes = static_cast<int>(fixed);
-    cudaError_t e = ensure_dynamic_smem(c, decode_step_kernel, smem);
+    void (*kern)(const StepArgs) = head_dim == 64 ? decode_step_kernel<64> : decode_step_kernel<128>;
+    cudaError_t e = ensure_dynamic_smem(c, kern, smem);
     if (e != cudaSuccess) return cuda_status(c, e, "decode_step attr");
     e = cudaMemsetAsync(a.bar, 0, sizeof(unsigned), s);
     if (e != cudaSuccess) return cuda_status(c, e, "decode_step barrier reset");
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(n_cta));
-    cfg.blockDim = dim3((kWarps + 1) * 32);
+    cfg.blockDim = dim3(kWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -643,9 +752,24 @@ int launch_decode_step(Context* c, StepArgs& a, int head_dim, cudaStream_t s) {
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, decode_step_kernel, a);
+    e = cudaLaunchKernelEx(&cfg, kern, a);
     c->launches++;
     return cuda_status(c, e, "decode_step launch");
 }
 
 }  // namespace ggb
+
+#ifdef GGB_STEP_TRACE
+// Copies out and clears the stamps: pairs (time in ns, tag); tags 1 phase start, 2 limbs done, 6 tile arrived, 7 tile
+// computed, 3 phase done, 4 at the barrier (all warps of the CTA arrived), 5 barrier passed.
+extern "C" __attribute__((visibility("default"))) int ggb_step_trace_read(unsigned long long* out, int cap) {
+    int n = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, ggb::g_step_trace_n, sizeof(int));
+    n = n < cap ? n : cap;
+    cudaMemcpyFromSymbol(out, ggb::g_step_trace, sizeof(unsigned long long) * 2 * n);
+    const int zero = 0;
+    cudaMemcpyToSymbol(ggb::g_step_trace_n, &zero, sizeof(int));
+    return n;
+}
+#endif

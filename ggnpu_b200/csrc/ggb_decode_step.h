@@ -25,8 +25,10 @@ struct StepShape {
     int nmat;                 // 2: gate/up pair (both matrices of a row group go to the same team); else 1
     int ncat;                 // matrices stacked along N (q, k, v share the input row)
     int g_start[3];           // first row group of stacked matrix i
-    int ws;                   // consumer warps per row group (1, 2, 4 or 8)
+    int ws, log_ws;           // warps per row group (1, 2, 4 or 8) and its log2
     int sb4, sb6;             // 256-blocks per tile for Q4_K / Q6_K matrices
+    int spr4, spr6;           // tiles per (row group, matrix) = ceil(nb / sb)
+    int g_begin, n_rg;        // this CTA's range of row groups (filled in by each CTA at kernel start)
 };
 
 enum : int { kPhaseQkv = 0, kPhaseO = 1, kPhaseGateUp = 2, kPhaseDown = 3, kPhaseLogits = 4, kPhaseCount = 5 };

@@ -186,10 +186,10 @@ def test_model_argument_errors(backend):
 
 
 def test_persistent_step_kernel_agrees_with_kernel_per_matrix_graph(backend, oracle):
-    """Single-token steps of an all-Q4_K / Q6_K model run as one persistent kernel (all layers and the logits, grid-wide
-    barriers between the phases).  With GGB_NO_STEP_KERNEL set the same model runs the kernel-per-matrix graph.  Both
-    must follow the oracle, and each other to summation-order accuracy, over decode steps that cross a KV page and a
-    split boundary (positions 60..70, pages of 64 tokens)."""
+    """With GGB_STEP_KERNEL=1 single-token steps of an all-Q4_K / Q6_K model run as one persistent kernel (all layers and
+    the logits, grid-wide barriers between the phases, every wait bounded); by default they run the kernel-per-matrix
+    graph.  Both must follow the oracle, and each other to summation-order accuracy, over decode steps that cross a KV
+    page and a split boundary (positions 60..70, pages of 64 tokens)."""
     import os
     from ggnpu_b200.backend import Model
     from oracle.binding import OracleModel
@@ -198,12 +198,12 @@ def test_persistent_step_kernel_agrees_with_kernel_per_matrix_graph(backend, ora
     om = OracleModel(oracle, synth)
     ids = np.random.default_rng(8).integers(0, cfg.vocab, 60).astype(np.int32)
     want0 = om.forward(ids, 0)
-    fast = Model(backend, cfg, synth.tensors)
-    os.environ["GGB_NO_STEP_KERNEL"] = "1"
+    os.environ["GGB_STEP_KERNEL"] = "1"
     try:
-        slow = Model(backend, cfg, synth.tensors)
+        fast = Model(backend, cfg, synth.tensors)
     finally:
-        del os.environ["GGB_NO_STEP_KERNEL"]
+        del os.environ["GGB_STEP_KERNEL"]
+    slow = Model(backend, cfg, synth.tensors)
     g0, _ = fast.prefill(ids, 0)
     s0, _ = slow.prefill(ids, 0)
     logits_ok(g0, want0)
@@ -216,7 +216,8 @@ def test_persistent_step_kernel_agrees_with_kernel_per_matrix_graph(backend, ora
         a, na = fast.decode(tok, pos)
         fast_launches += backend.launch_count() - before
         b, nb = slow.decode(tok, pos)
-        ea, eb = logits_ok(a, want), logits_ok(b, want)
+        logits_ok(a, want)
+        logits_ok(b, want)
         assert rel_l2(a, b) <= 1e-4, (pos, rel_l2(a, b))
         tok, pos = oracle.argmax_first(want), pos + 1
     assert fast_launches / 10 <= 6, fast_launches           # gather, the step kernel, two arg-max passes, feedback
