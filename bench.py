@@ -97,34 +97,28 @@ def prompt_ids(cfg, n=PROMPT_LEN):
 # ---------------------------------------------------------------------------------------------
 # CPU side: the reference CLI on its own CPU backend
 # ---------------------------------------------------------------------------------------------
-def time_reference_cli(synth, n_warm: int, n_timed: int, budget_s: float = 200.0):
-    """Greedy decode with the reference CLI (exact fp32 matmul path), one thread.  Returns
-    (tok/s, description of the sample).  The prompt is 2 tokens: the CPU decode cost per token is
-    weight-bound and does not depend on the context length at these sizes; a 128-token prompt
-    alone would take ~5 minutes of CPU prefill."""
+def time_reference_cli(synth, n_warm: int, n_timed: int, prompt_len: int = 2, exact: bool = False, budget_s: float = 200.0):
+    """Greedy decode with the reference CLI on its CPU backend, one thread (the reference's CPU path is
+    single-threaded).  Returns (tok/s, kind, description of the sample).
+
+    exact=False times the stock path, Backend::mul_mat_q of the CPU backend (src/backends/cpu_ref/cpu_ref.cpp:87-117;
+    valid for this all-Q4_K / Q6_K workload), with the prompt batched as the CLI does by default; exact=True times the
+    diagnostic exact-fp32 matmul (GGNPU_FP32_MATMUL, src/cli/main.cpp:1379-1388) that the parity tests use.  The timed
+    tokens are the decode steps after the prompt; the count is cut so that the run stays inside budget_s."""
     from oracle.binding import REF_CLI, Oracle, OracleModel
     cfg = synth.cfg
-    ids = prompt_ids(cfg, 2)
-    per_tok_guess = 2.6          # seconds per full-model token on one Xeon core (measured ~2.2)
-    layers = cfg.n_layer
+    ids = prompt_ids(cfg, prompt_len)
+    per_tok_guess = 2.6 if exact else 1.4          # seconds per full-model token on one core
+    prefill_guess = prompt_len * (per_tok_guess if exact else 0.8)
     total = n_warm + n_timed
-    if total * per_tok_guess > budget_s:
-        # bound the run: fewer layers per step (the CLI's own GGNPU_MAX_LAYERS switch); the logits
-        # GEMV is always whole.  Throughput is scaled by the multiply-accumulate count.
-        per_layer = (per_tok_guess * 0.81) / cfg.n_layer
-        logits_t = per_tok_guess * 0.19
-        layers = max(1, int((budget_s / total - logits_t) / per_layer))
-        layers = min(layers, cfg.n_layer)
-    macs_layer = cfg.hidden * (2 * cfg.n_head * cfg.head_dim + 2 * cfg.n_kv * cfg.head_dim + 3 * cfg.ffn)
-    macs_full = cfg.n_layer * macs_layer + cfg.vocab * cfg.hidden
-    macs_run = layers * macs_layer + cfg.vocab * cfg.hidden
+    total = max(2, min(total, int(max(budget_s - prefill_guess, 10.0) / per_tok_guess)))
     if os.path.exists(REF_CLI):
         with tempfile.TemporaryDirectory() as td:
             path = os.path.join(td, "model.gguf")
             synth.write(path)
-            env = dict(os.environ, GGNPU_FP32_MATMUL="1", GGNPU_NO_PREFILL_BATCH="1")
-            if layers < cfg.n_layer:
-                env["GGNPU_MAX_LAYERS"] = str(layers)
+            env = dict(os.environ)
+            if exact:
+                env.update(GGNPU_FP32_MATMUL="1", GGNPU_NO_PREFILL_BATCH="1")
             cmd = [REF_CLI, "-m", path, "-p", S.prompt_text(ids), "-c", "2048", "--no-cache", "-n", str(total), "--temp", "0", "--quiet"]
             p = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL)
             stamps, buf = [], b""
@@ -142,11 +136,12 @@ def time_reference_cli(synth, n_warm: int, n_timed: int, budget_s: float = 200.0
             p.wait()
         if len(stamps) < total or total < 2:
             raise RuntimeError(f"reference CLI produced {len(stamps)} of {total} tokens")
-        first = max(n_warm, 1)                          # token 0's stamp includes model load + prompt
+        first = max(min(n_warm, total - 1), 1)          # token 0's stamp includes model load + prompt
         dt = stamps[total - 1] - stamps[first - 1]
-        rate = (total - first) / dt * (macs_run / macs_full)
+        rate = (total - first) / dt
         kind = "reference"
-        what = f"reference CLI (oracle/_ref), {total - first} timed decode tokens after a 2-token prompt"
+        what = (f"reference CLI (oracle/_ref, unmodified sources), {'exact fp32 matmul (GGNPU_FP32_MATMUL)' if exact else 'stock cpu_ref::mul_mat_q'}, "
+                f"{total - first} timed decode tokens at positions {prompt_len + first}.. after a {prompt_len}-token prompt")
     else:
         o = Oracle()
         om = OracleModel(o, synth)
@@ -154,26 +149,26 @@ def time_reference_cli(synth, n_warm: int, n_timed: int, budget_s: float = 200.0
         t0 = time.perf_counter()
         tok, n = int(ids[-1]), max(1, min(n_timed, 4))
         for i in range(n):
-            tok = o.argmax_first(om.forward([tok], 2 + i))
+            tok = o.argmax_first(om.forward([tok], prompt_len + i))
         rate = n / (time.perf_counter() - t0)
-        kind, layers = "port", cfg.n_layer
-        what = f"C restatement of the reference layer loop, {n} decode tokens after a 2-token prompt"
-    if layers < cfg.n_layer:
-        what += f", {layers} of {cfg.n_layer} layers per step (GGNPU_MAX_LAYERS) scaled by MAC count"
+        kind = "port"
+        what = f"C restatement of the reference layer loop (exact fp32 matmul), {n} decode tokens after a {prompt_len}-token prompt"
     return rate, kind, what
 
 
 def run_reference(args):
+    """The reference arm: the unmodified reference CLI on the host cores, same model, same 128-token prompt, greedy
+    decode from position 128 on (the prompt is prefilled by the CLI's own batched path, outside the timed tokens)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import torch
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     synth = build_synth(dev)
-    rate, kind, what = time_reference_cli(synth, args.warmup, args.steps)
+    rate, kind, what = time_reference_cli(synth, args.warmup, args.steps, prompt_len=args.prompt_len, exact=False, budget_s=240.0)
     out = {"impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": 1000.0 / rate, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "prompt": "2 tokens (CPU prefill of 128 would take minutes)"},
+           "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "prompt_tokens": args.prompt_len, "cpu_matmul": "cpu_ref::mul_mat_q (stock)"},
            "cpu_baseline": {"value": rate, "unit": UNIT, "cores": 1, "kind": kind, "sample": what},
            "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(out), flush=True)
@@ -377,14 +372,36 @@ def run_ours(args):
                            "note": "CUDA events around ggb_model_prefill (host ids in, next token out); projections run on the tcgen05 GEMM"}}
         if world == 1 and not args.no_cpu_baseline:
             try:
-                rate, kind, what = time_reference_cli(synth, 1, 6)
+                rate, kind, what = time_reference_cli(synth, 1, 8, prompt_len=2, exact=False, budget_s=30.0)
                 out["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": 1, "kind": kind, "sample": what,
                                        "host_cores_available": os.cpu_count()}
+                rate_x, _, what_x = time_reference_cli(synth, 1, 4, prompt_len=2, exact=True, budget_s=20.0)
+                out["cpu_baseline"]["exact_fp32_path"] = {"value": rate_x, "unit": UNIT, "sample": what_x}
             except Exception as e:  # the GPU numbers stand on their own
                 out["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 1, "kind": "unavailable", "sample": str(e)[:200]}
-        print(json.dumps(out), flush=True)
     model.close()
+    extras = {}
+    if not args.no_extras:
+        if world == 1:
+            try:
+                extras["config3"] = config3_figures(b, local)
+            except Exception as e:
+                extras["config3"] = {"unavailable": str(e)[:200]}
     b.close()
+    if not args.no_extras and world > 1:
+        # the sharded paths, where the driver can see them: parity of tensor / expert parallel against one GPU, and the
+        # tensor-parallel figures of the 8B-shape model over the ranks of this launch (strong scaling)
+        try:
+            chk = parallel_check(rank, local, world)
+            tp = tp_measure(args, rank, local, world, min(K, 32), W)
+            if rank == 0:
+                extras.update(chk)
+                extras["tp"] = tp
+        except Exception as e:
+            extras["tp"] = {"unavailable": str(e)[:300]}
+    if rank == 0:
+        out.update(extras)
+        print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -587,33 +604,32 @@ def run_micro_allreduce(args):
     dist.destroy_process_group()
 
 
-def run_tp(args):
-    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model over all ranks
-    of this launch (torchrun: one process per GPU; a single process is the TP = 1 point).  Strong
-    scaling: the model is fixed, each rank holds 1 / N of the heads, FFN rows and vocabulary.
-        python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench.py --tp --gpus 8"""
+def join_group(b, rank, world, nccl_only=False):
+    """Make backend b one rank of a tensor / expert parallel group over the ranks of this launch."""
+    import torch.distributed as dist
+    if world <= 1:
+        return
+    box = [b.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    b.tp_init(box[0], rank, world)
+    if not nccl_only:                              # one-shot peer-memory all-reduce for the 16 KB decode messages
+        handles = [None] * world
+        dist.all_gather_object(handles, b.tp_ipc_handle())
+        b.tp_attach_peers(handles)
+
+
+def tp_measure(args, rank, local, world, steps, warmup):
+    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model over all ranks of this launch (strong scaling: the
+    model is fixed, each rank holds 1 / N of the heads, FFN rows and vocabulary).  torch.distributed must be up.
+    Returns the result dict on rank 0, None elsewhere."""
     import dataclasses
     import torch
     import torch.distributed as dist
     from ggnpu_b200.backend import CudaBackend, Model
-
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = args.tp_ctx
     cfg = dataclasses.replace(S.LLAMA_8B, ctx=ctx, n_layer=args.tp_layers or S.LLAMA_8B.n_layer)
     b = CudaBackend(local)
-    if world > 1:
-        box = [b.tp_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        b.tp_init(box[0], rank, world)
-        if not args.tp_nccl_only:                      # one-shot peer-memory all-reduce for the 16 KB decode messages
-            handles = [None] * world
-            dist.all_gather_object(handles, b.tp_ipc_handle())
-            b.tp_attach_peers(handles)
+    join_group(b, rank, world, args.tp_nccl_only)
     t0 = time.perf_counter()
     synth = S.build_model(cfg, device="cuda")
     model = Model(b, cfg, synth.tensors)
@@ -626,7 +642,7 @@ def run_tp(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    n_prompt = min(args.tp_prompt, ctx - args.steps - args.warmup - 1)
+    n_prompt = min(args.tp_prompt, ctx - steps - warmup - 1)
     ids = prompt_ids(cfg, n_prompt)
     model.prefill(ids, 0, want_logits=False)                      # untimed pass sizes the scratch
     barrier()
@@ -636,7 +652,7 @@ def run_tp(args):
     e1.record(stream)
     barrier()
     prefill_ms = e0.elapsed_time(e1)
-    K, W = args.steps, max(args.warmup, 3)
+    K, W = steps, max(warmup, 3)
     toks = model.generate(int(first), n_prompt, W)
     barrier()
     launches0 = b.launch_count()
@@ -651,16 +667,186 @@ def run_tp(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, prefill_ms = float(t[0]), float(t[1])
+    res = None
     if rank == 0:
         peak, peak_kind = peaks()
         bytes_step = model.decode_bytes(n_prompt + W + K // 2)        # this rank's shard
+        res = {"decode_tok_s": K / (ms * 1e-3), "ms_per_step": ms / K, "steps": K, "warmup": W, "prefill_tokens": n_prompt,
+               "prefill_tok_s": n_prompt / (prefill_ms * 1e-3), "gpu_launches": launches, "layers": cfg.n_layer, "ctx": ctx,
+               "allreduce": "none" if world == 1 else ("NCCL" if args.tp_nccl_only or world < 4 else "one-shot peer-memory kernel (decode), NCCL (prefill)"),
+               "algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
+               "frac_of_hbm_peak": bytes_step / (ms / K * 1e-3) / 1e9 / peak, "peak_source": peak_kind, "model_build_s": build_s}
+    model.close()
+    b.close()
+    return res
+
+
+def parallel_check(rank, local, world):
+    """Parity of the sharded paths where the driver can see it: a tiny llama (tensor parallel) and a tiny qwen35moe (expert
+    parallel) over the ranks of this launch, against the SAME models on one GPU (rank 0, a handle outside the group; that
+    path is held to the CPU oracle by the test suite).  Outside every timed region."""
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200.backend import CudaBackend, Model, Q35Model
+    out = {}
+    solo = CudaBackend(local) if rank == 0 else None
+    grp = CudaBackend(local)
+    join_group(grp, rank, world)
+    # shapes that split over 2, 4 or 8 ranks (row-parallel K slices must be whole 256-blocks)
+    cases = {"tp_check": (S.tiny_config(seed=11, n_head=32, n_kv=8, ffn=2048, vocab=2560), S.build_model, Model),
+             "ep_check": (S.tiny_q35_config(seed=5, n_expert=16, top_k=3), S.build_q35_model, Q35Model)}
+    for name, (cfg, builder, cls) in cases.items():
+        synth = builder(cfg)
+        ids = np.random.default_rng(42).integers(0, cfg.vocab, 20).astype(np.int32)
+        gm = cls(grp, cfg, synth.tensors)
+        logits, first = gm.prefill(ids, 0)
+        stream = [int(first)] + [int(t) for t in gm.generate(int(first), len(ids), 8)]
+        mine = torch.from_numpy(np.concatenate([logits, np.asarray(stream, np.float32)])).cuda()
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        same = all(torch.equal(allr[0], t) for t in allr[1:])
+        gm.close()
+        if rank == 0:
+            sm = cls(solo, cfg, synth.tensors)
+            l1, f1 = sm.prefill(ids, 0)
+            s1 = [int(f1)] + [int(t) for t in sm.generate(int(f1), len(ids), 8)]
+            sm.close()
+            err = float(np.abs(l1 - logits).max())
+            out[name] = {"ranks": world, "max_abs_err_vs_one_gpu": err, "logit_range": float(l1.max() - l1.min()),
+                         "ranks_identical": bool(same), "greedy_equal": s1 == stream}
+    grp.close()
+    if solo is not None:
+        solo.close()
+    return out if rank == 0 else None
+
+
+def run_tp(args):
+    """Tensor-parallel decode + prefill of the Llama-3-8B-shape model over all ranks of this launch (torchrun: one
+    process per GPU; a single process is the TP = 1 point).
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench.py --tp --gpus 8"""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    r = tp_measure(args, rank, local, world, args.steps, args.warmup)
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": r["decode_tok_s"], "unit": UNIT, "n_gpus": world, "steps": r["steps"], "warmup": r["warmup"],
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"llama-3-8b-shape Q4_K_M-style ({r['layers']} layers), tensor parallel over {world} GPU(s), batch-1 greedy decode after a {r['prefill_tokens']}-token prompt, ctx {r['ctx']}",
+                       "parallelism": f"tp{world}", "collectives": r["allreduce"] + " after attn_output and ffn_down, NCCL all-gather of the logits slices",
+                       "l2": "each step streams this rank's weight shard (> 126 MB L2 up to tp8)"},
+            "gpu_launches": r["gpu_launches"], "prefill": {"tokens": r["prefill_tokens"], "tok_per_s": r["prefill_tok_s"]},
+            "decode_step": {"algorithmic_bytes_per_rank": r["algorithmic_bytes_per_rank"], "achieved_gbs_per_rank": r["achieved_gbs_per_rank"],
+                            "frac_of_hbm_peak": r["frac_of_hbm_peak"], "peak_source": r["peak_source"]},
+            "model_build_s": r["model_build_s"]}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def config3_figures(b, local):
+    """Qwen2.5-1.5B shape, every matrix Q8_0 (28 layers, QKV bias, head_dim 128): prefill of 2048 random tokens, then 128
+    greedy decode tokens, on one GPU.  Returns {"decode": ..., "prefill": ...}."""
+    import dataclasses
+    import torch
+    from ggnpu_b200.backend import Model
+    cfg = dataclasses.replace(S.QWEN25_1P5B, ctx=2048 + 128 + 16)
+    synth = S.build_model(cfg, device="cuda")
+    model = Model(b, cfg, synth.tensors)
+    del synth
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
+    ids = prompt_ids(cfg, 2048)
+    model.prefill(ids, 0, want_logits=False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    _, first = model.prefill(ids, 0, want_logits=False)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    toks = model.generate(int(first), 2048, 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    toks = model.generate(int(toks[-1]), 2056, 128)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 128
+    peak, peak_kind = peaks()
+    bytes_step = model.decode_bytes(2056 + 64)
+    model.close()
+    return {"workload": "qwen2.5-1.5b shape, all Q8_0, 28 layers, QKV bias: 2048-token prefill then 128 greedy decode tokens",
+            "decode": {"tok_per_s": 1000.0 / ms, "ms_per_step": ms, "algorithmic_bytes": bytes_step,
+                       "achieved_gbs": bytes_step / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": bytes_step / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_kind},
+            "prefill": {"tokens": 2048, "tok_per_s": 2048 / (prefill_ms * 1e-3), "ms": prefill_ms}}
+
+
+def run_config5(args):
+    """qwen35moe shape (hidden 2048, 256 experts top-8 + shared expert of 512, every 4th layer gated full attention with
+    16 / 2 heads of 256, the others Gated DeltaNet with 16 / 32 heads of 128, vocab 248320): prompt of --q35-prompt tokens,
+    then --steps greedy decode tokens.  With torchrun the experts are split over the ranks (expert parallel).
+    --q35-layers bounds the layer count (40 = the full shape; the per-layer cost does not depend on it)."""
+    import dataclasses
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200.backend import CudaBackend, Q35Model
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = dataclasses.replace(S.QWEN35MOE, n_layer=args.q35_layers, ctx=args.q35_prompt + args.steps + args.warmup + 8)
+    b = CudaBackend(local)
+    join_group(b, rank, world)
+    t0 = time.perf_counter()
+    synth = S.build_q35_model(cfg, device="cuda")
+    model = Q35Model(b, cfg, synth.tensors)
+    build_s = time.perf_counter() - t0
+    del synth
+    stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    ids = prompt_ids(cfg, args.q35_prompt)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    _, first = model.prefill(ids, 0, want_logits=False)
+    e1.record(stream)
+    barrier()
+    prefill_ms = e0.elapsed_time(e1)
+    K, W = args.steps, max(args.warmup, 3)
+    toks = model.generate(int(first), len(ids), W)
+    barrier()
+    launches0 = b.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    toks = model.generate(int(toks[-1]), len(ids) + W, K)
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1), prefill_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, prefill_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        peak, peak_kind = peaks()
+        bytes_step = model.decode_bytes(len(ids) + W + K // 2)
         print(json.dumps({
             "metric": METRIC, "value": K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"llama-3-8b-shape Q4_K_M-style ({cfg.n_layer} layers), tensor parallel over {world} GPU(s), batch-1 greedy decode after a {n_prompt}-token prompt, ctx {ctx}",
-                       "parallelism": f"tp{world}", "collectives": ("NCCL all-reduce" if args.tp_nccl_only or world == 1 else "one-shot peer-memory all-reduce (decode), NCCL (prefill)") + " after attn_output and ffn_down, NCCL all-gather of the logits slices",
-                       "l2": "each step streams this rank's weight shard (> 126 MB L2 up to tp8)"},
-            "gpu_launches": launches, "prefill": {"tokens": n_prompt, "tok_per_s": n_prompt / (prefill_ms * 1e-3)},
+            "config": {"workload": f"qwen35moe shape, {cfg.n_layer} of 40 layers, Q4_K (Q6_K attention output and expert down), batch-1 greedy decode after a {len(ids)}-token prompt",
+                       "parallelism": f"ep{world}" if world > 1 else "single GPU", "collectives": "all-reduce of the FFN row after every MoE layer (batch-1 form of dispatch / combine)" if world > 1 else "none"},
+            "gpu_launches": b.launch_count() - launches0, "ms_per_token_layer": ms / K / cfg.n_layer,
+            "prefill": {"tokens": len(ids), "tok_per_s": len(ids) / (prefill_ms * 1e-3), "note": "one graph replay per prompt token (the architecture is a recurrence)"},
             "decode_step": {"algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
                             "frac_of_hbm_peak": bytes_step / (ms / K * 1e-3) / 1e9 / peak, "peak_source": peak_kind},
             "model_build_s": build_s}), flush=True)
@@ -689,6 +875,10 @@ def main():
     ap.add_argument("--tp-ctx", type=int, default=4352)
     ap.add_argument("--tp-prompt", type=int, default=4096)
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
+    ap.add_argument("--config5", action="store_true", help="qwen35moe-shape decode benchmark (expert parallel under torchrun)")
+    ap.add_argument("--q35-layers", type=int, default=40)
+    ap.add_argument("--q35-prompt", type=int, default=128)
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra figures of the default run (config 3 on one GPU; tensor / expert parallel figures and checks under torchrun)")
     ap.add_argument("--micro", action="store_true", help="quantised-matmul microbenchmark instead of the decode benchmark")
     ap.add_argument("--types", default="Q4_0,Q8_0,Q4_K,Q6_K,IQ4_XS")
     ap.add_argument("--shapes", default="2048x2048,8192x2048,2048x8192,8960x1536")
@@ -698,6 +888,9 @@ def main():
     args = ap.parse_args()
     if args.tp:
         run_tp(args)
+        return
+    if args.config5:
+        run_config5(args)
         return
     if args.micro_allreduce:
         run_micro_allreduce(args)
