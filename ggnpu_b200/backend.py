@@ -108,7 +108,7 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_model_generate_spec", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
     "ggb_q35_create", "ggb_q35_destroy", "ggb_q35_set_tensor", "ggb_q35_finalize", "ggb_q35_reset", "ggb_q35_prefill", "ggb_q35_decode",
     "ggb_q35_generate", "ggb_q35_read_state", "ggb_q35_decode_bytes",
 ]
@@ -174,6 +174,7 @@ def load_library() -> C.CDLL:
     L.ggb_model_decode.argtypes = [vp, C.c_int32, i32, vp, C.POINTER(C.c_int32)]
     L.ggb_model_generate.argtypes = [vp, C.c_int32, i32, i32, vp]
     L.ggb_model_read_kv.argtypes = [vp, i32, i32, i32, vp]
+    L.ggb_model_generate_spec.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp]
     L.ggb_model_decode_bytes.argtypes = [vp, i32]
     L.ggb_model_decode_bytes.restype = C.c_uint64
     L.ggb_q35_create.argtypes = [vp, vp, C.POINTER(vp)]
@@ -445,6 +446,15 @@ class Model:
         out = np.empty(n, dtype=np.int32)
         self.b.check(self.b.lib.ggb_model_generate(self.m, int(first_token), int(pos0), n, _ptr(out)), "generate")
         return out
+
+    def generate_spec(self, history, pos0, n, draft_k=8):
+        """Greedy generation with prompt-lookup speculative decoding; history ends with the token to feed at pos0.
+        Returns (tokens, stats dict)."""
+        hist = np.ascontiguousarray(history, dtype=np.int32)
+        out = np.empty(n, dtype=np.int32)
+        st = np.zeros(4, dtype=np.int32)
+        self.b.check(self.b.lib.ggb_model_generate_spec(self.m, _ptr(hist), hist.size, int(pos0), n, draft_k, _ptr(out), _ptr(st)), "generate_spec")
+        return out[:st[3]], {"steps": int(st[0]), "drafted": int(st[1]), "accepted": int(st[2])}
 
     def read_kv(self, layer, pos, want_v):
         out = np.empty((self.cfg_local.n_kv, self.cfg_local.head_dim), dtype=np.float32)

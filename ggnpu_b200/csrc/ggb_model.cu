@@ -28,6 +28,7 @@ struct Layer {
 // then dequantises its weights once per 2048 tokens); otherwise 256, which bounds the per-token
 // attention kernel's split scratch.
 constexpr int kSmallChunk = 256, kLargeChunk = 2048;
+constexpr int kSpecRows = 16;       // a verified block: the fed token + up to 15 drafted ones (src/cli/main.cpp:2305-2308)
 
 }  // namespace
 
@@ -58,6 +59,9 @@ struct ggb_model_s {
     float* h_logits = nullptr;
     cudaGraphExec_t decode_graph = nullptr;
     uint64_t launches_per_step = 0;
+    // speculative verification: logits and greedy token of every row of a block of up to kSpecRows tokens
+    float* logits_rows = nullptr;
+    int32_t* d_rows_next = nullptr;
     // persistent decode-step kernel (single-token steps of an all-Q4_K / Q6_K model on one GPU)
     bool use_step = false;
     StepArgs step{};
@@ -95,7 +99,7 @@ GemvArgs gemv_args(const DeviceWeight* w, const float* x, int M, int lda, float*
 
 // Enqueue one forward over n_tok tokens whose ids are in m->d_tokens.  Positions start at
 // d_pos[0] when dev_pos, else at pos0.  Ends with logits of the last row and its argmax in d_next.
-int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
+int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_rows = false) {
     Context* c = m->c;
     cudaStream_t s = c->stream;
     const ggb_model_desc& d = m->d;
@@ -191,6 +195,16 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0) {
     }
     // final norm fused into the logits GEMV; only the last row feeds sampling (main.cpp:3593-3598)
     // tensor parallel: each rank computes its slice of the vocabulary, then the slices are gathered
+    if (all_rows) {
+        // logits and greedy token of EVERY row (compute_logits_rows, src/cli/main.cpp:347-391): the verification of a
+        // speculative block.  One GPU only.
+        GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x, n_tok, H, m->logits_rows, d.vocab);
+        a.gamma = m->output_norm; a.eps = d.rms_eps;
+        M_TRY(launch_gemv(c, a, s));
+        for (int r = 0; r < n_tok; ++r)
+            M_TRY(launch_argmax(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, d.vocab, m->d_rows_next + r, m->amax_partial, s));
+        return GGB_OK;
+    }
     const int vocab_l = d.vocab / c->tp_size;
     GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H,
                            m->logits + static_cast<size_t>(c->tp_rank) * vocab_l, vocab_l);
@@ -354,6 +368,10 @@ int ggb_model_finalize(ggb_model m) {
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
     M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd)));
     M_TRY(dev_alloc(m, &m->amax_partial, 512));
+    if (c->tp_size == 1) {
+        M_TRY(dev_alloc(m, &m->logits_rows, static_cast<size_t>(kSpecRows) * d.vocab));
+        M_TRY(dev_alloc(m, &m->d_rows_next, kSpecRows));
+    }
     M_TRY(dev_alloc(m, &m->d_tokens, T));
     M_TRY(dev_alloc(m, &m->d_pos, 1));
     M_TRY(dev_alloc(m, &m->d_next, 1));
@@ -516,6 +534,75 @@ int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_
     c->launches += m->launches_per_step * n;
     M_TRY(cuda_status(c, cudaMemcpyAsync(host_out, m->d_gen, sizeof(int32_t) * n, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
     M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate"));
+    return check_device_error(c);
+}
+
+// Prompt-lookup drafter, src/cli/main.cpp:397-415: the most recent earlier occurrence of the last `ng` tokens (longest
+// n-gram first) and up to k tokens that followed it.
+static std::vector<int32_t> lookup_draft(const std::vector<int32_t>& seq, int ngram_max, int ngram_min, int k) {
+    const int n = static_cast<int>(seq.size());
+    for (int ng = ngram_max; ng >= ngram_min; --ng) {
+        if (n < ng + 1) continue;
+        for (int i = n - ng - 1; i >= 0; --i) {
+            bool match = true;
+            for (int j = 0; j < ng && match; ++j) match = seq[i + j] == seq[n - ng + j];
+            if (!match) continue;
+            std::vector<int32_t> draft;
+            for (int j = 0; j < k && i + ng + j < n; ++j) draft.push_back(seq[i + ng + j]);
+            if (!draft.empty()) return draft;
+        }
+    }
+    return {};
+}
+
+int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, int pos0, int n, int draft_k, int32_t* host_out, int32_t* stats) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate_spec: model not finalized");
+    if (c->tp_size > 1) return set_status(c, GGB_INVALID_PARAM, "generate_spec: one GPU only");
+    if (!history || n_history < 1 || n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || !host_out)
+        return set_status(c, GGB_INVALID_PARAM, "generate_spec: bad arguments");
+    for (int i = 0; i < n_history; ++i)
+        if (history[i] < 0 || history[i] >= m->d.vocab) return set_status(c, GGB_INVALID_PARAM, "generate_spec: token out of range");
+    GGB_LOCK(c);
+    const int k = std::max(1, std::min(kSpecRows - 1, draft_k));          // k + 1 rows per block (src/cli/main.cpp:2305-2308)
+    std::vector<int32_t> seq(history, history + n_history);
+    int32_t last = seq.back();
+    int pos = pos0, generated = 0;
+    long steps = 0, proposed = 0, accepted = 0;
+    std::vector<int32_t> block, rows(kSpecRows);
+    while (generated < n) {
+        // the block [last, draft_1 .. draft_k]: ngrams of 3 down to 1, as the reference (src/cli/main.cpp:2303-2304, 2343-2349)
+        std::vector<int32_t> draft = lookup_draft(seq, 3, 1, k);
+        const int room = m->d.ctx - pos - 1;                              // positions left after the fed token
+        if (static_cast<int>(draft.size()) > room) draft.resize(std::max(room, 0));
+        block.assign(1, last);
+        block.insert(block.end(), draft.begin(), draft.end());
+        const int n_tok = static_cast<int>(block.size()), n_draft = n_tok - 1;
+        M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, block.data(), sizeof(int32_t) * n_tok, cudaMemcpyHostToDevice, c->stream), "token upload"));
+        M_TRY(enqueue_forward(m, n_tok, false, pos, true));
+        M_TRY(cuda_status(c, cudaMemcpyAsync(rows.data(), m->d_rows_next, sizeof(int32_t) * n_tok, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
+        M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate_spec"));
+        // greedy verification (src/cli/main.cpp:3531-3588): accept the longest draft prefix whose token equals the row's
+        // arg-max; commit the accepted tokens plus one (the correction, or the bonus token after a full match)
+        int matched = 0;
+        std::vector<int32_t> committed;
+        for (;;) {
+            const int32_t t = rows[matched];
+            committed.push_back(t);
+            if (matched < n_draft && t == block[matched + 1]) ++matched; else break;
+        }
+        pos += 1 + matched;            // rows of rejected drafts are overwritten by the next block
+        ++steps; proposed += n_draft; accepted += matched;
+        for (int32_t t : committed) {
+            host_out[generated++] = t;
+            seq.push_back(t);
+            last = t;
+            if (generated >= n || pos >= m->d.ctx) break;
+        }
+        if (pos >= m->d.ctx) break;
+    }
+    if (stats) { stats[0] = static_cast<int32_t>(steps); stats[1] = static_cast<int32_t>(proposed); stats[2] = static_cast<int32_t>(accepted); stats[3] = generated; }
     return check_device_error(c);
 }
 

@@ -370,6 +370,15 @@ GGB_API int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_lo
 /* n greedy decode steps with the token fed back on the device (no host round trip inside);
  * the n generated ids land in host_out afterwards. */
 GGB_API int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_t* host_out);
+/* Greedy generation with prompt-lookup speculative decoding, the reference's GGNPU_SPEC_DECODE mode (drafter
+ * lookup_draft, src/cli/main.cpp:397-415; block building :2343-2349; verification :3531-3588).  history holds all
+ * tokens so far (prompt + generated), its last element is the token to feed at position pos0.  Each step drafts up
+ * to draft_k (1..15) tokens by matching the last 3, 2 or 1 tokens against the history, runs the block
+ * [last, drafts] as ONE forward, takes the arg-max of every row and commits the longest matching draft prefix plus
+ * one token, so the stream equals plain greedy decoding wherever the two forwards agree on the arg-max.  n tokens
+ * land in host_out; stats (optional, 4 ints) = steps, drafted, accepted, generated.  One GPU only. */
+GGB_API int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, int pos0, int n, int draft_k,
+                                    int32_t* host_out, int32_t* stats);
 /* Read back one KV row [n_kv][head_dim] as f32 (tests). */
 GGB_API int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out);
 /* Algorithmic HBM bytes one decode step at position pos reads+writes (weights once + KV). */

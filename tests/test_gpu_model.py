@@ -223,3 +223,54 @@ def test_persistent_step_kernel_agrees_with_kernel_per_matrix_graph(backend, ora
     assert fast_launches / 10 <= 6, fast_launches           # gather, the step kernel, two arg-max passes, feedback
     fast.close()
     slow.close()
+
+
+def ref_lookup_draft(seq, ngram_max, ngram_min, k):
+    """The reference's drafter, src/cli/main.cpp:397-415, restated for the test."""
+    n = len(seq)
+    for ng in range(ngram_max, ngram_min - 1, -1):
+        if n < ng + 1:
+            continue
+        for i in range(n - ng - 1, -1, -1):
+            if list(seq[i:i + ng]) == list(seq[n - ng:]):
+                draft = list(seq[i + ng:min(i + ng + k, n)])
+                if draft:
+                    return draft
+    return []
+
+
+@pytest.mark.parametrize("name,kw", [("llama", dict(seed=11)), ("llama_wide", dict(seed=41, hidden=512, ffn=1024, n_head=8, n_kv=2, ctx=256))])
+def test_prompt_lookup_speculative_decode_equals_plain_greedy(backend, oracle, name, kw):
+    """GGNPU_SPEC_DECODE of the reference (src/cli/main.cpp:2292-2350, 3531-3588): blocks of the fed token plus up to k
+    tokens drafted from the history are verified in one forward; the committed stream must be the plain greedy stream
+    (the reference's own claim: arg-max verification == sequential greedy).  Random-init models repeat themselves, so
+    drafts are accepted; the accepted count must be what replaying the reference's drafter over the stream predicts."""
+    from ggnpu_b200.backend import Model
+    cfg = S.tiny_config(**kw)
+    synth = S.build_model(cfg)
+    ids = np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32)
+    n = 40
+    plain = Model(backend, cfg, synth.tensors)
+    _, first = plain.prefill(ids, 0)
+    want = [int(first)] + [int(t) for t in plain.generate(first, len(ids), n - 1)]
+    spec = Model(backend, cfg, synth.tensors)
+    _, first2 = spec.prefill(ids, 0)
+    assert first2 == first
+    hist = list(ids) + [int(first)]
+    got, st = spec.generate_spec(hist, len(ids), n - 1, draft_k=8)
+    assert [int(first)] + [int(t) for t in got] == want, (got, want)
+    # replay: what the drafter proposes along this stream and how much of it the stream confirms
+    seq, i, steps, drafted, accepted = list(hist), 1, 0, 0, 0
+    while i < n:
+        draft = ref_lookup_draft(seq, 3, 1, 8)
+        matched = 0
+        while matched < len(draft) and i + matched < n and draft[matched] == want[i + matched]:
+            matched += 1
+        take = min(matched + 1, n - i)
+        seq += want[i:i + take]
+        i += take
+        steps, drafted, accepted = steps + 1, drafted + len(draft), accepted + matched
+    assert st["steps"] == steps and st["drafted"] == drafted, (st, steps, drafted, accepted)
+    assert st["accepted"] >= accepted - 1 and st["steps"] < n - 1          # fewer forwards than tokens
+    plain.close()
+    spec.close()
