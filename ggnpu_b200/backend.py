@@ -108,7 +108,8 @@ EXPORTS = [
     "ggb_last_error_message", "ggb_dequant_rows", "ggb_weight_upload", "ggb_weight_free", "ggb_weight_bytes",
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
-    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_model_generate_spec", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
+    "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_model_generate_spec", "ggb_model_set_cache", "ggb_model_cache_stats", "ggb_weight_upload_cached",
+    "ggb_pack_cache_key", "ggb_pack_file_write", "ggb_pack_file_read", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
     "ggb_q35_create", "ggb_q35_destroy", "ggb_q35_set_tensor", "ggb_q35_finalize", "ggb_q35_reset", "ggb_q35_prefill", "ggb_q35_decode",
     "ggb_q35_generate", "ggb_q35_read_state", "ggb_q35_decode_bytes",
 ]
@@ -175,6 +176,13 @@ def load_library() -> C.CDLL:
     L.ggb_model_generate.argtypes = [vp, C.c_int32, i32, i32, vp]
     L.ggb_model_read_kv.argtypes = [vp, i32, i32, i32, vp]
     L.ggb_model_generate_spec.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp]
+    L.ggb_model_set_cache.argtypes = [vp, C.c_char_p, C.c_char_p]
+    L.ggb_model_cache_stats.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.ggb_weight_upload_cached.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_char_p, u32, i64, i32, vp, C.POINTER(vp), C.POINTER(C.c_int)]
+    L.ggb_pack_cache_key.argtypes = [C.c_char_p, C.c_char_p, u32, C.c_uint64, C.c_char_p, i32]
+    L.ggb_pack_file_write.argtypes = [C.c_char_p, u32, i64, i32, i32, i32, vp, C.c_uint64, vp, C.c_uint64]
+    L.ggb_pack_file_read.argtypes = [C.c_char_p, u32, i64, i32, C.c_uint64, C.POINTER(C.c_int), C.POINTER(C.c_int), vp, vp, C.c_uint64,
+                                     C.POINTER(C.c_uint64)]
     L.ggb_model_decode_bytes.argtypes = [vp, i32]
     L.ggb_model_decode_bytes.restype = C.c_uint64
     L.ggb_q35_create.argtypes = [vp, vp, C.POINTER(vp)]
@@ -318,6 +326,16 @@ class CudaBackend:
     def gemv_swiglu_device(self, wg, wu, d_x, M, lda, d_y, ldc, d_gamma=None, eps=0.0):
         self.check(self.lib.ggb_gemv_swiglu_device(self.h, wg, wu, d_x, M, lda, d_y, ldc, d_gamma, eps), "gemv_swiglu_device")
 
+    def upload_weight_cached(self, cache_dir, model_id, tensor_name, type_id, raw, N, K):
+        """upload_weight through the packed-weight disk cache; raw may be None (load from the cache only).
+        Returns (weight handle, hit)."""
+        w, hit = C.c_void_p(), C.c_int()
+        if raw is not None:
+            raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        self.check(self.lib.ggb_weight_upload_cached(self.h, cache_dir.encode(), model_id.encode(), tensor_name.encode(), int(type_id), N, K,
+                                                     _ptr(raw), C.byref(w), C.byref(hit)), "weight_upload_cached")
+        return w, bool(hit.value)
+
     def attn_paged_device(self, q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos) -> Status:
         """All pointer arguments are device addresses (ints)."""
         p = AttnPagedParams(q, k_cache, v_cache, block_table, out, n_head, n_kv, head_dim, page, n_pages, pos)
@@ -399,7 +417,7 @@ class Model:
     `tensors` maps GGUF tensor names to (ggml type id, dims with dims[0]=K, raw bytes),
     the form ggnpu_b200.synth.SynthModel.tensors has."""
 
-    def __init__(self, backend: CudaBackend, cfg, tensors: dict):
+    def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = ""):
         self.b, self.cfg = backend, cfg
         L = backend.lib
         if backend.tp_size > 1:          # this process holds one shard; `cfg` and `tensors` describe the full model
@@ -412,6 +430,8 @@ class Model:
         m = C.c_void_p()
         backend.check(L.ggb_model_create(backend.h, C.byref(desc), C.byref(m)), "model_create")
         self.m = m
+        if cache_dir:                    # packed-weight disk cache for the matrices
+            backend.check(L.ggb_model_set_cache(m, cache_dir.encode(), model_id.encode()), "model_set_cache")
         if not hasattr(backend, "_models"):
             import weakref
             backend._models = weakref.WeakSet()
@@ -463,6 +483,12 @@ class Model:
 
     def decode_bytes(self, pos) -> int:
         return int(self.b.lib.ggb_model_decode_bytes(self.m, pos))
+
+    def cache_stats(self):
+        """(matrices loaded from packed files, matrices packed and written) of the packed-weight disk cache."""
+        h, mi = C.c_int(), C.c_int()
+        self.b.lib.ggb_model_cache_stats(self.m, C.byref(h), C.byref(mi))
+        return h.value, mi.value
 
     def close(self):
         if getattr(self, "m", None):

@@ -108,6 +108,9 @@ void* scratch(Context* c, int slot, size_t bytes);           // nullptr on failu
 int upload_weight(Context* c, uint32_t type, int64_t N, int K, const void* host_rows, DeviceWeight** out);
 void free_weight(DeviceWeight* w);
 size_t packed_bytes(uint32_t type, int64_t N, int K);
+// ggb_pack_cache.cu: upload through the packed-weight disk cache (hit: 1 when the packed file was used)
+int upload_weight_cached(Context* c, const char* cache_dir, const char* model_id, const char* tensor_name, uint32_t type, int64_t N, int K,
+                         const void* host_rows, DeviceWeight** out, int* hit);
 int launch_dequant_rows(Context* c, const PackedW& w, int64_t row0, int64_t n_rows, float* d_out, cudaStream_t s);
 int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int n_rows, float* d_out, int ld, cudaStream_t s);
 

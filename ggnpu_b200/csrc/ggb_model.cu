@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <cmath>
@@ -59,6 +60,8 @@ struct ggb_model_s {
     float* h_logits = nullptr;
     cudaGraphExec_t decode_graph = nullptr;
     uint64_t launches_per_step = 0;
+    std::string cache_dir, cache_model_id;     // packed-weight disk cache for the matrices (empty: none)
+    int cache_hits = 0, cache_misses = 0;
     // speculative verification: logits and greedy token of every row of a block of up to kSpecRows tokens
     float* logits_rows = nullptr;
     int32_t* d_rows_next = nullptr;
@@ -252,6 +255,21 @@ void ggb_model_destroy(ggb_model m) {
     delete m;
 }
 
+int ggb_model_set_cache(ggb_model m, const char* cache_dir, const char* model_id) {
+    if (!m) return GGB_INVALID_PARAM;
+    if (m->finalized) return set_status(m->c, GGB_INVALID_PARAM, "set_cache: model already finalized");
+    m->cache_dir = cache_dir ? cache_dir : "";
+    m->cache_model_id = model_id ? model_id : "";
+    return GGB_OK;
+}
+
+int ggb_model_cache_stats(ggb_model m, int* hits, int* misses) {
+    if (!m) return GGB_INVALID_PARAM;
+    if (hits) *hits = m->cache_hits;
+    if (misses) *misses = m->cache_misses;
+    return GGB_OK;
+}
+
 int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_t N, int K, const void* host) {
     if (!m) return GGB_INVALID_PARAM;
     Context* c = m->c;
@@ -263,7 +281,13 @@ int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_
     auto mat = [&](DeviceWeight** dst, int64_t wantN, int wantK) -> int {
         if (N != wantN || K != wantK) return set_status(c, GGB_INVALID_PARAM, "set_tensor: shape does not match the model description");
         if (*dst) { free_weight(*dst); *dst = nullptr; }
-        return upload_weight(c, type, N, K, host, dst);
+        if (m->cache_dir.empty()) return upload_weight(c, type, N, K, host, dst);
+        char name[48];
+        snprintf(name, sizeof(name), "slot%d.layer%d.rank%dof%d", slot, layer, c->tp_rank, c->tp_size);
+        int hit = 0;
+        const int st = upload_weight_cached(c, m->cache_dir.c_str(), m->cache_model_id.c_str(), name, type, N, K, host, dst, &hit);
+        if (st == GGB_OK) (hit ? m->cache_hits : m->cache_misses)++;
+        return st;
     };
     auto vec = [&](float** dst, int64_t wantN) -> int {
         if (type != GGB_F32 || N != wantN) return set_status(c, GGB_INVALID_PARAM, "set_tensor: vectors must be F32 of the model's size");

@@ -181,6 +181,23 @@ GGB_API int ggb_weight_upload(ggb_handle h, uint32_t type, int64_t N, int K, con
 GGB_API void ggb_weight_free(ggb_handle h, ggb_weight w);
 GGB_API size_t ggb_weight_bytes(ggb_weight w);
 
+/* Packed-weight disk cache: the role of the reference's WeightCache + CompileCache for its NPU backend
+ * (include/ggnpu/weight_cache.h:34-158, src/cache/cache.cpp:16-58): what is expensive to derive from the GGUF bytes is
+ * kept in a file per tensor under cache_dir and found again by a key built as WeightCache::make_key does
+ * (weight_cache.h:141-152): layout version, hash of model_id + tensor name, type, data size.  model_id is the caller's
+ * fingerprint of the model file, e.g. "<path>:<file size>" (src/cli/main.cpp:1203-1210).  Here the file holds the tensor
+ * in this library's HBM layout, so a hit is one read + one host-to-device copy, no repack kernels.  A file whose recorded
+ * fingerprint of the source bytes differs from host_rows is treated as a miss and rewritten.  host_rows == NULL loads
+ * from the cache only (GGB_NOT_FOUND on a miss).  *hit (optional) = 1 when the file was used. */
+GGB_API int ggb_weight_upload_cached(ggb_handle h, const char* cache_dir, const char* model_id, const char* tensor_name,
+                                     uint32_t type, int64_t N, int K, const void* host_rows, ggb_weight* out, int* hit);
+/* The cache's key and file format, usable without a GPU (tools, tests). */
+GGB_API int ggb_pack_cache_key(const char* model_id, const char* tensor_name, uint32_t type, uint64_t data_size, char* out, int cap);
+GGB_API int ggb_pack_file_write(const char* path, uint32_t type, int64_t N, int K, int nb, int layout, const uint64_t* stream_off,
+                                uint64_t src_fingerprint, const void* blob, uint64_t bytes);
+GGB_API int ggb_pack_file_read(const char* path, uint32_t type, int64_t N, int K, uint64_t src_fingerprint, int* nb, int* layout,
+                               uint64_t* stream_off, void* blob, uint64_t cap, uint64_t* bytes);
+
 /* y[M][ldc] = x[M][lda] * W^T with DEVICE pointers, M <= 16 (decode GEMV), on the handle's
  * stream.  epilogue: 0 store; 1 + bias[N]; 2 + resid[M][ldc].  gamma != NULL applies RMSNorm
  * (eps) to each x row first.  Asynchronous. */
@@ -357,6 +374,11 @@ enum ggb_tensor_slot {
 
 GGB_API int ggb_model_create(ggb_handle h, const ggb_model_desc* desc, ggb_model* out);
 GGB_API void ggb_model_destroy(ggb_model m);
+/* Optional, before the tensors are set: route the model's matrices through the packed-weight disk cache
+ * (ggb_weight_upload_cached) under cache_dir, keyed by model_id = the caller's fingerprint of the model file
+ * (src/cli/main.cpp:1203-1210).  ggb_model_cache_stats reports how many matrices came from packed files. */
+GGB_API int ggb_model_set_cache(ggb_model m, const char* cache_dir, const char* model_id);
+GGB_API int ggb_model_cache_stats(ggb_model m, int* hits, int* misses);
 /* One tensor of the model: matrices as GGUF rows ([N][K] of `type`), vectors as F32. */
 GGB_API int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_t N, int K, const void* host_data);
 /* Allocate KV pages, build the RoPE table (RopeCache::build, src/cli/main.cpp:665-692) and

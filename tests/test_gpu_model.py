@@ -5,6 +5,8 @@ Tolerances (logits are O(1) on random-init models): the KV cache is bf16 (relati
 and sums are reordered, so final logits are held to max-abs <= 0.15 (the reference's LOGIT_TOL,
 scripts/compare_logits.py:22) AND <= 2 % of the oracle's logit range; greedy tokens must agree
 wherever the oracle's top-1/top-2 margin exceeds twice the measured logit error."""
+import os
+
 import numpy as np
 import pytest
 
@@ -274,3 +276,56 @@ def test_prompt_lookup_speculative_decode_equals_plain_greedy(backend, oracle, n
     assert st["accepted"] >= accepted - 1 and st["steps"] < n - 1          # fewer forwards than tokens
     plain.close()
     spec.close()
+
+
+def test_packed_weight_disk_cache(backend, tmp_path):
+    """The packed-weight disk cache (the role of the reference's WeightCache, include/ggnpu/weight_cache.h:34-158): the
+    first model object packs every matrix and writes one file each; a second object with the same model id loads all of
+    them from the files and produces bit-identical logits; another model id shares nothing; changed tensor bytes under
+    the same id are detected (source fingerprint) and repacked."""
+    from ggnpu_b200.backend import Model
+    cfg = S.tiny_config(seed=17, wtype=S.Q4_K, wtype_alt=S.Q8_0)
+    synth = S.build_model(cfg)
+    n_mat = 1 + 7 * cfg.n_layer                       # token_embd + seven matrices per layer (tied output)
+    d = str(tmp_path / "cache")
+    ids = np.random.default_rng(2).integers(0, cfg.vocab, 9).astype(np.int32)
+    a = Model(backend, cfg, synth.tensors, cache_dir=d, model_id="model-a:123")
+    assert a.cache_stats() == (0, n_mat)
+    la, _ = a.prefill(ids, 0)
+    assert len([f for f in os.listdir(d) if f.endswith(".ggbpack")]) == n_mat
+    b2 = Model(backend, cfg, synth.tensors, cache_dir=d, model_id="model-a:123")
+    assert b2.cache_stats() == (n_mat, 0)
+    lb, _ = b2.prefill(ids, 0)
+    assert np.array_equal(la, lb)
+    c3 = Model(backend, cfg, synth.tensors, cache_dir=d, model_id="model-b:123")
+    assert c3.cache_stats() == (0, n_mat)
+    # same id, one tensor's bytes changed: that one is stale
+    t2 = dict(synth.tensors)
+    tid, dims, raw = t2["blk.0.ffn_up.weight"]
+    raw = raw.copy()
+    raw.reshape(-1)[::97] ^= 0x10
+    t2["blk.0.ffn_up.weight"] = (tid, dims, raw)
+    d4 = Model(backend, cfg, t2, cache_dir=d, model_id="model-a:123")
+    assert d4.cache_stats() == (n_mat - 1, 1)
+    ld, _ = d4.prefill(ids, 0)
+    assert not np.array_equal(la, ld)
+    # a single tensor through the C entry point, then from the cache alone (no host bytes)
+    tid, dims, raw = synth.tensors["blk.1.attn_q.weight"]
+    w1, hit1 = backend.upload_weight_cached(d, "solo", "q", tid, raw, dims[1], dims[0])
+    w2, hit2 = backend.upload_weight_cached(d, "solo", "q", tid, None, dims[1], dims[0])
+    assert (hit1, hit2) == (False, True)
+    import torch
+    x = torch.randn(1, dims[0], device="cuda")
+    y1, y2 = torch.empty(1, dims[1], device="cuda"), torch.empty(1, dims[1], device="cuda")
+    backend.gemv_device(w1, x.data_ptr(), 1, dims[0], y1.data_ptr(), dims[1], 0, None, None, 0.0)
+    backend.gemv_device(w2, x.data_ptr(), 1, dims[0], y2.data_ptr(), dims[1], 0, None, None, 0.0)
+    backend.sync()
+    assert torch.equal(y1, y2)
+    from ggnpu_b200.backend import BackendError, Status
+    with pytest.raises(BackendError) as e:
+        backend.upload_weight_cached(d, "solo", "missing", tid, None, dims[1], dims[0])
+    assert e.value.status == Status.NOT_FOUND
+    for w in (w1, w2):
+        backend.free_weight(w)
+    for mdl in (a, b2, c3, d4):
+        mdl.close()

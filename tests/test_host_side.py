@@ -84,3 +84,49 @@ def test_reference_cli_reads_our_gguf(tmp_path):
     r = run_ref_cli(str(p), S.prompt_text([5, 9, 2]), 3, ctx=cfg.ctx, timeout=120)
     assert r.returncode == 0, r.stderr
     assert len(S.text_ids(r.stdout)) == 3
+
+
+def test_pack_cache_key_and_file_round_trip(tmp_path):
+    """The packed-weight disk cache's key and file format, without a GPU.  The key follows WeightCache::make_key
+    (include/ggnpu/weight_cache.h:141-152): model fingerprint and tensor name hashed together, then type and data size, so
+    the same tensor name in two model files gives two keys.  A file reads back exactly; a file for another shape, with
+    another source fingerprint, truncated, or with trailing bytes is refused."""
+    import ctypes as C
+    from ggnpu_b200.backend import load_library
+    L = load_library()
+    buf = C.create_string_buffer(128)
+
+    def key(mid, name, t, size):
+        assert L.ggb_pack_cache_key(mid, name, t, size, buf, 128) == 0
+        return buf.value.decode()
+
+    k1 = key(b"/models/a.gguf:1000", b"blk.0.attn_q.weight", 12, 2359296)
+    assert k1 == key(b"/models/a.gguf:1000", b"blk.0.attn_q.weight", 12, 2359296)
+    assert k1 != key(b"/models/b.gguf:1000", b"blk.0.attn_q.weight", 12, 2359296)      # another model file
+    assert k1 != key(b"/models/a.gguf:1000", b"blk.1.attn_q.weight", 12, 2359296)
+    assert k1 != key(b"/models/a.gguf:1000", b"blk.0.attn_q.weight", 14, 2359296)
+    assert k1.endswith("_t12_2359296") and k1.startswith("p1_")
+    assert L.ggb_pack_cache_key(b"m", b"t", 12, 1, buf, 8) != 0                          # buffer too small
+
+    blob = np.random.default_rng(0).integers(0, 256, 5000, dtype=np.uint8)
+    off = (C.c_uint64 * 4)(0, 1024, 2**64 - 1, 2**64 - 1)
+    path = str(tmp_path / "w.ggbpack").encode()
+    assert L.ggb_pack_file_write(path, 12, 64, 512, 2, 1, off, 777, blob.ctypes.data, blob.size) == 0
+    nb, layout, n = C.c_int(), C.c_int(), C.c_uint64()
+    got_off = (C.c_uint64 * 4)()
+    out = np.zeros(8192, np.uint8)
+    args = (C.byref(nb), C.byref(layout), got_off, out.ctypes.data, out.size, C.byref(n))
+    assert L.ggb_pack_file_read(path, 12, 64, 512, 777, *args) == 0
+    assert (nb.value, layout.value, n.value) == (2, 1, 5000) and list(got_off) == list(off)
+    assert np.array_equal(out[:5000], blob)
+    assert L.ggb_pack_file_read(path, 12, 64, 512, 0, *args) == 0                        # fingerprint 0: not checked
+    assert L.ggb_pack_file_read(path, 12, 64, 512, 778, *args) == 1                      # stale: other source bytes
+    assert L.ggb_pack_file_read(path, 14, 64, 512, 777, *args) == 1                      # other type
+    assert L.ggb_pack_file_read(path, 12, 65, 512, 777, *args) == 1                      # other shape
+    assert L.ggb_pack_file_read(str(tmp_path / "none").encode(), 12, 64, 512, 777, *args) == 2   # NOT_FOUND
+    raw = open(path, "rb").read()
+    open(path, "wb").write(raw[:-10])
+    assert L.ggb_pack_file_read(path, 12, 64, 512, 777, *args) == 1                      # truncated
+    open(path, "wb").write(raw + b"x")
+    assert L.ggb_pack_file_read(path, 12, 64, 512, 777, *args) == 1                      # trailing bytes
+    assert not [f for f in os.listdir(tmp_path) if ".tmp." in f]                        # written through a temporary name
