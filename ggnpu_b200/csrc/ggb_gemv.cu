@@ -614,6 +614,11 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         if (st != GGB_NOT_FOUND) return st;
     }
     if (a.x_img || a.y_img) return set_status(c, GGB_INVALID_PARAM, "gemv: tile-image operands need the tensor-core GEMM");
+    if (a.w.layout == 1 && a.M >= 3 && a.M <= 16) {
+        // up to 16 activation rows in one pass over the weights
+        const int st = launch_gemv_mma_rows(c, a, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
     if (a.w.layout == 1) {
         // tensor-core kernel, two activation rows per pass (each pass streams the weights once)
         int st = GGB_OK;

@@ -1,0 +1,543 @@
+// Small-batch GEMV for Q4_K / Q6_K in the row-group-major layout, 3 <= M <= 16 activation rows in ONE pass over the
+// weights:   y[m][n] = sum_k x[m][k] * W[n][k]          (mul_mat_weight, src/cli/main.cpp:1367-1434, at M <= 16: the
+// reference's small-M decode kernel that its speculative verification relies on, src/cli/main.cpp:2295-2297).
+//
+// gemv_mma_q4k_kernel (ggb_gemv_mma.cu) carries two activation rows per pass, so 16 rows streamed a matrix eight times.
+// Here the three int8 limbs of up to 16 rows form up to 48 columns of the B operand = CG column groups of 8; a weight
+// fragment is loaded from shared memory once and feeds 2 * CG tensor-core instructions:
+//   column c = 3 m + p  (m activation row, p limb, weight 1, 1/128, 1/16384), column group c / 8, lane pair (c % 8) / 2.
+// The min term of Q4_K (dmin * m_sub * sum of x over the sub-block) and the -32 offset of Q6_K are subtracted in the
+// limb-0 column of each row (its weight is 1), so the three columns of a row simply add up.  At the end of a row group
+// every warp drops its column sums into a shared-memory slab; the team's first warp adds slabs and limb columns, applies
+// the epilogue and stores.
+// Shared memory bounds the rows per pass: 3 planes of K + 16 bytes per row (M = 16 at K = 2048, 8 at 4096, 4 at 8192);
+// the launcher cuts M into such chunks.  Eight warps, each with its own ring of bulk-copy stages: a warp requests the tile one
+// ring length ahead whenever it has consumed one (no producer warp, so 256 threads and the full register file per thread).
+#include "ggb_internal.h"
+
+namespace ggb {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kMaxStages = 64;
+constexpr uint32_t kSpinLimit = 1u << 17;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); }
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(b0), "r"(z));
+}
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+struct RowsArgs {
+    PackedW w, w2;
+    const float* x;
+    float* y;
+    const float* bias;
+    const float* resid;
+    const float* gamma;
+    float eps;
+    int M, lda, ldc, epi;
+    int sb, spr, nmat, groups, ws, P, stage_bytes;
+    int* err;
+};
+
+// dynamic shared memory: [ring: 8 * P * stage_bytes][limb planes: 3 M (K + 16)][asum: M K/32][asum16: M K/16][xs: M K/256]
+//                        [slab: 8 warps * nmat * 16 rows * 8 CG columns floats]
+template <int CG, int NMAT>
+__global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const RowsArgs a) {
+    constexpr int NC = 8 * CG;                         // B columns
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ float inv_s[16];
+    const int K = a.w.K, nb = a.w.nb, M = a.M;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tprg = NMAT * a.spr;
+    const int plane_stride = K + 16;
+    uint8_t* ring = smem;
+    int8_t* xl = reinterpret_cast<int8_t*>(ring + static_cast<size_t>(kWarps) * a.P * a.stage_bytes);
+    float* asum = reinterpret_cast<float*>(xl + static_cast<size_t>(3 * M) * plane_stride);
+    float* asum16 = asum + M * (K >> 5);
+    float* xs = asum16 + M * (K >> 4);
+    float* slab = xs + ((M * (K >> 8) + 3) & ~3);      // [warp][mat][16][NC], 16-byte aligned (float2 stores)
+
+    const int64_t g_begin = static_cast<int64_t>(blockIdx.x) * a.groups / gridDim.x;
+    const int n_rg = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * a.groups / gridDim.x - g_begin);
+    const int n_teams = kWarps / a.ws;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWarps * a.P; ++s) mbar_init(&full_bar[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch();
+
+    // ---------------- every warp requests its own tiles: the one a ring length ahead whenever it frees a stage ----------------
+    const int team = warp / a.ws, member = warp % a.ws;
+    const bool is_q6 = a.w.type == T_Q6_K;
+    int rg_i = team, ti_i = member, st_i = 0;          // next tile to request, and the stage it goes to
+    auto issue_next = [&]() {
+        while (rg_i < n_rg && ti_i >= tprg) { rg_i += n_teams; ti_i = member; }
+        if (rg_i >= n_rg) return;
+        const int s = warp * a.P + st_i;
+        if (lane == 0) {
+            const int mat = ti_i >= a.spr, sl = ti_i - mat * a.spr;
+            const int b0 = sl * a.sb, nbk = min(a.sb, nb - b0);
+            uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
+            const PackedW& w = mat ? a.w2 : a.w;
+            const int64_t gb = (g_begin + rg_i) * nb + b0;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
+            if (!is_q6) {
+                mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 2304u);
+                bulk_g2s(dst, w.s[1] + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, &full_bar[s]);
+                bulk_g2s(dst + a.sb * 2048, w.s[0] + gb * 256, static_cast<uint32_t>(nbk) * 256u, &full_bar[s]);
+            } else {
+                mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 3360u);
+                bulk_g2s(dst, w.s[0] + gb * 2048, static_cast<uint32_t>(nbk) * 2048u, &full_bar[s]);
+                bulk_g2s(dst + a.sb * 2048, w.s[1] + gb * 1024, static_cast<uint32_t>(nbk) * 1024u, &full_bar[s]);
+                bulk_g2s(dst + a.sb * 3072, w.s[2] + gb * 256, static_cast<uint32_t>(nbk) * 256u, &full_bar[s]);
+                bulk_g2s(dst + a.sb * 3328, w.s[3] + gb * 32, static_cast<uint32_t>(nbk) * 32u, &full_bar[s]);
+            }
+        }
+        ti_i += a.ws;
+        if (++st_i == a.P) st_i = 0;
+    };
+    for (int i = 0; i < a.P; ++i) issue_next();        // weights do not depend on the predecessor kernel: before the wait
+
+    // ---------------- consumers ----------------
+    const int g = lane >> 2, t = lane & 3;
+    const int ncol = 3 * M;
+    // per column group: this lane's B column (plane), its two C columns, their activation row, limb weight, and whether a
+    // column is the limb-0 column of its row (it then also carries the min / offset term)
+    const int8_t* bplane[CG];
+    int mrow[CG][2];
+    float lw[CG][2];
+    bool limb0[CG][2];
+#pragma unroll
+    for (int q = 0; q < CG; ++q) {
+        bplane[q] = xl + static_cast<size_t>(min(8 * q + g, ncol - 1)) * plane_stride + 4 * t;
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+            const int col = 8 * q + 2 * t + sl;
+            const bool valid = col < ncol;
+            mrow[q][sl] = valid ? col / 3 : M - 1;
+            const int p = col % 3;
+            lw[q][sl] = valid ? (p == 0 ? 1.0f : (p == 1 ? 1.0f / 128.0f : 1.0f / 16384.0f)) : 0.0f;
+            limb0[q][sl] = valid && p == 0;
+        }
+    }
+    pdl_wait();
+    // One pass over x: limbs of x * gamma, run sums, sum of squares (the RMS factor is applied at the end).  The (row,
+    // 256-block) items are dealt to the warps in batches of eight whose loads are all issued before the first conversion:
+    // sixteen rows would otherwise cost a warp sixteen dependent round trips to L2.
+    const int nblk = K >> 8, items = M * nblk;
+    float* ssb = slab;                                  // per-item sums of squares (the slabs are not in use yet)
+    for (int it0 = warp; it0 < items; it0 += 8 * kWarps) {
+        float v[8][8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int it = it0 + u * kWarps;
+            if (it < items) {
+                const int m = it / nblk, b = it - m * nblk;
+                const float* xr = a.x + static_cast<size_t>(m) * a.lda + b * 256 + lane * 8;
+                const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
+                v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int it = it0 + u * kWarps;
+            if (it < items) {
+                const int m = it / nblk, b = it - m * nblk;
+                const int k0 = b * 256 + lane * 8;
+                float ss = 0.0f;
+                if (a.gamma) {
+                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss = fmaf(v[u][i], v[u][i], ss);
+                    v[u][0] *= g0.x; v[u][1] *= g0.y; v[u][2] *= g0.z; v[u][3] *= g0.w; v[u][4] *= g1.x; v[u][5] *= g1.y; v[u][6] *= g1.z; v[u][7] *= g1.w;
+                }
+                float am = 0.0f, sm = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { am = fmaxf(am, fabsf(v[u][i])); sm += v[u][i]; }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+                const float rs = am > 0.0f ? 127.0f / am : 0.0f;
+                uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float kMagic = 12582912.0f;           // 1.5 * 2^23: round to nearest, the integer lands in the low mantissa bits
+                    const float r = fminf(fmaxf(v[u][i] * rs, -127.0f), 127.0f);
+                    const float t1 = r + kMagic;
+                    const float r2 = (r - (t1 - kMagic)) * 128.0f;
+                    const float t2 = r2 + kMagic;
+                    const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
+                    w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
+                    w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
+                    w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
+                }
+                int8_t* pl = xl + static_cast<size_t>(3 * m) * plane_stride + k0;
+                *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
+                *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
+                *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
+                if (lane == 0) xs[m * nblk + b] = am / 127.0f;
+                sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
+                if ((lane & 1) == 0) asum16[m * (K >> 4) + (k0 >> 4)] = sm;
+                sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
+                if ((lane & 3) == 0) asum[m * (K >> 5) + (k0 >> 5)] = sm;
+                ss = wsum(ss);
+                if (lane == 0) ssb[it] = ss;
+            }
+        }
+    }
+    consumer_sync();
+    if (threadIdx.x < M) {                              // fixed summation order: the result does not depend on warp timing
+        float tot = 0.0f;
+        for (int b = 0; b < nblk; ++b) tot += ssb[threadIdx.x * nblk + b];
+        inv_s[threadIdx.x] = a.gamma ? 1.0f / sqrtf(tot / static_cast<float>(K) + a.eps) : 1.0f;
+    }
+    consumer_sync();
+
+    int st = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    float* my_slab = slab + static_cast<size_t>(warp) * NMAT * 16 * NC;
+    for (int rg = team; rg < n_rg; rg += n_teams) {
+        // column sums of this warp's share of the row group: [matrix][column group][row g: slots 0, 1 | row g + 8: slots 2, 3]
+        float F[NMAT][CG][4];
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat)
+#pragma unroll
+            for (int q = 0; q < CG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) F[mat][q][i] = 0.0f;
+        for (int ti = member; ti < tprg; ti += a.ws) {
+            const int s = warp * a.P + st;
+            if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
+            if (++st == a.P) { st = 0; ph ^= 1; }
+            if (!ok) continue;
+            const int mat = ti >= a.spr, sl = ti - mat * a.spr;
+            const int b0 = sl * a.sb, nbk = min(a.sb, nb - b0);
+            const uint8_t* qsT = ring + static_cast<size_t>(s) * a.stage_bytes;
+            const uint8_t* s1T = qsT + a.sb * 2048;
+            float f[CG][4];
+#pragma unroll
+            for (int q = 0; q < CG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) f[q][i] = 0.0f;
+            if (!is_q6) {
+                for (int bl = 0; bl < nbk; ++bl) {
+                    const int b = b0 + bl;
+                    const uint4 ha = *reinterpret_cast<const uint4*>(s1T + (bl * 16 + g) * 16);
+                    const uint4 hb = *reinterpret_cast<const uint4*>(s1T + (bl * 16 + g + 8) * 16);
+                    const uint32_t sa03 = ha.y & 0x3F3F3F3Fu, sa47 = (ha.w & 0x0F0F0F0Fu) | ((ha.y >> 2) & 0x30303030u);
+                    const uint32_t sb03 = hb.y & 0x3F3F3F3Fu, sb47 = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
+                    const float dA = __half2float(__ushort_as_half(static_cast<uint16_t>(ha.x & 0xFFFF)));
+                    const float dB = __half2float(__ushort_as_half(static_cast<uint16_t>(hb.x & 0xFFFF)));
+                    {   // min term, subtracted in the limb-0 column of each activation row: dmin * sum_sub m_sub * sum(x over sub)
+                        const uint32_t ma03 = ha.z & 0x3F3F3F3Fu, ma47 = ((ha.w >> 4) & 0x0F0F0F0Fu) | ((ha.z >> 2) & 0x30303030u);
+                        const uint32_t mb03 = hb.z & 0x3F3F3F3Fu, mb47 = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
+                        const float dmA = __half2float(__ushort_as_half(static_cast<uint16_t>(ha.x >> 16)));
+                        const float dmB = __half2float(__ushort_as_half(static_cast<uint16_t>(hb.x >> 16)));
+                        float mAf[8], mBf[8];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            mAf[i] = dmA * static_cast<float>((ma03 >> (8 * i)) & 0xFFu); mAf[4 + i] = dmA * static_cast<float>((ma47 >> (8 * i)) & 0xFFu);
+                            mBf[i] = dmB * static_cast<float>((mb03 >> (8 * i)) & 0xFFu); mBf[4 + i] = dmB * static_cast<float>((mb47 >> (8 * i)) & 0xFFu);
+                        }
+#pragma unroll
+                        for (int q = 0; q < CG; ++q)
+#pragma unroll
+                            for (int sl2 = 0; sl2 < 2; ++sl2)
+                                if (limb0[q][sl2]) {
+                                    const float* as = asum + mrow[q][sl2] * (K >> 5) + b * 8;
+                                    const float4 a0 = *reinterpret_cast<const float4*>(as), a1 = *reinterpret_cast<const float4*>(as + 4);
+                                    f[q][sl2] -= mAf[0] * a0.x + mAf[1] * a0.y + mAf[2] * a0.z + mAf[3] * a0.w + mAf[4] * a1.x + mAf[5] * a1.y + mAf[6] * a1.z + mAf[7] * a1.w;
+                                    f[q][2 + sl2] -= mBf[0] * a0.x + mBf[1] * a0.y + mBf[2] * a0.z + mBf[3] * a0.w + mBf[4] * a1.x + mBf[5] * a1.y + mBf[6] * a1.z + mBf[7] * a1.w;
+                                }
+                    }
+                    int lo[CG][4], hi[CG][4];
+#pragma unroll
+                    for (int q = 0; q < CG; ++q)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { lo[q][i] = 0; hi[q][i] = 0; }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 qv = *reinterpret_cast<const uint4*>(qsT + (static_cast<size_t>(bl * 4 + j) * 32 + lane) * 16);
+                        const uint32_t l0 = qv.x & 0x0F0F0F0Fu, l1 = qv.y & 0x0F0F0F0Fu, l2 = qv.z & 0x0F0F0F0Fu, l3 = qv.w & 0x0F0F0F0Fu;
+                        const uint32_t h0 = qv.x & 0xF0F0F0F0u, h1 = qv.y & 0xF0F0F0F0u, h2 = qv.z & 0xF0F0F0F0u, h3 = qv.w & 0xF0F0F0F0u;
+                        const uint32_t wa = j < 2 ? sa03 : sa47, wb = j < 2 ? sb03 : sb47;
+                        const int sa0 = (wa >> (16 * (j & 1))) & 0xFF, sa1 = (wa >> (16 * (j & 1) + 8)) & 0xFF;
+                        const int sb0 = (wb >> (16 * (j & 1))) & 0xFF, sb1 = (wb >> (16 * (j & 1) + 8)) & 0xFF;
+#pragma unroll
+                        for (int q = 0; q < CG; ++q) {
+                            const int8_t* bp = bplane[q] + (b * 8 + 2 * j) * 32;
+                            const uint32_t bl0 = *reinterpret_cast<const uint32_t*>(bp), bl1 = *reinterpret_cast<const uint32_t*>(bp + 16);
+                            const uint32_t bh0 = *reinterpret_cast<const uint32_t*>(bp + 32), bh1 = *reinterpret_cast<const uint32_t*>(bp + 48);
+                            int cl[4], ch[4];
+                            mma_s8(cl, l0, l1, l2, l3, bl0, bl1);
+                            mma_u8s8(ch, h0, h1, h2, h3, bh0, bh1);
+                            lo[q][0] += sa0 * cl[0]; lo[q][1] += sa0 * cl[1]; lo[q][2] += sb0 * cl[2]; lo[q][3] += sb0 * cl[3];
+                            hi[q][0] += sa1 * ch[0]; hi[q][1] += sa1 * ch[1]; hi[q][2] += sb1 * ch[2]; hi[q][3] += sb1 * ch[3];
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < CG; ++q) {
+                        const float x0 = xs[mrow[q][0] * (K >> 8) + b] * lw[q][0], x1 = xs[mrow[q][1] * (K >> 8) + b] * lw[q][1];
+                        f[q][0] = fmaf(static_cast<float>(lo[q][0]) + static_cast<float>(hi[q][0]) * 0.0625f, dA * x0, f[q][0]);
+                        f[q][1] = fmaf(static_cast<float>(lo[q][1]) + static_cast<float>(hi[q][1]) * 0.0625f, dA * x1, f[q][1]);
+                        f[q][2] = fmaf(static_cast<float>(lo[q][2]) + static_cast<float>(hi[q][2]) * 0.0625f, dB * x0, f[q][2]);
+                        f[q][3] = fmaf(static_cast<float>(lo[q][3]) + static_cast<float>(hi[q][3]) * 0.0625f, dB * x1, f[q][3]);
+                    }
+                }
+            } else {
+                const uint8_t* s2T = s1T + a.sb * 1024;
+                const uint8_t* s3T = s2T + a.sb * 256;
+                for (int bl = 0; bl < nbk; ++bl) {
+                    const int b = b0 + bl;
+                    const uint4 sa = *reinterpret_cast<const uint4*>(s2T + (bl * 16 + g) * 16);
+                    const uint4 sb_ = *reinterpret_cast<const uint4*>(s2T + (bl * 16 + g + 8) * 16);
+                    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(s3T + (bl * 16 + g) * 2)));
+                    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(s3T + (bl * 16 + g + 8) * 2)));
+                    const uint32_t saw[4] = {sa.x, sa.y, sa.z, sa.w}, sbw[4] = {sb_.x, sb_.y, sb_.z, sb_.w};
+                    // quants are used unsigned (0..63): 32 * d * sum_run sc_run * sum(x over run) comes off in the limb-0 column of each row
+#pragma unroll
+                    for (int q = 0; q < CG; ++q)
+#pragma unroll
+                        for (int sl2 = 0; sl2 < 2; ++sl2)
+                            if (limb0[q][sl2]) {
+                                const float* as = asum16 + mrow[q][sl2] * (K >> 4) + b * 16;
+                                float ca = 0.0f, cb = 0.0f;
+#pragma unroll
+                                for (int w4 = 0; w4 < 4; ++w4) {
+                                    const float4 av = *reinterpret_cast<const float4*>(as + 4 * w4);
+                                    const uint32_t wa = saw[w4], wb = sbw[w4];
+                                    ca += static_cast<float>(static_cast<int8_t>(wa)) * av.x + static_cast<float>(static_cast<int8_t>(wa >> 8)) * av.y +
+                                          static_cast<float>(static_cast<int8_t>(wa >> 16)) * av.z + static_cast<float>(static_cast<int8_t>(wa >> 24)) * av.w;
+                                    cb += static_cast<float>(static_cast<int8_t>(wb)) * av.x + static_cast<float>(static_cast<int8_t>(wb >> 8)) * av.y +
+                                          static_cast<float>(static_cast<int8_t>(wb >> 16)) * av.z + static_cast<float>(static_cast<int8_t>(wb >> 24)) * av.w;
+                                }
+                                f[q][sl2] -= dA * 32.0f * ca;
+                                f[q][2 + sl2] -= dB * 32.0f * cb;
+                            }
+                    int c[CG][4];
+#pragma unroll
+                    for (int q = 0; q < CG; ++q)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) c[q][i] = 0;
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const uint4 qh = *reinterpret_cast<const uint4*>(s1T + (static_cast<size_t>(bl * 2 + hf) * 32 + lane) * 16);
+#pragma unroll
+                        for (int cc2 = 0; cc2 < 2; ++cc2) {
+                            const uint4 ql = *reinterpret_cast<const uint4*>(qsT + (static_cast<size_t>(bl * 4 + 2 * hf + cc2) * 32 + lane) * 16);
+                            const uint32_t hA = cc2 ? qh.z : qh.x, hB = cc2 ? qh.w : qh.y;
+                            const uint32_t kf = 0x0F0F0F0Fu, k3 = 0x30303030u;
+                            const uint32_t ag[4] = {(ql.x & kf) | ((hA << 4) & k3), (ql.y & kf) | ((hA << 2) & k3), ((ql.x >> 4) & kf) | (hA & k3),
+                                                    ((ql.y >> 4) & kf) | ((hA >> 2) & k3)};
+                            const uint32_t ah[4] = {(ql.z & kf) | ((hB << 4) & k3), (ql.w & kf) | ((hB << 2) & k3), ((ql.z >> 4) & kf) | (hB & k3),
+                                                    ((ql.w >> 4) & kf) | ((hB >> 2) & k3)};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int sidx = 8 * hf + 2 * i + cc2;
+                                const int sca = static_cast<int8_t>(saw[sidx >> 2] >> (8 * (sidx & 3)));
+                                const int scb = static_cast<int8_t>(sbw[sidx >> 2] >> (8 * (sidx & 3)));
+#pragma unroll
+                                for (int q = 0; q < CG; ++q) {
+                                    const uint32_t bw = *reinterpret_cast<const uint32_t*>(bplane[q] + (b * 16 + sidx) * 16);
+                                    int cc[4];
+                                    mma_u8s8_k16(cc, ag[i], ah[i], bw);
+                                    c[q][0] += sca * cc[0]; c[q][1] += sca * cc[1]; c[q][2] += scb * cc[2]; c[q][3] += scb * cc[3];
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < CG; ++q) {
+                        const float x0 = xs[mrow[q][0] * (K >> 8) + b] * lw[q][0], x1 = xs[mrow[q][1] * (K >> 8) + b] * lw[q][1];
+                        f[q][0] = fmaf(static_cast<float>(c[q][0]), dA * x0, f[q][0]); f[q][1] = fmaf(static_cast<float>(c[q][1]), dA * x1, f[q][1]);
+                        f[q][2] = fmaf(static_cast<float>(c[q][2]), dB * x0, f[q][2]); f[q][3] = fmaf(static_cast<float>(c[q][3]), dB * x1, f[q][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < CG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (NMAT == 1 || mat == 0) F[0][q][i] += f[q][i]; else F[NMAT - 1][q][i] += f[q][i];
+                }
+            __syncwarp();
+            issue_next();                               // the stage is free again
+        }
+        // ---- column sums into this warp's slab: [matrix][row 0..15][column 0..NC) ----
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+            {
+#pragma unroll
+                for (int q = 0; q < CG; ++q) {
+                    float* r0 = my_slab + (static_cast<size_t>(mat) * 16 + g) * NC + 8 * q + 2 * t;
+                    *reinterpret_cast<float2*>(r0) = make_float2(F[mat][q][0], F[mat][q][1]);
+                    *reinterpret_cast<float2*>(r0 + 8 * NC) = make_float2(F[mat][q][2], F[mat][q][3]);
+                }
+            }
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "r"(a.ws * 32) : "memory");
+        if (member == 0) {
+            // the team's first warp: (row r, activation row m) = sum over the team's slabs of columns 3m, 3m+1, 3m+2
+            for (int idx = lane; idx < 16 * M; idx += 32) {
+                const int r = idx & 15, m = idx >> 4;
+                float v = 0.0f, v2 = 0.0f;
+                for (int j = 0; j < a.ws; ++j) {
+                    const float* sj = slab + static_cast<size_t>(team * a.ws + j) * NMAT * 16 * NC + static_cast<size_t>(r) * NC + 3 * m;
+                    v += sj[0] + sj[1] + sj[2];
+                    if (NMAT == 2) { const float* s2 = sj + 16 * NC; v2 += s2[0] + s2[1] + s2[2]; }
+                }
+                v *= inv_s[m]; v2 *= inv_s[m];
+                const int64_t row = (g_begin + rg) * 16 + r;
+                if (row < a.w.N) {
+                    const size_t o = static_cast<size_t>(m) * a.ldc + row;
+                    if (NMAT == 2) v = (v / (1.0f + expf(-v))) * v2;
+                    else if (a.epi == EPI_ADD_BIAS && a.bias) v += __ldg(a.bias + row);
+                    else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
+                    a.y[o] = v;
+                }
+            }
+        }
+        // the slabs are reused by the next row group: wait until the first warp has read them
+        asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "r"(a.ws * 32) : "memory");
+    }
+}
+
+template <int CG>
+int launch_rows_t(Context* c, const GemvArgs& g, int m0, int mc, cudaStream_t s) {
+    constexpr int kThreads = kWarps * 32;
+    const int K = g.w.K, nb = g.w.nb;
+    const bool dual = g.epi == EPI_SWIGLU;
+    const bool q6 = g.w.type == T_Q6_K;
+    const int nmat = dual ? 2 : 1;
+    const int groups = static_cast<int>((g.w.N + 15) / 16);
+    const int gb_bytes = q6 ? 3360 : 2304;
+    const int G = std::min(c->sm_count, groups);
+    const int gpc = (groups + G - 1) / G;
+    int ws = 1;
+    while (ws < kWarps && gpc * ws < kWarps) ws <<= 1;
+    const size_t fixed = static_cast<size_t>(3 * mc) * (K + 16) + sizeof(float) * (mc * (K / 32 + K / 16) + ((mc * (K / 256) + 3) & ~3)) +
+                         sizeof(float) * kWarps * nmat * 16 * 8 * CG + 64;
+    const size_t budget = 216 * 1024;
+    // tile depth 1..2 blocks, ring as deep as the rest of shared memory allows (at least two stages per warp)
+    int sb = 2;
+    while (sb > 1 && nmat * ((nb + sb - 1) / sb) < ws) sb >>= 1;
+    sb = std::min(sb, nb);
+    int spr, stage_bytes, P;
+    for (;;) {
+        spr = (nb + sb - 1) / sb;
+        stage_bytes = sb * gb_bytes;
+        const int tiles_per_warp = ((gpc + kWarps / ws - 1) / (kWarps / ws)) * ((nmat * spr + ws - 1) / ws);
+        P = std::min(kMaxStages / kWarps, std::max(2, tiles_per_warp));
+        while (P > 2 && static_cast<size_t>(kWarps) * P * stage_bytes + fixed > budget) --P;
+        if (static_cast<size_t>(kWarps) * P * stage_bytes + fixed <= budget || sb == 1) break;
+        sb >>= 1;
+    }
+    const size_t smem = static_cast<size_t>(kWarps) * P * stage_bytes + fixed;
+    if (smem > budget) return GGB_NOT_FOUND;
+
+    RowsArgs a{};
+    a.w = g.w; a.w2 = g.w2; a.x = g.x + static_cast<size_t>(m0) * g.lda; a.y = g.y + static_cast<size_t>(m0) * g.ldc;
+    a.bias = g.bias; a.resid = g.resid ? g.resid + static_cast<size_t>(m0) * g.ldc : nullptr; a.gamma = g.gamma; a.eps = g.eps;
+    a.M = mc; a.lda = g.lda; a.ldc = g.ldc; a.epi = g.epi;
+    a.sb = sb; a.spr = spr; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
+    a.err = c->d_err;
+    void (*kern)(const RowsArgs) = dual ? gemv_mma_rows_kernel<CG, 2> : gemv_mma_rows_kernel<CG, 1>;
+    cudaError_t e = ensure_dynamic_smem(c, kern, smem);
+    if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma_rows attr");
+    e = launch_pdl(c, kern, dim3(static_cast<unsigned>(G)), dim3(kThreads), smem, s, a);
+    c->launches++;
+    return cuda_status(c, e, "gemv_mma_rows launch");
+}
+
+}  // namespace
+
+// Rows per pass that fit shared memory beside a ring of two stages per warp: 3 limb planes + run sums per row.
+static int rows_per_pass(int K, bool dual) {
+    const size_t per_row = static_cast<size_t>(3) * (K + 16) + sizeof(float) * (K / 32 + K / 16 + K / 256);
+    for (int r : {16, 8, 5}) {
+        const int cg = (3 * r + 7) / 8;
+        const size_t fixed = per_row * r + sizeof(float) * kWarps * (dual ? 2 : 1) * 16 * 8 * cg + 64;
+        if (fixed + static_cast<size_t>(kWarps) * 2 * 3360 <= 216 * 1024) return r;
+    }
+    return 0;
+}
+
+// 3 <= M <= 16 rows of a Q4_K / Q6_K matrix in the row-group-major layout, in as few passes over the weights as shared
+// memory allows.  GGB_NOT_FOUND: shape not covered (the caller falls back to two rows per pass).
+int launch_gemv_mma_rows(Context* c, const GemvArgs& g, cudaStream_t s) {
+    if ((g.w.type != T_Q4_K && g.w.type != T_Q6_K) || g.w.layout != 1 || g.M < 3 || g.M > 16 || g.w.K % 256) return GGB_NOT_FOUND;
+    if ((reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return GGB_NOT_FOUND;
+    const bool dual = g.epi == EPI_SWIGLU;
+    if (dual && (g.w2.layout != 1 || g.w2.type != g.w.type)) return GGB_NOT_FOUND;
+    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return GGB_NOT_FOUND;
+    const int R = rows_per_pass(g.w.K, dual);
+    if (R < 5) return GGB_NOT_FOUND;
+    for (int m0 = 0; m0 < g.M; m0 += R) {
+        const int mc = std::min(R, g.M - m0);
+        int st;
+        if (mc <= 2) {                                   // a tail of one or two rows: the two-row kernel
+            GemvArgs sub = g;
+            sub.M = mc; sub.x = g.x + static_cast<size_t>(m0) * g.lda; sub.y = g.y + static_cast<size_t>(m0) * g.ldc;
+            if (g.resid) sub.resid = g.resid + static_cast<size_t>(m0) * g.ldc;
+            st = launch_gemv_mma(c, sub, s);
+        } else if (mc <= 5) st = launch_rows_t<2>(c, g, m0, mc, s);
+        else if (mc <= 8) st = launch_rows_t<3>(c, g, m0, mc, s);
+        else st = launch_rows_t<6>(c, g, m0, mc, s);
+        if (st == GGB_NOT_FOUND && m0 > 0) return set_status(c, GGB_ERROR, "gemv_mma_rows: a later pass did not fit");
+        if (st != GGB_OK) return st;
+    }
+    return GGB_OK;
+}
+
+}  // namespace ggb

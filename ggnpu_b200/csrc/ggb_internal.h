@@ -118,6 +118,7 @@ int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int 
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
 int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
+int launch_gemv_mma_rows(Context* c, const GemvArgs& a, cudaStream_t s);   // 3..16 rows per pass; GGB_NOT_FOUND: shape not covered
 int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
 int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, float* d_ws, size_t ws_floats, cudaStream_t s);

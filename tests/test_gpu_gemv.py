@@ -135,3 +135,60 @@ def test_fused_epilogues_device_path(backend, oracle):
     assert rel_l2(got, want) <= 2e-5
     backend.free_weight(hg)
     backend.free_weight(hu)
+
+
+@pytest.mark.parametrize("t", [S.Q4_K, S.Q6_K])
+@pytest.mark.parametrize("M", [3, 5, 6, 8, 9, 13, 16])
+def test_rows_kernel_every_chunk_size(backend, oracle, t, M):
+    """3..16 activation rows in one pass over the weights (2, 3 or 6 column groups of the int8 tensor-core operand):
+    every group-count boundary, a row-group count that leaves some CTAs idle and one that gives every warp its own
+    groups, K with one and with several super-blocks."""
+    check(backend, oracle, t, 67, 1024, M, seed=M)            # N not a multiple of 16, few row groups: teams of 8 warps
+    check(backend, oracle, t, 4096, 256, M, seed=M + 1, sample_rows=40)     # many row groups per CTA, one super-block per row
+    check(backend, oracle, t, 1024, 2048, M, seed=M + 2, sample_rows=40)
+
+
+@pytest.mark.parametrize("K", [2048, 4096, 8192])
+def test_rows_kernel_row_chunks_by_k(backend, oracle, K):
+    """Shared memory holds the limb planes of 16 rows at K = 2048, 8 at 4096, 5 at 8192: M = 16 then takes 1, 2 or 4
+    passes (the last chunk of the K = 8192 case has a single row, which the two-row kernel takes)."""
+    for t in (S.Q4_K, S.Q6_K):
+        check(backend, oracle, t, 512, K, 16, seed=K, sample_rows=40)
+        check(backend, oracle, t, 512, K, 11, seed=K + 1, sample_rows=40)
+
+
+def test_rows_kernel_fused_epilogues(backend, oracle):
+    """RMSNorm prologue, bias, residual (in place) and the SwiGLU pair at M = 7 and 16 on device pointers."""
+    t, N, K = S.Q4_K, 208, 1024
+    wg, wu = make(t, N, K, 1), make(t, N, K, 2)
+    dev = torch.device("cuda:0")
+    hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
+    for M in (7, 16):
+        rng = np.random.default_rng(M)
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        gamma = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+        bias = rng.standard_normal(N).astype(np.float32)
+        resid = rng.standard_normal((M, N)).astype(np.float32)
+        dx, dg, db = torch.from_numpy(x).to(dev), torch.from_numpy(gamma).to(dev), torch.from_numpy(bias).to(dev)
+        dy = torch.empty((M, N), device=dev, dtype=torch.float32)
+        xn = np.stack([oracle.rms_norm(r, 1e-5, gamma) for r in x])
+        g_ref, u_ref = oracle.matmul_exact(xn, wg, t, N, K), oracle.matmul_exact(xn, wu, t, N, K)
+
+        def run(fn):
+            torch.cuda.synchronize()
+            fn()
+            backend.sync()
+            return dy.cpu().numpy()
+
+        got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 1, db.data_ptr(), dg.data_ptr(), 1e-5))
+        assert rel_l2(got, g_ref + bias) <= REL_L2
+        dy.copy_(torch.from_numpy(resid))
+        got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 2, dy.data_ptr(), dg.data_ptr(), 1e-5))
+        assert rel_l2(got, g_ref + resid) <= REL_L2
+        got = run(lambda: backend.gemv_swiglu_device(hg, hu, dx.data_ptr(), M, K, dy.data_ptr(), N, dg.data_ptr(), 1e-5))
+        want = np.stack([oracle.silu(r) for r in g_ref]) * u_ref
+        assert rel_l2(got, want) <= 2e-5
+        got = run(lambda: backend.gemv_device(hg, dx.data_ptr(), M, K, dy.data_ptr(), N, 0, None, None, 0.0))
+        assert rel_l2(got, oracle.matmul_exact(x, wg, t, N, K)) <= REL_L2
+    backend.free_weight(hg)
+    backend.free_weight(hu)
