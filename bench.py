@@ -388,6 +388,12 @@ def run_ours(args):
             except Exception as e:
                 extras["config3"] = {"unavailable": str(e)[:200]}
     b.close()
+    if not args.no_extras and world == 1:
+        # the 8B-shape model on one GPU: 4096-token prompt, decode at batch 1 and at batch 16
+        try:
+            extras["config4"] = tp_measure(args, rank, local, world, min(K, 32), W)
+        except Exception as e:
+            extras["config4"] = {"unavailable": str(e)[:300]}
     if not args.no_extras and world > 1:
         # the sharded paths, where the driver can see them: parity of tensor / expert parallel against one GPU, and the
         # tensor-parallel figures of the 8B-shape model over the ranks of this launch (strong scaling)
@@ -632,7 +638,8 @@ def tp_measure(args, rank, local, world, steps, warmup):
     join_group(b, rank, world, args.tp_nccl_only)
     t0 = time.perf_counter()
     synth = S.build_model(cfg, device="cuda")
-    model = Model(b, cfg, synth.tensors)
+    nb = max(1, min(16, args.tp_batch))
+    model = Model(b, cfg, synth.tensors, n_seq=nb)
     build_s = time.perf_counter() - t0
     del synth
     stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
@@ -642,7 +649,7 @@ def tp_measure(args, rank, local, world, steps, warmup):
             dist.barrier()
         torch.cuda.synchronize()
 
-    n_prompt = min(args.tp_prompt, ctx - steps - warmup - 1)
+    n_prompt = min(args.tp_prompt, ctx - steps - max(warmup, 3) - 1)
     ids = prompt_ids(cfg, n_prompt)
     model.prefill(ids, 0, want_logits=False)                      # untimed pass sizes the scratch
     barrier()
@@ -663,10 +670,30 @@ def tp_measure(args, rank, local, world, steps, warmup):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = b.launch_count() - launches0
-    t = torch.tensor([ms, prefill_ms], device="cuda", dtype=torch.float64)
+    # the batch leg: nb sequences (every KV stream holds the prompt), one forward per step for all of them
+    batch_ms, batch_same = 0.0, None
+    if nb > 1:
+        single = model.generate(int(first), n_prompt, W)
+        for r in range(1, nb):
+            model.select_sequence(r)
+            model.prefill(ids, 0, want_logits=False)
+        model.select_sequence(0)
+        firsts, pos = np.full(nb, int(first), np.int32), np.full(nb, n_prompt, np.int32)
+        out = model.generate_batch(firsts, pos, W)
+        batch_same = bool((out == out[:, :1]).all()) and bool(np.array_equal(out[:, 0], single))
+        barrier()
+        launches0 = b.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        model.generate_batch(out[-1], pos + W, K)
+        e1.record(stream)
+        barrier()
+        batch_ms = e0.elapsed_time(e1)
+        batch_launches = b.launch_count() - launches0
+    t = torch.tensor([ms, prefill_ms, batch_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, prefill_ms = float(t[0]), float(t[1])
+    ms, prefill_ms, batch_ms = float(t[0]), float(t[1]), float(t[2])
     res = None
     if rank == 0:
         peak, peak_kind = peaks()
@@ -676,6 +703,13 @@ def tp_measure(args, rank, local, world, steps, warmup):
                "allreduce": "none" if world == 1 else ("NCCL" if args.tp_nccl_only or world < 4 else "one-shot peer-memory kernel (decode), NCCL (prefill)"),
                "algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
                "frac_of_hbm_peak": bytes_step / (ms / K * 1e-3) / 1e9 / peak, "peak_source": peak_kind, "model_build_s": build_s}
+        if nb > 1:
+            # per step: the weights once, every sequence's KV stream once
+            kv_one = model.decode_bytes(n_prompt + W + K // 2) - model.decode_bytes(0)
+            bytes_b = model.decode_bytes(0) + nb * kv_one
+            res["batch"] = {"sequences": nb, "decode_tok_s": nb * K / (batch_ms * 1e-3), "ms_per_step": batch_ms / K, "gpu_launches": batch_launches,
+                            "algorithmic_bytes_per_rank": bytes_b, "frac_of_hbm_peak": bytes_b / (batch_ms / K * 1e-3) / 1e9 / peak,
+                            "rows_identical_and_equal_to_single_sequence": batch_same}
     model.close()
     b.close()
     return res
@@ -873,6 +907,7 @@ def main():
     ap.add_argument("--tp", action="store_true", help="tensor-parallel benchmark of the 8B-shape model over the ranks of this launch")
     ap.add_argument("--tp-nccl-only", action="store_true", help="keep every all-reduce on NCCL (no peer-memory one-shot kernel)")
     ap.add_argument("--tp-ctx", type=int, default=4352)
+    ap.add_argument("--tp-batch", type=int, default=16, help="sequences of the batched decode leg (1 = skip it)")
     ap.add_argument("--tp-prompt", type=int, default=4096)
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
     ap.add_argument("--config5", action="store_true", help="qwen35moe-shape decode benchmark (expert parallel under torchrun)")

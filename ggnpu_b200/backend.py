@@ -109,6 +109,7 @@ EXPORTS = [
     "ggb_gemv_device", "ggb_gemv_swiglu_device", "ggb_attn_paged_device", "ggb_attn_prefill_device", "ggb_attn_paged_static", "ggb_stream", "ggb_launch_count", "ggb_model_create", "ggb_model_destroy",
     "ggb_model_set_tensor", "ggb_model_finalize", "ggb_model_prefill", "ggb_model_decode", "ggb_model_generate",
     "ggb_model_read_kv", "ggb_model_decode_bytes", "ggb_model_generate_spec", "ggb_model_set_cache", "ggb_model_cache_stats", "ggb_weight_upload_cached",
+    "ggb_sample", "ggb_sample_device", "ggb_model_generate_sampled", "ggb_model_set_sequences", "ggb_model_select_sequence", "ggb_model_decode_batch", "ggb_model_generate_batch",
     "ggb_pack_cache_key", "ggb_pack_file_write", "ggb_pack_file_read", "ggb_tp_unique_id", "ggb_tp_init", "ggb_tp_all_reduce_device", "ggb_tp_ipc_handle", "ggb_tp_attach_peers", "ggb_moe_ffn_device", "ggb_deltanet_step_device", "ggb_qgate_split_device", "ggb_attn_gate_device",
     "ggb_q35_create", "ggb_q35_destroy", "ggb_q35_set_tensor", "ggb_q35_finalize", "ggb_q35_reset", "ggb_q35_prefill", "ggb_q35_decode",
     "ggb_q35_generate", "ggb_q35_read_state", "ggb_q35_decode_bytes",
@@ -176,6 +177,13 @@ def load_library() -> C.CDLL:
     L.ggb_model_generate.argtypes = [vp, C.c_int32, i32, i32, vp]
     L.ggb_model_read_kv.argtypes = [vp, i32, i32, i32, vp]
     L.ggb_model_generate_spec.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp]
+    L.ggb_model_set_sequences.argtypes = [vp, i32]
+    L.ggb_sample.argtypes = [vp, vp, i32, f32, vp, vp]
+    L.ggb_sample_device.argtypes = [vp, vp, i32, f32, vp, vp]
+    L.ggb_model_generate_sampled.argtypes = [vp, i32, i32, i32, f32, vp, vp]
+    L.ggb_model_select_sequence.argtypes = [vp, i32]
+    L.ggb_model_decode_batch.argtypes = [vp, vp, vp, i32, vp, vp]
+    L.ggb_model_generate_batch.argtypes = [vp, vp, vp, i32, i32, vp]
     L.ggb_model_set_cache.argtypes = [vp, C.c_char_p, C.c_char_p]
     L.ggb_model_cache_stats.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.ggb_weight_upload_cached.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_char_p, u32, i64, i32, vp, C.POINTER(vp), C.POINTER(C.c_int)]
@@ -282,6 +290,13 @@ class CudaBackend:
     def flash_attn(self, Q, K, V, output, n_head, head_dim, ctx_len, query_pos=-1) -> Status:
         p = AttnParams(_ptr(Q), _ptr(K), _ptr(V), _ptr(output), 1, n_head, head_dim, ctx_len, query_pos, None)
         return Status(self.lib.ggb_flash_attn(self.h, C.byref(p)))
+
+    def sample_token(self, logits, temp, seed):
+        """sample_token of the reference CLI (src/cli/main.cpp:827-864) on host logits: (token, advanced seed)."""
+        lg = _f32(logits).reshape(-1)
+        sd, tok = C.c_uint64(int(seed)), C.c_int32()
+        self.check(self.lib.ggb_sample(self.h, _ptr(lg), lg.size, float(temp), C.byref(sd), C.byref(tok)), "sample")
+        return tok.value, sd.value
 
     def sync(self) -> None:
         self.lib.ggb_sync(self.h)
@@ -417,7 +432,7 @@ class Model:
     `tensors` maps GGUF tensor names to (ggml type id, dims with dims[0]=K, raw bytes),
     the form ggnpu_b200.synth.SynthModel.tensors has."""
 
-    def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = ""):
+    def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = "", n_seq: int = 1):
         self.b, self.cfg = backend, cfg
         L = backend.lib
         if backend.tp_size > 1:          # this process holds one shard; `cfg` and `tensors` describe the full model
@@ -430,6 +445,8 @@ class Model:
         m = C.c_void_p()
         backend.check(L.ggb_model_create(backend.h, C.byref(desc), C.byref(m)), "model_create")
         self.m = m
+        if n_seq > 1:                    # KV streams for batched sequences
+            backend.check(L.ggb_model_set_sequences(m, n_seq), "model_set_sequences")
         if cache_dir:                    # packed-weight disk cache for the matrices
             backend.check(L.ggb_model_set_cache(m, cache_dir.encode(), model_id.encode()), "model_set_cache")
         if not hasattr(backend, "_models"):
@@ -475,6 +492,33 @@ class Model:
         st = np.zeros(4, dtype=np.int32)
         self.b.check(self.b.lib.ggb_model_generate_spec(self.m, _ptr(hist), hist.size, int(pos0), n, draft_k, _ptr(out), _ptr(st)), "generate_spec")
         return out[:st[3]], {"steps": int(st[0]), "drafted": int(st[1]), "accepted": int(st[2])}
+
+    def generate_sampled(self, first_token, pos0, n, temp, seed):
+        """n steps with the reference CLI's temperature sampling; returns (tokens, advanced seed)."""
+        out = np.empty(n, dtype=np.int32)
+        sd = C.c_uint64(int(seed))
+        self.b.check(self.b.lib.ggb_model_generate_sampled(self.m, int(first_token), int(pos0), n, float(temp), C.byref(sd), _ptr(out)), "generate_sampled")
+        return out, sd.value
+
+    def select_sequence(self, seq):
+        """The KV stream prefill / decode / read_kv work on (streams are reserved with n_seq at construction)."""
+        self.b.check(self.b.lib.ggb_model_select_sequence(self.m, int(seq)), "select_sequence")
+
+    def decode_batch(self, tokens, pos, want_logits=True):
+        """One step of len(tokens) sequences: row r is sequence r's next token at position pos[r].
+        Returns (logits [n_seq][vocab] or None, greedy next tokens)."""
+        toks, p = np.ascontiguousarray(tokens, dtype=np.int32), np.ascontiguousarray(pos, dtype=np.int32)
+        logits = np.empty((toks.size, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        nxt = np.empty(toks.size, dtype=np.int32)
+        self.b.check(self.b.lib.ggb_model_decode_batch(self.m, _ptr(toks), _ptr(p), toks.size, _ptr(logits), _ptr(nxt)), "decode_batch")
+        return logits, nxt
+
+    def generate_batch(self, first_tokens, pos0, n):
+        """n greedy steps of len(first_tokens) sequences with device-side feedback; returns ids [n][n_seq]."""
+        toks, p = np.ascontiguousarray(first_tokens, dtype=np.int32), np.ascontiguousarray(pos0, dtype=np.int32)
+        out = np.empty((n, toks.size), dtype=np.int32)
+        self.b.check(self.b.lib.ggb_model_generate_batch(self.m, _ptr(toks), _ptr(p), toks.size, n, _ptr(out)), "generate_batch")
+        return out
 
     def read_kv(self, layer, pos, want_v):
         out = np.empty((self.cfg_local.n_kv, self.cfg_local.head_dim), dtype=np.float32)

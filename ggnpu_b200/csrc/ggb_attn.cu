@@ -95,7 +95,7 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
     pdl_sync();
     const int t = blockIdx.y, hh = blockIdx.x * blockDim.y + threadIdx.y;
     const bool active = hh < a.n_head + a.n_kv;
-    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int pos = a.seq_pos ? a.seq_pos[t] : (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int hd = a.head_dim, half = hd >> 1;
     const int rot = a.rot_dims > 0 ? a.rot_dims : hd, rh = rot >> 1;       // rotated dims and pairs
     const bool is_q = hh < a.n_head;
@@ -132,7 +132,7 @@ __global__ void rope_append_kernel(KvAppendArgs a) {
         }
         if (is_q) { src[i0] = r0; src[i1] = r1; }
         else {
-            const int page = a.block_table[pos / a.page], slot = pos % a.page;
+            const int page = a.block_table[static_cast<size_t>(t) * a.seq_table_stride + pos / a.page], slot = pos % a.page;
             const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * hd;
             a.k_cache[o + i0] = __float2bfloat16_rn(r0);
             a.k_cache[o + i1] = __float2bfloat16_rn(r1);
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
 __global__ void attn_combine_kernel(AttnPagedArgs a) {
     pdl_sync();
     const int head = blockIdx.x, t = blockIdx.y, hd = a.head_dim;
-    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int pos = a.seq_pos ? a.seq_pos[t] : (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
     const int n_active = min(a.n_splits, pos / keys_per_split + 1);
     const float* part = a.partial + (static_cast<size_t>(t) * a.n_head + head) * a.n_splits * (hd + 2);
@@ -200,8 +200,8 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     if (G < 1 || G > 8 || a.n_head % a.n_kv) return set_status(c, GGB_INVALID_PARAM, "attention: query heads per KV head must be 1..8");
     const int hd = a.head_dim;
     if (a.page % 8) return set_status(c, GGB_INVALID_PARAM, "attention: page size must be a multiple of 8");
-    if (a.fuse && n_tok != 1) return set_status(c, GGB_INVALID_PARAM, "attention: fused append is for single-token steps");
-    if (c->use_tc && n_tok >= std::max(c->tc_min_m, 32) && !a.fuse) {      // prompt chunks: tensor-core flash attention
+    if (a.fuse && n_tok != 1 && !a.seq_pos) return set_status(c, GGB_INVALID_PARAM, "attention: fused append is for single-token steps (one per sequence)");
+    if (c->use_tc && n_tok >= std::max(c->tc_min_m, 32) && !a.fuse && !a.seq_pos) {      // prompt chunks: tensor-core flash attention
         const int st = launch_attn_prefill(c, a, n_tok, s);
         if (st != GGB_NOT_FOUND) return st;
     }

@@ -22,6 +22,10 @@ struct KvAppendArgs {
     int pos0;
     int n_head, n_kv, head_dim, page, neox;
     float eps;
+    // batched sequences (row t is the next token of sequence t): seq_pos[t] is row t's position and its block table
+    // starts at block_table + t * seq_table_stride; null / 0: one sequence, rows at consecutive positions
+    const int32_t* seq_pos;
+    int seq_table_stride;
     int rot_dims;             // leading dims of each head that rotate (0: all head_dim); tables hold rot_dims / 2 entries per position
     int norm_f32;             // 1: QK-norm sum of squares in float (qwen35: src/cli/main.cpp:896-901) instead of double
 };
@@ -36,6 +40,8 @@ struct AttnPagedArgs {
     float* out;               // [n_tok][n_head][hd]
     const int32_t* d_pos;
     int pos0;
+    const int32_t* seq_pos;   // batched sequences: position of row t (then d_pos / pos0 are unused) ...
+    int seq_table_stride;     // ... and row t's block table = block_table + t * seq_table_stride
     int n_head, n_kv, head_dim, page, n_splits, pages_per_split;
     // fused RoPE + KV append for a single-token step (fuse != 0): q is then PRE-RoPE, k_new / v_new are
     // this token's projections [n_kv][hd]; the kernel rotates, stores into the cache and attends.

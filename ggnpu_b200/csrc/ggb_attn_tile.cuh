@@ -50,12 +50,13 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             const int idx = tid + 128 * u, hh = idx / (HD / 2), i = idx - hh * (HD / 2);
             if (hh <= G) {
                 const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + HD / 2 : 2 * i + 1;
-                const float* src = hh < G ? qb + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                const float* src = hh < G ? qb + hh * HD : a.k_new + (static_cast<size_t>(t) * a.n_kv + h) * HD;
                 qpre0[u] = ldx<COHERENT>(src + i0); qpre1[u] = ldx<COHERENT>(src + i1);
             }
         }
     }
-    const int pos = (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int pos = a.seq_pos ? a.seq_pos[t] : (a.d_pos ? a.d_pos[0] : a.pos0) + t;
+    const int32_t* const bt = a.block_table + static_cast<size_t>(t) * a.seq_table_stride;
     const int keys_per_split = a.pages_per_split * a.page;
     const int j_begin = split * keys_per_split;
     const int j_end = min(j_begin + keys_per_split, pos + 1);
@@ -87,7 +88,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             const int row = i / (HD / 8), part = i - row * (HD / 8);
             if (row < nk0) {
                 const int j = j_begin + row;
-                const int page = a.block_table[j / a.page], slot = j % a.page;
+                const int page = bt[j / a.page], slot = j % a.page;
                 const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
                 kpre[u] = *reinterpret_cast<const uint4*>(a.k_cache + o);
                 vpre[u] = *reinterpret_cast<const uint4*>(a.v_cache + o);
@@ -102,7 +103,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             const float* nw = hh < G ? a.q_norm : a.k_norm;
             float inv = 1.0f;
             if (nw) {
-                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                const float* src = hh < G ? q + hh * HD : a.k_new + (static_cast<size_t>(t) * a.n_kv + h) * HD;
                 double ss = 0.0;
                 for (int i = lane; i < HD; i += 32) { const float sv = ldx<COHERENT>(src + i); ss += static_cast<double>(sv) * sv; }
 #pragma unroll
@@ -133,14 +134,14 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             for (int idx = tid; idx < n_items; idx += 128) {
                 const int hh = idx / half, i = idx - hh * half;
                 const int i0 = a.neox ? i : 2 * i, i1 = a.neox ? i + half : 2 * i + 1;
-                const float* src = hh < G ? q + hh * HD : a.k_new + static_cast<size_t>(h) * HD;
+                const float* src = hh < G ? q + hh * HD : a.k_new + (static_cast<size_t>(t) * a.n_kv + h) * HD;
                 rotate(idx, ldx<COHERENT>(src + i0), ldx<COHERENT>(src + i1));
             }
         }
-        if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(ldx<COHERENT>(a.v_new + static_cast<size_t>(h) * HD + i));
+        if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(ldx<COHERENT>(a.v_new + (static_cast<size_t>(t) * a.n_kv + h) * HD + i));
         sync();
         if (has_new) {     // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
-            const int page = a.block_table[pos / a.page], slot = pos % a.page;
+            const int page = bt[pos / a.page], slot = pos % a.page;
             const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD;
             for (int i = tid; i < HD; i += 128) { a.k_cache_w[o + i] = fresh[i]; a.v_cache_w[o + i] = fresh[HD + i]; }
         }
@@ -170,7 +171,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
         for (int i = tid; i < nk * (HD / 8); i += 128) {
             const int row = i / (HD / 8), part = i - row * (HD / 8);
             const int j = jc + row;
-            const int page = a.block_table[j / a.page], slot = j % a.page;
+            const int page = bt[j / a.page], slot = j % a.page;
             const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
             const uint4 kv = *reinterpret_cast<const uint4*>(a.k_cache + o);
             const uint4 vv = *reinterpret_cast<const uint4*>(a.v_cache + o);

@@ -40,7 +40,7 @@ constexpr int kDequantWarps = 16;
 constexpr int kThreadsG = (kDequantWarps + 2) * 32;      // dequant warps + MMA warp + producer warp
 constexpr int kMaxStagesG = 8;
 constexpr uint32_t kSpin = 1u << 17;
-enum : int { F_GEN = 0, F_Q4K = 1, F_Q6K = 2, F_Q80 = 3 };
+enum : int { F_GEN = 0, F_Q4K = 1, F_Q6K = 2, F_Q80 = 3, F_Q40 = 4, F_IQ4NL = 5, F_IQ4XS = 6 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -236,6 +236,30 @@ __device__ __forceinline__ uint4 q80_chunk(uint32_t wa, uint32_t wb, __half2 dd)
     bytes_to_half(wb ^ 0x80808080u, k1152, p2, p3);
     return make_uint4(as_u32(__hmul2(p0, dd)), as_u32(__hmul2(p1, dd)), as_u32(__hmul2(p2, dd)), as_u32(__hmul2(p3, dd)));
 }
+// Q4_0 (stream layout): the four bytes of wq hold elements 4 cc .. 4 cc + 3 (low nibbles, slots 0-3) and 16 + 4 cc ..
+// (high nibbles, slots 4-7) of the block; (q - 8) * d is exact in fp32, so the one fp16 rounding is the only one.
+__device__ __forceinline__ uint4 q40_chunk(uint32_t wq, __half2 dd) {
+    const __half2 k1032 = as_h2(0x64086408u);     // 1024 + 8
+    __half2 p0, p1, p2, p3;
+    bytes_to_half(wq & 0x0F0F0F0Fu, k1032, p0, p1);
+    bytes_to_half((wq >> 4) & 0x0F0F0F0Fu, k1032, p2, p3);
+    return make_uint4(as_u32(__hmul2(p0, dd)), as_u32(__hmul2(p1, dd)), as_u32(__hmul2(p2, dd)), as_u32(__hmul2(p3, dd)));
+}
+// The non-linear 4-bit codebook (src/quant/iq4_nl.cpp:16-18) as a byte-permute: four indices (one per byte of idx,
+// each < 16) -> their four signed code bytes.  The 16 codes sit in four registers; bit 3 of an index picks the pair.
+__device__ __forceinline__ uint32_t iq4_codes(uint32_t idx) {
+    const uint32_t x = idx | (idx >> 4);
+    const uint32_t p = __byte_perm(x, 0u, 0x4420);                     // the four nibbles in the low 16 bits
+    const uint32_t sel = p & 0x7777u;
+    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel);    // -127 -104 -83 -65 | -49 -35 -22 -10
+    const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, sel);    //    1   13  25  38 |  53  69  89 113
+    return __byte_perm(lo, hi, 0x3210u | ((p & 0x8888u) >> 1));
+}
+// IQ4_NL / IQ4_XS (stream layout): codes of the low nibbles (slots 0-3) and high nibbles (4-7) times the scale.
+// IQ4_NL: dd = the block's fp16 d, code * d exact before the one rounding.  IQ4_XS: dd = d * (ls - 32) rounded to fp16.
+__device__ __forceinline__ uint4 iq4_chunk(uint32_t wq, __half2 dd) {
+    return q80_chunk(iq4_codes(wq & 0x0F0F0F0Fu), iq4_codes((wq >> 4) & 0x0F0F0F0Fu), dd);
+}
 // Store chunks t (lo) and 4 + t (hi) of row r.  A quarter warp (lanes g, g + 1; t = 0..3) stores in one
 // wavefront when its eight 16-byte slots differ: even g writes lo first, odd g hi first.
 __device__ __forceinline__ void store_pair(uint8_t* tile, int r, int t, int odd, const uint4 lo, const uint4 hi) {
@@ -364,29 +388,31 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
         const int64_t row0 = a.dual ? n0 : n0 + 128 * tile;
         const FormatInfo fi = format_info(a.w.type);
         constexpr int NQ = FMT == F_Q6K ? 3 : (FMT == F_Q80 ? 2 : 1);
-        struct Frag { uint4 v[NQ]; uint32_t d; };
+        constexpr bool ROWF = FMT == F_Q80 || FMT == F_Q40 || FMT == F_IQ4NL || FMT == F_IQ4XS;     // thread = (row, 32-block of the step)
+        struct Frag { uint4 v[NQ]; uint32_t d, e; };
         struct Hdr { uint4 v; float d; };
         // per-thread stream positions
         const int64_t grp = (row0 >> 4) + grp_w;
         const bool grp_live = grp < ((w.N + 15) >> 4);
-        const uint8_t* q_base = nullptr;      // Q4_K: qs fragments; Q6_K: ql fragments; Q8_0: qs of this thread's row
-        const uint8_t* q_base2 = nullptr;     // Q6_K: qh fragments; Q8_0: block scales
+        const uint8_t* q_base = nullptr;      // Q4_K: qs fragments; Q6_K: ql fragments; row formats: qs of this thread's row
+        const uint8_t* q_base2 = nullptr;     // Q6_K: qh fragments; row formats: block scales / headers
         int q80_r = 0, q80_hh = 0;
         bool q80_live = false;
         if (FMT == F_Q4K) q_base = w.s[1] + (grp * w.nb * 4 * 32 + lane) * 16;
         if (FMT == F_Q6K) { q_base = w.s[0] + (grp * w.nb * 4 * 32 + lane) * 16; q_base2 = w.s[1] + (grp * w.nb * 2 * 32 + lane) * 16; }
-        if (FMT == F_Q80) {
+        if (ROWF) {
             const int lt = tid & 255;
             q80_r = lt >> 1; q80_hh = lt & 1;
             const int64_t row = row0 + q80_r;
             q80_live = row < w.N;
-            q_base = w.s[1] + (row * w.nb + q80_hh) * 32;
-            q_base2 = w.s[0] + (row * w.nb + q80_hh) * 2;
+            if (FMT == F_Q80) { q_base = w.s[1] + (row * w.nb + q80_hh) * 32; q_base2 = w.s[0] + (row * w.nb + q80_hh) * 2; }
+            else if (FMT == F_IQ4XS) { q_base = w.s[1] + row * w.nb * 128 + q80_hh * 16; q_base2 = w.s[0] + row * w.nb * 8; }
+            else { q_base = w.s[1] + (row * w.nb + q80_hh) * 16; q_base2 = w.s[0] + (row * w.nb + q80_hh) * 2; }
         }
         auto load_frag = [&](int ks, Frag& f) {
 #pragma unroll
             for (int j = 0; j < NQ; ++j) f.v[j] = make_uint4(0u, 0u, 0u, 0u);
-            f.d = 0u;
+            f.d = 0u; f.e = 0u;
             if (FMT == F_Q4K) {
                 if (grp_live) f.v[0] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>(ks) * 512));
             } else if (FMT == F_Q6K) {
@@ -401,6 +427,17 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                     f.v[0] = __ldg(reinterpret_cast<const uint4*>(p));
                     f.v[NQ - 1] = __ldg(reinterpret_cast<const uint4*>(p + 16));
                     f.d = __ldg(reinterpret_cast<const unsigned short*>(q_base2 + static_cast<size_t>(ks) * 4));
+                }
+            } else if (FMT == F_Q40 || FMT == F_IQ4NL) {
+                if (q80_live) {
+                    f.v[0] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>(ks) * 32));
+                    f.d = __ldg(reinterpret_cast<const unsigned short*>(q_base2 + static_cast<size_t>(ks) * 4));
+                }
+            } else if (FMT == F_IQ4XS) {
+                if (q80_live) {      // the 256-block's 8-byte header: d | scales_h, scales_l[4]
+                    f.v[0] = __ldg(reinterpret_cast<const uint4*>(q_base + static_cast<size_t>(ks) * 32));
+                    const uint2 h = __ldg(reinterpret_cast<const uint2*>(q_base2 + static_cast<size_t>(ks >> 2) * 8));
+                    f.d = h.x; f.e = h.y;
                 }
             }
         };
@@ -466,6 +503,28 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_tc_kernel(const GemmArgs a)
                 *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 1)) = q80_chunk(lo.y, hi4.y, dd);
                 *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = q80_chunk(lo.z, hi4.z, dd);
                 *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = q80_chunk(lo.w, hi4.w, dd);
+            } else if (FMT == F_Q40 || FMT == F_IQ4NL || FMT == F_IQ4XS) {
+                const uint4 q = cur.v[0];
+                __half2 dd;
+                if (FMT == F_IQ4XS) {
+                    const int ib = 2 * (ks & 3) + q80_hh;
+                    const int ls = static_cast<int>(((cur.e >> (4 * ib)) & 15u) | (((cur.d >> (16 + 2 * ib)) & 3u) << 4));
+                    dd = __float2half2_rn(__half2float(__ushort_as_half(static_cast<unsigned short>(cur.d & 0xFFFFu))) * static_cast<float>(ls - 32));
+                } else {
+                    dd = __half2half2(__ushort_as_half(static_cast<unsigned short>(cur.d)));
+                }
+                const int c0 = 4 * q80_hh;
+                if (FMT == F_Q40) {
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 0)) = q40_chunk(q.x, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 1)) = q40_chunk(q.y, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = q40_chunk(q.z, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = q40_chunk(q.w, dd);
+                } else {
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 0)) = iq4_chunk(q.x, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 1)) = iq4_chunk(q.y, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 2)) = iq4_chunk(q.z, dd);
+                    *reinterpret_cast<uint4*>(At + swz_off(q80_r, c0 + 3)) = iq4_chunk(q.w, dd);
+                }
             } else {
                 uint8_t* As = smem + static_cast<size_t>(s_cur) * a_bytes;
                 for (int it = (RT == 2 ? tid : (tid & 255)); it < RT * 128 * 8; it += RT * 256) {
@@ -627,6 +686,9 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     if (g.w.type == T_Q4_K && g.w.layout == 1) fmt = F_Q4K;
     else if (g.w.type == T_Q6_K && g.w.layout == 1) fmt = F_Q6K;
     else if (g.w.type == T_Q8_0 && g.w.layout == 0) fmt = F_Q80;
+    else if (g.w.type == T_Q4_0 && g.w.layout == 0) fmt = F_Q40;
+    else if (g.w.type == T_IQ4_NL && g.w.layout == 0) fmt = F_IQ4NL;
+    else if (g.w.type == T_IQ4_XS && g.w.layout == 0) fmt = F_IQ4XS;
     // two weight tiles per CTA halve the activation traffic per flop; one tile doubles the CTA count
     int rt = 2;
     if (!dual) {
@@ -664,7 +726,13 @@ int launch_gemm_tc(Context* c, const GemvArgs& g, void* d_xb_v, size_t xb_elems,
     case F_Q6K * 2 + 0: st = launch_one<F_Q6K, 1>(c, a, grid, smem, s); break;
     case F_Q6K * 2 + 1: st = launch_one<F_Q6K, 2>(c, a, grid, smem, s); break;
     case F_Q80 * 2 + 0: st = launch_one<F_Q80, 1>(c, a, grid, smem, s); break;
-    default: st = launch_one<F_Q80, 2>(c, a, grid, smem, s); break;
+    case F_Q80 * 2 + 1: st = launch_one<F_Q80, 2>(c, a, grid, smem, s); break;
+    case F_Q40 * 2 + 0: st = launch_one<F_Q40, 1>(c, a, grid, smem, s); break;
+    case F_Q40 * 2 + 1: st = launch_one<F_Q40, 2>(c, a, grid, smem, s); break;
+    case F_IQ4NL * 2 + 0: st = launch_one<F_IQ4NL, 1>(c, a, grid, smem, s); break;
+    case F_IQ4NL * 2 + 1: st = launch_one<F_IQ4NL, 2>(c, a, grid, smem, s); break;
+    case F_IQ4XS * 2 + 0: st = launch_one<F_IQ4XS, 1>(c, a, grid, smem, s); break;
+    default: st = launch_one<F_IQ4XS, 2>(c, a, grid, smem, s); break;
     }
     if (st != GGB_OK || splits == 1) return st;
     const size_t elems = static_cast<size_t>(g.M) * g.w.N;

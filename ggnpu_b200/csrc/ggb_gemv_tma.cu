@@ -186,6 +186,56 @@ struct TQ40 {
     }
 };
 
+// The non-linear 4-bit codebook (src/quant/iq4_nl.cpp:16-18) by byte-permute: four indices (one per byte, each < 16)
+// -> their four signed code bytes.
+__device__ __forceinline__ int iq4_codes(uint32_t idx) {
+    const uint32_t x = idx | (idx >> 4);
+    const uint32_t p = __byte_perm(x, 0u, 0x4420);                     // the four nibbles in the low 16 bits
+    const uint32_t sel = p & 0x7777u;
+    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel);    // -127 -104 -83 -65 | -49 -35 -22 -10
+    const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, sel);    //    1   13  25  38 |  53  69  89 113
+    return static_cast<int>(__byte_perm(lo, hi, 0x3210u | ((p & 0x8888u) >> 1)));
+}
+// sum over the 32 values of one sub-block: low nibbles against run a, high nibbles against run b (|code| <= 127, so
+// the limb sums are combined in float as for Q8_0)
+__device__ __forceinline__ float iq4_dot32(const uint4 q, const XUnit& x) {
+    const uint32_t kf = 0x0F0F0F0Fu;
+    const int a[4] = {iq4_codes(q.x & kf), iq4_codes(q.y & kf), iq4_codes(q.z & kf), iq4_codes(q.w & kf)};
+    const int b[4] = {iq4_codes((q.x >> 4) & kf), iq4_codes((q.y >> 4) & kf), iq4_codes((q.z >> 4) & kf), iq4_codes((q.w >> 4) & kf)};
+    int s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s1 = __dp4a(a[i], x.a.l1[i], s1); s2 = __dp4a(a[i], x.a.l2[i], s2); s3 = __dp4a(a[i], x.a.l3[i], s3);
+        s1 = __dp4a(b[i], x.b.l1[i], s1); s2 = __dp4a(b[i], x.b.l2[i], s2); s3 = __dp4a(b[i], x.b.l3[i], s3);
+    }
+    return static_cast<float>(s1) * 16384.0f + static_cast<float>(s2) * 128.0f + static_cast<float>(s3);
+}
+
+struct TIQ4NL {
+    static constexpr uint32_t TYPE = T_IQ4_NL;
+    static constexpr int NS = 2;                                   // d[2], qs[16] per 32-block
+    __device__ static void runs(int u, int& ka, int& kb) { ka = u * 32; kb = ka + 16; }
+    __device__ static float unit(const uint8_t* const (&s)[4], int rb, int u, const XUnit& x) {
+        const uint4 q = *reinterpret_cast<const uint4*>(s[1] + static_cast<size_t>(rb + u) * 16);
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(s[0] + static_cast<size_t>(rb + u) * 2)));
+        return d * x.scale * iq4_dot32(q, x);
+    }
+};
+
+struct TIQ4XS {
+    static constexpr uint32_t TYPE = T_IQ4_XS;
+    static constexpr int NS = 2;                                   // header d | scales_h | scales_l[4] (8 bytes), qs[128] per 256-block
+    __device__ static void runs(int u, int& ka, int& kb) { ka = u * 32; kb = ka + 16; }
+    __device__ static float unit(const uint8_t* const (&s)[4], int rb, int u, const XUnit& x) {
+        const uint4 q = *reinterpret_cast<const uint4*>(s[1] + (static_cast<size_t>(rb) * 8 + u) * 16);
+        const uint2 h = *reinterpret_cast<const uint2*>(s[0] + static_cast<size_t>(rb + (u >> 3)) * 8);
+        const int ib = u & 7;
+        const int ls = static_cast<int>(((h.y >> (4 * ib)) & 15u) | (((h.x >> (16 + 2 * ib)) & 3u) << 4));
+        const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(h.x & 0xFFFFu)));
+        return d * static_cast<float>(ls - 32) * x.scale * iq4_dot32(q, x);
+    }
+};
+
 // ---- kernel -----------------------------------------------------------------------------------
 
 struct TmaGemvArgs {
@@ -514,6 +564,8 @@ int launch_gemv_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     case T_Q6_K: return dual ? launch_tma<TQ6K, true>(c, g, s) : launch_tma<TQ6K, false>(c, g, s);
     case T_Q8_0: return dual ? launch_tma<TQ80, true>(c, g, s) : launch_tma<TQ80, false>(c, g, s);
     case T_Q4_0: return dual ? launch_tma<TQ40, true>(c, g, s) : launch_tma<TQ40, false>(c, g, s);
+    case T_IQ4_NL: return dual ? launch_tma<TIQ4NL, true>(c, g, s) : launch_tma<TIQ4NL, false>(c, g, s);
+    case T_IQ4_XS: return dual ? launch_tma<TIQ4XS, true>(c, g, s) : launch_tma<TIQ4XS, false>(c, g, s);
     default: return GGB_NOT_FOUND;
     }
 }

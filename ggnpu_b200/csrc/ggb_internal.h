@@ -169,6 +169,12 @@ int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, in
 int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s);
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
 
+// ggb_sample.cu: temperature sampling (src/cli/main.cpp:839-864) on logits in HBM
+size_t sample_scratch_bytes(int n);
+int sample_enqueue(Context* c, const float* d_logits, int n, const int32_t* d_argmax, const float* d_temp, const double* d_u, const int32_t* d_step,
+                   void* scratch, int32_t* d_out, cudaStream_t s);
+double sample_next_uniform(uint64_t* seed);
+
 // ggb_moe.cu / ggb_deltanet.cu: the operators of the qwen35moe layers with caller-owned scratch
 size_t moe_scratch_floats(const ggb_moe_params* p);
 int moe_ffn_enqueue(Context* c, const ggb_moe_params* p, float* scr, cudaStream_t s);

@@ -8,6 +8,7 @@
 #include <stdlib.h>
 
 #include <cmath>
+#include <map>
 #include <memory>
 
 #include "ggb_attn.h"
@@ -65,6 +66,19 @@ struct ggb_model_s {
     // speculative verification: logits and greedy token of every row of a block of up to kSpecRows tokens
     float* logits_rows = nullptr;
     int32_t* d_rows_next = nullptr;
+    // batched sequences: n_seq KV streams of n_pages pages each (sequence b owns logical pages [b * n_pages, (b + 1) * n_pages)
+    // of the block table); cur_seq is the stream the single-sequence entry points work on
+    int n_seq = 1, cur_seq = 0;
+    int32_t *d_seq_pos = nullptr, *d_gen_batch = nullptr;
+    std::map<int, cudaGraphExec_t> batch_graphs;       // one captured step per batch size
+    std::map<int, uint64_t> batch_launches;
+    // temperature sampling (ggb_model_generate_sampled): scratch, the step's uniform draws, the captured step
+    void* samp_scratch = nullptr;
+    float* d_temp = nullptr;
+    double* d_u = nullptr;
+    int32_t* d_sampled = nullptr;
+    cudaGraphExec_t sample_graph = nullptr;
+    uint64_t sample_launches = 0;
     // persistent decode-step kernel (single-token steps of an all-Q4_K / Q6_K model on one GPU)
     bool use_step = false;
     StepArgs step{};
@@ -82,6 +96,18 @@ int dev_alloc(ggb_model m, T** p, size_t count) {
     m->owned.push_back(v);
     *p = static_cast<T*>(v);
     return GGB_OK;
+}
+
+// One thread per sequence: the greedy token becomes the sequence's next input, its position advances.
+__global__ void feedback_batch_kernel(const int32_t* next, int32_t* tokens, int32_t* seq_pos, int32_t* gen, int32_t* step, int n_seq, int gen_cap) {
+    const int r = threadIdx.x, s = step[0];
+    if (r < n_seq) {
+        if (s < gen_cap) gen[static_cast<size_t>(s) * n_seq + r] = next[r];
+        tokens[r] = next[r];
+        seq_pos[r] += 1;
+    }
+    __syncthreads();
+    if (r == 0) step[0] = s + 1;
 }
 
 __global__ void feedback_kernel(const int32_t* next, int32_t* tokens, int32_t* pos, int32_t* gen, int32_t* step, int gen_cap) {
@@ -102,14 +128,19 @@ GemvArgs gemv_args(const DeviceWeight* w, const float* x, int M, int lda, float*
 
 // Enqueue one forward over n_tok tokens whose ids are in m->d_tokens.  Positions start at
 // d_pos[0] when dev_pos, else at pos0.  Ends with logits of the last row and its argmax in d_next.
-int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_rows = false) {
+// batch: row r is instead the next token of sequence r at position d_seq_pos[r] (its own KV stream), and the
+// pass ends with the logits and greedy token of every row (logits_rows, d_rows_next).
+int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_rows = false, bool batch = false) {
     Context* c = m->c;
     cudaStream_t s = c->stream;
     const ggb_model_desc& d = m->d;
     const int H = d.hidden, hd = d.head_dim, qd = d.n_head * hd, kvd = d.n_kv * hd, F = d.ffn;
     const int32_t* dpos = dev_pos ? m->d_pos : nullptr;
+    const int32_t* table = m->block_table + (batch ? 0 : static_cast<size_t>(m->cur_seq) * m->n_pages);
+    const bool single = n_tok == 1 && !batch;
+    if (batch) all_rows = true;
     M_TRY(launch_gather_rows(c, m->tok_embd->w, m->d_tokens, n_tok, m->x, H, s));
-    if (m->use_step && n_tok == 1) {
+    if (m->use_step && single && m->cur_seq == 0) {
         // all layers and the logits in one persistent kernel
         m->step.attn.d_pos = dpos; m->step.attn.pos0 = pos0;
         M_TRY(launch_decode_step(c, m->step, hd, s));
@@ -149,23 +180,24 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         ka.q = m->q; ka.k = m->k; ka.v = m->v;
         ka.k_cache = m->k_cache + static_cast<size_t>(L) * m->kv_layer_elems;
         ka.v_cache = m->v_cache + static_cast<size_t>(L) * m->kv_layer_elems;
-        ka.block_table = m->block_table; ka.cos_tab = m->cos_tab; ka.sin_tab = m->sin_tab;
+        ka.block_table = table; ka.cos_tab = m->cos_tab; ka.sin_tab = m->sin_tab;
         ka.q_norm = l.q_norm; ka.k_norm = l.k_norm; ka.d_pos = dpos; ka.pos0 = pos0;
         ka.n_head = d.n_head; ka.n_kv = d.n_kv; ka.head_dim = hd; ka.page = m->page; ka.neox = d.rope_neox; ka.eps = d.rms_eps;
-        if (n_tok > 1) M_TRY(launch_rope_append(c, ka, n_tok, s));   // single-token steps fuse this into attention
+        if (!single && !batch) M_TRY(launch_rope_append(c, ka, n_tok, s));   // single-token steps (one per sequence) fuse this into attention
 
         AttnPagedArgs aa{};
-        if (n_tok == 1) {
+        if (batch) { aa.seq_pos = m->d_seq_pos; aa.seq_table_stride = m->n_pages; }
+        if (single || batch) {
             aa.fuse = 1; aa.neox = d.rope_neox; aa.k_new = m->k; aa.v_new = m->v;
             aa.k_cache_w = ka.k_cache; aa.v_cache_w = ka.v_cache; aa.cos_tab = m->cos_tab; aa.sin_tab = m->sin_tab;
             aa.q_norm = l.q_norm; aa.k_norm = l.k_norm; aa.eps = d.rms_eps;
         }
-        aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = m->block_table;
+        aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = table;
         aa.partial = m->partial; aa.partial_tok_cap = kSmallChunk; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
         aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
         aa.pages_per_split = m->pages_per_split;
         // single-token steps: the output projection merges the attention splits itself
-        const bool merge_in_gemv = n_tok == 1 && l.o->w.layout == 1;
+        const bool merge_in_gemv = single && l.o->w.layout == 1;
         aa.skip_merge = merge_in_gemv ? 1 : 0;
         M_TRY(launch_attn_paged(c, aa, n_tok, s));
 
@@ -198,17 +230,20 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
     }
     // final norm fused into the logits GEMV; only the last row feeds sampling (main.cpp:3593-3598)
     // tensor parallel: each rank computes its slice of the vocabulary, then the slices are gathered
+    const int vocab_l = d.vocab / c->tp_size;
     if (all_rows) {
         // logits and greedy token of EVERY row (compute_logits_rows, src/cli/main.cpp:347-391): the verification of a
-        // speculative block.  One GPU only.
-        GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x, n_tok, H, m->logits_rows, d.vocab);
+        // speculative block, or one step of a batch of sequences.  Tensor parallel: each rank fills its slice of the
+        // vocabulary in every row, then the slices are gathered row by row.
+        GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x, n_tok, H, m->logits_rows + static_cast<size_t>(c->tp_rank) * vocab_l, d.vocab);
         a.gamma = m->output_norm; a.eps = d.rms_eps;
         M_TRY(launch_gemv(c, a, s));
-        for (int r = 0; r < n_tok; ++r)
+        for (int r = 0; r < n_tok; ++r) {
+            if (c->tp_size > 1) M_TRY(tp_all_gather_in_place(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, static_cast<size_t>(vocab_l), s));
             M_TRY(launch_argmax(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, d.vocab, m->d_rows_next + r, m->amax_partial, s));
+        }
         return GGB_OK;
     }
-    const int vocab_l = d.vocab / c->tp_size;
     GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H,
                            m->logits + static_cast<size_t>(c->tp_rank) * vocab_l, vocab_l);
     a.gamma = m->output_norm; a.eps = d.rms_eps;
@@ -246,6 +281,8 @@ void ggb_model_destroy(ggb_model m) {
         GGB_LOCK(m->c);
         cudaStreamSynchronize(m->c->stream);
         if (m->decode_graph) cudaGraphExecDestroy(m->decode_graph);
+        for (auto& g : m->batch_graphs) cudaGraphExecDestroy(g.second);
+        if (m->sample_graph) cudaGraphExecDestroy(m->sample_graph);
         for (void* p : m->owned) cudaFree(p);
         if (m->h_io) cudaFreeHost(m->h_io);
         if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -367,14 +404,14 @@ int ggb_model_finalize(ggb_model m) {
     m->n_pages = (d.ctx + m->page - 1) / m->page;
     m->pages_per_split = (m->n_pages + 31) / 32;
     m->n_splits = (m->n_pages + m->pages_per_split - 1) / m->pages_per_split;
-    m->kv_layer_elems = static_cast<size_t>(m->n_pages) * d.n_kv * m->page * hd;
+    m->kv_layer_elems = static_cast<size_t>(m->n_seq) * m->n_pages * d.n_kv * m->page * hd;
     M_TRY(dev_alloc(m, &m->k_cache, m->kv_layer_elems * d.n_layer));
     M_TRY(dev_alloc(m, &m->v_cache, m->kv_layer_elems * d.n_layer));
     M_TRY(cuda_status(c, cudaMemset(m->k_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
     M_TRY(cuda_status(c, cudaMemset(m->v_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
     {
-        std::vector<int32_t> bt(m->n_pages);
-        for (int i = 0; i < m->n_pages; ++i) bt[i] = i;
+        std::vector<int32_t> bt(static_cast<size_t>(m->n_seq) * m->n_pages);
+        for (size_t i = 0; i < bt.size(); ++i) bt[i] = static_cast<int32_t>(i);
         M_TRY(dev_alloc(m, &m->block_table, bt.size()));
         M_TRY(cuda_status(c, cudaMemcpy(m->block_table, bt.data(), sizeof(int32_t) * bt.size(), cudaMemcpyHostToDevice), "block table"));
     }
@@ -392,10 +429,11 @@ int ggb_model_finalize(ggb_model m) {
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
     M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd)));
     M_TRY(dev_alloc(m, &m->amax_partial, 512));
-    if (c->tp_size == 1) {
-        M_TRY(dev_alloc(m, &m->logits_rows, static_cast<size_t>(kSpecRows) * d.vocab));
-        M_TRY(dev_alloc(m, &m->d_rows_next, kSpecRows));
-    }
+    M_TRY(dev_alloc(m, &m->logits_rows, static_cast<size_t>(kSpecRows) * d.vocab));
+    M_TRY(dev_alloc(m, &m->d_rows_next, kSpecRows));
+    M_TRY(dev_alloc(m, &m->d_seq_pos, kSpecRows));
+    M_TRY(cuda_status(c, cudaMemset(m->d_seq_pos, 0, 4 * kSpecRows), "memset"));
+    if (m->n_seq > 1) M_TRY(dev_alloc(m, &m->d_gen_batch, static_cast<size_t>(d.ctx) * m->n_seq));
     M_TRY(dev_alloc(m, &m->d_tokens, T));
     M_TRY(dev_alloc(m, &m->d_pos, 1));
     M_TRY(dev_alloc(m, &m->d_next, 1));
@@ -531,8 +569,12 @@ int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, in
     m->h_io[0] = token; m->h_io[1] = pos;
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
-    M_TRY(cuda_status(c, cudaGraphLaunch(m->decode_graph, c->stream), "graph launch"));
-    c->launches += m->launches_per_step;
+    if (m->cur_seq == 0) {
+        M_TRY(cuda_status(c, cudaGraphLaunch(m->decode_graph, c->stream), "graph launch"));
+        c->launches += m->launches_per_step;
+    } else {
+        M_TRY(enqueue_forward(m, 1, true, 0));       // the captured step is bound to sequence 0's block table
+    }
     if (host_logits) M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_logits, m->logits, sizeof(float) * m->d.vocab, cudaMemcpyDeviceToHost, c->stream), "logits download"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 2, m->d_next, 4, cudaMemcpyDeviceToHost, c->stream), "token download"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->h_io + 4, c->d_err, 4, cudaMemcpyDeviceToHost, c->stream), "error word download"));
@@ -549,6 +591,7 @@ int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate: model not finalized");
     if (n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || first_token < 0 || first_token >= m->d.vocab || !host_out)
         return set_status(c, GGB_INVALID_PARAM, "generate: bad arguments");
+    if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate: the device-resident loop runs on sequence 0 (use ggb_model_generate_batch for several)");
     GGB_LOCK(c);
     m->h_io[0] = first_token; m->h_io[1] = pos0; m->h_io[3] = 0;
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
@@ -584,6 +627,7 @@ int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, 
     Context* c = m->c;
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate_spec: model not finalized");
     if (c->tp_size > 1) return set_status(c, GGB_INVALID_PARAM, "generate_spec: one GPU only");
+    if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate_spec: runs on sequence 0");
     if (!history || n_history < 1 || n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || !host_out)
         return set_status(c, GGB_INVALID_PARAM, "generate_spec: bad arguments");
     for (int i = 0; i < n_history; ++i)
@@ -630,6 +674,169 @@ int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, 
     return check_device_error(c);
 }
 
+int ggb_model_generate_sampled(ggb_model m, int32_t first_token, int pos0, int n, float temp, uint64_t* seed, int32_t* host_out) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate_sampled: model not finalized");
+    if (n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || first_token < 0 || first_token >= m->d.vocab || !host_out || !seed)
+        return set_status(c, GGB_INVALID_PARAM, "generate_sampled: bad arguments");
+    if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate_sampled: runs on sequence 0");
+    if (temp <= 0.0f) return ggb_model_generate(m, first_token, pos0, n, host_out);      // greedy (src/cli/main.cpp:828-837)
+    GGB_LOCK(c);
+    if (!m->samp_scratch) {
+        uint8_t* sc = nullptr;
+        M_TRY(dev_alloc(m, &sc, sample_scratch_bytes(m->d.vocab)));
+        M_TRY(dev_alloc(m, &m->d_temp, 1));
+        M_TRY(dev_alloc(m, &m->d_u, static_cast<size_t>(m->d.ctx)));
+        M_TRY(dev_alloc(m, &m->d_sampled, 1));
+        m->samp_scratch = sc;
+    }
+    auto step = [&]() -> int {
+        M_TRY(enqueue_forward(m, 1, true, 0));           // ends with the index of the first maximum in d_next
+        M_TRY(sample_enqueue(c, m->logits, m->d.vocab, m->d_next, m->d_temp, m->d_u, m->d_step, m->samp_scratch, m->d_sampled, c->stream));
+        feedback_kernel<<<1, 1, 0, c->stream>>>(m->d_sampled, m->d_tokens, m->d_pos, m->d_gen, m->d_step, m->d.ctx);
+        c->launches++;
+        return cuda_status(c, cudaGetLastError(), "feedback kernel");
+    };
+    // every step's uniform draw: the generator is re-seeded from its own first output at each call
+    // (src/cli/main.cpp:841,862), so the draws depend on the seed alone
+    std::vector<double> u(n);
+    for (int i = 0; i < n; ++i) u[i] = sample_next_uniform(seed);
+    m->h_io[0] = first_token; m->h_io[1] = pos0; m->h_io[3] = 0;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_step, m->h_io + 3, 4, cudaMemcpyHostToDevice, c->stream), "step upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_temp, &temp, 4, cudaMemcpyHostToDevice, c->stream), "temperature upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_u, u.data(), sizeof(double) * n, cudaMemcpyHostToDevice, c->stream), "draws upload"));
+    int done = 0;
+    if (!m->sample_graph) {
+        // the first step runs eagerly (kernel attributes are set outside capture), then the step is captured
+        M_TRY(step());
+        M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate_sampled"));
+        done = 1;
+        const uint64_t before = c->launches;
+        M_TRY(cuda_status(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "begin capture"));
+        const int st = step();
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+        m->sample_launches = c->launches - before;
+        c->launches = before;
+        if (st != GGB_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        M_TRY(cuda_status(c, e, "end capture"));
+        e = cudaGraphInstantiate(&m->sample_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        M_TRY(cuda_status(c, e, "graph instantiate"));
+    }
+    for (int i = done; i < n; ++i) M_TRY(cuda_status(c, cudaGraphLaunch(m->sample_graph, c->stream), "graph launch"));
+    c->launches += m->sample_launches * (n - done);
+    M_TRY(cuda_status(c, cudaMemcpyAsync(host_out, m->d_gen, sizeof(int32_t) * n, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate_sampled"));
+    return check_device_error(c);
+}
+
+int ggb_model_set_sequences(ggb_model m, int n_seq) {
+    if (!m) return GGB_INVALID_PARAM;
+    if (m->finalized) return set_status(m->c, GGB_INVALID_PARAM, "set_sequences: model already finalized");
+    if (n_seq < 1 || n_seq > kSpecRows) return set_status(m->c, GGB_INVALID_PARAM, "set_sequences: 1 to 16 sequences");
+    m->n_seq = n_seq;
+    return GGB_OK;
+}
+
+int ggb_model_select_sequence(ggb_model m, int seq) {
+    if (!m) return GGB_INVALID_PARAM;
+    if (seq < 0 || seq >= m->n_seq) return set_status(m->c, GGB_INVALID_PARAM, "select_sequence: no such sequence");
+    m->cur_seq = seq;
+    return GGB_OK;
+}
+
+namespace {
+
+int check_batch(ggb_model m, const int32_t* tokens, const int32_t* pos, int n_seq, int n_steps, const char* who) {
+    Context* c = m->c;
+    auto fail = [&](const char* what) { return set_status(c, GGB_INVALID_PARAM, (std::string(who) + ": " + what).c_str()); };
+    if (!m->finalized) return fail("model not finalized");
+    if (!tokens || !pos || n_seq < 1 || n_seq > m->n_seq) return fail("bad arguments (more sequences than ggb_model_set_sequences reserved?)");
+    for (int r = 0; r < n_seq; ++r)
+        if (tokens[r] < 0 || tokens[r] >= m->d.vocab || pos[r] < 0 || pos[r] + n_steps > m->d.ctx) return fail("token or position out of range");
+    return GGB_OK;
+}
+
+// The captured step of a batch of n_seq sequences: forward + feedback.  The first call for a batch size runs one eager
+// step on scratch inputs first (kernel attributes are set outside capture), so the caller uploads its inputs afterwards.
+int batch_graph(ggb_model m, int n_seq, cudaGraphExec_t* out) {
+    Context* c = m->c;
+    auto it = m->batch_graphs.find(n_seq);
+    if (it != m->batch_graphs.end()) { *out = it->second; return GGB_OK; }
+    // The warm-up step runs at the LAST position of each stream: the only cache slot it writes is one that a real
+    // step rewrites before reading (a step at position p stores slot p first), so prefilled streams stay intact.
+    std::vector<int32_t> pos(n_seq, m->d.ctx - 1), tok(n_seq, 0);
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, tok.data(), 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_seq_pos, pos.data(), 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(enqueue_forward(m, n_seq, false, 0, true, true));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "batch warm-up step"));
+    M_TRY(check_device_error(c));
+    const uint64_t before = c->launches;
+    M_TRY(cuda_status(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal), "begin capture"));
+    int st = enqueue_forward(m, n_seq, false, 0, true, true);
+    if (st == GGB_OK) {
+        feedback_batch_kernel<<<1, 32, 0, c->stream>>>(m->d_rows_next, m->d_tokens, m->d_seq_pos, m->d_gen_batch, m->d_step, n_seq, m->d.ctx);
+        c->launches++;
+        st = cuda_status(c, cudaGetLastError(), "feedback kernel");
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    m->batch_launches[n_seq] = c->launches - before;
+    c->launches = before;
+    if (st != GGB_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    M_TRY(cuda_status(c, e, "end capture"));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    M_TRY(cuda_status(c, e, "graph instantiate"));
+    m->batch_graphs[n_seq] = exec;
+    *out = exec;
+    return GGB_OK;
+}
+
+}  // namespace
+
+int ggb_model_decode_batch(ggb_model m, const int32_t* tokens, const int32_t* pos, int n_seq, float* host_logits, int32_t* next_tokens) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    M_TRY(check_batch(m, tokens, pos, n_seq, 1, "decode_batch"));
+    GGB_LOCK(c);
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, tokens, 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_seq_pos, pos, 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(enqueue_forward(m, n_seq, false, 0, true, true));
+    std::vector<int32_t> next(n_seq);
+    if (host_logits)
+        M_TRY(cuda_status(c, cudaMemcpyAsync(host_logits, m->logits_rows, sizeof(float) * static_cast<size_t>(n_seq) * m->d.vocab, cudaMemcpyDeviceToHost, c->stream), "logits download"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(next.data(), m->d_rows_next, 4 * n_seq, cudaMemcpyDeviceToHost, c->stream), "token download"));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "decode_batch"));
+    if (next_tokens) memcpy(next_tokens, next.data(), 4 * n_seq);
+    return check_device_error(c);
+}
+
+int ggb_model_generate_batch(ggb_model m, const int32_t* first_tokens, const int32_t* pos0, int n_seq, int n, int32_t* host_out) {
+    if (!m) return GGB_INVALID_PARAM;
+    Context* c = m->c;
+    if (n <= 0 || !host_out) return set_status(c, GGB_INVALID_PARAM, "generate_batch: bad arguments");
+    M_TRY(check_batch(m, first_tokens, pos0, n_seq, n, "generate_batch"));
+    if (m->n_seq < 2) return set_status(c, GGB_INVALID_PARAM, "generate_batch: reserve the sequences with ggb_model_set_sequences before finalize");
+    GGB_LOCK(c);
+    cudaGraphExec_t g = nullptr;
+    M_TRY(batch_graph(m, n_seq, &g));
+    const int32_t zero = 0;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, first_tokens, 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "token upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_seq_pos, pos0, 4 * n_seq, cudaMemcpyHostToDevice, c->stream), "pos upload"));
+    M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_step, &zero, 4, cudaMemcpyHostToDevice, c->stream), "step upload"));
+    for (int i = 0; i < n; ++i) M_TRY(cuda_status(c, cudaGraphLaunch(g, c->stream), "graph launch"));
+    c->launches += m->batch_launches[n_seq] * n;
+    M_TRY(cuda_status(c, cudaMemcpyAsync(host_out, m->d_gen_batch, sizeof(int32_t) * static_cast<size_t>(n) * n_seq, cudaMemcpyDeviceToHost, c->stream), "tokens download"));
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "generate_batch"));
+    return check_device_error(c);
+}
+
 int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out) {
     if (!m) return GGB_INVALID_PARAM;
     Context* c = m->c;
@@ -638,7 +845,7 @@ int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_o
     const int hd = m->d.head_dim;
     std::vector<__nv_bfloat16> tmp(hd);
     const __nv_bfloat16* base = (want_v ? m->v_cache : m->k_cache) + static_cast<size_t>(layer) * m->kv_layer_elems;
-    const int page = pos / m->page, slot = pos % m->page;   // identity block table
+    const int page = m->cur_seq * m->n_pages + pos / m->page, slot = pos % m->page;   // identity block table
     for (int h = 0; h < m->d.n_kv; ++h) {
         const size_t o = ((static_cast<size_t>(page) * m->d.n_kv + h) * m->page + slot) * hd;
         M_TRY(cuda_status(c, cudaMemcpy(tmp.data(), base + o, sizeof(__nv_bfloat16) * hd, cudaMemcpyDeviceToHost), "kv download"));

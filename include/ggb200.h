@@ -401,10 +401,37 @@ GGB_API int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n
  * land in host_out; stats (optional, 4 ints) = steps, drafted, accepted, generated.  One GPU only. */
 GGB_API int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, int pos0, int n, int draft_k,
                                     int32_t* host_out, int32_t* stats);
+/* n decode steps with temperature sampling and device-side feedback: sample_token of the reference CLI
+ * (src/cli/main.cpp:827-864) applied to each step's logits where they lie in HBM.  *seed is the CLI's rng_seed:
+ * it advances exactly as the reference's does (one std::mt19937 per call, re-seeded from its own first output), so
+ * a run split over several calls continues the same stream.  temp <= 0 is greedy decoding (ggb_model_generate). */
+GGB_API int ggb_model_generate_sampled(ggb_model m, int32_t first_token, int pos0, int n, float temp, uint64_t* seed, int32_t* host_out);
+/* Several sequences on one set of weights (no counterpart in the reference, whose CLI runs one sequence: the
+ * batch-16 decode scenario needs it).  ggb_model_set_sequences(n_seq <= 16), before finalize, reserves n_seq KV
+ * streams of ctx tokens each.  ggb_model_select_sequence picks the stream that prefill / decode / read_kv work on
+ * (default 0; ggb_model_generate and ggb_model_generate_spec run on stream 0 only).
+ * ggb_model_decode_batch: ONE forward in which row r is the next token of sequence r at position pos[r]; every
+ * matrix is streamed once for all rows, each row attends to its own KV stream.  Logits [n_seq][vocab] to host_logits
+ * (may be NULL), greedy tokens to next_tokens (may be NULL).  ggb_model_generate_batch: n such steps with tokens and
+ * positions fed back on the device (one CUDA graph per step); host_out[step * n_seq + r]. */
+GGB_API int ggb_model_set_sequences(ggb_model m, int n_seq);
+GGB_API int ggb_model_select_sequence(ggb_model m, int seq);
+GGB_API int ggb_model_decode_batch(ggb_model m, const int32_t* tokens, const int32_t* pos, int n_seq, float* host_logits, int32_t* next_tokens);
+GGB_API int ggb_model_generate_batch(ggb_model m, const int32_t* first_tokens, const int32_t* pos0, int n_seq, int n, int32_t* host_out);
 /* Read back one KV row [n_kv][head_dim] as f32 (tests). */
 GGB_API int ggb_model_read_kv(ggb_model m, int layer, int pos, int want_v, float* host_out);
 /* Algorithmic HBM bytes one decode step at position pos reads+writes (weights once + KV). */
 GGB_API uint64_t ggb_model_decode_bytes(ggb_model m, int pos);
+
+/* ---- sampling ----
+ * sample_token, src/cli/main.cpp:827-864 (the CLI's sampler; not a Backend member).  temp <= 0: index of the first
+ * maximum.  temp > 0: softmax((v - max) / temp) in float, then std::discrete_distribution driven by
+ * std::mt19937(*seed); *seed becomes the generator's first output, as in the reference.  The exponentials, both
+ * normalisations and the search run on the GPU; the chosen index equals the reference's unless the uniform draw lies
+ * within float rounding (~1e-7 relative) of the boundary between two tokens' cumulative probabilities.
+ * ggb_sample takes host logits, ggb_sample_device logits already in HBM. */
+GGB_API int ggb_sample(ggb_handle h, const float* host_logits, int n, float temp, uint64_t* seed, int32_t* token);
+GGB_API int ggb_sample_device(ggb_handle h, const float* d_logits, int n, float temp, uint64_t* seed, int32_t* token);
 
 /* ---- whole-model path, qwen35 / qwen35moe graph (src/cli/main.cpp:2859-3232) ----
  * Gated DeltaNet layers (those given an ssm_conv1d tensor, :2207-2213) and gated full-attention layers, a

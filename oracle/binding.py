@@ -96,6 +96,7 @@ class Oracle:
         L.ggo_rope_table.argtypes = [C.c_int64, C.c_int, C.c_float, C.c_float, _f32p, C.c_int, _f32p, _f32p]
         L.ggo_rope_apply.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_int]
         L.ggo_argmax_first.argtypes = [_f32p, C.c_int]
+        L.ggo_sample_token.argtypes = [_f32p, C.c_int, C.c_float, C.POINTER(C.c_uint64)]
         L.ggo_model_new.restype = C.c_void_p
         L.ggo_model_new.argtypes = [C.c_int] * 8 + [C.c_float] * 3 + [C.c_int]
         L.ggo_model_free.argtypes = [C.c_void_p]
@@ -264,6 +265,13 @@ class Oracle:
     def argmax_first(self, x):
         x = np.ascontiguousarray(x, dtype=np.float32)
         return self.lib.ggo_argmax_first(_fp(x), x.size)
+
+    def sample_token(self, x, temp, seed):
+        """sample_token (src/cli/main.cpp:827-864): (token, advanced seed)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        sd = C.c_uint64(int(seed))
+        tok = self.lib.ggo_sample_token(_fp(x), x.size, float(temp), C.byref(sd))
+        return tok, sd.value
 
 
 _W_SLOTS = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate": 4, "ffn_up": 5, "ffn_down": 6}
@@ -525,7 +533,8 @@ class Ref:
 
 
 def run_ref_cli(gguf_path: str, prompt: str, n_tokens: int, ctx: int = 2048, bench_logits: bool = False,
-                exact: bool = True, timeout: float | None = None, extra_env: dict | None = None):
+                exact: bool = True, timeout: float | None = None, extra_env: dict | None = None,
+                temp: float = 0.0, seed: int | None = None):
     """Run the reference CLI on its CPU backend.  exact=True sets the two
     environment switches that select the exact fp32 matmul for every format."""
     env = dict(os.environ)
@@ -538,5 +547,7 @@ def run_ref_cli(gguf_path: str, prompt: str, n_tokens: int, ctx: int = 2048, ben
         cmd.append("bench-logits")
     cmd += ["-m", gguf_path, "-p", prompt, "-c", str(ctx), "--no-cache"]
     if not bench_logits:
-        cmd += ["-n", str(n_tokens), "--temp", "0", "--quiet"]
+        cmd += ["-n", str(n_tokens), "--temp", repr(float(temp)) if temp else "0", "--quiet"]
+        if seed is not None:
+            cmd += ["--seed", str(int(seed))]
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)

@@ -564,6 +564,69 @@ GGO_API int ggo_argmax_first(const float* x, int n) {
     return best;
 }
 
+/* src/cli/main.cpp:839-864: temperature sampling.  The reference draws with std::mt19937 and
+ * std::discrete_distribution<int>; both are restated here from their published definitions (ISO C++ [rand.eng.mers],
+ * [rand.dist.samp.discrete]; the distribution's arithmetic as GNU libstdc++ implements it, which is what the
+ * reference links against):
+ *   - mt19937: the 32-bit Mersenne Twister, state seeded from (seed mod 2^32) by x[i] = 1812433253 *
+ *     (x[i-1] ^ (x[i-1] >> 30)) + i;
+ *   - the caller's seed is replaced by the generator's first output (main.cpp:862);
+ *   - probs_i = exp((v_i - max) / temp) / sum_exp, float, sum_exp accumulated sequentially in float (:849-859);
+ *   - the distribution divides the probs by their double sum, forms running sums in double, sets the last to 1
+ *     and returns the first index whose running sum is >= u, where u = (r1 + r2 * 2^32) / 2^64 in double from the
+ *     generator's next two outputs (generate_canonical<double, 53>), stepped just below 1 if it rounds to 1.
+ * Pinned by the sampled streams the reference CLI prints (tests/golden/ref_cli.npz). */
+typedef struct { uint32_t x[624]; int idx; } ggo_mt19937;
+static void ggo_mt_seed(ggo_mt19937* g, uint32_t seed) {
+    g->x[0] = seed;
+    for (int i = 1; i < 624; ++i) g->x[i] = 1812433253u * (g->x[i - 1] ^ (g->x[i - 1] >> 30)) + (uint32_t)i;
+    g->idx = 624;
+}
+static uint32_t ggo_mt_next(ggo_mt19937* g) {
+    if (g->idx >= 624) {
+        for (int i = 0; i < 624; ++i) {
+            const uint32_t y = (g->x[i] & 0x80000000u) | (g->x[(i + 1) % 624] & 0x7FFFFFFFu);
+            g->x[i] = g->x[(i + 397) % 624] ^ (y >> 1) ^ ((y & 1u) ? 0x9908B0DFu : 0u);
+        }
+        g->idx = 0;
+    }
+    uint32_t y = g->x[g->idx++];
+    y ^= y >> 11;
+    y ^= (y << 7) & 0x9D2C5680u;
+    y ^= (y << 15) & 0xEFC60000u;
+    y ^= y >> 18;
+    return y;
+}
+GGO_API int ggo_sample_token(const float* logits, int n, float temp, uint64_t* seed) {
+    if (temp <= 0.0f) return ggo_argmax_first(logits, n);
+    ggo_mt19937 g;
+    ggo_mt_seed(&g, (uint32_t)(*seed & 0xFFFFFFFFu));
+    float mx = -INFINITY;
+    for (int i = 0; i < n; ++i) if (logits[i] > mx) mx = logits[i];
+    float* probs = (float*)malloc(sizeof(float) * (size_t)n);
+    double* cp = (double*)malloc(sizeof(double) * (size_t)n);
+    float sum_exp = 0.0f;
+    for (int i = 0; i < n; ++i) { probs[i] = expf((logits[i] - mx) / temp); sum_exp += probs[i]; }
+    for (int i = 0; i < n; ++i) probs[i] /= sum_exp;
+    *seed = ggo_mt_next(&g);
+    int pick = 0;
+    if (n >= 2) {
+        double sum = 0.0;
+        for (int i = 0; i < n; ++i) sum += (double)probs[i];
+        double run = 0.0;
+        for (int i = 0; i < n; ++i) { run += (double)probs[i] / sum; cp[i] = run; }
+        cp[n - 1] = 1.0;
+        const double r1 = (double)ggo_mt_next(&g), r2 = (double)ggo_mt_next(&g);
+        double u = (r1 + r2 * 4294967296.0) / 18446744073709551616.0;
+        if (u >= 1.0) u = nextafter(1.0, 0.0);
+        int lo = 0, hi = n;                      /* std::lower_bound: first cp[i] >= u */
+        while (lo < hi) { const int mid = lo + (hi - lo) / 2; if (cp[mid] < u) lo = mid + 1; else hi = mid; }
+        pick = lo;
+    }
+    free(probs); free(cp);
+    return pick;
+}
+
 /* ---- generic (llama / qwen2 / qwen3) forward: src/cli/main.cpp:2367-2375,
  * 3235-3512, 3593-3599 ------------------------------------------------------ */
 

@@ -98,6 +98,11 @@ def cli_cases():
     }
 
 
+# temperature-sampled streams: name -> [(temp, seed)]
+SAMPLED_CASES = {"llama": [(0.8, 42), (1.5, 7)], "qwen2": [(0.7, 123456789012)]}
+N_SAMPLED = 12
+
+
 def cli_vectors():
     """End to end: the unmodified reference CLI (exact fp32 matmul path) on seeded synthetic models:
     top-10 logits after the prompt and the greedy continuation -> ref_cli.npz."""
@@ -123,6 +128,14 @@ def cli_vectors():
         e2e[f"{name}_top_ids"] = np.array([t for t, _ in top], dtype=np.int32)
         e2e[f"{name}_top_logits"] = np.array([v for _, v in top], dtype=np.float32)
         e2e[f"{name}_greedy"] = np.array(gen, dtype=np.int32)
+        if name in SAMPLED_CASES:
+            # temperature sampling (sample_token, src/cli/main.cpp:839-864): the stream the CLI prints for a seed
+            for temp, seed in SAMPLED_CASES[name]:
+                r3 = run_ref_cli(path, S.prompt_text(ids), N_SAMPLED, ctx=cfg.ctx, temp=temp, seed=seed)
+                smp = S.text_ids(r3.stdout)
+                assert len(smp) == N_SAMPLED, (r3.stdout, r3.stderr)
+                e2e[f"{name}_sampled_t{temp}_s{seed}"] = np.array(smp, dtype=np.int32)
+                print(name, "sampled", temp, seed, smp)
         os.remove(path)
         print(name, "top-1", top[0], "greedy", gen)
     np.savez_compressed(os.path.join(HERE, "ref_cli.npz"), **e2e)

@@ -2,12 +2,12 @@
 entry points) vs the CPU oracle.
 
 Operands are fp16 (weights dequantised to fp16, activations rounded to fp16 once), sums fp32.  Bars:
-  * "fp16 model", tight: formats filled by the exact decoder (and Q8_0, whose fast filler is exact)
-    equal the oracle's dequantised rows with the SAME two roundings applied (float64 accumulation)
+  * "fp16 model", tight: formats filled by the exact decoder (and Q8_0, Q4_0, IQ4_NL, whose fast fillers
+    multiply an integer by the block's fp16 scale and round once) equal the oracle's dequantised rows with the SAME two roundings applied (float64 accumulation)
     up to summation order: rel-L2 <= 1e-5, max-abs <= 2e-5 * max|ref|.  This pins tile layout,
     swizzle, K permutation, descriptors and the epilogue.
-  * "fp16 model", loose: the fast Q4_K / Q6_K fillers round the sub-block scale (and min term) to
-    fp16 before the multiply: rel-L2 <= 1.5e-3 against the same model.
+  * "fp16 model", loose: the fast Q4_K / Q6_K / IQ4_XS fillers round the sub-block scale (and min term)
+    to fp16 before the multiply: rel-L2 <= 1.5e-3 against the same model.
   * "reference": against the exact fp32 matmul of the reference's CPU path (dequant_tensor_row +
     sequential dot, src/cli/main.cpp:1379-1388): rel-L2 <= 2e-3."""
 import numpy as np
@@ -27,7 +27,7 @@ def f16(a):
     return np.ascontiguousarray(a, dtype=np.float32).astype(np.float16).astype(np.float64)
 
 
-LOOSE_TYPES = (S.Q4_K, S.Q6_K)      # fast fillers that round the scales to fp16
+LOOSE_TYPES = (S.Q4_K, S.Q6_K, S.IQ4_XS)      # fast fillers that round the scales to fp16
 
 
 def make(t, N, K, seed):
@@ -100,6 +100,47 @@ def test_benchmark_shapes_sampled_rows(backend, oracle):
         rb = S.row_bytes(t, K)
         sub = np.ascontiguousarray(raw.reshape(N, rb)[rows])
         check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
+
+
+ROW_FILL_TYPES = [S.Q8_0, S.Q4_0, S.IQ4_NL, S.IQ4_XS]
+
+
+@pytest.mark.parametrize("t", ROW_FILL_TYPES, ids=lambda t: S.TYPE_NAMES[t])
+def test_row_fillers_tiles_split_k_and_pair(backend, oracle, t):
+    """The formats whose weight tiles are filled one (row, 32-block) per thread: a ragged N with split-K
+    (K = 2048 over two output tiles), a grid large enough for two weight tiles per CTA (sampled rows), and the
+    SwiGLU pair (gate and up tiles side by side in one CTA)."""
+    N, K, M = 130, 2048, 70
+    raw = make(t, N, K, 11)
+    A = np.random.default_rng(11).standard_normal((M, K)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+    check_model(C, A, dequant(oracle, t, raw, N, K), t)
+
+    N, K, M = 8192, 512, 1024
+    raw = make(t, N, K, 12)
+    A = np.random.default_rng(12).standard_normal((M, K)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    assert backend.mul_mat_q(A, raw, C, M, N, K, t) == Status.OK, backend.last_error_message()
+    assert np.isfinite(C).all()
+    rows = np.unique(np.concatenate([np.arange(4), np.arange(N - 4, N), np.random.default_rng(2).integers(0, N, 40)]))
+    sub = np.ascontiguousarray(raw.reshape(N, S.row_bytes(t, K))[rows])
+    check_model(C[:, rows], A, dequant(oracle, t, sub, len(rows), K), t)
+
+    N, K, M = 200, 512, 40
+    wg, wu = make(t, N, K, 13), make(t, N, K, 14)
+    x = np.random.default_rng(13).standard_normal((M, K)).astype(np.float32)
+    dev = torch.device("cuda:0")
+    dx = torch.from_numpy(x).to(dev)
+    dy = torch.empty((M, N), device=dev, dtype=torch.float32)
+    hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
+    torch.cuda.synchronize()
+    backend.gemv_swiglu_device(hg, hu, dx.data_ptr(), M, K, dy.data_ptr(), N, None, 0.0)
+    backend.sync()
+    g_ref, u_ref = f16(x) @ f16(dequant(oracle, t, wg, N, K)).T, f16(x) @ f16(dequant(oracle, t, wu, N, K)).T
+    assert rel_l2(dy.cpu().numpy(), g_ref / (1.0 + np.exp(-g_ref)) * u_ref) <= (3e-3 if t in LOOSE_TYPES else 2e-5)
+    backend.free_weight(hg)
+    backend.free_weight(hu)
 
 
 MICRO_SHAPES = [(2048, 2048), (8192, 2048), (2048, 8192), (8960, 1536)]

@@ -227,6 +227,84 @@ def test_persistent_step_kernel_agrees_with_kernel_per_matrix_graph(backend, ora
     slow.close()
 
 
+@pytest.mark.parametrize("name,kw", [("llama_q4k_q6k", dict(seed=21, ctx=256)),
+                                     ("qwen2_q8_0_bias", dict(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=22, rope_base=1e6, tied=False, ctx=256)),
+                                     ("llama_hd128_gqa4", dict(n_head=8, n_kv=2, head_dim=128, hidden=512, ffn=1024, seed=23, wtype=S.Q4_0, wtype_alt=S.Q5_K, ctx=256))])
+def test_batched_sequences_equal_single_sequence_runs(backend, oracle, name, kw):
+    """Five sequences with prompts of different lengths (one crossing a KV page) share the weights: one batched step
+    (row r = sequence r's next token, its own position, its own KV stream) must give each row the logits that the
+    single-sequence step gives, which in turn match the oracle; the device-feedback batch loop must reproduce the
+    greedy streams of five separate single-sequence runs."""
+    from ggnpu_b200.backend import Model
+    from oracle.binding import OracleModel
+    cfg = S.tiny_config(**kw)
+    synth = S.build_model(cfg)
+    rng = np.random.default_rng(3)
+    lens = [3, 70, 17, 1, 40]
+    prompts = [rng.integers(0, cfg.vocab, n).astype(np.int32) for n in lens]
+    B, n_gen = len(lens), 6
+    gm = Model(backend, cfg, synth.tensors, n_seq=B)
+    one = Model(backend, cfg, synth.tensors)                # the single-sequence path
+    # prompts into their streams (all but the last token, which the batched step feeds)
+    for r, ids in enumerate(prompts):
+        gm.select_sequence(r)
+        if len(ids) > 1:
+            gm.prefill(ids[:-1], 0, want_logits=False)
+    gm.select_sequence(0)
+    toks = np.array([ids[-1] for ids in prompts], np.int32)
+    pos = np.array([len(ids) - 1 for ids in prompts], np.int32)
+    got, nxt = gm.decode_batch(toks, pos)
+    streams = []
+    for r, ids in enumerate(prompts):
+        want_single, nxt_single = one.prefill(ids, 0)
+        # same weights, same arithmetic up to the summation order of the multi-row kernels and bf16 KV
+        assert np.abs(got[r] - want_single).max() <= 2e-3 * max(1.0, np.abs(want_single).max()), (r, np.abs(got[r] - want_single).max())
+        if r in (1, 3):
+            om = OracleModel(oracle, synth)
+            err = logits_ok(got[r], om.forward(ids, 0))
+        srt = np.sort(want_single)
+        if srt[-1] - srt[-2] > 1e-2:
+            assert nxt[r] == nxt_single
+        streams.append(one.generate(int(nxt_single), len(ids), n_gen))
+    # KV rows written by the batched step land in the right stream and slot
+    for r in (1, 4):
+        gm.select_sequence(r)
+        one.prefill(prompts[r], 0, want_logits=False)
+        for want_v in (0, 1):
+            assert np.array_equal(gm.read_kv(cfg.n_layer - 1, int(pos[r]), want_v), one.read_kv(cfg.n_layer - 1, int(pos[r]), want_v)) or \
+                np.abs(gm.read_kv(cfg.n_layer - 1, int(pos[r]), want_v) - one.read_kv(cfg.n_layer - 1, int(pos[r]), want_v)).max() <= 2 ** -7
+    gm.select_sequence(0)
+    # device-resident loop over the batch, against the single-sequence greedy streams
+    out = gm.generate_batch(nxt, pos + 1, n_gen)
+    assert out.shape == (n_gen, B)
+    for r in range(B):
+        single = streams[r]
+        agree = 0
+        while agree < n_gen and out[agree, r] == single[agree]:
+            agree += 1
+        if agree < n_gen:
+            # a divergence must sit on a near-tie of the single-sequence logits at that step
+            hist = np.concatenate([prompts[r], [nxt[r]], single[:agree]]).astype(np.int32)
+            lg, _ = one.prefill(hist, 0)
+            srt = np.sort(lg)
+            assert srt[-1] - srt[-2] <= 1e-2, (r, agree, srt[-1] - srt[-2])
+    # a second call reuses the captured step and a smaller batch captures its own
+    out2 = gm.generate_batch(nxt, pos + 1, n_gen)
+    assert np.array_equal(out, out2)
+    out3 = gm.generate_batch(nxt[:2], pos[:2] + 1, n_gen)
+    assert np.array_equal(out3, out[:, :2])
+    # argument errors
+    from ggnpu_b200.backend import BackendError
+    with pytest.raises(BackendError):
+        gm.decode_batch(np.zeros(B + 1, np.int32), np.zeros(B + 1, np.int32))
+    with pytest.raises(BackendError):
+        gm.decode_batch(toks, np.full(B, cfg.ctx, np.int32))
+    with pytest.raises(BackendError):
+        one.generate_batch(toks[:1], pos[:1], 2)
+    gm.close()
+    one.close()
+
+
 def ref_lookup_draft(seq, ngram_max, ngram_min, k):
     """The reference's drafter, src/cli/main.cpp:397-415, restated for the test."""
     n = len(seq)
