@@ -587,6 +587,17 @@ static int dispatch(Context* c, const GemvArgs& a, cudaStream_t s) {
     }
 }
 
+// Grow the workspace for split-K / K-slice partial sums (never inside a stream capture: callers run one eager pass first).
+static int ensure_ws(Context* c, size_t floats, cudaStream_t s) {
+    if (floats <= c->d_ws_floats) return GGB_OK;
+    cudaStreamSynchronize(s);
+    if (c->d_ws) cudaFree(c->d_ws);
+    c->d_ws = nullptr; c->d_ws_floats = 0;
+    if (cuda_status(c, cudaMalloc(&c->d_ws, floats * sizeof(float)), "cudaMalloc(partial sums)") != GGB_OK) return c->last_status;
+    c->d_ws_floats = floats;
+    return GGB_OK;
+}
+
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
     if ((!a.x && !a.attn_partial && !a.x_img) || (!a.y && !a.y_img) || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
     if (a.attn_partial && (a.w.layout != 1 || a.M != 1)) return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input needs the tensor-core layout and M == 1");
@@ -602,21 +613,15 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
             if (cuda_status(c, cudaMalloc(&c->d_xb, need * 2), "cudaMalloc(fp16 activations)") != GGB_OK) return c->last_status;
             c->d_xb_elems = need;
         }
-        const size_t need_ws = gemm_tc_ws_floats(a);
-        if (need_ws > c->d_ws_floats) {
-            cudaStreamSynchronize(s);
-            if (c->d_ws) cudaFree(c->d_ws);
-            c->d_ws = nullptr; c->d_ws_floats = 0;
-            if (cuda_status(c, cudaMalloc(&c->d_ws, need_ws * sizeof(float)), "cudaMalloc(split-K partial sums)") != GGB_OK) return c->last_status;
-            c->d_ws_floats = need_ws;
-        }
+        if (ensure_ws(c, gemm_tc_ws_floats(a), s) != GGB_OK) return c->last_status;
         const int st = launch_gemm_tc(c, a, c->d_xb, c->d_xb_elems, c->d_ws, c->d_ws_floats, s);
         if (st != GGB_NOT_FOUND) return st;
     }
     if (a.x_img || a.y_img) return set_status(c, GGB_INVALID_PARAM, "gemv: tile-image operands need the tensor-core GEMM");
     if (a.w.layout == 1 && a.M >= 3 && a.M <= 16) {
         // up to 16 activation rows in one pass over the weights
-        const int st = launch_gemv_mma_rows(c, a, s);
+        if (ensure_ws(c, gemv_mma_rows_ws_floats(a), s) != GGB_OK) return c->last_status;
+        const int st = launch_gemv_mma_rows(c, a, c->d_ws, c->d_ws_floats, s);
         if (st != GGB_NOT_FOUND) return st;
     }
     if (a.w.layout == 1) {

@@ -10,8 +10,10 @@
 // limb-0 column of each row (its weight is 1), so the three columns of a row simply add up.  At the end of a row group
 // every warp drops its column sums into a shared-memory slab; the team's first warp adds slabs and limb columns, applies
 // the epilogue and stores.
-// Shared memory bounds the rows per pass: 3 planes of K + 16 bytes per row (M = 16 at K = 2048, 8 at 4096, 4 at 8192);
-// the launcher cuts M into such chunks.  Eight warps, each with its own ring of bulk-copy stages: a warp requests the tile one
+// Shared memory bounds rows x K: 3 planes of K + 16 bytes per row (16 rows at K = 2048, 8 at 4096).  A longer K is cut
+// into slices of whole 256-blocks along grid.y: CTA (x, y) covers its row groups over slice y only, so the matrix is
+// still streamed once; the slices' partial sums go to a workspace [slice][matrix][m][N] and a small second kernel adds
+// them in slice order and applies the epilogue.  Eight warps, each with its own ring of bulk-copy stages: a warp requests the tile one
 // ring length ahead whenever it has consumed one (no producer warp, so 256 threads and the full register file per thread).
 #include "ggb_internal.h"
 
@@ -83,7 +85,9 @@ struct RowsArgs {
     const float* gamma;
     float eps;
     int M, lda, ldc, epi;
-    int sb, spr, nmat, groups, ws, P, stage_bytes;
+    int sb, nmat, groups, ws, P, stage_bytes;
+    int kbs;              // 256-blocks of K per slice (grid.y slices); nb when K is not cut
+    float* part;          // K cut into slices: partial sums [slice][matrix][m][N], epilogue in rows_reduce_kernel; else nullptr
     int* err;
 };
 
@@ -95,9 +99,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ float inv_s[16];
-    const int K = a.w.K, nb = a.w.nb, M = a.M;
+    const int nb = a.w.nb, M = a.M;
+    const int kb0 = blockIdx.y * a.kbs, nbs = min(a.kbs, nb - kb0);      // this CTA's slice of K: blocks [kb0, kb0 + nbs)
+    const int K = a.kbs * 256;                         // capacity of the slice-local activation arrays
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tprg = NMAT * a.spr;
+    const int spr = (nbs + a.sb - 1) / a.sb;           // tiles per row group and matrix
+    const int tprg = NMAT * spr;
     const int plane_stride = K + 16;
     uint8_t* ring = smem;
     int8_t* xl = reinterpret_cast<int8_t*>(ring + static_cast<size_t>(kWarps) * a.P * a.stage_bytes);
@@ -126,11 +133,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
         if (rg_i >= n_rg) return;
         const int s = warp * a.P + st_i;
         if (lane == 0) {
-            const int mat = ti_i >= a.spr, sl = ti_i - mat * a.spr;
-            const int b0 = sl * a.sb, nbk = min(a.sb, nb - b0);
+            const int mat = ti_i >= spr, sl = ti_i - mat * spr;
+            const int b0 = sl * a.sb, nbk = min(a.sb, nbs - b0);
             uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
             const PackedW& w = mat ? a.w2 : a.w;
-            const int64_t gb = (g_begin + rg_i) * nb + b0;
+            const int64_t gb = (g_begin + rg_i) * nb + kb0 + b0;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
             if (!is_q6) {
                 mbar_expect_tx(&full_bar[s], static_cast<uint32_t>(nbk) * 2304u);
@@ -175,7 +182,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
     // One pass over x: limbs of x * gamma, run sums, sum of squares (the RMS factor is applied at the end).  The (row,
     // 256-block) items are dealt to the warps in batches of eight whose loads are all issued before the first conversion:
     // sixteen rows would otherwise cost a warp sixteen dependent round trips to L2.
-    const int nblk = K >> 8, items = M * nblk;
+    // (blocks of K outside this CTA's slice only add to the sum of squares)
+    const int nblk = nb, items = M * nblk;
     float* ssb = slab;                                  // per-item sums of squares (the slabs are not in use yet)
     for (int it0 = warp; it0 < items; it0 += 8 * kWarps) {
         float v[8][8];
@@ -184,6 +192,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
             const int it = it0 + u * kWarps;
             if (it < items) {
                 const int m = it / nblk, b = it - m * nblk;
+                if (!a.gamma && (b < kb0 || b >= kb0 + nbs)) continue;
                 const float* xr = a.x + static_cast<size_t>(m) * a.lda + b * 256 + lane * 8;
                 const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
                 v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
@@ -194,12 +203,18 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
             const int it = it0 + u * kWarps;
             if (it < items) {
                 const int m = it / nblk, b = it - m * nblk;
-                const int k0 = b * 256 + lane * 8;
+                const bool mine = b >= kb0 && b < kb0 + nbs;
+                if (!a.gamma && !mine) continue;
+                const int kg = b * 256 + lane * 8;              // position in the full row
+                const int k0 = (b - kb0) * 256 + lane * 8;      // position in the slice-local arrays
                 float ss = 0.0f;
                 if (a.gamma) {
-                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4));
 #pragma unroll
                     for (int i = 0; i < 8; ++i) ss = fmaf(v[u][i], v[u][i], ss);
+                    ss = wsum(ss);
+                    if (lane == 0) ssb[it] = ss;
+                    if (!mine) continue;
+                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + kg)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + kg + 4));
                     v[u][0] *= g0.x; v[u][1] *= g0.y; v[u][2] *= g0.z; v[u][3] *= g0.w; v[u][4] *= g1.x; v[u][5] *= g1.y; v[u][6] *= g1.z; v[u][7] *= g1.w;
                 }
                 float am = 0.0f, sm = 0.0f;
@@ -225,21 +240,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                 *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
                 *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
                 *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
-                if (lane == 0) xs[m * nblk + b] = am / 127.0f;
+                if (lane == 0) xs[m * (K >> 8) + (b - kb0)] = am / 127.0f;
                 sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
                 if ((lane & 1) == 0) asum16[m * (K >> 4) + (k0 >> 4)] = sm;
                 sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
                 if ((lane & 3) == 0) asum[m * (K >> 5) + (k0 >> 5)] = sm;
-                ss = wsum(ss);
-                if (lane == 0) ssb[it] = ss;
             }
         }
     }
     consumer_sync();
     if (threadIdx.x < M) {                              // fixed summation order: the result does not depend on warp timing
         float tot = 0.0f;
-        for (int b = 0; b < nblk; ++b) tot += ssb[threadIdx.x * nblk + b];
-        inv_s[threadIdx.x] = a.gamma ? 1.0f / sqrtf(tot / static_cast<float>(K) + a.eps) : 1.0f;
+        if (a.gamma) for (int b = 0; b < nblk; ++b) tot += ssb[threadIdx.x * nblk + b];
+        inv_s[threadIdx.x] = a.gamma ? 1.0f / sqrtf(tot / static_cast<float>(a.w.K) + a.eps) : 1.0f;
     }
     consumer_sync();
 
@@ -261,8 +274,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
             if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
             if (++st == a.P) { st = 0; ph ^= 1; }
             if (!ok) continue;
-            const int mat = ti >= a.spr, sl = ti - mat * a.spr;
-            const int b0 = sl * a.sb, nbk = min(a.sb, nb - b0);
+            const int mat = ti >= spr, sl = ti - mat * spr;
+            const int b0 = sl * a.sb, nbk = min(a.sb, nbs - b0);      // b, b0: block index inside the slice
             const uint8_t* qsT = ring + static_cast<size_t>(s) * a.stage_bytes;
             const uint8_t* s1T = qsT + a.sb * 2048;
             float f[CG][4];
@@ -439,7 +452,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                 }
                 v *= inv_s[m]; v2 *= inv_s[m];
                 const int64_t row = (g_begin + rg) * 16 + r;
-                if (row < a.w.N) {
+                if (row < a.w.N && a.part) {              // a slice of K: bare partial sums, the epilogue follows the reduction
+                    const size_t plane = static_cast<size_t>(M) * a.w.N;
+                    float* pz = a.part + static_cast<size_t>(blockIdx.y) * NMAT * plane + static_cast<size_t>(m) * a.w.N + row;
+                    pz[0] = v;
+                    if (NMAT == 2) pz[plane] = v2;
+                } else if (row < a.w.N) {
                     const size_t o = static_cast<size_t>(m) * a.ldc + row;
                     if (NMAT == 2) v = (v / (1.0f + expf(-v))) * v2;
                     else if (a.epi == EPI_ADD_BIAS && a.bias) v += __ldg(a.bias + row);
@@ -453,8 +471,49 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
     }
 }
 
+// y = epilogue(sum over the K slices, in slice order, of the partial sums); one thread per output element.
+__global__ void rows_reduce_kernel(const float* __restrict__ part, int slices, int nmat, int M, int64_t N, int epi,
+                                   const float* __restrict__ bias, const float* resid, float* y, int ldc) {
+    pdl_wait();
+    pdl_launch();
+    const size_t plane = static_cast<size_t>(M) * N;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < plane; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int m = static_cast<int>(i / N);
+        const int64_t n = static_cast<int64_t>(i - static_cast<size_t>(m) * N);
+        float v = 0.0f, v2 = 0.0f;
+        for (int z = 0; z < slices; ++z) {
+            const float* p = part + static_cast<size_t>(z) * nmat * plane;
+            v += p[i];
+            if (nmat == 2) v2 += p[plane + i];
+        }
+        const size_t o = static_cast<size_t>(m) * ldc + n;
+        if (nmat == 2) v = (v / (1.0f + expf(-v))) * v2;
+        else if (epi == EPI_ADD_BIAS && bias) v += __ldg(bias + n);
+        else if (epi == EPI_RESIDUAL) v += resid[o];
+        y[o] = v;
+    }
+}
+
+// Shared memory of one CTA for mc rows over kbs blocks of K, without the ring.
+size_t rows_fixed_bytes(int mc, int kbs, int nmat, int cg) {
+    const int K = kbs * 256;
+    return static_cast<size_t>(3 * mc) * (K + 16) + sizeof(float) * (mc * (K / 32 + K / 16) + ((mc * (K / 256) + 3) & ~3)) +
+           sizeof(float) * kWarps * nmat * 16 * 8 * cg + 64;
+}
+constexpr size_t kRowsBudget = 216 * 1024;
+
+// Slices of K: the fewest whose activation arrays leave room for a ring of three 1-block stages per warp.
+int rows_slices(int nb, int mc, int nmat, int cg) {
+    for (int S = 1; S <= nb; ++S) {
+        const int kbs = (nb + S - 1) / S;
+        if (rows_fixed_bytes(mc, kbs, nmat, cg) + static_cast<size_t>(kWarps) * 3 * 3360 <= kRowsBudget) return S;
+    }
+    return 0;
+}
+
 template <int CG>
-int launch_rows_t(Context* c, const GemvArgs& g, int m0, int mc, cudaStream_t s) {
+int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+    const int m0 = 0, mc = g.M;
     constexpr int kThreads = kWarps * 32;
     const int K = g.w.K, nb = g.w.nb;
     const bool dual = g.epi == EPI_SWIGLU;
@@ -462,20 +521,25 @@ int launch_rows_t(Context* c, const GemvArgs& g, int m0, int mc, cudaStream_t s)
     const int nmat = dual ? 2 : 1;
     const int groups = static_cast<int>((g.w.N + 15) / 16);
     const int gb_bytes = q6 ? 3360 : 2304;
-    const int G = std::min(c->sm_count, groups);
+    const int S = rows_slices(nb, mc, nmat, CG);
+    if (S < 1) return GGB_NOT_FOUND;
+    const int kbs = (nb + S - 1) / S;
+    const int slices = (nb + kbs - 1) / kbs;
+    if (slices > 1 && static_cast<size_t>(slices) * nmat * mc * g.w.N > part_floats) return GGB_NOT_FOUND;
+    if (static_cast<size_t>(mc) * nb > static_cast<size_t>(kWarps) * nmat * 16 * 8 * CG) return GGB_NOT_FOUND;      // per-block sums of squares borrow the slabs
+    const int G = std::min(std::max(1, c->sm_count / slices), groups);
     const int gpc = (groups + G - 1) / G;
     int ws = 1;
     while (ws < kWarps && gpc * ws < kWarps) ws <<= 1;
-    const size_t fixed = static_cast<size_t>(3 * mc) * (K + 16) + sizeof(float) * (mc * (K / 32 + K / 16) + ((mc * (K / 256) + 3) & ~3)) +
-                         sizeof(float) * kWarps * nmat * 16 * 8 * CG + 64;
-    const size_t budget = 216 * 1024;
+    const size_t fixed = rows_fixed_bytes(mc, kbs, nmat, CG);
+    const size_t budget = kRowsBudget;
     // tile depth 1..2 blocks, ring as deep as the rest of shared memory allows (at least two stages per warp)
     int sb = 2;
-    while (sb > 1 && nmat * ((nb + sb - 1) / sb) < ws) sb >>= 1;
-    sb = std::min(sb, nb);
+    while (sb > 1 && nmat * ((kbs + sb - 1) / sb) < ws) sb >>= 1;
+    sb = std::min(sb, kbs);
     int spr, stage_bytes, P;
     for (;;) {
-        spr = (nb + sb - 1) / sb;
+        spr = (kbs + sb - 1) / sb;
         stage_bytes = sb * gb_bytes;
         const int tiles_per_warp = ((gpc + kWarps / ws - 1) / (kWarps / ws)) * ((nmat * spr + ws - 1) / ws);
         P = std::min(kMaxStages / kWarps, std::max(2, tiles_per_warp));
@@ -490,54 +554,55 @@ int launch_rows_t(Context* c, const GemvArgs& g, int m0, int mc, cudaStream_t s)
     a.w = g.w; a.w2 = g.w2; a.x = g.x + static_cast<size_t>(m0) * g.lda; a.y = g.y + static_cast<size_t>(m0) * g.ldc;
     a.bias = g.bias; a.resid = g.resid ? g.resid + static_cast<size_t>(m0) * g.ldc : nullptr; a.gamma = g.gamma; a.eps = g.eps;
     a.M = mc; a.lda = g.lda; a.ldc = g.ldc; a.epi = g.epi;
-    a.sb = sb; a.spr = spr; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
+    a.sb = sb; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
+    a.kbs = kbs; a.part = slices > 1 ? d_part : nullptr;
     a.err = c->d_err;
     void (*kern)(const RowsArgs) = dual ? gemv_mma_rows_kernel<CG, 2> : gemv_mma_rows_kernel<CG, 1>;
     cudaError_t e = ensure_dynamic_smem(c, kern, smem);
     if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma_rows attr");
-    e = launch_pdl(c, kern, dim3(static_cast<unsigned>(G)), dim3(kThreads), smem, s, a);
+    e = launch_pdl(c, kern, dim3(static_cast<unsigned>(G), static_cast<unsigned>(slices)), dim3(kThreads), smem, s, a);
     c->launches++;
-    return cuda_status(c, e, "gemv_mma_rows launch");
+    if (e != cudaSuccess || slices == 1) return cuda_status(c, e, "gemv_mma_rows launch");
+    const size_t elems = static_cast<size_t>(mc) * g.w.N;
+    e = launch_pdl(c, rows_reduce_kernel, dim3(static_cast<unsigned>(std::min<size_t>((elems + 255) / 256, 148 * 8))), dim3(256), 0, s,
+                   static_cast<const float*>(d_part), slices, nmat, mc, g.w.N, g.epi, g.bias, g.resid, g.y, g.ldc);
+    c->launches++;
+    return cuda_status(c, e, "gemv_mma_rows reduce");
 }
 
 }  // namespace
 
-// Rows per pass that fit shared memory beside a ring of two stages per warp: 3 limb planes + run sums per row.
-static int rows_per_pass(int K, bool dual) {
-    const size_t per_row = static_cast<size_t>(3) * (K + 16) + sizeof(float) * (K / 32 + K / 16 + K / 256);
-    for (int r : {16, 8, 5}) {
-        const int cg = (3 * r + 7) / 8;
-        const size_t fixed = per_row * r + sizeof(float) * kWarps * (dual ? 2 : 1) * 16 * 8 * cg + 64;
-        if (fixed + static_cast<size_t>(kWarps) * 2 * 3360 <= 216 * 1024) return r;
-    }
-    return 0;
+static int rows_cg(int M) { return M <= 5 ? 2 : (M <= 8 ? 3 : 6); }
+
+static bool rows_covered(const GemvArgs& g) {
+    if ((g.w.type != T_Q4_K && g.w.type != T_Q6_K) || g.w.layout != 1 || g.M < 3 || g.M > 16 || g.w.K % 256) return false;
+    if ((reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return false;
+    const bool dual = g.epi == EPI_SWIGLU;
+    if (dual && (g.w2.layout != 1 || g.w2.type != g.w.type)) return false;
+    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return false;
+    return true;
 }
 
-// 3 <= M <= 16 rows of a Q4_K / Q6_K matrix in the row-group-major layout, in as few passes over the weights as shared
-// memory allows.  GGB_NOT_FOUND: shape not covered (the caller falls back to two rows per pass).
-int launch_gemv_mma_rows(Context* c, const GemvArgs& g, cudaStream_t s) {
-    if ((g.w.type != T_Q4_K && g.w.type != T_Q6_K) || g.w.layout != 1 || g.M < 3 || g.M > 16 || g.w.K % 256) return GGB_NOT_FOUND;
-    if ((reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return GGB_NOT_FOUND;
-    const bool dual = g.epi == EPI_SWIGLU;
-    if (dual && (g.w2.layout != 1 || g.w2.type != g.w.type)) return GGB_NOT_FOUND;
-    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return GGB_NOT_FOUND;
-    const int R = rows_per_pass(g.w.K, dual);
-    if (R < 5) return GGB_NOT_FOUND;
-    for (int m0 = 0; m0 < g.M; m0 += R) {
-        const int mc = std::min(R, g.M - m0);
-        int st;
-        if (mc <= 2) {                                   // a tail of one or two rows: the two-row kernel
-            GemvArgs sub = g;
-            sub.M = mc; sub.x = g.x + static_cast<size_t>(m0) * g.lda; sub.y = g.y + static_cast<size_t>(m0) * g.ldc;
-            if (g.resid) sub.resid = g.resid + static_cast<size_t>(m0) * g.ldc;
-            st = launch_gemv_mma(c, sub, s);
-        } else if (mc <= 5) st = launch_rows_t<2>(c, g, m0, mc, s);
-        else if (mc <= 8) st = launch_rows_t<3>(c, g, m0, mc, s);
-        else st = launch_rows_t<6>(c, g, m0, mc, s);
-        if (st == GGB_NOT_FOUND && m0 > 0) return set_status(c, GGB_ERROR, "gemv_mma_rows: a later pass did not fit");
-        if (st != GGB_OK) return st;
+// Floats of workspace launch_gemv_mma_rows needs for g (0: K is not cut, or the shape is not covered).
+size_t gemv_mma_rows_ws_floats(const GemvArgs& g) {
+    if (!rows_covered(g)) return 0;
+    const int nmat = g.epi == EPI_SWIGLU ? 2 : 1;
+    const int S = rows_slices(g.w.nb, g.M, nmat, rows_cg(g.M));
+    if (S <= 1) return 0;
+    const int kbs = (g.w.nb + S - 1) / S, slices = (g.w.nb + kbs - 1) / kbs;
+    return static_cast<size_t>(slices) * nmat * g.M * g.w.N;
+}
+
+// 3 <= M <= 16 rows of a Q4_K / Q6_K matrix in the row-group-major layout in one pass over the weights.
+// d_part: workspace of at least gemv_mma_rows_ws_floats(g) floats.  GGB_NOT_FOUND: shape not covered (the caller falls
+// back to two rows per pass).
+int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+    if (!rows_covered(g)) return GGB_NOT_FOUND;
+    switch (rows_cg(g.M)) {
+    case 2: return launch_rows_t<2>(c, g, d_part, part_floats, s);
+    case 3: return launch_rows_t<3>(c, g, d_part, part_floats, s);
+    default: return launch_rows_t<6>(c, g, d_part, part_floats, s);
     }
-    return GGB_OK;
 }
 
 }  // namespace ggb

@@ -118,7 +118,10 @@ int launch_gather_rows(Context* c, const PackedW& w, const int32_t* d_rows, int 
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s);
 int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
-int launch_gemv_mma_rows(Context* c, const GemvArgs& a, cudaStream_t s);   // 3..16 rows per pass; GGB_NOT_FOUND: shape not covered
+// 3..16 rows in one pass over the weights; d_part: gemv_mma_rows_ws_floats(a) floats of workspace (K cut into slices).
+// GGB_NOT_FOUND: shape not covered
+int launch_gemv_mma_rows(Context* c, const GemvArgs& a, float* d_part, size_t part_floats, cudaStream_t s);
+size_t gemv_mma_rows_ws_floats(const GemvArgs& a);
 int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
 int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, float* d_ws, size_t ws_floats, cudaStream_t s);
@@ -168,6 +171,7 @@ int launch_matmul_f32_kn(Context* c, const float* A, const float* B, float* C, i
 int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, int hd, cudaStream_t s);
 int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s);
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
+int launch_argmax_rows(Context* c, const float* x, int n, int64_t ld, int rows, int32_t* d_out, float* d_partial, cudaStream_t s);
 
 // ggb_sample.cu: temperature sampling (src/cli/main.cpp:839-864) on logits in HBM
 size_t sample_scratch_bytes(int n);

@@ -238,11 +238,9 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x, n_tok, H, m->logits_rows + static_cast<size_t>(c->tp_rank) * vocab_l, d.vocab);
         a.gamma = m->output_norm; a.eps = d.rms_eps;
         M_TRY(launch_gemv(c, a, s));
-        for (int r = 0; r < n_tok; ++r) {
-            if (c->tp_size > 1) M_TRY(tp_all_gather_in_place(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, static_cast<size_t>(vocab_l), s));
-            M_TRY(launch_argmax(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, d.vocab, m->d_rows_next + r, m->amax_partial, s));
-        }
-        return GGB_OK;
+        if (c->tp_size > 1)
+            for (int r = 0; r < n_tok; ++r) M_TRY(tp_all_gather_in_place(c, m->logits_rows + static_cast<size_t>(r) * d.vocab, static_cast<size_t>(vocab_l), s));
+        return launch_argmax_rows(c, m->logits_rows, d.vocab, d.vocab, n_tok, m->d_rows_next, m->amax_partial, s);
     }
     GemvArgs a = gemv_args(m->output ? m->output : m->tok_embd, m->x + static_cast<size_t>(n_tok - 1) * H, 1, H,
                            m->logits + static_cast<size_t>(c->tp_rank) * vocab_l, vocab_l);

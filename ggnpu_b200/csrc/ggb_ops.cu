@@ -211,9 +211,12 @@ int launch_matmul_f32_kn(Context* c, const float* A, const float* B, float* C, i
 
 // Greedy sampling (sample_token, src/cli/main.cpp:827-838): the FIRST index holding the maximum.
 // Two passes: per-CTA (max, first index) into d_partial, then one CTA combines.
-__global__ void argmax_pass1(const float* __restrict__ x, int n, float* __restrict__ pmax, int32_t* __restrict__ pidx) {
+// blockIdx.y = row of a [rows][ld] matrix (one row: ld unused); partials of row r at [r * gridDim.x ..).
+__global__ void argmax_pass1(const float* __restrict__ x, int n, int64_t ld, float* __restrict__ pmax, int32_t* __restrict__ pidx) {
     __shared__ float smax[32];
     __shared__ int sidx[32];
+    x += static_cast<size_t>(blockIdx.y) * ld;
+    pmax += blockIdx.y * gridDim.x; pidx += blockIdx.y * gridDim.x;
     float best = -INFINITY; int bi = 0x7FFFFFFF;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float v = x[i];
@@ -234,6 +237,7 @@ __global__ void argmax_pass1(const float* __restrict__ x, int n, float* __restri
     }
 }
 __global__ void argmax_pass2(const float* __restrict__ pmax, const int32_t* __restrict__ pidx, int parts, int32_t* __restrict__ out) {
+    pmax += blockIdx.x * parts; pidx += blockIdx.x * parts; out += blockIdx.x;
     float best = -INFINITY; int bi = 0x7FFFFFFF;
     for (int i = threadIdx.x; i < parts; i += 32) {
         const float v = pmax[i]; const int ix = pidx[i];
@@ -250,8 +254,17 @@ __global__ void argmax_pass2(const float* __restrict__ pmax, const int32_t* __re
 // d_partial must hold 2 * 256 words.
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s) {
     const int parts = std::min(256, (n + 1023) / 1024);
-    argmax_pass1<<<parts, 256, 0, s>>>(x, n, d_partial, reinterpret_cast<int32_t*>(d_partial) + 256);
+    argmax_pass1<<<parts, 256, 0, s>>>(x, n, 0, d_partial, reinterpret_cast<int32_t*>(d_partial) + 256);
     argmax_pass2<<<1, 32, 0, s>>>(d_partial, reinterpret_cast<const int32_t*>(d_partial) + 256, parts, d_out);
+    c->launches += 2;
+    return cuda_status(c, cudaGetLastError(), "argmax");
+}
+// The same for each of `rows` (<= 16) rows of a [rows][ld] matrix in one pair of launches: d_out[r] = first maximum of row r.
+int launch_argmax_rows(Context* c, const float* x, int n, int64_t ld, int rows, int32_t* d_out, float* d_partial, cudaStream_t s) {
+    if (rows < 1 || rows > 16) return set_status(c, GGB_INVALID_PARAM, "argmax: 1 to 16 rows");
+    const int parts = std::min(16, (n + 1023) / 1024);
+    argmax_pass1<<<dim3(parts, rows), 256, 0, s>>>(x, n, ld, d_partial, reinterpret_cast<int32_t*>(d_partial) + 256);
+    argmax_pass2<<<rows, 32, 0, s>>>(d_partial, reinterpret_cast<const int32_t*>(d_partial) + 256, parts, d_out);
     c->launches += 2;
     return cuda_status(c, cudaGetLastError(), "argmax");
 }

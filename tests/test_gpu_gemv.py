@@ -148,18 +148,20 @@ def test_rows_kernel_every_chunk_size(backend, oracle, t, M):
     check(backend, oracle, t, 1024, 2048, M, seed=M + 2, sample_rows=40)
 
 
-@pytest.mark.parametrize("K", [2048, 4096, 8192])
-def test_rows_kernel_row_chunks_by_k(backend, oracle, K):
-    """Shared memory holds the limb planes of 16 rows at K = 2048, 8 at 4096, 5 at 8192: M = 16 then takes 1, 2 or 4
-    passes (the last chunk of the K = 8192 case has a single row, which the two-row kernel takes)."""
+@pytest.mark.parametrize("K", [2048, 4096, 5632, 8192, 14336])
+def test_rows_kernel_k_slices(backend, oracle, K):
+    """Shared memory holds the limb planes of 16 rows over 2048 values of K: a longer K is cut into slices along the grid
+    (2, 3 with a shorter last slice, 4 and 7 here), whose partial sums a second kernel adds; M = 11 fits longer slices."""
     for t in (S.Q4_K, S.Q6_K):
         check(backend, oracle, t, 512, K, 16, seed=K, sample_rows=40)
         check(backend, oracle, t, 512, K, 11, seed=K + 1, sample_rows=40)
 
 
-def test_rows_kernel_fused_epilogues(backend, oracle):
-    """RMSNorm prologue, bias, residual (in place) and the SwiGLU pair at M = 7 and 16 on device pointers."""
-    t, N, K = S.Q4_K, 208, 1024
+@pytest.mark.parametrize("K", [1024, 5632])
+def test_rows_kernel_fused_epilogues(backend, oracle, K):
+    """RMSNorm prologue, bias, residual (in place) and the SwiGLU pair at M = 7 and 16 on device pointers; K = 5632 is
+    cut into three slices (8, 8 and 6 super-blocks) whose CTAs all need the whole row's sum of squares."""
+    t, N = S.Q4_K, 208
     wg, wu = make(t, N, K, 1), make(t, N, K, 2)
     dev = torch.device("cuda:0")
     hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
