@@ -777,7 +777,7 @@ def run_tp(args):
             "gpu_launches": r["gpu_launches"], "prefill": {"tokens": r["prefill_tokens"], "tok_per_s": r["prefill_tok_s"]},
             "decode_step": {"algorithmic_bytes_per_rank": r["algorithmic_bytes_per_rank"], "achieved_gbs_per_rank": r["achieved_gbs_per_rank"],
                             "frac_of_hbm_peak": r["frac_of_hbm_peak"], "peak_source": r["peak_source"]},
-            "model_build_s": r["model_build_s"]}), flush=True)
+            "batch": r.get("batch"), "model_build_s": r["model_build_s"]}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -131,6 +131,7 @@ void ggb_destroy(ggb_handle h) {
     for (int i = 0; i < 4; ++i) if (h->d_scratch[i]) cudaFree(h->d_scratch[i]);
     if (h->d_xb) cudaFree(h->d_xb);
     if (h->d_ws) cudaFree(h->d_ws);
+    if (h->d_limbs) cudaFree(h->d_limbs);
     if (h->h_pinned) cudaFreeHost(h->h_pinned);
     if (h->d_err) cudaFree(h->d_err);
     cudaStreamDestroy(h->stream);

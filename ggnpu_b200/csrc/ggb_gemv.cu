@@ -599,6 +599,7 @@ static int ensure_ws(Context* c, size_t floats, cudaStream_t s) {
 }
 
 int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
+    c->gemv_calls++;
     if ((!a.x && !a.attn_partial && !a.x_img) || (!a.y && !a.y_img) || a.M <= 0 || a.w.N <= 0 || a.w.K <= 0) return set_status(c, GGB_INVALID_PARAM, "gemv: bad arguments");
     if (a.attn_partial && (a.w.layout != 1 || a.M != 1)) return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input needs the tensor-core layout and M == 1");
     if (a.x && ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.lda & 3))) return set_status(c, GGB_INVALID_PARAM, "gemv: x must be 16-byte aligned with lda % 4 == 0");
@@ -621,7 +622,16 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
     if (a.w.layout == 1 && a.M >= 3 && a.M <= 16) {
         // up to 16 activation rows in one pass over the weights
         if (ensure_ws(c, gemv_mma_rows_ws_floats(a), s) != GGB_OK) return c->last_status;
-        const int st = launch_gemv_mma_rows(c, a, c->d_ws, c->d_ws_floats, s);
+        const size_t lb = gemv_mma_rows_limbs_bytes(a.M, a.w.K);
+        if (lb > c->d_limbs_bytes) {
+            c->limbs_x = nullptr;
+            cudaStreamSynchronize(s);
+            if (c->d_limbs) cudaFree(c->d_limbs);
+            c->d_limbs = nullptr; c->d_limbs_bytes = 0;
+            if (cuda_status(c, cudaMalloc(&c->d_limbs, lb), "cudaMalloc(activation limbs)") != GGB_OK) return c->last_status;
+            c->d_limbs_bytes = lb;
+        }
+        const int st = launch_gemv_mma_rows(c, a, c->d_ws, c->d_ws_floats, c->d_limbs, c->d_limbs_bytes, s);
         if (st != GGB_NOT_FOUND) return st;
     }
     if (a.w.layout == 1) {

@@ -76,6 +76,96 @@ __device__ __forceinline__ float wsum(float v) {
     return v;
 }
 
+// The activations of one call, converted once by rows_prep_kernel and bulk-copied by every GEMV CTA:
+//   planes int8 [M][3][K] (limbs of x * gamma, one scale per 256-block) | asum float [M][K / 32] | asum16 float [M][K / 16]
+//   | xs float [M][K / 256] (block scales) | inv_s float [16] (RMS factors; 1 without gamma)
+struct LimbImage {
+    size_t planes, asum, asum16, xs, inv_s, bytes;
+    __host__ __device__ LimbImage(int M, int K) {
+        planes = 0;
+        asum = static_cast<size_t>(3) * M * K;
+        asum16 = asum + sizeof(float) * static_cast<size_t>(M) * (K >> 5);
+        xs = asum16 + sizeof(float) * static_cast<size_t>(M) * (K >> 4);
+        inv_s = (xs + sizeof(float) * static_cast<size_t>(M) * (K >> 8) + 15) & ~static_cast<size_t>(15);
+        bytes = inv_s + 64;
+    }
+};
+
+// grid (M), 256 threads: row m.  Warp w converts the 256-blocks w, w + 8, ...: limbs of x * gamma, run sums, the block's
+// sum of squares; thread 0 then adds the sums of squares in block order (so the factor does not depend on timing).
+__global__ void __launch_bounds__(256) rows_prep_kernel(const float* __restrict__ x, int lda, int M, int K, const float* __restrict__ gamma, float eps,
+                                                         uint8_t* __restrict__ img) {
+    extern __shared__ float ssb[];                      // [K / 256]
+    const LimbImage L(M, K);
+    const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nblk = K >> 8;
+    int8_t* planes = reinterpret_cast<int8_t*>(img + L.planes) + static_cast<size_t>(3 * m) * K;
+    float* asum = reinterpret_cast<float*>(img + L.asum) + static_cast<size_t>(m) * (K >> 5);
+    float* asum16 = reinterpret_cast<float*>(img + L.asum16) + static_cast<size_t>(m) * (K >> 4);
+    float* xs = reinterpret_cast<float*>(img + L.xs) + static_cast<size_t>(m) * nblk;
+    pdl_wait();                                         // x is the predecessor's output; the image may still be read by it
+    pdl_launch();
+    for (int b0 = warp; b0 < nblk; b0 += 4 * 8) {       // four blocks per warp in flight
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int b = b0 + 8 * u;
+            if (b < nblk) {
+                const float* xr = x + static_cast<size_t>(m) * lda + b * 256 + lane * 8;
+                const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
+                v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int b = b0 + 8 * u;
+            if (b >= nblk) continue;
+            const int k0 = b * 256 + lane * 8;
+            if (gamma) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss = fmaf(v[u][i], v[u][i], ss);
+                ss = wsum(ss);
+                if (lane == 0) ssb[b] = ss;
+                const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + k0 + 4));
+                v[u][0] *= g0.x; v[u][1] *= g0.y; v[u][2] *= g0.z; v[u][3] *= g0.w; v[u][4] *= g1.x; v[u][5] *= g1.y; v[u][6] *= g1.z; v[u][7] *= g1.w;
+            }
+            float am = 0.0f, sm = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { am = fmaxf(am, fabsf(v[u][i])); sm += v[u][i]; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+            const float rs = am > 0.0f ? 127.0f / am : 0.0f;
+            uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float kMagic = 12582912.0f;           // 1.5 * 2^23: round to nearest, the integer lands in the low mantissa bits
+                const float r = fminf(fmaxf(v[u][i] * rs, -127.0f), 127.0f);
+                const float t1 = r + kMagic;
+                const float r2 = (r - (t1 - kMagic)) * 128.0f;
+                const float t2 = r2 + kMagic;
+                const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
+                w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
+                w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
+                w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
+            }
+            *reinterpret_cast<uint2*>(planes + k0) = make_uint2(w1[0], w1[1]);
+            *reinterpret_cast<uint2*>(planes + K + k0) = make_uint2(w2[0], w2[1]);
+            *reinterpret_cast<uint2*>(planes + 2 * static_cast<size_t>(K) + k0) = make_uint2(w3[0], w3[1]);
+            if (lane == 0) xs[b] = am / 127.0f;
+            sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
+            if ((lane & 1) == 0) asum16[k0 >> 4] = sm;
+            sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
+            if ((lane & 3) == 0) asum[k0 >> 5] = sm;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.0f;
+        if (gamma) for (int b = 0; b < nblk; ++b) tot += ssb[b];
+        reinterpret_cast<float*>(img + L.inv_s)[m] = gamma ? 1.0f / sqrtf(tot / static_cast<float>(K) + eps) : 1.0f;
+    }
+}
+
 struct RowsArgs {
     PackedW w, w2;
     const float* x;
@@ -86,6 +176,7 @@ struct RowsArgs {
     float eps;
     int M, lda, ldc, epi;
     int sb, nmat, groups, ws, P, stage_bytes;
+    const uint8_t* img;   // activation image written by rows_prep_kernel (layout: LimbImage)
     int kbs;              // 256-blocks of K per slice (grid.y slices); nb when K is not cut
     float* part;          // K cut into slices: partial sums [slice][matrix][m][N], epilogue in rows_reduce_kernel; else nullptr
     int* err;
@@ -97,7 +188,7 @@ template <int CG, int NMAT>
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const RowsArgs a) {
     constexpr int NC = 8 * CG;                         // B columns
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], x_bar;
     __shared__ float inv_s[16];
     const int nb = a.w.nb, M = a.M;
     const int kb0 = blockIdx.y * a.kbs, nbs = min(a.kbs, nb - kb0);      // this CTA's slice of K: blocks [kb0, kb0 + nbs)
@@ -119,6 +210,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWarps * a.P; ++s) mbar_init(&full_bar[s], 1);
+        mbar_init(&x_bar, kWarps);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -179,86 +271,32 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
         }
     }
     pdl_wait();
-    // One pass over x: limbs of x * gamma, run sums, sum of squares (the RMS factor is applied at the end).  The (row,
-    // 256-block) items are dealt to the warps in batches of eight whose loads are all issued before the first conversion:
-    // sixteen rows would otherwise cost a warp sixteen dependent round trips to L2.
-    // (blocks of K outside this CTA's slice only add to the sum of squares)
-    const int nblk = nb, items = M * nblk;
-    float* ssb = slab;                                  // per-item sums of squares (the slabs are not in use yet)
-    for (int it0 = warp; it0 < items; it0 += 8 * kWarps) {
-        float v[8][8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int it = it0 + u * kWarps;
-            if (it < items) {
-                const int m = it / nblk, b = it - m * nblk;
-                if (!a.gamma && (b < kb0 || b >= kb0 + nbs)) continue;
-                const float* xr = a.x + static_cast<size_t>(m) * a.lda + b * 256 + lane * 8;
-                const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
-                v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
+    // The activation image of this CTA's slice of K: 5 bulk copies per row (3 limb planes, 2 run-sum arrays), dealt to the
+    // warps' first lanes and counted on one barrier; block scales and RMS factors by plain loads.
+    bool ok = true;
+    {
+        const LimbImage L(M, a.w.K);
+        const int Kf = a.w.K, Ks = nbs * 256;
+        if (lane == 0) {
+            uint32_t bytes = 0;
+            for (int it = warp; it < 5 * M; it += kWarps) bytes += it % 5 < 3 ? Ks : (it % 5 == 3 ? Ks >> 3 : Ks >> 2);
+            mbar_expect_tx(&x_bar, bytes);
+            for (int it = warp; it < 5 * M; it += kWarps) {
+                const int m = it / 5, p = it - 5 * m;
+                if (p < 3) bulk_g2s(xl + static_cast<size_t>(3 * m + p) * plane_stride, a.img + L.planes + (static_cast<size_t>(3 * m + p) * Kf + kb0 * 256), Ks, &x_bar);
+                else if (p == 3) bulk_g2s(asum + m * (K >> 5), a.img + L.asum + sizeof(float) * (static_cast<size_t>(m) * (Kf >> 5) + kb0 * 8), Ks >> 3, &x_bar);
+                else bulk_g2s(asum16 + m * (K >> 4), a.img + L.asum16 + sizeof(float) * (static_cast<size_t>(m) * (Kf >> 4) + kb0 * 16), Ks >> 2, &x_bar);
             }
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int it = it0 + u * kWarps;
-            if (it < items) {
-                const int m = it / nblk, b = it - m * nblk;
-                const bool mine = b >= kb0 && b < kb0 + nbs;
-                if (!a.gamma && !mine) continue;
-                const int kg = b * 256 + lane * 8;              // position in the full row
-                const int k0 = (b - kb0) * 256 + lane * 8;      // position in the slice-local arrays
-                float ss = 0.0f;
-                if (a.gamma) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) ss = fmaf(v[u][i], v[u][i], ss);
-                    ss = wsum(ss);
-                    if (lane == 0) ssb[it] = ss;
-                    if (!mine) continue;
-                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + kg)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + kg + 4));
-                    v[u][0] *= g0.x; v[u][1] *= g0.y; v[u][2] *= g0.z; v[u][3] *= g0.w; v[u][4] *= g1.x; v[u][5] *= g1.y; v[u][6] *= g1.z; v[u][7] *= g1.w;
-                }
-                float am = 0.0f, sm = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { am = fmaxf(am, fabsf(v[u][i])); sm += v[u][i]; }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
-                const float rs = am > 0.0f ? 127.0f / am : 0.0f;
-                uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float kMagic = 12582912.0f;           // 1.5 * 2^23: round to nearest, the integer lands in the low mantissa bits
-                    const float r = fminf(fmaxf(v[u][i] * rs, -127.0f), 127.0f);
-                    const float t1 = r + kMagic;
-                    const float r2 = (r - (t1 - kMagic)) * 128.0f;
-                    const float t2 = r2 + kMagic;
-                    const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
-                    w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
-                    w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
-                    w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
-                }
-                int8_t* pl = xl + static_cast<size_t>(3 * m) * plane_stride + k0;
-                *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
-                *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
-                *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
-                if (lane == 0) xs[m * (K >> 8) + (b - kb0)] = am / 127.0f;
-                sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 1);
-                if ((lane & 1) == 0) asum16[m * (K >> 4) + (k0 >> 4)] = sm;
-                sm += __shfl_xor_sync(0xFFFFFFFFu, sm, 2);
-                if ((lane & 3) == 0) asum[m * (K >> 5) + (k0 >> 5)] = sm;
-            }
-        }
-    }
-    consumer_sync();
-    if (threadIdx.x < M) {                              // fixed summation order: the result does not depend on warp timing
-        float tot = 0.0f;
-        if (a.gamma) for (int b = 0; b < nblk; ++b) tot += ssb[threadIdx.x * nblk + b];
-        inv_s[threadIdx.x] = a.gamma ? 1.0f / sqrtf(tot / static_cast<float>(a.w.K) + a.eps) : 1.0f;
+        const float* gxs = reinterpret_cast<const float*>(a.img + L.xs);
+        for (int i = threadIdx.x; i < M * nbs; i += kWarps * 32) { const int m = i / nbs, b = i - m * nbs; xs[m * (K >> 8) + b] = gxs[m * nb + kb0 + b]; }
+        if (threadIdx.x < M) inv_s[threadIdx.x] = reinterpret_cast<const float*>(a.img + L.inv_s)[threadIdx.x];
+        ok = mbar_wait(&x_bar, 0, a.err, 3);
     }
     consumer_sync();
 
     int st = 0;
     uint32_t ph = 0;
-    bool ok = true;
     float* my_slab = slab + static_cast<size_t>(warp) * NMAT * 16 * NC;
     for (int rg = team; rg < n_rg; rg += n_teams) {
         // column sums of this warp's share of the row group: [matrix][column group][row g: slots 0, 1 | row g + 8: slots 2, 3]
@@ -512,7 +550,7 @@ int rows_slices(int nb, int mc, int nmat, int cg) {
 }
 
 template <int CG>
-int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, void* d_limbs, size_t limbs_bytes, cudaStream_t s) {
     const int m0 = 0, mc = g.M;
     constexpr int kThreads = kWarps * 32;
     const int K = g.w.K, nb = g.w.nb;
@@ -526,7 +564,7 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
     const int kbs = (nb + S - 1) / S;
     const int slices = (nb + kbs - 1) / kbs;
     if (slices > 1 && static_cast<size_t>(slices) * nmat * mc * g.w.N > part_floats) return GGB_NOT_FOUND;
-    if (static_cast<size_t>(mc) * nb > static_cast<size_t>(kWarps) * nmat * 16 * 8 * CG) return GGB_NOT_FOUND;      // per-block sums of squares borrow the slabs
+    if (LimbImage(mc, K).bytes > limbs_bytes || nb * sizeof(float) > 48 * 1024) return GGB_NOT_FOUND;
     const int G = std::min(std::max(1, c->sm_count / slices), groups);
     const int gpc = (groups + G - 1) / G;
     int ws = 1;
@@ -556,7 +594,18 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
     a.M = mc; a.lda = g.lda; a.ldc = g.ldc; a.epi = g.epi;
     a.sb = sb; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
     a.kbs = kbs; a.part = slices > 1 ? d_part : nullptr;
+    a.img = static_cast<const uint8_t*>(d_limbs);
     a.err = c->d_err;
+    const bool reuse = g.limbs_reuse && c->limbs_x == g.x && c->limbs_gamma == g.gamma && c->limbs_M == mc && c->limbs_K == K &&
+                       c->limbs_lda == g.lda && c->limbs_eps == g.eps && c->limbs_call + 1 == c->gemv_calls;
+    c->limbs_x = g.x; c->limbs_gamma = g.gamma; c->limbs_M = mc; c->limbs_K = K; c->limbs_lda = g.lda; c->limbs_eps = g.eps;
+    c->limbs_call = c->gemv_calls;
+    if (!reuse) {
+        const cudaError_t ep = launch_pdl(c, rows_prep_kernel, dim3(static_cast<unsigned>(mc)), dim3(256), nb * sizeof(float), s,
+                                          static_cast<const float*>(g.x), g.lda, mc, K, g.gamma, g.eps, static_cast<uint8_t*>(d_limbs));
+        c->launches++;
+        if (ep != cudaSuccess) return cuda_status(c, ep, "gemv_mma_rows activation image");
+    }
     void (*kern)(const RowsArgs) = dual ? gemv_mma_rows_kernel<CG, 2> : gemv_mma_rows_kernel<CG, 1>;
     cudaError_t e = ensure_dynamic_smem(c, kern, smem);
     if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma_rows attr");
@@ -596,13 +645,15 @@ size_t gemv_mma_rows_ws_floats(const GemvArgs& g) {
 // 3 <= M <= 16 rows of a Q4_K / Q6_K matrix in the row-group-major layout in one pass over the weights.
 // d_part: workspace of at least gemv_mma_rows_ws_floats(g) floats.  GGB_NOT_FOUND: shape not covered (the caller falls
 // back to two rows per pass).
-int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, void* d_limbs, size_t limbs_bytes, cudaStream_t s) {
     if (!rows_covered(g)) return GGB_NOT_FOUND;
     switch (rows_cg(g.M)) {
-    case 2: return launch_rows_t<2>(c, g, d_part, part_floats, s);
-    case 3: return launch_rows_t<3>(c, g, d_part, part_floats, s);
-    default: return launch_rows_t<6>(c, g, d_part, part_floats, s);
+    case 2: return launch_rows_t<2>(c, g, d_part, part_floats, d_limbs, limbs_bytes, s);
+    case 3: return launch_rows_t<3>(c, g, d_part, part_floats, d_limbs, limbs_bytes, s);
+    default: return launch_rows_t<6>(c, g, d_part, part_floats, d_limbs, limbs_bytes, s);
     }
 }
+
+size_t gemv_mma_rows_limbs_bytes(int M, int K) { return LimbImage(M, K).bytes; }
 
 }  // namespace ggb

@@ -52,6 +52,10 @@ struct GemvArgs {
     // following GEMM whose K is this N, instead of fp32 y.  gemm_tc_image_elems gives the buffer size.
     const void* x_img = nullptr;
     void* y_img = nullptr;
+    // optional (multi-row tensor-core GEMV, 3 <= M <= 16): the previous launch_gemv call on this stream had the same
+    // x, M, K, gamma and eps, so its int8-limb image of the activations is still in the workspace and is used again
+    // (q, k and v projections of one layer)
+    bool limbs_reuse = false;
 };
 
 struct DeviceWeight {
@@ -98,6 +102,14 @@ struct Context {
     size_t d_xb_elems = 0;
     float* d_ws = nullptr;    // split-K partial sums of the tcgen05 GEMM (grown on demand)
     size_t d_ws_floats = 0;
+    void* d_limbs = nullptr;     // int8-limb image of up to 16 activation rows (multi-row GEMV), grown on demand
+    size_t d_limbs_bytes = 0;
+    // what the image holds and which launch_gemv call wrote or last used it: a reuse request is honoured only by the
+    // very next call with the same source
+    const void *limbs_x = nullptr, *limbs_gamma = nullptr;
+    int limbs_M = 0, limbs_K = 0, limbs_lda = 0;
+    float limbs_eps = 0.0f;
+    uint64_t limbs_call = 0, gemv_calls = 0;
 };
 
 int set_status(Context* c, int status, const char* msg);
@@ -120,8 +132,9 @@ int launch_gemv_tma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT
 int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT_FOUND: shape not covered
 // 3..16 rows in one pass over the weights; d_part: gemv_mma_rows_ws_floats(a) floats of workspace (K cut into slices).
 // GGB_NOT_FOUND: shape not covered
-int launch_gemv_mma_rows(Context* c, const GemvArgs& a, float* d_part, size_t part_floats, cudaStream_t s);
+int launch_gemv_mma_rows(Context* c, const GemvArgs& a, float* d_part, size_t part_floats, void* d_limbs, size_t limbs_bytes, cudaStream_t s);
 size_t gemv_mma_rows_ws_floats(const GemvArgs& a);
+size_t gemv_mma_rows_limbs_bytes(int M, int K);
 int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
 int launch_gemm_tc(Context* c, const GemvArgs& a, void* d_xb, size_t xb_elems, float* d_ws, size_t ws_floats, cudaStream_t s);

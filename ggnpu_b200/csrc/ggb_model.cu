@@ -168,11 +168,13 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
             a.gamma = l.attn_norm; a.eps = d.rms_eps;
             if (l.bk) { a.epi = EPI_ADD_BIAS; a.bias = l.bk; }
             if (img) a.x_img = c->d_xb;
+            a.limbs_reuse = true;                 // 3..16 rows: the q projection's int8-limb image of the normalised x
             M_TRY(launch_gemv(c, a, s));
             a = gemv_args(l.v, m->x, n_tok, H, m->v, kvd);
             a.gamma = l.attn_norm; a.eps = d.rms_eps;
             if (l.bv) { a.epi = EPI_ADD_BIAS; a.bias = l.bv; }
             if (img) a.x_img = c->d_xb;
+            a.limbs_reuse = true;
             M_TRY(launch_gemv(c, a, s));
         }
 
