@@ -16,6 +16,7 @@
 // them in slice order and applies the epilogue.  Eight warps, each with its own ring of bulk-copy stages: a warp requests the tile one
 // ring length ahead whenever it has consumed one (no producer warp, so 256 threads and the full register file per thread).
 #include "ggb_internal.h"
+#include "ggb_limbs.h"
 
 namespace ggb {
 
@@ -75,21 +76,6 @@ __device__ __forceinline__ float wsum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
     return v;
 }
-
-// The activations of one call, converted once by rows_prep_kernel and bulk-copied by every GEMV CTA:
-//   planes int8 [M][3][K] (limbs of x * gamma, one scale per 256-block) | asum float [M][K / 32] | asum16 float [M][K / 16]
-//   | xs float [M][K / 256] (block scales) | inv_s float [16] (RMS factors; 1 without gamma)
-struct LimbImage {
-    size_t planes, asum, asum16, xs, inv_s, bytes;
-    __host__ __device__ LimbImage(int M, int K) {
-        planes = 0;
-        asum = static_cast<size_t>(3) * M * K;
-        asum16 = asum + sizeof(float) * static_cast<size_t>(M) * (K >> 5);
-        xs = asum16 + sizeof(float) * static_cast<size_t>(M) * (K >> 4);
-        inv_s = (xs + sizeof(float) * static_cast<size_t>(M) * (K >> 8) + 15) & ~static_cast<size_t>(15);
-        bytes = inv_s + 64;
-    }
-};
 
 // grid (M), 256 threads: row m.  Warp w converts the 256-blocks w, w + 8, ...: limbs of x * gamma, run sums, the block's
 // sum of squares; thread 0 then adds the sums of squares in block order (so the factor does not depend on timing).
@@ -564,7 +550,7 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
     const int kbs = (nb + S - 1) / S;
     const int slices = (nb + kbs - 1) / kbs;
     if (slices > 1 && static_cast<size_t>(slices) * nmat * mc * g.w.N > part_floats) return GGB_NOT_FOUND;
-    if (LimbImage(mc, K).bytes > limbs_bytes || nb * sizeof(float) > 48 * 1024) return GGB_NOT_FOUND;
+    if (LimbImage(mc, K).bytes > limbs_bytes || nb * sizeof(float) > 48 * 1024 || d_limbs != c->d_limbs) return GGB_NOT_FOUND;
     const int G = std::min(std::max(1, c->sm_count / slices), groups);
     const int gpc = (groups + G - 1) / G;
     int ws = 1;
@@ -596,15 +582,9 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
     a.kbs = kbs; a.part = slices > 1 ? d_part : nullptr;
     a.img = static_cast<const uint8_t*>(d_limbs);
     a.err = c->d_err;
-    const bool reuse = g.limbs_reuse && c->limbs_x == g.x && c->limbs_gamma == g.gamma && c->limbs_M == mc && c->limbs_K == K &&
-                       c->limbs_lda == g.lda && c->limbs_eps == g.eps && c->limbs_call + 1 == c->gemv_calls;
-    c->limbs_x = g.x; c->limbs_gamma = g.gamma; c->limbs_M = mc; c->limbs_K = K; c->limbs_lda = g.lda; c->limbs_eps = g.eps;
-    c->limbs_call = c->gemv_calls;
-    if (!reuse) {
-        const cudaError_t ep = launch_pdl(c, rows_prep_kernel, dim3(static_cast<unsigned>(mc)), dim3(256), nb * sizeof(float), s,
-                                          static_cast<const float*>(g.x), g.lda, mc, K, g.gamma, g.eps, static_cast<uint8_t*>(d_limbs));
-        c->launches++;
-        if (ep != cudaSuccess) return cuda_status(c, ep, "gemv_mma_rows activation image");
+    {
+        const int sp = limb_image_prepare(c, g, s);
+        if (sp != GGB_OK) return sp;
     }
     void (*kern)(const RowsArgs) = dual ? gemv_mma_rows_kernel<CG, 2> : gemv_mma_rows_kernel<CG, 1>;
     cudaError_t e = ensure_dynamic_smem(c, kern, smem);
@@ -655,5 +635,19 @@ int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t pa
 }
 
 size_t gemv_mma_rows_limbs_bytes(int M, int K) { return LimbImage(M, K).bytes; }
+
+int limb_image_prepare(Context* c, const GemvArgs& g, cudaStream_t s) {
+    const int M = g.M, K = g.w.K, nb = K >> 8;
+    if (LimbImage(M, K).bytes > c->d_limbs_bytes || nb * sizeof(float) > 48 * 1024) return set_status(c, GGB_ERROR, "activation image: workspace too small");
+    const bool reuse = g.limbs_reuse && c->limbs_x == g.x && c->limbs_gamma == g.gamma && c->limbs_M == M && c->limbs_K == K &&
+                       c->limbs_lda == g.lda && c->limbs_eps == g.eps && c->limbs_call + 1 == c->gemv_calls;
+    c->limbs_x = g.x; c->limbs_gamma = g.gamma; c->limbs_M = M; c->limbs_K = K; c->limbs_lda = g.lda; c->limbs_eps = g.eps;
+    c->limbs_call = c->gemv_calls;
+    if (reuse) return GGB_OK;
+    const cudaError_t e = launch_pdl(c, rows_prep_kernel, dim3(static_cast<unsigned>(M)), dim3(256), nb * sizeof(float), s,
+                                     static_cast<const float*>(g.x), g.lda, M, K, g.gamma, g.eps, static_cast<uint8_t*>(c->d_limbs));
+    c->launches++;
+    return cuda_status(c, e, "activation image");
+}
 
 }  // namespace ggb

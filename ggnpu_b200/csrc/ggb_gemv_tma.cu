@@ -23,6 +23,7 @@
 // global memory, stops consuming and the CTA drains and exits; the host turns the word into
 // Status::ERROR.  No kernel here can spin forever.
 #include "ggb_internal.h"
+#include "ggb_limbs.h"
 
 namespace ggb {
 
@@ -262,6 +263,9 @@ struct TmaGemvArgs {
     int64_t cat_N[2];
     float* cat_y[2];
     const float* cat_bias[2];
+    // multi-row kernel: rows [m0, m0 + M) of the activation image (full image: M_img rows)
+    int M, M_img, m0, ldc;
+    const uint8_t* img;
 };
 
 // Matrix and first row of tile t.
@@ -552,6 +556,233 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     return cuda_status(c, e, "gemv_tma launch");
 }
 
+
+// ---- 2..16 activation rows, stream layout ---------------------------------------------------------
+// The same tiles, ring and per-unit arithmetic as gemv_tma_kernel, for a.M rows of activations taken from the limb
+// image (ggb_limbs.h): all rows' limb planes, 16-run sums and block scales sit in shared memory, a tile is consumed
+// once per row (the lane's two units of that row are re-read from the planes, then every weight row of the tile is
+// multiplied), so the weights are streamed once for the whole chunk of rows.
+// Shared-memory map: [ring][planes 3 * M * K][asum16 M * K / 16 floats][xs M * K / 256 floats (padded to 16 B)]
+// [slice partials 2 * M * tile_rows * wk * (dual ? 2 : 1) floats]
+template <class F, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1) gemv_tma_rows_kernel(const TmaGemvArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], x_bar;
+    __shared__ float inv_s[16];
+    const int K = a.w.K, nb = a.w.nb, M = a.M;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const FormatInfo fi = format_info(F::TYPE);
+    uint8_t* ring = smem;
+    int8_t* xl = reinterpret_cast<int8_t*>(ring + static_cast<size_t>(a.stages) * a.stage_bytes);
+    float* xsum = reinterpret_cast<float*>(xl + static_cast<size_t>(3) * M * K);
+    float* xscale = xsum + static_cast<size_t>(M) * (K >> 4);
+    float* part = xscale + ((M * (K >> 8) + 3) & ~3);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kConsumerWarps); }
+        mbar_init(&x_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch();
+
+    int soff[2 * kMaxStreams];
+    {
+        int acc = 0;
+        for (int i = 0; i < F::NS; ++i) { soff[i] = acc; acc += a.tile_rows * nb * fi.size[i]; }
+        for (int i = 0; i < F::NS; ++i) { soff[kMaxStreams + i] = acc; if (DUAL) acc += a.tile_rows * nb * fi.size[i]; }
+    }
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer (as in gemv_tma_kernel) ----------------
+        if (lane == 0) {
+            int n = 0;
+            for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++n) {
+                const int s = n % a.stages;
+                const uint32_t ph = (n / a.stages) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1, a.err, 1)) break;
+                const int64_t row0 = static_cast<int64_t>(t) * a.tile_rows;
+                const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), a.w.N - row0));
+                uint32_t bytes = 0;
+                for (int i = 0; i < F::NS; ++i) bytes += rows * nb * fi.size[i];
+                mbar_expect_tx(&full_bar[s], DUAL ? 2 * bytes : bytes);
+                uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
+                for (int i = 0; i < F::NS; ++i) {
+                    const uint32_t sz = rows * nb * fi.size[i];
+                    bulk_g2s(dst + soff[i], a.w.s[i] + row0 * nb * fi.size[i], sz, &full_bar[s]);
+                    if (DUAL) bulk_g2s(dst + soff[kMaxStreams + i], a.w2.s[i] + row0 * nb * fi.size[i], sz, &full_bar[s]);
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int tid = threadIdx.x;
+        pdl_wait();                                       // the image (and resid) come from the previous kernels
+        bool ok = true;
+        {
+            const LimbImage L(a.M_img, K);
+            if (tid == 0) {                               // rows m0 .. m0 + M of the planes and of the 16-run sums are contiguous
+                const uint32_t pb = static_cast<uint32_t>(3) * M * K, sb16 = static_cast<uint32_t>(M) * (K >> 4) * 4;
+                mbar_expect_tx(&x_bar, pb + sb16);
+                bulk_g2s(xl, a.img + L.planes + static_cast<size_t>(3) * a.m0 * K, pb, &x_bar);
+                bulk_g2s(xsum, a.img + L.asum16 + sizeof(float) * static_cast<size_t>(a.m0) * (K >> 4), sb16, &x_bar);
+            }
+            const float* gxs = reinterpret_cast<const float*>(a.img + L.xs) + static_cast<size_t>(a.m0) * (K >> 8);
+            for (int i = tid; i < M * (K >> 8); i += kConsumerWarps * 32) xscale[i] = gxs[i] * (1.0f / 16384.0f);
+            if (tid < M) inv_s[tid] = reinterpret_cast<const float*>(a.img + L.inv_s)[a.m0 + tid];
+            ok = mbar_wait(&x_bar, 0, a.err, 3);
+        }
+        consumer_sync();
+        const int wk_i = warp % a.wk, wr_i = warp / a.wk, wr_n = kConsumerWarps / a.wk;
+        const int units = K >> 5;
+        const int u_begin = wk_i * a.units_per_slice, u_end = min(units, u_begin + a.units_per_slice);
+        int my_u[2], ka[2], kb[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int u = u_begin + lane + 32 * i;
+            my_u[i] = u < u_end ? u : -1;
+            ka[i] = 0; kb[i] = 0;
+            if (my_u[i] >= 0) F::runs(u, ka[i], kb[i]);
+        }
+        const int pstride = a.tile_rows * a.wk;           // partials of one activation row
+        int n = 0;
+        for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++n) {
+            const int s = n % a.stages;
+            const uint32_t ph = (n / a.stages) & 1;
+            if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
+            const int64_t row0 = static_cast<int64_t>(t) * a.tile_rows;
+            const int rows = static_cast<int>(min(static_cast<int64_t>(a.tile_rows), a.w.N - row0));
+            const uint8_t* base = ring + static_cast<size_t>(s) * a.stage_bytes;
+            const uint8_t* sa[4] = {nullptr, nullptr, nullptr, nullptr};
+            const uint8_t* sb[4] = {nullptr, nullptr, nullptr, nullptr};
+#pragma unroll
+            for (int i = 0; i < F::NS; ++i) { sa[i] = base + soff[i]; sb[i] = base + soff[kMaxStreams + i]; }
+            float* pp = part + (n & 1) * (M * pstride * (DUAL ? 2 : 1));
+            for (int m = 0; m < M && ok; ++m) {
+                XUnit xu[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (my_u[i] >= 0) {
+                        const int8_t* pl = xl + static_cast<size_t>(3 * m) * K;
+#pragma unroll
+                        for (int p = 0; p < 3; ++p) {
+                            const int4 va = *reinterpret_cast<const int4*>(pl + p * K + ka[i]), vb = *reinterpret_cast<const int4*>(pl + p * K + kb[i]);
+                            int* da = p == 0 ? xu[i].a.l1 : (p == 1 ? xu[i].a.l2 : xu[i].a.l3);
+                            int* db = p == 0 ? xu[i].b.l1 : (p == 1 ? xu[i].b.l2 : xu[i].b.l3);
+                            da[0] = va.x; da[1] = va.y; da[2] = va.z; da[3] = va.w; db[0] = vb.x; db[1] = vb.y; db[2] = vb.z; db[3] = vb.w;
+                        }
+                        xu[i].sum_a = xsum[m * (K >> 4) + (ka[i] >> 4)]; xu[i].sum_b = xsum[m * (K >> 4) + (kb[i] >> 4)];
+                        xu[i].scale = xscale[m * (K >> 8) + (ka[i] >> 8)];
+                    }
+                for (int r = wr_i; r < rows; r += wr_n) {
+                    float acc = 0.0f, acc2 = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+                        if (my_u[i] >= 0) {
+                            acc += F::unit(sa, r * nb, my_u[i], xu[i]);
+                            if constexpr (DUAL) acc2 += F::unit(sb, r * nb, my_u[i], xu[i]);
+                        }
+                    acc = wsum(acc);
+                    if constexpr (DUAL) acc2 = wsum(acc2);
+                    if (a.wk > 1) {
+                        if (lane == 0) { pp[m * pstride + r * a.wk + wk_i] = acc; if constexpr (DUAL) pp[(M + m) * pstride + r * a.wk + wk_i] = acc2; }
+                    } else if (lane == 0) {
+                        const int64_t nrow = row0 + r;
+                        const size_t o = static_cast<size_t>(m) * a.ldc + nrow;
+                        float v = acc * inv_s[m];
+                        if constexpr (DUAL) { const float u2 = acc2 * inv_s[m]; v = (v / (1.0f + expf(-v))) * u2; }
+                        else if (a.epi == EPI_ADD_BIAS) v += __ldg(a.bias + nrow);
+                        else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
+                        a.y[o] = v;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(&empty_bar[s]);     // this warp is done reading the stage
+            if (a.wk > 1) {
+                consumer_sync();                           // partials of every slice are in shared memory
+                for (int idx = tid; idx < rows * M && ok; idx += kConsumerWarps * 32) {
+                    const int m = idx / rows, r = idx - m * rows;
+                    float v = 0.0f, v2 = 0.0f;
+                    for (int k = 0; k < a.wk; ++k) { v += pp[m * pstride + r * a.wk + k]; if constexpr (DUAL) v2 += pp[(M + m) * pstride + r * a.wk + k]; }
+                    const int64_t nrow = row0 + r;
+                    const size_t o = static_cast<size_t>(m) * a.ldc + nrow;
+                    v *= inv_s[m];
+                    if constexpr (DUAL) { v2 *= inv_s[m]; v = (v / (1.0f + expf(-v))) * v2; }
+                    else if (a.epi == EPI_ADD_BIAS) v += __ldg(a.bias + nrow);
+                    else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
+                    a.y[o] = v;
+                }
+                // the partial buffers alternate between tiles (n & 1): the next tile writes the other one, and the one after
+                // that passes another consumer_sync first
+            }
+        }
+    }
+}
+
+// Rows of activations per pass: the limb planes, 16-run sums and scales of a chunk must fit beside the ring.
+static int tma_rows_chunk(int K, int M) {
+    const size_t per_row = static_cast<size_t>(3) * K + sizeof(float) * ((K >> 4) + (K >> 8));
+    const int fit = static_cast<int>((112 * 1024) / per_row);
+    return std::min(M, fit);
+}
+
+template <class F, bool DUAL>
+int launch_tma_rows(Context* c, const GemvArgs& g, cudaStream_t s) {
+    const FormatInfo fi = format_info(F::TYPE);
+    const int K = g.w.K, nb = g.w.nb;
+    const int64_t N = g.w.N;
+    const int units = K / 32;
+    if (K % 256 || N % 8 || units > 8 * 64) return GGB_NOT_FOUND;
+    const int Mc = tma_rows_chunk(K, g.M);
+    if (Mc < 1 || (Mc < 2 && g.M > 4)) return GGB_NOT_FOUND;        // K so long that a pass would carry one row: the general kernel's M tiles do better
+    int wk = 1;
+    while (wk < kConsumerWarps && (units + wk - 1) / wk > 64) wk *= 2;
+    const int ups = (units + wk - 1) / wk;
+    const int row_bytes = nb * fi.block_bytes * (DUAL ? 2 : 1);
+    int gran = 1;
+    for (int i = 0; i < fi.n_streams; ++i) while ((gran * nb * fi.size[i]) % 16) ++gran;
+    if (N % gran) return GGB_NOT_FOUND;
+    const int G = c->sm_count;
+    int tile_rows = gran;
+    double best = 1e30;
+    for (int tr = gran; tr <= 512 && static_cast<int64_t>(tr) * row_bytes <= 24 * 1024 + (tr == gran ? (1 << 30) : 0); tr += gran) {
+        const int64_t nt = (N + tr - 1) / tr;
+        const double cost = static_cast<double>((nt + G - 1) / G) * (static_cast<double>(tr) * row_bytes + 3072.0);
+        if (cost < best * 0.999) { best = cost; tile_rows = tr; }
+    }
+    const int stage_bytes = (tile_rows * row_bytes + 127) / 128 * 128;
+    const int n_tiles = static_cast<int>((N + tile_rows - 1) / tile_rows);
+    {
+        const int sp = limb_image_prepare(c, g, s);
+        if (sp != GGB_OK) return sp;
+    }
+    for (int m0 = 0; m0 < g.M; m0 += Mc) {
+        const int mc = std::min(Mc, g.M - m0);
+        const size_t fixed = static_cast<size_t>(3) * mc * K + sizeof(float) * (static_cast<size_t>(mc) * (K >> 4) + ((mc * (K >> 8) + 3) & ~3)) +
+                             sizeof(float) * 2 * mc * tile_rows * wk * (DUAL ? 2 : 1) + 256;
+        if (fixed + 2 * static_cast<size_t>(stage_bytes) > 216 * 1024) return m0 == 0 ? GGB_NOT_FOUND : set_status(c, GGB_ERROR, "gemv_tma_rows: a later pass did not fit");
+        int stages = static_cast<int>((216 * 1024 - fixed) / stage_bytes);
+        stages = std::max(2, std::min(stages, kMaxStages));
+        stages = std::min(stages, std::max(2, (n_tiles + c->sm_count - 1) / c->sm_count));
+        const size_t smem = static_cast<size_t>(stages) * stage_bytes + fixed;
+
+        TmaGemvArgs a{};
+        a.w = g.w; a.w2 = g.w2; a.x = nullptr; a.y = g.y + static_cast<size_t>(m0) * g.ldc; a.bias = g.bias;
+        a.resid = g.resid ? g.resid + static_cast<size_t>(m0) * g.ldc : nullptr; a.gamma = g.gamma; a.eps = g.eps; a.epi = g.epi;
+        a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
+        a.err = c->d_err;
+        a.M = mc; a.M_img = g.M; a.m0 = m0; a.ldc = g.ldc; a.img = static_cast<const uint8_t*>(c->d_limbs);
+        auto kern = gemv_tma_rows_kernel<F, DUAL>;
+        cudaError_t e = ensure_dynamic_smem(c, kern, smem);
+        if (e != cudaSuccess) return cuda_status(c, e, "gemv_tma_rows attr");
+        e = launch_pdl(c, kern, dim3(static_cast<unsigned>(std::min(n_tiles, c->sm_count))), dim3(kThreads), smem, s, a);
+        c->launches++;
+        if (e != cudaSuccess) return cuda_status(c, e, "gemv_tma_rows launch");
+    }
+    return GGB_OK;
+}
+
 }  // namespace
 
 // M == 1 fast path.  Returns GGB_NOT_FOUND when the shape or format is not covered (the caller then
@@ -566,6 +797,26 @@ int launch_gemv_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     case T_Q4_0: return dual ? launch_tma<TQ40, true>(c, g, s) : launch_tma<TQ40, false>(c, g, s);
     case T_IQ4_NL: return dual ? launch_tma<TIQ4NL, true>(c, g, s) : launch_tma<TIQ4NL, false>(c, g, s);
     case T_IQ4_XS: return dual ? launch_tma<TIQ4XS, true>(c, g, s) : launch_tma<TIQ4XS, false>(c, g, s);
+    default: return GGB_NOT_FOUND;
+    }
+}
+
+// 2 <= M <= 16 rows of a stream-layout matrix (Q8_0, Q4_0, IQ4_NL, IQ4_XS, and Q4_K / Q6_K when they are kept in that
+// layout): exact int8-limb activations as at M = 1, the weights streamed once per chunk of rows that fits shared memory.
+// The caller has made c->d_limbs large enough.  GGB_NOT_FOUND: shape or format not covered.
+int launch_gemv_tma_rows(Context* c, const GemvArgs& g, cudaStream_t s) {
+    if (g.M < 2 || g.M > 16 || g.w.layout != 0 || !g.x || (reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return GGB_NOT_FOUND;
+    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return GGB_NOT_FOUND;
+    const bool dual = g.epi == EPI_SWIGLU;
+    if (dual && g.w2.layout != 0) return GGB_NOT_FOUND;
+    if (g.epi == EPI_ADD_BIAS && !g.bias) return GGB_NOT_FOUND;
+    switch (g.w.type) {
+    case T_Q4_K: return dual ? launch_tma_rows<TQ4K, true>(c, g, s) : launch_tma_rows<TQ4K, false>(c, g, s);
+    case T_Q6_K: return dual ? launch_tma_rows<TQ6K, true>(c, g, s) : launch_tma_rows<TQ6K, false>(c, g, s);
+    case T_Q8_0: return dual ? launch_tma_rows<TQ80, true>(c, g, s) : launch_tma_rows<TQ80, false>(c, g, s);
+    case T_Q4_0: return dual ? launch_tma_rows<TQ40, true>(c, g, s) : launch_tma_rows<TQ40, false>(c, g, s);
+    case T_IQ4_NL: return dual ? launch_tma_rows<TIQ4NL, true>(c, g, s) : launch_tma_rows<TIQ4NL, false>(c, g, s);
+    case T_IQ4_XS: return dual ? launch_tma_rows<TIQ4XS, true>(c, g, s) : launch_tma_rows<TIQ4XS, false>(c, g, s);
     default: return GGB_NOT_FOUND;
     }
 }

@@ -157,11 +157,13 @@ def test_rows_kernel_k_slices(backend, oracle, K):
         check(backend, oracle, t, 512, K, 11, seed=K + 1, sample_rows=40)
 
 
+@pytest.mark.parametrize("t", [S.Q4_K, S.Q8_0, S.IQ4_XS], ids=lambda t: S.TYPE_NAMES[t])
 @pytest.mark.parametrize("K", [1024, 5632])
-def test_rows_kernel_fused_epilogues(backend, oracle, K):
-    """RMSNorm prologue, bias, residual (in place) and the SwiGLU pair at M = 7 and 16 on device pointers; K = 5632 is
-    cut into three slices (8, 8 and 6 super-blocks) whose CTAs all need the whole row's sum of squares."""
-    t, N = S.Q4_K, 208
+def test_rows_kernel_fused_epilogues(backend, oracle, K, t):
+    """RMSNorm prologue, bias, residual (in place) and the SwiGLU pair at M = 7 and 16 on device pointers.  Q4_K (tensor-
+    core layout): K = 5632 is cut into three slices (8, 8 and 6 super-blocks).  Q8_0 / IQ4_XS (stream layout): the
+    multi-row kernel takes the 16 rows in two chunks at K = 5632."""
+    N = 208
     wg, wu = make(t, N, K, 1), make(t, N, K, 2)
     dev = torch.device("cuda:0")
     hg, hu = backend.upload_weight(t, wg, N, K), backend.upload_weight(t, wu, N, K)
