@@ -394,6 +394,13 @@ def run_ours(args):
             extras["config4"] = tp_measure(args, rank, local, world, min(K, 32), W)
         except Exception as e:
             extras["config4"] = {"unavailable": str(e)[:300]}
+        # the qwen35moe shape (40 layers): 128-token prompt (one graph replay per token), batch-1 decode
+        try:
+            c5 = config5_measure(args, rank, local, world, min(K, 64), W)
+            extras["config5"] = {k: c5[k] for k in ("value", "unit", "ms_per_step", "steps", "gpu_launches", "ms_per_token_layer", "prefill", "decode_step", "model_build_s")}
+            extras["config5"]["workload"] = c5["config"]["workload"]
+        except Exception as e:
+            extras["config5"] = {"unavailable": str(e)[:300]}
     if not args.no_extras and world > 1:
         # the sharded paths, where the driver can see them: parity of tensor / expert parallel against one GPU, and the
         # tensor-parallel figures of the 8B-shape model over the ranks of this launch (strong scaling)
@@ -825,17 +832,30 @@ def run_config5(args):
     16 / 2 heads of 256, the others Gated DeltaNet with 16 / 32 heads of 128, vocab 248320): prompt of --q35-prompt tokens,
     then --steps greedy decode tokens.  With torchrun the experts are split over the ranks (expert parallel).
     --q35-layers bounds the layer count (40 = the full shape; the per-layer cost does not depend on it)."""
-    import dataclasses
     import torch
     import torch.distributed as dist
-    from ggnpu_b200.backend import CudaBackend, Q35Model
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    cfg = dataclasses.replace(S.QWEN35MOE, n_layer=args.q35_layers, ctx=args.q35_prompt + args.steps + args.warmup + 8)
+    line = config5_measure(args, rank, local, world, args.steps, args.warmup)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def config5_measure(args, rank, local, world, steps, warmup):
+    """The measurement behind run_config5 (torch.distributed already up when world > 1): the JSON line on rank 0, None
+    elsewhere."""
+    import dataclasses
+    import torch
+    import torch.distributed as dist
+    from ggnpu_b200.backend import CudaBackend, Q35Model
+    cfg = dataclasses.replace(S.QWEN35MOE, n_layer=args.q35_layers, ctx=args.q35_prompt + steps + max(warmup, 3) + 8)
     b = CudaBackend(local)
     join_group(b, rank, world)
     t0 = time.perf_counter()
@@ -858,7 +878,7 @@ def run_config5(args):
     e1.record(stream)
     barrier()
     prefill_ms = e0.elapsed_time(e1)
-    K, W = args.steps, max(args.warmup, 3)
+    K, W = steps, max(warmup, 3)
     toks = model.generate(int(first), len(ids), W)
     barrier()
     launches0 = b.launch_count()
@@ -871,10 +891,11 @@ def run_config5(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, prefill_ms = float(t[0]), float(t[1])
+    line = None
     if rank == 0:
         peak, peak_kind = peaks()
         bytes_step = model.decode_bytes(len(ids) + W + K // 2)
-        print(json.dumps({
+        line = ({
             "metric": METRIC, "value": K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"qwen35moe shape, {cfg.n_layer} of 40 layers, Q4_K (Q6_K attention output and expert down), batch-1 greedy decode after a {len(ids)}-token prompt",
@@ -883,12 +904,10 @@ def run_config5(args):
             "prefill": {"tokens": len(ids), "tok_per_s": len(ids) / (prefill_ms * 1e-3), "note": "one graph replay per prompt token (the architecture is a recurrence)"},
             "decode_step": {"algorithmic_bytes_per_rank": bytes_step, "achieved_gbs_per_rank": bytes_step / (ms / K * 1e-3) / 1e9,
                             "frac_of_hbm_peak": bytes_step / (ms / K * 1e-3) / 1e9 / peak, "peak_source": peak_kind},
-            "model_build_s": build_s}), flush=True)
+            "model_build_s": build_s})
     model.close()
     b.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return line
 
 
 def main():
