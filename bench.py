@@ -930,6 +930,7 @@ def main():
     ap.add_argument("--tp-prompt", type=int, default=4096)
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
     ap.add_argument("--config5", action="store_true", help="qwen35moe-shape decode benchmark (expert parallel under torchrun)")
+    ap.add_argument("--config3", action="store_true", help="Qwen2.5-1.5B shape, all Q8_0: 2048-token prefill and 128 decode tokens on one GPU")
     ap.add_argument("--q35-layers", type=int, default=40)
     ap.add_argument("--q35-prompt", type=int, default=128)
     ap.add_argument("--no-extras", action="store_true", help="skip the extra figures of the default run (config 3 on one GPU; tensor / expert parallel figures and checks under torchrun)")
@@ -942,6 +943,12 @@ def main():
     args = ap.parse_args()
     if args.tp:
         run_tp(args)
+        return
+    if args.config3:
+        from ggnpu_b200.backend import CudaBackend
+        b = CudaBackend(0)
+        print(json.dumps({"config3": config3_figures(b, 0)}), flush=True)
+        b.close()
         return
     if args.config5:
         run_config5(args)

@@ -63,5 +63,6 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_
 int launch_attn_prefill(Context* c, const AttnPagedArgs& a, int n_tok, cudaStream_t s);   // ggb_attn_prefill.cu; GGB_NOT_FOUND: geometry not covered
 size_t attn_partial_floats(int n_tok, int n_head, int n_splits, int head_dim);
 void attn_split_geometry(int n_pages, int* n_splits, int* pages_per_split);
+void attn_split_geometry(int n_pages, int n_kv, int* n_splits, int* pages_per_split);      // up to 64 splits when n_kv <= 2
 
 }  // namespace ggb

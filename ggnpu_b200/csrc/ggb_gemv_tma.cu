@@ -254,6 +254,7 @@ struct TmaGemvArgs {
     int stage_bytes;      // bytes of one ring stage (all streams of one tile, both weights if dual)
     int wk;               // K slices
     int units_per_slice;
+    int left_begin;       // >= 0: units [left_begin, K / 32) are a leftover slice that the warps take in turn, one row each (see launch_tma)
     int* err;
     // stacked matrices (q, k, v of one layer): tiles [tile_first[i], tile_first[i + 1]) belong to matrix
     // i + 1, which has its own streams, row count, output and bias; all share K, the format and x
@@ -402,13 +403,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
         // 3. this lane's units: slice wk_i of K, units u = slice_begin + lane + 32 i
         const int wk_i = warp % a.wk, wr_i = warp / a.wk, wr_n = kConsumerWarps / a.wk;
         const int units = K >> 5;
-        const int u_begin = wk_i * a.units_per_slice, u_end = min(units, u_begin + a.units_per_slice);
+        const int u_begin = wk_i * a.units_per_slice, u_end = min(a.left_begin >= 0 ? a.left_begin : units, u_begin + a.units_per_slice);
         XUnit xu[2];
         int my_u[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int u = u_begin + lane + 32 * i;
-            my_u[i] = u < u_end ? u : -1;
+            // leftover mode: the lane's second unit is its unit of the leftover slice (the same in every warp)
+            const int u = (i == 1 && a.left_begin >= 0) ? a.left_begin + lane : u_begin + lane + 32 * i;
+            my_u[i] = u < ((i == 1 && a.left_begin >= 0) ? units : u_end) ? u : -1;
             if (my_u[i] >= 0) {
                 int ka, kb;
                 F::runs(u, ka, kb);
@@ -445,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tma_kernel(const TmaGemvArgs
                 float acc = 0.0f, acc2 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 2; ++i)
-                    if (my_u[i] >= 0) {
+                    if (my_u[i] >= 0 && (i == 0 || a.left_begin < 0 || (r & (kConsumerWarps - 1)) == warp)) {
                         acc += F::unit(sa, r * nb, my_u[i], xu[i]);
                         if constexpr (DUAL) acc2 += F::unit(sb, r * nb, my_u[i], xu[i]);
                     }
@@ -496,7 +498,12 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     }
     int wk = 1;
     while (wk < kConsumerWarps && (units + wk - 1) / wk > 64) wk *= 2;
-    const int ups = (units + wk - 1) / wk;
+    int ups = (units + wk - 1) / wk;
+    // A few units more than one per lane (K = 8960: 280 units = 8 x 32 + 24) would cost every warp a second, nearly empty
+    // pass per row.  Then the slices take 32 units each and the rest forms a leftover slice that the eight warps take in
+    // turn, one row each: 9 warp passes per row instead of 16.
+    int left_begin = -1;
+    if (wk == kConsumerWarps && ups > 32 && units - 32 * kConsumerWarps <= 32) { ups = 32; left_begin = 32 * kConsumerWarps; }
     const int row_bytes = nb * fi.block_bytes * (DUAL ? 2 : 1);
     // Tile height: every stream slice of a tile must be a multiple of 16 bytes (granule g rows), a
     // tile should carry roughly 8-24 KB, and the busiest CTA should get as few bytes as possible.
@@ -528,6 +535,7 @@ int launch_tma(Context* c, const GemvArgs& g, cudaStream_t s) {
     TmaGemvArgs a{};
     a.w = g.w; a.w2 = g.w2; a.x = g.x; a.y = g.y; a.bias = g.bias; a.resid = g.resid; a.gamma = g.gamma; a.eps = g.eps; a.epi = g.epi;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
+    a.left_begin = left_begin;
     a.err = c->d_err;
     a.n_cat = g.n_cat;
     for (int i = 0; i < g.n_cat; ++i) {
@@ -771,6 +779,7 @@ int launch_tma_rows(Context* c, const GemvArgs& g, cudaStream_t s) {
         a.w = g.w; a.w2 = g.w2; a.x = nullptr; a.y = g.y + static_cast<size_t>(m0) * g.ldc; a.bias = g.bias;
         a.resid = g.resid ? g.resid + static_cast<size_t>(m0) * g.ldc : nullptr; a.gamma = g.gamma; a.eps = g.eps; a.epi = g.epi;
         a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.stages = stages; a.stage_bytes = stage_bytes; a.wk = wk; a.units_per_slice = ups;
+        a.left_begin = -1;
         a.err = c->d_err;
         a.M = mc; a.M_img = g.M; a.m0 = m0; a.ldc = g.ldc; a.img = static_cast<const uint8_t*>(c->d_limbs);
         auto kern = gemv_tma_rows_kernel<F, DUAL>;

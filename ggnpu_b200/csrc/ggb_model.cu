@@ -402,8 +402,7 @@ int ggb_model_finalize(ggb_model m) {
     }
     // paged KV
     m->n_pages = (d.ctx + m->page - 1) / m->page;
-    m->pages_per_split = (m->n_pages + 31) / 32;
-    m->n_splits = (m->n_pages + m->pages_per_split - 1) / m->pages_per_split;
+    attn_split_geometry(m->n_pages, d.n_kv, &m->n_splits, &m->pages_per_split);
     m->kv_layer_elems = static_cast<size_t>(m->n_seq) * m->n_pages * d.n_kv * m->page * hd;
     M_TRY(dev_alloc(m, &m->k_cache, m->kv_layer_elems * d.n_layer));
     M_TRY(dev_alloc(m, &m->v_cache, m->kv_layer_elems * d.n_layer));

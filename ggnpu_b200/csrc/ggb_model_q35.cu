@@ -349,7 +349,7 @@ int ggb_q35_finalize(ggb_q35_model m) {
         Q_TRY(cuda_status(c, cudaMemcpy(m->sin_tab, sn.data(), sizeof(float) * sn.size(), cudaMemcpyHostToDevice), "rope table"));
     }
     m->n_pages = (d.ctx + m->page - 1) / m->page;
-    attn_split_geometry(m->n_pages, &m->n_splits, &m->pages_per_split);
+    attn_split_geometry(m->n_pages, d.n_kv, &m->n_splits, &m->pages_per_split);
     m->kv_layer_elems = static_cast<size_t>(m->n_pages) * d.n_kv * m->page * Hd;
     Q_TRY(q_alloc(m, &m->k_cache, m->kv_layer_elems * std::max(m->n_attn_layers, 1), true));
     Q_TRY(q_alloc(m, &m->v_cache, m->kv_layer_elems * std::max(m->n_attn_layers, 1), true));

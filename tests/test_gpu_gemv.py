@@ -137,6 +137,15 @@ def test_fused_epilogues_device_path(backend, oracle):
     backend.free_weight(hu)
 
 
+@pytest.mark.parametrize("t", [S.Q8_0, S.Q4_0, S.IQ4_XS], ids=lambda t: S.TYPE_NAMES[t])
+@pytest.mark.parametrize("K", [8960, 8448, 9216])
+def test_m1_k_slightly_over_one_unit_per_lane(backend, oracle, t, K):
+    """K = 8960 (the Qwen2.5-1.5B down projection) has 280 units of 32 values: one per lane of the eight warps plus 24 that
+    the warps take in turn, one row each; 8448 leaves 8 such units, 9216 exactly 32.  M = 1 and the rows path (M = 5)."""
+    check(backend, oracle, t, 264, K, 1, seed=K)
+    check(backend, oracle, t, 264, K, 5, seed=K + 1, sample_rows=40)
+
+
 @pytest.mark.parametrize("t", [S.Q4_K, S.Q6_K])
 @pytest.mark.parametrize("M", [3, 5, 6, 8, 9, 13, 16])
 def test_rows_kernel_every_chunk_size(backend, oracle, t, M):
