@@ -195,7 +195,11 @@ double sample_next_uniform(uint64_t* seed);
 
 // ggb_moe.cu / ggb_deltanet.cu: the operators of the qwen35moe layers with caller-owned scratch
 size_t moe_scratch_floats(const ggb_moe_params* p);
-int moe_ffn_enqueue(Context* c, const ggb_moe_params* p, float* scr, cudaStream_t s);
+struct MoeStacked { const DeviceWeight *gate, *up, *down; };      // expert tensors with the shared expert appended as one more expert
+int moe_ffn_enqueue(Context* c, const ggb_moe_params* p, float* scr, cudaStream_t s, const MoeStacked* stacked = nullptr);
+// ggb_pack.cu: a new weight whose rows are a's followed by b's (both Q4_K or both Q6_K in the row-group-major layout, the
+// same K, a.N a multiple of 16); device-to-device copies on the context's stream
+int concat_weight_rows(Context* c, const DeviceWeight* a, const DeviceWeight* b, DeviceWeight** out);
 int deltanet_step_enqueue(Context* c, const ggb_deltanet_params* p, float* conv, cudaStream_t s);
 // y[n] = (rms_norm(x) * gamma) . W[n][:] for small F32 matrices (a warp per row); gamma may be nullptr
 int launch_f32_rows(Context* c, const float* x, const float* gamma, float eps, const float* W, int N, int K, float* y, cudaStream_t s);

@@ -41,6 +41,10 @@ struct Q35Layer {
     // MoE
     float* router = nullptr;
     DeviceWeight *gate_exps = nullptr, *up_exps = nullptr, *down_exps = nullptr, *sh_gate = nullptr, *sh_up = nullptr, *sh_down = nullptr;
+    // finalize appends the shared expert to the expert tensors as one more expert (stacked) when the types agree: it then
+    // rides in the routed experts' launches; bytes of the routed experts and of the shared expert for the traffic figure
+    bool stacked = false, has_shared = false;
+    uint64_t bytes_experts = 0, bytes_shared = 0;
     float* sh_gate_inp = nullptr;
 };
 
@@ -164,10 +168,11 @@ int q35_enqueue_step(ggb_q35_model m) {
         mp.down_exps = static_cast<ggb_weight>(l.down_exps);
         mp.sh_gate = static_cast<ggb_weight>(l.sh_gate); mp.sh_up = static_cast<ggb_weight>(l.sh_up); mp.sh_down = static_cast<ggb_weight>(l.sh_down);
         mp.sh_gate_inp = l.sh_gate_inp;
-        mp.hidden = H; mp.eff = d.eff; mp.eff_sh = l.sh_gate ? d.eff : 0; mp.n_expert = d.n_expert; mp.top_k = d.top_k;
+        mp.hidden = H; mp.eff = d.eff; mp.eff_sh = l.has_shared ? d.eff : 0; mp.n_expert = d.n_expert; mp.top_k = d.top_k;
         mp.gamma = l.post_norm; mp.eps = d.rms_eps;
         if (c->tp_size > 1) { mp.ep_first = m->ep_first; mp.ep_local = m->n_local_expert; }
-        Q_TRY(moe_ffn_enqueue(c, &mp, m->moe_scr, s));
+        const MoeStacked stacked{l.gate_exps, l.up_exps, l.down_exps};
+        Q_TRY(moe_ffn_enqueue(c, &mp, m->moe_scr, s, l.stacked ? &stacked : nullptr));
         std::swap(x, x2);
     }
     GemvArgs a = q_gemv(m->output ? m->output : m->tok_embd, x, H, m->logits, d.vocab);
@@ -323,6 +328,26 @@ int ggb_q35_finalize(ggb_q35_model m) {
         if (!l.attn_norm || !l.post_norm || !moe_ok) return set_status(c, GGB_INVALID_PARAM, "q35_finalize: a layer's norm or MoE tensor is missing");
         if (l.gate_exps->w.layout != 1 || l.up_exps->w.layout != 1 || l.down_exps->w.layout != 1)
             return set_status(c, GGB_INVALID_PARAM, "q35_finalize: expert tensors must be Q4_K or Q6_K");
+        {
+            auto wbytes = [](const DeviceWeight* w) -> uint64_t {
+                return w ? static_cast<uint64_t>(w->w.N) * w->w.nb * format_info(w->w.type).block_bytes : 0;
+            };
+            l.bytes_experts = wbytes(l.gate_exps) + wbytes(l.up_exps) + wbytes(l.down_exps);
+            l.bytes_shared = wbytes(l.sh_gate) + wbytes(l.sh_up) + wbytes(l.sh_down);
+            l.has_shared = l.sh_gate != nullptr;
+            if (l.has_shared && !l.stacked && d.top_k + 1 < 16 && l.sh_gate->w.layout == 1 && l.sh_up->w.layout == 1 && l.sh_down->w.layout == 1 &&
+                l.sh_gate->w.type == l.gate_exps->w.type && l.sh_up->w.type == l.up_exps->w.type && l.sh_down->w.type == l.down_exps->w.type) {
+                DeviceWeight *g2 = nullptr, *u2 = nullptr, *d2 = nullptr;
+                int st = concat_weight_rows(c, l.gate_exps, l.sh_gate, &g2);
+                if (st == GGB_OK) st = concat_weight_rows(c, l.up_exps, l.sh_up, &u2);
+                if (st == GGB_OK) st = concat_weight_rows(c, l.down_exps, l.sh_down, &d2);
+                if (st != GGB_OK) { free_weight(g2); free_weight(u2); free_weight(d2); return st; }
+                for (DeviceWeight* w : {l.gate_exps, l.up_exps, l.down_exps, l.sh_gate, l.sh_up, l.sh_down}) free_weight(w);
+                l.gate_exps = g2; l.up_exps = u2; l.down_exps = d2;
+                l.sh_gate = l.sh_up = l.sh_down = nullptr;
+                l.stacked = true;
+            }
+        }
         if (l.is_ssm) {
             if (!l.qkv || !l.zgate || !l.ssm_out || !l.have_alpha || !l.have_beta || !l.conv_w || !l.ssm_a || !l.dt_bias || !l.ssm_norm)
                 return set_status(c, GGB_INVALID_PARAM, "q35_finalize: a DeltaNet layer tensor is missing");
@@ -368,7 +393,7 @@ int ggb_q35_finalize(ggb_q35_model m) {
     {
         ggb_moe_params mp{};
         mp.top_k = d.top_k; mp.eff = d.eff; mp.eff_sh = d.eff; mp.n_expert = d.n_expert;
-        Q_TRY(q_alloc(m, &m->moe_scr, moe_scratch_floats(&mp)));
+        Q_TRY(q_alloc(m, &m->moe_scr, moe_scratch_floats(&mp), true));      // zeroed: the router kernel's ticket counter lives there
     }
     Q_TRY(q_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
     Q_TRY(q_alloc(m, &m->amax_partial, 512));
@@ -485,8 +510,8 @@ uint64_t ggb_q35_decode_bytes(ggb_q35_model m, int pos) {
             b += static_cast<uint64_t>(2) * (pos + 1) * d.n_kv * d.head_dim * 2;               // K and V read, bf16
         }
         // router + the top_k chosen experts of this rank's share (all of them on one GPU) + the shared expert
-        const uint64_t per_expert = (wb(l.gate_exps) + wb(l.up_exps) + wb(l.down_exps)) / std::max(m->n_local_expert, 1);
-        b += static_cast<uint64_t>(d.n_expert) * d.hidden * 4 + per_expert * d.top_k / m->c->tp_size + wb(l.sh_gate) + wb(l.sh_up) + wb(l.sh_down);
+        const uint64_t per_expert = l.bytes_experts / std::max(m->n_local_expert, 1);
+        b += static_cast<uint64_t>(d.n_expert) * d.hidden * 4 + per_expert * d.top_k / m->c->tp_size + l.bytes_shared;
         b += static_cast<uint64_t>(d.hidden) * 4 * 3;                                          // norms, shared-gate vector
     }
     b += static_cast<uint64_t>(d.hidden) * 4;

@@ -3,9 +3,9 @@
 // reference's layer loop, src/cli/main.cpp:3110-3193, which runs 9 experts x 3 host-pointer matmuls
 // with a sync after each.
 //
-// Six launches, no host round trip (the chosen expert ids never leave the GPU):
-//   1. moe_logits_kernel: logits = router[n_expert][hidden] . x (a warp per expert); moe_topk_kernel: k
-//      rounds of block-wide arg-max (lowest index wins a tie), weights exp(l - max) / sum over the
+// Five launches (three when the shared expert is stacked behind the routed ones), no host round trip (the chosen expert ids never leave the GPU):
+//   1. moe_route_kernel: logits = router[n_expert][hidden] . x (a warp per expert), then, in the CTA that finishes
+//      last, k rounds of block-wide arg-max (lowest index wins a tie), weights exp(l - max) / sum over the
 //      chosen, shared-expert gate sigmoid(g . x);
 //   2. gate/up of the k chosen experts as ONE tensor-core GEMV over gathered row ranges (the expert
 //      tensors are uploaded whole, [n_expert * eff][hidden]; the kernel's producer maps its row groups
@@ -22,55 +22,29 @@ namespace {
 
 constexpr int kMaxTopK = 16;
 
-// Router logits: one warp per expert row (row n_expert = the shared expert's gate vector), 8 rows per CTA,
-// so the 2 MB router matrix is read by dozens of SMs rather than one.
-__global__ void moe_logits_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float eps, const float* __restrict__ router,
-                                  int hidden, int n_expert, const float* __restrict__ sh_gate_inp, float* __restrict__ logits) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x * 8 + warp;
-    if (e > n_expert) return;
-    const float* wr = e < n_expert ? router + static_cast<size_t>(e) * hidden : sh_gate_inp;
-    if (!wr) return;
-    // with gamma: the logit of rms_norm(x) * gamma, formed as (x * gamma) . w times the row's 1 / rms
-    float acc = 0.0f, ss = 0.0f;
-    for (int i = lane * 4; i < hidden; i += 128) {
-        float4 a = *reinterpret_cast<const float4*>(x + i);
-        const float4 b = __ldg(reinterpret_cast<const float4*>(wr + i));
-        if (gamma) {
-            const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + i));
-            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-            a.x *= g.x; a.y *= g.y; a.z *= g.z; a.w *= g.w;
-        }
-        acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }
-    if (gamma) acc *= 1.0f / sqrtf(ss / static_cast<float>(hidden) + eps);
-    if (lane == 0) logits[e] = acc;
-}
-
-// grid 1, block 256: k rounds of block-wide arg-max over the logits (n_expert <= 1024), softmax over the chosen,
-// shared-expert gate.
+// k rounds of block-wide arg-max over the logits (n_expert <= 1024; lowest index wins a tie), softmax over the chosen,
+// shared-expert gate.  256 threads of one CTA.
 // Expert parallel: sel / w describe this rank's share -- experts outside [ep_first, ep_first + ep_local) get
 // id -1 (the GEMV kernels skip them) and weight 0; sel_glob / w_glob (optional) keep the global choice.
-__global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, int top_k, int has_gate, int ep_first, int ep_local,
-                                int32_t* __restrict__ sel, float* __restrict__ w, int32_t* __restrict__ sel_glob, float* __restrict__ w_glob) {
+// shared_slot >= 0: the shared expert is stacked behind the routed ones in the expert tensors; it then becomes choice
+// number top_k with id shared_slot (-2: stacked, but held by another rank -> id -1) and its sigmoid gate as weight.
+__device__ void moe_topk_body(const float* __restrict__ logits, int n_expert, int top_k, int has_gate, int ep_first, int ep_local, int shared_slot,
+                              int32_t* __restrict__ sel, float* __restrict__ w, int32_t* __restrict__ sel_glob, float* __restrict__ w_glob) {
     __shared__ float logit[1024];
-    __shared__ float red_v[8];
-    __shared__ int red_i[8];
     __shared__ float chosen[kMaxTopK];
     __shared__ int picked[kMaxTopK];
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) logit[e] = logits[e];
-    if (threadIdx.x == 0) w[top_k] = has_gate ? 1.0f / (1.0f + expf(-logits[n_expert])) : 1.0f;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) logit[e] = __ldcg(logits + e);      // written by other CTAs of this launch
+    if (threadIdx.x == 0) {
+        w[top_k] = has_gate ? 1.0f / (1.0f + expf(-__ldcg(logits + n_expert))) : 1.0f;
+        if (shared_slot != -1) sel[top_k] = shared_slot >= 0 ? shared_slot : -1;
+    }
     __syncthreads();
+    if (warp != 0) return;
+    // one warp, no block-wide barrier: k rounds of (each lane scans its strided share, warp arg-max by shuffles)
     for (int j = 0; j < top_k; ++j) {
         float bv = -INFINITY; int bi = 0x7FFFFFFF;
-        for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        for (int e = lane; e < n_expert; e += 32) {
             const float v = logit[e];
             if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
         }
@@ -80,13 +54,9 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
             const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            for (int q = 1; q < 8; ++q)
-                if (red_v[q] > red_v[0] || (red_v[q] == red_v[0] && red_i[q] < red_i[0])) { red_v[0] = red_v[q]; red_i[0] = red_i[q]; }
-            int e = red_i[0];
-            float ev = red_v[0];
+        if (lane == 0) {
+            int e = bi;
+            float ev = bv;
             bool none = e < 0 || e >= n_expert;
             for (int r = 0; r < j && !none; ++r) none = picked[r] == e;      // an exhausted (-inf) entry won the tie
             if (none) {
@@ -107,9 +77,9 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
             chosen[j] = ev;
             logit[e] = -INFINITY;
         }
-        __syncthreads();
+        __syncwarp();
     }
-    if (threadIdx.x == 0) {
+    if (lane == 0) {
         const float mx = chosen[0];
         float sum = 0.0f;
         for (int j = 0; j < top_k; ++j) { chosen[j] = expf(chosen[j] - mx); sum += chosen[j]; }
@@ -122,19 +92,82 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int n_expert, 
     }
 }
 
+struct MoeRouteArgs {
+    const float* x; const float* gamma; float eps; const float* router; int hidden, n_expert; const float* sh_gate_inp; float* logits;
+    unsigned* ticket;          // counts finished CTAs over all launches (starts at a multiple of the grid size)
+    int top_k, ep_first, ep_local, shared_slot;
+    int32_t* sel; float* w; int32_t* sel_glob; float* w_glob;
+};
+
+// Router logits and the choice in one launch.  One warp per expert row (row n_expert = the shared expert's gate vector),
+// 8 rows per CTA, so the 2 MB router matrix is read by dozens of SMs rather than one; the CTA that finishes last
+// (a ticket counter behind a fence) then holds all logits and runs the top-k.
+__global__ void __launch_bounds__(256) moe_route_kernel(const MoeRouteArgs a) {
+    __shared__ int is_last;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    const float* wr = e < a.n_expert ? a.router + static_cast<size_t>(e) * a.hidden : (e == a.n_expert ? a.sh_gate_inp : nullptr);
+    if (wr) {
+        // with gamma: the logit of rms_norm(x) * gamma, formed as (x * gamma) . w times the row's 1 / rms
+        float acc = 0.0f, ss = 0.0f;
+        // four 16-byte loads of the router row per lane in flight (hidden is a multiple of 256): one dependent load per
+        // step would pay a memory latency per step
+        for (int i0 = lane * 4; i0 < a.hidden; i0 += 512) {
+            float4 wv[4], xv[4], gv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + 128 * u;
+                if (i < a.hidden) {
+                    wv[u] = __ldg(reinterpret_cast<const float4*>(wr + i));
+                    xv[u] = *reinterpret_cast<const float4*>(a.x + i);
+                    gv[u] = a.gamma ? __ldg(reinterpret_cast<const float4*>(a.gamma + i)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + 128 * u < a.hidden) {
+                    float4 v = xv[u];
+                    const float4 b = wv[u], g = gv[u];
+                    if (a.gamma) {
+                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                        v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
+                    }
+                    acc += v.x * b.x + v.y * b.y + v.z * b.z + v.w * b.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }
+        if (a.gamma) acc *= 1.0f / sqrtf(ss / static_cast<float>(a.hidden) + a.eps);
+        if (lane == 0) a.logits[e] = acc;
+    }
+    __threadfence();                       // this CTA's logits are visible before its ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(a.ticket, 1u) + 1u) % gridDim.x == 0u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    moe_topk_body(a.logits, a.n_expert, a.top_k, a.sh_gate_inp ? 1 : 0, a.ep_first, a.ep_local, a.shared_slot, a.sel, a.w, a.sel_glob, a.w_glob);
+}
+
 }  // namespace
 
 size_t moe_scratch_floats(const ggb_moe_params* p) {
-    return 64 + static_cast<size_t>(p->top_k) * p->eff + static_cast<size_t>(p->eff_sh > 0 ? p->eff_sh : 0) + p->n_expert + 1;
+    return 64 + static_cast<size_t>(p->top_k + 1) * p->eff + static_cast<size_t>(p->eff_sh > 0 ? p->eff_sh : 0) + p->n_expert + 1;
 }
 
-// Validates and enqueues on stream s; `scr` holds moe_scratch_floats(p) floats.  The caller holds the handle's lock.
-int moe_ffn_enqueue(Context* h, const ggb_moe_params* p, float* scr, cudaStream_t s) {
+// Validates and enqueues on stream s; `scr` holds moe_scratch_floats(p) floats whose first 64 words were zero when the
+// scratch was first used (the ticket counter of moe_route_kernel lives there).  The caller holds the handle's lock.
+// stacked (optional): the expert tensors with the shared expert's matrices appended as expert number n_local
+// (concat_weight_rows); the shared expert then rides in the routed experts' two launches as choice number top_k.
+int moe_ffn_enqueue(Context* h, const ggb_moe_params* p, float* scr, cudaStream_t s, const MoeStacked* stacked) {
     if (!p || !p->x || !p->y || !p->router || !p->gate_exps || !p->up_exps || !p->down_exps)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: null pointer");
     if (p->hidden <= 0 || p->hidden % 256 || p->eff <= 0 || p->eff % 256 || p->n_expert < 1 || p->n_expert > 1024 || p->top_k < 1 ||
-        p->top_k > kMaxTopK || p->top_k > p->n_expert)
-        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden and eff must be multiples of 256, n_expert <= 1024, top_k <= 16");
+        p->top_k > kMaxTopK - 1 || p->top_k > p->n_expert)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden and eff must be multiples of 256, n_expert <= 1024, top_k <= 15");
     // expert parallel: this rank holds experts [ep_first, ep_first + ep_local) of the n_expert the router knows
     const bool ep = p->ep_local > 0;
     const int n_local = ep ? p->ep_local : p->n_expert, ep_first = ep ? p->ep_first : 0;
@@ -142,47 +175,51 @@ int moe_ffn_enqueue(Context* h, const ggb_moe_params* p, float* scr, cudaStream_
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert-parallel range outside the router's experts, or the handle is not in a group");
     const DeviceWeight *ge = reinterpret_cast<const DeviceWeight*>(p->gate_exps), *ue = reinterpret_cast<const DeviceWeight*>(p->up_exps),
                        *de = reinterpret_cast<const DeviceWeight*>(p->down_exps);
-    if (ge->w.N != static_cast<int64_t>(n_local) * p->eff || ue->w.N != ge->w.N || ge->w.K != p->hidden || ue->w.K != p->hidden ||
-        de->w.N != static_cast<int64_t>(n_local) * p->hidden || de->w.K != p->eff || ge->w.type != ue->w.type)
+    const int n_rows = stacked ? n_local + 1 : n_local;          // experts in the tensors
+    if (stacked) { ge = stacked->gate; ue = stacked->up; de = stacked->down; }
+    if (ge->w.N != static_cast<int64_t>(n_rows) * p->eff || ue->w.N != ge->w.N || ge->w.K != p->hidden || ue->w.K != p->hidden ||
+        de->w.N != static_cast<int64_t>(n_rows) * p->hidden || de->w.K != p->eff || ge->w.type != ue->w.type)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be [n_expert * eff][hidden] (gate, up) and [n_expert * hidden][eff] (down)");
     if (ge->w.layout != 1 || ue->w.layout != 1 || de->w.layout != 1)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert tensors must be Q4_K or Q6_K in the tensor-core layout");
     // expert parallel: rank 0 alone adds the residual and the shared expert; the all-reduce spreads them
     const bool lead = !ep || h->tp_rank == 0;
-    const bool shared = p->sh_gate && p->sh_up && p->sh_down && lead;
+    const bool shared = !stacked && p->sh_gate && p->sh_up && p->sh_down && lead;
     const DeviceWeight *sg = reinterpret_cast<const DeviceWeight*>(p->sh_gate), *su = reinterpret_cast<const DeviceWeight*>(p->sh_up),
                        *sd = reinterpret_cast<const DeviceWeight*>(p->sh_down);
     if (shared && (sg->w.N != p->eff_sh || su->w.N != p->eff_sh || sg->w.K != p->hidden || su->w.K != p->hidden || sd->w.N != p->hidden ||
                    sd->w.K != p->eff_sh || p->eff_sh <= 0 || p->eff_sh % 256))
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: shared expert shapes do not match");
-    // scratch: [sel: 16 ints][w: 17 floats][act: top_k * eff][act_sh: eff_sh][logits: n_expert + 1]
+    if (stacked && p->eff_sh != p->eff) return set_status(h, GGB_INVALID_PARAM, "moe_ffn: a stacked shared expert must have the routed experts' width");
+    // scratch: [sel: 16 ints][w: 17 floats][ticket at word 40][act: (top_k + 1) * eff][act_sh: eff_sh][logits: n_expert + 1]
     int32_t* sel = reinterpret_cast<int32_t*>(scr);
     float* w = scr + 16;
     float* act = scr + 64;
-    float* act_sh = act + static_cast<size_t>(p->top_k) * p->eff;
-    float* logits = act_sh + (shared ? p->eff_sh : 0);
-    const float* gate_vec = shared ? p->sh_gate_inp : static_cast<const float*>(nullptr);
+    float* act_sh = act + static_cast<size_t>(p->top_k + 1) * p->eff;
+    float* logits = act_sh + (p->eff_sh > 0 ? p->eff_sh : 0);
+    const bool gate = (shared || stacked) && p->sh_gate_inp;
+    const int n_sel = stacked ? p->top_k + 1 : p->top_k;
 
-    cudaError_t e = launch_pdl(h, moe_logits_kernel, dim3((p->n_expert + 1 + 7) / 8), dim3(256), 0, s, p->x, p->gamma, p->eps, p->router, p->hidden,
-                               p->n_expert, gate_vec, logits);
+    MoeRouteArgs ra{};
+    ra.x = p->x; ra.gamma = p->gamma; ra.eps = p->eps; ra.router = p->router; ra.hidden = p->hidden; ra.n_expert = p->n_expert;
+    ra.sh_gate_inp = gate ? p->sh_gate_inp : nullptr; ra.logits = logits; ra.ticket = reinterpret_cast<unsigned*>(scr + 40);
+    ra.top_k = p->top_k; ra.ep_first = ep_first; ra.ep_local = n_local; ra.shared_slot = stacked ? (lead ? n_local : -2) : -1;
+    ra.sel = sel; ra.w = w; ra.sel_glob = p->sel_out; ra.w_glob = p->w_out;
+    cudaError_t e = launch_pdl(h, moe_route_kernel, dim3((p->n_expert + 1 + 7) / 8), dim3(256), 0, s, ra);
     h->launches++;
-    if (e != cudaSuccess) return cuda_status(h, e, "moe router logits");
-    e = launch_pdl(h, moe_topk_kernel, dim3(1), dim3(256), 0, s, static_cast<const float*>(logits), p->n_expert, p->top_k, gate_vec ? 1 : 0,
-                   ep_first, n_local, sel, w, p->sel_out, p->w_out);
-    h->launches++;
-    if (e != cudaSuccess) return cuda_status(h, e, "moe top-k");
+    if (e != cudaSuccess) return cuda_status(h, e, "moe router");
 
     GemvArgs a{};
-    a.w = ge->w; a.w2 = ue->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act; a.ldc = p->top_k * p->eff; a.epi = EPI_SWIGLU;
+    a.w = ge->w; a.w2 = ue->w; a.x = p->x; a.M = 1; a.lda = p->hidden; a.y = act; a.ldc = n_sel * p->eff; a.epi = EPI_SWIGLU;
     a.gamma = p->gamma; a.eps = p->eps;
-    a.sel = sel; a.sel_mode = 1; a.sel_count = p->top_k; a.sel_rows = p->eff;
+    a.sel = sel; a.sel_mode = 1; a.sel_count = n_sel; a.sel_rows = p->eff;
     int st = launch_gemv_mma(h, a, s);
     if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert gate/up shape not covered") : st;
 
     a = GemvArgs{};
-    a.w = de->w; a.x = act; a.M = 1; a.lda = p->top_k * p->eff; a.y = p->y; a.ldc = p->hidden;
+    a.w = de->w; a.x = act; a.M = 1; a.lda = n_sel * p->eff; a.y = p->y; a.ldc = p->hidden;
     a.epi = (p->resid && lead) ? EPI_RESIDUAL : EPI_STORE; a.resid = lead ? p->resid : nullptr;
-    a.sel = sel; a.sel_mode = 2; a.sel_count = p->top_k; a.sel_rows = p->hidden; a.xscale = w; a.xscale_run = p->eff;
+    a.sel = sel; a.sel_mode = 2; a.sel_count = n_sel; a.sel_rows = p->hidden; a.xscale = w; a.xscale_run = p->eff;
     st = launch_gemv_mma(h, a, s);
     if (st != GGB_OK) return st == GGB_NOT_FOUND ? set_status(h, GGB_INVALID_PARAM, "moe_ffn: expert down shape not covered") : st;
 
@@ -213,5 +250,7 @@ extern "C" int ggb_moe_ffn_device(ggb_handle h, const ggb_moe_params* p) {
     cudaSetDevice(h->device);
     float* scr = static_cast<float*>(scratch(h, 3, sizeof(float) * moe_scratch_floats(p)));
     if (!scr) return h->last_status;
-    return moe_ffn_enqueue(h, p, scr, h->stream);
+    const int st = cuda_status(h, cudaMemsetAsync(scr, 0, 64 * sizeof(float), h->stream), "moe_ffn scratch");      // ticket counter
+    if (st != GGB_OK) return st;
+    return moe_ffn_enqueue(h, p, scr, h->stream, nullptr);
 }

@@ -131,10 +131,35 @@ __global__ void f32_rows_kernel(const float* __restrict__ x, const float* __rest
     if (n >= N) return;
     const float* wr = W + static_cast<size_t>(n) * K;
     float acc = 0.0f, ss = 0.0f;
-    for (int i = lane; i < K; i += 32) {
-        float v = x[i];
-        if (gamma) { ss = fmaf(v, v, ss); v *= gamma[i]; }
-        acc = fmaf(v, __ldg(wr + i), acc);
+    if ((K & 127) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0) {
+        // 16-byte loads, four per lane in flight: a loop of one dependent load per step pays a memory latency per step
+        // (64 of them at K = 2048)
+        for (int i0 = lane * 4; i0 < K; i0 += 512) {
+            float4 wv[4], xv[4], gv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + 128 * u;
+                if (i < K) {
+                    wv[u] = __ldg(reinterpret_cast<const float4*>(wr + i));
+                    xv[u] = *reinterpret_cast<const float4*>(x + i);
+                    gv[u] = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + i)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + 128 * u < K) {
+                    const float4 a = xv[u], g = gv[u], b = wv[u];
+                    if (gamma) ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                    acc += (a.x * g.x) * b.x + (a.y * g.y) * b.y + (a.z * g.z) * b.z + (a.w * g.w) * b.w;
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < K; i += 32) {
+            float v = x[i];
+            if (gamma) { ss = fmaf(v, v, ss); v *= gamma[i]; }
+            acc = fmaf(v, __ldg(wr + i), acc);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }

@@ -190,6 +190,36 @@ int upload_weight(Context* c, uint32_t type, int64_t N, int K, const void* host_
     return GGB_OK;
 }
 
+int concat_weight_rows(Context* c, const DeviceWeight* a, const DeviceWeight* b, DeviceWeight** out) {
+    if (!a || !b || a->w.layout != 1 || b->w.layout != 1 || a->w.type != b->w.type || a->w.K != b->w.K || a->w.N % 16 ||
+        (a->w.type != T_Q4_K && a->w.type != T_Q6_K))
+        return set_status(c, GGB_INVALID_PARAM, "concat_weight_rows: both weights must be Q4_K or Q6_K in the row-group-major layout with the same K");
+    const bool q4 = a->w.type == T_Q4_K;
+    const int per_gb[4] = {q4 ? 256 : 2048, q4 ? 2048 : 1024, q4 ? 0 : 256, q4 ? 0 : 32};
+    const int nb = a->w.nb;
+    const int64_t ga = a->w.N / 16, gb = (b->w.N + 15) / 16;
+    DeviceWeight* dw = new DeviceWeight();
+    size_t off[4], acc = 0;
+    for (int i = 0; i < 4; ++i) { off[i] = acc; acc += align_up(static_cast<size_t>(ga + gb) * nb * per_gb[i], 256); }
+    dw->bytes = acc;
+    cudaError_t e = cudaMalloc(&dw->base, dw->bytes);
+    if (e != cudaSuccess) { delete dw; return cuda_status(c, e, "cudaMalloc(weight)"); }
+    uint8_t* p = static_cast<uint8_t*>(dw->base);
+    dw->w = a->w;
+    dw->w.N = a->w.N + b->w.N;
+    for (int i = 0; i < 4 && e == cudaSuccess; ++i) {
+        dw->w.s[i] = per_gb[i] ? p + off[i] : nullptr;
+        if (!per_gb[i]) continue;
+        const size_t na = static_cast<size_t>(ga) * nb * per_gb[i], nbb = static_cast<size_t>(gb) * nb * per_gb[i];
+        e = cudaMemcpyAsync(p + off[i], a->w.s[i], na, cudaMemcpyDeviceToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(p + off[i] + na, b->w.s[i], nbb, cudaMemcpyDeviceToDevice, c->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { free_weight(dw); return cuda_status(c, e, "concat_weight_rows"); }
+    *out = dw;
+    return GGB_OK;
+}
+
 void free_weight(DeviceWeight* w) {
     if (!w) return;
     if (w->base) cudaFree(w->base);
