@@ -109,38 +109,48 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const MoeRouteArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x * 8 + warp;
     const float* wr = e < a.n_expert ? a.router + static_cast<size_t>(e) * a.hidden : (e == a.n_expert ? a.sh_gate_inp : nullptr);
-    if (wr) {
-        // with gamma: the logit of rms_norm(x) * gamma, formed as (x * gamma) . w times the row's 1 / rms
-        float acc = 0.0f, ss = 0.0f;
-        // four 16-byte loads of the router row per lane in flight (hidden is a multiple of 256): one dependent load per
-        // step would pay a memory latency per step
-        for (int i0 = lane * 4; i0 < a.hidden; i0 += 512) {
-            float4 wv[4], xv[4], gv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + 128 * u;
-                if (i < a.hidden) {
-                    wv[u] = __ldg(reinterpret_cast<const float4*>(wr + i));
-                    xv[u] = *reinterpret_cast<const float4*>(a.x + i);
-                    gv[u] = a.gamma ? __ldg(reinterpret_cast<const float4*>(a.gamma + i)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-                }
+    // x * gamma once per CTA into shared memory (hidden <= 8192), the sum of squares with it; a warp then has all the
+    // 16-byte loads of its router row in flight at once (sixteen at a time)
+    __shared__ __align__(16) float xg[8192];
+    __shared__ float ss_w[8];
+    {
+        float ss = 0.0f;
+        for (int i = threadIdx.x * 4; i < a.hidden; i += 1024) {
+            float4 v = *reinterpret_cast<const float4*>(a.x + i);
+            if (a.gamma) {
+                const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma + i));
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (i0 + 128 * u < a.hidden) {
-                    float4 v = xv[u];
-                    const float4 b = wv[u], g = gv[u];
-                    if (a.gamma) {
-                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                        v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w;
-                    }
-                    acc += v.x * b.x + v.y * b.y + v.z * b.z + v.w * b.w;
-                }
-            }
+            *reinterpret_cast<float4*>(xg + i) = v;
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o); ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o); }
-        if (a.gamma) acc *= 1.0f / sqrtf(ss / static_cast<float>(a.hidden) + a.eps);
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if (lane == 0) ss_w[warp] = ss;
+    }
+    __syncthreads();
+    if (wr) {
+        float acc = 0.0f;
+        for (int i0 = lane * 4; i0 < a.hidden; i0 += 2048) {
+            float4 wv[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (i0 + 128 * u < a.hidden) wv[u] = __ldg(reinterpret_cast<const float4*>(wr + i0 + 128 * u));
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (i0 + 128 * u < a.hidden) {
+                    const float4 v = *reinterpret_cast<const float4*>(xg + i0 + 128 * u), b = wv[u];
+                    acc += v.x * b.x + v.y * b.y + v.z * b.z + v.w * b.w;
+                }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+        if (a.gamma) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) ss += ss_w[q];
+            acc *= 1.0f / sqrtf(ss / static_cast<float>(a.hidden) + a.eps);
+        }
         if (lane == 0) a.logits[e] = acc;
     }
     __threadfence();                       // this CTA's logits are visible before its ticket is
@@ -166,8 +176,8 @@ int moe_ffn_enqueue(Context* h, const ggb_moe_params* p, float* scr, cudaStream_
     if (!p || !p->x || !p->y || !p->router || !p->gate_exps || !p->up_exps || !p->down_exps)
         return set_status(h, GGB_INVALID_PARAM, "moe_ffn: null pointer");
     if (p->hidden <= 0 || p->hidden % 256 || p->eff <= 0 || p->eff % 256 || p->n_expert < 1 || p->n_expert > 1024 || p->top_k < 1 ||
-        p->top_k > kMaxTopK - 1 || p->top_k > p->n_expert)
-        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden and eff must be multiples of 256, n_expert <= 1024, top_k <= 15");
+        p->top_k > kMaxTopK - 1 || p->top_k > p->n_expert || p->hidden > 8192)
+        return set_status(h, GGB_INVALID_PARAM, "moe_ffn: hidden (<= 8192) and eff must be multiples of 256, n_expert <= 1024, top_k <= 15");
     // expert parallel: this rank holds experts [ep_first, ep_first + ep_local) of the n_expert the router knows
     const bool ep = p->ep_local > 0;
     const int n_local = ep ? p->ep_local : p->n_expert, ep_first = ep ? p->ep_first : 0;
