@@ -33,7 +33,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from ggnpu_b200 import synth as S  # noqa: E402
+from ggnpu_b200.testing import synth as S  # noqa: E402
 
 PROMPT_LEN = 128
 WORKLOAD = "llama-3.2-1b-shape Q4_K_M-style (Q4_K; attn_v, ffn_down Q6_K), batch-1 greedy decode after a 128-token prompt, ctx 2048"
@@ -56,7 +56,7 @@ class ClockSampler:
     def __init__(self, index: int):
         self.rows, self.proc = [], None
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
@@ -67,12 +67,18 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self, t0=None, t1=None):
+    def close(self):
+        if self.proc:
+            self.proc.terminate()
+
+    def stats(self, t0=None, t1=None):
+        """Median SM clock, maximum clock and the throttle reasons seen in [t0, t1] (perf_counter times; None = open end)."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        rows = [r for t, r in self.rows if (t0 is None or t >= t0) and (t1 is None or t <= t1 + 0.2)] or [r for _, r in self.rows]
+        if t1 is not None:
+            time.sleep(0.05)                      # let the sample that covers the end of the window arrive
+        snap = list(self.rows)
+        rows = [r for t, r in snap if (t0 is None or t >= t0) and (t1 is None or t <= t1 + 0.03)] or [r for _, r in snap[-3:]]
         sm, mx, reasons = [], [], set()
         for r in rows:
             try:
@@ -236,9 +242,9 @@ def run_ours(args):
             n -= m
 
     # ---- value: device-resident loop ----
+    sampler = ClockSampler(local) if rank == 0 else None      # from before the warm-up to the end of the roofline sweeps
     if W:
         generate(W)
-    sampler = ClockSampler(local) if rank == 0 else None
     barrier()
     launches0 = b.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -250,7 +256,7 @@ def run_ours(args):
     t_end = time.perf_counter()
     launches = b.launch_count() - launches0
     ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop(t_start, t_end) if sampler else None
+    clocks = sampler.stats(t_start, t_end) if sampler else None
     first, pos = state["tok"], state["pos"]
     bytes_step = model.decode_bytes(max(PROMPT_LEN, pos - K // 2))
 
@@ -368,6 +374,10 @@ def run_ours(args):
         for wg, wu in copies:
             b.free_weight(wg); b.free_weight(wu)
 
+    if sampler:
+        # the same sampler over everything so far: warm-up, timed loop, end-to-end loop and the two roofline sweeps
+        clocks["whole_run"] = sampler.stats(None, None)
+        sampler.close()
     if rank == 0:
         peak, peak_kind = peaks()
         value = world * K / (ms_max * 1e-3)

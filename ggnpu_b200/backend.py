@@ -430,7 +430,7 @@ class Model:
     """A llama / qwen2 / qwen3-style decoder resident in HBM.
 
     `tensors` maps GGUF tensor names to (ggml type id, dims with dims[0]=K, raw bytes),
-    the form ggnpu_b200.synth.SynthModel.tensors has."""
+    the form ggnpu_b200.testing.synth.SynthModel.tensors has."""
 
     def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = "", n_seq: int = 1):
         self.b, self.cfg = backend, cfg
@@ -566,7 +566,7 @@ _Q35_EXPERT = ("ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weig
 
 class Q35Model:
     """A qwen35moe decoder (Gated DeltaNet + gated full attention + mixture-of-experts FFN, the reference's
-    src/cli/main.cpp:2859-3232) resident in HBM.  `tensors` as ggnpu_b200.synth.build_q35_model makes them.
+    src/cli/main.cpp:2859-3232) resident in HBM.  `tensors` as ggnpu_b200.testing.synth.build_q35_model makes them.
     On a backend that joined a group the model is expert parallel: this process keeps its slice of the
     experts (a contiguous range along the expert axis), everything else is replicated."""
 

@@ -22,7 +22,7 @@ import dataclasses
 
 import numpy as np
 
-from . import synth as S
+from . import gguf_types as S
 
 COLUMN = ("attn_q.weight", "attn_k.weight", "attn_v.weight", "ffn_gate.weight", "ffn_up.weight",
           "attn_q.bias", "attn_k.bias", "attn_v.bias")

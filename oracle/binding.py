@@ -281,7 +281,7 @@ _V_SLOTS = {"attn_norm.weight": 0, "ffn_norm.weight": 1, "attn_q.bias": 2, "attn
 
 class OracleModel:
     """The generic-architecture forward of the reference CLI, restated
-    (ggo_forward), over the tensors of a ggnpu_b200.synth.SynthModel."""
+    (ggo_forward), over the tensors of a ggnpu_b200.testing.synth.SynthModel."""
 
     def __init__(self, oracle: Oracle, synth):
         self.o, self.cfg = oracle, synth.cfg
@@ -352,7 +352,7 @@ _Q35_V = {"attn_norm.weight": 0, "post_attention_norm.weight": 1, "ssm_conv1d.we
 
 class OracleQ35Model:
     """The qwen35moe forward of the reference CLI, restated (ggo_q35_forward), over the tensors of
-    ggnpu_b200.synth.build_q35_model.  One token per call, like the reference."""
+    ggnpu_b200.testing.synth.build_q35_model.  One token per call, like the reference."""
 
     def __init__(self, oracle: Oracle, synth):
         self.o, self.cfg = oracle, synth.cfg

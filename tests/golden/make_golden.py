@@ -17,7 +17,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-from ggnpu_b200 import synth as S  # noqa: E402
+from ggnpu_b200.testing import synth as S  # noqa: E402
 from oracle.binding import Ref, run_ref_cli  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from conftest import ROOT
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 
 pytestmark = pytest.mark.gpu
 

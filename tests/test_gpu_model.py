@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from conftest import rel_l2
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 
 pytestmark = pytest.mark.gpu
 

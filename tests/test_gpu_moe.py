@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from conftest import rel_l2
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 from ggnpu_b200.backend import Status
 
 pytestmark = pytest.mark.gpu

@@ -8,7 +8,7 @@ float rounding of a boundary between two tokens; on the seeded cases below none 
 import numpy as np
 import pytest
 
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 
 pytestmark = pytest.mark.gpu
 

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from conftest import bits, rel_l2
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 from ggnpu_b200.backend import Status
 
 GGUF_NAMES = {S.IQ2_XXS: "IQ2_XXS", S.IQ2_XS: "IQ2_XS", S.IQ2_S: "IQ2_S", S.IQ3_XXS: "IQ3_XXS", S.IQ3_S: "IQ3_S",

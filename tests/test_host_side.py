@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from conftest import ROOT, bits
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 
 
 def test_library_exports_every_declared_symbol():

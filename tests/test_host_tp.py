@@ -11,7 +11,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 from ggnpu_b200 import tp
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import bits, rel_l2
-from ggnpu_b200 import synth as S
+from ggnpu_b200.testing import synth as S
 
 
 def f16_bytes(v):

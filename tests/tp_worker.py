@@ -16,7 +16,7 @@ def main():
     rank, size, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
     import torch
     import torch.distributed as dist
-    from ggnpu_b200 import synth as S
+    from ggnpu_b200.testing import synth as S
     from ggnpu_b200.backend import CudaBackend, Model
 
     torch.cuda.set_device(rank)
