@@ -47,6 +47,11 @@ struct AttnPagedArgs {
     // this token's projections [n_kv][hd]; the kernel rotates, stores into the cache and attends.
     int fuse, neox;
     int skip_merge;           // 1: leave the per-split partials for the consumer (the output projection merges them)
+    // optional: one counter per (token, KV head), zero before the first launch.  The CTA of a (token, KV head) that
+    // finishes last merges the splits of its query heads itself and writes `out`, so neither the merge kernel nor a
+    // merging consumer is needed (the counter is back at zero when the launch ends)
+    int* merge_ticket;
+    int merge_min_splits;     // with merge_ticket: merge in the kernel only when at least this many splits are visible (0: always)
     const float* k_new;
     const float* v_new;
     __nv_bfloat16* k_cache_w;

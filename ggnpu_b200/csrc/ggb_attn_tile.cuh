@@ -265,6 +265,62 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             if (w == 0) { pg[0] = mrun[gq]; pg[1] = lrun[gq]; }
         }
     }
+    if (!a.merge_ticket) return;
+    // ---- the last CTA of this (token, KV head) merges the splits ----
+    // Every CTA publishes its partials (fence), then takes a ticket; the one that takes the last ticket sees all partials
+    // (it reads them past L1) and owns the merge.  No CTA waits for another.
+    const int n_active = min(a.n_splits, pos / keys_per_split + 1);
+    if (n_active < a.merge_min_splits) return;                      // few splits: the consumer merges them in its prologue
+    int* flag = reinterpret_cast<int*>(corr);                       // corr[] is free now
+    __threadfence();
+    sync();
+    if (tid == 0) {
+        int* ticket = a.merge_ticket + static_cast<size_t>(t) * a.n_kv + h;
+        const int got = atomicAdd(ticket, 1);
+        const int last = got == n_active - 1;
+        if (last) *ticket = 0;                                      // every CTA of this (token, head) has taken its ticket
+        flag[0] = last;
+    }
+    sync();
+    if (!flag[0]) return;
+    __threadfence();
+    const float* base = a.partial + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits * (HD + 2);
+    float* wts = S;                                                 // [G][64]: exp(max_s - max) per head and split (n_splits <= 64)
+    float* lsm = reinterpret_cast<float*>(Kt);                      // [G][64]: the splits' sums (the K tile is free now)
+    for (int i = tid; i < G * n_active; i += 128) {                 // every split's (max, sum) by its own thread: independent loads
+        const int gq = i / n_active, s2 = i - gq * n_active;
+        const float* ps = base + (static_cast<size_t>(gq) * a.n_splits + s2) * (HD + 2);
+        wts[gq * 64 + s2] = __ldcg(ps);
+        lsm[gq * 64 + s2] = __ldcg(ps + 1);
+    }
+    sync();
+    if (tid < G) {
+        float mx = -INFINITY;
+        for (int s2 = 0; s2 < n_active; ++s2) mx = fmaxf(mx, wts[tid * 64 + s2]);
+        float lsum = 0.0f;
+        for (int s2 = 0; s2 < n_active; ++s2) {
+            const float wv = expf(wts[tid * 64 + s2] - mx);
+            wts[tid * 64 + s2] = wv;
+            lsum += lsm[tid * 64 + s2] * wv;
+        }
+        mrun[tid] = 1.0f / lsum;
+    }
+    sync();
+    for (int idx = tid; idx < G * HD; idx += 128) {
+        const int gq = idx / HD, d = idx - gq * HD;
+        const float* pg = base + static_cast<size_t>(gq) * a.n_splits * (HD + 2) + 2 + d;
+        float o = 0.0f;
+        int s2 = 0;
+        for (; s2 + 8 <= n_active; s2 += 8) {                       // eight loads in flight
+            float pv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) pv[u] = __ldcg(pg + static_cast<size_t>(s2 + u) * (HD + 2));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) o += pv[u] * wts[gq * 64 + s2 + u];
+        }
+        for (; s2 < n_active; ++s2) o += __ldcg(pg + static_cast<size_t>(s2) * (HD + 2)) * wts[gq * 64 + s2];
+        a.out[(static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G + gq) * HD + d] = o * mrun[gq];
+    }
 }
 
 }  // namespace ggb

@@ -96,6 +96,8 @@ __device__ __forceinline__ float wmax(float v) {
 // the paged attention kernel (max, sum, acc[hd] per head and split) are merged on the fly, which
 // saves the separate merge kernel.  partial == nullptr: x is read from memory as usual.
 struct AttnMerge {
+    const float* merged;      // with merge_below > 0: the row already merged by the attention kernel (many visible splits)
+    int merge_below;
     const float* partial;     // [n_head][n_splits][hd + 2]
     const int32_t* d_pos;     // position of the token (device scalar), or nullptr -> pos0
     int pos0;
@@ -299,8 +301,15 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 1) gemv_mma_q4k_kernel(cons
     // scalar that can be applied to the finished dot products; the limbs are taken from x * gamma.
     // A warp converts 256-blocks warp, warp+8, ...; four blocks are loaded before any is converted so
     // that their memory latencies overlap.
+    // attention splits: merged here while few are visible, by the attention kernel from merge_below on (the position is
+    // the same for every CTA, so all take the same branch)
+    bool merge_here = a.attn.partial != nullptr;
+    if (merge_here && a.attn.merge_below > 0) {
+        const int pos = a.attn.d_pos ? a.attn.d_pos[0] : a.attn.pos0;
+        merge_here = min(a.attn.n_splits, pos / a.attn.keys_per_split + 1) < a.attn.merge_below;
+    }
     for (int m = 0; m < M; ++m) {
-        const float* xr = a.x + static_cast<size_t>(m) * a.lda;
+        const float* xr = (a.attn.partial ? a.attn.merged : a.x) + static_cast<size_t>(m) * a.lda;
         float ss = 0.0f;
         for (int bb = warp; bb < (K >> 8); bb += 4 * kWarps) {
             float v[4][8];
@@ -309,7 +318,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 1) gemv_mma_q4k_kernel(cons
                 const int b = bb + u * kWarps;
                 if (b < (K >> 8)) {
                     const int k0 = b * 256 + lane * 8;
-                    if (a.attn.partial) attn_merge8(a.attn, k0, v[u]);
+                    if (merge_here) attn_merge8(a.attn, k0, v[u]);
                     else {
                         const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr + k0)), p1 = __ldg(reinterpret_cast<const float4*>(xr + k0 + 4));
                         v[u][0] = p0.x; v[u][1] = p0.y; v[u][2] = p0.z; v[u][3] = p0.w; v[u][4] = p1.x; v[u][5] = p1.y; v[u][6] = p1.z; v[u][7] = p1.w;
@@ -659,6 +668,7 @@ int launch_mma_t(Context* c, const GemvArgs& g, cudaStream_t s) {
     for (int i = 0; i < g.n_cat; ++i) { a.cat[i].w = g.cat_w[i]; a.cat[i].y = g.cat_y[i]; a.cat[i].bias = g.cat_bias[i]; a.cat[i].ldc = g.cat_ldc[i]; a.cat[i].g_start = cat_start[i]; }
     a.attn.partial = g.attn_partial; a.attn.d_pos = g.attn_d_pos; a.attn.pos0 = g.attn_pos0; a.attn.n_splits = g.attn_n_splits;
     a.attn.keys_per_split = g.attn_keys_per_split; a.attn.hd = g.attn_hd;
+    a.attn.merge_below = g.attn_merged ? g.attn_merge_below : 0; a.attn.merged = g.attn_merged;
     a.sb = sb; a.spr = spr; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = stage_bytes;
     a.sel = g.sel; a.sel_mode = g.sel ? g.sel_mode : 0; a.sel_groups = g.sel ? g.sel_rows / 16 : 0;
     a.klog = K; a.nblog = nb; a.nlog = n_log; a.xscale = g.xscale; a.xscale_run = g.xscale_run > 0 ? g.xscale_run : 1;

@@ -33,6 +33,11 @@ struct GemvArgs {
     const float* attn_partial = nullptr;
     const int32_t* attn_d_pos = nullptr;
     int attn_pos0 = 0, attn_n_splits = 0, attn_keys_per_split = 0, attn_hd = 0;
+    // attn_merge_below > 0: the kernel merges the partials only while fewer than that many splits are visible at the
+    // current position; from there on the attention kernel has merged them itself (AttnPagedArgs::merge_min_splits) and
+    // the merged row is read from attn_merged
+    int attn_merge_below = 0;
+    const float* attn_merged = nullptr;
     // optional (tensor-core kernel): up to two more matrices stacked along N sharing x, K, M, epilogue kind
     int n_cat = 0;
     PackedW cat_w[2];

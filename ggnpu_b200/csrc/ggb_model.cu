@@ -30,6 +30,7 @@ struct Layer {
 // then dequantises its weights once per 2048 tokens); otherwise 256, which bounds the per-token
 // attention kernel's split scratch.
 constexpr int kSmallChunk = 256, kLargeChunk = 2048;
+constexpr int kMergeInAttn = 12;    // visible context splits from which the attention kernel merges them itself
 constexpr int kSpecRows = 16;       // a verified block: the fed token + up to 15 drafted ones (src/cli/main.cpp:2305-2308)
 
 }  // namespace
@@ -53,6 +54,7 @@ struct ggb_model_s {
     // activations
     float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
     float *partial = nullptr, *amax_partial = nullptr;
+    int* attn_ticket = nullptr;          // per (token, KV head): the split that finishes last merges (AttnPagedArgs::merge_ticket)
     uint16_t* act_img = nullptr;         // SwiGLU output of a prompt chunk as the down projection's fp16 tile image
     bool tc_images = false;              // prompt chunks pass activations between GEMMs as tile images
     int32_t *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *d_gen = nullptr, *d_step = nullptr;
@@ -198,9 +200,18 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         aa.partial = m->partial; aa.partial_tok_cap = kSmallChunk; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
         aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
         aa.pages_per_split = m->pages_per_split;
-        // single-token steps: the output projection merges the attention splits itself
+        // Who merges the context splits.  Single-token step with the output projection in the tensor-core layout: that
+        // projection's prologue while few splits are visible (0.6 us per split, overlapped with its other loads).  From
+        // kMergeInAttn visible splits on, and for several rows, the attention kernel itself (its last CTA per KV head:
+        // ~3 us whatever the count; 8B shape at position 4100, 23 splits: 3.27 ms per step against 3.32) -- but only with four or more KV heads: with one or two, two CTAs would merge
+        // everything (measured on the 12 / 2-head shape: 1.74 ms per step against 1.55 with the merge kernel, whose grid
+        // is one CTA per query head).
         const bool merge_in_gemv = single && l.o->w.layout == 1;
-        aa.skip_merge = merge_in_gemv ? 1 : 0;
+        static const bool no_ticket = getenv("GGB_NO_ATTN_MERGE") != nullptr;      // keep every merge out of the attention kernel
+        const bool merge_in_attn = d.n_kv >= 4 && !no_ticket;
+        aa.merge_ticket = merge_in_attn ? m->attn_ticket : nullptr;
+        aa.merge_min_splits = merge_in_gemv ? kMergeInAttn : 0;
+        aa.skip_merge = (merge_in_gemv && !merge_in_attn) ? 1 : 0;
         M_TRY(launch_attn_paged(c, aa, n_tok, s));
 
         // Tensor parallel: attn_output and ffn_down are row parallel (this rank's K range), so their
@@ -212,6 +223,7 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (merge_in_gemv) {
             a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = m->n_splits;
+            if (merge_in_attn) { a.attn_merged = m->att; a.attn_merge_below = kMergeInAttn; }
             a.attn_keys_per_split = m->pages_per_split * m->page; a.attn_hd = hd;
         }
         M_TRY(launch_gemv(c, a, s));
@@ -428,6 +440,8 @@ int ggb_model_finalize(ggb_model m) {
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
     M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd)));
     M_TRY(dev_alloc(m, &m->amax_partial, 512));
+    M_TRY(dev_alloc(m, &m->attn_ticket, static_cast<size_t>(kSmallChunk) * d.n_kv));
+    M_TRY(cuda_status(c, cudaMemset(m->attn_ticket, 0, sizeof(int) * kSmallChunk * d.n_kv), "memset"));
     M_TRY(dev_alloc(m, &m->logits_rows, static_cast<size_t>(kSpecRows) * d.vocab));
     M_TRY(dev_alloc(m, &m->d_rows_next, kSpecRows));
     M_TRY(dev_alloc(m, &m->d_seq_pos, kSpecRows));

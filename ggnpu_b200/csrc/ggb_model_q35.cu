@@ -70,6 +70,7 @@ struct ggb_q35_model_s {
     float *mixed = nullptr, *zgate = nullptr, *ab = nullptr, *conv = nullptr, *o_all = nullptr;
     float *qg = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *partial = nullptr;
     float *moe_scr = nullptr, *logits = nullptr, *amax_partial = nullptr;
+    int* attn_ticket = nullptr;
     int32_t *d_tokens = nullptr, *d_pos = nullptr, *d_next = nullptr, *d_gen = nullptr, *d_step = nullptr, *d_forced = nullptr, *d_n_forced = nullptr;
     int32_t* h_io = nullptr;
     float* h_logits = nullptr;
@@ -156,6 +157,7 @@ int q35_enqueue_step(ggb_q35_model m) {
             aa.partial = m->partial; aa.partial_tok_cap = 1; aa.out = m->att; aa.d_pos = m->d_pos; aa.pos0 = 0;
             aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = Hd; aa.page = m->page; aa.n_splits = m->n_splits;
             aa.pages_per_split = m->pages_per_split;
+            aa.merge_ticket = d.n_kv >= 4 ? m->attn_ticket : nullptr;      // enough KV heads: the last split of each merges, no merge launch
             Q_TRY(launch_attn_paged(c, aa, 1, s));
             Q_TRY(launch_attn_gate(c, m->att, m->qg, d.n_head, Hd, s));
             a = q_gemv(l.o, m->att, qdim, x, H);
@@ -397,6 +399,7 @@ int ggb_q35_finalize(ggb_q35_model m) {
     }
     Q_TRY(q_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
     Q_TRY(q_alloc(m, &m->amax_partial, 512));
+    Q_TRY(q_alloc(m, &m->attn_ticket, static_cast<size_t>(std::max(d.n_kv, 1)), true));
     Q_TRY(q_alloc(m, &m->d_tokens, 1, true)); Q_TRY(q_alloc(m, &m->d_pos, 1, true)); Q_TRY(q_alloc(m, &m->d_next, 1, true));
     Q_TRY(q_alloc(m, &m->d_step, 1, true)); Q_TRY(q_alloc(m, &m->d_n_forced, 1, true));
     Q_TRY(q_alloc(m, &m->d_gen, static_cast<size_t>(d.ctx), true));
