@@ -217,7 +217,7 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     }
     if (a.partial_tok_cap > 0 && n_tok > a.partial_tok_cap)
         return set_status(c, GGB_INVALID_PARAM, "attention: prompt chunk larger than the split scratch and not covered by the tensor-core kernel");
-    if (a.merge_ticket && a.n_splits > 64) return set_status(c, GGB_INVALID_PARAM, "attention: more than 64 context splits");
+    if (a.merge_ticket && a.n_splits > 128) return set_status(c, GGB_INVALID_PARAM, "attention: more than 128 context splits");
     dim3 grid(a.n_kv, a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
     size_t smem = 0;

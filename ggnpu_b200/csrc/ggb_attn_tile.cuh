@@ -285,23 +285,23 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     if (!flag[0]) return;
     __threadfence();
     const float* base = a.partial + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits * (HD + 2);
-    float* wts = S;                                                 // [G][64]: exp(max_s - max) per head and split (n_splits <= 64)
-    float* lsm = reinterpret_cast<float*>(Kt);                      // [G][64]: the splits' sums (the K tile is free now)
+    float* wts = reinterpret_cast<float*>(Kt);                      // [G][128]: exp(max_s - max) per head and split (n_splits <= 128;
+    float* lsm = wts + 8 * 128;                                     // [G][128]: the splits' sums       the K tile is free now)
     for (int i = tid; i < G * n_active; i += 128) {                 // every split's (max, sum) by its own thread: independent loads
         const int gq = i / n_active, s2 = i - gq * n_active;
         const float* ps = base + (static_cast<size_t>(gq) * a.n_splits + s2) * (HD + 2);
-        wts[gq * 64 + s2] = __ldcg(ps);
-        lsm[gq * 64 + s2] = __ldcg(ps + 1);
+        wts[gq * 128 + s2] = __ldcg(ps);
+        lsm[gq * 128 + s2] = __ldcg(ps + 1);
     }
     sync();
     if (tid < G) {
         float mx = -INFINITY;
-        for (int s2 = 0; s2 < n_active; ++s2) mx = fmaxf(mx, wts[tid * 64 + s2]);
+        for (int s2 = 0; s2 < n_active; ++s2) mx = fmaxf(mx, wts[tid * 128 + s2]);
         float lsum = 0.0f;
         for (int s2 = 0; s2 < n_active; ++s2) {
-            const float wv = expf(wts[tid * 64 + s2] - mx);
-            wts[tid * 64 + s2] = wv;
-            lsum += lsm[tid * 64 + s2] * wv;
+            const float wv = expf(wts[tid * 128 + s2] - mx);
+            wts[tid * 128 + s2] = wv;
+            lsum += lsm[tid * 128 + s2] * wv;
         }
         mrun[tid] = 1.0f / lsum;
     }
@@ -316,9 +316,9 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
 #pragma unroll
             for (int u = 0; u < 8; ++u) pv[u] = __ldcg(pg + static_cast<size_t>(s2 + u) * (HD + 2));
 #pragma unroll
-            for (int u = 0; u < 8; ++u) o += pv[u] * wts[gq * 64 + s2 + u];
+            for (int u = 0; u < 8; ++u) o += pv[u] * wts[gq * 128 + s2 + u];
         }
-        for (; s2 < n_active; ++s2) o += __ldcg(pg + static_cast<size_t>(s2) * (HD + 2)) * wts[gq * 64 + s2];
+        for (; s2 < n_active; ++s2) o += __ldcg(pg + static_cast<size_t>(s2) * (HD + 2)) * wts[gq * 128 + s2];
         a.out[(static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G + gq) * HD + d] = o * mrun[gq];
     }
 }

@@ -49,6 +49,9 @@ struct ggb_model_s {
     __nv_bfloat16 *k_cache = nullptr, *v_cache = nullptr;
     int32_t* block_table = nullptr;
     int page = 64, n_pages = 0, n_splits = 1, pages_per_split = 1;
+    // single-token steps of a long context cut it finer (up to 128 splits, one 64-key chunk per CTA where possible: every
+    // CTA's K/V loads are then in flight from its first instruction); several rows per step keep the coarser cut
+    int n_splits1 = 1, pages_per_split1 = 1;
     size_t kv_layer_elems = 0;
     float *cos_tab = nullptr, *sin_tab = nullptr;
     // activations
@@ -198,8 +201,10 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         }
         aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = table;
         aa.partial = m->partial; aa.partial_tok_cap = kSmallChunk; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
-        aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = m->n_splits;
-        aa.pages_per_split = m->pages_per_split;
+        const bool fine = single && m->attn_ticket && d.n_kv >= 4;      // the fine cut relies on the in-kernel merge
+        const int n_splits = fine ? m->n_splits1 : m->n_splits, pps = fine ? m->pages_per_split1 : m->pages_per_split;
+        aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = n_splits;
+        aa.pages_per_split = pps;
         // Who merges the context splits.  Single-token step with the output projection in the tensor-core layout: that
         // projection's prologue while few splits are visible (0.6 us per split, overlapped with its other loads).  From
         // kMergeInAttn visible splits on, and for several rows, the attention kernel itself (its last CTA per KV head:
@@ -222,9 +227,9 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         a = gemv_args(l.o, m->att, n_tok, qd, m->x, H);
         a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (merge_in_gemv) {
-            a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = m->n_splits;
+            a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = n_splits;
             if (merge_in_attn) { a.attn_merged = m->att; a.attn_merge_below = kMergeInAttn; }
-            a.attn_keys_per_split = m->pages_per_split * m->page; a.attn_hd = hd;
+            a.attn_keys_per_split = pps * m->page; a.attn_hd = hd;
         }
         M_TRY(launch_gemv(c, a, s));
         if (tp) M_TRY(tp_all_reduce(c, m->x, static_cast<size_t>(n_tok) * H, s));
@@ -415,6 +420,8 @@ int ggb_model_finalize(ggb_model m) {
     // paged KV
     m->n_pages = (d.ctx + m->page - 1) / m->page;
     attn_split_geometry(m->n_pages, d.n_kv, &m->n_splits, &m->pages_per_split);
+    m->pages_per_split1 = (m->n_pages + 127) / 128;
+    m->n_splits1 = (m->n_pages + m->pages_per_split1 - 1) / m->pages_per_split1;
     m->kv_layer_elems = static_cast<size_t>(m->n_seq) * m->n_pages * d.n_kv * m->page * hd;
     M_TRY(dev_alloc(m, &m->k_cache, m->kv_layer_elems * d.n_layer));
     M_TRY(dev_alloc(m, &m->v_cache, m->kv_layer_elems * d.n_layer));
@@ -438,7 +445,7 @@ int ggb_model_finalize(ggb_model m) {
     m->tc_images = tensor_attn && d.hidden % 64 == 0 && d.ffn % 64 == 0;
     if (m->tc_images) M_TRY(dev_alloc(m, &m->act_img, gemm_tc_image_elems(m->chunk, d.ffn)));
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
-    M_TRY(dev_alloc(m, &m->partial, attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd)));
+    M_TRY(dev_alloc(m, &m->partial, std::max(attn_partial_floats(kSmallChunk, d.n_head, m->n_splits, hd), attn_partial_floats(1, d.n_head, m->n_splits1, hd))));
     M_TRY(dev_alloc(m, &m->amax_partial, 512));
     M_TRY(dev_alloc(m, &m->attn_ticket, static_cast<size_t>(kSmallChunk) * d.n_kv));
     M_TRY(cuda_status(c, cudaMemset(m->attn_ticket, 0, sizeof(int) * kSmallChunk * d.n_kv), "memset"));

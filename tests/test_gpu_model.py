@@ -67,6 +67,32 @@ def test_prefill_then_decode_matches_oracle(backend, oracle, name):
     gm.close()
 
 
+def test_long_context_splits_merged_in_the_attention_kernel(backend, oracle):
+    """900 prompt tokens of a model with four KV heads: a decode step then sees 15 context splits (one 64-key page each),
+    which the attention kernel's last CTA per KV head merges itself; below 12 visible splits the output projection does
+    it.  Both sides of the switch against the oracle, and the greedy stream across it."""
+    from ggnpu_b200.backend import Model
+    from oracle.binding import OracleModel
+    cfg = S.tiny_config(n_head=8, n_kv=4, head_dim=64, hidden=512, ffn=1024, seed=31, ctx=2048)
+    synth = S.build_model(cfg)
+    om = OracleModel(oracle, synth)
+    gm = Model(backend, cfg, synth.tensors)
+    ids = np.random.default_rng(8).integers(0, cfg.vocab, 900).astype(np.int32)
+    for n_prompt in (700, 900):            # 11 visible splits (merged by the projection), 15 (merged by the attention kernel)
+        want = om.forward(ids[:n_prompt], 0)
+        got, nxt = gm.prefill(ids[:n_prompt], 0)
+        logits_ok(got, want)
+        tok, pos = oracle.argmax_first(want), n_prompt
+        for _ in range(3):
+            want = om.forward([tok], pos)
+            got, nxt = gm.decode(tok, pos)
+            err = logits_ok(got, want)
+            pos += 1
+            tok = oracle.argmax_first(want)
+        om = OracleModel(oracle, synth)
+    gm.close()
+
+
 def test_device_feedback_loop_equals_host_loop(backend):
     """ggb_model_generate (token fed back on the device, CUDA graph replays) produces the same ids as
     stepping ggb_model_decode from the host."""
