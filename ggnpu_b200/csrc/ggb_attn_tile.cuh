@@ -80,21 +80,22 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     // overlaps the q / new-key preparation below (head_dim <= 128; larger heads load in the loop).
     constexpr int NPF = HD <= 128 ? HD / 16 : 0;
     uint4 kpre[NPF > 0 ? NPF : 1], vpre[NPF > 0 ? NPF : 1];
-    if (NPF > 0) {
-        const int nk0 = min(TK, j_end - j_begin);
+    // chunk [j0, j0 + n) of K and V into registers (16 bytes per thread and item, all loads in flight at once)
+    auto prefetch = [&](int j0, int n) {
 #pragma unroll
         for (int u = 0; u < NPF; ++u) {
             const int i = tid + 128 * u;
             const int row = i / (HD / 8), part = i - row * (HD / 8);
-            if (row < nk0) {
-                const int j = j_begin + row;
+            if (row < n) {
+                const int j = j0 + row;
                 const int page = bt[j / a.page], slot = j % a.page;
                 const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD + part * 8;
                 kpre[u] = *reinterpret_cast<const uint4*>(a.k_cache + o);
                 vpre[u] = *reinterpret_cast<const uint4*>(a.v_cache + o);
             }
         }
-    }
+    };
+    if (NPF > 0) prefetch(j_begin, min(TK, j_end - j_begin));
     if (tid < 8) { mrun[tid] = -INFINITY; lrun[tid] = 0.0f; }
     if (a.fuse) {
         // optional per-head RMS norm of q and k before the rotation, sum of squares in double
@@ -156,7 +157,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     for (int jc = j_begin; jc < j_end; jc += TK) {
         const int nk = min(TK, j_end - jc);
         sync();                                   // previous chunk fully consumed
-        if (NPF > 0 && jc == j_begin) {
+        if (NPF > 0) {
 #pragma unroll
             for (int u = 0; u < NPF; ++u) {
                 const int i = tid + 128 * u;
@@ -167,6 +168,8 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
                     *reinterpret_cast<uint4*>(Vt + row * KW + part * 4) = vpre[u];
                 }
             }
+            // the next chunk's rows are requested now and arrive while this chunk is scored and summed
+            if (jc + TK < j_end) prefetch(jc + TK, min(TK, j_end - jc - TK));
         } else
         for (int i = tid; i < nk * (HD / 8); i += 128) {
             const int row = i / (HD / 8), part = i - row * (HD / 8);
