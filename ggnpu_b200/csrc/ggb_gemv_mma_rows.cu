@@ -6,8 +6,9 @@
 // Here the three int8 limbs of up to 16 rows form up to 48 columns of the B operand = CG column groups of 8; a weight
 // fragment is loaded from shared memory once and feeds 2 * CG tensor-core instructions:
 //   column c = 3 m + p  (m activation row, p limb, weight 1, 1/128, 1/16384), column group c / 8, lane pair (c % 8) / 2.
-// The min term of Q4_K (dmin * m_sub * sum of x over the sub-block) and the -32 offset of Q6_K are subtracted in the
-// limb-0 column of each row (its weight is 1), so the three columns of a row simply add up.  At the end of a row group
+// The min term of Q4_K (dmin * m_sub * sum of x over the sub-block) and the -32 offset of Q6_K are float products per
+// (weight row, activation row); lane (g, t) accumulates those of rows g, g + 8 and activation rows t, t + 4, ... and adds
+// them to the limb-0 column of the row (its weight is 1) in the slab, so the three columns of a row simply add up.  At the end of a row group
 // every warp drops its column sums into a shared-memory slab; the team's first warp adds slabs and limb columns, applies
 // the epilogue and stores.
 // Shared memory bounds rows x K: 3 planes of K + 16 bytes per row (16 rows at K = 2048, 8 at 4096).  A longer K is cut
@@ -173,6 +174,7 @@ struct RowsArgs {
 template <int CG, int NMAT>
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const RowsArgs a) {
     constexpr int NC = 8 * CG;                         // B columns
+    constexpr int MI = CG == 2 ? 2 : (CG == 3 ? 2 : 4);   // activation rows per lane in the min / offset term: m = t + 4 i < M
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], x_bar;
     __shared__ float inv_s[16];
@@ -237,12 +239,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
     // ---------------- consumers ----------------
     const int g = lane >> 2, t = lane & 3;
     const int ncol = 3 * M;
-    // per column group: this lane's B column (plane), its two C columns, their activation row, limb weight, and whether a
-    // column is the limb-0 column of its row (it then also carries the min / offset term)
+    // per column group: this lane's B column (plane), its two C columns, their activation row and limb weight
     const int8_t* bplane[CG];
     int mrow[CG][2];
     float lw[CG][2];
-    bool limb0[CG][2];
 #pragma unroll
     for (int q = 0; q < CG; ++q) {
         bplane[q] = xl + static_cast<size_t>(min(8 * q + g, ncol - 1)) * plane_stride + 4 * t;
@@ -253,7 +253,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
             mrow[q][sl] = valid ? col / 3 : M - 1;
             const int p = col % 3;
             lw[q][sl] = valid ? (p == 0 ? 1.0f : (p == 1 ? 1.0f / 128.0f : 1.0f / 16384.0f)) : 0.0f;
-            limb0[q][sl] = valid && p == 0;
         }
     }
     pdl_wait();
@@ -286,13 +285,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
     float* my_slab = slab + static_cast<size_t>(warp) * NMAT * 16 * NC;
     for (int rg = team; rg < n_rg; rg += n_teams) {
         // column sums of this warp's share of the row group: [matrix][column group][row g: slots 0, 1 | row g + 8: slots 2, 3]
-        float F[NMAT][CG][4];
+        float F[NMAT][CG][4], Fm[NMAT][2][MI];
 #pragma unroll
-        for (int mat = 0; mat < NMAT; ++mat)
+        for (int mat = 0; mat < NMAT; ++mat) {
 #pragma unroll
             for (int q = 0; q < CG; ++q)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) F[mat][q][i] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MI; ++i) { Fm[mat][0][i] = 0.0f; Fm[mat][1][i] = 0.0f; }
+        }
         for (int ti = member; ti < tprg; ti += a.ws) {
             const int s = warp * a.P + st;
             if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
@@ -307,6 +309,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
             for (int q = 0; q < CG; ++q)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) f[q][i] = 0.0f;
+            float fmA[MI], fmB[MI];                      // min / offset terms: rows g, g + 8 x activation rows t + 4 i
+#pragma unroll
+            for (int i = 0; i < MI; ++i) { fmA[i] = 0.0f; fmB[i] = 0.0f; }
             if (!is_q6) {
                 for (int bl = 0; bl < nbk; ++bl) {
                     const int b = b0 + bl;
@@ -316,7 +321,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                     const uint32_t sb03 = hb.y & 0x3F3F3F3Fu, sb47 = (hb.w & 0x0F0F0F0Fu) | ((hb.y >> 2) & 0x30303030u);
                     const float dA = __half2float(__ushort_as_half(static_cast<uint16_t>(ha.x & 0xFFFF)));
                     const float dB = __half2float(__ushort_as_half(static_cast<uint16_t>(hb.x & 0xFFFF)));
-                    {   // min term, subtracted in the limb-0 column of each activation row: dmin * sum_sub m_sub * sum(x over sub)
+                    {   // min term of each (weight row, activation row): dmin * sum_sub m_sub * sum(x over sub)
                         const uint32_t ma03 = ha.z & 0x3F3F3F3Fu, ma47 = ((ha.w >> 4) & 0x0F0F0F0Fu) | ((ha.z >> 2) & 0x30303030u);
                         const uint32_t mb03 = hb.z & 0x3F3F3F3Fu, mb47 = ((hb.w >> 4) & 0x0F0F0F0Fu) | ((hb.z >> 2) & 0x30303030u);
                         const float dmA = __half2float(__ushort_as_half(static_cast<uint16_t>(ha.x >> 16)));
@@ -327,16 +332,18 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                             mAf[i] = dmA * static_cast<float>((ma03 >> (8 * i)) & 0xFFu); mAf[4 + i] = dmA * static_cast<float>((ma47 >> (8 * i)) & 0xFFu);
                             mBf[i] = dmB * static_cast<float>((mb03 >> (8 * i)) & 0xFFu); mBf[4 + i] = dmB * static_cast<float>((mb47 >> (8 * i)) & 0xFFu);
                         }
+                        // lane (g, t) owns the terms of weight rows g, g + 8 and activation rows t, t + 4, ...: every lane does
+                        // the same amount, nothing diverges; the sums join the limb-0 columns in the slab
 #pragma unroll
-                        for (int q = 0; q < CG; ++q)
-#pragma unroll
-                            for (int sl2 = 0; sl2 < 2; ++sl2)
-                                if (limb0[q][sl2]) {
-                                    const float* as = asum + mrow[q][sl2] * (K >> 5) + b * 8;
-                                    const float4 a0 = *reinterpret_cast<const float4*>(as), a1 = *reinterpret_cast<const float4*>(as + 4);
-                                    f[q][sl2] -= mAf[0] * a0.x + mAf[1] * a0.y + mAf[2] * a0.z + mAf[3] * a0.w + mAf[4] * a1.x + mAf[5] * a1.y + mAf[6] * a1.z + mAf[7] * a1.w;
-                                    f[q][2 + sl2] -= mBf[0] * a0.x + mBf[1] * a0.y + mBf[2] * a0.z + mBf[3] * a0.w + mBf[4] * a1.x + mBf[5] * a1.y + mBf[6] * a1.z + mBf[7] * a1.w;
-                                }
+                        for (int i = 0; i < MI; ++i) {
+                            const int mm = t + 4 * i;
+                            if (mm < M) {
+                                const float* as = asum + mm * (K >> 5) + b * 8;
+                                const float4 a0 = *reinterpret_cast<const float4*>(as), a1 = *reinterpret_cast<const float4*>(as + 4);
+                                fmA[i] -= mAf[0] * a0.x + mAf[1] * a0.y + mAf[2] * a0.z + mAf[3] * a0.w + mAf[4] * a1.x + mAf[5] * a1.y + mAf[6] * a1.z + mAf[7] * a1.w;
+                                fmB[i] -= mBf[0] * a0.x + mBf[1] * a0.y + mBf[2] * a0.z + mBf[3] * a0.w + mBf[4] * a1.x + mBf[5] * a1.y + mBf[6] * a1.z + mBf[7] * a1.w;
+                            }
+                        }
                     }
                     int lo[CG][4], hi[CG][4];
 #pragma unroll
@@ -382,26 +389,34 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                     const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(s3T + (bl * 16 + g) * 2)));
                     const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(s3T + (bl * 16 + g + 8) * 2)));
                     const uint32_t saw[4] = {sa.x, sa.y, sa.z, sa.w}, sbw[4] = {sb_.x, sb_.y, sb_.z, sb_.w};
-                    // quants are used unsigned (0..63): 32 * d * sum_run sc_run * sum(x over run) comes off in the limb-0 column of each row
+                    // quants are used unsigned (0..63): 32 * d * sum_run sc_run * sum(x over run) comes off each (weight row,
+                    // activation row); lane (g, t) owns rows g, g + 8 and activation rows t, t + 4, ... (see the Q4_K branch)
+                    {
+                        float scA[16], scB[16];
 #pragma unroll
-                    for (int q = 0; q < CG; ++q)
+                        for (int w4 = 0; w4 < 4; ++w4)
 #pragma unroll
-                        for (int sl2 = 0; sl2 < 2; ++sl2)
-                            if (limb0[q][sl2]) {
-                                const float* as = asum16 + mrow[q][sl2] * (K >> 4) + b * 16;
+                            for (int k = 0; k < 4; ++k) {
+                                scA[4 * w4 + k] = static_cast<float>(static_cast<int8_t>(saw[w4] >> (8 * k)));
+                                scB[4 * w4 + k] = static_cast<float>(static_cast<int8_t>(sbw[w4] >> (8 * k)));
+                            }
+#pragma unroll
+                        for (int i = 0; i < MI; ++i) {
+                            const int mm = t + 4 * i;
+                            if (mm < M) {
+                                const float* as = asum16 + mm * (K >> 4) + b * 16;
                                 float ca = 0.0f, cb = 0.0f;
 #pragma unroll
                                 for (int w4 = 0; w4 < 4; ++w4) {
                                     const float4 av = *reinterpret_cast<const float4*>(as + 4 * w4);
-                                    const uint32_t wa = saw[w4], wb = sbw[w4];
-                                    ca += static_cast<float>(static_cast<int8_t>(wa)) * av.x + static_cast<float>(static_cast<int8_t>(wa >> 8)) * av.y +
-                                          static_cast<float>(static_cast<int8_t>(wa >> 16)) * av.z + static_cast<float>(static_cast<int8_t>(wa >> 24)) * av.w;
-                                    cb += static_cast<float>(static_cast<int8_t>(wb)) * av.x + static_cast<float>(static_cast<int8_t>(wb >> 8)) * av.y +
-                                          static_cast<float>(static_cast<int8_t>(wb >> 16)) * av.z + static_cast<float>(static_cast<int8_t>(wb >> 24)) * av.w;
+                                    ca += scA[4 * w4] * av.x + scA[4 * w4 + 1] * av.y + scA[4 * w4 + 2] * av.z + scA[4 * w4 + 3] * av.w;
+                                    cb += scB[4 * w4] * av.x + scB[4 * w4 + 1] * av.y + scB[4 * w4 + 2] * av.z + scB[4 * w4 + 3] * av.w;
                                 }
-                                f[q][sl2] -= dA * 32.0f * ca;
-                                f[q][2 + sl2] -= dB * 32.0f * cb;
+                                fmA[i] -= dA * 32.0f * ca;
+                                fmB[i] -= dB * 32.0f * cb;
                             }
+                        }
+                    }
                     int c[CG][4];
 #pragma unroll
                     for (int q = 0; q < CG; ++q)
@@ -448,6 +463,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                 for (int i = 0; i < 4; ++i) {
                     if (NMAT == 1 || mat == 0) F[0][q][i] += f[q][i]; else F[NMAT - 1][q][i] += f[q][i];
                 }
+#pragma unroll
+            for (int i = 0; i < MI; ++i) {
+                if (NMAT == 1 || mat == 0) { Fm[0][0][i] += fmA[i]; Fm[0][1][i] += fmB[i]; }
+                else { Fm[NMAT - 1][0][i] += fmA[i]; Fm[NMAT - 1][1][i] += fmB[i]; }
+            }
             __syncwarp();
             issue_next();                               // the stage is free again
         }
@@ -463,6 +483,18 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_rows_kernel(const Row
                 }
             }
         }
+        __syncwarp();
+        // the min / offset terms join the limb-0 column (3 m) of their activation row: (row, m) pairs are unique per lane
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat)
+#pragma unroll
+            for (int i = 0; i < MI; ++i) {
+                const int mm = t + 4 * i;
+                if (mm < M) {
+                    my_slab[(static_cast<size_t>(mat) * 16 + g) * NC + 3 * mm] += Fm[mat][0][i];
+                    my_slab[(static_cast<size_t>(mat) * 16 + g + 8) * NC + 3 * mm] += Fm[mat][1][i];
+                }
+            }
         asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "r"(a.ws * 32) : "memory");
         if (member == 0) {
             // the team's first warp: (row r, activation row m) = sum over the team's slabs of columns 3m, 3m+1, 3m+2
