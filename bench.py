@@ -957,7 +957,7 @@ def main():
     ap.add_argument("--config3", action="store_true", help="Qwen2.5-1.5B shape, all Q8_0: 2048-token prefill and 128 decode tokens on one GPU")
     ap.add_argument("--q35-layers", type=int, default=40)
     ap.add_argument("--q35-prompt", type=int, default=128)
-    ap.add_argument("--no-extras", action="store_true", help="skip the extra figures of the default run (config 3 on one GPU; tensor / expert parallel figures and checks under torchrun)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra figures of the default run (the Qwen2.5-1.5B, Llama-3-8B and qwen35moe shapes on one GPU; tensor / expert parallel figures and checks under torchrun)")
     ap.add_argument("--micro", action="store_true", help="quantised-matmul microbenchmark instead of the decode benchmark")
     ap.add_argument("--types", default="Q4_0,Q8_0,Q4_K,Q6_K,IQ4_XS")
     ap.add_argument("--shapes", default="2048x2048,8192x2048,2048x8192,8960x1536")
