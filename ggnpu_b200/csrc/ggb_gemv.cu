@@ -658,6 +658,14 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         const int st = launch_gemv_tma(c, a, s);
         if (st != GGB_NOT_FOUND) return st;
     }
+    if (c->use_mma && a.M >= 3 && a.M <= 16 && a.w.layout == 0 && a.w.K % 256 == 0 && !a.n_cat &&
+        (a.w.type == T_Q8_0 || a.w.type == T_Q4_0 || a.w.type == T_IQ4_NL)) {
+        // 3..16 rows of a 32-block format on the int8 tensor cores, straight from the stream layout
+        if (ensure_ws(c, gemv_mma_stream_ws_floats(a), s) != GGB_OK) return c->last_status;
+        if (ensure_limbs(c, gemv_mma_rows_limbs_bytes(a.M, a.w.K), s) != GGB_OK) return c->last_status;
+        const int st = launch_gemv_mma_stream(c, a, c->d_ws, c->d_ws_floats, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
     if (c->use_tma && a.M >= 3 && a.M <= 16 && a.w.layout == 0 && a.w.K % 256 == 0 && !a.n_cat && a.w.type != T_Q8_0) {
         // 3..16 rows of a stream-layout matrix: the weights once per chunk of rows, exact int8-limb activations.
         // Measured at M = 16 against the general kernel below: IQ4_XS 31-116 us against 90-342, Q4_0 23-85 against 35-128;

@@ -631,6 +631,289 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
     return cuda_status(c, e, "gemv_mma_rows reduce");
 }
 
+// ---- stream-layout formats (Q8_0, Q4_0, IQ4_NL) on the tensor cores ------------------------------------------------
+// The weights stay in the stream layout ([row][32-block]: quants and fp16 scales in two streams).  A tile is 16 weight rows
+// x one 256-run of K, brought by one bulk copy per row and stream into rows PADDED by 16 bytes, so that ldmatrix reads eight
+// rows without a bank conflict; ldmatrix delivers exactly the int8 A fragment of mma.m16n8k32 (Q8_0: the 32 bytes of a
+// block = four 8 x 16-byte matrices; Q4_0 / IQ4_NL: the 16 bytes hold elements 0..15 in the low and 16..31 in the high
+// nibbles, which are the two K halves of the fragment).  Everything else is the K-quant kernel above: limb image of the
+// activations, column c = 3 m + p, slabs, K slices.  The block scale d is applied to the int32 sums per 32-block.
+enum : int { SF_Q80 = 0, SF_Q40 = 1, SF_IQ4NL = 2 };
+
+__device__ __forceinline__ uint32_t iq4_codes_u(uint32_t idx) {      // four codebook indices (one per byte) -> four int8 codes (src/quant/iq4_nl.cpp:16-18)
+    const uint32_t x = idx | (idx >> 4);
+    const uint32_t p = __byte_perm(x, 0u, 0x4420);
+    const uint32_t sel = p & 0x7777u;
+    const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel);
+    const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, sel);
+    return __byte_perm(lo, hi, 0x3210u | ((p & 0x8888u) >> 1));
+}
+
+template <int SF> struct StreamGeom {
+    static constexpr int QB = SF == SF_Q80 ? 32 : 16;      // quant bytes per 32-block
+    static constexpr int QROW = 8 * QB + 16;               // padded bytes of one row's 256-run in a stage
+    static constexpr int STAGE = 16 * QROW + 256;          // + 16 rows x 8 fp16 scales
+    static constexpr int TX = 16 * (8 * QB + 16);          // bytes a tile's copies deliver
+};
+
+template <int SF, int CG, int NMAT>
+__global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const RowsArgs a) {
+    using G = StreamGeom<SF>;
+    constexpr int NC = 8 * CG;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], x_bar;
+    __shared__ float inv_s[16];
+    const int nb = a.w.K >> 8, nb32 = a.w.K >> 5, M = a.M;        // 256-runs and 32-blocks per row
+    const int kb0 = blockIdx.y * a.kbs, nbs = min(a.kbs, nb - kb0);
+    const int K = a.kbs * 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tprg = NMAT * nbs;                        // tiles per row group: one per 256-run and matrix
+    const int plane_stride = K + 16;
+    uint8_t* ring = smem;
+    int8_t* xl = reinterpret_cast<int8_t*>(ring + static_cast<size_t>(kWarps) * a.P * G::STAGE);
+    float* xs = reinterpret_cast<float*>(xl + static_cast<size_t>(3 * M) * plane_stride);
+    float* slab = xs + ((M * (K >> 8) + 3) & ~3);
+
+    const int64_t g_begin = static_cast<int64_t>(blockIdx.x) * a.groups / gridDim.x;
+    const int n_rg = static_cast<int>(static_cast<int64_t>(blockIdx.x + 1) * a.groups / gridDim.x - g_begin);
+    const int n_teams = kWarps / a.ws;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWarps * a.P; ++s) mbar_init(&full_bar[s], 1);
+        mbar_init(&x_bar, kWarps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch();
+
+    const int team = warp / a.ws, member = warp % a.ws;
+    int rg_i = team, ti_i = member, st_i = 0;
+    // the whole warp issues a tile: lane r < 16 copies row r's quants, lane 16 + r its scales
+    auto issue_next = [&]() {
+        while (rg_i < n_rg && ti_i >= tprg) { rg_i += n_teams; ti_i = member; }
+        if (rg_i >= n_rg) return;
+        const int s = warp * a.P + st_i;
+        const int mat = ti_i >= nbs, bl = ti_i - mat * nbs;
+        uint8_t* dst = ring + static_cast<size_t>(s) * G::STAGE;
+        const PackedW& w = mat ? a.w2 : a.w;
+        const int r = lane & 15;
+        const int64_t blk = ((g_begin + rg_i) * 16 + r) * nb32 + static_cast<int64_t>(kb0 + bl) * 8;      // first 32-block of the row's run
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
+        if (lane == 0) mbar_expect_tx(&full_bar[s], G::TX);
+        __syncwarp();
+        if (lane < 16) bulk_g2s(dst + r * G::QROW, w.s[1] + blk * G::QB, 8 * G::QB, &full_bar[s]);
+        else bulk_g2s(dst + 16 * G::QROW + r * 16, w.s[0] + blk * 2, 16, &full_bar[s]);
+        ti_i += a.ws;
+        if (++st_i == a.P) st_i = 0;
+    };
+    for (int i = 0; i < a.P; ++i) issue_next();
+
+    const int g = lane >> 2, t = lane & 3;
+    const int ncol = 3 * M;
+    const int8_t* bplane[CG];
+    int mrow[CG][2];
+    float lw[CG][2];
+#pragma unroll
+    for (int q = 0; q < CG; ++q) {
+        bplane[q] = xl + static_cast<size_t>(min(8 * q + g, ncol - 1)) * plane_stride + 4 * t;
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+            const int col = 8 * q + 2 * t + sl;
+            const bool valid = col < ncol;
+            mrow[q][sl] = valid ? col / 3 : M - 1;
+            const int p = col % 3;
+            lw[q][sl] = valid ? (p == 0 ? 1.0f : (p == 1 ? 1.0f / 128.0f : 1.0f / 16384.0f)) : 0.0f;
+        }
+    }
+    pdl_wait();
+    bool ok = true;
+    {
+        const LimbImage L(M, a.w.K);
+        const int Kf = a.w.K, Ks = nbs * 256;
+        if (lane == 0) {
+            uint32_t bytes = 0;
+            for (int it = warp; it < 3 * M; it += kWarps) bytes += Ks;
+            mbar_expect_tx(&x_bar, bytes);
+            for (int it = warp; it < 3 * M; it += kWarps)
+                bulk_g2s(xl + static_cast<size_t>(it) * plane_stride, a.img + L.planes + (static_cast<size_t>(it) * Kf + kb0 * 256), Ks, &x_bar);
+        }
+        const float* gxs = reinterpret_cast<const float*>(a.img + L.xs);
+        for (int i = threadIdx.x; i < M * nbs; i += kWarps * 32) { const int m = i / nbs, b = i - m * nbs; xs[m * (K >> 8) + b] = gxs[m * nb + kb0 + b]; }
+        if (threadIdx.x < M) inv_s[threadIdx.x] = reinterpret_cast<const float*>(a.img + L.inv_s)[threadIdx.x];
+        ok = mbar_wait(&x_bar, 0, a.err, 3);
+    }
+    consumer_sync();
+
+    // ldmatrix row address of this lane inside a stage: matrix lane / 8 -> rows (0..7 | 8..15), K half (bytes 0..15 | 16..31)
+    const int lm_row = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int lm_off = lm_row * G::QROW + (SF == SF_Q80 ? 16 * (lane >> 4) : 0);
+
+    int st = 0;
+    uint32_t ph = 0;
+    float* my_slab = slab + static_cast<size_t>(warp) * NMAT * 16 * NC;
+    for (int rg = team; rg < n_rg; rg += n_teams) {
+        float F[NMAT][CG][4];
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat)
+#pragma unroll
+            for (int q = 0; q < CG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) F[mat][q][i] = 0.0f;
+        for (int ti = member; ti < tprg; ti += a.ws) {
+            const int s = warp * a.P + st;
+            if (ok) ok = mbar_wait(&full_bar[s], ph, a.err, 2);
+            if (++st == a.P) { st = 0; ph ^= 1; }
+            if (!ok) continue;
+            const int mat = ti >= nbs, b = ti - mat * nbs;           // b: 256-run inside the slice
+            const uint8_t* qsT = ring + static_cast<size_t>(s) * G::STAGE;
+            const uint4 dAv = *reinterpret_cast<const uint4*>(qsT + 16 * G::QROW + g * 16);            // the 8 block scales of rows g, g + 8
+            const uint4 dBv = *reinterpret_cast<const uint4*>(qsT + 16 * G::QROW + (g + 8) * 16);
+            const uint32_t dAw[4] = {dAv.x, dAv.y, dAv.z, dAv.w}, dBw[4] = {dBv.x, dBv.y, dBv.z, dBv.w};
+            float f[CG][4];
+#pragma unroll
+            for (int q = 0; q < CG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) f[q][i] = 0.0f;
+#pragma unroll
+            for (int kb = 0; kb < 8; ++kb) {
+                uint32_t a0, a1, a2, a3;
+                const uint32_t addr = smem_u32(qsT + lm_off + kb * G::QB);
+                if (SF == SF_Q80) {
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
+                } else {
+                    uint32_t w0, w1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(addr));
+                    if (SF == SF_Q40) {
+                        a0 = __vsub4(w0 & 0x0F0F0F0Fu, 0x08080808u); a1 = __vsub4(w1 & 0x0F0F0F0Fu, 0x08080808u);
+                        a2 = __vsub4((w0 >> 4) & 0x0F0F0F0Fu, 0x08080808u); a3 = __vsub4((w1 >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+                    } else {
+                        a0 = iq4_codes_u(w0 & 0x0F0F0F0Fu); a1 = iq4_codes_u(w1 & 0x0F0F0F0Fu);
+                        a2 = iq4_codes_u((w0 >> 4) & 0x0F0F0F0Fu); a3 = iq4_codes_u((w1 >> 4) & 0x0F0F0F0Fu);
+                    }
+                }
+                const float dA = __half2float(__ushort_as_half(static_cast<uint16_t>(dAw[kb >> 1] >> (16 * (kb & 1)))));
+                const float dB = __half2float(__ushort_as_half(static_cast<uint16_t>(dBw[kb >> 1] >> (16 * (kb & 1)))));
+#pragma unroll
+                for (int q = 0; q < CG; ++q) {
+                    const int8_t* bp = bplane[q] + (b * 8 + kb) * 32;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp), b1 = *reinterpret_cast<const uint32_t*>(bp + 16);
+                    int c[4];
+                    mma_s8(c, a0, a1, a2, a3, b0, b1);
+                    f[q][0] = fmaf(static_cast<float>(c[0]), dA, f[q][0]); f[q][1] = fmaf(static_cast<float>(c[1]), dA, f[q][1]);
+                    f[q][2] = fmaf(static_cast<float>(c[2]), dB, f[q][2]); f[q][3] = fmaf(static_cast<float>(c[3]), dB, f[q][3]);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < CG; ++q) {
+                // the activations' block scale (one per 256-run = per tile) and limb weight of the lane's two columns
+                const float x0 = xs[mrow[q][0] * (K >> 8) + b] * lw[q][0], x1 = xs[mrow[q][1] * (K >> 8) + b] * lw[q][1];
+                if (NMAT == 1 || mat == 0) { F[0][q][0] += f[q][0] * x0; F[0][q][1] += f[q][1] * x1; F[0][q][2] += f[q][2] * x0; F[0][q][3] += f[q][3] * x1; }
+                else { F[NMAT - 1][q][0] += f[q][0] * x0; F[NMAT - 1][q][1] += f[q][1] * x1; F[NMAT - 1][q][2] += f[q][2] * x0; F[NMAT - 1][q][3] += f[q][3] * x1; }
+            }
+            __syncwarp();
+            issue_next();
+        }
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat)
+#pragma unroll
+            for (int q = 0; q < CG; ++q) {
+                float* r0 = my_slab + (static_cast<size_t>(mat) * 16 + g) * NC + 8 * q + 2 * t;
+                *reinterpret_cast<float2*>(r0) = make_float2(F[mat][q][0], F[mat][q][1]);
+                *reinterpret_cast<float2*>(r0 + 8 * NC) = make_float2(F[mat][q][2], F[mat][q][3]);
+            }
+        asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "r"(a.ws * 32) : "memory");
+        if (member == 0) {
+            for (int idx = lane; idx < 16 * M; idx += 32) {
+                const int r = idx & 15, m = idx >> 4;
+                float v = 0.0f, v2 = 0.0f;
+                for (int j = 0; j < a.ws; ++j) {
+                    const float* sj = slab + static_cast<size_t>(team * a.ws + j) * NMAT * 16 * NC + static_cast<size_t>(r) * NC + 3 * m;
+                    v += sj[0] + sj[1] + sj[2];
+                    if (NMAT == 2) { const float* s2 = sj + 16 * NC; v2 += s2[0] + s2[1] + s2[2]; }
+                }
+                v *= inv_s[m]; v2 *= inv_s[m];
+                const int64_t row = (g_begin + rg) * 16 + r;
+                if (row < a.w.N && a.part) {
+                    const size_t plane = static_cast<size_t>(M) * a.w.N;
+                    float* pz = a.part + static_cast<size_t>(blockIdx.y) * NMAT * plane + static_cast<size_t>(m) * a.w.N + row;
+                    pz[0] = v;
+                    if (NMAT == 2) pz[plane] = v2;
+                } else if (row < a.w.N) {
+                    const size_t o = static_cast<size_t>(m) * a.ldc + row;
+                    if (NMAT == 2) v = (v / (1.0f + expf(-v))) * v2;
+                    else if (a.epi == EPI_ADD_BIAS && a.bias) v += __ldg(a.bias + row);
+                    else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
+                    a.y[o] = v;
+                }
+            }
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(2 + team), "r"(a.ws * 32) : "memory");
+    }
+}
+
+template <int SF, int CG>
+int launch_stream_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+    using G = StreamGeom<SF>;
+    constexpr int kThreads = kWarps * 32;
+    const int K = g.w.K, nb = K >> 8, mc = g.M;
+    const bool dual = g.epi == EPI_SWIGLU;
+    const int nmat = dual ? 2 : 1;
+    const int groups = static_cast<int>(g.w.N / 16);
+    // K slices: activation arrays (planes, scales, slabs) beside a ring of at least two stages per warp
+    auto fixed_bytes = [&](int kbs) {
+        return static_cast<size_t>(3 * mc) * (kbs * 256 + 16) + sizeof(float) * ((mc * kbs + 3) & ~3) + sizeof(float) * kWarps * nmat * 16 * 8 * CG + 64;
+    };
+    int S = 0;
+    for (int cand = 1; cand <= nb; ++cand) {
+        const int kbs = (nb + cand - 1) / cand;
+        if (fixed_bytes(kbs) + static_cast<size_t>(kWarps) * 2 * G::STAGE <= kRowsBudget) { S = cand; break; }
+    }
+    if (S < 1) return GGB_NOT_FOUND;
+    const int kbs = (nb + S - 1) / S, slices = (nb + kbs - 1) / kbs;
+    if (slices > 1 && static_cast<size_t>(slices) * nmat * mc * g.w.N > part_floats) return GGB_NOT_FOUND;
+    if (LimbImage(mc, K).bytes > c->d_limbs_bytes || nb * sizeof(float) > 48 * 1024) return GGB_NOT_FOUND;
+    const int Gx = std::min(std::max(1, c->sm_count / slices), groups);
+    const int gpc = (groups + Gx - 1) / Gx;
+    int ws = 1;
+    while (ws < kWarps && gpc * ws < kWarps) ws <<= 1;
+    const size_t fixed = fixed_bytes(kbs);
+    const int tiles_per_warp = ((gpc + kWarps / ws - 1) / (kWarps / ws)) * ((nmat * kbs + ws - 1) / ws);
+    int P = std::min(kMaxStages / kWarps, std::max(2, tiles_per_warp));
+    while (P > 2 && static_cast<size_t>(kWarps) * P * G::STAGE + fixed > kRowsBudget) --P;
+    const size_t smem = static_cast<size_t>(kWarps) * P * G::STAGE + fixed;
+    if (smem > kRowsBudget) return GGB_NOT_FOUND;
+    {
+        const int sp = limb_image_prepare(c, g, s);
+        if (sp != GGB_OK) return sp;
+    }
+    RowsArgs a{};
+    a.w = g.w; a.w2 = g.w2; a.x = g.x; a.y = g.y; a.bias = g.bias; a.resid = g.resid; a.gamma = g.gamma; a.eps = g.eps;
+    a.M = mc; a.lda = g.lda; a.ldc = g.ldc; a.epi = g.epi;
+    a.sb = 1; a.nmat = nmat; a.groups = groups; a.ws = ws; a.P = P; a.stage_bytes = G::STAGE;
+    a.kbs = kbs; a.part = slices > 1 ? d_part : nullptr;
+    a.img = static_cast<const uint8_t*>(c->d_limbs);
+    a.err = c->d_err;
+    void (*kern)(const RowsArgs) = dual ? gemv_mma_stream_kernel<SF, CG, 2> : gemv_mma_stream_kernel<SF, CG, 1>;
+    cudaError_t e = ensure_dynamic_smem(c, kern, smem);
+    if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma_stream attr");
+    e = launch_pdl(c, kern, dim3(static_cast<unsigned>(Gx), static_cast<unsigned>(slices)), dim3(kThreads), smem, s, a);
+    c->launches++;
+    if (e != cudaSuccess || slices == 1) return cuda_status(c, e, "gemv_mma_stream launch");
+    const size_t elems = static_cast<size_t>(mc) * g.w.N;
+    e = launch_pdl(c, rows_reduce_kernel, dim3(static_cast<unsigned>(std::min<size_t>((elems + 255) / 256, 148 * 8))), dim3(256), 0, s,
+                   static_cast<const float*>(d_part), slices, nmat, mc, g.w.N, g.epi, g.bias, g.resid, g.y, g.ldc);
+    c->launches++;
+    return cuda_status(c, e, "gemv_mma_stream reduce");
+}
+
+template <int SF>
+int launch_stream_f(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+    if (g.M <= 2) return launch_stream_t<SF, 1>(c, g, d_part, part_floats, s);
+    if (g.M <= 5) return launch_stream_t<SF, 2>(c, g, d_part, part_floats, s);
+    if (g.M <= 8) return launch_stream_t<SF, 3>(c, g, d_part, part_floats, s);
+    return launch_stream_t<SF, 6>(c, g, d_part, part_floats, s);
+}
+
 }  // namespace
 
 static int rows_cg(int M) { return M <= 5 ? 2 : (M <= 8 ? 3 : 6); }
@@ -667,6 +950,33 @@ int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t pa
 }
 
 size_t gemv_mma_rows_limbs_bytes(int M, int K) { return LimbImage(M, K).bytes; }
+
+static bool stream_covered(const GemvArgs& g) {
+    if (g.w.layout != 0 || (g.w.type != T_Q8_0 && g.w.type != T_Q4_0 && g.w.type != T_IQ4_NL)) return false;
+    if (g.M < 2 || g.M > 16 || g.w.K % 256 || g.w.N % 16 || !g.x || (reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return false;
+    const bool dual = g.epi == EPI_SWIGLU;
+    if (dual && (g.w2.layout != 0 || g.w2.type != g.w.type)) return false;
+    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return false;
+    return true;
+}
+
+// Workspace floats (K slices) of launch_gemv_mma_stream: an upper bound, one slice per 256-run.
+size_t gemv_mma_stream_ws_floats(const GemvArgs& g) {
+    if (!stream_covered(g)) return 0;
+    return static_cast<size_t>(g.w.K >> 8) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N > (size_t(64) << 20) ? 0
+           : static_cast<size_t>(g.w.K >> 8) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N;
+}
+
+// 2 <= M <= 16 rows of a Q8_0 / Q4_0 / IQ4_NL matrix (stream layout) on the int8 tensor cores, one pass over the weights.
+// c->d_limbs holds room for the activation image (the caller grew it).  GGB_NOT_FOUND: not covered.
+int launch_gemv_mma_stream(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
+    if (!stream_covered(g)) return GGB_NOT_FOUND;
+    switch (g.w.type) {
+    case T_Q8_0: return launch_stream_f<SF_Q80>(c, g, d_part, part_floats, s);
+    case T_Q4_0: return launch_stream_f<SF_Q40>(c, g, d_part, part_floats, s);
+    default: return launch_stream_f<SF_IQ4NL>(c, g, d_part, part_floats, s);
+    }
+}
 
 int limb_image_prepare(Context* c, const GemvArgs& g, cudaStream_t s) {
     const int M = g.M, K = g.w.K, nb = K >> 8;

@@ -140,6 +140,9 @@ int launch_gemv_mma(Context* c, const GemvArgs& a, cudaStream_t s);   // GGB_NOT
 int launch_gemv_mma_rows(Context* c, const GemvArgs& a, float* d_part, size_t part_floats, void* d_limbs, size_t limbs_bytes, cudaStream_t s);
 size_t gemv_mma_rows_ws_floats(const GemvArgs& a);
 size_t gemv_mma_rows_limbs_bytes(int M, int K);
+// the same for Q8_0 / Q4_0 / IQ4_NL in the stream layout (ldmatrix on padded rows), 2..16 rows
+int launch_gemv_mma_stream(Context* c, const GemvArgs& a, float* d_part, size_t part_floats, cudaStream_t s);
+size_t gemv_mma_stream_ws_floats(const GemvArgs& a);
 int launch_gemv_tma_rows(Context* c, const GemvArgs& a, cudaStream_t s);   // 2..16 rows, stream layout; needs c->d_limbs sized by the caller
 int check_device_error(Context* c);
 // ggb_gemm_tc.cu: prefill GEMM on tcgen05; GGB_NOT_FOUND: shape not covered
