@@ -659,7 +659,7 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
         if (st != GGB_NOT_FOUND) return st;
     }
     if (c->use_mma && a.M >= 3 && a.M <= 16 && a.w.layout == 0 && a.w.K % 256 == 0 && !a.n_cat &&
-        (a.w.type == T_Q8_0 || a.w.type == T_Q4_0 || a.w.type == T_IQ4_NL)) {
+        (a.w.type == T_Q8_0 || a.w.type == T_Q4_0 || a.w.type == T_IQ4_NL || a.w.type == T_IQ4_XS)) {
         // 3..16 rows of a 32-block format on the int8 tensor cores, straight from the stream layout
         if (ensure_ws(c, gemv_mma_stream_ws_floats(a), s) != GGB_OK) return c->last_status;
         if (ensure_limbs(c, gemv_mma_rows_limbs_bytes(a.M, a.w.K), s) != GGB_OK) return c->last_status;

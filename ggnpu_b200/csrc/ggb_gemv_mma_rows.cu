@@ -638,7 +638,9 @@ int launch_rows_t(Context* c, const GemvArgs& g, float* d_part, size_t part_floa
 // block = four 8 x 16-byte matrices; Q4_0 / IQ4_NL: the 16 bytes hold elements 0..15 in the low and 16..31 in the high
 // nibbles, which are the two K halves of the fragment).  Everything else is the K-quant kernel above: limb image of the
 // activations, column c = 3 m + p, slabs, K slices.  The block scale d is applied to the int32 sums per 32-block.
-enum : int { SF_Q80 = 0, SF_Q40 = 1, SF_IQ4NL = 2 };
+// IQ4_XS (256-blocks: an 8-byte header d | scales_h | scales_l[4], then eight 16-byte sub-blocks) runs the same path: the
+// scale of sub-block kb is d * (ls_kb - 32); a tile brings the aligned 16-byte pair of headers that holds its block's.
+enum : int { SF_Q80 = 0, SF_Q40 = 1, SF_IQ4NL = 2, SF_IQ4XS = 3 };
 
 __device__ __forceinline__ uint32_t iq4_codes_u(uint32_t idx) {      // four codebook indices (one per byte) -> four int8 codes (src/quant/iq4_nl.cpp:16-18)
     const uint32_t x = idx | (idx >> 4);
@@ -698,11 +700,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
         const PackedW& w = mat ? a.w2 : a.w;
         const int r = lane & 15;
         const int64_t blk = ((g_begin + rg_i) * 16 + r) * nb32 + static_cast<int64_t>(kb0 + bl) * 8;      // first 32-block of the row's run
+        // IQ4_XS: the row's 256-block headers are 8 bytes each; the aligned pair that contains this block's
+        const int64_t hdr = (((g_begin + rg_i) * 16 + r) * nb + ((kb0 + bl) & ~1)) * 8;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
         if (lane == 0) mbar_expect_tx(&full_bar[s], G::TX);
         __syncwarp();
         if (lane < 16) bulk_g2s(dst + r * G::QROW, w.s[1] + blk * G::QB, 8 * G::QB, &full_bar[s]);
-        else bulk_g2s(dst + 16 * G::QROW + r * 16, w.s[0] + blk * 2, 16, &full_bar[s]);
+        else bulk_g2s(dst + 16 * G::QROW + r * 16, w.s[0] + (SF == SF_IQ4XS ? hdr : blk * 2), 16, &full_bar[s]);
         ti_i += a.ws;
         if (++st_i == a.P) st_i = 0;
     };
@@ -769,6 +773,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
             const uint4 dAv = *reinterpret_cast<const uint4*>(qsT + 16 * G::QROW + g * 16);            // the 8 block scales of rows g, g + 8
             const uint4 dBv = *reinterpret_cast<const uint4*>(qsT + 16 * G::QROW + (g + 8) * 16);
             const uint32_t dAw[4] = {dAv.x, dAv.y, dAv.z, dAv.w}, dBw[4] = {dBv.x, dBv.y, dBv.z, dBv.w};
+            // IQ4_XS: this block's header is the first or second half of the pair
+            const int hsel = 2 * ((kb0 + b) & 1);
+            const uint32_t hAx = dAw[hsel], hAy = dAw[hsel + 1], hBx = dBw[hsel], hBy = dBw[hsel + 1];
+            const float dA0 = __half2float(__ushort_as_half(static_cast<uint16_t>(hAx & 0xFFFFu))), dB0 = __half2float(__ushort_as_half(static_cast<uint16_t>(hBx & 0xFFFFu)));
             float f[CG][4];
 #pragma unroll
             for (int q = 0; q < CG; ++q)
@@ -791,8 +799,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
                         a2 = iq4_codes_u((w0 >> 4) & 0x0F0F0F0Fu); a3 = iq4_codes_u((w1 >> 4) & 0x0F0F0F0Fu);
                     }
                 }
-                const float dA = __half2float(__ushort_as_half(static_cast<uint16_t>(dAw[kb >> 1] >> (16 * (kb & 1)))));
-                const float dB = __half2float(__ushort_as_half(static_cast<uint16_t>(dBw[kb >> 1] >> (16 * (kb & 1)))));
+                float dA, dB;
+                if (SF == SF_IQ4XS) {
+                    const int lsA = static_cast<int>(((hAy >> (4 * kb)) & 15u) | (((hAx >> (16 + 2 * kb)) & 3u) << 4));
+                    const int lsB = static_cast<int>(((hBy >> (4 * kb)) & 15u) | (((hBx >> (16 + 2 * kb)) & 3u) << 4));
+                    dA = dA0 * static_cast<float>(lsA - 32); dB = dB0 * static_cast<float>(lsB - 32);
+                } else {
+                    dA = __half2float(__ushort_as_half(static_cast<uint16_t>(dAw[kb >> 1] >> (16 * (kb & 1)))));
+                    dB = __half2float(__ushort_as_half(static_cast<uint16_t>(dBw[kb >> 1] >> (16 * (kb & 1)))));
+                }
 #pragma unroll
                 for (int q = 0; q < CG; ++q) {
                     const int8_t* bp = bplane[q] + (b * 8 + kb) * 32;
@@ -952,7 +967,8 @@ int launch_gemv_mma_rows(Context* c, const GemvArgs& g, float* d_part, size_t pa
 size_t gemv_mma_rows_limbs_bytes(int M, int K) { return LimbImage(M, K).bytes; }
 
 static bool stream_covered(const GemvArgs& g) {
-    if (g.w.layout != 0 || (g.w.type != T_Q8_0 && g.w.type != T_Q4_0 && g.w.type != T_IQ4_NL)) return false;
+    if (g.w.layout != 0 || (g.w.type != T_Q8_0 && g.w.type != T_Q4_0 && g.w.type != T_IQ4_NL && g.w.type != T_IQ4_XS)) return false;
+    if (g.w.type == T_IQ4_XS && (g.w.K % 512)) return false;       // block headers are fetched as aligned 16-byte pairs
     if (g.M < 2 || g.M > 16 || g.w.K % 256 || g.w.N % 16 || !g.x || (reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return false;
     const bool dual = g.epi == EPI_SWIGLU;
     if (dual && (g.w2.layout != 0 || g.w2.type != g.w.type)) return false;
@@ -967,13 +983,14 @@ size_t gemv_mma_stream_ws_floats(const GemvArgs& g) {
            : static_cast<size_t>(g.w.K >> 8) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N;
 }
 
-// 2 <= M <= 16 rows of a Q8_0 / Q4_0 / IQ4_NL matrix (stream layout) on the int8 tensor cores, one pass over the weights.
+// 2 <= M <= 16 rows of a Q8_0 / Q4_0 / IQ4_NL / IQ4_XS matrix (stream layout) on the int8 tensor cores, one pass over the weights.
 // c->d_limbs holds room for the activation image (the caller grew it).  GGB_NOT_FOUND: not covered.
 int launch_gemv_mma_stream(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
     if (!stream_covered(g)) return GGB_NOT_FOUND;
     switch (g.w.type) {
     case T_Q8_0: return launch_stream_f<SF_Q80>(c, g, d_part, part_floats, s);
     case T_Q4_0: return launch_stream_f<SF_Q40>(c, g, d_part, part_floats, s);
+    case T_IQ4_XS: return launch_stream_f<SF_IQ4XS>(c, g, d_part, part_floats, s);
     default: return launch_stream_f<SF_IQ4NL>(c, g, d_part, part_floats, s);
     }
 }

@@ -146,13 +146,15 @@ def test_m1_k_slightly_over_one_unit_per_lane(backend, oracle, t, K):
     check(backend, oracle, t, 264, K, 5, seed=K + 1, sample_rows=40)
 
 
-@pytest.mark.parametrize("t", [S.Q8_0, S.Q4_0, S.IQ4_NL], ids=lambda t: S.TYPE_NAMES[t])
+@pytest.mark.parametrize("t", [S.Q8_0, S.Q4_0, S.IQ4_NL, S.IQ4_XS], ids=lambda t: S.TYPE_NAMES[t])
 @pytest.mark.parametrize("M", [3, 5, 8, 11, 16])
 def test_stream_formats_on_tensor_cores(backend, oracle, t, M):
-    """Q8_0 / Q4_0 / IQ4_NL at 3..16 rows: int8 MMAs fed by ldmatrix from the stream layout (padded rows in shared memory).
-    Few row groups (teams of warps share one), many row groups, K of one 256-run, K cut into slices (8192 at 16 rows)."""
+    """Q8_0 / Q4_0 / IQ4_NL / IQ4_XS at 3..16 rows: int8 MMAs fed by ldmatrix from the stream layout (padded rows in shared
+    memory).  Few row groups (teams of warps share one), many row groups, K of one 256-run (IQ4_XS then takes the general
+    path: its headers are fetched in pairs), K cut into slices (8192 at 16 rows)."""
     check(backend, oracle, t, 64, 1024, M, seed=M)
     check(backend, oracle, t, 4096, 256, M, seed=M + 1, sample_rows=40)
+    check(backend, oracle, t, 256, 1536, M, seed=M + 4, sample_rows=40)
     check(backend, oracle, t, 1024, 2048, M, seed=M + 2, sample_rows=40)
     check(backend, oracle, t, 512, 8192, M, seed=M + 3, sample_rows=40)
 
