@@ -15,6 +15,8 @@
 //   * products are accumulated in fp32 on integer quant values, the block scales are applied per
 //     sub-block (d*sc*sum(x*q) - dmin*m*sum(x)), which differs from dequantise-then-dot only by
 //     fp32 summation order.
+#include <stdlib.h>
+
 #include "ggb_internal.h"
 
 namespace ggb {
@@ -654,6 +656,15 @@ int launch_gemv(Context* c, const GemvArgs& a, cudaStream_t s) {
     }
     if (a.attn_partial || a.sel || a.xscale)
         return set_status(c, GGB_INVALID_PARAM, "gemv: attention-merge input, routed experts and scaled activations need the tensor-core kernel (Q4_K / Q6_K)");
+    static const bool stream_mma_m1 = getenv("GGB_NO_STREAM_MMA") == nullptr;
+    if (c->use_mma && stream_mma_m1 && a.M <= 2 && a.w.layout == 0 && a.w.K % 256 == 0 && (a.w.type == T_Q8_0 || a.w.type == T_Q4_0)) {
+        // One or two rows of Q8_0 / Q4_0 on the int8 tensor cores (the activations are converted in the kernel's prologue).
+        // Against the dp4a kernel below at M = 1: Q4_0 5.7-8.6 us against 5.8-9.0, Q8_0 6.3-10.4 against 5.9-10.3 per matrix
+        // but 1.50 against 1.60 ms for the Qwen2.5-1.5B-shape decode step; the IQ4 formats (codebook look-ups per fragment)
+        // are slower here (12.7 against 8.6 us) and stay on the dp4a kernel.
+        const int st = launch_gemv_mma_stream(c, a, c->d_ws, c->d_ws_floats, s);
+        if (st != GGB_NOT_FOUND) return st;
+    }
     if (c->use_tma && a.M == 1) {
         const int st = launch_gemv_tma(c, a, s);
         if (st != GGB_NOT_FOUND) return st;

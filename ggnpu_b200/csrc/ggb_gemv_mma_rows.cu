@@ -167,6 +167,14 @@ struct RowsArgs {
     int kbs;              // 256-blocks of K per slice (grid.y slices); nb when K is not cut
     float* part;          // K cut into slices: partial sums [slice][matrix][m][N], epilogue in rows_reduce_kernel; else nullptr
     int* err;
+    // stream kernel only: up to two more matrices stacked along N behind w (q | k | v of one layer): they share x, K and the
+    // format; row groups from cat_g0[i] on belong to matrix i + 1, which has its own streams, output, bias and row count
+    int ncat;
+    int cat_g0[2];
+    PackedW cat_w[2];
+    float* cat_y[2];
+    const float* cat_bias[2];
+    int cat_ldc[2];
 };
 
 // dynamic shared memory: [ring: 8 * P * stage_bytes][limb planes: 3 M (K + 16)][asum: M K/32][asum16: M K/16][xs: M K/256]
@@ -658,13 +666,16 @@ template <int SF> struct StreamGeom {
     static constexpr int TX = 16 * (8 * QB + 16);          // bytes a tile's copies deliver
 };
 
-template <int SF, int CG, int NMAT>
+// INLINE_X (one or two rows, K not cut): the CTA converts the activations itself in its prologue instead of copying the
+// image -- a decode step cannot afford a second launch per matrix.
+template <int SF, int CG, int NMAT, bool INLINE_X>
 __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const RowsArgs a) {
     using G = StreamGeom<SF>;
     constexpr int NC = 8 * CG;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], x_bar;
     __shared__ float inv_s[16];
+    __shared__ float ssb[2][64];                        // INLINE_X: sums of squares per (row, 256-run)
     const int nb = a.w.K >> 8, nb32 = a.w.K >> 5, M = a.M;        // 256-runs and 32-blocks per row
     const int kb0 = blockIdx.y * a.kbs, nbs = min(a.kbs, nb - kb0);
     const int K = a.kbs * 256;
@@ -690,6 +701,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
 
     const int team = warp / a.ws, member = warp % a.ws;
     int rg_i = team, ti_i = member, st_i = 0;
+    // stacked matrices: which matrix a row group of the stacked numbering belongs to, and its first group
+    auto cat_of = [&](int64_t gi, int& first) -> int {
+        int j = 0; first = 0;
+        if (a.ncat > 0 && gi >= a.cat_g0[0]) { j = 1; first = a.cat_g0[0]; }
+        if (a.ncat > 1 && gi >= a.cat_g0[1]) { j = 2; first = a.cat_g0[1]; }
+        return j;
+    };
     // the whole warp issues a tile: lane r < 16 copies row r's quants, lane 16 + r its scales
     auto issue_next = [&]() {
         while (rg_i < n_rg && ti_i >= tprg) { rg_i += n_teams; ti_i = member; }
@@ -697,11 +715,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
         const int s = warp * a.P + st_i;
         const int mat = ti_i >= nbs, bl = ti_i - mat * nbs;
         uint8_t* dst = ring + static_cast<size_t>(s) * G::STAGE;
-        const PackedW& w = mat ? a.w2 : a.w;
+        int gfirst;
+        const int cj = cat_of(g_begin + rg_i, gfirst);
+        const PackedW& w = mat ? a.w2 : (cj == 0 ? a.w : a.cat_w[cj - 1]);
         const int r = lane & 15;
-        const int64_t blk = ((g_begin + rg_i) * 16 + r) * nb32 + static_cast<int64_t>(kb0 + bl) * 8;      // first 32-block of the row's run
+        const int64_t lrow = (g_begin + rg_i - gfirst) * 16 + r;          // row inside its matrix
+        const int64_t blk = lrow * nb32 + static_cast<int64_t>(kb0 + bl) * 8;      // first 32-block of the row's run
         // IQ4_XS: the row's 256-block headers are 8 bytes each; the aligned pair that contains this block's
-        const int64_t hdr = (((g_begin + rg_i) * 16 + r) * nb + ((kb0 + bl) & ~1)) * 8;
+        const int64_t hdr = (lrow * nb + ((kb0 + bl) & ~1)) * 8;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was last read through the generic proxy
         if (lane == 0) mbar_expect_tx(&full_bar[s], G::TX);
         __syncwarp();
@@ -731,7 +752,55 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
     }
     pdl_wait();
     bool ok = true;
-    {
+    if (INLINE_X) {
+        // one or two rows, the whole K: limbs of x * gamma and block scales straight into shared memory (as rows_prep_kernel)
+        for (int m = 0; m < M; ++m)
+            for (int b = warp; b < nb; b += kWarps) {
+                const int k0 = b * 256 + lane * 8;
+                const float* xr = a.x + static_cast<size_t>(m) * a.lda + k0;
+                const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
+                float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                if (a.gamma) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+                    ss = wsum(ss);
+                    if (lane == 0) ssb[m][b] = ss;
+                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4));
+                    v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w; v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+                }
+                float am = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+                const float rs = am > 0.0f ? 127.0f / am : 0.0f;
+                uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float kMagic = 12582912.0f;
+                    const float r = fminf(fmaxf(v[i] * rs, -127.0f), 127.0f);
+                    const float t1 = r + kMagic;
+                    const float r2 = (r - (t1 - kMagic)) * 128.0f;
+                    const float t2 = r2 + kMagic;
+                    const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
+                    w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
+                    w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
+                    w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
+                }
+                int8_t* pl = xl + static_cast<size_t>(3 * m) * plane_stride + k0;
+                *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
+                *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
+                *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
+                if (lane == 0) xs[m * (K >> 8) + b] = am / 127.0f;
+            }
+        consumer_sync();
+        if (threadIdx.x < M) {
+            float tot = 0.0f;
+            if (a.gamma) for (int b = 0; b < nb; ++b) tot += ssb[threadIdx.x][b];
+            inv_s[threadIdx.x] = a.gamma ? 1.0f / sqrtf(tot / static_cast<float>(a.w.K) + a.eps) : 1.0f;
+        }
+    } else {
         const LimbImage L(M, a.w.K);
         const int Kf = a.w.K, Ks = nbs * 256;
         if (lane == 0) {
@@ -847,18 +916,24 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
                     if (NMAT == 2) { const float* s2 = sj + 16 * NC; v2 += s2[0] + s2[1] + s2[2]; }
                 }
                 v *= inv_s[m]; v2 *= inv_s[m];
-                const int64_t row = (g_begin + rg) * 16 + r;
-                if (row < a.w.N && a.part) {
+                int gfirst;
+                const int cj = cat_of(g_begin + rg, gfirst);
+                const int64_t row = (g_begin + rg - gfirst) * 16 + r;        // row inside its matrix
+                const int64_t Nj = cj == 0 ? a.w.N : a.cat_w[cj - 1].N;
+                float* yj = cj == 0 ? a.y : a.cat_y[cj - 1];
+                const float* bj = cj == 0 ? a.bias : a.cat_bias[cj - 1];
+                const int ldj = cj == 0 ? a.ldc : a.cat_ldc[cj - 1];
+                if (row < Nj && a.part) {
                     const size_t plane = static_cast<size_t>(M) * a.w.N;
                     float* pz = a.part + static_cast<size_t>(blockIdx.y) * NMAT * plane + static_cast<size_t>(m) * a.w.N + row;
                     pz[0] = v;
                     if (NMAT == 2) pz[plane] = v2;
-                } else if (row < a.w.N) {
-                    const size_t o = static_cast<size_t>(m) * a.ldc + row;
+                } else if (row < Nj) {
+                    const size_t o = static_cast<size_t>(m) * ldj + row;
                     if (NMAT == 2) v = (v / (1.0f + expf(-v))) * v2;
-                    else if (a.epi == EPI_ADD_BIAS && a.bias) v += __ldg(a.bias + row);
+                    else if (a.epi == EPI_ADD_BIAS && bj) v += __ldg(bj + row);
                     else if (a.epi == EPI_RESIDUAL) v += a.resid[o];
-                    a.y[o] = v;
+                    yj[o] = v;
                 }
             }
         }
@@ -873,7 +948,10 @@ int launch_stream_t(Context* c, const GemvArgs& g, float* d_part, size_t part_fl
     const int K = g.w.K, nb = K >> 8, mc = g.M;
     const bool dual = g.epi == EPI_SWIGLU;
     const int nmat = dual ? 2 : 1;
-    const int groups = static_cast<int>(g.w.N / 16);
+    int groups = static_cast<int>(g.w.N / 16);
+    int cat_g0[2] = {0, 0};
+    for (int i = 0; i < g.n_cat; ++i) { cat_g0[i] = groups; groups += static_cast<int>(g.cat_w[i].N / 16); }
+    const bool inline_x = mc <= 2;                      // decode steps: no second launch for the activations
     // K slices: activation arrays (planes, scales, slabs) beside a ring of at least two stages per warp
     auto fixed_bytes = [&](int kbs) {
         return static_cast<size_t>(3 * mc) * (kbs * 256 + 16) + sizeof(float) * ((mc * kbs + 3) & ~3) + sizeof(float) * kWarps * nmat * 16 * 8 * CG + 64;
@@ -885,8 +963,10 @@ int launch_stream_t(Context* c, const GemvArgs& g, float* d_part, size_t part_fl
     }
     if (S < 1) return GGB_NOT_FOUND;
     const int kbs = (nb + S - 1) / S, slices = (nb + kbs - 1) / kbs;
+    if (slices > 1 && (g.n_cat || inline_x)) return GGB_NOT_FOUND;
     if (slices > 1 && static_cast<size_t>(slices) * nmat * mc * g.w.N > part_floats) return GGB_NOT_FOUND;
-    if (LimbImage(mc, K).bytes > c->d_limbs_bytes || nb * sizeof(float) > 48 * 1024) return GGB_NOT_FOUND;
+    if (inline_x && nb > 64) return GGB_NOT_FOUND;
+    if (!inline_x && (LimbImage(mc, K).bytes > c->d_limbs_bytes || nb * sizeof(float) > 48 * 1024)) return GGB_NOT_FOUND;
     const int Gx = std::min(std::max(1, c->sm_count / slices), groups);
     const int gpc = (groups + Gx - 1) / Gx;
     int ws = 1;
@@ -897,7 +977,7 @@ int launch_stream_t(Context* c, const GemvArgs& g, float* d_part, size_t part_fl
     while (P > 2 && static_cast<size_t>(kWarps) * P * G::STAGE + fixed > kRowsBudget) --P;
     const size_t smem = static_cast<size_t>(kWarps) * P * G::STAGE + fixed;
     if (smem > kRowsBudget) return GGB_NOT_FOUND;
-    {
+    if (!inline_x) {
         const int sp = limb_image_prepare(c, g, s);
         if (sp != GGB_OK) return sp;
     }
@@ -908,7 +988,11 @@ int launch_stream_t(Context* c, const GemvArgs& g, float* d_part, size_t part_fl
     a.kbs = kbs; a.part = slices > 1 ? d_part : nullptr;
     a.img = static_cast<const uint8_t*>(c->d_limbs);
     a.err = c->d_err;
-    void (*kern)(const RowsArgs) = dual ? gemv_mma_stream_kernel<SF, CG, 2> : gemv_mma_stream_kernel<SF, CG, 1>;
+    a.ncat = g.n_cat;
+    for (int i = 0; i < g.n_cat; ++i) { a.cat_g0[i] = cat_g0[i]; a.cat_w[i] = g.cat_w[i]; a.cat_y[i] = g.cat_y[i]; a.cat_bias[i] = g.cat_bias[i]; a.cat_ldc[i] = g.cat_ldc[i]; }
+    void (*kern)(const RowsArgs);
+    if constexpr (CG == 1) kern = dual ? gemv_mma_stream_kernel<SF, 1, 2, true> : gemv_mma_stream_kernel<SF, 1, 1, true>;
+    else kern = dual ? gemv_mma_stream_kernel<SF, CG, 2, false> : gemv_mma_stream_kernel<SF, CG, 1, false>;
     cudaError_t e = ensure_dynamic_smem(c, kern, smem);
     if (e != cudaSuccess) return cuda_status(c, e, "gemv_mma_stream attr");
     e = launch_pdl(c, kern, dim3(static_cast<unsigned>(Gx), static_cast<unsigned>(slices)), dim3(kThreads), smem, s, a);
@@ -969,10 +1053,13 @@ size_t gemv_mma_rows_limbs_bytes(int M, int K) { return LimbImage(M, K).bytes; }
 static bool stream_covered(const GemvArgs& g) {
     if (g.w.layout != 0 || (g.w.type != T_Q8_0 && g.w.type != T_Q4_0 && g.w.type != T_IQ4_NL && g.w.type != T_IQ4_XS)) return false;
     if (g.w.type == T_IQ4_XS && (g.w.K % 512)) return false;       // block headers are fetched as aligned 16-byte pairs
-    if (g.M < 2 || g.M > 16 || g.w.K % 256 || g.w.N % 16 || !g.x || (reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return false;
+    if (g.M < 1 || g.M > 16 || g.w.K % 256 || g.w.N % 16 || !g.x || (reinterpret_cast<uintptr_t>(g.x) & 15) || (g.lda & 3)) return false;
     const bool dual = g.epi == EPI_SWIGLU;
     if (dual && (g.w2.layout != 0 || g.w2.type != g.w.type)) return false;
-    if (g.n_cat || g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return false;
+    if (g.attn_partial || g.sel || g.xscale || g.x_img || g.y_img) return false;
+    if (g.n_cat && (dual || g.n_cat > 2 || g.M > 2 || (g.epi != EPI_STORE && g.epi != EPI_ADD_BIAS))) return false;
+    for (int i = 0; i < g.n_cat; ++i)
+        if (g.cat_w[i].type != g.w.type || g.cat_w[i].K != g.w.K || g.cat_w[i].layout != 0 || g.cat_w[i].N % 16 || !g.cat_y[i]) return false;
     return true;
 }
 
@@ -983,7 +1070,7 @@ size_t gemv_mma_stream_ws_floats(const GemvArgs& g) {
            : static_cast<size_t>(g.w.K >> 8) * (g.epi == EPI_SWIGLU ? 2 : 1) * g.M * g.w.N;
 }
 
-// 2 <= M <= 16 rows of a Q8_0 / Q4_0 / IQ4_NL / IQ4_XS matrix (stream layout) on the int8 tensor cores, one pass over the weights.
+// 1 <= M <= 16 rows of a Q8_0 / Q4_0 / IQ4_NL / IQ4_XS matrix (stream layout; at M <= 2 also q | k | v stacked) on the int8 tensor cores, one pass over the weights.
 // c->d_limbs holds room for the activation image (the caller grew it).  GGB_NOT_FOUND: not covered.
 int launch_gemv_mma_stream(Context* c, const GemvArgs& g, float* d_part, size_t part_floats, cudaStream_t s) {
     if (!stream_covered(g)) return GGB_NOT_FOUND;
