@@ -56,7 +56,9 @@ static int d2h_sync(Context* c, void* h, const void* d, size_t n) {
 }
 
 cudaError_t ensure_dynamic_smem(Context* c, const void* func, size_t smem) {
-    if (smem <= 48 * 1024) return cudaSuccess;
+    // 48 KB is the limit without the opt-in for static + dynamic shared memory together: kernels here hold up to a few KB
+    // of static arrays (barriers, small tables), so the opt-in is taken from 40 KB of dynamic memory on
+    if (smem <= 40 * 1024) return cudaSuccess;
     static std::mutex mu;
     static std::map<std::pair<int, const void*>, size_t> granted;
     std::lock_guard<std::mutex> lk(mu);

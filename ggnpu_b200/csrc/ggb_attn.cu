@@ -218,7 +218,11 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     if (a.partial_tok_cap > 0 && n_tok > a.partial_tok_cap)
         return set_status(c, GGB_INVALID_PARAM, "attention: prompt chunk larger than the split scratch and not covered by the tensor-core kernel");
     if (a.merge_ticket && a.n_splits > 128) return set_status(c, GGB_INVALID_PARAM, "attention: more than 128 context splits");
-    dim3 grid(a.n_kv, a.n_splits, n_tok);
+    // one or two KV heads: 2 x splits CTAs leave most SMs idle, so the query heads of a KV head are dealt to two CTAs
+    // (each re-reads the K / V chunk, which is small next to the idle SMs)
+    if (a.head_split <= 1 && !a.merge_ticket && a.n_kv <= 2 && G >= 4 && G % 2 == 0 && static_cast<int64_t>(a.n_kv) * a.n_splits * n_tok < c->sm_count) a.head_split = 2;
+    if (a.head_split > 1 && (a.merge_ticket || G % a.head_split)) a.head_split = 1;
+    dim3 grid(a.n_kv * std::max(a.head_split, 1), a.n_splits, n_tok);
     cudaError_t e = cudaSuccess;
     size_t smem = 0;
 #define GGB_ATTN_CASE(HD)                                                                                              \

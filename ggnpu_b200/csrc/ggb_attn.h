@@ -50,6 +50,7 @@ struct AttnPagedArgs {
     // optional: one counter per (token, KV head), zero before the first launch.  The CTA of a (token, KV head) that
     // finishes last merges the splits of its query heads itself and writes `out`, so neither the merge kernel nor a
     // merging consumer is needed (the counter is back at zero when the launch ends)
+    int head_split;           // > 1: the query heads of a KV head are dealt to this many CTAs (grid.x = n_kv * head_split); no merge_ticket then
     int* merge_ticket;
     int merge_min_splits;     // with merge_ticket: merge in the kernel only when at least this many splits are visible (0: always)
     const float* k_new;

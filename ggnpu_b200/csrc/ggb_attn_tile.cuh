@@ -30,21 +30,26 @@ constexpr size_t attn_tile_smem(int HD) {
 // once, then scores, an online softmax and P*V run out of shared memory in fp32.  With a.fuse (single-token decode)
 // the body also rotates q and the new key, and the split that contains pos stores the new key and value.
 template <int HD, bool COHERENT, class Sync>
-__device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int h, const int split, const int t, const int tid,
+__device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int hx, const int split, const int t, const int tid,
                                                uint32_t* sm_u, Sync sync) {
     constexpr int KW = HD / 2;           // 32-bit words (bf16 pairs) per K or V row
     constexpr int KS = KW + 1;           // padded K row stride: thread-per-key reads hit distinct banks
     constexpr int TK = 64;               // keys per chunk
     constexpr int NP = (8 * KW + 127) / 128;   // (head, dim pair) items per thread in P*V
     const int lane = tid & 31, warp = tid >> 5;
-    const int G = a.n_head / a.n_kv;
+    // hx = KV head * head_split + part: with head_split > 1 the query heads that share a KV head are dealt to several CTAs
+    // (models with one or two KV heads would otherwise fill a fraction of the SMs)
+    const int hs = a.head_split > 1 ? a.head_split : 1;
+    const int h = hx / hs, hpart = hx - h * hs;
+    const int G = (a.n_head / a.n_kv) / hs;                                   // query heads of this CTA
+    const size_t head0 = static_cast<size_t>(h) * (a.n_head / a.n_kv) + static_cast<size_t>(hpart) * G;      // the first of them
     // Fused step: the values the rotation below needs (the G query heads and the new key) do not depend
     // on the position, so their loads are issued before the position is looked at; the position's own
     // round trip to memory then overlaps theirs instead of preceding it.
     constexpr int NQ = HD <= 128 ? (9 * (HD / 2) + 127) / 128 : 0;       // rotation items per thread, G <= 8
     float qpre0[NQ > 0 ? NQ : 1], qpre1[NQ > 0 ? NQ : 1];
     if (NQ > 0 && a.fuse) {
-        const float* qb = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
+        const float* qb = a.q + (static_cast<size_t>(t) * a.n_head + head0) * HD;
 #pragma unroll
         for (int u = 0; u < NQ; ++u) {
             const int idx = tid + 128 * u, hh = idx / (HD / 2), i = idx - hh * (HD / 2);
@@ -72,7 +77,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     float* hinv = corr + 8;                                // [9] per-head norm factors (q heads, then k)
     __nv_bfloat16* fresh = reinterpret_cast<__nv_bfloat16*>(hinv + 12);   // [2][HD] new key and value
     const float scale = 1.0f / sqrtf(static_cast<float>(HD));
-    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * HD;
+    const float* q = a.q + (static_cast<size_t>(t) * a.n_head + head0) * HD;
     const bool has_new = a.fuse && pos >= j_begin && pos < j_begin + keys_per_split;
     const int half = HD >> 1;
 
@@ -141,7 +146,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
         }
         if (has_new) for (int i = tid; i < HD; i += 128) fresh[HD + i] = __float2bfloat16_rn(ldx<COHERENT>(a.v_new + (static_cast<size_t>(t) * a.n_kv + h) * HD + i));
         sync();
-        if (has_new) {     // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
+        if (has_new && hpart == 0) {     // K is cached after RoPE, V raw (src/cli/main.cpp:3354-3356)
             const int page = bt[pos / a.page], slot = pos % a.page;
             const size_t o = ((static_cast<size_t>(page) * a.n_kv + h) * a.page + slot) * HD;
             for (int i = tid; i < HD; i += 128) { a.k_cache_w[o + i] = fresh[i]; a.v_cache_w[o + i] = fresh[HD + i]; }
@@ -257,7 +262,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             }
         }
     }
-    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits + split) * (HD + 2);
+    float* part = a.partial + ((static_cast<size_t>(t) * a.n_head + head0) * a.n_splits + split) * (HD + 2);
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
         const int idx = tid + 128 * p;
@@ -287,7 +292,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     sync();
     if (!flag[0]) return;
     __threadfence();
-    const float* base = a.partial + (static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G) * a.n_splits * (HD + 2);
+    const float* base = a.partial + (static_cast<size_t>(t) * a.n_head + head0) * a.n_splits * (HD + 2);
     float* wts = reinterpret_cast<float*>(Kt);                      // [G][128]: exp(max_s - max) per head and split (n_splits <= 128;
     float* lsm = wts + 8 * 128;                                     // [G][128]: the splits' sums       the K tile is free now)
     for (int i = tid; i < G * n_active; i += 128) {                 // every split's (max, sum) by its own thread: independent loads
@@ -322,7 +327,7 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
             for (int u = 0; u < 8; ++u) o += pv[u] * wts[gq * 128 + s2 + u];
         }
         for (; s2 < n_active; ++s2) o += __ldcg(pg + static_cast<size_t>(s2) * (HD + 2)) * wts[gq * 128 + s2];
-        a.out[(static_cast<size_t>(t) * a.n_head + static_cast<size_t>(h) * G + gq) * HD + d] = o * mrun[gq];
+        a.out[(static_cast<size_t>(t) * a.n_head + head0 + gq) * HD + d] = o * mrun[gq];
     }
 }
 
