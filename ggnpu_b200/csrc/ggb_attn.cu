@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnPagedArgs a) {
     const int pos = a.seq_pos ? a.seq_pos[t] : (a.d_pos ? a.d_pos[0] : a.pos0) + t;
     const int keys_per_split = a.pages_per_split * a.page;
     const int n_active = min(a.n_splits, pos / keys_per_split + 1);      // at most 64 (attn_split_geometry)
+    if (n_active < a.merge_min_splits) return;         // few splits: the consumer merges them in its prologue
     const size_t stride = static_cast<size_t>(hd) + 2;
     const float* part = a.partial + (static_cast<size_t>(t) * a.n_head + head) * a.n_splits * stride;
     if (tid < n_active) { m_s[tid] = part[tid * stride]; l_s[tid] = part[tid * stride + 1]; }

@@ -52,7 +52,7 @@ struct AttnPagedArgs {
     // merging consumer is needed (the counter is back at zero when the launch ends)
     int head_split;           // > 1: the query heads of a KV head are dealt to this many CTAs (grid.x = n_kv * head_split); no merge_ticket then
     int* merge_ticket;
-    int merge_min_splits;     // with merge_ticket: merge in the kernel only when at least this many splits are visible (0: always)
+    int merge_min_splits;     // merge (in the kernel with merge_ticket, else in the merge kernel) only when at least this many splits are visible (0: always)
     const float* k_new;
     const float* v_new;
     __nv_bfloat16* k_cache_w;

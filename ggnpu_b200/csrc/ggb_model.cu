@@ -201,22 +201,24 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         }
         aa.q = m->q; aa.k_cache = ka.k_cache; aa.v_cache = ka.v_cache; aa.block_table = table;
         aa.partial = m->partial; aa.partial_tok_cap = kSmallChunk; aa.out = m->att; aa.d_pos = dpos; aa.pos0 = pos0;
-        const bool fine = single && m->attn_ticket && d.n_kv >= 4;      // the fine cut relies on the in-kernel merge
+        static const bool no_ticket = getenv("GGB_NO_ATTN_MERGE") != nullptr;      // keep every merge out of the attention kernel
+        const bool merge_in_attn = d.n_kv >= 4 && !no_ticket;
+        const bool fine = single && merge_in_attn;                      // the fine cut relies on the in-kernel merge
         const int n_splits = fine ? m->n_splits1 : m->n_splits, pps = fine ? m->pages_per_split1 : m->pages_per_split;
         aa.n_head = d.n_head; aa.n_kv = d.n_kv; aa.head_dim = hd; aa.page = m->page; aa.n_splits = n_splits;
         aa.pages_per_split = pps;
         // Who merges the context splits.  Single-token step with the output projection in the tensor-core layout: that
         // projection's prologue while few splits are visible (0.6 us per split, overlapped with its other loads).  From
         // kMergeInAttn visible splits on, and for several rows, the attention kernel itself (its last CTA per KV head:
-        // ~3 us whatever the count; 8B shape at position 4100, 23 splits: 3.27 ms per step against 3.32) -- but only with four or more KV heads: with one or two, two CTAs would merge
-        // everything (measured on the 12 / 2-head shape: 1.74 ms per step against 1.55 with the merge kernel, whose grid
-        // is one CTA per query head).
+        // ~3 us whatever the count; 8B shape at position 4100, 23 splits: 3.27 ms per step against 3.32) -- but only with
+        // four or more KV heads: with one or two, two CTAs would merge everything (measured on the 12 / 2-head shape:
+        // 1.74 ms per step against 1.55 with the merge kernel, whose grid is one CTA per query head).
         const bool merge_in_gemv = single && l.o->w.layout == 1;
-        static const bool no_ticket = getenv("GGB_NO_ATTN_MERGE") != nullptr;      // keep every merge out of the attention kernel
-        const bool merge_in_attn = d.n_kv >= 4 && !no_ticket;
         aa.merge_ticket = merge_in_attn ? m->attn_ticket : nullptr;
+        // below kMergeInAttn visible splits the projection merges; from there on the attention kernel (four or more KV
+        // heads) or the merge kernel does, which then returns at once while few splits are visible
         aa.merge_min_splits = merge_in_gemv ? kMergeInAttn : 0;
-        aa.skip_merge = (merge_in_gemv && !merge_in_attn) ? 1 : 0;
+        aa.skip_merge = 0;
         M_TRY(launch_attn_paged(c, aa, n_tok, s));
 
         // Tensor parallel: attn_output and ffn_down are row parallel (this rank's K range), so their
@@ -228,7 +230,7 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (merge_in_gemv) {
             a.x = nullptr; a.attn_partial = m->partial; a.attn_d_pos = dpos; a.attn_pos0 = pos0; a.attn_n_splits = n_splits;
-            if (merge_in_attn) { a.attn_merged = m->att; a.attn_merge_below = kMergeInAttn; }
+            a.attn_merged = m->att; a.attn_merge_below = kMergeInAttn;
             a.attn_keys_per_split = pps * m->page; a.attn_hd = hd;
         }
         M_TRY(launch_gemv(c, a, s));
