@@ -198,8 +198,9 @@ GGB_API int ggb_pack_file_write(const char* path, uint32_t type, int64_t N, int 
 GGB_API int ggb_pack_file_read(const char* path, uint32_t type, int64_t N, int K, uint64_t src_fingerprint, int* nb, int* layout,
                                uint64_t* stream_off, void* blob, uint64_t cap, uint64_t* bytes);
 
-/* y[M][ldc] = x[M][lda] * W^T with DEVICE pointers, M <= 16 (decode GEMV), on the handle's
- * stream.  epilogue: 0 store; 1 + bias[N]; 2 + resid[M][ldc].  gamma != NULL applies RMSNorm
+/* y[M][ldc] = x[M][lda] * W^T with DEVICE pointers on the handle's stream.  M <= 16: the exact-activation GEMVs
+ * (rel-L2 <= 1e-5 against the reference's exact fp32 product; M of 3..16 streams the weights once for all rows);
+ * M >= 17: the tcgen05 GEMM (fp16 operands).  epilogue: 0 store; 1 + bias[N]; 2 + resid[M][ldc].  gamma != NULL applies RMSNorm
  * (eps) to each x row first.  Asynchronous. */
 GGB_API int ggb_gemv_device(ggb_handle h, ggb_weight w, const float* d_x, int M, int lda, float* d_y, int ldc,
                             int epilogue, const float* d_extra, const float* d_gamma, float eps);
@@ -258,8 +259,8 @@ GGB_API int ggb_attn_paged_static(ggb_handle h, const ggb_attn_paged_params* p);
  * weights = softmax over just those; y = (resid +) sum_j w_j * down_j(silu(gate_j x) * up_j x)
  * (+ sigmoid(sh_gate_inp . x) * shared expert).  x is the FFN-normed hidden row.  The expert tensors are
  * the GGUF 3-D tensors uploaded whole with ggb_weight_upload as 2-D matrices: gate_exps / up_exps as
- * [n_expert * eff][hidden], down_exps as [n_expert * hidden][eff] (Q4_K or Q6_K).  The chosen ids stay on
- * the device: four kernels, no host round trip.  All pointers are device memory; asynchronous on the
+ * [n_expert * eff][hidden], down_exps as [n_expert * hidden][eff] (Q4_K or Q6_K); top_k <= 15, hidden <= 8192.
+ * The chosen ids stay on the device: five launches (router + top-k in one), no host round trip.  All pointers are device memory; asynchronous on the
  * handle's stream.  sel_out / w_out (optional) receive the chosen ids [top_k] and weights [top_k + 1,
  * the last one the shared expert's gate]. */
 typedef struct ggb_moe_params {
