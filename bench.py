@@ -814,13 +814,13 @@ def run_tp(args):
         dist.destroy_process_group()
 
 
-def config3_figures(b, local):
+def config3_figures(b, local, n_layer=0):
     """Qwen2.5-1.5B shape, every matrix Q8_0 (28 layers, QKV bias, head_dim 128): prefill of 2048 random tokens, then 128
     greedy decode tokens, on one GPU.  Returns {"decode": ..., "prefill": ...}."""
     import dataclasses
     import torch
     from ggnpu_b200.backend import Model
-    cfg = dataclasses.replace(S.QWEN25_1P5B, ctx=2048 + 128 + 16)
+    cfg = dataclasses.replace(S.QWEN25_1P5B, ctx=2048 + 128 + 16, n_layer=n_layer or S.QWEN25_1P5B.n_layer)
     synth = S.build_model(cfg, device="cuda")
     model = Model(b, cfg, synth.tensors)
     del synth
@@ -955,6 +955,7 @@ def main():
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
     ap.add_argument("--config5", action="store_true", help="qwen35moe-shape decode benchmark (expert parallel under torchrun)")
     ap.add_argument("--config3", action="store_true", help="Qwen2.5-1.5B shape, all Q8_0: 2048-token prefill and 128 decode tokens on one GPU")
+    ap.add_argument("--c3-layers", type=int, default=0, help="layers to build for --config3 (0 = all 28; fewer for profiling)")
     ap.add_argument("--q35-layers", type=int, default=40)
     ap.add_argument("--q35-prompt", type=int, default=128)
     ap.add_argument("--no-extras", action="store_true", help="skip the extra figures of the default run (the Qwen2.5-1.5B, Llama-3-8B and qwen35moe shapes on one GPU; tensor / expert parallel figures and checks under torchrun)")
@@ -971,7 +972,7 @@ def main():
     if args.config3:
         from ggnpu_b200.backend import CudaBackend
         b = CudaBackend(0)
-        print(json.dumps({"config3": config3_figures(b, 0)}), flush=True)
+        print(json.dumps({"config3": config3_figures(b, 0, args.c3_layers)}), flush=True)
         b.close()
         return
     if args.config5:

@@ -171,12 +171,14 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
     attn_tile_body<HD, false>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, sm_u, [] { __syncthreads(); });
 }
 
-// grid (n_head, n_tok), 128 threads: merge the visible splits, normalise, write out[t][head][hd].  The splits' (max, sum)
-// pairs are fetched by one thread each and the weights exp(max_s - max) kept in shared memory, so that the sum over
-// splits of every output element is a run of independent loads (a thread that walked the splits one dependent load
-// after the other took 18 us for 18 splits).
-__global__ void __launch_bounds__(128) attn_combine_kernel(AttnPagedArgs a) {
+// grid (n_head, n_tok), 512 threads: merge the visible splits, normalise, write out[t][head][hd].  The splits' (max, sum)
+// pairs are fetched by one thread each and the weights exp(max_s - max) kept in shared memory; the sum over splits of
+// an output element is cut over four groups of 128 threads (splits g, g + 4, ...), each a run of independent loads,
+// and the four partial sums meet in shared memory.  (One thread walking 18 splits one dependent load after the other
+// took 18 us; one group of 128 over 64 splits, four loads in flight, 9 us.)
+__global__ void __launch_bounds__(512) attn_combine_kernel(AttnPagedArgs a) {
     __shared__ float m_s[64], l_s[64], w_s[64];
+    __shared__ float acc_s[3][256];
     pdl_sync();
     const int head = blockIdx.x, t = blockIdx.y, hd = a.head_dim, tid = threadIdx.x;
     const int pos = a.seq_pos ? a.seq_pos[t] : (a.d_pos ? a.d_pos[0] : a.pos0) + t;
@@ -191,13 +193,23 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnPagedArgs a) {
     for (int s = 0; s < n_active; ++s) mx = fmaxf(mx, m_s[s]);
     if (tid < n_active) w_s[tid] = expf(m_s[tid] - mx);
     __syncthreads();
-    float lsum = 0.0f;                                  // every thread, the same order
-    for (int s = 0; s < n_active; ++s) lsum += l_s[s] * w_s[s];
-    for (int d = tid; d < hd; d += 128) {
-        float o = 0.0f;
-#pragma unroll 4
-        for (int s = 0; s < n_active; ++s) o += part[s * stride + 2 + d] * w_s[s];
-        a.out[(static_cast<size_t>(t) * a.n_head + head) * hd + d] = o / lsum;
+    const int g = tid >> 7, lane = tid & 127;
+    float o[2] = {0.0f, 0.0f};                          // head_dim <= 256: elements lane and lane + 128
+#pragma unroll 8
+    for (int s = g; s < n_active; s += 4) {
+        const float w = w_s[s];
+        const float* ps = part + s * stride + 2;
+        if (lane < hd) o[0] += ps[lane] * w;
+        if (lane + 128 < hd) o[1] += ps[lane + 128] * w;
+    }
+    if (g > 0) { acc_s[g - 1][lane] = o[0]; acc_s[g - 1][lane + 128] = o[1]; }
+    __syncthreads();
+    if (g == 0) {
+        float lsum = 0.0f;                              // every thread, the same order
+        for (int s = 0; s < n_active; ++s) lsum += l_s[s] * w_s[s];
+        float* dst = a.out + (static_cast<size_t>(t) * a.n_head + head) * hd;
+        if (lane < hd) dst[lane] = (o[0] + acc_s[0][lane] + acc_s[1][lane] + acc_s[2][lane]) / lsum;
+        if (lane + 128 < hd) dst[lane + 128] = (o[1] + acc_s[0][lane + 128] + acc_s[1][lane + 128] + acc_s[2][lane + 128]) / lsum;
     }
 }
 
@@ -242,7 +254,7 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
     if (e != cudaSuccess) return cuda_status(c, e, "attention split");
     if (a.skip_merge || a.merge_ticket) return GGB_OK;
     if (a.n_splits > 64) return set_status(c, GGB_INVALID_PARAM, "attention: more than 64 context splits");
-    e = launch_pdl(c, attn_combine_kernel, dim3(a.n_head, n_tok), dim3(128), 0, s, a);
+    e = launch_pdl(c, attn_combine_kernel, dim3(a.n_head, n_tok), dim3(512), 0, s, a);
     c->launches++;
     if (e != cudaSuccess) return cuda_status(c, e, "attention combine");
     return cuda_status(c, cudaGetLastError(), "attention combine");

@@ -754,45 +754,62 @@ __global__ void __launch_bounds__(kWarps * 32, 1) gemv_mma_stream_kernel(const R
     bool ok = true;
     if (INLINE_X) {
         // one or two rows, the whole K: limbs of x * gamma and block scales straight into shared memory (as rows_prep_kernel)
+        // a warp's 256-runs are converted four at a time, their loads issued together: one run per trip pays the
+        // memory latency once per run, which at K = 8192 was a third of the kernel
+        constexpr int XB = 4;
         for (int m = 0; m < M; ++m)
-            for (int b = warp; b < nb; b += kWarps) {
-                const int k0 = b * 256 + lane * 8;
-                const float* xr = a.x + static_cast<size_t>(m) * a.lda + k0;
-                const float4 p0 = __ldg(reinterpret_cast<const float4*>(xr)), p1 = __ldg(reinterpret_cast<const float4*>(xr + 4));
-                float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                if (a.gamma) {
-                    float ss = 0.0f;
+            for (int b0 = warp; b0 < nb; b0 += kWarps * XB) {
+                float4 xp[XB][2], gp[XB][2];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-                    ss = wsum(ss);
-                    if (lane == 0) ssb[m][b] = ss;
-                    const float4 g0 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)), g1 = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4));
-                    v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w; v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+                for (int u = 0; u < XB; ++u) {
+                    const int b = b0 + u * kWarps;
+                    if (b >= nb) continue;
+                    const int k0 = b * 256 + lane * 8;
+                    const float* xr = a.x + static_cast<size_t>(m) * a.lda + k0;
+                    xp[u][0] = __ldg(reinterpret_cast<const float4*>(xr)); xp[u][1] = __ldg(reinterpret_cast<const float4*>(xr + 4));
+                    if (a.gamma) { gp[u][0] = __ldg(reinterpret_cast<const float4*>(a.gamma + k0)); gp[u][1] = __ldg(reinterpret_cast<const float4*>(a.gamma + k0 + 4)); }
                 }
-                float am = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
+                for (int u = 0; u < XB; ++u) {
+                    const int b = b0 + u * kWarps;
+                    if (b >= nb) continue;
+                    const int k0 = b * 256 + lane * 8;
+                    const float4 p0 = xp[u][0], p1 = xp[u][1];
+                    float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+                    if (a.gamma) {
+                        float ss = 0.0f;
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
-                const float rs = am > 0.0f ? 127.0f / am : 0.0f;
-                uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
+                        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+                        ss = wsum(ss);
+                        if (lane == 0) ssb[m][b] = ss;
+                        const float4 g0 = gp[u][0], g1 = gp[u][1];
+                        v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w; v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+                    }
+                    float am = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float kMagic = 12582912.0f;
-                    const float r = fminf(fmaxf(v[i] * rs, -127.0f), 127.0f);
-                    const float t1 = r + kMagic;
-                    const float r2 = (r - (t1 - kMagic)) * 128.0f;
-                    const float t2 = r2 + kMagic;
-                    const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
-                    w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
-                    w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
-                    w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
+                    for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xFFFFFFFFu, am, o));
+                    const float rs = am > 0.0f ? 127.0f / am : 0.0f;
+                    uint32_t w1[2] = {0, 0}, w2[2] = {0, 0}, w3[2] = {0, 0};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float kMagic = 12582912.0f;
+                        const float r = fminf(fmaxf(v[i] * rs, -127.0f), 127.0f);
+                        const float t1 = r + kMagic;
+                        const float r2 = (r - (t1 - kMagic)) * 128.0f;
+                        const float t2 = r2 + kMagic;
+                        const float t3 = (r2 - (t2 - kMagic)) * 128.0f + kMagic;
+                        w1[i >> 2] |= (__float_as_uint(t1) & 0xFFu) << (8 * (i & 3));
+                        w2[i >> 2] |= (__float_as_uint(t2) & 0xFFu) << (8 * (i & 3));
+                        w3[i >> 2] |= (__float_as_uint(t3) & 0xFFu) << (8 * (i & 3));
+                    }
+                    int8_t* pl = xl + static_cast<size_t>(3 * m) * plane_stride + k0;
+                    *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
+                    *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
+                    *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
+                    if (lane == 0) xs[m * (K >> 8) + b] = am / 127.0f;
                 }
-                int8_t* pl = xl + static_cast<size_t>(3 * m) * plane_stride + k0;
-                *reinterpret_cast<uint2*>(pl) = make_uint2(w1[0], w1[1]);
-                *reinterpret_cast<uint2*>(pl + plane_stride) = make_uint2(w2[0], w2[1]);
-                *reinterpret_cast<uint2*>(pl + 2 * plane_stride) = make_uint2(w3[0], w3[1]);
-                if (lane == 0) xs[m * (K >> 8) + b] = am / 127.0f;
             }
         consumer_sync();
         if (threadIdx.x < M) {
