@@ -53,6 +53,10 @@ class ModelConfig:
     out_type: int | None = None  # output.weight type when not tied
     norm_jitter: float = 0.1     # norm gammas = 1 + jitter*N(0,1)
     seed: int = 1234
+    qk_norm: bool = False        # per-head attn_q_norm / attn_k_norm (qwen3, lfm2)
+    # lfm2 (src/cli/main.cpp:2145-2167): layers listed here carry shortconv.* instead of attn_*; taps = shortconv.l_cache
+    conv_layers: tuple = ()
+    d_conv: int = 3
 
 
 # The benchmark shapes (model dims only; weights are random-init).

@@ -271,6 +271,14 @@ def tiny_config(**kw) -> ModelConfig:
     return ModelConfig(**base)
 
 
+# lfm2 test models (keyword arguments of tiny_config): gated short-convolution layers around GQA attention layers with
+# per-head QK-norm; tied output, final norm stored as token_embd_norm
+LFM2_CASES = {
+    "lfm2": dict(arch="lfm2", n_layer=4, conv_layers=(0, 1, 3), qk_norm=True, rope_base=1e6, seed=33),
+    "lfm2_q8": dict(arch="lfm2", n_layer=3, conv_layers=(0, 2), d_conv=4, qk_norm=True, rope_base=1e6, wtype=Q8_0, wtype_alt=Q8_0, seed=22),
+}
+
+
 @dataclass
 class SynthModel:
     cfg: ModelConfig
@@ -294,6 +302,8 @@ class SynthModel:
             "tokenizer.ggml.scores": [0.0] * c.vocab,
             "tokenizer.ggml.add_space_prefix": False,
         }
+        if a == "lfm2":
+            kv["lfm2.shortconv.l_cache"] = c.d_conv
         return kv
 
     def write(self, path: str) -> None:
@@ -331,18 +341,31 @@ def build_model(cfg: ModelConfig, device: str = "cpu") -> SynthModel:
         m.add(name, F32, [n], v.numpy().view(np.uint8).copy())
 
     qd, kvd = cfg.n_head * cfg.head_dim, cfg.n_kv * cfg.head_dim
+    lfm2 = cfg.arch == "lfm2"
     mat("token_embd.weight", cfg.vocab, cfg.hidden, cfg.wtype)
-    vec("output_norm.weight", cfg.hidden, "norm")
+    vec("token_embd_norm.weight" if lfm2 else "output_norm.weight", cfg.hidden, "norm")   # lfm2's final norm (src/cli/main.cpp:2853-2855)
     if not cfg.tied:
         mat("output.weight", cfg.vocab, cfg.hidden, cfg.out_type if cfg.out_type is not None else cfg.wtype)
     for l in range(cfg.n_layer):
         p = f"blk.{l}."
         vec(p + "attn_norm.weight", cfg.hidden, "norm")
         vec(p + "ffn_norm.weight", cfg.hidden, "norm")
-        mat(p + "attn_q.weight", qd, cfg.hidden, cfg.wtype)
-        mat(p + "attn_k.weight", kvd, cfg.hidden, cfg.wtype)
-        mat(p + "attn_v.weight", kvd, cfg.hidden, cfg.wtype_alt)
-        mat(p + "attn_output.weight", cfg.hidden, qd, cfg.wtype)
+        if lfm2 and l in cfg.conv_layers:
+            # gated short convolution (src/cli/main.cpp:2693-2732): in_proj -> [B | C | x], F32 conv {d_conv, hidden}
+            mat(p + "shortconv.in_proj.weight", 3 * cfg.hidden, cfg.hidden, cfg.wtype)
+            mat(p + "shortconv.out_proj.weight", cfg.hidden, cfg.hidden, cfg.wtype_alt)
+            g = torch.Generator(device="cpu")
+            g.manual_seed(_name_seed(cfg.seed, p + "shortconv.conv.weight"))
+            cw = (torch.randn(cfg.hidden, cfg.d_conv, generator=g, dtype=torch.float32) * 0.5).contiguous()
+            m.add(p + "shortconv.conv.weight", F32, [cfg.d_conv, cfg.hidden], cw.numpy().view(np.uint8).reshape(-1).copy())
+        else:
+            mat(p + "attn_q.weight", qd, cfg.hidden, cfg.wtype)
+            mat(p + "attn_k.weight", kvd, cfg.hidden, cfg.wtype)
+            mat(p + "attn_v.weight", kvd, cfg.hidden, cfg.wtype_alt)
+            mat(p + "attn_output.weight", cfg.hidden, qd, cfg.wtype)
+            if cfg.qk_norm:
+                vec(p + "attn_q_norm.weight", cfg.head_dim, "norm")
+                vec(p + "attn_k_norm.weight", cfg.head_dim, "norm")
         mat(p + "ffn_gate.weight", cfg.ffn, cfg.hidden, cfg.wtype)
         mat(p + "ffn_up.weight", cfg.ffn, cfg.hidden, cfg.wtype)
         mat(p + "ffn_down.weight", cfg.hidden, cfg.ffn, cfg.wtype_alt)

@@ -103,6 +103,8 @@ class Oracle:
         L.ggo_model_set_globals.argtypes = [C.c_void_p, _u8p, C.c_uint32, _u8p, C.c_uint32, _f32p, _f32p, C.c_int]
         L.ggo_model_set_weight.argtypes = [C.c_void_p, C.c_int, C.c_int, _u8p, C.c_uint32]
         L.ggo_model_set_vec.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p]
+        L.ggo_model_set_lfm2.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.ggo_model_reset_conv.argtypes = [C.c_void_p]
         L.ggo_forward.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, _f32p, _f32p]
         L.ggo_model_kv.restype = _f32p
         L.ggo_model_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
@@ -274,22 +276,28 @@ class Oracle:
         return tok, sd.value
 
 
-_W_SLOTS = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate": 4, "ffn_up": 5, "ffn_down": 6}
+_W_SLOTS = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate": 4, "ffn_up": 5, "ffn_down": 6,
+            "shortconv.in_proj": 7, "shortconv.out_proj": 8}
 _V_SLOTS = {"attn_norm.weight": 0, "ffn_norm.weight": 1, "attn_q.bias": 2, "attn_k.bias": 3, "attn_v.bias": 4,
-            "attn_q_norm.weight": 5, "attn_k_norm.weight": 6}
+            "attn_q_norm.weight": 5, "attn_k_norm.weight": 6, "shortconv.conv.weight": 7}
 
 
 class OracleModel:
     """The generic-architecture forward of the reference CLI, restated
     (ggo_forward), over the tensors of a ggnpu_b200.testing.synth.SynthModel."""
 
-    def __init__(self, oracle: Oracle, synth):
+    def __init__(self, oracle: Oracle, synth, cpu_rope: bool = True):
+        """lfm2 models: cpu_rope=True rotates as the reference CLI does on its CPU backend (adjacent pairs, base
+        10000); False as the branch asks its backend to (split-half pairs, the model's base)."""
         self.o, self.cfg = oracle, synth.cfg
         c = synth.cfg
         L = oracle.lib
         self._keep = []
+        lfm2 = c.arch == "lfm2"
         self.h = L.ggo_model_new(c.n_layer, c.hidden, c.n_head, c.n_kv, c.head_dim, c.ffn, c.vocab, c.ctx,
-                                 c.rms_eps, float(np.float32(c.rope_base)), 1.0, 1 if c.arch == "qwen3" else 0)
+                                 c.rms_eps, float(np.float32(c.rope_base)), 1.0, 1 if c.arch in ("qwen3", "lfm2") else 0)
+        if lfm2:
+            L.ggo_model_set_lfm2(self.h, c.d_conv, 1 if cpu_rope else 0)
         t = synth.tensors
 
         def raw(name):
@@ -305,10 +313,12 @@ class OracleModel:
         emb, et = raw("token_embd.weight")
         out, ot = raw("output.weight") if "output.weight" in t else (None, 0)
         ff = f32("rope_freqs.weight") if "rope_freqs.weight" in t else None
-        L.ggo_model_set_globals(self.h, _bp(emb), et, _bp(out), ot, _fp(f32("output_norm.weight")), _fp(ff),
+        L.ggo_model_set_globals(self.h, _bp(emb), et, _bp(out), ot, _fp(f32("token_embd_norm.weight" if lfm2 else "output_norm.weight")), _fp(ff),
                                 0 if ff is None else ff.size)
         for l in range(c.n_layer):
             for nm, slot in _W_SLOTS.items():
+                if f"blk.{l}.{nm}.weight" not in t:        # lfm2: a layer has attention or the short convolution
+                    continue
                 b, tid = raw(f"blk.{l}.{nm}.weight")
                 L.ggo_model_set_weight(self.h, l, slot, _bp(b), tid)
             for nm, slot in _V_SLOTS.items():
@@ -324,6 +334,11 @@ class OracleModel:
         rc = self.o.lib.ggo_forward(self.h, toks.ctypes.data_as(C.POINTER(C.c_int32)), toks.size, pos, _fp(logits), _fp(hid))
         assert rc == 0
         return (logits, hid) if want_hidden else logits
+
+    def reset(self):
+        """A new sequence (lfm2: the convolution states return to zero; the KV cache is overwritten by position)."""
+        if self.cfg.arch == "lfm2":
+            self.o.lib.ggo_model_reset_conv(self.h)
 
     def kv_row(self, layer, pos, want_v):
         c = self.cfg
@@ -398,6 +413,11 @@ class OracleQ35Model:
         for i, tk in enumerate(tokens):
             out = self.forward(tk, pos0 + i)
         return out
+
+    def reset(self):
+        """A new sequence (lfm2: the convolution states return to zero; the KV cache is overwritten by position)."""
+        if self.cfg.arch == "lfm2":
+            self.o.lib.ggo_model_reset_conv(self.h)
 
     def kv_row(self, layer, pos, want_v):
         c = self.cfg

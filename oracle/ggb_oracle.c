@@ -637,6 +637,10 @@ typedef struct {
     const float *attn_norm, *ffn_norm;          /* F32 [hidden] */
     const float *bq, *bk, *bv;                  /* optional F32 biases */
     const float *q_norm, *k_norm;               /* optional F32 [head_dim] */
+    /* lfm2 gated short-convolution layer (present instead of attn_*): in_proj [3 hidden][hidden],
+     * out_proj [hidden][hidden], conv F32 [hidden][taps] (tap-contiguous) */
+    ggo_weight sc_in, sc_out;
+    const float* sc_conv;
 } ggo_layer;
 
 typedef struct {
@@ -650,6 +654,10 @@ typedef struct {
     /* state owned by the model object */
     float *kcache, *vcache;                      /* [L][ctx][n_kv][hd], K post-RoPE (src/runtime/kv_cache.cpp:38-48) */
     float *rope_cos, *rope_sin;                  /* [ctx][hd/2] */
+    /* lfm2 (src/cli/main.cpp:2145-2167, 2680-2856): taps of the short convolution, the state of every layer
+     * [n_layer][taps - 1][hidden] (oldest first), and whether RoPE goes through the CPU backend's rope() */
+    int lfm2, conv_taps, cpu_rope;
+    float* conv_state;
 } ggo_model;
 
 GGO_API ggo_model* ggo_model_new(int n_layer, int hidden, int n_head, int n_kv, int head_dim, int ffn,
@@ -671,7 +679,24 @@ GGO_API ggo_model* ggo_model_new(int n_layer, int hidden, int n_head, int n_kv, 
 
 GGO_API void ggo_model_free(ggo_model* m) {
     if (!m) return;
-    free((void*)m->layers); free(m->kcache); free(m->vcache); free(m->rope_cos); free(m->rope_sin); free(m);
+    free((void*)m->layers); free(m->kcache); free(m->vcache); free(m->rope_cos); free(m->rope_sin); free(m->conv_state); free(m);
+}
+
+/* Switch the model to the lfm2 branch: per-head QK-norm through the backend's rms_norm (g_rmsnorm, :2231-2245),
+ * final norm = token_embd_norm (pass it as output_norm), layers with sc_in set run the short convolution.
+ * cpu_rope = 1 restates what the reference CLI does on its CPU backend: g_rope (:2250-2268) calls
+ * Backend::rope_batched, whose default (include/ggnpu/backend.h:123-141) loops the CPU backend's rope()
+ * (cpu_ref.cpp:158-174): adjacent pairs at base 10000, whatever freq_base and neox_split_half say.
+ * cpu_rope = 0 is what the branch asks its backend for (split-half pairs at the model's base), from the table. */
+GGO_API void ggo_model_set_lfm2(ggo_model* m, int conv_taps, int cpu_rope) {
+    m->lfm2 = 1; m->conv_taps = conv_taps; m->cpu_rope = cpu_rope;
+    free(m->conv_state);
+    m->conv_state = (float*)calloc((size_t)m->n_layer * (size_t)(conv_taps > 1 ? conv_taps - 1 : 1) * m->hidden, sizeof(float));
+}
+
+/* A new sequence: the convolution states start at zero (lconv_state, :2159). */
+GGO_API void ggo_model_reset_conv(ggo_model* m) {
+    if (m->conv_state) memset(m->conv_state, 0, sizeof(float) * (size_t)m->n_layer * (size_t)(m->conv_taps > 1 ? m->conv_taps - 1 : 1) * m->hidden);
 }
 
 GGO_API void ggo_model_set_globals(ggo_model* m, const uint8_t* tok_embd, uint32_t tok_type,
@@ -684,17 +709,17 @@ GGO_API void ggo_model_set_globals(ggo_model* m, const uint8_t* tok_embd, uint32
     ggo_rope_table(m->ctx, m->head_dim, m->rope_scale, m->rope_base, rope_ff, n_rope_ff, m->rope_cos, m->rope_sin);
 }
 
-/* which: 0 q,1 k,2 v,3 o,4 gate,5 up,6 down */
+/* which: 0 q,1 k,2 v,3 o,4 gate,5 up,6 down,7 shortconv in_proj,8 shortconv out_proj */
 GGO_API void ggo_model_set_weight(ggo_model* m, int layer, int which, const uint8_t* data, uint32_t type) {
     ggo_layer* l = (ggo_layer*)&m->layers[layer];
-    ggo_weight* w[7] = {&l->attn_q, &l->attn_k, &l->attn_v, &l->attn_o, &l->ffn_gate, &l->ffn_up, &l->ffn_down};
+    ggo_weight* w[9] = {&l->attn_q, &l->attn_k, &l->attn_v, &l->attn_o, &l->ffn_gate, &l->ffn_up, &l->ffn_down, &l->sc_in, &l->sc_out};
     w[which]->data = data; w[which]->type = type;
 }
 
-/* which: 0 attn_norm,1 ffn_norm,2 bq,3 bk,4 bv,5 q_norm,6 k_norm */
+/* which: 0 attn_norm,1 ffn_norm,2 bq,3 bk,4 bv,5 q_norm,6 k_norm,7 shortconv conv */
 GGO_API void ggo_model_set_vec(ggo_model* m, int layer, int which, const float* v) {
     ggo_layer* l = (ggo_layer*)&m->layers[layer];
-    const float** p[7] = {&l->attn_norm, &l->ffn_norm, &l->bq, &l->bk, &l->bv, &l->q_norm, &l->k_norm};
+    const float** p[8] = {&l->attn_norm, &l->ffn_norm, &l->bq, &l->bk, &l->bv, &l->q_norm, &l->k_norm, &l->sc_conv};
     *p[which] = v;
 }
 
@@ -871,6 +896,31 @@ GGO_API int ggo_forward(ggo_model* m, const int32_t* tokens, int n_tok, int pos,
     for (int L = 0; L < m->n_layer; ++L) {
         const ggo_layer* l = &m->layers[L];
         for (int t = 0; t < n_tok; ++t) ggo_rms_norm(x + (size_t)t * H, xn + (size_t)t * H, H, m->rms_eps, l->attn_norm);
+        if (m->lfm2 && l->sc_in.data) {
+            /* gated short convolution, main.cpp:2693-2732: bcx = in_proj(xn) = [B | C | x]; bx = B * x; depthwise causal
+             * conv over the last `taps` values of bx (newest = this token); y = C * conv; out_proj(y) joins the residual.
+             * Tokens in order: the state of the layer carries from one to the next. */
+            const int taps = m->conv_taps, dcm1 = taps - 1;
+            float* bcx = (float*)malloc(sizeof(float) * T * 3 * H);
+            float* yc = (float*)malloc(sizeof(float) * T * H);
+            float* st = m->conv_state + (size_t)L * (size_t)(dcm1 > 0 ? dcm1 : 1) * H;
+            ggo_matmul_exact(xn, n_tok, H, l->sc_in.data, l->sc_in.type, 3 * H, H, bcx, 3 * H);
+            for (int t = 0; t < n_tok; ++t) {
+                const float *b = bcx + (size_t)t * 3 * H, *c = b + H, *xx = b + 2 * H;
+                for (int ch = 0; ch < H; ++ch) {
+                    const float bx = b[ch] * xx[ch];
+                    float acc = l->sc_conv[ch * taps + dcm1] * bx;
+                    for (int kk = 0; kk < dcm1; ++kk) acc += l->sc_conv[ch * taps + kk] * st[(size_t)kk * H + ch];
+                    yc[(size_t)t * H + ch] = c[ch] * acc;
+                    for (int kk = 0; kk < dcm1 - 1; ++kk) st[(size_t)kk * H + ch] = st[(size_t)(kk + 1) * H + ch];
+                    if (dcm1 > 0) st[(size_t)(dcm1 - 1) * H + ch] = bx;
+                }
+            }
+            ggo_matmul_exact(yc, n_tok, H, l->sc_out.data, l->sc_out.type, H, H, proj, H);
+            for (size_t i = 0; i < T * H; ++i) x[i] += proj[i];
+            free(bcx); free(yc);
+            goto ffn;
+        }
         ggo_matmul_exact(xn, n_tok, H, l->attn_q.data, l->attn_q.type, qd, H, q, qd);
         ggo_matmul_exact(xn, n_tok, H, l->attn_k.data, l->attn_k.type, kvd, H, k, kvd);
         ggo_matmul_exact(xn, n_tok, H, l->attn_v.data, l->attn_v.type, kvd, H, v, kvd);
@@ -880,12 +930,24 @@ GGO_API int ggo_forward(ggo_model* m, const int32_t* tokens, int n_tok, int pos,
             if (l->bv) for (int j = 0; j < kvd; ++j) v[(size_t)t * kvd + j] += l->bv[j];
         }
         for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3289-3312 */
+            if (m->lfm2) {                                        /* main.cpp:2756-2761: the backend's rms_norm, in place */
+                if (l->q_norm) for (int h = 0; h < m->n_head; ++h) { float* p = q + (size_t)t * qd + (size_t)h * hd; ggo_rms_norm(p, p, hd, m->rms_eps, l->q_norm); }
+                if (l->k_norm) for (int h = 0; h < m->n_kv; ++h) { float* p = k + (size_t)t * kvd + (size_t)h * hd; ggo_rms_norm(p, p, hd, m->rms_eps, l->k_norm); }
+                continue;
+            }
             if (l->q_norm) for (int h = 0; h < m->n_head; ++h) ggo_rms_norm_head_f64(q + (size_t)t * qd + (size_t)h * hd, hd, m->rms_eps, l->q_norm);
             if (l->k_norm) for (int h = 0; h < m->n_kv; ++h) ggo_rms_norm_head_f64(k + (size_t)t * kvd + (size_t)h * hd, hd, m->rms_eps, l->k_norm);
         }
         for (int t = 0; t < n_tok; ++t) {                         /* main.cpp:3314-3351 */
             const float* c = m->rope_cos + (size_t)(pos + t) * (hd / 2);
             const float* s = m->rope_sin + (size_t)(pos + t) * (hd / 2);
+            if (m->lfm2 && m->cpu_rope) {                         /* main.cpp:2762-2763 on the CPU backend */
+                memcpy(qr + (size_t)t * qd, q + (size_t)t * qd, sizeof(float) * qd);
+                memcpy(kr + (size_t)t * kvd, k + (size_t)t * kvd, sizeof(float) * kvd);
+                for (int h = 0; h < m->n_head; ++h) ggo_rope_cpu_ref(qr + (size_t)t * qd + (size_t)h * hd, hd, pos + t, 1.0f, hd);
+                for (int h = 0; h < m->n_kv; ++h) ggo_rope_cpu_ref(kr + (size_t)t * kvd + (size_t)h * hd, hd, pos + t, 1.0f, hd);
+                continue;
+            }
             ggo_rope_apply(qr + (size_t)t * qd, q + (size_t)t * qd, m->n_head, hd, hd, c, s, m->rope_neox);
             ggo_rope_apply(kr + (size_t)t * kvd, k + (size_t)t * kvd, m->n_kv, hd, hd, c, s, m->rope_neox);
         }
@@ -904,6 +966,7 @@ GGO_API int ggo_forward(ggo_model* m, const int32_t* tokens, int n_tok, int pos,
             ggo_flash_attn(qr + (size_t)t * qd, kexp, vexp, att + (size_t)t * qd, m->n_head, hd, ctx_len, pos + t);
         ggo_matmul_exact(att, n_tok, qd, l->attn_o.data, l->attn_o.type, H, qd, proj, H);
         for (size_t i = 0; i < T * H; ++i) x[i] += proj[i];
+    ffn:
         for (int t = 0; t < n_tok; ++t) ggo_rms_norm(x + (size_t)t * H, xn + (size_t)t * H, H, m->rms_eps, l->ffn_norm);
         ggo_matmul_exact(xn, n_tok, H, l->ffn_gate.data, l->ffn_gate.type, F, H, g, F);
         ggo_matmul_exact(xn, n_tok, H, l->ffn_up.data, l->ffn_up.type, F, H, u, F);

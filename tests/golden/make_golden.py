@@ -2,7 +2,7 @@
 
 Run where the reference tree is available:
 
-    make -C oracle ref REF=/path/to/ggnpu && python tests/golden/make_golden.py [--cli-only | --grid-only]
+    make -C oracle ref REF=/path/to/ggnpu && python tests/golden/make_golden.py [--cli-only | --grid-only | --cli-cases a,b]
 
 Every array stored here is an INPUT (seeded random bytes / floats) or an OUTPUT of
 the reference's functions on that input (oracle/_ref/libggnpu_ref.so, built from
@@ -95,6 +95,10 @@ def cli_cases():
         # qwen35moe: 3 Gated DeltaNet layers + 1 gated full-attention layer, 8 experts top-2 + shared expert
         "qwen35moe": (S.tiny_q35_config(), S.build_q35_model, 7, 6),
         "qwen35moe_sk128": (S.tiny_q35_config(sk=128, seed=77), S.build_q35_model, 9, 6),
+        # lfm2: gated short-convolution layers around GQA attention layers with per-head QK-norm; tied output,
+        # final norm stored as token_embd_norm
+        "lfm2": (S.tiny_config(**S.LFM2_CASES["lfm2"]), S.build_model, 7, 6),
+        "lfm2_q8": (S.tiny_config(**S.LFM2_CASES["lfm2_q8"]), S.build_model, 9, 6),
     }
 
 
@@ -103,11 +107,17 @@ SAMPLED_CASES = {"llama": [(0.8, 42), (1.5, 7)], "qwen2": [(0.7, 123456789012)]}
 N_SAMPLED = 12
 
 
-def cli_vectors():
+def cli_vectors(only=None):
     """End to end: the unmodified reference CLI (exact fp32 matmul path) on seeded synthetic models:
-    top-10 logits after the prompt and the greedy continuation -> ref_cli.npz."""
+    top-10 logits after the prompt and the greedy continuation -> ref_cli.npz.  only: names of the cases to
+    (re)generate; the other cases keep the arrays the file already holds."""
     e2e = {}
+    if only:
+        with np.load(os.path.join(HERE, "ref_cli.npz")) as old:
+            e2e = {k: old[k] for k in old.files}
     for name, (cfg, builder, n_prompt, n_gen) in cli_cases().items():
+        if only and name not in only:
+            continue
         m = builder(cfg)
         path = f"/tmp/ggb_golden_{name}.gguf"
         m.write(path)
@@ -166,6 +176,8 @@ if __name__ == "__main__":
         grid_vectors()
     elif "--cli-only" in sys.argv:
         cli_vectors()
+    elif "--cli-cases" in sys.argv:                      # --cli-cases lfm2,lfm2_q8: only these, the rest kept
+        cli_vectors(only=sys.argv[sys.argv.index("--cli-cases") + 1].split(","))
     else:
         main()
         cli_vectors()

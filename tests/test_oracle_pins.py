@@ -110,6 +110,9 @@ def test_matmul_matches_reference_vectors(oracle, vectors, t):
 
 CLI_CASES = {"llama": dict(seed=11), "qwen2": dict(arch="qwen2", qkv_bias=True, wtype=S.Q8_0, wtype_alt=S.Q8_0, seed=12,
                                                     rope_base=1e6, tied=False)}
+# lfm2 (src/cli/main.cpp:2680-2856): the same test holds the short-convolution branch, the backend-side QK-norm and the
+# CPU backend's rotation to the CLI's output
+CLI_CASES.update(S.LFM2_CASES)
 
 
 SAMPLED = [("llama", 0.8, 42), ("llama", 1.5, 7), ("qwen2", 0.7, 123456789012)]
