@@ -92,7 +92,7 @@ class DeltaNetParams(C.Structure):
 class ModelDesc(C.Structure):
     _fields_ = [("n_layer", C.c_int), ("hidden", C.c_int), ("n_head", C.c_int), ("n_kv", C.c_int), ("head_dim", C.c_int),
                 ("ffn", C.c_int), ("vocab", C.c_int), ("ctx", C.c_int), ("rms_eps", C.c_float), ("rope_base", C.c_float),
-                ("rope_scale", C.c_float), ("rope_neox", C.c_int), ("kv_page", C.c_int)]
+                ("rope_scale", C.c_float), ("rope_neox", C.c_int), ("kv_page", C.c_int), ("conv_taps", C.c_int)]
 
 
 class Q35Desc(C.Structure):
@@ -419,20 +419,25 @@ class CudaBackend:
         return int(self.lib.ggb_launch_count(self.h))
 
 
-_SLOTS = {"token_embd.weight": 0, "output.weight": 1, "output_norm.weight": 2, "rope_freqs.weight": 3}
+_SLOTS = {"token_embd.weight": 0, "output.weight": 1, "output_norm.weight": 2, "rope_freqs.weight": 3,
+          "token_embd_norm.weight": 2}        # lfm2 keeps its final norm under this name (src/cli/main.cpp:2853-2855)
 _LAYER_SLOTS = {"attn_norm.weight": 10, "attn_q.weight": 11, "attn_k.weight": 12, "attn_v.weight": 13,
                 "attn_output.weight": 14, "ffn_norm.weight": 15, "ffn_gate.weight": 16, "ffn_up.weight": 17,
                 "ffn_down.weight": 18, "attn_q.bias": 19, "attn_k.bias": 20, "attn_v.bias": 21, "attn_q_norm.weight": 22,
-                "attn_k_norm.weight": 23}
+                "attn_k_norm.weight": 23,
+                "shortconv.in_proj.weight": 24, "shortconv.out_proj.weight": 25, "shortconv.conv.weight": 26}
 
 
 class Model:
-    """A llama / qwen2 / qwen3-style decoder resident in HBM.
+    """A llama / qwen2 / qwen3 / lfm2-style decoder resident in HBM.
 
     `tensors` maps GGUF tensor names to (ggml type id, dims with dims[0]=K, raw bytes),
     the form ggnpu_b200.testing.synth.SynthModel.tensors has."""
 
-    def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = "", n_seq: int = 1):
+    def __init__(self, backend: CudaBackend, cfg, tensors: dict, cache_dir: str | None = None, model_id: str = "", n_seq: int = 1,
+                 rope_neox: int | None = None, rope_base: float | None = None):
+        """rope_neox / rope_base override what the architecture implies (qwen3 and lfm2: split-half pairs at the model's
+        base); rope_neox=0, rope_base=10000 on an lfm2 model is the rotation the reference CLI applies on its CPU backend."""
         self.b, self.cfg = backend, cfg
         L = backend.lib
         if backend.tp_size > 1:          # this process holds one shard; `cfg` and `tensors` describe the full model
@@ -440,8 +445,10 @@ class Model:
             tensors = tp.shard_tensors(cfg, tensors, backend.tp_rank, backend.tp_size)
             cfg = tp.shard_config(cfg, backend.tp_size)
         self.cfg_local = cfg
+        neox = (1 if cfg.arch in ("qwen3", "lfm2") else 0) if rope_neox is None else int(rope_neox)
+        base = cfg.rope_base if rope_base is None else rope_base
         desc = ModelDesc(cfg.n_layer, cfg.hidden, cfg.n_head, cfg.n_kv, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.ctx,
-                         cfg.rms_eps, float(np.float32(cfg.rope_base)), 1.0, 1 if cfg.arch == "qwen3" else 0, 0)
+                         cfg.rms_eps, float(np.float32(base)), 1.0, neox, 0, getattr(cfg, "d_conv", 0) if cfg.arch == "lfm2" else 0)
         m = C.c_void_p()
         backend.check(L.ggb_model_create(backend.h, C.byref(desc), C.byref(m)), "model_create")
         self.m = m
@@ -463,6 +470,8 @@ class Model:
                     raise KeyError(f"tensor {name} has no slot in the generic graph")
                 slot, layer = _LAYER_SLOTS[parts[2]], int(parts[1])
             n, k = (dims[1], dims[0]) if len(dims) == 2 else (dims[0], 1)
+            if slot == 26:               # F32 {taps, hidden}: one vector of hidden x taps values
+                n, k = dims[0] * dims[1], 1
             backend.check(L.ggb_model_set_tensor(m, slot, layer, int(tid), n, k, _ptr(raw)), f"set_tensor({name})")
         backend.check(L.ggb_model_finalize(m), "model_finalize")
 

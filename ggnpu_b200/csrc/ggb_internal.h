@@ -192,6 +192,7 @@ int launch_rope_angles(Context* c, float* x, int n_heads, int n_dims, int64_t ro
 int launch_matmul_f32_kn(Context* c, const float* A, const float* B, float* C, int M, int N, int K, int lda, int ldc, cudaStream_t s);
 int launch_qgate_split(Context* c, const float* qg, float* q_out, int n_head, int hd, cudaStream_t s);
 int launch_attn_gate(Context* c, float* out, const float* qg, int n_head, int hd, cudaStream_t s);
+int launch_shortconv(Context* c, const float* bcx, const float* conv_w, float* state, float* y, int n_tok, int hidden, int taps, cudaStream_t s);
 int launch_argmax(Context* c, const float* x, int n, int32_t* d_out, float* d_partial, cudaStream_t s);
 int launch_argmax_rows(Context* c, const float* x, int n, int64_t ld, int rows, int32_t* d_out, float* d_partial, cudaStream_t s);
 

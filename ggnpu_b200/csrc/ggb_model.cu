@@ -23,6 +23,10 @@ namespace {
 struct Layer {
     DeviceWeight *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
     float *attn_norm = nullptr, *ffn_norm = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    // lfm2 gated short-convolution layer (instead of q / k / v / o): projections, taps [hidden][conv_taps], state [conv_taps - 1][hidden]
+    DeviceWeight *sc_in = nullptr, *sc_out = nullptr;
+    float *sc_conv = nullptr, *sc_state = nullptr;
+    bool conv() const { return sc_in != nullptr; }
 };
 
 // Prompt tokens per forward pass.  The reference chunks at 256 (main.cpp:2326); results do not depend
@@ -84,6 +88,10 @@ struct ggb_model_s {
     int32_t* d_sampled = nullptr;
     cudaGraphExec_t sample_graph = nullptr;
     uint64_t sample_launches = 0;
+    // lfm2: any short-convolution layer; [B | C | x] rows of its in_proj and the convolution's output rows
+    bool has_conv = false;
+    int conv_taps = 3;
+    float *bcx = nullptr, *yconv = nullptr;
     // persistent decode-step kernel (single-token steps of an all-Q4_K / Q6_K model on one GPU)
     bool use_step = false;
     StepArgs step{};
@@ -153,7 +161,21 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
     }
     for (int L = 0; L < d.n_layer; ++L) {
         const Layer& l = m->layers[L];
-        GemvArgs a = gemv_args(l.q, m->x, n_tok, H, m->q, qd);
+        const bool tp = c->tp_size > 1;
+        const int resid_epi = (!tp || c->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
+        GemvArgs a{};
+        if (l.conv()) {
+            // gated short convolution (src/cli/main.cpp:2693-2732): in_proj with the norm in its prologue, the per-channel
+            // convolution over the rows in order, out_proj with the residual in its epilogue
+            a = gemv_args(l.sc_in, m->x, n_tok, H, m->bcx, 3 * H);
+            a.gamma = l.attn_norm; a.eps = d.rms_eps;
+            M_TRY(launch_gemv(c, a, s));
+            M_TRY(launch_shortconv(c, m->bcx, l.sc_conv, l.sc_state, m->yconv, n_tok, H, m->conv_taps, s));
+            a = gemv_args(l.sc_out, m->yconv, n_tok, H, m->x, H);
+            a.epi = EPI_RESIDUAL; a.resid = m->x;
+            M_TRY(launch_gemv(c, a, s));
+        } else {
+        a = gemv_args(l.q, m->x, n_tok, H, m->q, qd);
         a.gamma = l.attn_norm; a.eps = d.rms_eps;
         if (l.bq) { a.epi = EPI_ADD_BIAS; a.bias = l.bq; }
         const bool biases_agree = (l.bq != nullptr) == (l.bk != nullptr) && (l.bq != nullptr) == (l.bv != nullptr);
@@ -224,8 +246,6 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         // Tensor parallel: attn_output and ffn_down are row parallel (this rank's K range), so their
         // results are partial sums.  Rank 0 adds the residual stream, the other ranks overwrite their
         // copy of it with the bare partial product, and the all-reduce leaves resid + sum on every rank.
-        const bool tp = c->tp_size > 1;
-        const int resid_epi = (!tp || c->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
         a = gemv_args(l.o, m->att, n_tok, qd, m->x, H);
         a.epi = resid_epi; a.resid = resid_epi == EPI_RESIDUAL ? m->x : nullptr;
         if (merge_in_gemv) {
@@ -235,6 +255,7 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
         }
         M_TRY(launch_gemv(c, a, s));
         if (tp) M_TRY(tp_all_reduce(c, m->x, static_cast<size_t>(n_tok) * H, s));
+        }
 
         // prompt chunks: silu(gate) * up goes straight into the down projection's fp16 tile image
         const bool act_as_image = m->tc_images && n_tok >= c->tc_min_m;
@@ -272,6 +293,16 @@ int enqueue_forward(ggb_model m, int n_tok, bool dev_pos, int pos0, bool all_row
     return GGB_OK;
 }
 
+// A call that starts at position 0 starts a new sequence: the short-convolution states return to zero
+// (lconv_state, src/cli/main.cpp:2159).  The KV cache needs no such step (a position is written before it is read).
+int conv_reset(ggb_model m, int pos0) {
+    if (!m->has_conv || pos0 != 0) return GGB_OK;
+    for (Layer& l : m->layers)
+        if (l.conv())
+            M_TRY(cuda_status(m->c, cudaMemsetAsync(l.sc_state, 0, sizeof(float) * static_cast<size_t>(std::max(m->conv_taps - 1, 1)) * m->d.hidden, m->c->stream), "conv state reset"));
+    return GGB_OK;
+}
+
 }  // namespace
 
 #define GGB_LOCK(h) std::lock_guard<std::mutex> _lk((h)->mu); cudaSetDevice((h)->device)
@@ -289,6 +320,8 @@ int ggb_model_create(ggb_handle h, const ggb_model_desc* desc, ggb_model* out) {
     m->c = h; m->d = d;
     if (m->d.rope_scale == 0.0f) m->d.rope_scale = 1.0f;
     m->page = d.kv_page > 0 ? d.kv_page : 64;
+    m->conv_taps = d.conv_taps > 0 ? d.conv_taps : 3;          // lfm2.shortconv.l_cache, default as src/cli/main.cpp:2146-2147
+    if (m->conv_taps > 8) { delete m; return set_status(h, GGB_INVALID_PARAM, "model_create: at most 8 convolution taps"); }
     m->layers.resize(d.n_layer);
     *out = m;
     return GGB_OK;
@@ -306,7 +339,7 @@ void ggb_model_destroy(ggb_model m) {
         if (m->h_io) cudaFreeHost(m->h_io);
         if (m->h_logits) cudaFreeHost(m->h_logits);
         free_weight(m->tok_embd); free_weight(m->output);
-        for (Layer& l : m->layers) { free_weight(l.q); free_weight(l.k); free_weight(l.v); free_weight(l.o); free_weight(l.gate); free_weight(l.up); free_weight(l.down); }
+        for (Layer& l : m->layers) { free_weight(l.q); free_weight(l.k); free_weight(l.v); free_weight(l.o); free_weight(l.gate); free_weight(l.up); free_weight(l.down); free_weight(l.sc_in); free_weight(l.sc_out); }
     }
     delete m;
 }
@@ -382,6 +415,9 @@ int ggb_model_set_tensor(ggb_model m, int slot, int layer, uint32_t type, int64_
     case GGB_T_BIAS_V: return vec(&l.bv, kvd);
     case GGB_T_Q_NORM: return vec(&l.q_norm, d.head_dim);
     case GGB_T_K_NORM: return vec(&l.k_norm, d.head_dim);
+    case GGB_T_SC_IN_PROJ: return mat(&l.sc_in, 3 * static_cast<int64_t>(d.hidden), d.hidden);
+    case GGB_T_SC_OUT_PROJ: return mat(&l.sc_out, d.hidden, d.hidden);
+    case GGB_T_SC_CONV: return vec(&l.sc_conv, static_cast<int64_t>(d.hidden) * m->conv_taps);
     default: return set_status(c, GGB_NOT_FOUND, "set_tensor: unknown slot");
     }
 }
@@ -396,10 +432,15 @@ int ggb_model_finalize(ggb_model m) {
     if (c->tp_size > 1 && (!m->output || d.vocab % c->tp_size))
         return set_status(c, GGB_INVALID_PARAM, "finalize: a tensor-parallel shard needs its slice of the output matrix (vocab divisible by the group size)");
     for (const Layer& l : m->layers) {
-        if (!l.q || !l.k || !l.v || !l.o || !l.gate || !l.up || !l.down || !l.attn_norm || !l.ffn_norm)
+        // a layer carries the short convolution or attention, told apart by tensor presence (src/cli/main.cpp:2155-2164)
+        const bool mixer_ok = l.conv() ? (l.sc_out && l.sc_conv && !l.q && !l.k && !l.v && !l.o) : (l.q && l.k && l.v && l.o && !l.sc_out && !l.sc_conv);
+        if (!mixer_ok || !l.gate || !l.up || !l.down || !l.attn_norm || !l.ffn_norm)
             return set_status(c, GGB_INVALID_PARAM, "finalize: a layer tensor is missing");
         if (l.gate->w.type != l.up->w.type) return set_status(c, GGB_INVALID_PARAM, "finalize: ffn_gate and ffn_up must share a type");
+        m->has_conv = m->has_conv || l.conv();
     }
+    if (m->has_conv && (c->tp_size > 1 || m->n_seq > 1))
+        return set_status(c, GGB_INVALID_PARAM, "finalize: a model with short-convolution layers runs one sequence on one GPU");
     const int hd = d.head_dim, qd = d.n_head * hd, kvd = d.n_kv * hd;
     // RoPE table exactly as RopeCache::build (src/cli/main.cpp:665-692): float pow/cos/sin on the host.
     {
@@ -444,6 +485,12 @@ int ggb_model_finalize(ggb_model m) {
     M_TRY(dev_alloc(m, &m->v, T * kvd));
     M_TRY(dev_alloc(m, &m->att, T * qd));
     M_TRY(dev_alloc(m, &m->act, T * d.ffn));
+    if (m->has_conv) {
+        M_TRY(dev_alloc(m, &m->bcx, T * 3 * d.hidden));
+        M_TRY(dev_alloc(m, &m->yconv, T * d.hidden));
+        for (Layer& l : m->layers)
+            if (l.conv()) M_TRY(dev_alloc(m, &l.sc_state, static_cast<size_t>(std::max(m->conv_taps - 1, 1)) * d.hidden));
+    }
     m->tc_images = tensor_attn && d.hidden % 64 == 0 && d.ffn % 64 == 0;
     if (m->tc_images) M_TRY(dev_alloc(m, &m->act_img, gemm_tc_image_elems(m->chunk, d.ffn)));
     M_TRY(dev_alloc(m, &m->logits, static_cast<size_t>(d.vocab)));
@@ -472,12 +519,12 @@ int ggb_model_finalize(ggb_model m) {
     // 0.93 ms per step against 0.61 ms for the kernel-per-matrix graph (grid-wide barriers of ~2 us each, and a code
     // footprint of ~140 KB that is fetched anew in every phase), so the graph stays the default.
     {
-        bool ok = c->use_mma && c->tp_size == 1 && (hd == 64 || hd == 128) && m->page % 8 == 0 && getenv("GGB_STEP_KERNEL") != nullptr &&
+        bool ok = !m->has_conv && c->use_mma && c->tp_size == 1 && (hd == 64 || hd == 128) && m->page % 8 == 0 && getenv("GGB_STEP_KERNEL") != nullptr &&
                   d.hidden % 256 == 0 && d.ffn % 256 == 0 && qd % 256 == 0;
         const DeviceWeight* outw = m->output ? m->output : m->tok_embd;
         ok = ok && step_mat_ok(outw->w);
         for (const Layer& l : m->layers)
-            ok = ok && step_mat_ok(l.q->w) && step_mat_ok(l.k->w) && step_mat_ok(l.v->w) && step_mat_ok(l.o->w) && step_mat_ok(l.gate->w) &&
+            ok = ok && !l.conv() && step_mat_ok(l.q->w) && step_mat_ok(l.k->w) && step_mat_ok(l.v->w) && step_mat_ok(l.o->w) && step_mat_ok(l.gate->w) &&
                  step_mat_ok(l.up->w) && step_mat_ok(l.down->w) && l.gate->w.type == l.up->w.type && !l.bq && !l.bk && !l.bv && !l.q_norm && !l.k_norm;
         if (ok) {
             const int n_cta = c->sm_count;
@@ -560,6 +607,8 @@ int ggb_model_finalize(ggb_model m) {
     }
     M_TRY(cuda_status(c, cudaMemset(m->k_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
     M_TRY(cuda_status(c, cudaMemset(m->v_cache, 0, sizeof(__nv_bfloat16) * m->kv_layer_elems * d.n_layer), "kv memset"));
+    M_TRY(conv_reset(m, 0));              // the warm-up step advanced the convolution states
+    M_TRY(cuda_status(c, cudaStreamSynchronize(c->stream), "finalize"));
     m->finalized = true;
     return GGB_OK;
 }
@@ -570,6 +619,7 @@ int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int po
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "prefill: model not finalized");
     if (!host_tokens || n_tok <= 0 || pos0 < 0 || pos0 + n_tok > m->d.ctx) return set_status(c, GGB_INVALID_PARAM, "prefill: bad arguments");
     GGB_LOCK(c);
+    M_TRY(conv_reset(m, pos0));
     for (int t0 = 0; t0 < n_tok; t0 += m->chunk) {
         const int n = std::min(m->chunk, n_tok - t0);
         M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, host_tokens + t0, sizeof(int32_t) * n, cudaMemcpyHostToDevice, c->stream), "token upload"));
@@ -588,6 +638,7 @@ int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, in
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "decode: model not finalized");
     if (pos < 0 || pos >= m->d.ctx || token < 0 || token >= m->d.vocab) return set_status(c, GGB_INVALID_PARAM, "decode: token or position out of range");
     GGB_LOCK(c);
+    M_TRY(conv_reset(m, pos));
     m->h_io[0] = token; m->h_io[1] = pos;
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
@@ -615,6 +666,7 @@ int ggb_model_generate(ggb_model m, int32_t first_token, int pos0, int n, int32_
         return set_status(c, GGB_INVALID_PARAM, "generate: bad arguments");
     if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate: the device-resident loop runs on sequence 0 (use ggb_model_generate_batch for several)");
     GGB_LOCK(c);
+    M_TRY(conv_reset(m, pos0));
     m->h_io[0] = first_token; m->h_io[1] = pos0; m->h_io[3] = 0;
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_tokens, m->h_io, 4, cudaMemcpyHostToDevice, c->stream), "token upload"));
     M_TRY(cuda_status(c, cudaMemcpyAsync(m->d_pos, m->h_io + 1, 4, cudaMemcpyHostToDevice, c->stream), "pos upload"));
@@ -649,6 +701,8 @@ int ggb_model_generate_spec(ggb_model m, const int32_t* history, int n_history, 
     Context* c = m->c;
     if (!m->finalized) return set_status(c, GGB_INVALID_PARAM, "generate_spec: model not finalized");
     if (c->tp_size > 1) return set_status(c, GGB_INVALID_PARAM, "generate_spec: one GPU only");
+    // a rejected draft cannot be taken back out of a recurrent state; the reference keeps lfm2 off this path too (src/cli/main.cpp:2299-2301)
+    if (m->has_conv) return set_status(c, GGB_INVALID_PARAM, "generate_spec: not for models with short-convolution layers");
     if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate_spec: runs on sequence 0");
     if (!history || n_history < 1 || n <= 0 || pos0 < 0 || pos0 + n > m->d.ctx || !host_out)
         return set_status(c, GGB_INVALID_PARAM, "generate_spec: bad arguments");
@@ -705,6 +759,7 @@ int ggb_model_generate_sampled(ggb_model m, int32_t first_token, int pos0, int n
     if (m->cur_seq != 0) return set_status(c, GGB_INVALID_PARAM, "generate_sampled: runs on sequence 0");
     if (temp <= 0.0f) return ggb_model_generate(m, first_token, pos0, n, host_out);      // greedy (src/cli/main.cpp:828-837)
     GGB_LOCK(c);
+    M_TRY(conv_reset(m, pos0));
     if (!m->samp_scratch) {
         uint8_t* sc = nullptr;
         M_TRY(dev_alloc(m, &sc, sample_scratch_bytes(m->d.vocab)));
@@ -777,6 +832,7 @@ int check_batch(ggb_model m, const int32_t* tokens, const int32_t* pos, int n_se
     Context* c = m->c;
     auto fail = [&](const char* what) { return set_status(c, GGB_INVALID_PARAM, (std::string(who) + ": " + what).c_str()); };
     if (!m->finalized) return fail("model not finalized");
+    if (m->has_conv) return fail("not for models with short-convolution layers (one sequence, its state inside the model)");
     if (!tokens || !pos || n_seq < 1 || n_seq > m->n_seq) return fail("bad arguments (more sequences than ggb_model_set_sequences reserved?)");
     for (int r = 0; r < n_seq; ++r)
         if (tokens[r] < 0 || tokens[r] >= m->d.vocab || pos[r] < 0 || pos[r] + n_steps > m->d.ctx) return fail("token or position out of range");

@@ -294,6 +294,50 @@ int launch_argmax_rows(Context* c, const float* x, int n, int64_t ld, int rows, 
     return cuda_status(c, cudaGetLastError(), "argmax");
 }
 
+// ---- gated short convolution (lfm2) ---------------------------------------------------------------
+// src/cli/main.cpp:2704-2724, per channel: bx = B * x; acc = w[taps - 1] * bx + sum_k w[k] * state[k] (k ascending, the
+// products and sums rounded one by one as the reference's loop does); y = C * acc; the state drops its oldest value and
+// takes bx.  bcx [n_tok][3 hidden] = [B | C | x] rows of the in_proj output, conv_w [hidden][taps] (tap-contiguous),
+// state [taps - 1][hidden] oldest first.  One thread per channel walks the rows in order with the state in registers.
+template <int TAPS>
+__global__ void __launch_bounds__(128) shortconv_kernel(const float* __restrict__ bcx, const float* __restrict__ conv_w, float* __restrict__ state,
+                                                        float* __restrict__ y, int n_tok, int H) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int ch = blockIdx.x * 128 + threadIdx.x;
+    if (ch >= H) return;
+    float w[TAPS], st[TAPS > 1 ? TAPS - 1 : 1];
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) w[k] = conv_w[static_cast<size_t>(ch) * TAPS + k];
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) st[k] = state[static_cast<size_t>(k) * H + ch];
+    for (int t = 0; t < n_tok; ++t) {
+        const float* row = bcx + static_cast<size_t>(t) * 3 * H;
+        const float bx = __fmul_rn(row[ch], row[2 * H + ch]);
+        float acc = __fmul_rn(w[TAPS - 1], bx);
+#pragma unroll
+        for (int k = 0; k < TAPS - 1; ++k) acc = __fadd_rn(acc, __fmul_rn(w[k], st[k]));
+        y[static_cast<size_t>(t) * H + ch] = __fmul_rn(row[H + ch], acc);
+#pragma unroll
+        for (int k = 0; k < TAPS - 2; ++k) st[k] = st[k + 1];
+        if (TAPS > 1) st[TAPS - 2] = bx;
+    }
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) state[static_cast<size_t>(k) * H + ch] = st[k];
+}
+
+int launch_shortconv(Context* c, const float* bcx, const float* conv_w, float* state, float* y, int n_tok, int hidden, int taps, cudaStream_t s) {
+    const dim3 grid((hidden + 127) / 128), block(128);
+    cudaError_t e = cudaErrorInvalidValue;
+    switch (taps) {
+#define GGB_SC_CASE(T) case T: e = launch_pdl(c, shortconv_kernel<T>, grid, block, 0, s, bcx, conv_w, state, y, n_tok, hidden); break;
+        GGB_SC_CASE(1) GGB_SC_CASE(2) GGB_SC_CASE(3) GGB_SC_CASE(4) GGB_SC_CASE(5) GGB_SC_CASE(6) GGB_SC_CASE(7) GGB_SC_CASE(8)
+#undef GGB_SC_CASE
+    default: return set_status(c, GGB_INVALID_PARAM, "shortconv: 1 to 8 taps");
+    }
+    c->launches++;
+    return cuda_status(c, e, "shortconv");
+}
+
 // ---- gated attention (qwen35 full-attention layers) -----------------------------------------------
 // The attn_q projection emits, per query head, [query(hd) | gate(hd)] (src/cli/main.cpp:3054-3060).
 // qgate_split: q_out[h][i] = qg[h][i] (contiguous heads for the attention kernels; the gate stays in qg).

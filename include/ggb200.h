@@ -353,7 +353,17 @@ typedef struct ggb_model_desc {
     float rms_eps, rope_base, rope_scale;
     int rope_neox;   /* 1: split-half pairs (qwen3); 0: adjacent pairs (llama, qwen2) */
     int kv_page;     /* tokens per KV page; 0 = default (64) */
+    int conv_taps;   /* lfm2 only: taps of the gated short convolution (lfm2.shortconv.l_cache, src/cli/main.cpp:2146-2147);
+                        0 = the reference's default (3); at most 8 */
 } ggb_model_desc;
+/* lfm2 (src/cli/main.cpp:2145-2167, 2680-2856): a layer that is given GGB_T_SC_IN_PROJ / GGB_T_SC_OUT_PROJ / GGB_T_SC_CONV
+ * instead of the attention tensors runs the gated short convolution: [B | C | x] = in_proj(norm(h)); bx = B * x; y = C *
+ * (causal depthwise convolution over the last conv_taps values of bx); h += out_proj(y).  The layer's state (the previous
+ * conv_taps - 1 values of bx) lives in device memory and returns to zero whenever a call starts at position 0.  Attention
+ * layers take GGB_T_Q_NORM / GGB_T_K_NORM; the final norm (token_embd_norm) goes to GGB_T_OUTPUT_NORM.  rope_neox = 1 and
+ * rope_base = lfm2.rope.freq_base give the rotation the branch asks its backend for (:2250-2268); the reference's CPU
+ * backend ignores both (cpu_ref.cpp:158-174: adjacent pairs, base 10000), which rope_neox = 0, rope_base = 10000
+ * reproduces.  Such a model runs one sequence on one GPU; ggb_model_generate_spec refuses it as the reference does (:2299-2301). */
 /* On a handle that belongs to a tensor-parallel group of `size` ranks the description and the tensors
  * are those of ONE SHARD (Megatron-style): n_head, n_kv and ffn are the full model's divided by size;
  * attn_q/k/v, ffn_gate/up and their biases hold this rank's rows (column parallel); attn_output and
@@ -370,7 +380,9 @@ enum ggb_tensor_slot {
     GGB_T_TOKEN_EMBD = 0, GGB_T_OUTPUT = 1, GGB_T_OUTPUT_NORM = 2, GGB_T_ROPE_FREQS = 3,
     GGB_T_ATTN_NORM = 10, GGB_T_ATTN_Q = 11, GGB_T_ATTN_K = 12, GGB_T_ATTN_V = 13, GGB_T_ATTN_OUT = 14,
     GGB_T_FFN_NORM = 15, GGB_T_FFN_GATE = 16, GGB_T_FFN_UP = 17, GGB_T_FFN_DOWN = 18,
-    GGB_T_BIAS_Q = 19, GGB_T_BIAS_K = 20, GGB_T_BIAS_V = 21, GGB_T_Q_NORM = 22, GGB_T_K_NORM = 23
+    GGB_T_BIAS_Q = 19, GGB_T_BIAS_K = 20, GGB_T_BIAS_V = 21, GGB_T_Q_NORM = 22, GGB_T_K_NORM = 23,
+    /* lfm2 short-convolution layers: in_proj [3 hidden][hidden], out_proj [hidden][hidden], conv F32 [hidden][conv_taps] */
+    GGB_T_SC_IN_PROJ = 24, GGB_T_SC_OUT_PROJ = 25, GGB_T_SC_CONV = 26
 };
 
 GGB_API int ggb_model_create(ggb_handle h, const ggb_model_desc* desc, ggb_model* out);
