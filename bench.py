@@ -411,6 +411,10 @@ def run_ours(args):
                 extras["config3"] = config3_figures(b, local)
             except Exception as e:
                 extras["config3"] = {"unavailable": str(e)[:200]}
+            try:
+                extras["lfm2"] = lfm2_figures(b, local)
+            except Exception as e:
+                extras["lfm2"] = {"unavailable": str(e)[:200]}
     b.close()
     if not args.no_extras and world == 1:
         # the 8B-shape model on one GPU: 4096-token prompt, decode at batch 1 and at batch 16
@@ -814,18 +818,16 @@ def run_tp(args):
         dist.destroy_process_group()
 
 
-def config3_figures(b, local, n_layer=0):
-    """Qwen2.5-1.5B shape, every matrix Q8_0 (28 layers, QKV bias, head_dim 128): prefill of 2048 random tokens, then 128
-    greedy decode tokens, on one GPU.  Returns {"decode": ..., "prefill": ...}."""
-    import dataclasses
+def model_figures(b, local, cfg, workload, n_prompt, n_decode=128):
+    """Prefill of n_prompt random tokens, then n_decode greedy decode tokens of a random-init model of shape cfg, on one
+    GPU, timed with CUDA events on the library's stream.  Returns {"workload", "decode", "prefill"}."""
     import torch
     from ggnpu_b200.backend import Model
-    cfg = dataclasses.replace(S.QWEN25_1P5B, ctx=2048 + 128 + 16, n_layer=n_layer or S.QWEN25_1P5B.n_layer)
     synth = S.build_model(cfg, device="cuda")
     model = Model(b, cfg, synth.tensors)
     del synth
     stream = torch.cuda.ExternalStream(b.stream(), device=torch.device("cuda", local))
-    ids = prompt_ids(cfg, 2048)
+    ids = prompt_ids(cfg, n_prompt)
     model.prefill(ids, 0, want_logits=False)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -834,21 +836,38 @@ def config3_figures(b, local, n_layer=0):
     e1.record(stream)
     torch.cuda.synchronize()
     prefill_ms = e0.elapsed_time(e1)
-    toks = model.generate(int(first), 2048, 8)
+    toks = model.generate(int(first), n_prompt, 8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record(stream)
-    toks = model.generate(int(toks[-1]), 2056, 128)
+    toks = model.generate(int(toks[-1]), n_prompt + 8, n_decode)
     e1.record(stream)
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / 128
+    ms = e0.elapsed_time(e1) / n_decode
     peak, peak_kind = peaks()
-    bytes_step = model.decode_bytes(2056 + 64)
+    bytes_step = model.decode_bytes(n_prompt + 8 + n_decode // 2)
     model.close()
-    return {"workload": "qwen2.5-1.5b shape, all Q8_0, 28 layers, QKV bias: 2048-token prefill then 128 greedy decode tokens",
+    return {"workload": workload,
             "decode": {"tok_per_s": 1000.0 / ms, "ms_per_step": ms, "algorithmic_bytes": bytes_step,
                        "achieved_gbs": bytes_step / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": bytes_step / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_kind},
-            "prefill": {"tokens": 2048, "tok_per_s": 2048 / (prefill_ms * 1e-3), "ms": prefill_ms}}
+            "prefill": {"tokens": n_prompt, "tok_per_s": n_prompt / (prefill_ms * 1e-3), "ms": prefill_ms}}
+
+
+def config3_figures(b, local, n_layer=0):
+    """Qwen2.5-1.5B shape, every matrix Q8_0 (28 layers, QKV bias, head_dim 128): prefill of 2048 random tokens, then 128
+    greedy decode tokens, on one GPU."""
+    import dataclasses
+    cfg = dataclasses.replace(S.QWEN25_1P5B, ctx=2048 + 128 + 16, n_layer=n_layer or S.QWEN25_1P5B.n_layer)
+    return model_figures(b, local, cfg, "qwen2.5-1.5b shape, all Q8_0, 28 layers, QKV bias: 2048-token prefill then 128 greedy decode tokens", 2048)
+
+
+def lfm2_figures(b, local):
+    """An lfm2 shape of about 1.2 B parameters (16 layers: 10 gated short-convolution, 6 GQA attention with QK-norm; hidden
+    2048, FFN 8192, vocab 65536, Q4_K / Q6_K): prefill of 512 random tokens, then 128 greedy decode tokens, on one GPU."""
+    import dataclasses
+    cfg = dataclasses.replace(S.LFM2_1P2B, ctx=512 + 128 + 16)
+    return model_figures(b, local, cfg, "lfm2 shape (~1.2 B: 10 short-convolution + 6 attention layers, hidden 2048, FFN 8192, vocab 65536), "
+                         "Q4_K / Q6_K: 512-token prefill then 128 greedy decode tokens", 512)
 
 
 def run_config5(args):
@@ -955,6 +974,7 @@ def main():
     ap.add_argument("--tp-layers", type=int, default=0, help="layers to build (0 = all 32)")
     ap.add_argument("--config5", action="store_true", help="qwen35moe-shape decode benchmark (expert parallel under torchrun)")
     ap.add_argument("--config3", action="store_true", help="Qwen2.5-1.5B shape, all Q8_0: 2048-token prefill and 128 decode tokens on one GPU")
+    ap.add_argument("--lfm2", action="store_true", help="lfm2 shape (~1.2 B, short-convolution + attention layers): 512-token prefill and 128 decode tokens on one GPU")
     ap.add_argument("--c3-layers", type=int, default=0, help="layers to build for --config3 (0 = all 28; fewer for profiling)")
     ap.add_argument("--q35-layers", type=int, default=40)
     ap.add_argument("--q35-prompt", type=int, default=128)
@@ -973,6 +993,12 @@ def main():
         from ggnpu_b200.backend import CudaBackend
         b = CudaBackend(0)
         print(json.dumps({"config3": config3_figures(b, 0, args.c3_layers)}), flush=True)
+        b.close()
+        return
+    if args.lfm2:
+        from ggnpu_b200.backend import CudaBackend
+        b = CudaBackend(0)
+        print(json.dumps({"lfm2": lfm2_figures(b, 0)}), flush=True)
         b.close()
         return
     if args.config5:

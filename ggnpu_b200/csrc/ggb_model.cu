@@ -941,9 +941,14 @@ uint64_t ggb_model_decode_bytes(ggb_model m, int pos) {
         return static_cast<uint64_t>(w->w.N) * w->w.nb * f.block_bytes;
     };
     uint64_t b = wb(m->output ? m->output : m->tok_embd);
-    for (const Layer& l : m->layers) b += wb(l.q) + wb(l.k) + wb(l.v) + wb(l.o) + wb(l.gate) + wb(l.up) + wb(l.down);
+    int n_attn = 0;
+    for (const Layer& l : m->layers) {
+        b += wb(l.q) + wb(l.k) + wb(l.v) + wb(l.o) + wb(l.gate) + wb(l.up) + wb(l.down) + wb(l.sc_in) + wb(l.sc_out);
+        if (l.conv()) b += static_cast<uint64_t>(d.hidden) * 4 * (m->conv_taps + 2 * (m->conv_taps - 1));   // taps, state read and written
+        else ++n_attn;
+    }
     b += static_cast<uint64_t>(d.hidden) * 4 * (2 * d.n_layer + 1);                        // norm gammas
-    b += static_cast<uint64_t>(2) * d.n_layer * (pos + 1) * d.n_kv * d.head_dim * 2;       // K and V read, bf16
+    b += static_cast<uint64_t>(2) * n_attn * (pos + 1) * d.n_kv * d.head_dim * 2;          // K and V read, bf16
     const FormatInfo fe = format_info(m->tok_embd->w.type);
     b += static_cast<uint64_t>(m->tok_embd->w.nb) * fe.block_bytes;                        // one embedding row
     return b;

@@ -64,6 +64,9 @@ LLAMA_1B = ModelConfig()
 QWEN25_1P5B = ModelConfig(arch="qwen2", n_layer=28, hidden=1536, n_head=12, n_kv=2, head_dim=128, ffn=8960,
                           vocab=151936, rope_base=1e6, qkv_bias=True, tied=True, wtype=Q8_0, wtype_alt=Q8_0,
                           rms_eps=1e-6)
+# an lfm2 shape of about 1.2 B parameters: 10 gated short-convolution layers (3 taps) around 6 GQA attention layers
+LFM2_1P2B = ModelConfig(arch="lfm2", n_layer=16, hidden=2048, n_head=32, n_kv=8, head_dim=64, ffn=8192, vocab=65536,
+                        rope_base=1e6, qk_norm=True, conv_layers=(0, 1, 3, 4, 6, 7, 9, 11, 13, 15), d_conv=3)
 LLAMA_8B = ModelConfig(n_layer=32, hidden=4096, n_head=32, n_kv=8, head_dim=128, ffn=14336, vocab=128256,
                        tied=False, out_type=Q6_K)
 
