@@ -261,7 +261,7 @@ def run_ours(args):
     bytes_step = model.decode_bytes(max(PROMPT_LEN, pos - K // 2))
 
     # ---- e2e: host buffers through ggb_model_decode ----
-    logits = np.empty(cfg.vocab, dtype=np.float32)
+    logits = torch.empty(cfg.vocab, dtype=torch.float32, pin_memory=True).numpy()      # page-locked: the library copies straight into it
     tok = first
     for i in range(min(W, 3)):
         pos = pos if pos < cfg.ctx else PROMPT_LEN

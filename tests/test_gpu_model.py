@@ -115,6 +115,25 @@ def test_device_feedback_loop_equals_host_loop(backend):
     gm2.close()
 
 
+def test_decode_into_page_locked_and_pageable_buffers(backend):
+    """ggb_model_decode copies the logits straight into a caller's page-locked buffer and through its own staging buffer
+    into any other: the same bits either way."""
+    import torch
+    from ggnpu_b200.backend import Model
+    cfg = S.tiny_config(seed=23)
+    synth = S.build_model(cfg)
+    gm = Model(backend, cfg, synth.tensors)
+    ids = np.random.default_rng(2).integers(0, cfg.vocab, 6).astype(np.int32)
+    _, tok = gm.prefill(ids, 0)
+    pinned = torch.empty(cfg.vocab, dtype=torch.float32, pin_memory=True).numpy()
+    pinned[:] = -1.0
+    pageable = np.full(cfg.vocab, -2.0, dtype=np.float32)
+    _, n1 = gm.decode(tok, 6, logits_out=pinned)
+    _, n2 = gm.decode(tok, 6, logits_out=pageable)
+    assert n1 == n2 and np.array_equal(pinned.view(np.uint32), pageable.view(np.uint32))
+    gm.close()
+
+
 def test_reference_cli_greedy_stream(backend, cli_vectors):
     """Against the unmodified reference CLI's recorded output (tests/golden/ref_cli.npz): its top-10
     logits after the prompt, and its greedy continuation where margins allow."""
