@@ -170,6 +170,13 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(AttnPagedArgs a) {
     pdl_sync();
     attn_tile_body<HD, false>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, sm_u, [] { __syncthreads(); });
 }
+// The same with the query heads of a KV head dealt to a.head_split CTAs (grid.x = n_kv * head_split).
+template <int HD>
+__global__ void __launch_bounds__(128) attn_tile_split_kernel(AttnPagedArgs a) {
+    extern __shared__ __align__(16) uint32_t sm_u[];
+    pdl_sync();
+    attn_tile_body<HD, false, true>(a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x, sm_u, [] { __syncthreads(); });
+}
 
 // grid (n_head, n_tok), 1024 threads: merge the visible splits, normalise, write out[t][head][hd].  The splits' (max, sum)
 // pairs are fetched by one thread each and the weights exp(max_s - max) kept in shared memory; the sum over splits of
@@ -245,8 +252,9 @@ int launch_attn_paged(Context* c, const AttnPagedArgs& a_in, int n_tok, cudaStre
 #define GGB_ATTN_CASE(HD)                                                                                              \
     {                                                                                                                  \
         smem = attn_tile_smem(HD);                                                                                     \
-        e = ensure_dynamic_smem(c, attn_tile_kernel<HD>, smem);                                                        \
-        if (e == cudaSuccess) e = launch_pdl(c, attn_tile_kernel<HD>, grid, dim3(128), smem, s, a);                     \
+        void (*kern)(AttnPagedArgs) = a.head_split > 1 ? attn_tile_split_kernel<HD> : attn_tile_kernel<HD>;            \
+        e = ensure_dynamic_smem(c, kern, smem);                                                                        \
+        if (e == cudaSuccess) e = launch_pdl(c, kern, grid, dim3(128), smem, s, a);                                     \
     }
     if (hd == 64) GGB_ATTN_CASE(64)
     else if (hd == 128) GGB_ATTN_CASE(128)

@@ -29,7 +29,7 @@ constexpr size_t attn_tile_smem(int HD) {
 // chunks of 64: the chunk's K and V rows are first copied into shared memory with every 16-byte load in flight at
 // once, then scores, an online softmax and P*V run out of shared memory in fp32.  With a.fuse (single-token decode)
 // the body also rotates q and the new key, and the split that contains pos stores the new key and value.
-template <int HD, bool COHERENT, class Sync>
+template <int HD, bool COHERENT, bool HSPLIT = false, class Sync>
 __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int hx, const int split, const int t, const int tid,
                                                uint32_t* sm_u, Sync sync) {
     constexpr int KW = HD / 2;           // 32-bit words (bf16 pairs) per K or V row
@@ -37,12 +37,15 @@ __device__ __forceinline__ void attn_tile_body(const AttnPagedArgs& a, const int
     constexpr int TK = 64;               // keys per chunk
     constexpr int NP = (8 * KW + 127) / 128;   // (head, dim pair) items per thread in P*V
     const int lane = tid & 31, warp = tid >> 5;
-    // hx = KV head * head_split + part: with head_split > 1 the query heads that share a KV head are dealt to several CTAs
-    // (models with one or two KV heads would otherwise fill a fraction of the SMs)
-    const int hs = a.head_split > 1 ? a.head_split : 1;
-    const int h = hx / hs, hpart = hx - h * hs;
-    const int G = (a.n_head / a.n_kv) / hs;                                   // query heads of this CTA
-    const size_t head0 = static_cast<size_t>(h) * (a.n_head / a.n_kv) + static_cast<size_t>(hpart) * G;      // the first of them
+    // HSPLIT: hx = KV head * head_split + part, the query heads that share a KV head are dealt to several CTAs (models
+    // with one or two KV heads would otherwise fill a fraction of the SMs).  It is a template parameter because the
+    // general form, compiled into the one-CTA-per-KV-head kernel, made that kernel slower (a 16-sequence step of the
+    // 8B shape: 12.4 ms against 10.9) although it computes the same values there.
+    const int hs = HSPLIT ? max(a.head_split, 1) : 1;
+    const int h = HSPLIT ? hx / hs : hx, hpart = HSPLIT ? hx - h * hs : 0;
+    const int G = HSPLIT ? (a.n_head / a.n_kv) / hs : a.n_head / a.n_kv;      // query heads of this CTA
+    const size_t head0 = HSPLIT ? static_cast<size_t>(h) * (a.n_head / a.n_kv) + static_cast<size_t>(hpart) * G
+                                : static_cast<size_t>(h) * G;                 // the first of them
     // Fused step: the values the rotation below needs (the G query heads and the new key) do not depend
     // on the position, so their loads are issued before the position is looked at; the position's own
     // round trip to memory then overlaps theirs instead of preceding it.
