@@ -400,7 +400,9 @@ GGB_API int ggb_model_finalize(ggb_model m);
 /* Forward over n_tok prompt tokens at positions pos0.. (writes KV); logits of the LAST row to
  * host_logits (may be NULL), greedy token to *next_token (may be NULL). */
 GGB_API int ggb_model_prefill(ggb_model m, const int32_t* host_tokens, int n_tok, int pos0, float* host_logits, int32_t* next_token);
-/* One decode step from host buffers: token in, logits (optional) and greedy next token out. */
+/* One decode step from host buffers: token in, logits (optional) and greedy next token out.  A host_logits buffer in
+ * page-locked memory (cudaHostAlloc / cudaHostRegister) receives the device copy directly; any other buffer is filled
+ * through the model's own page-locked staging buffer and one host copy. */
 GGB_API int ggb_model_decode(ggb_model m, int32_t token, int pos, float* host_logits, int32_t* next_token);
 /* n greedy decode steps with the token fed back on the device (no host round trip inside);
  * the n generated ids land in host_out afterwards. */
