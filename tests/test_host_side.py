@@ -130,3 +130,31 @@ def test_pack_cache_key_and_file_round_trip(tmp_path):
     open(path, "wb").write(raw + b"x")
     assert L.ggb_pack_file_read(path, 12, 64, 512, 777, *args) == 1                      # trailing bytes
     assert not [f for f in os.listdir(tmp_path) if ".tmp." in f]                        # written through a temporary name
+
+
+def test_model_description_mirror_and_lfm2_tensor_names():
+    """The ctypes mirror of ggb_model_desc has the header's fields in the header's order (the library reads it by
+    offset), and every tensor an lfm2 model carries has a slot in the generic graph."""
+    import re
+    from ggnpu_b200 import backend as B
+    hdr = open(os.path.join(ROOT, "include", "ggb200.h")).read()
+    body = hdr[hdr.index("typedef struct ggb_model_desc {"):hdr.index("} ggb_model_desc;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for decl in body.split("{", 1)[1].split(";"):
+        decl = decl.strip()
+        if decl:
+            names += [n.strip() for n in decl.split(None, 1)[1].split(",")]
+    assert names == [f[0] for f in B.ModelDesc._fields_]
+    cfg = S.tiny_config(**S.LFM2_CASES["lfm2"])
+    m = S.build_model(cfg)
+    conv = attn = 0
+    for name in m.tensors:
+        if name in B._SLOTS:
+            continue
+        blk, layer, rest = name.split(".", 2)
+        assert blk == "blk" and rest in B._LAYER_SLOTS, name
+        conv += rest == "shortconv.conv.weight"
+        attn += rest == "attn_q.weight"
+    assert conv == len(cfg.conv_layers) and attn == cfg.n_layer - conv
+    assert m.kv()["lfm2.shortconv.l_cache"] == cfg.d_conv and "token_embd_norm.weight" in m.tensors
